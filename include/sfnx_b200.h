@@ -1,0 +1,178 @@
+/* sfnx_b200 - C ABI of the B200 (sm_100a) verify-window kernels.
+ *
+ * A drop-in for the host<->kernel boundary of johnfink8/sfnx (src/kernels.hpp, namespace fnx): the same launch
+ * wrappers, with the model's shapes as run-time arguments instead of compile-time constants, plain pointers and
+ * sizes, an int status instead of exceptions, and no C++ types in the signatures.
+ *
+ * Conventions (as the reference's, src/kernels.hpp:1-2 and 36-49):
+ *  - every pointer is device memory unless its comment says "host"; `st` is a cudaStream_t; all launches are
+ *    asynchronous on `st`, allocate nothing, read no device data on the host and may be captured into a CUDA graph
+ *    (per-window values such as the position, the job count and the history parity live in device memory);
+ *  - activations are f32 rows, one row per window row (or per routed pair); quantised activations are q8_1 rows
+ *    (36-byte blocks of 32: f16 d, f16 sum, 32 int8);
+ *  - the return value is 0, or non-zero after a refused argument or a failed launch, with the text in
+ *    fnx_last_error() (the reference throws std::runtime_error with the same kind of text);
+ *  - device-side faults never trap: kernels OR bits into a caller-supplied `unsigned* err` word
+ *    (bit 16: a non-finite logit; reference src/kernels.hpp:329-332) and run to completion.
+ */
+#ifndef SFNX_B200_H
+#define SFNX_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FNX_MAXT 16   /* rows per window (reference src/model.hpp:45) */
+#define FNX_TOPK_N 64 /* sampler candidates per row (reference src/kernels.hpp:392) */
+#define FNX_HS 128    /* DeltaNet head size (reference src/model.hpp:42) */
+
+/* one matrix (an expert's) applied to up to FNX_MAXT activation rows: reference src/kernels.hpp:18-23 (Job) */
+typedef struct FnxJob {
+    int w;             /* expert */
+    int n;             /* rows of the job */
+    int y[FNX_MAXT];   /* activation rows */
+    int out[FNX_MAXT]; /* output rows */
+} FnxJob;
+
+/* a Q8_0 matrix in the split layout: int8 values [rows][cols], f16 scales [rows][cols / 32]
+ * (reference src/model.hpp:71-87, Q8S) */
+typedef struct FnxQ8S {
+    const int8_t* q;
+    const uint16_t* d;
+} FnxQ8S;
+
+/* the routed experts' matrices of one projection (reference src/moe_w.cuh:2-9 MoeW, src/model.hpp DW):
+ *  type FNX_Q4_K: GGUF Q4_K rows (144-byte super-blocks), expert e at a + e * stride bytes;
+ *  type FNX_Q8_0: split layout, expert e's values at a + e * stride, its scales at b + e * stride_b;
+ *  type FNX_Q6_K: Q6_K regrouped in 32-column units (fnx_repack_q6k_units): planes QL a (16 B a unit), QH b (8 B),
+ *                 SC c (2 B), D d (f16), expert e at unit index e * stride */
+enum { FNX_Q4_K = 12, FNX_Q6_K = 14, FNX_Q8_0 = 8 }; /* GGUF type numbers */
+typedef struct FnxExperts {
+    int type;
+    int nrows, ncols;
+    const void *a, *b, *c, *d;
+    size_t stride, stride_b;
+} FnxExperts;
+
+/* the paged K/V pool of one layer on this GPU: reference src/kernels.hpp:160-165 (KvPages); pt null: local rows
+ * are contiguous */
+typedef struct FnxKvPages {
+    const int* pt; /* device: logical page -> physical page */
+    size_t page;   /* halves per page */
+    int rows;      /* local rows per page */
+} FnxKvPages;
+
+/* unscaled rotary: reference src/rope.hpp:22-27 (Rope, base only) */
+typedef struct FnxRope {
+    float base;
+    int nrot;
+} FnxRope;
+
+/* device-to-device copy job: reference src/kernels.hpp:375-379 (CopyJob) */
+typedef struct FnxCopyJob {
+    void* dst;
+    const void* src;
+    size_t bytes;
+} FnxCopyJob;
+
+const char* fnx_last_error(void);
+/* the compute capability the library was built for (100) and whether the current device matches it */
+int fnx_built_arch(void);
+
+/* ---- activations */
+/* reference src/kernels.hpp:36 quantize_q8_1 (src/kernels.cu:99-113): f32 rows of n -> q8_1 rows */
+int fnx_quantize_q8_1(const float* x, void* q, int n, int rows, void* st);
+/* reference src/kernels.hpp:359 rms_norm_rows (src/kernels.cu:2199-2206): y = x / sqrt(mean(x^2) + eps) * w.
+ * With add: x += add first (the residual update of the previous half), written back to x.  With q: y also as
+ * q8_1 rows (the reference's hc_read hands both forms to the layer, src/kernels.hpp:64-66) */
+int fnx_rms_norm_rows(float* x, const float* add, const float* w, float* y, void* q, int rows, int n, float eps, void* st);
+
+/* ---- dense projections */
+/* reference src/kernels.hpp:47 q8s_gemv (src/dense.cuh:24-160): out[t][r] = W[r] . y[t], T <= FNX_MAXT */
+int fnx_q8s_gemv(FnxQ8S w, int rows, int cols, const void* y, float* out, int out_stride, int T, void* st);
+/* reference src/kernels.hpp:49 gemv_f32 (src/kernels.cu:184-227, the block-per-row form): y[t][r] = W[r] . x[t] */
+int fnx_gemv_f32(const float* W, const float* x, float* y, int rows, int n, int T, void* st);
+
+/* ---- routed experts */
+/* reference src/kernels.hpp:276-278 router_route (src/moe.cuh:73-202): logits [T][nexp + 1] = W . x, top-k per row
+ * by logit (ties: lower index), weights = softmax over the picks, one job per distinct expert numbered by first
+ * pick; njobs[0] = the count.  scratch: fnx_router_scratch_bytes() bytes, zeroed once */
+size_t fnx_router_scratch_bytes(void);
+int fnx_router_route(const float* W, const float* x, float* logits, int T, int n, int nexp, int topk, int* topi, float* topw,
+                     FnxJob* jobs_gu, FnxJob* jobs_dn, int* njobs, void* scratch, void* st);
+/* reference src/kernels.hpp:281-282 moe_gate_up (src/moe_q4k.cuh:91-154; src/moe.cuh:258-272): gu[out][2 ffs] =
+ * [gate | up] rows of each job's expert over its q8_1 rows of xq (rows of A.ncols) */
+int fnx_moe_gate_up(const FnxExperts* A, const FnxJob* jobs, const int* njobs, int njobs_max, const void* xq, float* gu, void* st);
+/* reference src/kernels.hpp:305 moe_down (src/moe.cuh:284-345): part[out][n] from h = silu(gate) * up of the gu rows.
+ * hq: fnx_moe_h_bytes(pairs, ffs) bytes of scratch for the pairs' quantised h (the reference keeps it in a
+ * __device__ global, src/moe.cuh:281) */
+size_t fnx_moe_h_bytes(int pairs, int ffs);
+int fnx_moe_down(const FnxExperts* A, const FnxJob* jobs, const int* njobs, int njobs_max, const float* gu, int npairs, void* hq,
+                 float* part, void* st);
+/* reference src/kernels.hpp:307 swiglu_stacked_q8_1 + src/dense.cuh:162-198 (the shared expert): T rows of
+ * [gate | up] -> h as int8 + f16-rounded scales, then the Q8_0 down into out[t][n] */
+int fnx_shared_expert(FnxQ8S gate_up, FnxQ8S down, const void* xq, int T, int n, int ffs, float* sh_gu, void* hq, float* out,
+                      void* st);
+/* reference src/kernels.hpp:77 moe_combine / 308-313 RingMoe (src/kernels.cu:797-803): out[t] = sum_k topw[t][k]
+ * part[t topk + k] + sigmoid(logits[t][nexp]) sh[t] */
+int fnx_moe_combine(const float* part, const float* topw, const float* sh, const float* logits, int nexp, float* out, int T,
+                    int n, int topk, void* st);
+
+/* ---- Gated DeltaNet */
+/* reference src/kernels.hpp:90-93 gdn_scratch_floats, gdn_core (src/gdn_core.cuh:17-229).  scratch zeroed once. */
+size_t fnx_gdn_scratch_floats(int nv);
+int fnx_gdn_core(const float* qkvz, const float* ab, float* hist, const float* convw, const float* dt, const float* a,
+                 const float* nw, float* S, void* yq, const int* ctl, float* scratch, float* snap, float* hsnap, int nk, int nv,
+                 const int* vmap, int T, float eps, void* st, float* y32);
+/* reference src/kernels.hpp:380 copy_many (src/kernels.cu:1473-1485): the rollback's batched copies */
+int fnx_copy_many(const FnxCopyJob* jobs, int n, void* st);
+
+/* ---- attention */
+/* reference src/kernels.hpp:262 kv_rows_per_card */
+int fnx_kv_rows_per_card(int n_ctx, int ncard);
+/* reference src/kernels.hpp:251-252 attn_prep_append (src/kernels.cu:1539-1569) */
+int fnx_attn_prep_append(float* qg, float* k, const float* v, const float* q_norm, const float* k_norm, uint16_t* kc, uint16_t* vc,
+                         FnxKvPages g, int card, int ncard, int T, const int* pos0, float eps, FnxRope rope, int nq, int nkv,
+                         int hd, void* st);
+/* reference src/kernels.hpp:125 attn_scratch_floats, 230-236 attn / attn_part_lanes / attn_finish
+ * (src/kernels.cu:497-691).  fnx_attn_partial leaves this GPU's partial per (row, head) in part
+ * [T][nq][hd + 2] (acc, m, z); fnx_attn_finish merges nparts partials (this GPU's and the peers', gathered by the
+ * caller, parts[p] at parts + p * T * nq * (hd + 2)) in ring order for heads [h0, h0 + nh) and applies the gate */
+size_t fnx_attn_scratch_floats(int nq, int hd, int T);
+int fnx_attn_partial(const float* qg, const uint16_t* kc, const uint16_t* vc, FnxKvPages g, float* part, int card, int ncard, int T,
+                     const int* pos0, int nq, int nkv, int hd, float* scratch, void* st);
+int fnx_attn_finish(const float* parts, int nparts, int first_part, const float* qg, float* out, int T, int nq, int h0, int nh,
+                    int hd, void* st);
+
+/* ---- head */
+/* reference src/kernels.hpp:384 argmax (src/kernels.cu:870-908); keys: FNX_MAXT words zeroed once */
+int fnx_argmax(const float* logits, int rows, int T, int v0, float* best_v, int* best_i, unsigned long long* keys, unsigned* err,
+               void* st);
+/* reference src/kernels.hpp:387 penalize_row (src/kernels.cu:1454-1470) */
+int fnx_penalize_row(float* row, int n, const int* pen, const float* par, void* st);
+/* reference src/kernels.hpp:393-394 top_tokens (src/topk.cuh:17-138) */
+int fnx_top_tokens(float* logits, int n, int T, int v0, const int* pen_tok, const int* pen_cnt, const int* pen_n, int pen_stride,
+                   const float* pen_par, float* out_v, int* out_i, unsigned* err, void* st);
+
+/* ---- load-time repacks (the reference's loader does the same kind of work, src/model.cpp:554-606) */
+/* GGUF Q8_0 blocks [rows][cols / 32] -> split layout */
+int fnx_repack_q8_0_split(const void* blocks, int8_t* q, uint16_t* d, size_t rows, size_t cols, void* st);
+/* GGUF Q6_K rows of src_cols -> 32-column units of columns [c0, c0 + cols): the same bytes regrouped so that the
+ * FF width can be cut at any multiple of 32 */
+int fnx_repack_q6k_units(const void* blocks, size_t rows, size_t src_cols, size_t c0, size_t cols, void* QL, void* QH, void* SC,
+                         void* D, void* st);
+
+/* ---- synthetic weights: counter-based N(0, sigma) values quantised on the device (seeded, reproducible) */
+int fnx_synth_normal(float* out, size_t n, float sigma, unsigned long long seed, void* st);
+int fnx_synth_quant(int type, void* blocks, size_t nvalues, float sigma, unsigned long long seed, void* st);
+
+/* element-wise probes of the kernels' exact math (tests): op 0 exp, 1 log1p, 2 sigmoid, 3 silu, 4 rsqrt, 5 sin, 6 cos */
+int fnx_math_probe(int op, const float* x, float* y, size_t n, void* st);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,201 @@
+// Dense projections of the verify window: split-layout Q8_0 matrix x up to 16 quantised activation rows (output head,
+// qkvz, wq/wk/wv/wo, ssm_out, the shared expert), and the small f32 GEMV (alpha/beta).  Replaces reference
+// src/dense.cuh and src/kernels.cu:184-227 with the same order of every sum: a lane takes 16 columns at
+// c = 16 lane + 512 k, acc = fma(dw da, (float) isum16, acc) in ascending k, lanes combined by xor 16..1.
+#include "common.cuh"
+#include "exact_math.cuh"
+
+namespace fnxk {
+
+constexpr int Q8S_THREADS = 256, Q8S_R = 4;
+
+__device__ __forceinline__ uint4 ldg_stream16(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+
+// activations into shared memory as an int8 plane [T][cols] and float scales [T][cols / 32]: from q8_1 rows (yq), or
+// from planes already in that form (pq, pd)
+__device__ __forceinline__ void stage_act(int8_t* sq, float* sd, const uint8_t* __restrict__ yq, const int8_t* __restrict__ pq,
+                                          const float* __restrict__ pd, int T, int cols) {
+    const int nb = cols / 32;
+    if (yq) {
+        for (int it = threadIdx.x; it < T * nb; it += blockDim.x) {
+            const unsigned* src = reinterpret_cast<const unsigned*>(yq + (size_t) it * 36);
+            unsigned w[9];
+#pragma unroll
+            for (int k = 0; k < 9; ++k) w[k] = src[k];
+            uint4* dst = reinterpret_cast<uint4*>(sq + (size_t) it * 32);
+            dst[0] = make_uint4(w[1], w[2], w[3], w[4]);
+            dst[1] = make_uint4(w[5], w[6], w[7], w[8]);
+            sd[it] = h2f((uint16_t) (w[0] & 0xffff));
+        }
+    } else {
+        for (int it = threadIdx.x; it < T * cols / 16; it += blockDim.x)
+            reinterpret_cast<uint4*>(sq)[it] = reinterpret_cast<const uint4*>(pq)[it];
+        for (int it = threadIdx.x; it < T * nb; it += blockDim.x) sd[it] = pd[it];
+    }
+}
+
+// rows [row0, row0 + Q8S_R) of one warp against the staged activations; out[t * out_stride + row]
+template <int TT>
+__device__ __forceinline__ void q8s_rows(const int8_t* __restrict__ wq, const uint16_t* __restrict__ wd, int rows, int cols, int row0,
+                                         const int8_t* sq, const float* sd, int T, float* __restrict__ out, int out_stride) {
+    const int lane = threadIdx.x & 31, nb = cols / 32;
+    float acc[Q8S_R][TT];
+#pragma unroll
+    for (int r = 0; r < Q8S_R; ++r)
+#pragma unroll
+        for (int t = 0; t < TT; ++t) acc[r][t] = 0.f;
+#pragma unroll 2
+    for (int c = lane * 16; c < cols; c += 512) {
+        const int b = c >> 5;
+        uint4 w[Q8S_R];
+        float dw[Q8S_R];
+#pragma unroll
+        for (int r = 0; r < Q8S_R; ++r) {
+            const size_t row = (size_t) min(row0 + r, rows - 1);
+            w[r] = ldg_stream16(wq + row * cols + c);
+            dw[r] = h2f(__ldg(wd + row * nb + b));
+        }
+#pragma unroll
+        for (int t = 0; t < TT; ++t) {
+            if (t >= T) break;
+            const uint4 a = *reinterpret_cast<const uint4*>(sq + (size_t) t * cols + c);
+            const float da = sd[t * nb + b];
+#pragma unroll
+            for (int r = 0; r < Q8S_R; ++r) {
+                int s = __dp4a((int) w[r].x, (int) a.x, 0);
+                s = __dp4a((int) w[r].y, (int) a.y, s);
+                s = __dp4a((int) w[r].z, (int) a.z, s);
+                s = __dp4a((int) w[r].w, (int) a.w, s);
+                acc[r][t] = ffma(fmul(dw[r], da), (float) s, acc[r][t]);
+            }
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < Q8S_R; ++r)
+#pragma unroll
+        for (int t = 0; t < TT; ++t) {
+            if (t >= T) break;
+            const float v = wsum(acc[r][t]);
+            if (lane == 0 && row0 + r < rows) out[(size_t) t * out_stride + row0 + r] = v;
+        }
+}
+
+template <int TT>
+__global__ void __launch_bounds__(Q8S_THREADS, 2) k_q8s(const int8_t* __restrict__ wq, const uint16_t* __restrict__ wd, int rows, int cols,
+                                                    const uint8_t* __restrict__ yq, const int8_t* __restrict__ pq,
+                                                    const float* __restrict__ pd, int T, float* __restrict__ out, int out_stride,
+                                                    int rows_per_block) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    int8_t* sq = reinterpret_cast<int8_t*>(smem);
+    float* sd = reinterpret_cast<float*>(smem + (size_t) T * cols);
+    stage_act(sq, sd, yq, pq, pd, T, cols);
+    __syncthreads();
+    const int warp = threadIdx.x >> 5;
+    const int base = blockIdx.x * rows_per_block;
+    for (int r0 = warp * Q8S_R; r0 < rows_per_block; r0 += (Q8S_THREADS / 32) * Q8S_R) {
+        if (base + r0 >= rows) break;
+        q8s_rows<TT>(wq, wd, rows, cols, base + r0, sq, sd, T, out, out_stride);
+    }
+}
+
+// f32 GEMV, a block of 4 warps per row, warp p the p-th quarter of the float4 chunks (reference
+// src/kernels.cu:184-227 with WPR = 4): lane sums its chunks in ascending order, xor-tree, 0 + p0 + p1 + p2 + p3
+__global__ void __launch_bounds__(128) k_gemv_f32(const float* __restrict__ W, const float* __restrict__ x, float* __restrict__ y,
+                                                  int rows, int n, int T) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, row = blockIdx.x, nc = n / 512;
+    __shared__ float red[FNX_MAXT][4];
+    const float4* w4 = reinterpret_cast<const float4*>(W + (size_t) row * n) + warp * nc * 32;
+    for (int t = 0; t < T; ++t) {
+        const float4* x4 = reinterpret_cast<const float4*>(x + (size_t) t * n) + warp * nc * 32;
+        float a = 0.f;
+        for (int i = 0; i < nc; ++i) {
+            const float4 w = __ldg(w4 + i * 32 + lane), b = x4[i * 32 + lane];
+            float p = fmul(w.x, b.x);
+            p = ffma(w.y, b.y, p);
+            p = ffma(w.z, b.z, p);
+            p = ffma(w.w, b.w, p);
+            a = fadd(a, p);
+        }
+        a = wsum(a);
+        if (lane == 0) red[t][warp] = a;
+    }
+    __syncthreads();
+    if (threadIdx.x < T) {
+        float v = 0.f;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) v = fadd(v, red[threadIdx.x][k]);
+        y[(size_t) threadIdx.x * rows + row] = v;
+    }
+}
+
+// h = silu(gate) * up of T rows [gate | up] as an int8 plane + float(f16(d)) scales (see moe.cu k_swiglu_q8)
+__global__ void __launch_bounds__(256) k_swiglu_rows(const float* __restrict__ gu, int ffs, int nrows, int8_t* __restrict__ hq,
+                                                     float* __restrict__ hd) {
+    const int nb = ffs / 32, q = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (q >= nrows * nb) return;
+    const int e = q / nb, b = q % nb;
+    const float* g = gu + (size_t) e * 2 * ffs;
+    const float xi = fmul(ex_silu(g[b * 32 + lane]), g[ffs + b * 32 + lane]);
+    const float amax = wmax(fabsf(xi));
+    const float d = fdiv(amax, 127.0f);
+    hq[(size_t) e * ffs + b * 32 + lane] = amax == 0.0f ? 0 : (int8_t) roundf(fdiv(xi, d));
+    if (lane == 0) hd[(size_t) e * nb + b] = h2f(f2h(d));
+}
+
+int q8s_launch(FnxQ8S w, int rows, int cols, const void* yq, const int8_t* pq, const float* pd, float* out, int out_stride, int T,
+               cudaStream_t st, const char* what) {
+    if (!(T >= 1 && T <= FNX_MAXT)) return fail("%s: T %d outside 1..%d", what, T, FNX_MAXT);
+    if (!(cols > 0 && cols % 32 == 0 && rows > 0)) return fail("%s: %d x %d (columns a multiple of 32)", what, rows, cols);
+    // enough blocks to fill the GPU twice over, at most 128 rows each so the staged activations are amortised
+    int rpb = (rows / 296 + 31) / 32 * 32;
+    rpb = rpb < 32 ? 32 : rpb > 128 ? 128 : rpb;
+    const int grid = (rows + rpb - 1) / rpb;
+    const size_t sm = (size_t) T * cols + (size_t) T * (cols / 32) * 4;
+    if (sm > 227 * 1024) return fail("%s: %d columns x %d rows of activations do not fit shared memory", what, cols, T);
+#define Q8S_CASE(TT)                                                                                                          \
+    {                                                                                                                         \
+        if (sm > 48 * 1024 && cudaFuncSetAttribute(k_q8s<TT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) sm) != cudaSuccess) \
+            return fail("%s: shared memory opt-in failed", what);                                                             \
+        k_q8s<TT><<<grid, Q8S_THREADS, sm, st>>>(w.q, w.d, rows, cols, (const uint8_t*) yq, pq, pd, T, out, out_stride, rpb);  \
+    }
+    if (T <= 1) Q8S_CASE(1)
+    else if (T <= 2) Q8S_CASE(2)
+    else if (T <= 4) Q8S_CASE(4)
+    else if (T <= 8) Q8S_CASE(8)
+    else Q8S_CASE(16)
+#undef Q8S_CASE
+    return launch_ok(what);
+}
+
+}  // namespace fnxk
+
+using namespace fnxk;
+
+extern "C" {
+
+int fnx_q8s_gemv(FnxQ8S w, int rows, int cols, const void* y, float* out, int out_stride, int T, void* st) {
+    return q8s_launch(w, rows, cols, y, nullptr, nullptr, out, out_stride, T, strm(st), "q8s_gemv");
+}
+
+int fnx_gemv_f32(const float* W, const float* x, float* y, int rows, int n, int T, void* st) {
+    FNX_REQUIRE(T >= 1 && T <= FNX_MAXT, "gemv_f32: T %d outside 1..%d", T, FNX_MAXT);
+    FNX_REQUIRE(n > 0 && n % 512 == 0 && rows > 0, "gemv_f32: %d x %d (columns a multiple of 512)", rows, n);
+    k_gemv_f32<<<rows, 128, 0, strm(st)>>>(W, x, y, rows, n, T);
+    return launch_ok("gemv_f32");
+}
+
+int fnx_shared_expert(FnxQ8S gate_up, FnxQ8S down, const void* xq, int T, int n, int ffs, float* sh_gu, void* hq, float* out,
+                      void* st) {
+    FNX_REQUIRE(ffs > 0 && ffs % 32 == 0 && ((size_t) T * ffs) % 16 == 0, "shared_expert: ff width %d", ffs);
+    if (q8s_launch(gate_up, 2 * ffs, n, xq, nullptr, nullptr, sh_gu, 2 * ffs, T, strm(st), "shared expert gate|up")) return 1;
+    int8_t* h8 = (int8_t*) hq;
+    float* hd = (float*) ((char*) hq + (size_t) T * ffs);
+    k_swiglu_rows<<<(T * (ffs / 32) + 7) / 8, 256, 0, strm(st)>>>(sh_gu, ffs, T, h8, hd);
+    if (launch_ok("shared expert swiglu")) return 1;
+    return q8s_launch(down, n, ffs, nullptr, h8, hd, out, n, T, strm(st), "shared expert down");
+}
+}

@@ -1,0 +1,458 @@
+// Routed-expert FFN of the verify window: router + top-k + job list, dequant-fused gate|up, SwiGLU + down, combine.
+// Replaces reference src/moe.cuh, src/moe_q4k.cuh and the combine of src/kernels.cu:797-803; the arithmetic order of
+// every sum is the reference's, stated with IEEE operations (exact_math.cuh), so results can be checked bit for bit.
+#include "common.cuh"
+#include "exact_math.cuh"
+
+namespace fnxk {
+
+// ================================================================ router (reference src/moe.cuh:73-202)
+// logits: two warps per row (column halves); lane l accumulates the float4 chunks i * 32 + l in ascending i, each chunk
+// ((wx bx + wy by) + wz bz) + ww bw with fused steps; xor-tree; half0 + half1.  The grid's last block then picks the
+// top-k per row and builds the jobs.
+constexpr int RR_THREADS = 128, RR_ROWS = RR_THREADS / 64;
+
+struct RouterArgs {
+    const float* W;
+    const float* x;
+    float* logits;
+    int T, n, nexp, topk;
+    int* topi;
+    float* topw;
+    FnxJob *gu, *dn;
+    int* njobs;
+    unsigned* counter;
+};
+
+__device__ __forceinline__ float dot4(const float4& w, const float4& b) {
+    float t = fmul(w.x, b.x);
+    t = ffma(w.y, b.y, t);
+    t = ffma(w.z, b.z, t);
+    return ffma(w.w, b.w, t);
+}
+
+__device__ void route_tail(const RouterArgs& a);
+
+__global__ void __launch_bounds__(RR_THREADS) k_router_route(const RouterArgs a) {
+    const int e = threadIdx.x, warp = e >> 5, lane = e & 31, rw = warp >> 1, half = warp & 1;
+    const int L = a.nexp + 1, row = blockIdx.x * RR_ROWS + rw, nc = a.n / 256;   // float4 chunks per lane
+    __shared__ float rsum[FNX_MAXT][RR_THREADS / 32];
+    if (row < L) {
+        const float4* w4 = reinterpret_cast<const float4*>(a.W + (size_t) row * a.n) + half * nc * 32;
+        for (int t = 0; t < a.T; ++t) {
+            const float4* x4 = reinterpret_cast<const float4*>(a.x + (size_t) t * a.n) + half * nc * 32;
+            float s = 0.f;
+#pragma unroll 4
+            for (int i = 0; i < nc; ++i) s = fadd(s, dot4(__ldg(w4 + i * 32 + lane), x4[i * 32 + lane]));
+            s = wsum(s);
+            if (lane == 0) rsum[t][warp] = s;
+        }
+    }
+    __syncthreads();
+    for (int q = e; q < a.T * RR_ROWS; q += RR_THREADS) {
+        const int t = q / RR_ROWS, r = q % RR_ROWS, lrow = blockIdx.x * RR_ROWS + r;
+        if (lrow < L) a.logits[(size_t) t * L + lrow] = fadd(rsum[t][2 * r], rsum[t][2 * r + 1]);
+    }
+    __shared__ bool last;
+    __threadfence();
+    __syncthreads();
+    if (e == 0) last = atomicAdd(a.counter, 1u) == gridDim.x - 1;
+    __syncthreads();
+    if (!last) return;
+    __threadfence();
+    route_tail(a);
+}
+
+// top-k per row by logit (ties: the lower index), weights exp(l - l_top) / sum in pick order; jobs: one per distinct
+// expert numbered by its first pick in pair order p = t topk + k, a job's rows in pair order
+__device__ void route_tail(const RouterArgs& a) {
+    const int e = threadIdx.x, warp = e >> 5, lane = e & 31, L = a.nexp + 1, P = a.T * a.topk, per = a.nexp / 32;
+    __shared__ int ex[FNX_MAXT * 16];
+    for (int t = warp; t < a.T; t += RR_THREADS / 32) {
+        float v[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) v[i] = i < per ? __ldcg(a.logits + (size_t) t * L + lane + 32 * i) : -INFINITY;
+        unsigned taken = 0;
+        float top0 = 0.f, z = 0.f, wk = 0.f;
+        for (int k = 0; k < a.topk; ++k) {
+            float bv = -INFINITY;
+            int bi = a.nexp;
+#pragma unroll
+            for (int i = 0; i < 16; ++i)
+                if (i < per && !(taken >> i & 1u) && v[i] > bv) {
+                    bv = v[i];
+                    bi = lane + 32 * i;
+                }
+#pragma unroll
+            for (int o = 16; o; o >>= 1) {
+                const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+                const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+                if (ov > bv || (ov == bv && oi < bi)) {
+                    bv = ov;
+                    bi = oi;
+                }
+            }
+            if ((bi & 31) == lane && bi < a.nexp) taken |= 1u << (bi >> 5);
+            if (k == 0) top0 = bv;
+            const float ek = ex_expf(fsub(bv, top0));
+            z = fadd(z, ek);
+            if (lane == k) {
+                wk = ek;
+                a.topi[t * a.topk + k] = bi;
+                ex[t * a.topk + k] = bi;
+            }
+        }
+        if (lane < a.topk) a.topw[t * a.topk + lane] = fdiv(wk, z);
+    }
+    __syncthreads();
+    __shared__ unsigned char first[FNX_MAXT * 16];
+    __shared__ int jobof[FNX_MAXT * 16];
+    for (int p = e; p < P; p += RR_THREADS) {
+        bool f = true;
+        for (int q = 0; q < p; ++q) f = f && ex[q] != ex[p];
+        first[p] = f;
+    }
+    __syncthreads();
+    for (int p = e; p < P; p += RR_THREADS) {
+        int fp = p;   // the pair's expert's first pair, and how many jobs start before it
+        for (int q = p - 1; q >= 0; --q)
+            if (ex[q] == ex[p]) fp = q;
+        int j = 0;
+        for (int q = 0; q < fp; ++q) j += first[q];
+        jobof[p] = j;
+    }
+    __syncthreads();
+    for (int p = e; p < P; p += RR_THREADS) {
+        const int j = jobof[p];
+        int s = 0, cnt = 0;
+        for (int q = 0; q < P; ++q)
+            if (ex[q] == ex[p]) {
+                s += q < p;
+                ++cnt;
+            }
+        a.gu[j].y[s] = p / a.topk;
+        a.gu[j].out[s] = a.dn[j].y[s] = a.dn[j].out[s] = p;
+        if (first[p]) {
+            a.gu[j].w = a.dn[j].w = ex[p];
+            a.gu[j].n = a.dn[j].n = cnt;
+        }
+    }
+    if (e == 0) {
+        int n = 0;
+        for (int q = 0; q < P; ++q) n += first[q];
+        a.njobs[0] = n;
+        a.njobs[1] = 0;
+        *a.counter = 0u;
+    }
+}
+
+// ================================================================ job activations in shared memory
+// the job's q8_1 rows as an int8 plane [nj][n] (16-byte loads), the f16-rounded block scales and the blocks' integer
+// sums [nj][n / 32]
+struct JobAct {
+    int8_t* q;
+    float* d;
+    int* s;
+};
+__device__ __forceinline__ JobAct job_act_carve(unsigned char* smem, int maxrows, int n) {
+    JobAct a;
+    a.q = reinterpret_cast<int8_t*>(smem);
+    a.d = reinterpret_cast<float*>(smem + (size_t) maxrows * n);
+    a.s = reinterpret_cast<int*>(smem + (size_t) maxrows * n + (size_t) maxrows * (n / 32) * 4);
+    return a;
+}
+__host__ __device__ inline size_t job_act_bytes(int maxrows, int n) { return (size_t) maxrows * (n + (n / 32) * 8); }
+
+__device__ __forceinline__ void job_act_stage(const JobAct& a, const uint8_t* __restrict__ xq, const FnxJob& jb, int n) {
+    const int nb = n / 32;
+    for (int it = threadIdx.x; it < jb.n * nb; it += blockDim.x) {
+        const int j = it / nb, b = it % nb;
+        const unsigned* src = reinterpret_cast<const unsigned*>(xq + ((size_t) jb.y[j] * nb + b) * 36);
+        unsigned w[9];
+#pragma unroll
+        for (int k = 0; k < 9; ++k) w[k] = src[k];
+        int sum = 0;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) sum = __dp4a(0x01010101, (int) w[1 + k], sum);
+        uint4* dst = reinterpret_cast<uint4*>(a.q + (size_t) j * n + b * 32);
+        dst[0] = make_uint4(w[1], w[2], w[3], w[4]);
+        dst[1] = make_uint4(w[5], w[6], w[7], w[8]);
+        a.d[j * nb + b] = h2f((uint16_t) (w[0] & 0xffff));
+        a.s[j * nb + b] = sum;
+    }
+}
+
+// ================================================================ gate|up, Q4_K (reference src/moe_q4k.cuh:30-109)
+// 8 lanes a weight row; lane l owns the 64-value groups l + 8 i (32 bytes of nibbles + the super-block's 16-byte
+// header: three 16-byte loads), all of a row's groups in flight at once; per group and activation row the integer
+// sub-block dots, then d (d8l (sc0 dl) + d8h (sc1 dh)) - dmin (d8l (m0 sl) + d8h (m1 sh)) added in group order; the 8
+// lanes combined by xor 4, 2, 1.
+constexpr int GU_THREADS = 256;
+
+__device__ __forceinline__ unsigned q4k_sbyte(const uint4& h, int k) {
+    const unsigned word = k < 4 ? h.y : k < 8 ? h.z : h.w;
+    return (word >> (8 * (k & 3))) & 0xFFu;
+}
+__device__ __forceinline__ void q4k_scale_min(const uint4& h, int j, float& sc, float& m) {
+    if (j < 4) {
+        sc = (float) (q4k_sbyte(h, j) & 63);
+        m = (float) (q4k_sbyte(h, j + 4) & 63);
+    } else {
+        sc = (float) ((q4k_sbyte(h, j + 4) & 0xF) | ((q4k_sbyte(h, j - 4) >> 6) << 4));
+        m = (float) ((q4k_sbyte(h, j + 4) >> 4) | ((q4k_sbyte(h, j) >> 6) << 4));
+    }
+}
+__device__ __forceinline__ uint4 ldg_stream(const void* p) {   // read-once weights: do not keep them in L1
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+
+template <int GPL>
+__global__ void __launch_bounds__(GU_THREADS, 2) k_moe_gu_q4k(const uint8_t* __restrict__ A, size_t sa, int nrows, int n,
+                                                          const FnxJob* __restrict__ jobs, const int* __restrict__ njobs,
+                                                          const uint8_t* __restrict__ xq, float* __restrict__ out, int rows_per_block,
+                                                          int maxrows) {
+    const int ji = blockIdx.y;
+    if (ji >= *njobs) return;
+    extern __shared__ __align__(16) unsigned char smem[];
+    __shared__ FnxJob jb;
+    if (threadIdx.x < sizeof(FnxJob) / 4) reinterpret_cast<int*>(&jb)[threadIdx.x] = reinterpret_cast<const int*>(jobs + ji)[threadIdx.x];
+    __syncthreads();
+    const JobAct act = job_act_carve(smem, maxrows, n);
+    job_act_stage(act, xq, jb, n);
+    __syncthreads();
+    const int lane8 = threadIdx.x & 7, nb = n / 32;
+    const size_t row_b = (size_t) n / 256 * 144;
+    const uint8_t* We = A + (size_t) jb.w * sa;
+    for (int rb = 0; rb < rows_per_block; rb += GU_THREADS / 8) {
+        const int row = blockIdx.x * rows_per_block + rb + (threadIdx.x >> 3);
+        const bool live = row < nrows;   // uniform over the 8 lanes of a row
+        const uint8_t* wrow = We + (size_t) (live ? row : 0) * row_b;
+        uint4 hdr[GPL], q0[GPL], q1[GPL];
+#pragma unroll
+        for (int ii = 0; ii < GPL; ++ii) {
+            const int g = lane8 + ii * 8, b = g >> 2, jg = g & 3;
+            const uint8_t* blk = wrow + (size_t) b * 144;
+            hdr[ii] = ldg_stream(blk);
+            q0[ii] = ldg_stream(blk + 16 + 32 * jg);
+            q1[ii] = ldg_stream(blk + 32 + 32 * jg);
+        }
+#pragma unroll 1
+        for (int j = 0; j < jb.n; ++j) {
+            float tmp = 0.f;
+#pragma unroll
+            for (int ii = 0; ii < GPL; ++ii) {
+                const int g = lane8 + ii * 8, b = g >> 2, jg = g & 3, yb = b * 8 + jg * 2;
+                const float d = h2f((uint16_t) (hdr[ii].x & 0xffff)), dmin = h2f((uint16_t) (hdr[ii].x >> 16));
+                float sc0, m0, sc1, m1;
+                q4k_scale_min(hdr[ii], 2 * jg, sc0, m0);
+                q4k_scale_min(hdr[ii], 2 * jg + 1, sc1, m1);
+                const uint4* ap = reinterpret_cast<const uint4*>(act.q + (size_t) j * n + yb * 32);
+                const uint4 a0 = ap[0], a1 = ap[1], a2 = ap[2], a3 = ap[3];
+                const unsigned qw[8] = {q0[ii].x, q0[ii].y, q0[ii].z, q0[ii].w, q1[ii].x, q1[ii].y, q1[ii].z, q1[ii].w};
+                const unsigned al[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+                const unsigned ah[8] = {a2.x, a2.y, a2.z, a2.w, a3.x, a3.y, a3.z, a3.w};
+                int dl = 0, dh = 0;
+#pragma unroll
+                for (int w = 0; w < 8; ++w) {
+                    dl = __dp4a((int) (qw[w] & 0x0F0F0F0Fu), (int) al[w], dl);
+                    dh = __dp4a((int) ((qw[w] >> 4) & 0x0F0F0F0Fu), (int) ah[w], dh);
+                }
+                const int sl = act.s[j * nb + yb], sh = act.s[j * nb + yb + 1];
+                const float d8l = act.d[j * nb + yb], d8h = act.d[j * nb + yb + 1];
+                const float pos = fmul(d, fadd(fmul(d8l, fmul(sc0, (float) dl)), fmul(d8h, fmul(sc1, (float) dh))));
+                const float neg = fmul(dmin, fadd(fmul(d8l, fmul(m0, (float) sl)), fmul(d8h, fmul(m1, (float) sh))));
+                tmp = fadd(tmp, fsub(pos, neg));
+            }
+            tmp = sum8(tmp);
+            if (live && lane8 == 0) out[(size_t) jb.out[j] * nrows + row] = tmp;
+        }
+    }
+}
+
+// ================================================================ h = silu(gate) * up as int8 + scales
+// a warp per (row, 32 columns) of gu rows [gate (ffs) | up (ffs)]: the q8_1 rounding with the scale kept as the float
+// of its f16 value (reference src/moe.cuh:284-295, src/dense.cuh:187-194).  hq: int8 [rows][ffs], then float
+// [rows][ffs / 32] from hq + rows_cap * ffs
+__global__ void __launch_bounds__(256) k_swiglu_q8(const float* __restrict__ gu, int ffs, int nrows, int8_t* __restrict__ hq,
+                                                   float* __restrict__ hd) {
+    const int nb = ffs / 32, q = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (q >= nrows * nb) return;
+    const int e = q / nb, b = q % nb;
+    const float* g = gu + (size_t) e * 2 * ffs;
+    const float xi = fmul(ex_silu(g[b * 32 + lane]), g[ffs + b * 32 + lane]);
+    const float amax = wmax(fabsf(xi));
+    const float d = fdiv(amax, 127.0f);
+    hq[(size_t) e * ffs + b * 32 + lane] = amax == 0.0f ? 0 : (int8_t) roundf(fdiv(xi, d));
+    if (lane == 0) hd[(size_t) e * nb + b] = h2f(f2h(d));
+}
+
+// ================================================================ down, Q6_K in 32-column units
+// thread per unit (16 B low nibbles, 8 B high bits, 2 int8 scales, f16 d: all coalesced across a warp's consecutive
+// units); unit value d (d8 (float) (sc0 isum0 + sc1 isum1)) per activation row into shared memory; then a row's units
+// added in ascending order (reference src/moe.cuh:330-344).
+constexpr int DN_THREADS = 256;
+
+__global__ void __launch_bounds__(DN_THREADS) k_moe_down_q6p(const uint4* __restrict__ QL, const uint2* __restrict__ QH,
+                                                            const uint16_t* __restrict__ SC, const uint16_t* __restrict__ D,
+                                                            size_t expert_units, int nrows, int ffs, const FnxJob* __restrict__ jobs,
+                                                            const int* __restrict__ njobs, const int8_t* __restrict__ hq,
+                                                            const float* __restrict__ hd, float* __restrict__ out, int rows_per_block,
+                                                            int maxrows) {
+    const int ji = blockIdx.y;
+    if (ji >= *njobs) return;
+    extern __shared__ __align__(16) unsigned char smem[];
+    __shared__ FnxJob jb;
+    if (threadIdx.x < sizeof(FnxJob) / 4) reinterpret_cast<int*>(&jb)[threadIdx.x] = reinterpret_cast<const int*>(jobs + ji)[threadIdx.x];
+    __syncthreads();
+    const int nu = ffs / 32, units = rows_per_block * nu;
+    int8_t* sq = reinterpret_cast<int8_t*>(smem);                                 // [maxrows][ffs]
+    float* sd = reinterpret_cast<float*>(smem + (size_t) maxrows * ffs);          // [maxrows][nu]
+    float* part = sd + (size_t) maxrows * nu;                                     // [maxrows][units]
+    for (int it = threadIdx.x; it < jb.n * (ffs / 16); it += DN_THREADS) {
+        const int j = it / (ffs / 16), c = it % (ffs / 16);
+        reinterpret_cast<uint4*>(sq + (size_t) j * ffs)[c] = reinterpret_cast<const uint4*>(hq + (size_t) jb.y[j] * ffs)[c];
+    }
+    for (int it = threadIdx.x; it < jb.n * nu; it += DN_THREADS) sd[(it / nu) * nu + it % nu] = hd[(size_t) jb.y[it / nu] * nu + it % nu];
+    __syncthreads();
+    const int row0 = blockIdx.x * rows_per_block;
+    const size_t ebase = (size_t) jb.w * expert_units + (size_t) row0 * nu;
+    const int live_units = min(units, (nrows - row0) * nu);
+    for (int g = threadIdx.x; g < live_units; g += DN_THREADS) {
+        const uint4 ql = ldg_stream(QL + ebase + g);
+        const uint2 qh = __ldg(QH + ebase + g);
+        const unsigned scw = SC[ebase + g];
+        const float d = h2f(D[ebase + g]);
+        const int sc0 = (int) (int8_t) (scw & 0xff), sc1 = (int) (int8_t) (scw >> 8);
+        const int u = g % nu;
+        const unsigned lw[4] = {ql.x, ql.y, ql.z, ql.w};
+        unsigned v[8];
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            v[w] = __vsub4((lw[w] & 0x0F0F0F0Fu) | (((qh.x >> (2 * w)) & 0x03030303u) << 4), 0x20202020u);
+            v[4 + w] = __vsub4(((lw[w] >> 4) & 0x0F0F0F0Fu) | (((qh.y >> (2 * w)) & 0x03030303u) << 4), 0x20202020u);
+        }
+        for (int j = 0; j < jb.n; ++j) {
+            const uint4* ap = reinterpret_cast<const uint4*>(sq + (size_t) j * ffs + u * 32);
+            const uint4 a0 = ap[0], a1 = ap[1];
+            int is0 = __dp4a((int) v[0], (int) a0.x, 0);
+            is0 = __dp4a((int) v[1], (int) a0.y, is0);
+            is0 = __dp4a((int) v[2], (int) a0.z, is0);
+            is0 = __dp4a((int) v[3], (int) a0.w, is0);
+            int is1 = __dp4a((int) v[4], (int) a1.x, 0);
+            is1 = __dp4a((int) v[5], (int) a1.y, is1);
+            is1 = __dp4a((int) v[6], (int) a1.z, is1);
+            is1 = __dp4a((int) v[7], (int) a1.w, is1);
+            const int I = sc0 * is0 + sc1 * is1;
+            part[(size_t) j * units + g] = fmul(d, fmul(sd[j * nu + u], (float) I));
+        }
+    }
+    __syncthreads();
+    const int live_rows = min(rows_per_block, nrows - row0);
+    for (int e = threadIdx.x; e < jb.n * live_rows; e += DN_THREADS) {
+        const int j = e / live_rows, rr = e % live_rows;
+        float s = 0.f;
+        for (int k = 0; k < nu; ++k) s = fadd(s, part[(size_t) j * units + rr * nu + k]);
+        out[(size_t) jb.out[j] * nrows + row0 + rr] = s;
+    }
+}
+
+// ================================================================ combine (reference src/kernels.cu:797-803)
+__global__ void __launch_bounds__(256) k_moe_combine(const float* __restrict__ part, const float* __restrict__ topw,
+                                                     const float* __restrict__ sh, const float* __restrict__ logits, int nexp,
+                                                     float* __restrict__ out, int n, int topk) {
+    const int t = blockIdx.y, i = blockIdx.x * 256 + threadIdx.x;
+    if (i >= n) return;
+    float s = 0.f;
+    for (int k = 0; k < topk; ++k) s = ffma(topw[t * topk + k], part[((size_t) t * topk + k) * n + i], s);
+    out[(size_t) t * n + i] = ffma(ex_sigmoid(logits[(size_t) t * (nexp + 1) + nexp]), sh[(size_t) t * n + i], s);
+}
+
+template <typename K> int smem_optin(K kernel, size_t bytes, const char* what) {
+    if (bytes > 227 * 1024) return fail("%s: %zu bytes of shared memory exceed an SM's 227 KB", what, bytes);
+    if (bytes > 48 * 1024) {
+        const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) bytes);
+        if (e != cudaSuccess) return fail("%s: shared memory opt-in: %s", what, cudaGetErrorString(e));
+    }
+    return 0;
+}
+
+}  // namespace fnxk
+
+using namespace fnxk;
+
+extern "C" {
+
+size_t fnx_router_scratch_bytes(void) { return 16; }
+
+int fnx_router_route(const float* W, const float* x, float* logits, int T, int n, int nexp, int topk, int* topi, float* topw,
+                     FnxJob* jobs_gu, FnxJob* jobs_dn, int* njobs, void* scratch, void* st) {
+    FNX_REQUIRE(T >= 1 && T <= FNX_MAXT, "router_route: T %d outside 1..%d", T, FNX_MAXT);
+    FNX_REQUIRE(n > 0 && n % 256 == 0, "router_route: n %d must be a multiple of 256", n);
+    FNX_REQUIRE(nexp % 32 == 0 && nexp >= 32 && nexp <= 512, "router_route: %d experts (a multiple of 32 up to 512)", nexp);
+    FNX_REQUIRE(topk >= 1 && topk <= 16 && topk <= nexp, "router_route: top-%d", topk);
+    RouterArgs a{W, x, logits, T, n, nexp, topk, topi, topw, jobs_gu, jobs_dn, njobs, (unsigned*) scratch};
+    k_router_route<<<(nexp + 1 + RR_ROWS - 1) / RR_ROWS, RR_THREADS, 0, strm(st)>>>(a);
+    return launch_ok("router_route");
+}
+
+size_t fnx_moe_h_bytes(int pairs, int ffs) { return (size_t) pairs * ffs + (size_t) pairs * (ffs / 32) * 4; }
+
+int fnx_moe_gate_up(const FnxExperts* A, const FnxJob* jobs, const int* njobs, int njobs_max, const void* xq, float* gu, void* st) {
+    FNX_REQUIRE(A && njobs_max >= 1, "moe_gate_up: no experts or jobs");
+    const int n = A->ncols, nrows = A->nrows, maxrows = FNX_MAXT;
+    if (A->type == FNX_Q4_K) {
+        FNX_REQUIRE(n % 512 == 0 && n / 512 >= 1 && n / 512 <= 8, "moe gate|up q4_K: %d columns (multiples of 512 up to 4096)", n);
+        // blocks of 64 rows: the staged activations amortised over two passes, several thousand blocks a layer
+        const int rpb = 64;
+        const dim3 grid((nrows + rpb - 1) / rpb, njobs_max);
+        const size_t sm = job_act_bytes(maxrows, n);
+        const uint8_t* a = (const uint8_t*) A->a;
+#define GU_CASE(G)                                                                                                          \
+    case G:                                                                                                                 \
+        if (smem_optin(k_moe_gu_q4k<G>, sm, "moe gate|up q4_K")) return 1;                                                  \
+        k_moe_gu_q4k<G><<<grid, GU_THREADS, sm, strm(st)>>>(a, A->stride, nrows, n, jobs, njobs, (const uint8_t*) xq, gu, rpb, maxrows); \
+        break;
+        switch (n / 512) {
+            GU_CASE(1) GU_CASE(2) GU_CASE(3) GU_CASE(4) GU_CASE(5) GU_CASE(6) GU_CASE(7) GU_CASE(8)
+        }
+#undef GU_CASE
+        return launch_ok("moe gate|up q4_K");
+    }
+    return fail("moe_gate_up: expert type %d not supported (Q4_K)", A->type);
+}
+
+int fnx_moe_down(const FnxExperts* A, const FnxJob* jobs, const int* njobs, int njobs_max, const float* gu, int npairs, void* hq,
+                 float* part, void* st) {
+    FNX_REQUIRE(A && njobs_max >= 1 && npairs >= 1, "moe_down: no experts, jobs or pairs");
+    const int ffs = A->ncols, nrows = A->nrows, maxrows = FNX_MAXT;
+    FNX_REQUIRE(ffs % 32 == 0 && ffs > 0, "moe_down: ff width %d not a multiple of 32", ffs);
+    int8_t* h8 = (int8_t*) hq;
+    float* hd = (float*) ((char*) hq + (size_t) npairs * ffs);
+    FNX_REQUIRE(((size_t) npairs * ffs) % 16 == 0 && ffs % 16 == 0, "moe_down: h rows must be 16-byte multiples");
+    k_swiglu_q8<<<(npairs * (ffs / 32) + 7) / 8, 256, 0, strm(st)>>>(gu, ffs, npairs, h8, hd);
+    if (launch_ok("moe_down swiglu")) return 1;
+    if (A->type == FNX_Q6_K) {
+        const int nu = ffs / 32;
+        int rpb = 768 / nu;   // ~768 units a block
+        if (rpb < 1) rpb = 1;
+        if (rpb > nrows) rpb = nrows;
+        const size_t sm = (size_t) maxrows * ffs + (size_t) maxrows * nu * 4 + (size_t) maxrows * rpb * nu * 4;
+        if (smem_optin(k_moe_down_q6p, sm, "moe_down q6_K")) return 1;
+        const dim3 grid((nrows + rpb - 1) / rpb, njobs_max);
+        k_moe_down_q6p<<<grid, DN_THREADS, sm, strm(st)>>>((const uint4*) A->a, (const uint2*) A->b, (const uint16_t*) A->c,
+                                                        (const uint16_t*) A->d, A->stride, nrows, ffs, jobs, njobs, h8, hd, part, rpb,
+                                                        maxrows);
+        return launch_ok("moe_down q6_K");
+    }
+    return fail("moe_down: expert type %d not supported (Q6_K units)", A->type);
+}
+
+int fnx_moe_combine(const float* part, const float* topw, const float* sh, const float* logits, int nexp, float* out, int T,
+                    int n, int topk, void* st) {
+    FNX_REQUIRE(T >= 1 && n >= 1, "moe_combine: empty");
+    k_moe_combine<<<dim3((n + 255) / 256, T), 256, 0, strm(st)>>>(part, topw, sh, logits, nexp, out, n, topk);
+    return launch_ok("moe_combine");
+}
+}

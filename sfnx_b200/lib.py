@@ -1,0 +1,129 @@
+"""ctypes binding of libsfnx_b200.so, the C ABI declared in include/sfnx_b200.h.
+
+Pointers are plain integers (torch `tensor.data_ptr()`), streams are `torch.cuda.Stream.cuda_stream` values.  A call
+that returns non-zero raises FnxError with fnx_last_error()'s text, as the reference's launch wrappers throw
+std::runtime_error.  There is no CPU fallback: without the built library, loading raises.
+"""
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libsfnx_b200.so")
+
+MAXT = 16
+TOPK_N = 64
+HS = 128
+Q4_K, Q6_K, Q8_0 = 12, 14, 8
+
+
+class FnxError(RuntimeError):
+    pass
+
+
+class Job(C.Structure):
+    _fields_ = [("w", C.c_int), ("n", C.c_int), ("y", C.c_int * MAXT), ("out", C.c_int * MAXT)]
+
+
+class Q8S(C.Structure):
+    _fields_ = [("q", C.c_void_p), ("d", C.c_void_p)]
+
+
+class Experts(C.Structure):
+    _fields_ = [("type", C.c_int), ("nrows", C.c_int), ("ncols", C.c_int), ("a", C.c_void_p), ("b", C.c_void_p),
+                ("c", C.c_void_p), ("d", C.c_void_p), ("stride", C.c_size_t), ("stride_b", C.c_size_t)]
+
+
+class KvPages(C.Structure):
+    _fields_ = [("pt", C.c_void_p), ("page", C.c_size_t), ("rows", C.c_int)]
+
+
+class Rope(C.Structure):
+    _fields_ = [("base", C.c_float), ("nrot", C.c_int)]
+
+
+class CopyJob(C.Structure):
+    _fields_ = [("dst", C.c_void_p), ("src", C.c_void_p), ("bytes", C.c_size_t)]
+
+
+_p, _i, _f, _z, _u64 = C.c_void_p, C.c_int, C.c_float, C.c_size_t, C.c_ulonglong
+
+# name -> argument types; every function returns int status unless listed in _OTHER
+_SIGS = {
+    "fnx_quantize_q8_1": [_p, _p, _i, _i, _p],
+    "fnx_rms_norm_rows": [_p, _p, _p, _p, _p, _i, _i, _f, _p],
+    "fnx_q8s_gemv": [Q8S, _i, _i, _p, _p, _i, _i, _p],
+    "fnx_gemv_f32": [_p, _p, _p, _i, _i, _i, _p],
+    "fnx_router_route": [_p, _p, _p, _i, _i, _i, _i, _p, _p, _p, _p, _p, _p, _p],
+    "fnx_moe_gate_up": [C.POINTER(Experts), _p, _p, _i, _p, _p, _p],
+    "fnx_moe_down": [C.POINTER(Experts), _p, _p, _i, _p, _i, _p, _p, _p],
+    "fnx_shared_expert": [Q8S, Q8S, _p, _i, _i, _i, _p, _p, _p, _p],
+    "fnx_moe_combine": [_p, _p, _p, _p, _i, _p, _i, _i, _i, _p],
+    "fnx_gdn_core": [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _p, _i, _f, _p, _p],
+    "fnx_copy_many": [_p, _i, _p],
+    "fnx_attn_prep_append": [_p, _p, _p, _p, _p, _p, _p, KvPages, _i, _i, _i, _p, _f, Rope, _i, _i, _i, _p],
+    "fnx_attn_partial": [_p, _p, _p, KvPages, _p, _i, _i, _i, _p, _i, _i, _i, _p, _p],
+    "fnx_attn_finish": [_p, _i, _i, _p, _p, _i, _i, _i, _i, _i, _p],
+    "fnx_argmax": [_p, _i, _i, _i, _p, _p, _p, _p, _p],
+    "fnx_penalize_row": [_p, _i, _p, _p, _p],
+    "fnx_top_tokens": [_p, _i, _i, _i, _p, _p, _p, _i, _p, _p, _p, _p, _p],
+    "fnx_repack_q8_0_split": [_p, _p, _p, _z, _z, _p],
+    "fnx_repack_q6k_units": [_p, _z, _z, _z, _z, _p, _p, _p, _p, _p],
+    "fnx_synth_normal": [_p, _z, _f, _u64, _p],
+    "fnx_synth_quant": [_i, _p, _z, _f, _u64, _p],
+    "fnx_math_probe": [_i, _p, _p, _z, _p],
+}
+_OTHER = {
+    "fnx_last_error": (C.c_char_p, []),
+    "fnx_built_arch": (_i, []),
+    "fnx_router_scratch_bytes": (_z, []),
+    "fnx_moe_h_bytes": (_z, [_i, _i]),
+    "fnx_gdn_scratch_floats": (_z, [_i]),
+    "fnx_attn_scratch_floats": (_z, [_i, _i, _i]),
+    "fnx_kv_rows_per_card": (_i, [_i, _i]),
+}
+
+_lib = None
+
+
+def declared_symbols():
+    """Every entry point include/sfnx_b200.h declares."""
+    return sorted(list(_SIGS) + list(_OTHER))
+
+
+def load():
+    """The loaded library (raises if it has not been built: there is no other implementation to fall back to)."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise FnxError("libsfnx_b200.so is not built: run `python -m sfnx_b200.build` (nvcc, sm_100a)")
+        lib = C.CDLL(LIB_PATH)
+        for name, args in _SIGS.items():
+            fn = getattr(lib, name)
+            fn.argtypes = args
+            fn.restype = _i
+        for name, (res, args) in _OTHER.items():
+            fn = getattr(lib, name)
+            fn.argtypes = args
+            fn.restype = res
+        _lib = lib
+    return _lib
+
+
+def call(name, *args):
+    """Calls a status-returning entry point; raises FnxError with the library's text on failure."""
+    lib = load()
+    rc = getattr(lib, name)(*args)
+    if rc != 0:
+        raise FnxError(lib.fnx_last_error().decode())
+    return 0
+
+
+def ptr(t):
+    """Device (or host) address of a torch tensor, None -> NULL."""
+    return None if t is None else t.data_ptr()
+
+
+def stream():
+    import torch
+
+    return torch.cuda.current_stream().cuda_stream

@@ -1,0 +1,135 @@
+"""Seeded synthetic cases of the verify window and their evaluation by the CPU oracle (test infrastructure).
+
+Shapes follow the benchmark configurations: one MoE FFN layer (T rows, hidden n, nexp experts, top-k + shared expert,
+Q4_K gate|up, Q6_K down, Q8_0 shared expert), one Gated DeltaNet layer with rollback, position-split attention.
+"""
+import numpy as np
+
+from oracle import binding as O
+
+
+# ---------------------------------------------------------------- MoE layer
+def moe_weights(n, nexp, ffs, seed=0, sigma=0.02):
+    rng = np.random.default_rng(seed)
+    w = {"n": n, "nexp": nexp, "ffs": ffs}
+    w["router"] = (rng.standard_normal((nexp + 1, n)) * sigma).astype(np.float32)
+    gu = (rng.standard_normal((nexp, 2 * ffs, n)) * sigma).astype(np.float32)
+    w["gu_q4k"] = O.quantize_q4k(gu).reshape(nexp, 2 * ffs * (n // 256) * 144)
+    dn = (rng.standard_normal((nexp, n, ffs)) * sigma).astype(np.float32)
+    w["dn_q6k"] = O.quantize_q6k(dn).reshape(nexp, n * (ffs // 256) * 210)
+    planes = [O.q6k_to_planes(w["dn_q6k"][e], n, ffs) for e in range(nexp)]
+    w["dn_planes"] = tuple(np.stack([p[i] for p in planes]) for i in range(4))
+    sgu = (rng.standard_normal((2 * ffs, n)) * sigma).astype(np.float32)
+    sdn = (rng.standard_normal((n, ffs)) * sigma).astype(np.float32)
+    w["sh_gu"] = O.q8_0_to_split(O.quantize_q8_0(sgu), 2 * ffs, n)
+    w["sh_dn"] = O.q8_0_to_split(O.quantize_q8_0(sdn), n, ffs)
+    return w
+
+
+def moe_oracle(w, x, topk=10):
+    """The whole FFN half on the CPU oracle; returns every intermediate."""
+    n, ffs = w["n"], w["ffs"]
+    T = x.shape[0]
+    r = {}
+    r["xq"] = O.quantize_q8_1(x)
+    r["logits"], r["topi"], r["topw"], r["jobs_gu"], r["jobs_dn"], r["njobs"] = O.router_route(w["router"], x, topk)
+    r["gu"] = O.moe_gate_up_q4k(w["gu_q4k"], w["gu_q4k"].shape[1], r["jobs_gu"], r["njobs"], r["xq"], n, 2 * ffs, T * topk)
+    r["part"] = O.moe_down_q6p(w["dn_planes"], r["jobs_dn"], r["njobs"], r["gu"], n, ffs, T * topk)
+    r["sh_gu"], r["sh"] = O.shared_expert(w["sh_gu"][0], w["sh_gu"][1], w["sh_dn"][0], w["sh_dn"][1], r["xq"], T)
+    r["out"] = O.moe_combine(r["part"], r["topw"], r["sh"], r["logits"], T, n, topk)
+    return r
+
+
+# ---------------------------------------------------------------- Gated DeltaNet layer
+def gdn_case(T, nk, nv, seed=0):
+    """q/k/v/z rows, gates and state with the distributions of the benchmark configuration: state N(0, 0.1), q/k/v
+    N(0, 1) before the conv (the core L2-normalises q and k itself), beta = sigmoid(N(0, 1)), decay = exp(-softplus(N(0,
+    1))) through a = -1, dt = 0; conv width 4."""
+    rng = np.random.default_rng(seed)
+    ch = (2 * nk + nv) * 128
+    c = {"T": T, "nk": nk, "nv": nv, "ch": ch}
+    c["qkvz"] = rng.standard_normal((T, ch + nv * 128)).astype(np.float32)
+    c["ab"] = rng.standard_normal((T, 2 * nv)).astype(np.float32)
+    c["hist"] = rng.standard_normal((2, 3, ch)).astype(np.float32)
+    c["convw"] = (rng.standard_normal((ch, 4)) * 0.5).astype(np.float32)
+    c["dt"] = np.zeros(nv, np.float32)
+    c["a"] = -np.ones(nv, np.float32)
+    c["nw"] = (1 + 0.1 * rng.standard_normal(128)).astype(np.float32)
+    c["S"] = (rng.standard_normal((nv, 128, 128)) * 0.1).astype(np.float32)
+    vpk = nv // nk
+    vmap = np.zeros(nv, np.int32)
+    for lv in range(nv):   # value heads in key-head order; the first value head of a key head writes its history
+        vmap[lv] = (lv // vpk) | ((1 if lv % vpk == 0 else 0) << 8)
+    c["vmap"] = vmap
+    c["ctl"] = np.array([1000, 5], np.int32)   # position, tag (odd: history parity 1)
+    c["eps"] = 1e-6
+    return c
+
+
+def gdn_oracle(c):
+    S, hist = c["S"].copy(), c["hist"].copy()
+    yq, y32, snap, hsnap = O.gdn_core(c["qkvz"], c["ab"], hist, c["convw"], c["dt"], c["a"], c["nw"], S, c["ctl"], c["nk"], c["nv"],
+                                      c["vmap"], c["eps"])
+    return {"S": S, "hist": hist, "yq": yq, "y32": y32, "snap": snap, "hsnap": hsnap}
+
+
+# ---------------------------------------------------------------- attention
+def attn_case(T, ctx, nq=24, nkv=4, hd=256, ncard=1, seed=0):
+    """A K/V cache of ctx positions N(0, 1) rounded to f16, split by position over ncard GPUs, and a window of T rows at
+    positions ctx .. ctx + T - 1."""
+    rng = np.random.default_rng(seed)
+    c = {"T": T, "ctx": ctx, "nq": nq, "nkv": nkv, "hd": hd, "ncard": ncard, "pos0": ctx}
+    c["qg"] = rng.standard_normal((T, nq, 2 * hd)).astype(np.float32)
+    c["k"] = rng.standard_normal((T, nkv, hd)).astype(np.float32)
+    c["v"] = rng.standard_normal((T, nkv, hd)).astype(np.float32)
+    c["qn"] = (1 + 0.1 * rng.standard_normal(hd)).astype(np.float32)
+    c["kn"] = (1 + 0.1 * rng.standard_normal(hd)).astype(np.float32)
+    rows = ((ctx + T + 3) // 4 + ncard - 1) // ncard * 4
+    full_k = rng.standard_normal((ctx, nkv, hd)).astype(np.float16)
+    full_v = rng.standard_normal((ctx, nkv, hd)).astype(np.float16)
+    c["kc"], c["vc"] = [], []
+    for card in range(ncard):
+        kc = np.zeros((rows, nkv, hd), np.float16)
+        vc = np.zeros((rows, nkv, hd), np.float16)
+        for p in range(ctx):
+            j = p // 4
+            if j % ncard == card:
+                kc[(j // ncard) * 4 + p % 4] = full_k[p]
+                vc[(j // ncard) * 4 + p % 4] = full_v[p]
+        c["kc"].append(kc.view(np.uint16))
+        c["vc"].append(vc.view(np.uint16))
+    c["eps"] = 1e-6
+    c["rope_base"] = 1e7
+    return c
+
+
+def attn_oracle(c):
+    """Runs prep + append + partials + merge per GPU on copies; returns qg/k after prep, the caches, partials, out."""
+    T, nq, nkv, hd, ncard = c["T"], c["nq"], c["nkv"], c["hd"], c["ncard"]
+    r = {"kc": [], "vc": [], "part": []}
+    for card in range(ncard):
+        qg, k = c["qg"].copy(), c["k"].copy()
+        kc, vc = c["kc"][card].copy(), c["vc"][card].copy()
+        O.attn_prep_append(qg, k, c["v"], c["qn"], c["kn"], kc, vc, card, ncard, c["pos0"], c["eps"], c["rope_base"], nq, nkv, hd)
+        r["qg"], r["k"] = qg, k
+        r["kc"].append(kc)
+        r["vc"].append(vc)
+        r["part"].append(O.attn_partial(qg, kc, vc, card, ncard, c["pos0"], nq, nkv, hd))
+    r["out"] = O.attn_merge(r["part"], r["qg"], nq, hd)
+    return r
+
+
+# ---------------------------------------------------------------- logits comparison (the reference's exactness bar)
+def kl_top64(ref, new):
+    """Per-row KL(ref || new) over the union of both rows' 64 highest logits, a token outside a side's 64 taking that
+    side's 64th logit, probabilities from each side's full-row log-sum-exp (reference tools/fnx_run.cpp:244-288)."""
+    out = []
+    for a, b in zip(ref.astype(np.float64), new.astype(np.float64)):
+        ia, ib = np.argsort(-a, kind="stable")[:64], np.argsort(-b, kind="stable")[:64]
+        union = np.union1d(ia, ib)
+        la = a.max() + np.log(np.exp(a - a.max()).sum())
+        lb = b.max() + np.log(np.exp(b - b.max()).sum())
+        va = np.where(np.isin(union, ia), a[union], a[ia[-1]]) - la
+        vb = np.where(np.isin(union, ib), b[union], b[ib[-1]]) - lb
+        out.append(float(np.sum(np.exp(va) * (va - vb))))
+    return np.array(out)

@@ -1,0 +1,29 @@
+import os
+import sys
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a CUDA device (run with -m gpu on a B200)")
+
+
+@pytest.fixture(scope="session")
+def oracle():
+    from oracle import binding
+
+    binding.build()
+    return binding
+
+
+@pytest.fixture(scope="session")
+def fnx():
+    """The CUDA library through its C ABI.  GPU tests must fail, not skip, when it is missing."""
+    from sfnx_b200 import lib
+
+    lib.load()
+    return lib
