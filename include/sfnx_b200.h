@@ -90,6 +90,10 @@ int fnx_quantize_q8_1(const float* x, void* q, int n, int rows, void* st);
  * q8_1 rows (the reference's hc_read hands both forms to the layer, src/kernels.hpp:64-66) */
 int fnx_rms_norm_rows(float* x, const float* add, const float* w, float* y, void* q, int rows, int n, float eps, void* st);
 
+/* the window's input rows from an f16 embedding table in device memory: x[t] = table[ids[t]] (the reference embeds
+ * on the host and uploads the rows, src/engine.cu:783-789; a B200 holds the table) */
+int fnx_embed_rows(const uint16_t* table, const int* ids, float* x, int T, int n, void* st);
+
 /* ---- dense projections */
 /* reference src/kernels.hpp:47 q8s_gemv (src/dense.cuh:24-160): out[t][r] = W[r] . y[t], T <= FNX_MAXT */
 int fnx_q8s_gemv(FnxQ8S w, int rows, int cols, const void* y, float* out, int out_stride, int T, void* st);
@@ -140,7 +144,8 @@ int fnx_attn_prep_append(float* qg, float* k, const float* v, const float* q_nor
 /* reference src/kernels.hpp:125 attn_scratch_floats, 230-236 attn / attn_part_lanes / attn_finish
  * (src/kernels.cu:497-691).  fnx_attn_partial leaves this GPU's partial per (row, head) in part
  * [T][nq][hd + 2] (acc, m, z); fnx_attn_finish merges nparts partials (this GPU's and the peers', gathered by the
- * caller, parts[p] at parts + p * T * nq * (hd + 2)) in ring order for heads [h0, h0 + nh) and applies the gate */
+ * caller, parts[p] at parts + p * T * nq * (hd + 2)) in ring order for heads [h0, h0 + nh) and applies the gate:
+ * out [T][nh][hd] */
 size_t fnx_attn_scratch_floats(int nq, int hd, int T);
 int fnx_attn_partial(const float* qg, const uint16_t* kc, const uint16_t* vc, FnxKvPages g, float* part, int card, int ncard, int T,
                      const int* pos0, int nq, int nkv, int hd, float* scratch, void* st);
@@ -156,6 +161,96 @@ int fnx_penalize_row(float* row, int n, const int* pen, const float* par, void* 
 /* reference src/kernels.hpp:393-394 top_tokens (src/topk.cuh:17-138) */
 int fnx_top_tokens(float* logits, int n, int T, int v0, const int* pen_tok, const int* pen_cnt, const int* pen_n, int pen_stride,
                    const float* pen_par, float* out_v, int* out_i, unsigned* err, void* st);
+
+/* ---- the window: every GPU's work for one verify window of T rows over a stack of layers, in stream order.
+ * The counterpart of the reference's Engine::enqueue / ffn_half / attention (src/engine.cu:900-1054), without the
+ * hyper-connection, QSA and n-gram blocks: each layer is (RMS norm -> DeltaNet or attention mixer -> sum across GPUs ->
+ * residual) then (RMS norm -> routed + shared experts -> sum across GPUs -> residual); then the head.  The caller owns
+ * all memory: weights and states through FnxLayer, everything a window writes through one workspace. */
+typedef struct FnxStackCfg {
+    int n, nexp, topk, ff; /* hidden width, experts, picks per row, this GPU's FF slice */
+    int nk, nv;            /* this GPU's DeltaNet key and value heads */
+    int nq, nkv, hd, nrot; /* attention: query heads, KV heads, head dim, rotary width */
+    int vocab0, vocab_rows; /* this GPU's vocabulary slice [vocab0, vocab0 + vocab_rows) */
+    int nlayers, ncard, card;
+    float eps, rope_base;
+} FnxStackCfg;
+
+typedef struct FnxLayer {
+    int kind; /* 0: Gated DeltaNet, 1: attention */
+    const float *norm1, *norm2;
+    /* DeltaNet (reference LayerW: attn_qkv + attn_gate as qkvz, ssm_alpha/beta as ab, ssm_conv1d, ssm_dt.bias, ssm_a,
+     * ssm_norm, ssm_out; src/model.cpp:759-836) and its per-sequence state */
+    FnxQ8S qkvz;
+    const float* ab;
+    const float *conv, *dt, *a, *ssm_norm;
+    FnxQ8S ssm_out;
+    const int* vmap;
+    float *S, *hist, *snap, *hsnap;
+    /* attention (attn_q, attn_k, attn_v, attn_output, attn_q_norm, attn_k_norm) and its K/V cache */
+    FnxQ8S wq, wk, wv, wo;
+    const float *q_norm, *k_norm;
+    uint16_t *kc, *vc;
+    FnxKvPages pages;
+    /* FFN (ffn_gate_inp + ffn_gate_inp_shexp as router rows, ffn_gate_exps | ffn_up_exps stacked, ffn_down_exps,
+     * ffn_{gate,up,down}_shexp) */
+    const float* router;
+    FnxExperts gate_up, down;
+    FnxQ8S sh_gate_up, sh_down;
+} FnxLayer;
+
+typedef struct FnxHead {
+    const float* norm;
+    FnxQ8S out;
+} FnxHead;
+
+/* what the caller must do across GPUs after a stage (nothing when ncard is 1) */
+enum { FNX_AFTER_NONE = 0, FNX_AFTER_SUM_BO = 1, FNX_AFTER_GATHER_PARTIALS = 2, FNX_AFTER_GATHER_BEST = 3 };
+/* workspace buffers a caller reads or writes */
+enum { FNX_BUF_X = 0, FNX_BUF_BO = 1, FNX_BUF_PARTIALS = 2, FNX_BUF_BEST_V = 3, FNX_BUF_BEST_I = 4, FNX_BUF_ERR = 5, FNX_BUF_CTL = 6,
+       FNX_BUF_LOGITS = 7, FNX_BUF_COPY_JOBS = 8, FNX_BUF_NJOBS = 9 };
+
+size_t fnx_window_workspace_bytes(const FnxStackCfg* cfg);
+/* zeroes the counters the kernels expect at zero (once, before the first window) */
+int fnx_window_init(const FnxStackCfg* cfg, void* ws, void* st);
+/* the stages of a window over these layers: returns their number and fills after[i] (up to max) */
+int fnx_window_plan(const FnxStackCfg* cfg, const FnxLayer* layers, int* after, int max);
+/* enqueues stage `stage` of a window of T rows: the input rows are in FNX_BUF_X (f32 [T][n]), the position and the
+ * window tag in FNX_BUF_CTL (int [2]); capture-safe */
+int fnx_window_stage(const FnxStackCfg* cfg, const FnxLayer* layers, const FnxHead* head, void* ws, int T, int stage, void* st);
+void* fnx_window_buf(const FnxStackCfg* cfg, void* ws, int which);
+/* keep the first n of the last window's T rows (reference Engine::commit, src/engine_common.cu:525-568): per DeltaNet
+ * layer S <- snap[n-1] and the written history half <- hsnap[n-1]; tag is the window's tag (its parity names the
+ * half).  host_jobs: pinned host memory for nlayers * 2 FnxCopyJob, copied to FNX_BUF_COPY_JOBS */
+int fnx_window_commit(const FnxStackCfg* cfg, const FnxLayer* layers, void* ws, int T, int n, int tag, void* host_jobs, void* st);
+
+/* per-call timing of windows enqueued outside a graph (the reference's engine keeps per-window timers,
+ * src/engine.hpp:182-187): between fnx_trace_begin and fnx_trace_end every C ABI call of fnx_window_stage is bracketed by
+ * CUDA events on its stream; fnx_trace_end waits for them and returns each call's name, layer and milliseconds.
+ * fnx_window_kernel_count: kernels launched through fnx_window_stage so far (reset != 0 zeroes the count) */
+int fnx_trace_begin(void);
+int fnx_trace_end(float* ms, int* layer, const char** names, int cap);
+long fnx_window_kernel_count(int reset);
+
+/* ---- acceptance on the host (reference src/session.cpp:39-82, 469-510) */
+typedef struct FnxSampling {
+    float temperature, top_p, min_p;
+    int top_k;
+} FnxSampling;
+/* rows[0] the last committed token, rows[1..T) the drafts, out[t] row t's argmax: 1 + the matching prefix */
+int fnx_accept_greedy(const int* rows, const int* out, int T);
+/* rejection sampling against fixed (one-hot) drafts over the rows' 64 candidates; rng: a std::mt19937_64 stream made
+ * by fnx_rng_new(seed); o receives the emitted tokens; returns their number */
+void* fnx_rng_new(unsigned long long seed);
+void fnx_rng_free(void* rng);
+int fnx_accept_sampled(const int* rows, int T, const float* cand_v, const int* cand_i, const FnxSampling* s, void* rng, int* o);
+/* merges nslice per-GPU candidate lists [nslice][T][64] into the rows' 64 best (reference src/engine_common.cu:640-653) */
+int fnx_top_merge(const float* vs, const int* is, int nslice, int T, float* out_v, int* out_i);
+/* the partition rule (reference src/card_split.hpp:12-26): FF slice, value-head owner, key heads of a GPU */
+int fnx_ff_lo(int ff, int n, int c);
+int fnx_vhead_card(int nkh, int nvh, int n, int v);
+int fnx_khead_first(int nkh, int nvh, int n, int c);
+int fnx_khead_count(int nkh, int nvh, int n, int c);
 
 /* ---- load-time repacks (the reference's loader does the same kind of work, src/model.cpp:554-606) */
 /* GGUF Q8_0 blocks [rows][cols / 32] -> split layout */

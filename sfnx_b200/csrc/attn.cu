@@ -184,7 +184,7 @@ __global__ void k_attn_local(const float* __restrict__ acc_in, const AttPart* __
 }
 
 // the GPUs' partials of head h0 + blockIdx.x merged in ring order starting at partial `first` + 1 and ending with
-// `first` (the head's owner): ((P[f+1] + P[f+2]) + ...) + P[f]; out = a / z * sigmoid(gate)
+// `first` (the head's owner): ((P[f+1] + P[f+2]) + ...) + P[f]; out[t][head - h0] = a / z * sigmoid(gate)
 __global__ void k_attn_finish(const float* __restrict__ parts, int nparts, int first, const float* __restrict__ qg,
                               float* __restrict__ out, int nq, int h0, int hd) {
     const int h = h0 + blockIdx.x, t = blockIdx.y, i = threadIdx.x, T = gridDim.y;
@@ -200,7 +200,7 @@ __global__ void k_attn_finish(const float* __restrict__ parts, int nparts, int f
         a = ffma(w2, p2[i], fmul(w1, a));
         m = mn;
     }
-    out[((size_t) t * nq + h) * hd + i] = fmul(fdiv(a, z), ex_sigmoid(qg[((size_t) t * nq + h) * 2 * hd + hd + i]));
+    out[((size_t) t * gridDim.x + blockIdx.x) * hd + i] = fmul(fdiv(a, z), ex_sigmoid(qg[((size_t) t * nq + h) * 2 * hd + hd + i]));
 }
 
 }  // namespace fnxk

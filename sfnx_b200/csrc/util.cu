@@ -233,6 +233,12 @@ __global__ void k_synth_q6k(uint8_t* blocks, size_t nblocks, float sigma, unsign
     }
 }
 
+// x[t][:] = table[ids[t]][:] (f16 rows -> f32): the window's input rows from a device-resident embedding table
+__global__ void k_embed_rows(const uint16_t* __restrict__ table, const int* __restrict__ ids, float* __restrict__ x, int n) {
+    const int t = blockIdx.y, i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) x[(size_t) t * n + i] = h2f(table[(size_t) ids[t] * n + i]);
+}
+
 __global__ void k_math_probe(int op, const float* x, float* y, size_t n) {
     const size_t i = (size_t) blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
@@ -317,6 +323,12 @@ int fnx_synth_quant(int type, void* blocks, size_t nvalues, float sigma, unsigne
         return fail("synth_quant: type %d is not Q4_K, Q6_K or Q8_0", type);
     }
     return launch_ok("synth_quant");
+}
+
+int fnx_embed_rows(const uint16_t* table, const int* ids, float* x, int T, int n, void* st) {
+    if (T <= 0 || n <= 0) return 0;
+    k_embed_rows<<<dim3((n + 255) / 256, T), 256, 0, strm(st)>>>(table, ids, x, n);
+    return launch_ok("embed_rows");
 }
 
 int fnx_math_probe(int op, const float* x, float* y, size_t n, void* st) {

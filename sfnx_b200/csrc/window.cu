@@ -1,0 +1,338 @@
+// The window: one verify window of T rows over a stack of layers, enqueued stage by stage on a stream, and the
+// rollback after acceptance.  Host code only (the counterpart of the reference's Engine::enqueue, ffn_half, attention
+// and commit: src/engine.cu:900-1054, src/engine_common.cu:525-568); every kernel goes through the same C ABI entry
+// points an external caller would use.  The stages end where the GPUs must exchange data, so that a caller driving
+// several GPUs can put its collective between two stages.
+#include <cstring>
+
+#include "common.cuh"
+
+namespace fnxk {
+
+static inline size_t al(size_t v) { return (v + 255) & ~(size_t) 255; }
+
+// per-call timing of a window enqueued outside a graph: an event before and after every C ABI call of a stage, and the
+// count of kernels the calls launch (the engine's own per-window timers are the reference's counterpart,
+// src/engine.hpp:182-187)
+constexpr int TRACE_CAP = 4096;
+struct Trace {
+    bool on = false;
+    int n = 0;
+    cudaEvent_t ev[2 * TRACE_CAP];
+    const char* name[TRACE_CAP];
+    int layer[TRACE_CAP];
+    bool made = false;
+    long kernels = 0;
+};
+static Trace g_trace;
+
+struct Traced {
+    int slot = -1;
+    cudaStream_t st;
+    Traced(const char* name, int layer, int kernels, void* stream) : st((cudaStream_t) stream) {
+        g_trace.kernels += kernels;
+        if (!g_trace.on || g_trace.n >= TRACE_CAP) return;
+        slot = g_trace.n++;
+        g_trace.name[slot] = name;
+        g_trace.layer[slot] = layer;
+        cudaEventRecord(g_trace.ev[2 * slot], st);
+    }
+    ~Traced() {
+        if (slot >= 0) cudaEventRecord(g_trace.ev[2 * slot + 1], st);
+    }
+};
+
+// the workspace's buffers, as offsets from its base
+struct Ws {
+    size_t x, bo, xn, xq, qkvz, ab, yq, qg, k, v, att, partials, att_scratch, rlogits, topi, topw, jobs_gu, jobs_dn, njobs, rscratch, gu,
+        hq, part, sh_gu, shq, sh, logits, keys, best_v, best_i, err, ctl, gdn_scratch, copy_jobs, total;
+};
+
+static Ws carve(const FnxStackCfg& c) {
+    Ws w;
+    size_t o = 0;
+    const size_t T = FNX_MAXT, n = c.n, P = T * c.topk;
+    auto take = [&](size_t bytes) {
+        const size_t at = o;
+        o += al(bytes);
+        return at;
+    };
+    const size_t gdn_rows = (size_t) (2 * c.nk + 2 * c.nv) * FNX_HS, vwidth = (size_t) c.nv * FNX_HS, qwidth = (size_t) c.nq * c.hd;
+    const size_t widest = vwidth > qwidth ? vwidth : qwidth;
+    w.x = take(T * n * 4);
+    w.bo = take(T * n * 4);
+    w.xn = take(T * n * 4);
+    w.xq = take(T * ((n > widest ? n : widest) / 32) * 36);
+    w.qkvz = take(T * gdn_rows * 4);
+    w.ab = take(T * 2 * c.nv * 4);
+    w.yq = take(T * (widest / 32) * 36);
+    w.qg = take(T * qwidth * 2 * 4);
+    w.k = take(T * (size_t) c.nkv * c.hd * 4);
+    w.v = take(T * (size_t) c.nkv * c.hd * 4);
+    w.att = take(T * qwidth * 4);
+    w.partials = take((size_t) c.ncard * T * c.nq * (c.hd + 2) * 4);
+    w.att_scratch = take(fnx_attn_scratch_floats(c.nq, c.hd, (int) T) * 4);
+    w.rlogits = take(T * (c.nexp + 1) * 4);
+    w.topi = take(P * 4);
+    w.topw = take(P * 4);
+    w.jobs_gu = take(P * sizeof(FnxJob));
+    w.jobs_dn = take(P * sizeof(FnxJob));
+    w.njobs = take(16);
+    w.rscratch = take(fnx_router_scratch_bytes());
+    w.gu = take(P * 2 * (size_t) c.ff * 4);
+    w.hq = take(fnx_moe_h_bytes((int) P, c.ff));
+    w.part = take(P * n * 4);
+    w.sh_gu = take(T * 2 * (size_t) c.ff * 4);
+    w.shq = take(fnx_moe_h_bytes((int) T, c.ff));
+    w.sh = take(T * n * 4);
+    w.logits = take(T * (size_t) c.vocab_rows * 4);
+    w.keys = take(T * 8);
+    w.best_v = take(T * 4);
+    w.best_i = take(T * 4);
+    w.err = take(16);
+    w.ctl = take(16);
+    w.gdn_scratch = take(fnx_gdn_scratch_floats(c.nv) * 4);
+    w.copy_jobs = take((size_t) c.nlayers * 2 * sizeof(FnxCopyJob));
+    w.total = o;
+    return w;
+}
+
+static int check_cfg(const FnxStackCfg* c) {
+    if (!c) return fail("window: no configuration");
+    if (c->n <= 0 || c->n % 512 || c->ff <= 0 || c->ff % 32 || c->nlayers < 1 || c->ncard < 1 || c->card < 0 || c->card >= c->ncard)
+        return fail("window: hidden %d, ff slice %d, %d layers, GPU %d of %d", c->n, c->ff, c->nlayers, c->card, c->ncard);
+    if (c->topk < 1 || c->topk > 16 || c->nq % c->ncard) return fail("window: top-%d, %d query heads over %d GPUs", c->topk, c->nq, c->ncard);
+    return 0;
+}
+
+// stage s of the plan: which layer, which part (0 mixer / first attention part, 1 attention finish, 2 FFN, 3 head)
+struct Stage {
+    int layer, part;
+};
+static int plan(const FnxStackCfg& c, const FnxLayer* L, Stage* out, int* after, int max) {
+    int s = 0;
+    auto put = [&](int layer, int part, int aft) {
+        if (s < max) {
+            if (out) out[s] = Stage{layer, part};
+            if (after) after[s] = aft;
+        }
+        ++s;
+    };
+    for (int l = 0; l < c.nlayers; ++l) {
+        if (L[l].kind == 1) {
+            put(l, 0, FNX_AFTER_GATHER_PARTIALS);
+            put(l, 1, FNX_AFTER_SUM_BO);
+        } else {
+            put(l, 0, FNX_AFTER_SUM_BO);
+        }
+        put(l, 2, FNX_AFTER_SUM_BO);
+    }
+    put(c.nlayers, 3, FNX_AFTER_GATHER_BEST);
+    return s;
+}
+
+}  // namespace fnxk
+
+using namespace fnxk;
+
+#define TRY(call)         \
+    do {                  \
+        if (call) return 1; \
+    } while (0)
+// a traced call: name, kernels it launches
+#define TRK(name, kernels, call)                      \
+    do {                                              \
+        Traced tr_(name, sg.layer, kernels, st);      \
+        if (call) return 1;                           \
+    } while (0)
+
+extern "C" {
+
+size_t fnx_window_workspace_bytes(const FnxStackCfg* cfg) {
+    if (check_cfg(cfg)) return 0;
+    return carve(*cfg).total;
+}
+
+void* fnx_window_buf(const FnxStackCfg* cfg, void* ws, int which) {
+    if (check_cfg(cfg) || !ws) return nullptr;
+    const Ws w = carve(*cfg);
+    char* b = (char*) ws;
+    switch (which) {
+        case FNX_BUF_X: return b + w.x;
+        case FNX_BUF_BO: return b + w.bo;
+        case FNX_BUF_PARTIALS: return b + w.partials;
+        case FNX_BUF_BEST_V: return b + w.best_v;
+        case FNX_BUF_BEST_I: return b + w.best_i;
+        case FNX_BUF_ERR: return b + w.err;
+        case FNX_BUF_CTL: return b + w.ctl;
+        case FNX_BUF_LOGITS: return b + w.logits;
+        case FNX_BUF_COPY_JOBS: return b + w.copy_jobs;
+        case FNX_BUF_NJOBS: return b + w.njobs;
+    }
+    fail("window_buf: no buffer %d", which);
+    return nullptr;
+}
+
+int fnx_window_init(const FnxStackCfg* cfg, void* ws, void* st) {
+    TRY(check_cfg(cfg));
+    const Ws w = carve(*cfg);
+    char* b = (char*) ws;
+    auto zero = [&](size_t at, size_t bytes) { return cudaMemsetAsync(b + at, 0, bytes, strm(st)) != cudaSuccess; };
+    if (zero(w.rscratch, fnx_router_scratch_bytes()) || zero(w.keys, FNX_MAXT * 8) || zero(w.err, 16) || zero(w.njobs, 16) ||
+        zero(w.gdn_scratch, fnx_gdn_scratch_floats(cfg->nv) * 4))
+        return fail("window_init: %s", cudaGetErrorString(cudaGetLastError()));
+    return 0;
+}
+
+int fnx_window_plan(const FnxStackCfg* cfg, const FnxLayer* layers, int* after, int max) {
+    if (check_cfg(cfg) || !layers) return -1;
+    return plan(*cfg, layers, nullptr, after, max);
+}
+
+int fnx_window_stage(const FnxStackCfg* cfg, const FnxLayer* layers, const FnxHead* head, void* ws, int T, int stage, void* st) {
+    TRY(check_cfg(cfg));
+    FNX_REQUIRE(T >= 1 && T <= FNX_MAXT, "window: T %d outside 1..%d", T, FNX_MAXT);
+    const FnxStackCfg& c = *cfg;
+    Stage stages[1024];
+    const int ns = plan(c, layers, stages, nullptr, 1024);
+    FNX_REQUIRE(ns <= 1024 && stage >= 0 && stage < ns, "window: stage %d of %d", stage, ns);
+    const Stage sg = stages[stage];
+    const Ws w = carve(c);
+    char* b = (char*) ws;
+    float* x = (float*) (b + w.x);
+    float* bo = (float*) (b + w.bo);
+    float* xn = (float*) (b + w.xn);
+    void* xq = b + w.xq;
+    const int* ctl = (const int*) (b + w.ctl);
+    // the previous half's output is still pending: every stage that reads x first folds bo into it (not stage 0, and
+    // not the attention's second part, which continues its own layer's mixer)
+    const float* pending = stage == 0 ? nullptr : bo;
+    if (sg.part == 3) {
+        FNX_REQUIRE(head, "window: no head");
+        TRK("rms_norm", 1, fnx_rms_norm_rows(x, pending, head->norm, nullptr, xq, T, c.n, c.eps, st));
+        float* logits = (float*) (b + w.logits);
+        TRK("head", 1, fnx_q8s_gemv(head->out, c.vocab_rows, c.n, xq, logits, c.vocab_rows, T, st));
+        TRK("argmax", 2, fnx_argmax(logits, c.vocab_rows, T, c.vocab0, (float*) (b + w.best_v), (int*) (b + w.best_i),
+                                    (unsigned long long*) (b + w.keys), (unsigned*) (b + w.err), st));
+        return 0;
+    }
+    const FnxLayer& L = layers[sg.layer];
+    if (sg.part == 0 && L.kind == 0) {   // Gated DeltaNet mixer
+        const int rows = (2 * c.nk + 2 * c.nv) * FNX_HS;
+        TRK("rms_norm", 1, fnx_rms_norm_rows(x, pending, L.norm1, xn, xq, T, c.n, c.eps, st));
+        TRK("qkvz", 1, fnx_q8s_gemv(L.qkvz, rows, c.n, xq, (float*) (b + w.qkvz), rows, T, st));
+        TRK("ab", 1, fnx_gemv_f32(L.ab, xn, (float*) (b + w.ab), 2 * c.nv, c.n, T, st));
+        TRK("gdn_core", 1, fnx_gdn_core((const float*) (b + w.qkvz), (const float*) (b + w.ab), L.hist, L.conv, L.dt, L.a, L.ssm_norm, L.S,
+                                        b + w.yq, ctl, (float*) (b + w.gdn_scratch), L.snap, L.hsnap, c.nk, c.nv, L.vmap, T, c.eps, st, nullptr));
+        TRK("ssm_out", 1, fnx_q8s_gemv(L.ssm_out, c.n, c.nv * FNX_HS, b + w.yq, bo, c.n, T, st));
+        return 0;
+    }
+    if (sg.part == 0) {   // attention, up to this GPU's partials
+        float* qg = (float*) (b + w.qg);
+        float* k = (float*) (b + w.k);
+        float* v = (float*) (b + w.v);
+        TRK("rms_norm", 1, fnx_rms_norm_rows(x, pending, L.norm1, nullptr, xq, T, c.n, c.eps, st));
+        TRK("wq", 1, fnx_q8s_gemv(L.wq, c.nq * c.hd * 2, c.n, xq, qg, c.nq * c.hd * 2, T, st));
+        TRK("wk", 1, fnx_q8s_gemv(L.wk, c.nkv * c.hd, c.n, xq, k, c.nkv * c.hd, T, st));
+        TRK("wv", 1, fnx_q8s_gemv(L.wv, c.nkv * c.hd, c.n, xq, v, c.nkv * c.hd, T, st));
+        const FnxRope rope{c.rope_base, c.nrot};
+        TRK("attn_prep_append", 1, fnx_attn_prep_append(qg, k, v, L.q_norm, L.k_norm, L.kc, L.vc, L.pages, c.card, c.ncard, T, ctl, c.eps,
+                                                        rope, c.nq, c.nkv, c.hd, st));
+        float* mine = (float*) (b + w.partials) + (size_t) c.card * T * c.nq * (c.hd + 2);
+        TRK("attn_partial", 2, fnx_attn_partial(qg, L.kc, L.vc, L.pages, mine, c.card, c.ncard, T, ctl, c.nq, c.nkv, c.hd,
+                                                (float*) (b + w.att_scratch), st));
+        return 0;
+    }
+    if (sg.part == 1) {   // attention: merge the GPUs' partials for this GPU's heads, gate, output projection
+        const int own = c.nq / c.ncard;
+        float* att = (float*) (b + w.att);
+        TRK("attn_finish", 1, fnx_attn_finish((const float*) (b + w.partials), c.ncard, c.card, (const float*) (b + w.qg), att, T, c.nq,
+                                              c.card * own, own, c.hd, st));
+        TRK("quantize", 1, fnx_quantize_q8_1(att, b + w.yq, own * c.hd, T, st));
+        TRK("wo", 1, fnx_q8s_gemv(L.wo, c.n, own * c.hd, b + w.yq, bo, c.n, T, st));
+        return 0;
+    }
+    // FFN half
+    const int P = T * c.topk;
+    float* rl = (float*) (b + w.rlogits);
+    TRK("rms_norm", 1, fnx_rms_norm_rows(x, pending, L.norm2, xn, xq, T, c.n, c.eps, st));
+    TRK("router_route", 1, fnx_router_route(L.router, xn, rl, T, c.n, c.nexp, c.topk, (int*) (b + w.topi), (float*) (b + w.topw),
+                                            (FnxJob*) (b + w.jobs_gu), (FnxJob*) (b + w.jobs_dn), (int*) (b + w.njobs), b + w.rscratch, st));
+    TRK("moe_gate_up", 1, fnx_moe_gate_up(&L.gate_up, (const FnxJob*) (b + w.jobs_gu), (const int*) (b + w.njobs), P, xq, (float*) (b + w.gu), st));
+    TRK("moe_down", 2, fnx_moe_down(&L.down, (const FnxJob*) (b + w.jobs_dn), (const int*) (b + w.njobs), P, (const float*) (b + w.gu), P,
+                                    b + w.hq, (float*) (b + w.part), st));
+    TRK("shared_expert", 3, fnx_shared_expert(L.sh_gate_up, L.sh_down, xq, T, c.n, c.ff, (float*) (b + w.sh_gu), b + w.shq, (float*) (b + w.sh), st));
+    TRK("moe_combine", 1, fnx_moe_combine((const float*) (b + w.part), (const float*) (b + w.topw), (const float*) (b + w.sh), rl, c.nexp, bo,
+                                          T, c.n, c.topk, st));
+    return 0;
+}
+
+int fnx_window_commit(const FnxStackCfg* cfg, const FnxLayer* layers, void* ws, int T, int n, int tag, void* host_jobs, void* st) {
+    TRY(check_cfg(cfg));
+    FNX_REQUIRE(T >= 1 && T <= FNX_MAXT && n >= 1 && n <= T, "commit: %d of %d rows", n, T);
+    if (n == T) return 0;
+    const FnxStackCfg& c = *cfg;
+    const Ws w = carve(c);
+    FnxCopyJob* hj = (FnxCopyJob*) host_jobs;
+    FNX_REQUIRE(hj, "commit: no host job table");
+    const size_t ch = (size_t) (2 * c.nk + c.nv) * FNX_HS, state = (size_t) c.nv * FNX_HS * FNX_HS;
+    const unsigned written = ((unsigned) tag & 1u) ^ 1u;   // the window read half (tag & 1) and wrote the other
+    int nj = 0;
+    for (int l = 0; l < c.nlayers; ++l) {
+        if (layers[l].kind != 0) continue;
+        hj[nj++] = FnxCopyJob{layers[l].S, layers[l].snap + (size_t) (n - 1) * state, state * 4};
+        hj[nj++] = FnxCopyJob{layers[l].hist + (size_t) written * 3 * ch, layers[l].hsnap + (size_t) (n - 1) * 3 * ch, 3 * ch * 4};
+    }
+    if (!nj) return 0;
+    FnxCopyJob* dj = (FnxCopyJob*) ((char*) ws + w.copy_jobs);
+    if (cudaMemcpyAsync(dj, hj, (size_t) nj * sizeof(FnxCopyJob), cudaMemcpyHostToDevice, strm(st)) != cudaSuccess)
+        return fail("commit: job table upload: %s", cudaGetErrorString(cudaGetLastError()));
+    return fnx_copy_many(dj, nj, st);
+}
+
+// ---- per-call trace of windows enqueued outside a graph
+int fnx_trace_begin(void) {
+    if (!g_trace.made) {
+        for (int i = 0; i < 2 * TRACE_CAP; ++i)
+            if (cudaEventCreate(&g_trace.ev[i]) != cudaSuccess) return fail("trace: event create failed");
+        g_trace.made = true;
+    }
+    g_trace.n = 0;
+    g_trace.on = true;
+    return 0;
+}
+// stops tracing; after the stream has drained, fills ms[i], layer[i] and name pointers for the traced calls (up to cap);
+// returns how many there were
+int fnx_trace_end(float* ms, int* layer, const char** names, int cap) {
+    g_trace.on = false;
+    int n = g_trace.n < cap ? g_trace.n : cap;
+    for (int i = 0; i < n; ++i) {
+        if (cudaEventSynchronize(g_trace.ev[2 * i + 1]) != cudaSuccess) return -1;
+        cudaEventElapsedTime(&ms[i], g_trace.ev[2 * i], g_trace.ev[2 * i + 1]);
+        layer[i] = g_trace.layer[i];
+        names[i] = g_trace.name[i];
+    }
+    return n;
+}
+// kernels launched by fnx_window_stage calls since the last reset (reset != 0: read and zero)
+long fnx_window_kernel_count(int reset) {
+    const long k = g_trace.kernels;
+    if (reset) g_trace.kernels = 0;
+    return k;
+}
+
+// ---- the partition rule (reference src/card_split.hpp:12-26)
+int fnx_ff_lo(int ff, int n, int c) {
+    const int B = ff / 32;
+    return 32 * (c * (B / n) + (c < B % n ? c : B % n));
+}
+int fnx_vhead_card(int nkh, int nvh, int n, int v) {
+    const int vpk = nvh / nkh;
+    return ((v % nkh) * vpk + v / nkh) / (nvh / n);
+}
+int fnx_khead_first(int nkh, int nvh, int n, int c) { return c * (nvh / n) / (nvh / nkh); }
+int fnx_khead_count(int nkh, int nvh, int n, int c) {
+    const int vpk = nvh / nkh;
+    return ((c + 1) * (nvh / n) - 1) / vpk - fnx_khead_first(nkh, nvh, n, c) + 1;
+}
+}

@@ -41,6 +41,29 @@ class Rope(C.Structure):
     _fields_ = [("base", C.c_float), ("nrot", C.c_int)]
 
 
+class StackCfg(C.Structure):
+    _fields_ = [(k, C.c_int) for k in ("n", "nexp", "topk", "ff", "nk", "nv", "nq", "nkv", "hd", "nrot", "vocab0", "vocab_rows",
+                                        "nlayers", "ncard", "card")] + [("eps", C.c_float), ("rope_base", C.c_float)]
+
+
+class Layer(C.Structure):
+    _fields_ = [("kind", C.c_int), ("norm1", C.c_void_p), ("norm2", C.c_void_p),
+                ("qkvz", Q8S), ("ab", C.c_void_p), ("conv", C.c_void_p), ("dt", C.c_void_p), ("a", C.c_void_p),
+                ("ssm_norm", C.c_void_p), ("ssm_out", Q8S), ("vmap", C.c_void_p),
+                ("S", C.c_void_p), ("hist", C.c_void_p), ("snap", C.c_void_p), ("hsnap", C.c_void_p),
+                ("wq", Q8S), ("wk", Q8S), ("wv", Q8S), ("wo", Q8S), ("q_norm", C.c_void_p), ("k_norm", C.c_void_p),
+                ("kc", C.c_void_p), ("vc", C.c_void_p), ("pages", KvPages),
+                ("router", C.c_void_p), ("gate_up", Experts), ("down", Experts), ("sh_gate_up", Q8S), ("sh_down", Q8S)]
+
+
+class Head(C.Structure):
+    _fields_ = [("norm", C.c_void_p), ("out", Q8S)]
+
+
+class Sampling(C.Structure):
+    _fields_ = [("temperature", C.c_float), ("top_p", C.c_float), ("min_p", C.c_float), ("top_k", C.c_int)]
+
+
 class CopyJob(C.Structure):
     _fields_ = [("dst", C.c_void_p), ("src", C.c_void_p), ("bytes", C.c_size_t)]
 
@@ -71,6 +94,11 @@ _SIGS = {
     "fnx_synth_normal": [_p, _z, _f, _u64, _p],
     "fnx_synth_quant": [_i, _p, _z, _f, _u64, _p],
     "fnx_math_probe": [_i, _p, _p, _z, _p],
+    "fnx_embed_rows": [_p, _p, _p, _i, _i, _p],
+    "fnx_window_init": [_p, _p, _p],
+    "fnx_window_stage": [_p, _p, _p, _p, _i, _i, _p],
+    "fnx_window_commit": [_p, _p, _p, _i, _i, _i, _p, _p],
+    "fnx_top_merge": [_p, _p, _i, _i, _p, _p],
 }
 _OTHER = {
     "fnx_last_error": (C.c_char_p, []),
@@ -80,6 +108,20 @@ _OTHER = {
     "fnx_gdn_scratch_floats": (_z, [_i]),
     "fnx_attn_scratch_floats": (_z, [_i, _i, _i]),
     "fnx_kv_rows_per_card": (_i, [_i, _i]),
+    "fnx_window_workspace_bytes": (_z, [_p]),
+    "fnx_window_plan": (_i, [_p, _p, _p, _i]),
+    "fnx_window_buf": (_p, [_p, _p, _i]),
+    "fnx_accept_greedy": (_i, [_p, _p, _i]),
+    "fnx_trace_begin": (_i, []),
+    "fnx_trace_end": (_i, [_p, _p, _p, _i]),
+    "fnx_window_kernel_count": (C.c_long, [_i]),
+    "fnx_rng_new": (_p, [_u64]),
+    "fnx_rng_free": (None, [_p]),
+    "fnx_accept_sampled": (_i, [_p, _i, _p, _p, _p, _p, _p]),
+    "fnx_ff_lo": (_i, [_i, _i, _i]),
+    "fnx_vhead_card": (_i, [_i, _i, _i, _i]),
+    "fnx_khead_first": (_i, [_i, _i, _i, _i]),
+    "fnx_khead_count": (_i, [_i, _i, _i, _i]),
 }
 
 _lib = None

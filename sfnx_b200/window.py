@@ -1,0 +1,335 @@
+"""Host-side plumbing of the verify window: a seeded synthetic stack in device memory, its slice for one GPU of several,
+and a runner that captures the window's stages (and the collectives between them) into one CUDA graph.
+
+torch is used for device memory, streams, CUDA graphs and torch.distributed (NCCL); every kernel is launched by
+libsfnx_b200.so through the C ABI.  The split across GPUs follows the reference's rule (src/card_split.hpp:12-26,
+docs/config.md:62-71): experts by FF width in 32-value blocks, DeltaNet by value heads, K/V by position in blocks of 4,
+the vocabulary in contiguous ranges; the router, the norms and the embeddings are copied.
+"""
+import ctypes as C
+from dataclasses import dataclass, field
+
+import torch
+
+from . import lib as L
+
+
+@dataclass
+class StackShape:
+    """The whole model's shapes (the benchmark configurations' defaults)."""
+    n: int = 3072
+    nexp: int = 512
+    topk: int = 10
+    ff: int = 768
+    nkh: int = 16
+    nvh: int = 48
+    nq: int = 24
+    nkv: int = 4
+    hd: int = 256
+    nrot: int = 64
+    vocab: int = 151936
+    kinds: list = field(default_factory=lambda: [0, 0, 0, 1, 0, 0, 0, 1])   # 0 DeltaNet, 1 attention
+    ctx: int = 32768
+    eps: float = 1e-6
+    rope_base: float = 1e7
+    sigma: float = 0.02
+
+
+def _seed(base, layer, name):
+    h = 1469598103934665603
+    for ch in ("%d/%d/%s" % (base, layer, name)).encode():
+        h = ((h ^ ch) * 1099511628211) & 0xFFFFFFFFFFFFFFFF
+    return h & 0x7FFFFFFFFFFFFFFF
+
+
+class SyntheticStack:
+    """Random-init weights and states of one GPU's slice, generated on the device from seeds: every GPU generates the
+    same full tensor and keeps its slice, so the slices of N GPUs are one model."""
+
+    def __init__(self, shape, ncard=1, card=0, seed=0, device="cuda"):
+        self.shape, self.ncard, self.card, self.seed = shape, ncard, card, seed
+        self.dev = torch.device(device)
+        self.keep = []
+        self.named = {}   # (layer, name) -> tensors, for callers that need the values (tests, CPU baselines)
+        s = shape
+        lib = L.load()
+        self.ff0 = lib.fnx_ff_lo(s.ff, ncard, card)
+        self.ffs = lib.fnx_ff_lo(s.ff, ncard, card + 1) - self.ff0
+        self.vheads = [v for v in range(s.nvh) if lib.fnx_vhead_card(s.nkh, s.nvh, ncard, v) == card]
+        self.kh0 = lib.fnx_khead_first(s.nkh, s.nvh, ncard, card)
+        self.nk = lib.fnx_khead_count(s.nkh, s.nvh, ncard, card)
+        self.nv = len(self.vheads)
+        per = (s.vocab + ncard - 1) // ncard
+        self.v0 = card * per
+        self.vrows = max(0, min(s.vocab, self.v0 + per) - self.v0)
+        self.kv_rows = lib.fnx_kv_rows_per_card(s.ctx + 2 * L.MAXT + 4, ncard)
+        self.cfg = L.StackCfg(s.n, s.nexp, s.topk, self.ffs, self.nk, self.nv, s.nq, s.nkv, s.hd, s.nrot, self.v0, self.vrows,
+                              len(s.kinds), ncard, card, s.eps, s.rope_base)
+        self.layers = (L.Layer * len(s.kinds))()
+        self.gdn_state = []   # (S, hist) of the DeltaNet layers, for snapshots
+        for l, kind in enumerate(s.kinds):
+            self._build_layer(l, kind)
+        self.head = L.Head(self._t(torch.ones(s.n, device=self.dev)).data_ptr(), self._q8s(len(s.kinds), "output", s.vocab, s.n,
+                                                                                          row_slice=slice(self.v0, self.v0 + self.vrows)))
+        emb = torch.empty(s.vocab * s.n, dtype=torch.float32, device=self.dev)
+        L.call("fnx_synth_normal", emb.data_ptr(), emb.numel(), 1.0, _seed(seed, -1, "embed"), L.stream())
+        self.embed = self._t(emb.half().view(s.vocab, s.n).view(torch.int16))
+        del emb
+        nbytes = lib.fnx_window_workspace_bytes(C.byref(self.cfg))
+        assert nbytes > 0, lib.fnx_last_error()
+        self.ws = torch.zeros(nbytes, dtype=torch.uint8, device=self.dev)
+        L.call("fnx_window_init", C.byref(self.cfg), self.ws.data_ptr(), L.stream())
+        torch.cuda.synchronize()
+
+    # ---- tensors
+    def _t(self, t):
+        t = t.contiguous()
+        self.keep.append(t)
+        return t
+
+    def _normal(self, layer, name, shape, sigma):
+        t = torch.empty(shape, dtype=torch.float32, device=self.dev)
+        L.call("fnx_synth_normal", t.data_ptr(), t.numel(), sigma, _seed(self.seed, layer, name), L.stream())
+        return t
+
+    def _blocks(self, layer, name, qtype, nvalues):
+        bsz, per = {L.Q4_K: (144, 256), L.Q6_K: (210, 256), L.Q8_0: (34, 32)}[qtype]
+        b = torch.empty(nvalues // per * bsz, dtype=torch.uint8, device=self.dev)
+        L.call("fnx_synth_quant", qtype, b.data_ptr(), nvalues, self.shape.sigma, _seed(self.seed, layer, name), L.stream())
+        return b
+
+    def _q8s(self, layer, name, rows, cols, rows_idx=None, cols_idx=None, row_slice=None):
+        """A Q8_0 matrix [rows][cols] of the full model in the split layout, cut to this GPU's rows / 32-aligned columns."""
+        b = self._blocks(layer, name, L.Q8_0, rows * cols)
+        q = torch.empty((rows, cols), dtype=torch.int8, device=self.dev)
+        d = torch.empty((rows, cols // 32), dtype=torch.int16, device=self.dev)
+        L.call("fnx_repack_q8_0_split", b.data_ptr(), q.data_ptr(), d.data_ptr(), rows, cols, L.stream())
+        if row_slice is not None:
+            q, d = q[row_slice], d[row_slice]
+        if rows_idx is not None:
+            q, d = q[rows_idx], d[rows_idx]
+        if cols_idx is not None:
+            q = q.view(q.shape[0], cols // 32, 32)[:, cols_idx].reshape(q.shape[0], -1)
+            d = d[:, cols_idx]
+        q, d = self._t(q), self._t(d)
+        self.named[(layer, name)] = (q, d)
+        return L.Q8S(q.data_ptr(), d.data_ptr())
+
+    def _idx(self, lst):
+        return torch.tensor(lst, dtype=torch.long, device=self.dev)
+
+    def _build_layer(self, l, kind):
+        s, Lr = self.shape, self.layers[l]
+        Lr.kind = kind
+        Lr.norm1 = self._t(torch.ones(s.n, device=self.dev)).data_ptr()
+        Lr.norm2 = self._t(torch.ones(s.n, device=self.dev)).data_ptr()
+        if kind == 0:
+            HS = L.HS
+            khs = list(range(self.kh0, self.kh0 + self.nk))
+            rows = []
+            for base, heads in ((0, khs), (s.nkh * HS, khs), (2 * s.nkh * HS, self.vheads), ((2 * s.nkh + s.nvh) * HS, self.vheads)):
+                for h in heads:
+                    rows += list(range(base + h * HS, base + (h + 1) * HS))
+            Lr.qkvz = self._q8s(l, "qkvz", (2 * s.nkh + 2 * s.nvh) * HS, s.n, rows_idx=self._idx(rows))
+            ab = self._normal(l, "ab", (2 * s.nvh, s.n), s.sigma)
+            self.named[(l, "ab")] = self._t(ab[self._idx(self.vheads + [s.nvh + v for v in self.vheads])])
+            Lr.ab = self.named[(l, "ab")].data_ptr()
+            ch_full = (2 * s.nkh + s.nvh) * HS
+            conv = self._normal(l, "conv", (ch_full, 4), 0.5)
+            self.named[(l, "conv")] = self._t(conv[self._idx(rows[: (2 * self.nk + self.nv) * HS])])
+            Lr.conv = self.named[(l, "conv")].data_ptr()
+            Lr.dt = self._t(torch.zeros(self.nv, device=self.dev)).data_ptr()
+            Lr.a = self._t(-torch.ones(self.nv, device=self.dev)).data_ptr()
+            Lr.ssm_norm = self._t(torch.ones(HS, device=self.dev)).data_ptr()
+            Lr.ssm_out = self._q8s(l, "ssm_out", s.n, s.nvh * HS, cols_idx=self._idx([v * 4 + b for v in self.vheads for b in range(4)]))
+            seen, vmap = set(), []
+            for v in self.vheads:   # value head v belongs to key head v % nkh; its first value head here writes q/k history
+                kh = v % s.nkh
+                vmap.append((kh - self.kh0) | ((0 if kh in seen else 1) << 8))
+                seen.add(kh)
+            self.named[(l, "vmap")] = self._t(torch.tensor(vmap, dtype=torch.int32, device=self.dev))
+            Lr.vmap = self.named[(l, "vmap")].data_ptr()
+            S = self._t(self._normal(l, "S", (s.nvh, HS, HS), 0.1)[self._idx(self.vheads)])
+            hist = self._t(self._normal(l, "hist", (2, 3, ch_full), 1.0)[:, :, self._idx(rows[: (2 * self.nk + self.nv) * HS])])
+            snap = self._t(torch.zeros((L.MAXT - 1, self.nv, HS, HS), device=self.dev))
+            hsnap = self._t(torch.zeros((L.MAXT, 3, (2 * self.nk + self.nv) * HS), device=self.dev))
+            Lr.S, Lr.hist, Lr.snap, Lr.hsnap = S.data_ptr(), hist.data_ptr(), snap.data_ptr(), hsnap.data_ptr()
+            self.gdn_state.append((S, hist))
+            self.named[(l, "S")], self.named[(l, "hist")] = S, hist
+        else:
+            own = s.nq // self.ncard
+            Lr.wq = self._q8s(l, "wq", s.nq * s.hd * 2, s.n)
+            Lr.wk = self._q8s(l, "wk", s.nkv * s.hd, s.n)
+            Lr.wv = self._q8s(l, "wv", s.nkv * s.hd, s.n)
+            nb = s.hd // 32
+            Lr.wo = self._q8s(l, "wo", s.n, s.nq * s.hd, cols_idx=self._idx(list(range(self.card * own * nb, (self.card + 1) * own * nb))))
+            Lr.q_norm = self._t(torch.ones(s.hd, device=self.dev)).data_ptr()
+            Lr.k_norm = self._t(torch.ones(s.hd, device=self.dev)).data_ptr()
+            kv = (self.kv_rows, s.nkv, s.hd)
+            kc = self._t(self._normal(l, "kc%d" % self.card, kv, 1.0).half().view(torch.int16))
+            vc = self._t(self._normal(l, "vc%d" % self.card, kv, 1.0).half().view(torch.int16))
+            Lr.kc, Lr.vc = kc.data_ptr(), vc.data_ptr()
+            self.named[(l, "kc")], self.named[(l, "vc")] = kc, vc
+            Lr.pages = L.KvPages(None, 0, 0)
+        # FFN
+        self.named[(l, "router")] = self._t(self._normal(l, "router", (s.nexp + 1, s.n), s.sigma))
+        Lr.router = self.named[(l, "router")].data_ptr()
+        row_b = s.n // 256 * 144
+        gu = self._blocks(l, "gate_up", L.Q4_K, s.nexp * 2 * s.ff * s.n).view(s.nexp, 2, s.ff, row_b)
+        gu = self._t(gu[:, :, self.ff0:self.ff0 + self.ffs].reshape(s.nexp, 2 * self.ffs * row_b))
+        Lr.gate_up = L.Experts(L.Q4_K, 2 * self.ffs, s.n, gu.data_ptr(), None, None, None, 2 * self.ffs * row_b, 0)
+        dn = self._blocks(l, "down", L.Q6_K, s.nexp * s.n * s.ff)
+        nu, units = self.ffs // 32, s.nexp * s.n * (self.ffs // 32)
+        QL = self._t(torch.empty(units * 16, dtype=torch.uint8, device=self.dev))
+        QH = self._t(torch.empty(units * 8, dtype=torch.uint8, device=self.dev))
+        SC = self._t(torch.empty(units * 2, dtype=torch.uint8, device=self.dev))
+        D = self._t(torch.empty(units, dtype=torch.int16, device=self.dev))
+        L.call("fnx_repack_q6k_units", dn.data_ptr(), s.nexp * s.n, s.ff, self.ff0, self.ffs, QL.data_ptr(), QH.data_ptr(), SC.data_ptr(),
+               D.data_ptr(), L.stream())
+        self.named[(l, "gate_up")] = gu
+        self.named[(l, "down")] = (QL.view(s.nexp, s.n, nu, 16), QH.view(s.nexp, s.n, nu, 8), SC.view(s.nexp, s.n, nu, 2), D.view(s.nexp, s.n, nu))
+        Lr.down = L.Experts(L.Q6_K, s.n, self.ffs, QL.data_ptr(), QH.data_ptr(), SC.data_ptr(), D.data_ptr(), s.n * nu, 0)
+        ffr = list(range(self.ff0, self.ff0 + self.ffs))
+        Lr.sh_gate_up = self._q8s(l, "sh_gate_up", 2 * s.ff, s.n, rows_idx=self._idx(ffr + [s.ff + r for r in ffr]))
+        Lr.sh_down = self._q8s(l, "sh_down", s.n, s.ff, cols_idx=self._idx(list(range(self.ff0 // 32, (self.ff0 + self.ffs) // 32))))
+        torch.cuda.synchronize()
+        del dn
+
+    # ---- state
+    def save_state(self):
+        return [(S.clone(), h.clone()) for S, h in self.gdn_state]
+
+    def load_state(self, saved):
+        for (S, h), (S0, h0) in zip(self.gdn_state, saved):
+            S.copy_(S0)
+            h.copy_(h0)
+
+    def buf(self, which, dtype, numel):
+        """A tensor over one of the workspace's buffers."""
+        p = L.load().fnx_window_buf(C.byref(self.cfg), self.ws.data_ptr(), which)
+        off = p - self.ws.data_ptr()
+        return self.ws[off: off + numel * torch.empty(0, dtype=dtype).element_size()].view(dtype)
+
+    def weight_bytes(self):
+        return sum(t.numel() * t.element_size() for t in self.keep)
+
+
+class WindowRunner:
+    """One window of T rows as a CUDA graph on its own stream: embedding rows from the token ids, every stage, and
+    between stages the collectives of the process group (NCCL) when there is more than one GPU."""
+
+    def __init__(self, stack, T, group=None, graph=True):
+        import torch.distributed as dist
+
+        self.stack, self.T, self.group = stack, T, group
+        self.dist = dist if stack.ncard > 1 else None
+        cfg, s = stack.cfg, stack.shape
+        lib = L.load()
+        after = (C.c_int * 1024)()
+        self.nstages = lib.fnx_window_plan(C.byref(cfg), stack.layers, after, 1024)
+        assert 0 < self.nstages <= 1024, lib.fnx_last_error()
+        self.after = list(after[: self.nstages])
+        self.stream = torch.cuda.Stream()
+        self.ids = torch.zeros(L.MAXT, dtype=torch.int32, device=stack.dev)
+        self.x = stack.buf(0, torch.float32, T * s.n)
+        self.bo = stack.buf(1, torch.float32, T * s.n)
+        self.partials = stack.buf(2, torch.float32, stack.ncard * T * s.nq * (s.hd + 2))
+        self.best_v = stack.buf(3, torch.float32, T)
+        self.best_i = stack.buf(4, torch.int32, T)
+        self.err = stack.buf(5, torch.int32, 1)
+        self.ctl = stack.buf(6, torch.int32, 2)
+        self.logits = stack.buf(7, torch.float32, T * stack.vrows).view(T, stack.vrows)
+        # what the host reads back: every GPU's (value, index) per row and the error word
+        self.all_v = torch.zeros((stack.ncard, T), dtype=torch.float32, device=stack.dev)
+        self.all_i = torch.zeros((stack.ncard, T), dtype=torch.int32, device=stack.dev)
+        self.h_ids = torch.zeros(L.MAXT, dtype=torch.int32).pin_memory()
+        self.h_ctl = torch.zeros(2, dtype=torch.int32).pin_memory()
+        self.h_v = torch.zeros((stack.ncard, T), dtype=torch.float32).pin_memory()
+        self.h_i = torch.zeros((stack.ncard, T), dtype=torch.int32).pin_memory()
+        self.h_err = torch.zeros(1, dtype=torch.int32).pin_memory()
+        self.job_bytes = len(s.kinds) * 2 * C.sizeof(L.CopyJob)
+        self.h_jobs = torch.zeros(64 * self.job_bytes, dtype=torch.uint8).pin_memory()   # a ring of job tables
+        self.commits = 0
+        self.launches = 0
+        self.graph = None
+        with torch.cuda.stream(self.stream):
+            for _ in range(2):   # warm-up: shared-memory opt-ins, NCCL channels
+                self._enqueue()
+            self.stream.synchronize()
+            if graph:
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=self.stream):
+                    self._enqueue()
+                self.graph = g
+        torch.cuda.synchronize()
+
+    def _enqueue(self):
+        st, stack, T = torch.cuda.current_stream().cuda_stream, self.stack, self.T
+        L.call("fnx_embed_rows", stack.embed.data_ptr(), self.ids.data_ptr(), self.x.data_ptr(), T, stack.shape.n, st)
+        for i in range(self.nstages):
+            L.call("fnx_window_stage", C.byref(stack.cfg), stack.layers, C.byref(stack.head), stack.ws.data_ptr(), T, i, st)
+            if self.dist is None:
+                continue
+            if self.after[i] == 1:
+                self.dist.all_reduce(self.bo, group=self.group)
+            elif self.after[i] == 2:
+                per = self.partials.numel() // stack.ncard
+                self.dist.all_gather_into_tensor(self.partials, self.partials[stack.card * per:(stack.card + 1) * per], group=self.group)
+        if self.dist is None:
+            self.all_v[0].copy_(self.best_v)
+            self.all_i[0].copy_(self.best_i)
+        else:
+            self.dist.all_gather_into_tensor(self.all_v.view(-1), self.best_v, group=self.group)
+            self.dist.all_gather_into_tensor(self.all_i.view(-1), self.best_i, group=self.group)
+
+    def launch(self):
+        """Enqueues one window on the runner's stream (the caller has set ids and ctl)."""
+        with torch.cuda.stream(self.stream):
+            if self.graph is not None:
+                self.graph.replay()
+            else:
+                self._enqueue()
+
+    def window(self, rows, pos0, tag):
+        """One window from host token ids: uploads ids and (position, tag), runs, reads back every row's argmax (merged
+        across GPUs: the lower GPU wins a tie) and the error word.  Returns the argmax tokens as a list."""
+        T = self.T
+        self.h_ids[:T] = torch.as_tensor(rows, dtype=torch.int32)
+        self.h_ctl[0], self.h_ctl[1] = pos0, tag
+        with torch.cuda.stream(self.stream):
+            self.ids.copy_(self.h_ids, non_blocking=True)
+            self.ctl.copy_(self.h_ctl, non_blocking=True)
+            self.launch()
+            self.h_v.copy_(self.all_v, non_blocking=True)
+            self.h_i.copy_(self.all_i, non_blocking=True)
+            self.h_err.copy_(self.err, non_blocking=True)
+        self.stream.synchronize()
+        if int(self.h_err[0]) != 0:
+            raise L.FnxError("window error word %d (bit 16: a non-finite logit)" % int(self.h_err[0]))
+        return self.merge_best()
+
+    def merge_best(self):
+        v, i = self.h_v, self.h_i
+        out = []
+        for t in range(self.T):
+            b = 0
+            for c in range(1, self.stack.ncard):
+                if v[c, t] > v[b, t]:
+                    b = c
+            out.append(int(i[b, t]))
+        return out
+
+    def commit(self, n, tag):
+        """Keep the first n rows of the last window: the DeltaNet layers' states and histories back to row n - 1."""
+        if n >= self.T:
+            return
+        slot = self.commits % 64   # the table is read by an asynchronous copy: a slot is reused only 64 commits later
+        self.commits += 1
+        if slot == 0 and self.commits > 1:
+            self.stream.synchronize()
+        with torch.cuda.stream(self.stream):
+            L.call("fnx_window_commit", C.byref(self.stack.cfg), self.stack.layers, self.stack.ws.data_ptr(), self.T, n, tag,
+                   self.h_jobs.data_ptr() + slot * self.job_bytes, torch.cuda.current_stream().cuda_stream)
+
+    h2d_bytes = property(lambda self: self.T * 4 + 8)
+    d2h_bytes = property(lambda self: self.stack.ncard * self.T * 8 + 4)

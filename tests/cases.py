@@ -10,14 +10,19 @@ from oracle import binding as O
 
 # ---------------------------------------------------------------- MoE layer
 def moe_weights(n, nexp, ffs, seed=0, sigma=0.02):
+    """ffs not a multiple of 256 (an FF slice of a wider expert, as one GPU of several holds): the down matrix is cut
+    out of a 256-column-aligned Q6_K matrix at column 64."""
     rng = np.random.default_rng(seed)
     w = {"n": n, "nexp": nexp, "ffs": ffs}
+    src_cols = ffs if ffs % 256 == 0 else (64 + ffs + 255) // 256 * 256
+    c0 = 0 if ffs % 256 == 0 else 64
     w["router"] = (rng.standard_normal((nexp + 1, n)) * sigma).astype(np.float32)
     gu = (rng.standard_normal((nexp, 2 * ffs, n)) * sigma).astype(np.float32)
     w["gu_q4k"] = O.quantize_q4k(gu).reshape(nexp, 2 * ffs * (n // 256) * 144)
-    dn = (rng.standard_normal((nexp, n, ffs)) * sigma).astype(np.float32)
-    w["dn_q6k"] = O.quantize_q6k(dn).reshape(nexp, n * (ffs // 256) * 210)
-    planes = [O.q6k_to_planes(w["dn_q6k"][e], n, ffs) for e in range(nexp)]
+    dn = (rng.standard_normal((nexp, n, src_cols)) * sigma).astype(np.float32)
+    w["dn_q6k"] = O.quantize_q6k(dn).reshape(nexp, n * (src_cols // 256) * 210)
+    w["dn_src_cols"], w["dn_c0"] = src_cols, c0
+    planes = [O.q6k_to_planes(w["dn_q6k"][e], n, src_cols, c0, ffs) for e in range(nexp)]
     w["dn_planes"] = tuple(np.stack([p[i] for p in planes]) for i in range(4))
     sgu = (rng.standard_normal((2 * ffs, n)) * sigma).astype(np.float32)
     sdn = (rng.standard_normal((n, ffs)) * sigma).astype(np.float32)

@@ -249,7 +249,7 @@ def test_moe_layer_against_dequantised_float64(oracle):
     x = rng.standard_normal((T, n)).astype(np.float32)
     r = cases.moe_oracle(w, x, topk=4)
     gu_w = oracle.dequant(w["gu_q4k"].reshape(-1), "q4k").reshape(nexp, 2 * ffs, n).astype(np.float64)
-    dn_w = oracle.dequant(w["dn_q6k"].reshape(-1), "q6k").reshape(nexp, n, ffs).astype(np.float64)
+    dn_w = oracle.dequant(w["dn_q6k"].reshape(-1), "q6k").reshape(nexp, n, w["dn_src_cols"])[:, :, w["dn_c0"]:w["dn_c0"] + ffs].astype(np.float64)
     for t in range(T):
         acc = np.zeros(n)
         for k in range(4):
