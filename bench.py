@@ -114,8 +114,8 @@ def main():
 
     L.load()
     kinds = [1 if (i % 4) == 3 else 0 for i in range(args.layers)]
-    shape = StackShape(kinds=kinds, ctx=args.ctx)
     T = L.MAXT
+    shape = StackShape(kinds=kinds, ctx=args.ctx, kv_slack=(args.warmup + args.steps + 2) * T)
     t_build = time.time()
     stack = SyntheticStack(shape, ncard=world, card=rank, seed=args.seed, device="cuda:%d" % local)
     runner = WindowRunner(stack, T, group=group, graph=True)
@@ -181,12 +181,12 @@ def main():
         runner.commit(rec[i][3], rec[i][2])
 
     stack.load_state(state0)
+    clocks.start()
     for i in range(args.warmup):
         device_step(i)
     barrier()
     lib.fnx_window_kernel_count(1)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    clocks.start()
     e0.record(runner.stream)
     for i in range(args.warmup, nsteps):
         device_step(i)

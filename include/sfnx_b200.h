@@ -63,6 +63,7 @@ typedef struct FnxKvPages {
     const int* pt; /* device: logical page -> physical page */
     size_t page;   /* halves per page */
     int rows;      /* local rows per page */
+    int cap;       /* local rows the cache holds when pt is null (0: unchecked); a row past it is not appended */
 } FnxKvPages;
 
 /* unscaled rotary: reference src/rope.hpp:22-27 (Rope, base only) */

@@ -75,6 +75,7 @@ __global__ void k_attn_prep_append(float* qg, float* k, const float* v, const fl
     }
     if (j % ncard != card) return;
     const int r = (j / ncard) * 4 + p % 4;
+    if (!g.pt && g.cap > 0 && r >= g.cap) return;   // past the cache: the caller refuses such windows; never write outside
     (is_k ? kc : vc)[kv_row_at(g, r, nkv, hd) + e] = f2h(x);
 }
 

@@ -34,7 +34,7 @@ class Experts(C.Structure):
 
 
 class KvPages(C.Structure):
-    _fields_ = [("pt", C.c_void_p), ("page", C.c_size_t), ("rows", C.c_int)]
+    _fields_ = [("pt", C.c_void_p), ("page", C.c_size_t), ("rows", C.c_int), ("cap", C.c_int)]
 
 
 class Rope(C.Structure):

@@ -30,6 +30,7 @@ class StackShape:
     vocab: int = 151936
     kinds: list = field(default_factory=lambda: [0, 0, 0, 1, 0, 0, 0, 1])   # 0 DeltaNet, 1 attention
     ctx: int = 32768
+    kv_slack: int = 64   # positions the K/V cache holds past ctx (the tokens a run appends)
     eps: float = 1e-6
     rope_base: float = 1e7
     sigma: float = 0.02
@@ -62,7 +63,7 @@ class SyntheticStack:
         per = (s.vocab + ncard - 1) // ncard
         self.v0 = card * per
         self.vrows = max(0, min(s.vocab, self.v0 + per) - self.v0)
-        self.kv_rows = lib.fnx_kv_rows_per_card(s.ctx + 2 * L.MAXT + 4, ncard)
+        self.kv_rows = lib.fnx_kv_rows_per_card(s.ctx + s.kv_slack, ncard)
         self.cfg = L.StackCfg(s.n, s.nexp, s.topk, self.ffs, self.nk, self.nv, s.nq, s.nkv, s.hd, s.nrot, self.v0, self.vrows,
                               len(s.kinds), ncard, card, s.eps, s.rope_base)
         self.layers = (L.Layer * len(s.kinds))()
@@ -170,7 +171,7 @@ class SyntheticStack:
             vc = self._t(self._normal(l, "vc%d" % self.card, kv, 1.0).half().view(torch.int16))
             Lr.kc, Lr.vc = kc.data_ptr(), vc.data_ptr()
             self.named[(l, "kc")], self.named[(l, "vc")] = kc, vc
-            Lr.pages = L.KvPages(None, 0, 0)
+            Lr.pages = L.KvPages(None, 0, 0, self.kv_rows)
         # FFN
         self.named[(l, "router")] = self._t(self._normal(l, "router", (s.nexp + 1, s.n), s.sigma))
         Lr.router = self.named[(l, "router")].data_ptr()
@@ -294,6 +295,9 @@ class WindowRunner:
         """One window from host token ids: uploads ids and (position, tag), runs, reads back every row's argmax (merged
         across GPUs: the lower GPU wins a tie) and the error word.  Returns the argmax tokens as a list."""
         T = self.T
+        if pos0 + T > self.stack.shape.ctx + self.stack.shape.kv_slack:
+            raise L.FnxError("window at position %d + %d rows is past the K/V cache (%d positions)" %
+                             (pos0, T, self.stack.shape.ctx + self.stack.shape.kv_slack))
         self.h_ids[:T] = torch.as_tensor(rows, dtype=torch.int32)
         self.h_ctl[0], self.h_ctl[1] = pos0, tag
         with torch.cuda.stream(self.stream):

@@ -23,7 +23,7 @@ def _run(c):
         qg, k, v = G.dev(c["qg"]), G.dev(c["k"]), G.dev(c["v"])
         qn, kn = G.dev(c["qn"]), G.dev(c["kn"])
         kc, vc = G.dev(c["kc"][card]), G.dev(c["vc"][card])
-        g = L.KvPages(None, 0, 0)
+        g = L.KvPages(None, 0, 0, 0)
         L.call("fnx_attn_prep_append", qg.data_ptr(), k.data_ptr(), v.data_ptr(), qn.data_ptr(), kn.data_ptr(), kc.data_ptr(),
                vc.data_ptr(), g, card, ncard, T, pos0.data_ptr(), c["eps"], L.Rope(c["rope_base"], 64), nq, nkv, hd, st)
         scratch = G.zeros(L.load().fnx_attn_scratch_floats(nq, hd, T))
