@@ -148,8 +148,13 @@ int fnx_attn_prep_append(float* qg, float* k, const float* v, const float* q_nor
  * caller, parts[p] at parts + p * T * nq * (hd + 2)) in ring order for heads [h0, h0 + nh) and applies the gate:
  * out [T][nh][hd] */
 size_t fnx_attn_scratch_floats(int nq, int hd, int T);
+/* the fast scan (all rows of the window in one pass over the K/V rows, tensor cores, sums in its own order: equal to
+ * the exact-order scan to f32 rounding) and the scan in the reference's order of sums (bit-reproducible, slower) */
 int fnx_attn_partial(const float* qg, const uint16_t* kc, const uint16_t* vc, FnxKvPages g, float* part, int card, int ncard, int T,
                      const int* pos0, int nq, int nkv, int hd, float* scratch, void* st);
+int fnx_attn_partial_exact(const float* qg, const uint16_t* kc, const uint16_t* vc, FnxKvPages g, float* part, int card, int ncard,
+                           int T, const int* pos0, int nq, int nkv, int hd, float* scratch, void* st);
+int fnx_attn_splits(int nkv);
 int fnx_attn_finish(const float* parts, int nparts, int first_part, const float* qg, float* out, int T, int nq, int h0, int nh,
                     int hd, void* st);
 

@@ -227,9 +227,12 @@ int fnx_attn_prep_append(float* qg, float* k, const float* v, const float* q_nor
     return launch_ok("attn_prep_append");
 }
 
-size_t fnx_attn_scratch_floats(int nq, int hd, int T) { return (size_t) T * nq * ATT_SPLITS * (hd + 2); }
+size_t fnx_attn_scratch_floats(int nq, int hd, int T) {   // the larger of the exact scan's 16 splits and the fast scan's (at most 148)
+    const size_t exact = (size_t) T * nq * ATT_SPLITS * (hd + 2), fast = (size_t) T * nq * 148 * (hd + 2);
+    return exact > fast ? exact : fast;
+}
 
-int fnx_attn_partial(const float* qg, const uint16_t* kc, const uint16_t* vc, FnxKvPages g, float* part, int card, int ncard, int T,
+int fnx_attn_partial_exact(const float* qg, const uint16_t* kc, const uint16_t* vc, FnxKvPages g, float* part, int card, int ncard, int T,
                      const int* pos0, int nq, int nkv, int hd, float* scratch, void* st) {
     FNX_REQUIRE(T >= 1 && T <= FNX_MAXT, "attn: T %d outside 1..%d", T, FNX_MAXT);
     FNX_REQUIRE(hd == 256 || hd == 128, "attn: head dim %d (128 or 256)", hd);

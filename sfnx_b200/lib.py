@@ -85,6 +85,7 @@ _SIGS = {
     "fnx_copy_many": [_p, _i, _p],
     "fnx_attn_prep_append": [_p, _p, _p, _p, _p, _p, _p, KvPages, _i, _i, _i, _p, _f, Rope, _i, _i, _i, _p],
     "fnx_attn_partial": [_p, _p, _p, KvPages, _p, _i, _i, _i, _p, _i, _i, _i, _p, _p],
+    "fnx_attn_partial_exact": [_p, _p, _p, KvPages, _p, _i, _i, _i, _p, _i, _i, _i, _p, _p],
     "fnx_attn_finish": [_p, _i, _i, _p, _p, _i, _i, _i, _i, _i, _p],
     "fnx_argmax": [_p, _i, _i, _i, _p, _p, _p, _p, _p],
     "fnx_penalize_row": [_p, _i, _p, _p, _p],
@@ -108,6 +109,7 @@ _OTHER = {
     "fnx_gdn_scratch_floats": (_z, [_i]),
     "fnx_attn_scratch_floats": (_z, [_i, _i, _i]),
     "fnx_kv_rows_per_card": (_i, [_i, _i]),
+    "fnx_attn_splits": (_i, [_i]),
     "fnx_window_workspace_bytes": (_z, [_p]),
     "fnx_window_plan": (_i, [_p, _p, _p, _i]),
     "fnx_window_buf": (_p, [_p, _p, _i]),

@@ -8,7 +8,7 @@ from tests import cases
 pytestmark = pytest.mark.gpu
 
 
-def _run(c):
+def _run(c, entry="fnx_attn_partial_exact"):
     import torch
 
     from sfnx_b200 import lib as L
@@ -27,7 +27,7 @@ def _run(c):
         L.call("fnx_attn_prep_append", qg.data_ptr(), k.data_ptr(), v.data_ptr(), qn.data_ptr(), kn.data_ptr(), kc.data_ptr(),
                vc.data_ptr(), g, card, ncard, T, pos0.data_ptr(), c["eps"], L.Rope(c["rope_base"], 64), nq, nkv, hd, st)
         scratch = G.zeros(L.load().fnx_attn_scratch_floats(nq, hd, T))
-        L.call("fnx_attn_partial", qg.data_ptr(), kc.data_ptr(), vc.data_ptr(), g, parts[card].data_ptr(), card, ncard, T,
+        L.call(entry, qg.data_ptr(), kc.data_ptr(), vc.data_ptr(), g, parts[card].data_ptr(), card, ncard, T,
                pos0.data_ptr(), nq, nkv, hd, scratch.data_ptr(), st)
         res["kc"].append(G.host(kc, np.uint16))
         res["vc"].append(G.host(vc, np.uint16))
@@ -54,3 +54,20 @@ def test_attention_exact(T, ctx, ncard, hd):
         assert np.array_equal(got["kc"][card], ref["kc"][card]) and np.array_equal(got["vc"][card], ref["vc"][card]), "append"
         assert np.array_equal(got["part"][card].view(np.uint32), ref["part"][card].view(np.uint32)), "partials"
     assert np.array_equal(got["out"].view(np.uint32), ref["out"].view(np.uint32)), "merged, gated output"
+
+
+@pytest.mark.parametrize("T,ctx,ncard,hd", [(16, 3000, 1, 256), (16, 70, 1, 256), (7, 1500, 2, 256), (5, 515, 4, 128), (1, 0, 1, 256),
+                                            (16, 40000, 1, 256)])
+def test_attention_fast_scan(T, ctx, ncard, hd):
+    """The one-pass tensor-core scan against the oracle: the same partial format and merge, values equal to f32 rounding
+    (its sums run in another order; queries and weights enter the f16 MMAs as high + low halves)."""
+    c = cases.attn_case(T=T, ctx=ctx, nq=8 if hd == 128 else 24, nkv=2 if hd == 128 else 4, hd=hd, ncard=ncard, seed=60 + T)
+    ref = cases.attn_oracle(c)
+    got = _run(c, "fnx_attn_partial")
+    assert np.isfinite(got["out"]).all()
+    err = np.abs(got["out"] - ref["out"])
+    assert np.allclose(got["out"], ref["out"], rtol=3e-5, atol=2e-6), (err.max(), np.abs(ref["out"]).max())
+    for card in range(ncard):   # the normalisers of the partials agree too
+        zr, zg = ref["part"][card][..., hd + 1], got["part"][card][..., hd + 1]
+        mr, mg = ref["part"][card][..., hd], got["part"][card][..., hd]
+        assert np.allclose(zg * np.exp(mg - mr), zr, rtol=1e-4)
