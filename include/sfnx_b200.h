@@ -82,6 +82,10 @@ typedef struct FnxCopyJob {
 const char* fnx_last_error(void);
 /* the compute capability the library was built for (100) and whether the current device matches it */
 int fnx_built_arch(void);
+/* reads and clears the device-side fault word of the staged kernels: 0, or bit 1 when a bounded wait for a bulk copy ran
+ * out (the kernel then finished without the data instead of spinning; reference kernels report through err words the
+ * same way, src/kernels.hpp:329-332) */
+unsigned fnx_device_fault(void);
 
 /* ---- activations */
 /* reference src/kernels.hpp:36 quantize_q8_1 (src/kernels.cu:99-113): f32 rows of n -> q8_1 rows */

@@ -109,19 +109,36 @@ __global__ void __launch_bounds__(128) k_gemv_f32(const float* __restrict__ W, c
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, row = blockIdx.x, nc = n / 512;
     __shared__ float red[FNX_MAXT][4];
     const float4* w4 = reinterpret_cast<const float4*>(W + (size_t) row * n) + warp * nc * 32;
-    for (int t = 0; t < T; ++t) {
+    float4 wv[8];   // the warp's quarter of the row (n <= 4096)
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+        if (i < nc) wv[i] = __ldg(w4 + i * 32 + lane);
+    for (int t = 0; t < T; t += 2) {
+        const bool two = t + 1 < T;
         const float4* x4 = reinterpret_cast<const float4*>(x + (size_t) t * n) + warp * nc * 32;
-        float a = 0.f;
-        for (int i = 0; i < nc; ++i) {
-            const float4 w = __ldg(w4 + i * 32 + lane), b = x4[i * 32 + lane];
-            float p = fmul(w.x, b.x);
-            p = ffma(w.y, b.y, p);
-            p = ffma(w.z, b.z, p);
-            p = ffma(w.w, b.w, p);
-            a = fadd(a, p);
-        }
+        const float4* y4 = two ? x4 + n / 4 : x4;
+        float a = 0.f, c = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+            if (i < nc) {
+                const float4 w = wv[i], b = x4[i * 32 + lane], d = y4[i * 32 + lane];
+                float p = fmul(w.x, b.x);
+                p = ffma(w.y, b.y, p);
+                p = ffma(w.z, b.z, p);
+                p = ffma(w.w, b.w, p);
+                a = fadd(a, p);
+                float q = fmul(w.x, d.x);
+                q = ffma(w.y, d.y, q);
+                q = ffma(w.z, d.z, q);
+                q = ffma(w.w, d.w, q);
+                c = fadd(c, q);
+            }
         a = wsum(a);
-        if (lane == 0) red[t][warp] = a;
+        c = wsum(c);
+        if (lane == 0) {
+            red[t][warp] = a;
+            if (two) red[t + 1][warp] = c;
+        }
     }
     __syncthreads();
     if (threadIdx.x < T) {
@@ -183,7 +200,7 @@ int fnx_q8s_gemv(FnxQ8S w, int rows, int cols, const void* y, float* out, int ou
 
 int fnx_gemv_f32(const float* W, const float* x, float* y, int rows, int n, int T, void* st) {
     FNX_REQUIRE(T >= 1 && T <= FNX_MAXT, "gemv_f32: T %d outside 1..%d", T, FNX_MAXT);
-    FNX_REQUIRE(n > 0 && n % 512 == 0 && rows > 0, "gemv_f32: %d x %d (columns a multiple of 512)", rows, n);
+    FNX_REQUIRE(n > 0 && n % 512 == 0 && n <= 4096 && rows > 0, "gemv_f32: %d x %d (columns a multiple of 512 up to 4096)", rows, n);
     k_gemv_f32<<<rows, 128, 0, strm(st)>>>(W, x, y, rows, n, T);
     return launch_ok("gemv_f32");
 }

@@ -3,6 +3,7 @@
 // every sum is the reference's, stated with IEEE operations (exact_math.cuh), so results can be checked bit for bit.
 #include "common.cuh"
 #include "exact_math.cuh"
+#include "moe_internal.cuh"
 
 namespace fnxk {
 
@@ -38,14 +39,30 @@ __global__ void __launch_bounds__(RR_THREADS) k_router_route(const RouterArgs a)
     const int L = a.nexp + 1, row = blockIdx.x * RR_ROWS + rw, nc = a.n / 256;   // float4 chunks per lane
     __shared__ float rsum[FNX_MAXT][RR_THREADS / 32];
     if (row < L) {
+        // the row half's weights held in registers (up to 16 float4 a lane: n <= 4096), the rows of x two at a time so
+        // that their loads and sums overlap; each logit's summation order is unchanged
         const float4* w4 = reinterpret_cast<const float4*>(a.W + (size_t) row * a.n) + half * nc * 32;
-        for (int t = 0; t < a.T; ++t) {
+        float4 wv[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i)
+            if (i < nc) wv[i] = __ldg(w4 + i * 32 + lane);
+        for (int t = 0; t < a.T; t += 2) {
+            const bool two = t + 1 < a.T;
             const float4* x4 = reinterpret_cast<const float4*>(a.x + (size_t) t * a.n) + half * nc * 32;
-            float s = 0.f;
-#pragma unroll 4
-            for (int i = 0; i < nc; ++i) s = fadd(s, dot4(__ldg(w4 + i * 32 + lane), x4[i * 32 + lane]));
-            s = wsum(s);
-            if (lane == 0) rsum[t][warp] = s;
+            const float4* y4 = two ? x4 + a.n / 4 : x4;
+            float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+            for (int i = 0; i < 16; ++i)
+                if (i < nc) {
+                    s0 = fadd(s0, dot4(wv[i], x4[i * 32 + lane]));
+                    s1 = fadd(s1, dot4(wv[i], y4[i * 32 + lane]));
+                }
+            s0 = wsum(s0);
+            s1 = wsum(s1);
+            if (lane == 0) {
+                rsum[t][warp] = s0;
+                if (two) rsum[t + 1][warp] = s1;
+            }
         }
     }
     __syncthreads();
@@ -389,7 +406,7 @@ size_t fnx_router_scratch_bytes(void) { return 16; }
 int fnx_router_route(const float* W, const float* x, float* logits, int T, int n, int nexp, int topk, int* topi, float* topw,
                      FnxJob* jobs_gu, FnxJob* jobs_dn, int* njobs, void* scratch, void* st) {
     FNX_REQUIRE(T >= 1 && T <= FNX_MAXT, "router_route: T %d outside 1..%d", T, FNX_MAXT);
-    FNX_REQUIRE(n > 0 && n % 256 == 0, "router_route: n %d must be a multiple of 256", n);
+    FNX_REQUIRE(n > 0 && n % 256 == 0 && n <= 4096, "router_route: n %d must be a multiple of 256 up to 4096", n);
     FNX_REQUIRE(nexp % 32 == 0 && nexp >= 32 && nexp <= 512, "router_route: %d experts (a multiple of 32 up to 512)", nexp);
     FNX_REQUIRE(topk >= 1 && topk <= 16 && topk <= nexp, "router_route: top-%d", topk);
     RouterArgs a{W, x, logits, T, n, nexp, topk, topi, topw, jobs_gu, jobs_dn, njobs, (unsigned*) scratch};
@@ -404,7 +421,9 @@ int fnx_moe_gate_up(const FnxExperts* A, const FnxJob* jobs, const int* njobs, i
     const int n = A->ncols, nrows = A->nrows, maxrows = FNX_MAXT;
     if (A->type == FNX_Q4_K) {
         FNX_REQUIRE(n % 512 == 0 && n / 512 >= 1 && n / 512 <= 8, "moe gate|up q4_K: %d columns (multiples of 512 up to 4096)", n);
-        // blocks of 64 rows: the staged activations amortised over two passes, several thousand blocks a layer
+        // the TMA-staged persistent kernel wherever its panels fit shared memory; else blocks of 64 rows with direct loads
+        if (gu_q4k_tma_smem(n) + 1024 <= 227 * 1024 && ((uintptr_t) A->a % 16) == 0 && A->stride % 16 == 0)
+            return gu_q4k_tma_launch((const uint8_t*) A->a, A->stride, nrows, n, jobs, njobs, (const uint8_t*) xq, gu, strm(st));
         const int rpb = 64;
         const dim3 grid((nrows + rpb - 1) / rpb, njobs_max);
         const size_t sm = job_act_bytes(maxrows, n);

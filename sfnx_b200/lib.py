@@ -104,6 +104,7 @@ _SIGS = {
 _OTHER = {
     "fnx_last_error": (C.c_char_p, []),
     "fnx_built_arch": (_i, []),
+    "fnx_device_fault": (C.c_uint, []),
     "fnx_router_scratch_bytes": (_z, []),
     "fnx_moe_h_bytes": (_z, [_i, _i]),
     "fnx_gdn_scratch_floats": (_z, [_i]),
