@@ -36,6 +36,8 @@ def parse():
     ap.add_argument("--layers", type=int, default=8, help="stack depth (8 = the benchmark configuration)")
     ap.add_argument("--ctx", type=int, default=32768)
     ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--experts", type=int, default=512, help="routed experts (512 = the benchmark configuration; fewer for small profiling runs)")
+    ap.add_argument("--vocab", type=int, default=151936, help="vocabulary (151936 = the benchmark configuration)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     return ap.parse_args()
 
@@ -115,7 +117,7 @@ def main():
     L.load()
     kinds = [1 if (i % 4) == 3 else 0 for i in range(args.layers)]
     T = L.MAXT
-    shape = StackShape(kinds=kinds, ctx=args.ctx, kv_slack=(args.warmup + args.steps + 2) * T)
+    shape = StackShape(kinds=kinds, ctx=args.ctx, kv_slack=(args.warmup + args.steps + 2) * T, nexp=args.experts, vocab=args.vocab)
     t_build = time.time()
     stack = SyntheticStack(shape, ncard=world, card=rank, seed=args.seed, device="cuda:%d" % local)
     runner = WindowRunner(stack, T, group=group, graph=True)

@@ -3,8 +3,10 @@
 // checked bit for bit): 4 blocks per local value head, each owning 32 value columns of the head's 128 x 128 fp32
 // state; thread (column, part) keeps key rows [32 part, 32 part + 32) of its column in registers over the whole
 // window; the state after every row but the last is streamed to snap (the dominant HBM traffic: T state-sized writes
-// per head), the conv history variants to hsnap.  The head's last block to finish applies the gated RMS norm and
-// writes q8_1.
+// per head), the conv history variants to hsnap.  The head's four blocks form a thread-block cluster: they exchange
+// their outputs' square sums through distributed shared memory and each norms, gates and quantises its own columns.
+#include <cooperative_groups.h>
+
 #include "common.cuh"
 #include "exact_math.cuh"
 
@@ -27,21 +29,20 @@ struct GdnArgs {
     float* y32;
 };
 
-__global__ void __launch_bounds__(GDN_THREADS) k_gdn_core(const GdnArgs g) {
+__global__ void __cluster_dims__(GDN_Q, 1, 1) __launch_bounds__(GDN_THREADS) k_gdn_core(const GdnArgs g) {
+    namespace cg = cooperative_groups;
     const int lv = blockIdx.x / GDN_Q, qq = blockIdx.x % GDN_Q, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int vm = g.vmap[lv], kh = vm & 255, writes_hist = vm >> 8, nk = g.nk, nv = g.nv, T = g.T;
     const int ch = (2 * nk + nv) * HS, row_stride = ch + nv * HS;
     const unsigned parity = ((const unsigned*) g.ctl)[1] & 1u;
     const float* hin = g.hist + (size_t) parity * 3 * ch;
     float* hout = g.hist + (size_t) (parity ^ 1u) * 3 * ch;
-    float* o_all = g.scratch;                                              // [MAXT][nv HS]
-    float* sq_all = g.scratch + (size_t) FNX_MAXT * nv * HS;               // [nv][MAXT][4]
-    unsigned* counters = (unsigned*) (sq_all + (size_t) nv * FNX_MAXT * GDN_Q);   // [nv]
-
     __shared__ float xs[2][FNX_MAXT][32][4];   // q, k after conv, silu, L2 norm: element i at [i % 32][i / 32]
     __shared__ float vs[FNX_MAXT][GDN_QC];
     __shared__ float red[GDN_THREADS / 32][2 * FNX_MAXT];
     __shared__ float gates[FNX_MAXT][2];
+    __shared__ float osm[FNX_MAXT][GDN_QC];   // this block's outputs and, per row, their square sum
+    __shared__ float sqs[FNX_MAXT];
     if (tid < T) {
         const float* abt = g.ab + (size_t) tid * 2 * nv;
         const float x = fadd(abt[lv], g.dt[lv]);
@@ -56,8 +57,13 @@ __global__ void __launch_bounds__(GDN_THREADS) k_gdn_core(const GdnArgs g) {
         const bool wh = part == 2 || (writes_hist && qq == 0);
         float h0 = hin[c], h1 = hin[(size_t) ch + c], h2 = hin[(size_t) 2 * ch + c];
         const float4 w = *reinterpret_cast<const float4*>(g.convw + (size_t) c * 4);
-        for (int t = 0; t < T; ++t) {
-            const float xt = g.qkvz[(size_t) t * row_stride + c];
+        float xr[FNX_MAXT];   // the window's rows of this channel, all loads in flight before any store
+#pragma unroll
+        for (int t = 0; t < FNX_MAXT; ++t) xr[t] = t < T ? g.qkvz[(size_t) t * row_stride + c] : 0.f;
+#pragma unroll
+        for (int t = 0; t < FNX_MAXT; ++t) {
+            if (t >= T) break;
+            const float xt = xr[t];
             float x = fmul(w.x, h0);
             x = ffma(w.y, h1, x);
             x = ffma(w.z, h2, x);
@@ -130,7 +136,7 @@ __global__ void __launch_bounds__(GDN_THREADS) k_gdn_core(const GdnArgs g) {
         at = fadd(at, __shfl_xor_sync(0xffffffffu, at, 1));
         at = fadd(at, __shfl_xor_sync(0xffffffffu, at, 2));
         const float ov = part == 0 ? fmul(at, scale) : 0.f;
-        if (part == 0) o_all[(size_t) t * nv * HS + lv * HS + col] = ov;
+        if (part == 0) osm[t][cl] = ov;
         const float ss = wsum(fmul(ov, ov));
         if (lane == 0) red[warp][t] = ss;
         if (t < T - 1) {
@@ -146,34 +152,33 @@ __global__ void __launch_bounds__(GDN_THREADS) k_gdn_core(const GdnArgs g) {
         float v = 0.f;
 #pragma unroll
         for (int w = 0; w < GDN_THREADS / 32; ++w) v = fadd(v, red[w][tid]);
-        sq_all[((size_t) lv * FNX_MAXT + tid) * GDN_Q + qq] = v;
+        sqs[tid] = v;
     }
-    // ---- the head's last block: gated RMS norm over the head's 128 outputs, q8_1
-    __shared__ bool last;
-    __threadfence();
-    __syncthreads();
-    if (tid == 0) last = atomicAdd(&counters[lv], 1u) == GDN_Q - 1;
-    __syncthreads();
-    if (!last) return;
-    __threadfence();
-    for (int w = warp; w < 4 * T; w += GDN_THREADS / 32) {
-        const int t = w / 4, b = w % 4, c = b * 32 + lane;
-        const float* sqv = sq_all + ((size_t) lv * FNX_MAXT + t) * GDN_Q;
-        const float ms = fdiv(fadd(fadd(fadd(__ldcg(sqv), __ldcg(sqv + 1)), __ldcg(sqv + 2)), __ldcg(sqv + 3)), (float) HS);
-        const float v = __ldcg(o_all + (size_t) t * nv * HS + lv * HS + c);
+    // ---- gated RMS norm over the head's 128 outputs: the head's four blocks are one thread-block cluster and read each
+    // other's square sums through distributed shared memory; each block then norms, gates and quantises its own 32
+    // columns (one q8_1 block per row)
+    cg::cluster_group cluster = cg::this_cluster();
+    cluster.sync();
+    const float* rsq[GDN_Q];
+#pragma unroll
+    for (int r = 0; r < GDN_Q; ++r) rsq[r] = cluster.map_shared_rank(sqs, r);
+    for (int t = warp; t < T; t += GDN_THREADS / 32) {
+        const float ms = fdiv(fadd(fadd(fadd(rsq[0][t], rsq[1][t]), rsq[2][t]), rsq[3][t]), (float) HS);
+        const int c = qq * GDN_QC + lane;
+        const float v = osm[t][lane];
         const float z = g.qkvz[(size_t) t * row_stride + ch + lv * HS + c];
         const float xi = fdiv(fmul(fmul(v, ex_rsqrt(fadd(ms, g.eps))), g.nw[c]), fadd(1.0f, ex_expf(-z)));
         if (g.y32) g.y32[(size_t) t * nv * HS + lv * HS + c] = xi;
         const float amax = wmax(fabsf(xi)), sm = wsum(xi);
         const float d = fdiv(amax, 127.0f);
-        uint8_t* blk = g.yq + ((size_t) t * (nv * HS / 32) + lv * 4 + b) * 36;
+        uint8_t* blk = g.yq + ((size_t) t * (nv * HS / 32) + lv * 4 + qq) * 36;
         reinterpret_cast<int8_t*>(blk + 4)[lane] = amax == 0.0f ? 0 : (int8_t) roundf(fdiv(xi, d));
         if (lane == 0) {
             reinterpret_cast<uint16_t*>(blk)[0] = f2h(d);
             reinterpret_cast<uint16_t*>(blk)[1] = f2h(sm);
         }
     }
-    if (tid == 0) counters[lv] = 0u;
+    cluster.sync();   // no block leaves while its square sums may still be read
 }
 
 }  // namespace fnxk

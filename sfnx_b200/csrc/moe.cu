@@ -1,6 +1,8 @@
 // Routed-expert FFN of the verify window: router + top-k + job list, dequant-fused gate|up, SwiGLU + down, combine.
 // Replaces reference src/moe.cuh, src/moe_q4k.cuh and the combine of src/kernels.cu:797-803; the arithmetic order of
 // every sum is the reference's, stated with IEEE operations (exact_math.cuh), so results can be checked bit for bit.
+#include <cstdlib>
+
 #include "common.cuh"
 #include "exact_math.cuh"
 #include "moe_internal.cuh"
@@ -11,7 +13,7 @@ namespace fnxk {
 // logits: two warps per row (column halves); lane l accumulates the float4 chunks i * 32 + l in ascending i, each chunk
 // ((wx bx + wy by) + wz bz) + ww bw with fused steps; xor-tree; half0 + half1.  The grid's last block then picks the
 // top-k per row and builds the jobs.
-constexpr int RR_THREADS = 128, RR_ROWS = RR_THREADS / 64;
+constexpr int RR_THREADS = 256, RR_ROWS = RR_THREADS / 64, RR_TG = 4;   // rows a block; rows of x taken together
 
 struct RouterArgs {
     const float* W;
@@ -39,29 +41,31 @@ __global__ void __launch_bounds__(RR_THREADS) k_router_route(const RouterArgs a)
     const int L = a.nexp + 1, row = blockIdx.x * RR_ROWS + rw, nc = a.n / 256;   // float4 chunks per lane
     __shared__ float rsum[FNX_MAXT][RR_THREADS / 32];
     if (row < L) {
-        // the row half's weights held in registers (up to 16 float4 a lane: n <= 4096), the rows of x two at a time so
+        // the row half's weights held in registers (up to 16 float4 a lane: n <= 4096), the rows of x four at a time so
         // that their loads and sums overlap; each logit's summation order is unchanged
         const float4* w4 = reinterpret_cast<const float4*>(a.W + (size_t) row * a.n) + half * nc * 32;
         float4 wv[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i)
             if (i < nc) wv[i] = __ldg(w4 + i * 32 + lane);
-        for (int t = 0; t < a.T; t += 2) {
-            const bool two = t + 1 < a.T;
-            const float4* x4 = reinterpret_cast<const float4*>(a.x + (size_t) t * a.n) + half * nc * 32;
-            const float4* y4 = two ? x4 + a.n / 4 : x4;
-            float s0 = 0.f, s1 = 0.f;
+        for (int t = 0; t < a.T; t += RR_TG) {
+            float s[RR_TG];
+            const float4* x4[RR_TG];
+#pragma unroll
+            for (int k = 0; k < RR_TG; ++k) {
+                s[k] = 0.f;
+                x4[k] = reinterpret_cast<const float4*>(a.x + (size_t) min(t + k, a.T - 1) * a.n) + half * nc * 32;
+            }
 #pragma unroll
             for (int i = 0; i < 16; ++i)
                 if (i < nc) {
-                    s0 = fadd(s0, dot4(wv[i], x4[i * 32 + lane]));
-                    s1 = fadd(s1, dot4(wv[i], y4[i * 32 + lane]));
+#pragma unroll
+                    for (int k = 0; k < RR_TG; ++k) s[k] = fadd(s[k], dot4(wv[i], x4[k][i * 32 + lane]));
                 }
-            s0 = wsum(s0);
-            s1 = wsum(s1);
-            if (lane == 0) {
-                rsum[t][warp] = s0;
-                if (two) rsum[t + 1][warp] = s1;
+#pragma unroll
+            for (int k = 0; k < RR_TG; ++k) {
+                const float v = wsum(s[k]);
+                if (lane == 0 && t + k < a.T) rsum[t + k][warp] = v;
             }
         }
     }
@@ -81,11 +85,16 @@ __global__ void __launch_bounds__(RR_THREADS) k_router_route(const RouterArgs a)
 }
 
 // top-k per row by logit (ties: the lower index), weights exp(l - l_top) / sum in pick order; jobs: one per distinct
-// expert numbered by its first pick in pair order p = t topk + k, a job's rows in pair order
+// expert numbered by its first pick in pair order p = t topk + k, a job's rows in pair order.  The pair-against-pair
+// matches are warp ballots: pair p's expert against 32 pairs at a time.
 __device__ void route_tail(const RouterArgs& a) {
     const int e = threadIdx.x, warp = e >> 5, lane = e & 31, L = a.nexp + 1, P = a.T * a.topk, per = a.nexp / 32;
+    constexpr int NW = RR_THREADS / 32, PW = FNX_MAXT * 16 / 32;   // warps; 32-pair words
     __shared__ int ex[FNX_MAXT * 16];
-    for (int t = warp; t < a.T; t += RR_THREADS / 32) {
+    __shared__ int firstp[FNX_MAXT * 16], slot[FNX_MAXT * 16], count[FNX_MAXT * 16];
+    __shared__ unsigned firstmask[PW];
+    if (e < PW) firstmask[e] = 0u;
+    for (int t = warp; t < a.T; t += NW) {
         float v[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) v[i] = i < per ? __ldcg(a.logits + (size_t) t * L + lane + 32 * i) : -INFINITY;
@@ -122,41 +131,42 @@ __device__ void route_tail(const RouterArgs& a) {
         if (lane < a.topk) a.topw[t * a.topk + lane] = fdiv(wk, z);
     }
     __syncthreads();
-    __shared__ unsigned char first[FNX_MAXT * 16];
-    __shared__ int jobof[FNX_MAXT * 16];
-    for (int p = e; p < P; p += RR_THREADS) {
-        bool f = true;
-        for (int q = 0; q < p; ++q) f = f && ex[q] != ex[p];
-        first[p] = f;
+    const int words = (P + 31) / 32;
+    for (int p = warp; p < P; p += NW) {
+        const int my = ex[p];
+        int fp = P, below = 0, cnt = 0;
+        for (int k = 0; k < words; ++k) {
+            const int q = 32 * k + lane;
+            const unsigned bal = __ballot_sync(0xffffffffu, q < P && ex[q] == my);
+            if (bal && fp == P) fp = 32 * k + __ffs(bal) - 1;
+            cnt += __popc(bal);
+            if (32 * k + 31 < p) below += __popc(bal);
+            else if (32 * k <= p) below += __popc(bal & ((1u << (p - 32 * k)) - 1u));
+        }
+        if (lane == 0) {
+            firstp[p] = fp, slot[p] = below, count[p] = cnt;
+            if (fp == p) atomicOr(&firstmask[p >> 5], 1u << (p & 31));
+        }
     }
     __syncthreads();
     for (int p = e; p < P; p += RR_THREADS) {
-        int fp = p;   // the pair's expert's first pair, and how many jobs start before it
-        for (int q = p - 1; q >= 0; --q)
-            if (ex[q] == ex[p]) fp = q;
-        int j = 0;
-        for (int q = 0; q < fp; ++q) j += first[q];
-        jobof[p] = j;
-    }
-    __syncthreads();
-    for (int p = e; p < P; p += RR_THREADS) {
-        const int j = jobof[p];
-        int s = 0, cnt = 0;
-        for (int q = 0; q < P; ++q)
-            if (ex[q] == ex[p]) {
-                s += q < p;
-                ++cnt;
-            }
+        const int fp = firstp[p];
+        int j = 0;   // jobs that start before this pair's expert's first pair
+        for (int k = 0; k < words; ++k) {
+            if (32 * k + 31 < fp) j += __popc(firstmask[k]);
+            else if (32 * k <= fp) j += __popc(firstmask[k] & ((1u << (fp - 32 * k)) - 1u));
+        }
+        const int s = slot[p];
         a.gu[j].y[s] = p / a.topk;
         a.gu[j].out[s] = a.dn[j].y[s] = a.dn[j].out[s] = p;
-        if (first[p]) {
+        if (fp == p) {
             a.gu[j].w = a.dn[j].w = ex[p];
-            a.gu[j].n = a.dn[j].n = cnt;
+            a.gu[j].n = a.dn[j].n = count[p];
         }
     }
     if (e == 0) {
         int n = 0;
-        for (int q = 0; q < P; ++q) n += first[q];
+        for (int k = 0; k < words; ++k) n += __popc(firstmask[k]);
         a.njobs[0] = n;
         a.njobs[1] = 0;
         *a.counter = 0u;
@@ -225,65 +235,104 @@ __device__ __forceinline__ uint4 ldg_stream(const void* p) {   // read-once weig
     return v;
 }
 
+// Rows of a job are taken GU_TC at a time (almost every job of a window has one to three rows): their activations sit in
+// 15 KB of shared memory and the per-row sums in registers, so four blocks fit an SM and their loads overlap.
+constexpr int GU_TC = 4;
+
 template <int GPL>
-__global__ void __launch_bounds__(GU_THREADS, 2) k_moe_gu_q4k(const uint8_t* __restrict__ A, size_t sa, int nrows, int n,
+__global__ void __launch_bounds__(GU_THREADS, 4) k_moe_gu_q4k(const uint8_t* __restrict__ A, size_t sa, int nrows, int n,
                                                           const FnxJob* __restrict__ jobs, const int* __restrict__ njobs,
-                                                          const uint8_t* __restrict__ xq, float* __restrict__ out, int rows_per_block,
-                                                          int maxrows) {
+                                                          const uint8_t* __restrict__ xq, float* __restrict__ out, int rows_per_block) {
     const int ji = blockIdx.y;
     if (ji >= *njobs) return;
     extern __shared__ __align__(16) unsigned char smem[];
     __shared__ FnxJob jb;
     if (threadIdx.x < sizeof(FnxJob) / 4) reinterpret_cast<int*>(&jb)[threadIdx.x] = reinterpret_cast<const int*>(jobs + ji)[threadIdx.x];
     __syncthreads();
-    const JobAct act = job_act_carve(smem, maxrows, n);
-    job_act_stage(act, xq, jb, n);
-    __syncthreads();
     const int lane8 = threadIdx.x & 7, nb = n / 32;
+    int8_t* aq = reinterpret_cast<int8_t*>(smem);                              // [GU_TC][n]
+    float* ad = reinterpret_cast<float*>(smem + (size_t) GU_TC * n);           // [GU_TC][nb]
+    int* as = reinterpret_cast<int*>(ad + (size_t) GU_TC * nb);                // [GU_TC][nb]
     const size_t row_b = (size_t) n / 256 * 144;
     const uint8_t* We = A + (size_t) jb.w * sa;
-    for (int rb = 0; rb < rows_per_block; rb += GU_THREADS / 8) {
-        const int row = blockIdx.x * rows_per_block + rb + (threadIdx.x >> 3);
-        const bool live = row < nrows;   // uniform over the 8 lanes of a row
-        const uint8_t* wrow = We + (size_t) (live ? row : 0) * row_b;
-        uint4 hdr[GPL], q0[GPL], q1[GPL];
-#pragma unroll
-        for (int ii = 0; ii < GPL; ++ii) {
-            const int g = lane8 + ii * 8, b = g >> 2, jg = g & 3;
-            const uint8_t* blk = wrow + (size_t) b * 144;
-            hdr[ii] = ldg_stream(blk);
-            q0[ii] = ldg_stream(blk + 16 + 32 * jg);
-            q1[ii] = ldg_stream(blk + 32 + 32 * jg);
-        }
 #pragma unroll 1
-        for (int j = 0; j < jb.n; ++j) {
-            float tmp = 0.f;
+    for (int c0 = 0; c0 < jb.n; c0 += GU_TC) {
+        const int cn = min(GU_TC, jb.n - c0);
+        if (c0) __syncthreads();
+        for (int it = threadIdx.x; it < cn * nb; it += GU_THREADS) {
+            const int j = it / nb, b = it % nb;
+            const unsigned* src = reinterpret_cast<const unsigned*>(xq + ((size_t) jb.y[c0 + j] * nb + b) * 36);
+            unsigned w[9];
 #pragma unroll
-            for (int ii = 0; ii < GPL; ++ii) {
-                const int g = lane8 + ii * 8, b = g >> 2, jg = g & 3, yb = b * 8 + jg * 2;
-                const float d = h2f((uint16_t) (hdr[ii].x & 0xffff)), dmin = h2f((uint16_t) (hdr[ii].x >> 16));
-                float sc0, m0, sc1, m1;
-                q4k_scale_min(hdr[ii], 2 * jg, sc0, m0);
-                q4k_scale_min(hdr[ii], 2 * jg + 1, sc1, m1);
-                const uint4* ap = reinterpret_cast<const uint4*>(act.q + (size_t) j * n + yb * 32);
-                const uint4 a0 = ap[0], a1 = ap[1], a2 = ap[2], a3 = ap[3];
-                const unsigned qw[8] = {q0[ii].x, q0[ii].y, q0[ii].z, q0[ii].w, q1[ii].x, q1[ii].y, q1[ii].z, q1[ii].w};
-                const unsigned al[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
-                const unsigned ah[8] = {a2.x, a2.y, a2.z, a2.w, a3.x, a3.y, a3.z, a3.w};
-                int dl = 0, dh = 0;
+            for (int k = 0; k < 9; ++k) w[k] = src[k];
+            int sum = 0;
 #pragma unroll
-                for (int w = 0; w < 8; ++w) {
-                    dl = __dp4a((int) (qw[w] & 0x0F0F0F0Fu), (int) al[w], dl);
-                    dh = __dp4a((int) ((qw[w] >> 4) & 0x0F0F0F0Fu), (int) ah[w], dh);
+            for (int k = 0; k < 8; ++k) sum = __dp4a(0x01010101, (int) w[1 + k], sum);
+            uint4* dst = reinterpret_cast<uint4*>(aq + (size_t) j * n + b * 32);
+            dst[0] = make_uint4(w[1], w[2], w[3], w[4]);
+            dst[1] = make_uint4(w[5], w[6], w[7], w[8]);
+            ad[j * nb + b] = h2f((uint16_t) (w[0] & 0xffff));
+            as[j * nb + b] = sum;
+        }
+        __syncthreads();
+#pragma unroll 1
+        for (int rb = 0; rb < rows_per_block; rb += GU_THREADS / 8) {
+            const int row = blockIdx.x * rows_per_block + rb + (threadIdx.x >> 3);
+            const bool live = row < nrows;   // uniform over the 8 lanes of a row
+            const uint8_t* wrow = We + (size_t) (live ? row : 0) * row_b;
+            float tmp[GU_TC];
+#pragma unroll
+            for (int r = 0; r < GU_TC; ++r) tmp[r] = 0.f;
+#pragma unroll 1
+            for (int i0 = 0; i0 < GPL; i0 += 2) {   // two groups' loads in flight per lane, many warps per SM
+                uint4 hdr[2], q0[2], q1[2];
+#pragma unroll
+                for (int u = 0; u < 2; ++u) {
+                    const int g = lane8 + min(i0 + u, GPL - 1) * 8;
+                    const uint8_t* blk = wrow + (size_t) (g >> 2) * 144;
+                    hdr[u] = ldg_stream(blk);
+                    q0[u] = ldg_stream(blk + 16 + 32 * (g & 3));
+                    q1[u] = ldg_stream(blk + 32 + 32 * (g & 3));
                 }
-                const int sl = act.s[j * nb + yb], sh = act.s[j * nb + yb + 1];
-                const float d8l = act.d[j * nb + yb], d8h = act.d[j * nb + yb + 1];
-                const float pos = fmul(d, fadd(fmul(d8l, fmul(sc0, (float) dl)), fmul(d8h, fmul(sc1, (float) dh))));
-                const float neg = fmul(dmin, fadd(fmul(d8l, fmul(m0, (float) sl)), fmul(d8h, fmul(m1, (float) sh))));
-                tmp = fadd(tmp, fsub(pos, neg));
+#pragma unroll
+                for (int u = 0; u < 2; ++u) {
+                    if (i0 + u >= GPL) break;
+                    const int g = lane8 + (i0 + u) * 8, jg = g & 3, yb = (g >> 2) * 8 + jg * 2;
+                    const float d = h2f((uint16_t) (hdr[u].x & 0xffff)), dmin = h2f((uint16_t) (hdr[u].x >> 16));
+                    float sc0, m0, sc1, m1;
+                    q4k_scale_min(hdr[u], 2 * jg, sc0, m0);
+                    q4k_scale_min(hdr[u], 2 * jg + 1, sc1, m1);
+                    const unsigned qw[8] = {q0[u].x, q0[u].y, q0[u].z, q0[u].w, q1[u].x, q1[u].y, q1[u].z, q1[u].w};
+                    unsigned ql[8], qh[8];
+#pragma unroll
+                    for (int w = 0; w < 8; ++w) ql[w] = qw[w] & 0x0F0F0F0Fu, qh[w] = (qw[w] >> 4) & 0x0F0F0F0Fu;
+#pragma unroll
+                    for (int r = 0; r < GU_TC; ++r) {
+                        if (r >= cn) break;
+                        const uint4* ap = reinterpret_cast<const uint4*>(aq + (size_t) r * n + yb * 32);
+                        const uint4 a0 = ap[0], a1 = ap[1], a2 = ap[2], a3 = ap[3];
+                        int dl = __dp4a((int) ql[0], (int) a0.x, 0), dh = __dp4a((int) qh[0], (int) a2.x, 0);
+                        dl = __dp4a((int) ql[1], (int) a0.y, dl), dh = __dp4a((int) qh[1], (int) a2.y, dh);
+                        dl = __dp4a((int) ql[2], (int) a0.z, dl), dh = __dp4a((int) qh[2], (int) a2.z, dh);
+                        dl = __dp4a((int) ql[3], (int) a0.w, dl), dh = __dp4a((int) qh[3], (int) a2.w, dh);
+                        dl = __dp4a((int) ql[4], (int) a1.x, dl), dh = __dp4a((int) qh[4], (int) a3.x, dh);
+                        dl = __dp4a((int) ql[5], (int) a1.y, dl), dh = __dp4a((int) qh[5], (int) a3.y, dh);
+                        dl = __dp4a((int) ql[6], (int) a1.z, dl), dh = __dp4a((int) qh[6], (int) a3.z, dh);
+                        dl = __dp4a((int) ql[7], (int) a1.w, dl), dh = __dp4a((int) qh[7], (int) a3.w, dh);
+                        const int sl = as[r * nb + yb], sh = as[r * nb + yb + 1];
+                        const float d8l = ad[r * nb + yb], d8h = ad[r * nb + yb + 1];
+                        const float pos = fmul(d, fadd(fmul(d8l, fmul(sc0, (float) dl)), fmul(d8h, fmul(sc1, (float) dh))));
+                        const float neg = fmul(dmin, fadd(fmul(d8l, fmul(m0, (float) sl)), fmul(d8h, fmul(m1, (float) sh))));
+                        tmp[r] = fadd(tmp[r], fsub(pos, neg));
+                    }
+                }
             }
-            tmp = sum8(tmp);
-            if (live && lane8 == 0) out[(size_t) jb.out[j] * nrows + row] = tmp;
+#pragma unroll
+            for (int r = 0; r < GU_TC; ++r) {
+                if (r >= cn) break;
+                const float v = sum8(tmp[r]);
+                if (live && lane8 == 0) out[(size_t) jb.out[c0 + r] * nrows + row] = v;
+            }
         }
     }
 }
@@ -311,67 +360,92 @@ __global__ void __launch_bounds__(256) k_swiglu_q8(const float* __restrict__ gu,
 // added in ascending order (reference src/moe.cuh:330-344).
 constexpr int DN_THREADS = 256;
 
-__global__ void __launch_bounds__(DN_THREADS) k_moe_down_q6p(const uint4* __restrict__ QL, const uint2* __restrict__ QH,
-                                                            const uint16_t* __restrict__ SC, const uint16_t* __restrict__ D,
-                                                            size_t expert_units, int nrows, int ffs, const FnxJob* __restrict__ jobs,
-                                                            const int* __restrict__ njobs, const int8_t* __restrict__ hq,
-                                                            const float* __restrict__ hd, float* __restrict__ out, int rows_per_block,
-                                                            int maxrows) {
+constexpr int DN_TC = 4, DN_UPT = 3;   // activation rows a pass; units a thread (its loads all in flight)
+
+__global__ void __launch_bounds__(DN_THREADS, 4) k_moe_down_q6p(const uint4* __restrict__ QL, const uint2* __restrict__ QH,
+                                                               const uint16_t* __restrict__ SC, const uint16_t* __restrict__ D,
+                                                               size_t expert_units, int nrows, int ffs, const FnxJob* __restrict__ jobs,
+                                                               const int* __restrict__ njobs, const int8_t* __restrict__ hq,
+                                                               const float* __restrict__ hd, float* __restrict__ out, int rows_per_block) {
     const int ji = blockIdx.y;
     if (ji >= *njobs) return;
     extern __shared__ __align__(16) unsigned char smem[];
     __shared__ FnxJob jb;
     if (threadIdx.x < sizeof(FnxJob) / 4) reinterpret_cast<int*>(&jb)[threadIdx.x] = reinterpret_cast<const int*>(jobs + ji)[threadIdx.x];
     __syncthreads();
-    const int nu = ffs / 32, units = rows_per_block * nu;
-    int8_t* sq = reinterpret_cast<int8_t*>(smem);                                 // [maxrows][ffs]
-    float* sd = reinterpret_cast<float*>(smem + (size_t) maxrows * ffs);          // [maxrows][nu]
-    float* part = sd + (size_t) maxrows * nu;                                     // [maxrows][units]
-    for (int it = threadIdx.x; it < jb.n * (ffs / 16); it += DN_THREADS) {
-        const int j = it / (ffs / 16), c = it % (ffs / 16);
-        reinterpret_cast<uint4*>(sq + (size_t) j * ffs)[c] = reinterpret_cast<const uint4*>(hq + (size_t) jb.y[j] * ffs)[c];
-    }
-    for (int it = threadIdx.x; it < jb.n * nu; it += DN_THREADS) sd[(it / nu) * nu + it % nu] = hd[(size_t) jb.y[it / nu] * nu + it % nu];
-    __syncthreads();
+    const int nu = ffs / 32, units = rows_per_block * nu;   // units <= DN_THREADS * DN_UPT
+    int8_t* sq = reinterpret_cast<int8_t*>(smem);                                // [DN_TC][ffs]
+    float* sd = reinterpret_cast<float*>(smem + (size_t) DN_TC * ffs);            // [DN_TC][nu]
+    float* part = sd + (size_t) DN_TC * nu;                                       // [DN_TC][units]
     const int row0 = blockIdx.x * rows_per_block;
     const size_t ebase = (size_t) jb.w * expert_units + (size_t) row0 * nu;
-    const int live_units = min(units, (nrows - row0) * nu);
-    for (int g = threadIdx.x; g < live_units; g += DN_THREADS) {
-        const uint4 ql = ldg_stream(QL + ebase + g);
-        const uint2 qh = __ldg(QH + ebase + g);
-        const unsigned scw = SC[ebase + g];
-        const float d = h2f(D[ebase + g]);
-        const int sc0 = (int) (int8_t) (scw & 0xff), sc1 = (int) (int8_t) (scw >> 8);
-        const int u = g % nu;
-        const unsigned lw[4] = {ql.x, ql.y, ql.z, ql.w};
-        unsigned v[8];
+    const int live_units = min(units, (nrows - row0) * nu), live_rows = min(rows_per_block, nrows - row0);
+    // this thread's units: the weights are read once and kept for every pass over the job's rows
+    unsigned v[DN_UPT][8];
+    float d[DN_UPT];
+    int sc0[DN_UPT], sc1[DN_UPT];
+    {
+        uint4 ql[DN_UPT];
+        uint2 qh[DN_UPT];
+        unsigned scw[DN_UPT];
 #pragma unroll
-        for (int w = 0; w < 4; ++w) {
-            v[w] = __vsub4((lw[w] & 0x0F0F0F0Fu) | (((qh.x >> (2 * w)) & 0x03030303u) << 4), 0x20202020u);
-            v[4 + w] = __vsub4(((lw[w] >> 4) & 0x0F0F0F0Fu) | (((qh.y >> (2 * w)) & 0x03030303u) << 4), 0x20202020u);
+        for (int k = 0; k < DN_UPT; ++k) {
+            const int g = min(threadIdx.x + k * DN_THREADS, live_units - 1);
+            ql[k] = ldg_stream(QL + ebase + g);
+            qh[k] = __ldg(QH + ebase + g);
+            scw[k] = SC[ebase + g];
+            d[k] = h2f(D[ebase + g]);
         }
-        for (int j = 0; j < jb.n; ++j) {
-            const uint4* ap = reinterpret_cast<const uint4*>(sq + (size_t) j * ffs + u * 32);
-            const uint4 a0 = ap[0], a1 = ap[1];
-            int is0 = __dp4a((int) v[0], (int) a0.x, 0);
-            is0 = __dp4a((int) v[1], (int) a0.y, is0);
-            is0 = __dp4a((int) v[2], (int) a0.z, is0);
-            is0 = __dp4a((int) v[3], (int) a0.w, is0);
-            int is1 = __dp4a((int) v[4], (int) a1.x, 0);
-            is1 = __dp4a((int) v[5], (int) a1.y, is1);
-            is1 = __dp4a((int) v[6], (int) a1.z, is1);
-            is1 = __dp4a((int) v[7], (int) a1.w, is1);
-            const int I = sc0 * is0 + sc1 * is1;
-            part[(size_t) j * units + g] = fmul(d, fmul(sd[j * nu + u], (float) I));
+#pragma unroll
+        for (int k = 0; k < DN_UPT; ++k) {
+            sc0[k] = (int) (int8_t) (scw[k] & 0xff), sc1[k] = (int) (int8_t) (scw[k] >> 8);
+            const unsigned lw[4] = {ql[k].x, ql[k].y, ql[k].z, ql[k].w};
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+                v[k][w] = __vsub4((lw[w] & 0x0F0F0F0Fu) | (((qh[k].x >> (2 * w)) & 0x03030303u) << 4), 0x20202020u);
+                v[k][4 + w] = __vsub4(((lw[w] >> 4) & 0x0F0F0F0Fu) | (((qh[k].y >> (2 * w)) & 0x03030303u) << 4), 0x20202020u);
+            }
         }
     }
-    __syncthreads();
-    const int live_rows = min(rows_per_block, nrows - row0);
-    for (int e = threadIdx.x; e < jb.n * live_rows; e += DN_THREADS) {
-        const int j = e / live_rows, rr = e % live_rows;
-        float s = 0.f;
-        for (int k = 0; k < nu; ++k) s = fadd(s, part[(size_t) j * units + rr * nu + k]);
-        out[(size_t) jb.out[j] * nrows + row0 + rr] = s;
+#pragma unroll 1
+    for (int c0 = 0; c0 < jb.n; c0 += DN_TC) {
+        const int cn = min(DN_TC, jb.n - c0);
+        if (c0) __syncthreads();
+        for (int it = threadIdx.x; it < cn * (ffs / 16); it += DN_THREADS) {
+            const int j = it / (ffs / 16), c = it % (ffs / 16);
+            reinterpret_cast<uint4*>(sq + (size_t) j * ffs)[c] = reinterpret_cast<const uint4*>(hq + (size_t) jb.y[c0 + j] * ffs)[c];
+        }
+        for (int it = threadIdx.x; it < cn * nu; it += DN_THREADS) sd[it] = hd[(size_t) jb.y[c0 + it / nu] * nu + it % nu];
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < DN_UPT; ++k) {
+            const int g = threadIdx.x + k * DN_THREADS;
+            if (g >= live_units) break;
+            const int u = g % nu;
+#pragma unroll
+            for (int j = 0; j < DN_TC; ++j) {
+                if (j >= cn) break;
+                const uint4* ap = reinterpret_cast<const uint4*>(sq + (size_t) j * ffs + u * 32);
+                const uint4 a0 = ap[0], a1 = ap[1];
+                int is0 = __dp4a((int) v[k][0], (int) a0.x, 0);
+                is0 = __dp4a((int) v[k][1], (int) a0.y, is0);
+                is0 = __dp4a((int) v[k][2], (int) a0.z, is0);
+                is0 = __dp4a((int) v[k][3], (int) a0.w, is0);
+                int is1 = __dp4a((int) v[k][4], (int) a1.x, 0);
+                is1 = __dp4a((int) v[k][5], (int) a1.y, is1);
+                is1 = __dp4a((int) v[k][6], (int) a1.z, is1);
+                is1 = __dp4a((int) v[k][7], (int) a1.w, is1);
+                const int I = sc0[k] * is0 + sc1[k] * is1;
+                part[(size_t) j * units + g] = fmul(d[k], fmul(sd[j * nu + u], (float) I));
+            }
+        }
+        __syncthreads();
+        for (int e = threadIdx.x; e < cn * live_rows; e += DN_THREADS) {
+            const int j = e / live_rows, rr = e % live_rows;
+            float s = 0.f;
+            for (int k = 0; k < nu; ++k) s = fadd(s, part[(size_t) j * units + rr * nu + k]);
+            out[(size_t) jb.out[c0 + j] * nrows + row0 + rr] = s;
+        }
     }
 }
 
@@ -421,17 +495,19 @@ int fnx_moe_gate_up(const FnxExperts* A, const FnxJob* jobs, const int* njobs, i
     const int n = A->ncols, nrows = A->nrows, maxrows = FNX_MAXT;
     if (A->type == FNX_Q4_K) {
         FNX_REQUIRE(n % 512 == 0 && n / 512 >= 1 && n / 512 <= 8, "moe gate|up q4_K: %d columns (multiples of 512 up to 4096)", n);
-        // the TMA-staged persistent kernel wherever its panels fit shared memory; else blocks of 64 rows with direct loads
-        if (gu_q4k_tma_smem(n) + 1024 <= 227 * 1024 && ((uintptr_t) A->a % 16) == 0 && A->stride % 16 == 0)
+        // blocks of 64 rows with direct 16-byte loads, four blocks an SM (measured faster than staging the panels through
+        // shared memory with bulk copies: each weight byte is used once and the consumer is instruction-bound)
+        static const bool staged = getenv("FNX_GU_TMA") != nullptr;   // a tuning knob: the TMA-staged persistent kernel instead
+        if (staged && gu_q4k_tma_smem(n) + 1024 <= 227 * 1024 && ((uintptr_t) A->a % 16) == 0 && A->stride % 16 == 0)
             return gu_q4k_tma_launch((const uint8_t*) A->a, A->stride, nrows, n, jobs, njobs, (const uint8_t*) xq, gu, strm(st));
         const int rpb = 64;
         const dim3 grid((nrows + rpb - 1) / rpb, njobs_max);
-        const size_t sm = job_act_bytes(maxrows, n);
+        const size_t sm = (size_t) GU_TC * (n + (n / 32) * 8);
         const uint8_t* a = (const uint8_t*) A->a;
 #define GU_CASE(G)                                                                                                          \
     case G:                                                                                                                 \
         if (smem_optin(k_moe_gu_q4k<G>, sm, "moe gate|up q4_K")) return 1;                                                  \
-        k_moe_gu_q4k<G><<<grid, GU_THREADS, sm, strm(st)>>>(a, A->stride, nrows, n, jobs, njobs, (const uint8_t*) xq, gu, rpb, maxrows); \
+        k_moe_gu_q4k<G><<<grid, GU_THREADS, sm, strm(st)>>>(a, A->stride, nrows, n, jobs, njobs, (const uint8_t*) xq, gu, rpb); \
         break;
         switch (n / 512) {
             GU_CASE(1) GU_CASE(2) GU_CASE(3) GU_CASE(4) GU_CASE(5) GU_CASE(6) GU_CASE(7) GU_CASE(8)
@@ -454,15 +530,14 @@ int fnx_moe_down(const FnxExperts* A, const FnxJob* jobs, const int* njobs, int 
     if (launch_ok("moe_down swiglu")) return 1;
     if (A->type == FNX_Q6_K) {
         const int nu = ffs / 32;
-        int rpb = 768 / nu;   // ~768 units a block
-        if (rpb < 1) rpb = 1;
+        FNX_REQUIRE(nu <= DN_THREADS * DN_UPT, "moe_down: ff width %d too wide for a block", ffs);
+        int rpb = DN_THREADS * DN_UPT / nu;   // up to 768 units a block
         if (rpb > nrows) rpb = nrows;
-        const size_t sm = (size_t) maxrows * ffs + (size_t) maxrows * nu * 4 + (size_t) maxrows * rpb * nu * 4;
+        const size_t sm = (size_t) DN_TC * ffs + (size_t) DN_TC * nu * 4 + (size_t) DN_TC * rpb * nu * 4;
         if (smem_optin(k_moe_down_q6p, sm, "moe_down q6_K")) return 1;
         const dim3 grid((nrows + rpb - 1) / rpb, njobs_max);
         k_moe_down_q6p<<<grid, DN_THREADS, sm, strm(st)>>>((const uint4*) A->a, (const uint2*) A->b, (const uint16_t*) A->c,
-                                                        (const uint16_t*) A->d, A->stride, nrows, ffs, jobs, njobs, h8, hd, part, rpb,
-                                                        maxrows);
+                                                        (const uint16_t*) A->d, A->stride, nrows, ffs, jobs, njobs, h8, hd, part, rpb);
         return launch_ok("moe_down q6_K");
     }
     return fail("moe_down: expert type %d not supported (Q6_K units)", A->type);
