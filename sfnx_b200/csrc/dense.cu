@@ -102,6 +102,146 @@ __global__ void __launch_bounds__(Q8S_THREADS, 2) k_q8s(const int8_t* __restrict
     }
 }
 
+// ---------------------------------------------------------------- the same sums on the tensor cores
+// A row's result is the xor-tree over 32 "lanes" of per-lane sums, lane l adding the scaled integer dots of the 16-column
+// pieces at c = 16 l + 512 k in ascending k.  Here a 16-column piece of 16 weight rows against up to 16 activation rows
+// is one (or two) mma.sync m16n8k16 s8 x s8 -> s32, exact; the scaling by fl(dw da) and the per-lane f32 sums are done on
+// the accumulator fragments in the same order, so the result has the same bits as the dp4a kernel's.  Warp w owns lanes
+// 4 w .. 4 w + 3 (64 contiguous columns of every 512), for two 16-row tiles; the 32 lane sums of every output meet in
+// shared memory for the tree.  The integer accumulator starts at the bits of 1.5 * 2^23, so reinterpreting it as f32
+// and subtracting that constant converts it without a convert instruction (|dot| < 2^22).
+constexpr int QM_THREADS = 256, QM_MT = 2, QM_ROWS = 16 * QM_MT, QM_APAD = 16;
+constexpr int QM_MAGIC = 0x4B400000;
+
+__device__ __forceinline__ void mma_s8_16816(int (&d)[4], unsigned a0, unsigned a1, unsigned b0) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%7,%7,%7,%7};"
+                 : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+                 : "r"(a0), "r"(a1), "r"(b0), "r"(QM_MAGIC));
+}
+__device__ __forceinline__ unsigned ldg_u32(const void* p) {
+    unsigned v;
+    asm volatile("ld.global.nc.u32 %0, [%1];" : "=r"(v) : "l"(p));
+    return v;
+}
+
+template <int NT>   // activation rows in tiles of 8: 1 (T <= 8) or 2
+__global__ void __launch_bounds__(QM_THREADS, 2) k_q8s_mma(const int8_t* __restrict__ wq, const uint16_t* __restrict__ wd, int rows, int cols,
+                                                          const uint8_t* __restrict__ yq, const int8_t* __restrict__ pq,
+                                                          const float* __restrict__ pd, int T, float* __restrict__ out, int out_stride) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    const int nb = cols / 32, lda = cols + QM_APAD, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, q = lane & 3, r8 = lane >> 2;
+    int8_t* sq = reinterpret_cast<int8_t*>(smem);                          // [8 NT][cols + pad], rows >= T zero
+    float* sd = reinterpret_cast<float*>(smem + (size_t) 8 * NT * lda);    // [8 NT][nb]
+    float* red = reinterpret_cast<float*>(smem);                           // after the main loop: [32 lanes][QM_ROWS][8 NT]
+    for (int it = tid; it < 8 * NT * nb; it += QM_THREADS) {
+        const int t = it / nb, b = it % nb;
+        uint4 v0 = make_uint4(0, 0, 0, 0), v1 = v0;
+        float d = 0.f;
+        if (t < T) {
+            if (yq) {
+                const unsigned* src = reinterpret_cast<const unsigned*>(yq + (size_t) it * 36);
+                d = h2f((uint16_t) (src[0] & 0xffff));
+                v0 = make_uint4(src[1], src[2], src[3], src[4]);
+                v1 = make_uint4(src[5], src[6], src[7], src[8]);
+            } else {
+                const uint4* src = reinterpret_cast<const uint4*>(pq + (size_t) t * cols + b * 32);
+                v0 = src[0], v1 = src[1];
+                d = pd[it];
+            }
+        }
+        uint4* dst = reinterpret_cast<uint4*>(sq + (size_t) t * lda + b * 32);
+        dst[0] = v0, dst[1] = v1;
+        sd[it] = d;
+    }
+    __syncthreads();
+    const int row0 = blockIdx.x * QM_ROWS;
+    float acc[QM_MT][4][NT][4];
+#pragma unroll
+    for (int mt = 0; mt < QM_MT; ++mt)
+#pragma unroll
+        for (int v = 0; v < 4; ++v)
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) acc[mt][v][nt][0] = acc[mt][v][nt][1] = acc[mt][v][nt][2] = acc[mt][v][nt][3] = 0.f;
+    const int8_t* wr[QM_MT][2];
+    const uint16_t* dr[QM_MT][2];
+#pragma unroll
+    for (int mt = 0; mt < QM_MT; ++mt)
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const size_t row = (size_t) min(row0 + 16 * mt + 8 * h + r8, rows - 1);
+            wr[mt][h] = wq + row * cols + 4 * q;
+            dr[mt][h] = wd + row * nb;
+        }
+#pragma unroll 1
+    for (int cb = 64 * warp; cb < cols; cb += 512) {
+        unsigned a[QM_MT][4][2];
+#pragma unroll
+        for (int mt = 0; mt < QM_MT; ++mt)
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+                a[mt][v][0] = ldg_u32(wr[mt][0] + cb + 16 * v);
+                a[mt][v][1] = ldg_u32(wr[mt][1] + cb + 16 * v);
+            }
+#pragma unroll
+        for (int bb = 0; bb < 2; ++bb) {   // the two 32-column blocks of the warp's 64 columns
+            const int b = (cb >> 5) + bb;
+            float w[QM_MT][2][NT][2];   // fl(dw da) of (row, activation row) for this block
+            float da[NT][2];
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) da[nt][0] = sd[(8 * nt + 2 * q) * nb + b], da[nt][1] = sd[(8 * nt + 2 * q + 1) * nb + b];
+#pragma unroll
+            for (int mt = 0; mt < QM_MT; ++mt)
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const float dw = h2f(__ldg(dr[mt][h] + b));
+#pragma unroll
+                    for (int nt = 0; nt < NT; ++nt) w[mt][h][nt][0] = fmul(dw, da[nt][0]), w[mt][h][nt][1] = fmul(dw, da[nt][1]);
+                }
+#pragma unroll
+            for (int vv = 0; vv < 2; ++vv) {
+                const int v = 2 * bb + vv, c = cb + 16 * v;
+                unsigned bf[NT];
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) bf[nt] = *reinterpret_cast<const unsigned*>(sq + (size_t) (8 * nt + r8) * lda + c + 4 * q);
+#pragma unroll
+                for (int mt = 0; mt < QM_MT; ++mt)
+#pragma unroll
+                    for (int nt = 0; nt < NT; ++nt) {
+                        int d[4];
+                        mma_s8_16816(d, a[mt][v][0], a[mt][v][1], bf[nt]);
+#pragma unroll
+                        for (int i = 0; i < 4; ++i)
+                            acc[mt][v][nt][i] = ffma(w[mt][i >> 1][nt][i & 1], fsub(__int_as_float(d[i]), 12582912.0f), acc[mt][v][nt][i]);
+                    }
+            }
+        }
+    }
+    __syncthreads();   // the activations are no longer read: their memory takes the lane sums
+    constexpr int TO = 8 * NT, OUTS = QM_ROWS * TO;
+#pragma unroll
+    for (int mt = 0; mt < QM_MT; ++mt)
+#pragma unroll
+        for (int v = 0; v < 4; ++v)
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                    red[(size_t) (4 * warp + v) * OUTS + (16 * mt + 8 * (i >> 1) + r8) * TO + 8 * nt + 2 * q + (i & 1)] = acc[mt][v][nt][i];
+    __syncthreads();
+    for (int o = tid; o < OUTS; o += QM_THREADS) {
+        float p[32];
+#pragma unroll
+        for (int l = 0; l < 32; ++l) p[l] = red[(size_t) l * OUTS + o];
+#pragma unroll
+        for (int w2 = 16; w2; w2 >>= 1)
+#pragma unroll
+            for (int l = 0; l < 16; ++l)
+                if (l < w2) p[l] = fadd(p[l], p[l + w2]);
+        const int row = row0 + o / TO, t = o % TO;
+        if (row < rows && t < T) out[(size_t) t * out_stride + row] = p[0];
+    }
+}
+
 // f32 GEMV, a block of 4 warps per row, warp p the p-th quarter of the float4 chunks (reference
 // src/kernels.cu:184-227 with WPR = 4): lane sums its chunks in ascending order, xor-tree, 0 + p0 + p1 + p2 + p3
 __global__ void __launch_bounds__(128) k_gemv_f32(const float* __restrict__ W, const float* __restrict__ x, float* __restrict__ y,
@@ -167,6 +307,24 @@ int q8s_launch(FnxQ8S w, int rows, int cols, const void* yq, const int8_t* pq, c
                cudaStream_t st, const char* what) {
     if (!(T >= 1 && T <= FNX_MAXT)) return fail("%s: T %d outside 1..%d", what, T, FNX_MAXT);
     if (!(cols > 0 && cols % 32 == 0 && rows > 0)) return fail("%s: %d x %d (columns a multiple of 32)", what, rows, cols);
+    if (cols % 64 == 0) {   // the tensor-core kernel: 32 rows a block
+        const int NT = T <= 8 ? 1 : 2;
+        const size_t act = (size_t) 8 * NT * (cols + QM_APAD) + (size_t) 8 * NT * (cols / 32) * 4, redb = (size_t) 32 * QM_ROWS * 8 * NT * 4;
+        const size_t smm = act > redb ? act : redb;
+        if (smm <= 227 * 1024) {
+            const int g = (rows + QM_ROWS - 1) / QM_ROWS;
+            if (NT == 1) {
+                if (smm > 48 * 1024 && cudaFuncSetAttribute(k_q8s_mma<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smm) != cudaSuccess)
+                    return fail("%s: shared memory opt-in failed", what);
+                k_q8s_mma<1><<<g, QM_THREADS, smm, st>>>(w.q, w.d, rows, cols, (const uint8_t*) yq, pq, pd, T, out, out_stride);
+            } else {
+                if (smm > 48 * 1024 && cudaFuncSetAttribute(k_q8s_mma<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smm) != cudaSuccess)
+                    return fail("%s: shared memory opt-in failed", what);
+                k_q8s_mma<2><<<g, QM_THREADS, smm, st>>>(w.q, w.d, rows, cols, (const uint8_t*) yq, pq, pd, T, out, out_stride);
+            }
+            return launch_ok(what);
+        }
+    }
     // enough blocks to fill the GPU twice over, at most 128 rows each so the staged activations are amortised
     int rpb = (rows / 296 + 31) / 32 * 32;
     rpb = rpb < 32 ? 32 : rpb > 128 ? 128 : rpb;

@@ -36,43 +36,55 @@ __device__ __forceinline__ float dot4(const float4& w, const float4& b) {
 
 __device__ void route_tail(const RouterArgs& a);
 
-__global__ void __launch_bounds__(RR_THREADS) k_router_route(const RouterArgs a) {
+__global__ void __launch_bounds__(RR_THREADS) k_router_route(const RouterArgs a, int x_in_smem) {
     const int e = threadIdx.x, warp = e >> 5, lane = e & 31, rw = warp >> 1, half = warp & 1;
-    const int L = a.nexp + 1, row = blockIdx.x * RR_ROWS + rw, nc = a.n / 256;   // float4 chunks per lane
+    const int L = a.nexp + 1, nc = a.n / 256;   // float4 chunks per lane
+    extern __shared__ __align__(16) float xs_sm[];   // the window's rows of x, read once per block (when they fit)
     __shared__ float rsum[FNX_MAXT][RR_THREADS / 32];
-    if (row < L) {
-        // the row half's weights held in registers (up to 16 float4 a lane: n <= 4096), the rows of x four at a time so
-        // that their loads and sums overlap; each logit's summation order is unchanged
-        const float4* w4 = reinterpret_cast<const float4*>(a.W + (size_t) row * a.n) + half * nc * 32;
-        float4 wv[16];
-#pragma unroll
-        for (int i = 0; i < 16; ++i)
-            if (i < nc) wv[i] = __ldg(w4 + i * 32 + lane);
-        for (int t = 0; t < a.T; t += RR_TG) {
-            float s[RR_TG];
-            const float4* x4[RR_TG];
-#pragma unroll
-            for (int k = 0; k < RR_TG; ++k) {
-                s[k] = 0.f;
-                x4[k] = reinterpret_cast<const float4*>(a.x + (size_t) min(t + k, a.T - 1) * a.n) + half * nc * 32;
-            }
+    const float* xs = a.x;
+    if (x_in_smem) {
+        for (int i = e; i < a.T * a.n / 4; i += RR_THREADS) reinterpret_cast<float4*>(xs_sm)[i] = reinterpret_cast<const float4*>(a.x)[i];
+        xs = xs_sm;
+        __syncthreads();
+    }
+    // a block takes rows b, b + grid, ... four at a time, two warps a row (column halves)
+    for (int row0 = blockIdx.x * RR_ROWS; row0 < L; row0 += gridDim.x * RR_ROWS) {
+        const int row = row0 + rw;
+        if (row < L) {
+            // the row half's weights held in registers (up to 16 float4 a lane: n <= 4096), the rows of x four at a time
+            // so that their loads and sums overlap; each logit's summation order is unchanged
+            const float4* w4 = reinterpret_cast<const float4*>(a.W + (size_t) row * a.n) + half * nc * 32;
+            float4 wv[16];
 #pragma unroll
             for (int i = 0; i < 16; ++i)
-                if (i < nc) {
+                if (i < nc) wv[i] = __ldg(w4 + i * 32 + lane);
+            for (int t = 0; t < a.T; t += RR_TG) {
+                float s[RR_TG];
+                const float4* x4[RR_TG];
 #pragma unroll
-                    for (int k = 0; k < RR_TG; ++k) s[k] = fadd(s[k], dot4(wv[i], x4[k][i * 32 + lane]));
+                for (int k = 0; k < RR_TG; ++k) {
+                    s[k] = 0.f;
+                    x4[k] = reinterpret_cast<const float4*>(xs + (size_t) min(t + k, a.T - 1) * a.n) + half * nc * 32;
                 }
 #pragma unroll
-            for (int k = 0; k < RR_TG; ++k) {
-                const float v = wsum(s[k]);
-                if (lane == 0 && t + k < a.T) rsum[t + k][warp] = v;
+                for (int i = 0; i < 16; ++i)
+                    if (i < nc) {
+#pragma unroll
+                        for (int k = 0; k < RR_TG; ++k) s[k] = fadd(s[k], dot4(wv[i], x4[k][i * 32 + lane]));
+                    }
+#pragma unroll
+                for (int k = 0; k < RR_TG; ++k) {
+                    const float v = wsum(s[k]);
+                    if (lane == 0 && t + k < a.T) rsum[t + k][warp] = v;
+                }
             }
         }
-    }
-    __syncthreads();
-    for (int q = e; q < a.T * RR_ROWS; q += RR_THREADS) {
-        const int t = q / RR_ROWS, r = q % RR_ROWS, lrow = blockIdx.x * RR_ROWS + r;
-        if (lrow < L) a.logits[(size_t) t * L + lrow] = fadd(rsum[t][2 * r], rsum[t][2 * r + 1]);
+        __syncthreads();
+        for (int q = e; q < a.T * RR_ROWS; q += RR_THREADS) {
+            const int t = q / RR_ROWS, r = q % RR_ROWS, lrow = row0 + r;
+            if (lrow < L) a.logits[(size_t) t * L + lrow] = fadd(rsum[t][2 * r], rsum[t][2 * r + 1]);
+        }
+        __syncthreads();
     }
     __shared__ bool last;
     __threadfence();
@@ -484,7 +496,13 @@ int fnx_router_route(const float* W, const float* x, float* logits, int T, int n
     FNX_REQUIRE(nexp % 32 == 0 && nexp >= 32 && nexp <= 512, "router_route: %d experts (a multiple of 32 up to 512)", nexp);
     FNX_REQUIRE(topk >= 1 && topk <= 16 && topk <= nexp, "router_route: top-%d", topk);
     RouterArgs a{W, x, logits, T, n, nexp, topk, topi, topw, jobs_gu, jobs_dn, njobs, (unsigned*) scratch};
-    k_router_route<<<(nexp + 1 + RR_ROWS - 1) / RR_ROWS, RR_THREADS, 0, strm(st)>>>(a);
+    // one block per SM when the rows of x fit its shared memory (each block then reads x once instead of once per row)
+    const size_t xbytes = (size_t) T * n * 4;
+    const int fits = xbytes <= 200 * 1024;
+    int grid = (nexp + 1 + RR_ROWS - 1) / RR_ROWS;
+    if (fits && grid > 148) grid = 148;
+    if (fits && smem_optin(k_router_route, xbytes, "router_route")) return 1;
+    k_router_route<<<grid, RR_THREADS, fits ? xbytes : 0, strm(st)>>>(a, fits);
     return launch_ok("router_route");
 }
 
