@@ -102,6 +102,10 @@ int fnx_embed_rows(const uint16_t* table, const int* ids, float* x, int T, int n
 /* ---- dense projections */
 /* reference src/kernels.hpp:47 q8s_gemv (src/dense.cuh:24-160): out[t][r] = W[r] . y[t], T <= FNX_MAXT */
 int fnx_q8s_gemv(FnxQ8S w, int rows, int cols, const void* y, float* out, int out_stride, int T, void* st);
+/* reference src/kernels.hpp:365-368 q8s_gemv_segs: n (1..3) Q8_0 matrices of `cols` columns over the same q8_1 rows in one
+ * launch; each output as fnx_q8s_gemv of that matrix alone gives it */
+int fnx_q8s_gemv_segs(const FnxQ8S* w, const int* rows, float* const* out, const int* out_stride, int n, int cols, const void* y, int T,
+                      void* st);
 /* reference src/kernels.hpp:49 gemv_f32 (src/kernels.cu:184-227, the block-per-row form): y[t][r] = W[r] . x[t] */
 int fnx_gemv_f32(const float* W, const float* x, float* y, int rows, int n, int T, void* st);
 

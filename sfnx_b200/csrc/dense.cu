@@ -124,15 +124,38 @@ __device__ __forceinline__ unsigned ldg_u32(const void* p) {
     return v;
 }
 
+// up to three matrices of the same width over the same activations in one launch (reference src/dense.cuh:8-19): the
+// blocks of segment s follow those of segment s - 1
+struct QSegs {
+    const int8_t* q[3];
+    const uint16_t* d[3];
+    float* out[3];
+    int stride[3], rows[3], blk_end[3];
+};
+
 template <int NT>   // activation rows in tiles of 8: 1 (T <= 8) or 2
-__global__ void __launch_bounds__(QM_THREADS, 2) k_q8s_mma(const int8_t* __restrict__ wq, const uint16_t* __restrict__ wd, int rows, int cols,
+__global__ void __launch_bounds__(QM_THREADS, 2) k_q8s_mma(const QSegs sg, int cols,
                                                           const uint8_t* __restrict__ yq, const int8_t* __restrict__ pq,
-                                                          const float* __restrict__ pd, int T, float* __restrict__ out, int out_stride) {
+                                                          const float* __restrict__ pd, int T, unsigned sw_off) {
     extern __shared__ __align__(16) unsigned char smem[];
+    // this block's segment, by selects (indexing the parameter arrays at run time would put them in local memory)
+    const int seg = (int) blockIdx.x < sg.blk_end[0] ? 0 : (int) blockIdx.x < sg.blk_end[1] ? 1 : 2;
+    const int8_t* __restrict__ wq = seg == 0 ? sg.q[0] : seg == 1 ? sg.q[1] : sg.q[2];
+    const uint16_t* __restrict__ wd = seg == 0 ? sg.d[0] : seg == 1 ? sg.d[1] : sg.d[2];
+    float* __restrict__ out = seg == 0 ? sg.out[0] : seg == 1 ? sg.out[1] : sg.out[2];
+    const int out_stride = seg == 0 ? sg.stride[0] : seg == 1 ? sg.stride[1] : sg.stride[2];
+    const int rows = seg == 0 ? sg.rows[0] : seg == 1 ? sg.rows[1] : sg.rows[2];
+    const int blk0 = seg == 0 ? 0 : seg == 1 ? sg.blk_end[0] : sg.blk_end[1];
     const int nb = cols / 32, lda = cols + QM_APAD, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, q = lane & 3, r8 = lane >> 2;
     int8_t* sq = reinterpret_cast<int8_t*>(smem);                          // [8 NT][cols + pad], rows >= T zero
     float* sd = reinterpret_cast<float*>(smem + (size_t) 8 * NT * lda);    // [8 NT][nb]
     float* red = reinterpret_cast<float*>(smem);                           // after the main loop: [32 lanes][QM_ROWS][8 NT]
+    float* sw = reinterpret_cast<float*>(smem + sw_off);                   // the block's weight scales [QM_ROWS][nb + 1]
+    const int row0 = ((int) blockIdx.x - blk0) * QM_ROWS;
+    for (int it = tid; it < QM_ROWS * nb; it += QM_THREADS) {
+        const int r = it / nb, b = it % nb;
+        sw[r * (nb + 1) + b] = h2f(__ldg(wd + (size_t) min(row0 + r, rows - 1) * nb + b));
+    }
     for (int it = tid; it < 8 * NT * nb; it += QM_THREADS) {
         const int t = it / nb, b = it % nb;
         uint4 v0 = make_uint4(0, 0, 0, 0), v1 = v0;
@@ -154,7 +177,6 @@ __global__ void __launch_bounds__(QM_THREADS, 2) k_q8s_mma(const int8_t* __restr
         sd[it] = d;
     }
     __syncthreads();
-    const int row0 = blockIdx.x * QM_ROWS;
     float acc[QM_MT][4][NT][4];
 #pragma unroll
     for (int mt = 0; mt < QM_MT; ++mt)
@@ -163,15 +185,10 @@ __global__ void __launch_bounds__(QM_THREADS, 2) k_q8s_mma(const int8_t* __restr
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt) acc[mt][v][nt][0] = acc[mt][v][nt][1] = acc[mt][v][nt][2] = acc[mt][v][nt][3] = 0.f;
     const int8_t* wr[QM_MT][2];
-    const uint16_t* dr[QM_MT][2];
 #pragma unroll
     for (int mt = 0; mt < QM_MT; ++mt)
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-            const size_t row = (size_t) min(row0 + 16 * mt + 8 * h + r8, rows - 1);
-            wr[mt][h] = wq + row * cols + 4 * q;
-            dr[mt][h] = wd + row * nb;
-        }
+        for (int h = 0; h < 2; ++h) wr[mt][h] = wq + (size_t) min(row0 + 16 * mt + 8 * h + r8, rows - 1) * cols + 4 * q;
 #pragma unroll 1
     for (int cb = 64 * warp; cb < cols; cb += 512) {
         unsigned a[QM_MT][4][2];
@@ -193,7 +210,7 @@ __global__ void __launch_bounds__(QM_THREADS, 2) k_q8s_mma(const int8_t* __restr
             for (int mt = 0; mt < QM_MT; ++mt)
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
-                    const float dw = h2f(__ldg(dr[mt][h] + b));
+                    const float dw = sw[(16 * mt + 8 * h + r8) * (nb + 1) + b];
 #pragma unroll
                     for (int nt = 0; nt < NT; ++nt) w[mt][h][nt][0] = fmul(dw, da[nt][0]), w[mt][h][nt][1] = fmul(dw, da[nt][1]);
                 }
@@ -303,27 +320,44 @@ __global__ void __launch_bounds__(256) k_swiglu_rows(const float* __restrict__ g
     if (lane == 0) hd[(size_t) e * nb + b] = h2f(f2h(d));
 }
 
+// the tensor-core kernel over 1..3 matrices; -1 when its shared memory does not fit (the caller falls back)
+int q8s_mma_launch(const FnxQ8S* w, const int* rows, float* const* out, const int* out_stride, int nseg, int cols, const void* yq,
+                   const int8_t* pq, const float* pd, int T, cudaStream_t st, const char* what) {
+    const int NT = T <= 8 ? 1 : 2;
+    const size_t act = (size_t) 8 * NT * (cols + QM_APAD) + (size_t) 8 * NT * (cols / 32) * 4, redb = (size_t) 32 * QM_ROWS * 8 * NT * 4;
+    const size_t sw_off = ((act > redb ? act : redb) + 15) & ~(size_t) 15;
+    const size_t smm = sw_off + (size_t) QM_ROWS * (cols / 32 + 1) * 4;
+    if (smm > 227 * 1024) return -1;
+    QSegs sg{};
+    int g = 0;
+    for (int s = 0; s < 3; ++s) {
+        const int k = s < nseg ? s : nseg - 1;
+        sg.q[s] = w[k].q, sg.d[s] = w[k].d, sg.out[s] = out[k], sg.stride[s] = out_stride[k], sg.rows[s] = rows[k];
+        if (s < nseg) g += (rows[s] + QM_ROWS - 1) / QM_ROWS;
+        sg.blk_end[s] = g;
+    }
+    if (NT == 1) {
+        if (smm > 48 * 1024 && cudaFuncSetAttribute(k_q8s_mma<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smm) != cudaSuccess)
+            return fail("%s: shared memory opt-in failed", what);
+        k_q8s_mma<1><<<g, QM_THREADS, smm, st>>>(sg, cols, (const uint8_t*) yq, pq, pd, T, (unsigned) sw_off);
+    } else {
+        if (smm > 48 * 1024 && cudaFuncSetAttribute(k_q8s_mma<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smm) != cudaSuccess)
+            return fail("%s: shared memory opt-in failed", what);
+        k_q8s_mma<2><<<g, QM_THREADS, smm, st>>>(sg, cols, (const uint8_t*) yq, pq, pd, T, (unsigned) sw_off);
+    }
+    return launch_ok(what);
+}
+
 int q8s_launch(FnxQ8S w, int rows, int cols, const void* yq, const int8_t* pq, const float* pd, float* out, int out_stride, int T,
                cudaStream_t st, const char* what) {
     if (!(T >= 1 && T <= FNX_MAXT)) return fail("%s: T %d outside 1..%d", what, T, FNX_MAXT);
     if (!(cols > 0 && cols % 32 == 0 && rows > 0)) return fail("%s: %d x %d (columns a multiple of 32)", what, rows, cols);
     if (cols % 64 == 0) {   // the tensor-core kernel: 32 rows a block
-        const int NT = T <= 8 ? 1 : 2;
-        const size_t act = (size_t) 8 * NT * (cols + QM_APAD) + (size_t) 8 * NT * (cols / 32) * 4, redb = (size_t) 32 * QM_ROWS * 8 * NT * 4;
-        const size_t smm = act > redb ? act : redb;
-        if (smm <= 227 * 1024) {
-            const int g = (rows + QM_ROWS - 1) / QM_ROWS;
-            if (NT == 1) {
-                if (smm > 48 * 1024 && cudaFuncSetAttribute(k_q8s_mma<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smm) != cudaSuccess)
-                    return fail("%s: shared memory opt-in failed", what);
-                k_q8s_mma<1><<<g, QM_THREADS, smm, st>>>(w.q, w.d, rows, cols, (const uint8_t*) yq, pq, pd, T, out, out_stride);
-            } else {
-                if (smm > 48 * 1024 && cudaFuncSetAttribute(k_q8s_mma<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smm) != cudaSuccess)
-                    return fail("%s: shared memory opt-in failed", what);
-                k_q8s_mma<2><<<g, QM_THREADS, smm, st>>>(w.q, w.d, rows, cols, (const uint8_t*) yq, pq, pd, T, out, out_stride);
-            }
-            return launch_ok(what);
-        }
+        const FnxQ8S ws[1] = {w};
+        const int rs[1] = {rows}, strides[1] = {out_stride};
+        float* outs[1] = {out};
+        const int rc = q8s_mma_launch(ws, rs, outs, strides, 1, cols, yq, pq, pd, T, st, what);
+        if (rc >= 0) return rc;
     }
     // enough blocks to fill the GPU twice over, at most 128 rows each so the staged activations are amortised
     int rpb = (rows / 296 + 31) / 32 * 32;
@@ -354,6 +388,19 @@ extern "C" {
 
 int fnx_q8s_gemv(FnxQ8S w, int rows, int cols, const void* y, float* out, int out_stride, int T, void* st) {
     return q8s_launch(w, rows, cols, y, nullptr, nullptr, out, out_stride, T, strm(st), "q8s_gemv");
+}
+
+int fnx_q8s_gemv_segs(const FnxQ8S* w, const int* rows, float* const* out, const int* out_stride, int n, int cols, const void* y, int T,
+                      void* st) {
+    FNX_REQUIRE(n >= 1 && n <= 3, "q8s_gemv_segs: %d matrices (1..3)", n);
+    FNX_REQUIRE(T >= 1 && T <= FNX_MAXT, "q8s_gemv_segs: T %d outside 1..%d", T, FNX_MAXT);
+    if (cols % 64 == 0) {
+        const int rc = q8s_mma_launch(w, rows, out, out_stride, n, cols, y, nullptr, nullptr, T, strm(st), "q8s_gemv_segs");
+        if (rc >= 0) return rc;
+    }
+    for (int s = 0; s < n; ++s)
+        if (q8s_launch(w[s], rows[s], cols, y, nullptr, nullptr, out[s], out_stride[s], T, strm(st), "q8s_gemv_segs")) return 1;
+    return 0;
 }
 
 int fnx_gemv_f32(const float* W, const float* x, float* y, int rows, int n, int T, void* st) {

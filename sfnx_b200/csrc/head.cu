@@ -27,7 +27,14 @@ __global__ void __launch_bounds__(AM_THREADS) k_argmax(const float* __restrict__
         const unsigned long long ok = __shfl_xor_sync(0xffffffffu, best, o);
         best = ok > best ? ok : best;
     }
-    if ((threadIdx.x & 31) == 0) atomicMax(&keys[t], best);
+    __shared__ unsigned long long wbest[AM_THREADS / 32];   // one atomic per block
+    if ((threadIdx.x & 31) == 0) wbest[threadIdx.x >> 5] = best;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+#pragma unroll
+        for (int w = 1; w < AM_THREADS / 32; ++w) best = wbest[w] > best ? wbest[w] : best;
+        atomicMax(&keys[t], best);
+    }
 }
 // decodes the keys into (value, index + v0) and leaves them at zero for the next call
 __global__ void k_argmax_fin(unsigned long long* keys, int T, int v0, float* bv, int* bi) {

@@ -232,9 +232,12 @@ int fnx_window_stage(const FnxStackCfg* cfg, const FnxLayer* layers, const FnxHe
         float* k = (float*) (b + w.k);
         float* v = (float*) (b + w.v);
         TRK("rms_norm", 1, fnx_rms_norm_rows(x, pending, L.norm1, nullptr, xq, T, c.n, c.eps, st));
-        TRK("wq", 1, fnx_q8s_gemv(L.wq, c.nq * c.hd * 2, c.n, xq, qg, c.nq * c.hd * 2, T, st));
-        TRK("wk", 1, fnx_q8s_gemv(L.wk, c.nkv * c.hd, c.n, xq, k, c.nkv * c.hd, T, st));
-        TRK("wv", 1, fnx_q8s_gemv(L.wv, c.nkv * c.hd, c.n, xq, v, c.nkv * c.hd, T, st));
+        {   // q, k and v in one launch
+            const FnxQ8S ws[3] = {L.wq, L.wk, L.wv};
+            const int rows3[3] = {c.nq * c.hd * 2, c.nkv * c.hd, c.nkv * c.hd};
+            float* const outs[3] = {qg, k, v};
+            TRK("wqkv", 1, fnx_q8s_gemv_segs(ws, rows3, outs, rows3, 3, c.n, xq, T, st));
+        }
         const FnxRope rope{c.rope_base, c.nrot};
         TRK("attn_prep_append", 1, fnx_attn_prep_append(qg, k, v, L.q_norm, L.k_norm, L.kc, L.vc, L.pages, c.card, c.ncard, T, ctl, c.eps,
                                                         rope, c.nq, c.nkv, c.hd, st));
