@@ -249,7 +249,7 @@ __device__ __forceinline__ uint4 ldg_stream(const void* p) {   // read-once weig
 
 // Rows of a job are taken GU_TC at a time (almost every job of a window has one to three rows): their activations sit in
 // 15 KB of shared memory and the per-row sums in registers, so four blocks fit an SM and their loads overlap.
-constexpr int GU_TC = 4;
+constexpr int GU_TC = 4, GU_MAGIC = 0x4B400000;
 
 template <int GPL>
 __global__ void __launch_bounds__(GU_THREADS, 4) k_moe_gu_q4k(const uint8_t* __restrict__ A, size_t sa, int nrows, int n,
@@ -263,8 +263,7 @@ __global__ void __launch_bounds__(GU_THREADS, 4) k_moe_gu_q4k(const uint8_t* __r
     __syncthreads();
     const int lane8 = threadIdx.x & 7, nb = n / 32;
     int8_t* aq = reinterpret_cast<int8_t*>(smem);                              // [GU_TC][n]
-    float* ad = reinterpret_cast<float*>(smem + (size_t) GU_TC * n);           // [GU_TC][nb]
-    int* as = reinterpret_cast<int*>(ad + (size_t) GU_TC * nb);                // [GU_TC][nb]
+    float4* ag = reinterpret_cast<float4*>(smem + (size_t) GU_TC * n);         // [GU_TC][n / 64]: d8 low, d8 high, sum low, sum high
     const size_t row_b = (size_t) n / 256 * 144;
     const uint8_t* We = A + (size_t) jb.w * sa;
 #pragma unroll 1
@@ -283,8 +282,9 @@ __global__ void __launch_bounds__(GU_THREADS, 4) k_moe_gu_q4k(const uint8_t* __r
             uint4* dst = reinterpret_cast<uint4*>(aq + (size_t) j * n + b * 32);
             dst[0] = make_uint4(w[1], w[2], w[3], w[4]);
             dst[1] = make_uint4(w[5], w[6], w[7], w[8]);
-            ad[j * nb + b] = h2f((uint16_t) (w[0] & 0xffff));
-            as[j * nb + b] = sum;
+            float* gq = reinterpret_cast<float*>(ag + (size_t) j * (nb / 2) + (b >> 1));
+            gq[b & 1] = h2f((uint16_t) (w[0] & 0xffff));
+            gq[2 + (b & 1)] = (float) sum;
         }
         __syncthreads();
 #pragma unroll 1
@@ -323,7 +323,7 @@ __global__ void __launch_bounds__(GU_THREADS, 4) k_moe_gu_q4k(const uint8_t* __r
                         if (r >= cn) break;
                         const uint4* ap = reinterpret_cast<const uint4*>(aq + (size_t) r * n + yb * 32);
                         const uint4 a0 = ap[0], a1 = ap[1], a2 = ap[2], a3 = ap[3];
-                        int dl = __dp4a((int) ql[0], (int) a0.x, 0), dh = __dp4a((int) qh[0], (int) a2.x, 0);
+                        int dl = __dp4a((int) ql[0], (int) a0.x, GU_MAGIC), dh = __dp4a((int) qh[0], (int) a2.x, GU_MAGIC);
                         dl = __dp4a((int) ql[1], (int) a0.y, dl), dh = __dp4a((int) qh[1], (int) a2.y, dh);
                         dl = __dp4a((int) ql[2], (int) a0.z, dl), dh = __dp4a((int) qh[2], (int) a2.z, dh);
                         dl = __dp4a((int) ql[3], (int) a0.w, dl), dh = __dp4a((int) qh[3], (int) a2.w, dh);
@@ -331,10 +331,11 @@ __global__ void __launch_bounds__(GU_THREADS, 4) k_moe_gu_q4k(const uint8_t* __r
                         dl = __dp4a((int) ql[5], (int) a1.y, dl), dh = __dp4a((int) qh[5], (int) a3.y, dh);
                         dl = __dp4a((int) ql[6], (int) a1.z, dl), dh = __dp4a((int) qh[6], (int) a3.z, dh);
                         dl = __dp4a((int) ql[7], (int) a1.w, dl), dh = __dp4a((int) qh[7], (int) a3.w, dh);
-                        const int sl = as[r * nb + yb], sh = as[r * nb + yb + 1];
-                        const float d8l = ad[r * nb + yb], d8h = ad[r * nb + yb + 1];
-                        const float pos = fmul(d, fadd(fmul(d8l, fmul(sc0, (float) dl)), fmul(d8h, fmul(sc1, (float) dh))));
-                        const float neg = fmul(dmin, fadd(fmul(d8l, fmul(m0, (float) sl)), fmul(d8h, fmul(m1, (float) sh))));
+                        const float4 sg = ag[(size_t) r * (nb / 2) + (yb >> 1)];   // d8l, d8h, (float) sl, (float) sh
+                        // the dots started at the bits of 1.5 * 2^23: as floats, minus that constant, they are (float) dot
+                        const float fl = fsub(__int_as_float(dl), 12582912.0f), fh = fsub(__int_as_float(dh), 12582912.0f);
+                        const float pos = fmul(d, fadd(fmul(sg.x, fmul(sc0, fl)), fmul(sg.y, fmul(sc1, fh))));
+                        const float neg = fmul(dmin, fadd(fmul(sg.x, fmul(m0, sg.z)), fmul(sg.y, fmul(m1, sg.w))));
                         tmp[r] = fadd(tmp[r], fsub(pos, neg));
                     }
                 }
@@ -388,7 +389,8 @@ __global__ void __launch_bounds__(DN_THREADS, 4) k_moe_down_q6p(const uint4* __r
     const int nu = ffs / 32, units = rows_per_block * nu;   // units <= DN_THREADS * DN_UPT
     int8_t* sq = reinterpret_cast<int8_t*>(smem);                                // [DN_TC][ffs]
     float* sd = reinterpret_cast<float*>(smem + (size_t) DN_TC * ffs);            // [DN_TC][nu]
-    float* part = sd + (size_t) DN_TC * nu;                                       // [DN_TC][units]
+    int2* ss = reinterpret_cast<int2*>(sd + (size_t) DN_TC * nu);                 // [DN_TC][nu]: 32 x the sums of each half
+    float* part = reinterpret_cast<float*>(ss + (size_t) DN_TC * nu);             // [DN_TC][units]
     const int row0 = blockIdx.x * rows_per_block;
     const size_t ebase = (size_t) jb.w * expert_units + (size_t) row0 * nu;
     const int live_units = min(units, (nrows - row0) * nu), live_rows = min(rows_per_block, nrows - row0);
@@ -414,8 +416,8 @@ __global__ void __launch_bounds__(DN_THREADS, 4) k_moe_down_q6p(const uint4* __r
             const unsigned lw[4] = {ql[k].x, ql[k].y, ql[k].z, ql[k].w};
 #pragma unroll
             for (int w = 0; w < 4; ++w) {
-                v[k][w] = __vsub4((lw[w] & 0x0F0F0F0Fu) | (((qh[k].x >> (2 * w)) & 0x03030303u) << 4), 0x20202020u);
-                v[k][4 + w] = __vsub4(((lw[w] >> 4) & 0x0F0F0F0Fu) | (((qh[k].y >> (2 * w)) & 0x03030303u) << 4), 0x20202020u);
+                v[k][w] = (lw[w] & 0x0F0F0F0Fu) | (((qh[k].x >> (2 * w)) & 0x03030303u) << 4);          // codes 0..63; the -32
+                v[k][4 + w] = ((lw[w] >> 4) & 0x0F0F0F0Fu) | (((qh[k].y >> (2 * w)) & 0x03030303u) << 4);   // goes through ss
             }
         }
     }
@@ -427,7 +429,17 @@ __global__ void __launch_bounds__(DN_THREADS, 4) k_moe_down_q6p(const uint4* __r
             const int j = it / (ffs / 16), c = it % (ffs / 16);
             reinterpret_cast<uint4*>(sq + (size_t) j * ffs)[c] = reinterpret_cast<const uint4*>(hq + (size_t) jb.y[c0 + j] * ffs)[c];
         }
-        for (int it = threadIdx.x; it < cn * nu; it += DN_THREADS) sd[it] = hd[(size_t) jb.y[c0 + it / nu] * nu + it % nu];
+        for (int it = threadIdx.x; it < cn * nu; it += DN_THREADS) {
+            const int j = it / nu, u = it % nu;
+            sd[it] = hd[(size_t) jb.y[c0 + j] * nu + u];
+            const uint4* hp = reinterpret_cast<const uint4*>(hq + (size_t) jb.y[c0 + j] * ffs + u * 32);
+            const uint4 h0 = hp[0], h1 = hp[1];
+            int s0 = __dp4a(0x01010101, (int) h0.x, 0), s1 = __dp4a(0x01010101, (int) h1.x, 0);
+            s0 = __dp4a(0x01010101, (int) h0.y, s0), s1 = __dp4a(0x01010101, (int) h1.y, s1);
+            s0 = __dp4a(0x01010101, (int) h0.z, s0), s1 = __dp4a(0x01010101, (int) h1.z, s1);
+            s0 = __dp4a(0x01010101, (int) h0.w, s0), s1 = __dp4a(0x01010101, (int) h1.w, s1);
+            ss[it] = make_int2(32 * s0, 32 * s1);
+        }
         __syncthreads();
 #pragma unroll
         for (int k = 0; k < DN_UPT; ++k) {
@@ -439,11 +451,12 @@ __global__ void __launch_bounds__(DN_THREADS, 4) k_moe_down_q6p(const uint4* __r
                 if (j >= cn) break;
                 const uint4* ap = reinterpret_cast<const uint4*>(sq + (size_t) j * ffs + u * 32);
                 const uint4 a0 = ap[0], a1 = ap[1];
-                int is0 = __dp4a((int) v[k][0], (int) a0.x, 0);
+                const int2 bias = ss[j * nu + u];   // sum (code - 32) a = sum code a - 32 sum a, exactly
+                int is0 = __dp4a((int) v[k][0], (int) a0.x, -bias.x);
                 is0 = __dp4a((int) v[k][1], (int) a0.y, is0);
                 is0 = __dp4a((int) v[k][2], (int) a0.z, is0);
                 is0 = __dp4a((int) v[k][3], (int) a0.w, is0);
-                int is1 = __dp4a((int) v[k][4], (int) a1.x, 0);
+                int is1 = __dp4a((int) v[k][4], (int) a1.x, -bias.y);
                 is1 = __dp4a((int) v[k][5], (int) a1.y, is1);
                 is1 = __dp4a((int) v[k][6], (int) a1.z, is1);
                 is1 = __dp4a((int) v[k][7], (int) a1.w, is1);
@@ -520,7 +533,7 @@ int fnx_moe_gate_up(const FnxExperts* A, const FnxJob* jobs, const int* njobs, i
             return gu_q4k_tma_launch((const uint8_t*) A->a, A->stride, nrows, n, jobs, njobs, (const uint8_t*) xq, gu, strm(st));
         const int rpb = 64;
         const dim3 grid((nrows + rpb - 1) / rpb, njobs_max);
-        const size_t sm = (size_t) GU_TC * (n + (n / 32) * 8);
+        const size_t sm = (size_t) GU_TC * (n + (n / 64) * 16);
         const uint8_t* a = (const uint8_t*) A->a;
 #define GU_CASE(G)                                                                                                          \
     case G:                                                                                                                 \
@@ -551,7 +564,7 @@ int fnx_moe_down(const FnxExperts* A, const FnxJob* jobs, const int* njobs, int 
         FNX_REQUIRE(nu <= DN_THREADS * DN_UPT, "moe_down: ff width %d too wide for a block", ffs);
         int rpb = DN_THREADS * DN_UPT / nu;   // up to 768 units a block
         if (rpb > nrows) rpb = nrows;
-        const size_t sm = (size_t) DN_TC * ffs + (size_t) DN_TC * nu * 4 + (size_t) DN_TC * rpb * nu * 4;
+        const size_t sm = (size_t) DN_TC * ffs + (size_t) DN_TC * nu * 12 + (size_t) DN_TC * rpb * nu * 4;
         if (smem_optin(k_moe_down_q6p, sm, "moe_down q6_K")) return 1;
         const dim3 grid((nrows + rpb - 1) / rpb, njobs_max);
         k_moe_down_q6p<<<grid, DN_THREADS, sm, strm(st)>>>((const uint4*) A->a, (const uint2*) A->b, (const uint16_t*) A->c,
