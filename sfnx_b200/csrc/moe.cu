@@ -247,14 +247,15 @@ __device__ __forceinline__ uint4 ldg_stream(const void* p) {   // read-once weig
     return v;
 }
 
-// Rows of a job are taken GU_TC at a time (almost every job of a window has one to three rows): their activations sit in
-// 15 KB of shared memory and the per-row sums in registers, so four blocks fit an SM and their loads overlap.
-constexpr int GU_TC = 4, GU_MAGIC = 0x4B400000;
+// What bounds this kernel is the shared-memory data pipe (the activations every lane reads), not HBM: so a lane keeps the
+// activations of its group in registers and applies them to GU_R rows, and the rows of a job are taken GU_TC at a time
+// (three jobs in four have one row, one in a hundred more than three).
+constexpr int GU_TC = 2, GU_R = 4, GU_MAGIC = 0x4B400000, GU_RPB = GU_THREADS / 8 * GU_R;
 
 template <int GPL>
-__global__ void __launch_bounds__(GU_THREADS, 4) k_moe_gu_q4k(const uint8_t* __restrict__ A, size_t sa, int nrows, int n,
+__global__ void __launch_bounds__(GU_THREADS, 2) k_moe_gu_q4k(const uint8_t* __restrict__ A, size_t sa, int nrows, int n,
                                                           const FnxJob* __restrict__ jobs, const int* __restrict__ njobs,
-                                                          const uint8_t* __restrict__ xq, float* __restrict__ out, int rows_per_block) {
+                                                          const uint8_t* __restrict__ xq, float* __restrict__ out) {
     const int ji = blockIdx.y;
     if (ji >= *njobs) return;
     extern __shared__ __align__(16) unsigned char smem[];
@@ -265,7 +266,11 @@ __global__ void __launch_bounds__(GU_THREADS, 4) k_moe_gu_q4k(const uint8_t* __r
     int8_t* aq = reinterpret_cast<int8_t*>(smem);                              // [GU_TC][n]
     float4* ag = reinterpret_cast<float4*>(smem + (size_t) GU_TC * n);         // [GU_TC][n / 64]: d8 low, d8 high, sum low, sum high
     const size_t row_b = (size_t) n / 256 * 144;
-    const uint8_t* We = A + (size_t) jb.w * sa;
+    const int row0 = blockIdx.x * GU_RPB + (threadIdx.x >> 3) * GU_R;          // this lane group's GU_R consecutive rows
+    const uint8_t* wrow = A + (size_t) jb.w * sa + (size_t) min(row0, nrows - 1) * row_b;
+    size_t roff[GU_R];
+#pragma unroll
+    for (int rr = 0; rr < GU_R; ++rr) roff[rr] = (size_t) (min(row0 + rr, nrows - 1) - min(row0, nrows - 1)) * row_b;
 #pragma unroll 1
     for (int c0 = 0; c0 < jb.n; c0 += GU_TC) {
         const int cn = min(GU_TC, jb.n - c0);
@@ -287,66 +292,61 @@ __global__ void __launch_bounds__(GU_THREADS, 4) k_moe_gu_q4k(const uint8_t* __r
             gq[2 + (b & 1)] = (float) sum;
         }
         __syncthreads();
+        float tmp[GU_R][GU_TC];
+#pragma unroll
+        for (int rr = 0; rr < GU_R; ++rr)
+#pragma unroll
+            for (int r = 0; r < GU_TC; ++r) tmp[rr][r] = 0.f;
 #pragma unroll 1
-        for (int rb = 0; rb < rows_per_block; rb += GU_THREADS / 8) {
-            const int row = blockIdx.x * rows_per_block + rb + (threadIdx.x >> 3);
-            const bool live = row < nrows;   // uniform over the 8 lanes of a row
-            const uint8_t* wrow = We + (size_t) (live ? row : 0) * row_b;
-            float tmp[GU_TC];
+        for (int i = 0; i < GPL; ++i) {
+            const int g = lane8 + i * 8, jg = g & 3, yb = (g >> 2) * 8 + jg * 2;
+            uint4 hdr[GU_R], q0[GU_R], q1[GU_R];
 #pragma unroll
-            for (int r = 0; r < GU_TC; ++r) tmp[r] = 0.f;
-#pragma unroll 1
-            for (int i0 = 0; i0 < GPL; i0 += 2) {   // two groups' loads in flight per lane, many warps per SM
-                uint4 hdr[2], q0[2], q1[2];
+            for (int rr = 0; rr < GU_R; ++rr) {
+                const uint8_t* blk = wrow + roff[rr] + (size_t) (g >> 2) * 144;
+                hdr[rr] = ldg_stream(blk);
+                q0[rr] = ldg_stream(blk + 16 + 32 * jg);
+                q1[rr] = ldg_stream(blk + 32 + 32 * jg);
+            }
+            float d[GU_R], dmin[GU_R], sc0[GU_R], m0[GU_R], sc1[GU_R], m1[GU_R];
 #pragma unroll
-                for (int u = 0; u < 2; ++u) {
-                    const int g = lane8 + min(i0 + u, GPL - 1) * 8;
-                    const uint8_t* blk = wrow + (size_t) (g >> 2) * 144;
-                    hdr[u] = ldg_stream(blk);
-                    q0[u] = ldg_stream(blk + 16 + 32 * (g & 3));
-                    q1[u] = ldg_stream(blk + 32 + 32 * (g & 3));
-                }
-#pragma unroll
-                for (int u = 0; u < 2; ++u) {
-                    if (i0 + u >= GPL) break;
-                    const int g = lane8 + (i0 + u) * 8, jg = g & 3, yb = (g >> 2) * 8 + jg * 2;
-                    const float d = h2f((uint16_t) (hdr[u].x & 0xffff)), dmin = h2f((uint16_t) (hdr[u].x >> 16));
-                    float sc0, m0, sc1, m1;
-                    q4k_scale_min(hdr[u], 2 * jg, sc0, m0);
-                    q4k_scale_min(hdr[u], 2 * jg + 1, sc1, m1);
-                    const unsigned qw[8] = {q0[u].x, q0[u].y, q0[u].z, q0[u].w, q1[u].x, q1[u].y, q1[u].z, q1[u].w};
-                    unsigned ql[8], qh[8];
-#pragma unroll
-                    for (int w = 0; w < 8; ++w) ql[w] = qw[w] & 0x0F0F0F0Fu, qh[w] = (qw[w] >> 4) & 0x0F0F0F0Fu;
-#pragma unroll
-                    for (int r = 0; r < GU_TC; ++r) {
-                        if (r >= cn) break;
-                        const uint4* ap = reinterpret_cast<const uint4*>(aq + (size_t) r * n + yb * 32);
-                        const uint4 a0 = ap[0], a1 = ap[1], a2 = ap[2], a3 = ap[3];
-                        int dl = __dp4a((int) ql[0], (int) a0.x, GU_MAGIC), dh = __dp4a((int) qh[0], (int) a2.x, GU_MAGIC);
-                        dl = __dp4a((int) ql[1], (int) a0.y, dl), dh = __dp4a((int) qh[1], (int) a2.y, dh);
-                        dl = __dp4a((int) ql[2], (int) a0.z, dl), dh = __dp4a((int) qh[2], (int) a2.z, dh);
-                        dl = __dp4a((int) ql[3], (int) a0.w, dl), dh = __dp4a((int) qh[3], (int) a2.w, dh);
-                        dl = __dp4a((int) ql[4], (int) a1.x, dl), dh = __dp4a((int) qh[4], (int) a3.x, dh);
-                        dl = __dp4a((int) ql[5], (int) a1.y, dl), dh = __dp4a((int) qh[5], (int) a3.y, dh);
-                        dl = __dp4a((int) ql[6], (int) a1.z, dl), dh = __dp4a((int) qh[6], (int) a3.z, dh);
-                        dl = __dp4a((int) ql[7], (int) a1.w, dl), dh = __dp4a((int) qh[7], (int) a3.w, dh);
-                        const float4 sg = ag[(size_t) r * (nb / 2) + (yb >> 1)];   // d8l, d8h, (float) sl, (float) sh
-                        // the dots started at the bits of 1.5 * 2^23: as floats, minus that constant, they are (float) dot
-                        const float fl = fsub(__int_as_float(dl), 12582912.0f), fh = fsub(__int_as_float(dh), 12582912.0f);
-                        const float pos = fmul(d, fadd(fmul(sg.x, fmul(sc0, fl)), fmul(sg.y, fmul(sc1, fh))));
-                        const float neg = fmul(dmin, fadd(fmul(sg.x, fmul(m0, sg.z)), fmul(sg.y, fmul(m1, sg.w))));
-                        tmp[r] = fadd(tmp[r], fsub(pos, neg));
-                    }
-                }
+            for (int rr = 0; rr < GU_R; ++rr) {
+                d[rr] = h2f((uint16_t) (hdr[rr].x & 0xffff)), dmin[rr] = h2f((uint16_t) (hdr[rr].x >> 16));
+                q4k_scale_min(hdr[rr], 2 * jg, sc0[rr], m0[rr]);
+                q4k_scale_min(hdr[rr], 2 * jg + 1, sc1[rr], m1[rr]);
             }
 #pragma unroll
             for (int r = 0; r < GU_TC; ++r) {
                 if (r >= cn) break;
-                const float v = sum8(tmp[r]);
-                if (live && lane8 == 0) out[(size_t) jb.out[c0 + r] * nrows + row] = v;
+                const uint4* ap = reinterpret_cast<const uint4*>(aq + (size_t) r * n + yb * 32);
+                const uint4 a0 = ap[0], a1 = ap[1], a2 = ap[2], a3 = ap[3];
+                const float4 sg = ag[(size_t) r * (nb / 2) + (yb >> 1)];   // d8l, d8h, (float) sl, (float) sh
+                const unsigned al[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+                const unsigned ah[8] = {a2.x, a2.y, a2.z, a2.w, a3.x, a3.y, a3.z, a3.w};
+#pragma unroll
+                for (int rr = 0; rr < GU_R; ++rr) {
+                    const unsigned qw[8] = {q0[rr].x, q0[rr].y, q0[rr].z, q0[rr].w, q1[rr].x, q1[rr].y, q1[rr].z, q1[rr].w};
+                    int dl = GU_MAGIC, dh = GU_MAGIC;   // started at the bits of 1.5 * 2^23: as floats minus that, (float) dot
+#pragma unroll
+                    for (int w = 0; w < 8; ++w) {
+                        dl = __dp4a((int) (qw[w] & 0x0F0F0F0Fu), (int) al[w], dl);
+                        dh = __dp4a((int) ((qw[w] >> 4) & 0x0F0F0F0Fu), (int) ah[w], dh);
+                    }
+                    const float fl = fsub(__int_as_float(dl), 12582912.0f), fh = fsub(__int_as_float(dh), 12582912.0f);
+                    const float pos = fmul(d[rr], fadd(fmul(sg.x, fmul(sc0[rr], fl)), fmul(sg.y, fmul(sc1[rr], fh))));
+                    const float neg = fmul(dmin[rr], fadd(fmul(sg.x, fmul(m0[rr], sg.z)), fmul(sg.y, fmul(m1[rr], sg.w))));
+                    tmp[rr][r] = fadd(tmp[rr][r], fsub(pos, neg));
+                }
             }
         }
+#pragma unroll
+        for (int rr = 0; rr < GU_R; ++rr)
+#pragma unroll
+            for (int r = 0; r < GU_TC; ++r) {
+                if (r >= cn) break;
+                const float v = sum8(tmp[rr][r]);
+                if (lane8 == 0 && row0 + rr < nrows) out[(size_t) jb.out[c0 + r] * nrows + row0 + rr] = v;
+            }
     }
 }
 
@@ -373,27 +373,31 @@ __global__ void __launch_bounds__(256) k_swiglu_q8(const float* __restrict__ gu,
 // added in ascending order (reference src/moe.cuh:330-344).
 constexpr int DN_THREADS = 256;
 
-constexpr int DN_TC = 4, DN_UPT = 3;   // activation rows a pass; units a thread (its loads all in flight)
+constexpr int DN_TC = 2, DN_UPT = 3;   // activation rows a pass; weight rows a thread (its loads all in flight)
 
+// Thread (u, r) takes 32-column unit u of rows r, r + RP, r + 2 RP of the block (RP = 256 / units-per-row rows a pass), so
+// the activations of its unit are read from shared memory once per activation row and used for three weight rows: the
+// kernel is bound by the shared-memory data pipe otherwise.  Lanes run over consecutive units of consecutive rows, so
+// every plane is read in contiguous 16-, 8- and 2-byte pieces.
 __global__ void __launch_bounds__(DN_THREADS, 4) k_moe_down_q6p(const uint4* __restrict__ QL, const uint2* __restrict__ QH,
                                                                const uint16_t* __restrict__ SC, const uint16_t* __restrict__ D,
                                                                size_t expert_units, int nrows, int ffs, const FnxJob* __restrict__ jobs,
                                                                const int* __restrict__ njobs, const int8_t* __restrict__ hq,
-                                                               const float* __restrict__ hd, float* __restrict__ out, int rows_per_block) {
+                                                               const float* __restrict__ hd, float* __restrict__ out) {
     const int ji = blockIdx.y;
     if (ji >= *njobs) return;
     extern __shared__ __align__(16) unsigned char smem[];
     __shared__ FnxJob jb;
     if (threadIdx.x < sizeof(FnxJob) / 4) reinterpret_cast<int*>(&jb)[threadIdx.x] = reinterpret_cast<const int*>(jobs + ji)[threadIdx.x];
     __syncthreads();
-    const int nu = ffs / 32, units = rows_per_block * nu;   // units <= DN_THREADS * DN_UPT
-    int8_t* sq = reinterpret_cast<int8_t*>(smem);                                // [DN_TC][ffs]
-    float* sd = reinterpret_cast<float*>(smem + (size_t) DN_TC * ffs);            // [DN_TC][nu]
+    const int nu = ffs / 32, RP = DN_THREADS / nu, rpb = RP * DN_UPT, pu = nu + 1;   // pu: padded units a row in `part`
+    uint4* sq = reinterpret_cast<uint4*>(smem);                                   // [DN_TC][2 halves][nu] 16 bytes each
+    float* sd = reinterpret_cast<float*>(sq + (size_t) DN_TC * 2 * nu);           // [DN_TC][nu]
     int2* ss = reinterpret_cast<int2*>(sd + (size_t) DN_TC * nu);                 // [DN_TC][nu]: 32 x the sums of each half
-    float* part = reinterpret_cast<float*>(ss + (size_t) DN_TC * nu);             // [DN_TC][units]
-    const int row0 = blockIdx.x * rows_per_block;
+    float* part = reinterpret_cast<float*>(ss + (size_t) DN_TC * nu);             // [DN_TC][rpb][pu]
+    const int row0 = blockIdx.x * rpb, u = threadIdx.x % nu, r = threadIdx.x / nu;
+    const bool active = r < RP;
     const size_t ebase = (size_t) jb.w * expert_units + (size_t) row0 * nu;
-    const int live_units = min(units, (nrows - row0) * nu), live_rows = min(rows_per_block, nrows - row0);
     // this thread's units: the weights are read once and kept for every pass over the job's rows
     unsigned v[DN_UPT][8];
     float d[DN_UPT];
@@ -404,11 +408,12 @@ __global__ void __launch_bounds__(DN_THREADS, 4) k_moe_down_q6p(const uint4* __r
         unsigned scw[DN_UPT];
 #pragma unroll
         for (int k = 0; k < DN_UPT; ++k) {
-            const int g = min(threadIdx.x + k * DN_THREADS, live_units - 1);
-            ql[k] = ldg_stream(QL + ebase + g);
-            qh[k] = __ldg(QH + ebase + g);
-            scw[k] = SC[ebase + g];
-            d[k] = h2f(D[ebase + g]);
+            const int row = min(row0 + k * RP + min(r, RP - 1), nrows - 1);
+            const size_t g = (size_t) jb.w * expert_units + (size_t) row * nu + u;
+            ql[k] = ldg_stream(QL + g);
+            qh[k] = __ldg(QH + g);
+            scw[k] = SC[g];
+            d[k] = h2f(D[g]);
         }
 #pragma unroll
         for (int k = 0; k < DN_UPT; ++k) {
@@ -421,19 +426,18 @@ __global__ void __launch_bounds__(DN_THREADS, 4) k_moe_down_q6p(const uint4* __r
             }
         }
     }
+    (void) ebase;
 #pragma unroll 1
     for (int c0 = 0; c0 < jb.n; c0 += DN_TC) {
         const int cn = min(DN_TC, jb.n - c0);
         if (c0) __syncthreads();
-        for (int it = threadIdx.x; it < cn * (ffs / 16); it += DN_THREADS) {
-            const int j = it / (ffs / 16), c = it % (ffs / 16);
-            reinterpret_cast<uint4*>(sq + (size_t) j * ffs)[c] = reinterpret_cast<const uint4*>(hq + (size_t) jb.y[c0 + j] * ffs)[c];
-        }
         for (int it = threadIdx.x; it < cn * nu; it += DN_THREADS) {
-            const int j = it / nu, u = it % nu;
-            sd[it] = hd[(size_t) jb.y[c0 + j] * nu + u];
-            const uint4* hp = reinterpret_cast<const uint4*>(hq + (size_t) jb.y[c0 + j] * ffs + u * 32);
+            const int j = it / nu, uu = it % nu;
+            sd[it] = hd[(size_t) jb.y[c0 + j] * nu + uu];
+            const uint4* hp = reinterpret_cast<const uint4*>(hq + (size_t) jb.y[c0 + j] * ffs + uu * 32);
             const uint4 h0 = hp[0], h1 = hp[1];
+            sq[(size_t) (j * 2) * nu + uu] = h0;        // the two halves in planes of their own: a warp's 16-byte reads
+            sq[(size_t) (j * 2 + 1) * nu + uu] = h1;    // are contiguous
             int s0 = __dp4a(0x01010101, (int) h0.x, 0), s1 = __dp4a(0x01010101, (int) h1.x, 0);
             s0 = __dp4a(0x01010101, (int) h0.y, s0), s1 = __dp4a(0x01010101, (int) h1.y, s1);
             s0 = __dp4a(0x01010101, (int) h0.z, s0), s1 = __dp4a(0x01010101, (int) h1.z, s1);
@@ -441,34 +445,35 @@ __global__ void __launch_bounds__(DN_THREADS, 4) k_moe_down_q6p(const uint4* __r
             ss[it] = make_int2(32 * s0, 32 * s1);
         }
         __syncthreads();
-#pragma unroll
-        for (int k = 0; k < DN_UPT; ++k) {
-            const int g = threadIdx.x + k * DN_THREADS;
-            if (g >= live_units) break;
-            const int u = g % nu;
+        if (active) {
 #pragma unroll
             for (int j = 0; j < DN_TC; ++j) {
                 if (j >= cn) break;
-                const uint4* ap = reinterpret_cast<const uint4*>(sq + (size_t) j * ffs + u * 32);
-                const uint4 a0 = ap[0], a1 = ap[1];
+                const uint4 a0 = sq[(size_t) (j * 2) * nu + u], a1 = sq[(size_t) (j * 2 + 1) * nu + u];
                 const int2 bias = ss[j * nu + u];   // sum (code - 32) a = sum code a - 32 sum a, exactly
-                int is0 = __dp4a((int) v[k][0], (int) a0.x, -bias.x);
-                is0 = __dp4a((int) v[k][1], (int) a0.y, is0);
-                is0 = __dp4a((int) v[k][2], (int) a0.z, is0);
-                is0 = __dp4a((int) v[k][3], (int) a0.w, is0);
-                int is1 = __dp4a((int) v[k][4], (int) a1.x, -bias.y);
-                is1 = __dp4a((int) v[k][5], (int) a1.y, is1);
-                is1 = __dp4a((int) v[k][6], (int) a1.z, is1);
-                is1 = __dp4a((int) v[k][7], (int) a1.w, is1);
-                const int I = sc0[k] * is0 + sc1[k] * is1;
-                part[(size_t) j * units + g] = fmul(d[k], fmul(sd[j * nu + u], (float) I));
+                const float dj = sd[j * nu + u];
+#pragma unroll
+                for (int k = 0; k < DN_UPT; ++k) {
+                    int is0 = __dp4a((int) v[k][0], (int) a0.x, -bias.x);
+                    is0 = __dp4a((int) v[k][1], (int) a0.y, is0);
+                    is0 = __dp4a((int) v[k][2], (int) a0.z, is0);
+                    is0 = __dp4a((int) v[k][3], (int) a0.w, is0);
+                    int is1 = __dp4a((int) v[k][4], (int) a1.x, -bias.y);
+                    is1 = __dp4a((int) v[k][5], (int) a1.y, is1);
+                    is1 = __dp4a((int) v[k][6], (int) a1.z, is1);
+                    is1 = __dp4a((int) v[k][7], (int) a1.w, is1);
+                    const int I = sc0[k] * is0 + sc1[k] * is1;
+                    part[((size_t) j * rpb + k * RP + r) * pu + u] = fmul(d[k], fmul(dj, (float) I));
+                }
             }
         }
         __syncthreads();
+        const int live_rows = min(rpb, nrows - row0);
         for (int e = threadIdx.x; e < cn * live_rows; e += DN_THREADS) {
             const int j = e / live_rows, rr = e % live_rows;
+            const float* pr = part + ((size_t) j * rpb + rr) * pu;
             float s = 0.f;
-            for (int k = 0; k < nu; ++k) s = fadd(s, part[(size_t) j * units + rr * nu + k]);
+            for (int k = 0; k < nu; ++k) s = fadd(s, pr[k]);
             out[(size_t) jb.out[c0 + j] * nrows + row0 + rr] = s;
         }
     }
@@ -526,19 +531,18 @@ int fnx_moe_gate_up(const FnxExperts* A, const FnxJob* jobs, const int* njobs, i
     const int n = A->ncols, nrows = A->nrows, maxrows = FNX_MAXT;
     if (A->type == FNX_Q4_K) {
         FNX_REQUIRE(n % 512 == 0 && n / 512 >= 1 && n / 512 <= 8, "moe gate|up q4_K: %d columns (multiples of 512 up to 4096)", n);
-        // blocks of 64 rows with direct 16-byte loads, four blocks an SM (measured faster than staging the panels through
+        // blocks of 128 rows with direct 16-byte loads (measured faster than staging the panels through
         // shared memory with bulk copies: each weight byte is used once and the consumer is instruction-bound)
         static const bool staged = getenv("FNX_GU_TMA") != nullptr;   // a tuning knob: the TMA-staged persistent kernel instead
         if (staged && gu_q4k_tma_smem(n) + 1024 <= 227 * 1024 && ((uintptr_t) A->a % 16) == 0 && A->stride % 16 == 0)
             return gu_q4k_tma_launch((const uint8_t*) A->a, A->stride, nrows, n, jobs, njobs, (const uint8_t*) xq, gu, strm(st));
-        const int rpb = 64;
-        const dim3 grid((nrows + rpb - 1) / rpb, njobs_max);
+        const dim3 grid((nrows + GU_RPB - 1) / GU_RPB, njobs_max);
         const size_t sm = (size_t) GU_TC * (n + (n / 64) * 16);
         const uint8_t* a = (const uint8_t*) A->a;
 #define GU_CASE(G)                                                                                                          \
     case G:                                                                                                                 \
         if (smem_optin(k_moe_gu_q4k<G>, sm, "moe gate|up q4_K")) return 1;                                                  \
-        k_moe_gu_q4k<G><<<grid, GU_THREADS, sm, strm(st)>>>(a, A->stride, nrows, n, jobs, njobs, (const uint8_t*) xq, gu, rpb); \
+        k_moe_gu_q4k<G><<<grid, GU_THREADS, sm, strm(st)>>>(a, A->stride, nrows, n, jobs, njobs, (const uint8_t*) xq, gu); \
         break;
         switch (n / 512) {
             GU_CASE(1) GU_CASE(2) GU_CASE(3) GU_CASE(4) GU_CASE(5) GU_CASE(6) GU_CASE(7) GU_CASE(8)
@@ -561,14 +565,13 @@ int fnx_moe_down(const FnxExperts* A, const FnxJob* jobs, const int* njobs, int 
     if (launch_ok("moe_down swiglu")) return 1;
     if (A->type == FNX_Q6_K) {
         const int nu = ffs / 32;
-        FNX_REQUIRE(nu <= DN_THREADS * DN_UPT, "moe_down: ff width %d too wide for a block", ffs);
-        int rpb = DN_THREADS * DN_UPT / nu;   // up to 768 units a block
-        if (rpb > nrows) rpb = nrows;
-        const size_t sm = (size_t) DN_TC * ffs + (size_t) DN_TC * nu * 12 + (size_t) DN_TC * rpb * nu * 4;
+        FNX_REQUIRE(nu <= DN_THREADS, "moe_down: ff width %d too wide for a block", ffs);
+        const int rpb = DN_THREADS / nu * DN_UPT;
+        const size_t sm = (size_t) DN_TC * nu * (32 + 4 + 8) + (size_t) DN_TC * rpb * (nu + 1) * 4;
         if (smem_optin(k_moe_down_q6p, sm, "moe_down q6_K")) return 1;
         const dim3 grid((nrows + rpb - 1) / rpb, njobs_max);
         k_moe_down_q6p<<<grid, DN_THREADS, sm, strm(st)>>>((const uint4*) A->a, (const uint2*) A->b, (const uint16_t*) A->c,
-                                                        (const uint16_t*) A->d, A->stride, nrows, ffs, jobs, njobs, h8, hd, part, rpb);
+                                                        (const uint16_t*) A->d, A->stride, nrows, ffs, jobs, njobs, h8, hd, part);
         return launch_ok("moe_down q6_K");
     }
     return fail("moe_down: expert type %d not supported (Q6_K units)", A->type);
