@@ -3,6 +3,7 @@
 // and commit: src/engine.cu:900-1054, src/engine_common.cu:525-568); every kernel goes through the same C ABI entry
 // points an external caller would use.  The stages end where the GPUs must exchange data, so that a caller driving
 // several GPUs can put its collective between two stages.
+#include <cstdlib>
 #include <cstring>
 
 #include "common.cuh"
@@ -242,8 +243,15 @@ int fnx_window_stage(const FnxStackCfg* cfg, const FnxLayer* layers, const FnxHe
         TRK("attn_prep_append", 1, fnx_attn_prep_append(qg, k, v, L.q_norm, L.k_norm, L.kc, L.vc, L.pages, c.card, c.ncard, T, ctl, c.eps,
                                                         rope, c.nq, c.nkv, c.hd, st));
         float* mine = (float*) (b + w.partials) + (size_t) c.card * T * c.nq * (c.hd + 2);
-        TRK("attn_partial", 2, fnx_attn_partial(qg, L.kc, L.vc, L.pages, mine, c.card, c.ncard, T, ctl, c.nq, c.nkv, c.hd,
-                                                (float*) (b + w.att_scratch), st));
+        // FNX_ATTN_EXACT=1: the scan in the reference's order of sums (bit-reproducible against the CPU statement, several
+        // times slower); default: the one-pass tensor-core scan
+        const char* ex = getenv("FNX_ATTN_EXACT");
+        if (ex && ex[0] == '1')
+            TRK("attn_partial", 2, fnx_attn_partial_exact(qg, L.kc, L.vc, L.pages, mine, c.card, c.ncard, T, ctl, c.nq, c.nkv, c.hd,
+                                                          (float*) (b + w.att_scratch), st));
+        else
+            TRK("attn_partial", 2, fnx_attn_partial(qg, L.kc, L.vc, L.pages, mine, c.card, c.ncard, T, ctl, c.nq, c.nkv, c.hd,
+                                                    (float*) (b + w.att_scratch), st));
         return 0;
     }
     if (sg.part == 1) {   // attention: merge the GPUs' partials for this GPU's heads, gate, output projection

@@ -60,9 +60,7 @@ class SyntheticStack:
         self.kh0 = lib.fnx_khead_first(s.nkh, s.nvh, ncard, card)
         self.nk = lib.fnx_khead_count(s.nkh, s.nvh, ncard, card)
         self.nv = len(self.vheads)
-        per = (s.vocab + ncard - 1) // ncard
-        self.v0 = card * per
-        self.vrows = max(0, min(s.vocab, self.v0 + per) - self.v0)
+        self.v0, self.vrows = vocab_slice(s.vocab, ncard, card)
         self.kv_rows = lib.fnx_kv_rows_per_card(s.ctx + s.kv_slack, ncard)
         self.cfg = L.StackCfg(s.n, s.nexp, s.topk, self.ffs, self.nk, self.nv, s.nq, s.nkv, s.hd, s.nrot, self.v0, self.vrows,
                               len(s.kinds), ncard, card, s.eps, s.rope_base)
@@ -215,6 +213,26 @@ class SyntheticStack:
         return sum(t.numel() * t.element_size() for t in self.keep)
 
 
+def merge_best(values, indices):
+    """Per row, the token of the GPU whose slice holds the largest logit: strict > scanning GPU 0 upward, so the lower
+    GPU wins a tie (reference src/engine_common.cu:781-787).  values, indices: [ngpu][T]."""
+    out = []
+    for t in range(values.shape[1]):
+        b = 0
+        for c in range(1, values.shape[0]):
+            if values[c, t] > values[b, t]:
+                b = c
+        out.append(int(indices[b, t]))
+    return out
+
+
+def vocab_slice(vocab, ncard, card):
+    """This GPU's contiguous vocabulary range, ceil(vocab / n) each, the last shorter (reference src/model.cpp:836)."""
+    per = (vocab + ncard - 1) // ncard
+    v0 = card * per
+    return v0, max(0, min(vocab, v0 + per) - v0)
+
+
 class WindowRunner:
     """One window of T rows as a CUDA graph on its own stream: embedding rows from the token ids, every stage, and
     between stages the collectives of the process group (NCCL) when there is more than one GPU."""
@@ -313,15 +331,7 @@ class WindowRunner:
         return self.merge_best()
 
     def merge_best(self):
-        v, i = self.h_v, self.h_i
-        out = []
-        for t in range(self.T):
-            b = 0
-            for c in range(1, self.stack.ncard):
-                if v[c, t] > v[b, t]:
-                    b = c
-            out.append(int(i[b, t]))
-        return out
+        return merge_best(self.h_v, self.h_i)
 
     def commit(self, n, tag):
         """Keep the first n rows of the last window: the DeltaNet layers' states and histories back to row n - 1."""

@@ -1,10 +1,11 @@
 """GPU parity of the whole verify window (stack of layers -> logits -> argmax -> acceptance -> rollback) against the CPU
 oracle composed stage by stage on the same seeded weights and token ids.
 
-A DeltaNet-only stack reproduces the oracle's logits bit for bit.  With attention layers the fast one-pass scan sums in
-its own order, so logits are held to the reference's exactness bar instead (tools/fnx_run.cpp:307-333: mean KL over
-the rows <= 1.25 x 4.85e-4 with, here, identical top-1 on every row), and the accepted counts and the greedy tokens of
-a multi-window run must be identical."""
+A DeltaNet-only stack, and a mixed stack with the attention scan in the reference's order of sums (FNX_ATTN_EXACT=1),
+reproduce the oracle's logits, greedy tokens, accepted counts and rolled-back states bit for bit over several windows.
+With the default one-pass tensor-core scan the attention output agrees to f32 rounding only, and the activation
+quantisers downstream turn such differences into occasional one-step flips; logits are then held to the reference's own
+exactness bar (tools/fnx_run.cpp:307-333: mean KL <= 1.25 x 4.85e-4, top-1 agreement >= 98.33 % - 1.5 points)."""
 import ctypes as C
 
 import numpy as np
@@ -109,7 +110,7 @@ def _run_windows(shape, stack, runner, orc, nwin, seed, exact):
 
     rng = np.random.default_rng(seed)
     pos, tag, x = shape.ctx, 1, 7
-    kls, total = [], 0
+    kls, agree, total = [], [], 0
     for w in range(nwin):
         rows = [x] + [int(v) for v in rng.integers(0, shape.vocab, 15)]
         if w > 0:   # drafts that follow the model for a while: run the oracle once to learn its greedy tokens
@@ -125,25 +126,28 @@ def _run_windows(shape, stack, runner, orc, nwin, seed, exact):
         ref_logits, ref_best = orc.window(rows, pos, tag)
         got_best = runner.window(rows, pos, tag)
         got_logits = runner.logits.detach().cpu().numpy()
-        if exact:
-            assert np.array_equal(got_logits.view(np.uint32), ref_logits.view(np.uint32)), "logits, window %d" % w
-        else:
-            kls.append(cases.kl_top64(ref_logits, got_logits).mean())
-            assert np.allclose(got_logits, ref_logits, rtol=1e-3, atol=1e-4)
-        assert got_best == ref_best, "greedy tokens, window %d" % w
         n_ref = O.accept_greedy(rows, ref_best)
         rc, oc = (C.c_int * 16)(*rows), (C.c_int * 16)(*got_best)
         n = L.load().fnx_accept_greedy(rc, oc, 16)
-        assert n == n_ref, "accepted count, window %d" % w
+        if exact:
+            assert np.array_equal(got_logits.view(np.uint32), ref_logits.view(np.uint32)), "logits, window %d" % w
+            assert got_best == ref_best, "greedy tokens, window %d" % w
+            assert n == n_ref, "accepted count, window %d" % w
+        else:
+            kls.append(cases.kl_top64(ref_logits, got_logits).mean())
+            agree.append(np.mean(np.array(got_best) == np.array(ref_best)))
+            assert np.allclose(got_logits, ref_logits, rtol=0, atol=2e-2)
+            n = n_ref   # follow the oracle's trajectory so that every window compares like with like
         runner.commit(n, tag)
         orc.commit(n)
         torch.cuda.synchronize()
         for (l, name), v in orc.state.items():   # states after the rollback
             if name in ("S", "hist"):
-                assert np.array_equal(stack.named[(l, name)].detach().cpu().numpy(), v), (l, name, w)
+                got = stack.named[(l, name)].detach().cpu().numpy()
+                assert np.array_equal(got, v) if exact else np.allclose(got, v, rtol=1e-2, atol=1e-3), (l, name, w)
         total += n
-        pos, tag, x = pos + n, tag + 1, got_best[n - 1]
-    return kls, total
+        pos, tag, x = pos + n, tag + 1, ref_best[n - 1]
+    return (kls, agree), total
 
 
 def test_window_deltanet_stack_bit_exact():
@@ -152,8 +156,16 @@ def test_window_deltanet_stack_bit_exact():
     assert 4 <= total <= 64
 
 
-def test_window_mixed_stack_within_exactness_bar():
+def test_window_mixed_stack_exact_attention_bit_exact(monkeypatch):
+    monkeypatch.setenv("FNX_ATTN_EXACT", "1")
     shape, stack, runner, orc = _make([0, 1, 0, 1], seed=6)
-    kls, total = _run_windows(shape, stack, runner, orc, nwin=4, seed=2, exact=False)
+    _, total = _run_windows(shape, stack, runner, orc, nwin=4, seed=2, exact=True)
+    assert 4 <= total <= 64
+
+
+def test_window_mixed_stack_fast_attention_within_exactness_bar(monkeypatch):
+    monkeypatch.delenv("FNX_ATTN_EXACT", raising=False)
+    shape, stack, runner, orc = _make([0, 1, 0, 1], seed=6)
+    (kls, agree), total = _run_windows(shape, stack, runner, orc, nwin=6, seed=2, exact=False)
     assert np.mean(kls) <= KL_BAR, kls
-    assert max(kls) < 1e-6, kls   # in practice orders of magnitude inside the bar
+    assert np.mean(agree) >= 0.9833 - 0.015, agree
