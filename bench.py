@@ -283,8 +283,12 @@ def main():
         result["cpu_baseline"] = bench_reference.cpu_baseline(stack, runner, rec[args.warmup], shape, accepted / args.steps)
     if rank == 0:
         print(json.dumps(result))
+    sys.stdout.flush()
     if world > 1:
-        dist.destroy_process_group()
+        # leave without tearing the communicator down: its destruction can wait for ever on the captured graphs' kernels
+        dist.barrier()
+        torch.cuda.synchronize()
+        os._exit(0)
 
 
 def distinct_experts(stack, runner, step, T):
