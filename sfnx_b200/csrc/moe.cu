@@ -43,7 +43,20 @@ __global__ void __launch_bounds__(RR_THREADS) k_router_route(const RouterArgs a,
     __shared__ float rsum[FNX_MAXT][RR_THREADS / 32];
     const float* xs = a.x;
     if (x_in_smem) {
-        for (int i = e; i < a.T * a.n / 4; i += RR_THREADS) reinterpret_cast<float4*>(xs_sm)[i] = reinterpret_cast<const float4*>(a.x)[i];
+        const int n4 = a.T * a.n / 4;
+        for (int i0 = 0; i0 < n4; i0 += RR_THREADS * 8) {   // eight loads in flight per thread before the stores
+            float4 v[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                const int i = i0 + k * RR_THREADS + e;
+                if (i < n4) v[k] = __ldg(reinterpret_cast<const float4*>(a.x) + i);
+            }
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                const int i = i0 + k * RR_THREADS + e;
+                if (i < n4) reinterpret_cast<float4*>(xs_sm)[i] = v[k];
+            }
+        }
         xs = xs_sm;
         __syncthreads();
     }
