@@ -125,6 +125,17 @@ int fnx_moe_gate_up(const FnxExperts* A, const FnxJob* jobs, const int* njobs, i
 size_t fnx_moe_h_bytes(int pairs, int ffs);
 int fnx_moe_down(const FnxExperts* A, const FnxJob* jobs, const int* njobs, int njobs_max, const float* gu, int npairs, void* hq,
                  float* part, void* st);
+/* No counterpart in the reference.  fnx_moe_down for callers that cannot allocate device memory (a plug-in inside another
+ * engine's stream, a host whose memory was all handed out at start-up): the scratch for the pairs' quantised h is an
+ * array inside the library, FNX_DOWN_NOALLOC_BYTES on every GPU that loads it, so the caller passes only inputs and
+ * outputs and the call allocates nothing.  Refused (non-zero, text in fnx_last_error) when fnx_moe_h_bytes(npairs,
+ * A->ncols) exceeds the array.  The first call on a device looks the array's address up (once per device, with that
+ * device current): make that first call before any stream capture.  All calls share the one array and it keeps the last
+ * call's contents; each call writes what it reads, so nothing is cleared, but two calls that overlap on the GPU (two
+ * streams, two threads) race on it: keep them in stream order. */
+#define FNX_DOWN_NOALLOC_BYTES (288 * 1024) /* 256 pairs x ff 1024: 256 KiB of int8 h + 32 KiB of scales */
+int fnx_moe_down_noalloc(const FnxExperts* A, const FnxJob* jobs, const int* njobs, int njobs_max, const float* gu, int npairs,
+                         float* part, void* st);
 /* reference src/kernels.hpp:307 swiglu_stacked_q8_1 + src/dense.cuh:162-198 (the shared expert): T rows of
  * [gate | up] -> h as int8 + f16-rounded scales, then the Q8_0 down into out[t][n] */
 int fnx_shared_expert(FnxQ8S gate_up, FnxQ8S down, const void* xq, int T, int n, int ffs, float* sh_gu, void* hq, float* out,

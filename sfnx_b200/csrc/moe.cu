@@ -590,6 +590,46 @@ int fnx_moe_down(const FnxExperts* A, const FnxJob* jobs, const int* njobs, int 
     return fail("moe_down: expert type %d not supported (Q6_K units)", A->type);
 }
 
+// ---- the down projection for callers that cannot allocate device memory
+// Some hosts of these kernels have no allocator to give: a plug-in running inside another engine's captured stream, a
+// callback with a fixed memory budget, a process whose allocations are all made at start-up by someone else.  For them the
+// scratch of fnx_moe_down (the pairs' quantised h) lives in the library itself: a file-scope device array of
+// FNX_DOWN_NOALLOC_BYTES, resident on every GPU that loads the library until the process exits.
+static __device__ __align__(256) unsigned char g_down_scratch[FNX_DOWN_NOALLOC_BYTES];
+
+// In host code the array's name is only a handle for the runtime, not a device address; the address comes from
+// cudaGetSymbolAddress, asked once per device with that device current.
+static void* down_scratch_ptr(void) {
+    static void* ptr[64] = {};
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+        fail("moe_down_noalloc: no current device");
+        return nullptr;
+    }
+    if (!ptr[dev]) {
+        void* p = nullptr;
+        const cudaError_t e = cudaGetSymbolAddress(&p, g_down_scratch);
+        if (e != cudaSuccess) {
+            fail("moe_down_noalloc: scratch address: %s", cudaGetErrorString(e));
+            return nullptr;
+        }
+        ptr[dev] = p;
+    }
+    return ptr[dev];
+}
+
+int fnx_moe_down_noalloc(const FnxExperts* A, const FnxJob* jobs, const int* njobs, int njobs_max, const float* gu, int npairs,
+                         float* part, void* st) {
+    FNX_REQUIRE(A && npairs >= 1, "moe_down_noalloc: no experts or pairs");
+    const size_t need = fnx_moe_h_bytes(npairs, A->ncols);
+    FNX_REQUIRE(need <= FNX_DOWN_NOALLOC_BYTES, "moe_down_noalloc: %d pairs x ff %d need %zu bytes of scratch, the built-in array holds %d",
+                npairs, A->ncols, need, FNX_DOWN_NOALLOC_BYTES);
+    void* hq = down_scratch_ptr();
+    if (!hq) return 1;
+    // every byte of the scratch that is read is written first by this call (the pairs' h), so nothing needs clearing
+    return fnx_moe_down(A, jobs, njobs, njobs_max, gu, npairs, hq, part, st);
+}
+
 int fnx_moe_combine(const float* part, const float* topw, const float* sh, const float* logits, int nexp, float* out, int T,
                     int n, int topk, void* st) {
     FNX_REQUIRE(T >= 1 && n >= 1, "moe_combine: empty");
