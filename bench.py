@@ -39,6 +39,7 @@ def parse():
     ap.add_argument("--experts", type=int, default=512, help="routed experts (512 = the benchmark configuration; fewer for small profiling runs)")
     ap.add_argument("--vocab", type=int, default=151936, help="vocabulary (151936 = the benchmark configuration)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-graph", action="store_true", help="enqueue every window call by call instead of replaying a CUDA graph")
     return ap.parse_args()
 
 
@@ -120,7 +121,7 @@ def main():
     shape = StackShape(kinds=kinds, ctx=args.ctx, kv_slack=(args.warmup + args.steps + 2) * T, nexp=args.experts, vocab=args.vocab)
     t_build = time.time()
     stack = SyntheticStack(shape, ncard=world, card=rank, seed=args.seed, device="cuda:%d" % local)
-    runner = WindowRunner(stack, T, group=group, graph=True)
+    runner = WindowRunner(stack, T, group=group, graph=not args.no_graph)
     t_build = time.time() - t_build
     lib = L.load()
 
