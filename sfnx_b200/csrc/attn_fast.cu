@@ -218,15 +218,24 @@ __global__ void k_attn_fast_merge(const float* __restrict__ scratch, float* __re
     const int h = blockIdx.x, t = blockIdx.y, i = threadIdx.x, qpk = nq / nkv, kvl = h / qpk, m = (h % qpk) * T + t, M = T * qpk;
     const float* base = scratch + ((size_t) kvl * nsplit * M + m) * (hd + 2);
     const size_t step = (size_t) M * (hd + 2);
+    __shared__ float sm_m[160], sm_w[160], sm_z[160];   // nsplit <= 148
+    for (int s = i; s < nsplit; s += blockDim.x) sm_m[s] = base[s * step + hd], sm_z[s] = base[s * step + hd + 1];
+    __syncthreads();
     float mx = -INFINITY;
-    for (int s = 0; s < nsplit; ++s) mx = fmaxf(mx, base[s * step + hd]);
+    for (int s = 0; s < nsplit; ++s) mx = fmaxf(mx, sm_m[s]);
+    for (int s = i; s < nsplit; s += blockDim.x) sm_w[s] = sm_m[s] == -INFINITY ? 0.f : ex_expf(fsub(sm_m[s], mx));
+    __syncthreads();
     float z = 0.f, acc = 0.f;
-    for (int s = 0; s < nsplit; ++s) {
-        const float ms = base[s * step + hd];
-        if (ms == -INFINITY) continue;
-        const float w = ex_expf(fsub(ms, mx));
-        z = ffma(w, base[s * step + hd + 1], z);
-        acc = ffma(w, base[s * step + i], acc);
+    for (int s0 = 0; s0 < nsplit; s0 += 8) {   // eight splits' loads in flight
+        float v[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) v[k] = s0 + k < nsplit ? base[(s0 + k) * step + i] : 0.f;
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+            if (s0 + k < nsplit && sm_m[s0 + k] != -INFINITY) {
+                z = ffma(sm_w[s0 + k], sm_z[s0 + k], z);
+                acc = ffma(sm_w[s0 + k], v[k], acc);
+            }
     }
     float* o = part + ((size_t) t * nq + h) * (hd + 2);
     o[i] = acc;

@@ -111,7 +111,7 @@ __global__ void __launch_bounds__(Q8S_THREADS, 2) k_q8s(const int8_t* __restrict
 // shared memory for the tree.  The integer accumulator starts at the bits of 1.5 * 2^23, so reinterpreting it as f32
 // and subtracting that constant converts it without a convert instruction (|dot| < 2^22).
 constexpr int QM_THREADS = 256, QM_MT = 2, QM_ROWS = 16 * QM_MT, QM_APAD = 16;
-constexpr int QM_MAGIC = 0x4B400000;
+constexpr int QM_MAGIC = 0x4B400000, QM_RING_LD = 80;
 
 __device__ __forceinline__ void mma_s8_16816(int (&d)[4], unsigned a0, unsigned a1, unsigned b0) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%7,%7,%7,%7};"
@@ -136,7 +136,7 @@ struct QSegs {
 template <int NT>   // activation rows in tiles of 8: 1 (T <= 8) or 2
 __global__ void __launch_bounds__(QM_THREADS, 2) k_q8s_mma(const QSegs sg, int cols,
                                                           const uint8_t* __restrict__ yq, const int8_t* __restrict__ pq,
-                                                          const float* __restrict__ pd, int T, unsigned sw_off) {
+                                                          const float* __restrict__ pd, int T, unsigned sw_off, unsigned ring_off) {
     extern __shared__ __align__(16) unsigned char smem[];
     // this block's segment, by selects (indexing the parameter arrays at run time would put them in local memory)
     const int seg = (int) blockIdx.x < sg.blk_end[0] ? 0 : (int) blockIdx.x < sg.blk_end[1] ? 1 : 2;
@@ -184,20 +184,43 @@ __global__ void __launch_bounds__(QM_THREADS, 2) k_q8s_mma(const QSegs sg, int c
         for (int v = 0; v < 4; ++v)
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt) acc[mt][v][nt][0] = acc[mt][v][nt][1] = acc[mt][v][nt][2] = acc[mt][v][nt][3] = 0.f;
-    const int8_t* wr[QM_MT][2];
+    // the warp's weights: its 64 columns of the block's 32 rows per step (2 KB) come through a two-stage ring of its own,
+    // filled with 16-byte cp.async (4 lanes cover a row's 64 contiguous bytes) one step ahead of the MMAs; rows are padded
+    // to 80 bytes so that the fragment reads (row lane / 4, 4 bytes at 4 (lane % 4)) hit 32 different banks
+    unsigned char* ring = smem + ring_off + (size_t) warp * 2 * QM_ROWS * QM_RING_LD;
+    const int8_t* src[4];
+    unsigned dst[4];
 #pragma unroll
-    for (int mt = 0; mt < QM_MT; ++mt)
+    for (int i = 0; i < 4; ++i) {
+        const int j = lane + 32 * i, row = j >> 2, seg = j & 3;
+        src[i] = wq + (size_t) min(row0 + row, rows - 1) * cols + 16 * seg;
+        dst[i] = (unsigned) __cvta_generic_to_shared(ring + row * QM_RING_LD + 16 * seg);
+    }
+    auto issue = [&](int cb, int stage) {
 #pragma unroll
-        for (int h = 0; h < 2; ++h) wr[mt][h] = wq + (size_t) min(row0 + 16 * mt + 8 * h + r8, rows - 1) * cols + 4 * q;
+        for (int i = 0; i < 4; ++i)
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst[i] + stage * QM_ROWS * QM_RING_LD), "l"(src[i] + cb));
+        asm volatile("cp.async.commit_group;");
+    };
+    if (64 * warp < cols) issue(64 * warp, 0);
+    int it = 0;
 #pragma unroll 1
-    for (int cb = 64 * warp; cb < cols; cb += 512) {
+    for (int cb = 64 * warp; cb < cols; cb += 512, ++it) {
+        if (cb + 512 < cols) {
+            issue(cb + 512, (it + 1) & 1);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        }
+        __syncwarp();
+        const unsigned char* rs = ring + (size_t) (it & 1) * QM_ROWS * QM_RING_LD + r8 * QM_RING_LD + 4 * q;
         unsigned a[QM_MT][4][2];
 #pragma unroll
         for (int mt = 0; mt < QM_MT; ++mt)
 #pragma unroll
             for (int v = 0; v < 4; ++v) {
-                a[mt][v][0] = ldg_u32(wr[mt][0] + cb + 16 * v);
-                a[mt][v][1] = ldg_u32(wr[mt][1] + cb + 16 * v);
+                a[mt][v][0] = *reinterpret_cast<const unsigned*>(rs + (16 * mt) * QM_RING_LD + 16 * v);
+                a[mt][v][1] = *reinterpret_cast<const unsigned*>(rs + (16 * mt + 8) * QM_RING_LD + 16 * v);
             }
 #pragma unroll
         for (int bb = 0; bb < 2; ++bb) {   // the two 32-column blocks of the warp's 64 columns
@@ -232,6 +255,7 @@ __global__ void __launch_bounds__(QM_THREADS, 2) k_q8s_mma(const QSegs sg, int c
                     }
             }
         }
+        __syncwarp();   // every lane has read this stage before the next step's copies land in it
     }
     __syncthreads();   // the activations are no longer read: their memory takes the lane sums
     constexpr int TO = 8 * NT, OUTS = QM_ROWS * TO;
@@ -263,46 +287,45 @@ __global__ void __launch_bounds__(QM_THREADS, 2) k_q8s_mma(const QSegs sg, int c
 // src/kernels.cu:184-227 with WPR = 4): lane sums its chunks in ascending order, xor-tree, 0 + p0 + p1 + p2 + p3
 __global__ void __launch_bounds__(128) k_gemv_f32(const float* __restrict__ W, const float* __restrict__ x, float* __restrict__ y,
                                                   int rows, int n, int T) {
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, row = blockIdx.x, nc = n / 512;
-    __shared__ float red[FNX_MAXT][4];
+    // block (row, group of 4 activation rows): the four rows' loads and sums overlap, and the groups run side by side
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, row = blockIdx.x, nc = n / 512, t0 = blockIdx.y * 4;
+    __shared__ float red[4][4];
     const float4* w4 = reinterpret_cast<const float4*>(W + (size_t) row * n) + warp * nc * 32;
     float4 wv[8];   // the warp's quarter of the row (n <= 4096)
 #pragma unroll
     for (int i = 0; i < 8; ++i)
         if (i < nc) wv[i] = __ldg(w4 + i * 32 + lane);
-    for (int t = 0; t < T; t += 2) {
-        const bool two = t + 1 < T;
-        const float4* x4 = reinterpret_cast<const float4*>(x + (size_t) t * n) + warp * nc * 32;
-        const float4* y4 = two ? x4 + n / 4 : x4;
-        float a = 0.f, c = 0.f;
+    float a[4];
+    const float4* x4[4];
 #pragma unroll
-        for (int i = 0; i < 8; ++i)
-            if (i < nc) {
-                const float4 w = wv[i], b = x4[i * 32 + lane], d = y4[i * 32 + lane];
+    for (int k = 0; k < 4; ++k) {
+        a[k] = 0.f;
+        x4[k] = reinterpret_cast<const float4*>(x + (size_t) min(t0 + k, T - 1) * n) + warp * nc * 32;
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+        if (i < nc) {
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const float4 w = wv[i], b = x4[k][i * 32 + lane];
                 float p = fmul(w.x, b.x);
                 p = ffma(w.y, b.y, p);
                 p = ffma(w.z, b.z, p);
                 p = ffma(w.w, b.w, p);
-                a = fadd(a, p);
-                float q = fmul(w.x, d.x);
-                q = ffma(w.y, d.y, q);
-                q = ffma(w.z, d.z, q);
-                q = ffma(w.w, d.w, q);
-                c = fadd(c, q);
+                a[k] = fadd(a[k], p);
             }
-        a = wsum(a);
-        c = wsum(c);
-        if (lane == 0) {
-            red[t][warp] = a;
-            if (two) red[t + 1][warp] = c;
         }
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const float v = wsum(a[k]);
+        if (lane == 0) red[k][warp] = v;
     }
     __syncthreads();
-    if (threadIdx.x < T) {
+    if (threadIdx.x < 4 && t0 + threadIdx.x < T) {
         float v = 0.f;
 #pragma unroll
         for (int k = 0; k < 4; ++k) v = fadd(v, red[threadIdx.x][k]);
-        y[(size_t) threadIdx.x * rows + row] = v;
+        y[(size_t) (t0 + threadIdx.x) * rows + row] = v;
     }
 }
 
@@ -325,9 +348,14 @@ int q8s_mma_launch(const FnxQ8S* w, const int* rows, float* const* out, const in
                    const int8_t* pq, const float* pd, int T, cudaStream_t st, const char* what) {
     const int NT = T <= 8 ? 1 : 2;
     const size_t act = (size_t) 8 * NT * (cols + QM_APAD) + (size_t) 8 * NT * (cols / 32) * 4, redb = (size_t) 32 * QM_ROWS * 8 * NT * 4;
-    const size_t sw_off = ((act > redb ? act : redb) + 15) & ~(size_t) 15;
-    const size_t smm = sw_off + (size_t) QM_ROWS * (cols / 32 + 1) * 4;
+    // activations | weight scales | the warps' rings; the lane sums reuse the whole region after the main loop
+    const size_t sw_off = (act + 15) & ~(size_t) 15;
+    const size_t ring_off = (sw_off + (size_t) QM_ROWS * (cols / 32 + 1) * 4 + 15) & ~(size_t) 15;
+    const size_t used = ring_off + (size_t) (QM_THREADS / 32) * 2 * QM_ROWS * QM_RING_LD;
+    const size_t smm = used > redb ? used : redb;
     if (smm > 227 * 1024) return -1;
+    for (int s = 0; s < nseg; ++s)
+        if ((uintptr_t) w[s].q % 16) return -1;   // the 16-byte copies need aligned rows
     QSegs sg{};
     int g = 0;
     for (int s = 0; s < 3; ++s) {
@@ -339,11 +367,11 @@ int q8s_mma_launch(const FnxQ8S* w, const int* rows, float* const* out, const in
     if (NT == 1) {
         if (smm > 48 * 1024 && cudaFuncSetAttribute(k_q8s_mma<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smm) != cudaSuccess)
             return fail("%s: shared memory opt-in failed", what);
-        k_q8s_mma<1><<<g, QM_THREADS, smm, st>>>(sg, cols, (const uint8_t*) yq, pq, pd, T, (unsigned) sw_off);
+        k_q8s_mma<1><<<g, QM_THREADS, smm, st>>>(sg, cols, (const uint8_t*) yq, pq, pd, T, (unsigned) sw_off, (unsigned) ring_off);
     } else {
         if (smm > 48 * 1024 && cudaFuncSetAttribute(k_q8s_mma<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smm) != cudaSuccess)
             return fail("%s: shared memory opt-in failed", what);
-        k_q8s_mma<2><<<g, QM_THREADS, smm, st>>>(sg, cols, (const uint8_t*) yq, pq, pd, T, (unsigned) sw_off);
+        k_q8s_mma<2><<<g, QM_THREADS, smm, st>>>(sg, cols, (const uint8_t*) yq, pq, pd, T, (unsigned) sw_off, (unsigned) ring_off);
     }
     return launch_ok(what);
 }
@@ -406,7 +434,7 @@ int fnx_q8s_gemv_segs(const FnxQ8S* w, const int* rows, float* const* out, const
 int fnx_gemv_f32(const float* W, const float* x, float* y, int rows, int n, int T, void* st) {
     FNX_REQUIRE(T >= 1 && T <= FNX_MAXT, "gemv_f32: T %d outside 1..%d", T, FNX_MAXT);
     FNX_REQUIRE(n > 0 && n % 512 == 0 && n <= 4096 && rows > 0, "gemv_f32: %d x %d (columns a multiple of 512 up to 4096)", rows, n);
-    k_gemv_f32<<<rows, 128, 0, strm(st)>>>(W, x, y, rows, n, T);
+    k_gemv_f32<<<dim3(rows, (T + 3) / 4), 128, 0, strm(st)>>>(W, x, y, rows, n, T);
     return launch_ok("gemv_f32");
 }
 
