@@ -249,6 +249,11 @@ void* fnx_window_buf(const FnxStackCfg* cfg, void* ws, int which);
  * half).  host_jobs: pinned host memory for nlayers * 2 FnxCopyJob, copied to FNX_BUF_COPY_JOBS */
 int fnx_window_commit(const FnxStackCfg* cfg, const FnxLayer* layers, void* ws, int T, int n, int tag, void* host_jobs, void* st);
 
+/* a second stream for work that does not depend on its neighbours (the shared expert beside the routed experts, the
+ * alpha/beta projection beside qkvz; the reference's st2, src/engine.cu:939-946), with the two events (cudaEvent_t) the
+ * forks and joins record; set per host thread, null to stay on one stream.  Capture-safe. */
+int fnx_window_side_stream(void* st2, void* ev_fork, void* ev_join);
+
 /* per-call timing of windows enqueued outside a graph (the reference's engine keeps per-window timers,
  * src/engine.hpp:182-187): between fnx_trace_begin and fnx_trace_end every C ABI call of fnx_window_stage is bracketed by
  * CUDA events on its stream; fnx_trace_end waits for them and returns each call's name, layer and milliseconds.

@@ -1,10 +1,13 @@
 // Gated DeltaNet core of the verify window in one launch, with per-row state checkpoints for the rollback.
 // Replaces reference src/gdn_core.cuh (k_gdn_core) with the same decomposition of the sums (so each value can be
 // checked bit for bit): 4 blocks per local value head, each owning 32 value columns of the head's 128 x 128 fp32
-// state; thread (column, part) keeps key rows [32 part, 32 part + 32) of its column in registers over the whole
-// window; the state after every row but the last is streamed to snap (the dominant HBM traffic: T state-sized writes
-// per head), the conv history variants to hsnap.  The head's four blocks form a thread-block cluster: they exchange
-// their outputs' square sums through distributed shared memory and each norms, gates and quantises its own columns.
+// state.  A column's 128 key rows are cut as the reference cuts them, into 4 parts of 32 rows with 4 interleaved
+// partial sums each, but every partial sum has a thread of its own here: thread (part, column, j) keeps rows
+// 32 part + 4 i + j (i = 0..7) in registers over the whole window, the four j of a part meet by warp shuffles and the
+// four parts through shared memory, in the reference's order.  The state after every row but the last is streamed to
+// snap (the dominant HBM traffic: T state-sized writes per head), the conv history variants to hsnap.  The head's four
+// blocks form a thread-block cluster: they exchange their outputs' square sums through distributed shared memory and
+// each norms, gates and quantises its own columns.
 #include <cooperative_groups.h>
 
 #include "common.cuh"
@@ -12,7 +15,7 @@
 
 namespace fnxk {
 
-constexpr int HS = FNX_HS, GDN_Q = 4, GDN_QC = HS / GDN_Q, GDN_THREADS = 128;
+constexpr int HS = FNX_HS, GDN_Q = 4, GDN_QC = HS / GDN_Q, GDN_THREADS = 512, GDN_WARPS = GDN_THREADS / 32;
 
 struct GdnArgs {
     const float *qkvz, *ab;
@@ -39,9 +42,9 @@ __global__ void __cluster_dims__(GDN_Q, 1, 1) __launch_bounds__(GDN_THREADS) k_g
     float* hout = g.hist + (size_t) (parity ^ 1u) * 3 * ch;
     __shared__ float xs[2][FNX_MAXT][32][4];   // q, k after conv, silu, L2 norm: element i at [i % 32][i / 32]
     __shared__ float vs[FNX_MAXT][GDN_QC];
-    __shared__ float red[GDN_THREADS / 32][2 * FNX_MAXT];
     __shared__ float gates[FNX_MAXT][2];
-    __shared__ float osm[FNX_MAXT][GDN_QC];   // this block's outputs and, per row, their square sum
+    __shared__ float pk[4][GDN_QC], pa[4][GDN_QC];   // the four parts' sums of a column: k . S and q . S
+    __shared__ float osm[FNX_MAXT][GDN_QC];          // this block's outputs and, per row, their square sum
     __shared__ float sqs[FNX_MAXT];
     if (tid < T) {
         const float* abt = g.ab + (size_t) tid * 2 * nv;
@@ -50,108 +53,100 @@ __global__ void __cluster_dims__(GDN_Q, 1, 1) __launch_bounds__(GDN_THREADS) k_g
         gates[tid][0] = ex_expf(fmul(sp, g.a[lv]));
         gates[tid][1] = fdiv(1.0f, fadd(1.0f, ex_expf(-abt[nv + lv])));
     }
-    // ---- causal conv (width 4) + silu: the key head's q and k channels, this block's 32 v channels
-    for (int e = tid; e < 2 * HS + GDN_QC; e += GDN_THREADS) {
-        const int part = e < HS ? 0 : e < 2 * HS ? 1 : 2, i = part < 2 ? e - part * HS : e - 2 * HS;
-        const int c = part == 0 ? kh * HS + i : part == 1 ? nk * HS + kh * HS + i : 2 * nk * HS + lv * HS + qq * GDN_QC + i;
-        const bool wh = part == 2 || (writes_hist && qq == 0);
-        float h0 = hin[c], h1 = hin[(size_t) ch + c], h2 = hin[(size_t) 2 * ch + c];
+    // ---- the state's loads go out first: they have the whole prologue to land
+    const int part = tid >> 7, cl = (tid >> 2) & 31, j = tid & 3, col = qq * GDN_QC + cl;
+    float* st = g.S + (size_t) lv * HS * HS + (size_t) (part * 32 + j) * HS + col;
+    float s[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) s[i] = __ldcs(st + (size_t) 4 * i * HS);
+    // ---- causal conv (width 4) + silu: the key head's q and k channels, this block's 32 v channels; one item per
+    // (row, channel), its four taps read from the window's rows or, before row 0, from the history
+    constexpr int NCH = 2 * HS + GDN_QC;
+    for (int it = tid; it < T * NCH; it += GDN_THREADS) {
+        const int t = it / NCH, e = it % NCH;
+        const int pt = e < HS ? 0 : e < 2 * HS ? 1 : 2, i = pt < 2 ? e - pt * HS : e - 2 * HS;
+        const int c = pt == 0 ? kh * HS + i : pt == 1 ? nk * HS + kh * HS + i : 2 * nk * HS + lv * HS + qq * GDN_QC + i;
+        const bool wh = pt == 2 || (writes_hist && qq == 0);
         const float4 w = *reinterpret_cast<const float4*>(g.convw + (size_t) c * 4);
-        float xr[FNX_MAXT];   // the window's rows of this channel, all loads in flight before any store
+        float in[4];
 #pragma unroll
-        for (int t = 0; t < FNX_MAXT; ++t) xr[t] = t < T ? g.qkvz[(size_t) t * row_stride + c] : 0.f;
-#pragma unroll
-        for (int t = 0; t < FNX_MAXT; ++t) {
-            if (t >= T) break;
-            const float xt = xr[t];
-            float x = fmul(w.x, h0);
-            x = ffma(w.y, h1, x);
-            x = ffma(w.z, h2, x);
-            x = ffma(w.w, xt, x);
-            const float y = ex_silu(x);
-            if (part < 2) xs[part][t][i % 32][i / 32] = y;
-            else vs[t][i] = y;
-            h0 = h1, h1 = h2, h2 = xt;
-            if (wh && t + 1 < T) {   // the history if only rows 0..t are kept
-                g.hsnap[((size_t) t * 3 + 0) * ch + c] = h0;
-                g.hsnap[((size_t) t * 3 + 1) * ch + c] = h1;
-                g.hsnap[((size_t) t * 3 + 2) * ch + c] = h2;
-            }
+        for (int k = 0; k < 4; ++k) {
+            const int tt = t - 3 + k;
+            in[k] = tt >= 0 ? g.qkvz[(size_t) tt * row_stride + c] : hin[(size_t) (tt + 3) * ch + c];
         }
-        if (wh) hout[c] = h0, hout[(size_t) ch + c] = h1, hout[(size_t) 2 * ch + c] = h2;
+        float x = fmul(w.x, in[0]);
+        x = ffma(w.y, in[1], x);
+        x = ffma(w.z, in[2], x);
+        x = ffma(w.w, in[3], x);
+        const float y = ex_silu(x);
+        if (pt < 2) xs[pt][t][i % 32][i / 32] = y;
+        else vs[t][i] = y;
+        if (wh) {   // the history if only rows 0..t are kept; after the last row, the new history
+            float* h = t + 1 < T ? g.hsnap + (size_t) t * 3 * ch : hout;
+            h[c] = in[1], h[(size_t) ch + c] = in[2], h[(size_t) 2 * ch + c] = in[3];
+        }
     }
     __syncthreads();
-    // ---- L2 norms of q and k per row: thread i holds element i of each; warp trees, the four warps in order
-    {
-        for (int t = 0; t < T; ++t) {
-            const float qv = xs[0][t][tid % 32][tid / 32], kv = xs[1][t][tid % 32][tid / 32];
-            const float sq = wsum(fmul(qv, qv)), sk = wsum(fmul(kv, kv));
-            if (lane == 0) red[warp][t] = sq, red[warp][FNX_MAXT + t] = sk;
-        }
-        __syncthreads();
-        for (int t = 0; t < T; ++t) {
-            float sq = 0.f, sk = 0.f;
+    // ---- L2 norms of q and k, a warp per row: 32-element groups by warp trees, the four groups in order
+    for (int t = warp; t < T; t += GDN_WARPS) {
+        float qv[4], kv[4], sq = 0.f, sk = 0.f;
 #pragma unroll
-            for (int w = 0; w < GDN_THREADS / 32; ++w) sq = fadd(sq, red[w][t]), sk = fadd(sk, red[w][FNX_MAXT + t]);
-            xs[0][t][tid % 32][tid / 32] = fmul(xs[0][t][tid % 32][tid / 32], ex_rsqrt(fadd(sq, 1e-6f)));
-            xs[1][t][tid % 32][tid / 32] = fmul(xs[1][t][tid % 32][tid / 32], ex_rsqrt(fadd(sk, 1e-6f)));
+        for (int gI = 0; gI < 4; ++gI) {
+            qv[gI] = xs[0][t][lane][gI], kv[gI] = xs[1][t][lane][gI];
+            sq = fadd(sq, wsum(fmul(qv[gI], qv[gI])));
+            sk = fadd(sk, wsum(fmul(kv[gI], kv[gI])));
         }
+        const float rq = ex_rsqrt(fadd(sq, 1e-6f)), rk = ex_rsqrt(fadd(sk, 1e-6f));
+#pragma unroll
+        for (int gI = 0; gI < 4; ++gI) xs[0][t][lane][gI] = fmul(qv[gI], rq), xs[1][t][lane][gI] = fmul(kv[gI], rk);
     }
     __syncthreads();
     // ---- the delta rule over the rows
-    const int cl = tid >> 2, part = tid & 3, col = qq * GDN_QC + cl;
-    float* st = g.S + (size_t) lv * HS * HS + (size_t) part * 32 * HS + col;
-    float s[32];
-#pragma unroll
-    for (int r = 0; r < 32; ++r) s[r] = st[(size_t) r * HS];
     const float scale = ex_rsqrt((float) HS);
 #pragma unroll 1
     for (int t = 0; t < T; ++t) {
         const float gv = gates[t][0], bv = gates[t][1];
-        float k0 = 0.f, k1 = 0.f, k2 = 0.f, k3 = 0.f;
+        float kx[8], kj = 0.f;
 #pragma unroll
-        for (int r = 0; r < 32; r += 4) {
-            k0 = ffma(s[r], xs[1][t][r][part], k0);
-            k1 = ffma(s[r + 1], xs[1][t][r + 1][part], k1);
-            k2 = ffma(s[r + 2], xs[1][t][r + 2][part], k2);
-            k3 = ffma(s[r + 3], xs[1][t][r + 3][part], k3);
+        for (int i = 0; i < 8; ++i) {
+            kx[i] = xs[1][t][4 * i + j][part];
+            kj = ffma(s[i], kx[i], kj);
         }
-        float kvd = fadd(fadd(k0, k1), fadd(k2, k3));
-        kvd = fadd(kvd, __shfl_xor_sync(0xffffffffu, kvd, 1));
-        kvd = fadd(kvd, __shfl_xor_sync(0xffffffffu, kvd, 2));
+        kj = fadd(kj, __shfl_xor_sync(0xffffffffu, kj, 1));   // (k0 + k1), (k2 + k3)
+        kj = fadd(kj, __shfl_xor_sync(0xffffffffu, kj, 2));
+        if (j == 0) pk[part][cl] = kj;
+        __syncthreads();
+        const float kvd = fadd(fadd(pk[0][cl], pk[1][cl]), fadd(pk[2][cl], pk[3][cl]));
         const float delta = fmul(ffma(-gv, kvd, vs[t][cl]), bv);
-        float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+        float aj = 0.f;
 #pragma unroll
-        for (int r = 0; r < 32; r += 4) {
-            s[r] = ffma(xs[1][t][r][part], delta, fmul(gv, s[r]));
-            s[r + 1] = ffma(xs[1][t][r + 1][part], delta, fmul(gv, s[r + 1]));
-            s[r + 2] = ffma(xs[1][t][r + 2][part], delta, fmul(gv, s[r + 2]));
-            s[r + 3] = ffma(xs[1][t][r + 3][part], delta, fmul(gv, s[r + 3]));
-            a0 = ffma(s[r], xs[0][t][r][part], a0);
-            a1 = ffma(s[r + 1], xs[0][t][r + 1][part], a1);
-            a2 = ffma(s[r + 2], xs[0][t][r + 2][part], a2);
-            a3 = ffma(s[r + 3], xs[0][t][r + 3][part], a3);
+        for (int i = 0; i < 8; ++i) {
+            s[i] = ffma(kx[i], delta, fmul(gv, s[i]));
+            aj = ffma(s[i], xs[0][t][4 * i + j][part], aj);
         }
-        float at = fadd(fadd(a0, a1), fadd(a2, a3));
-        at = fadd(at, __shfl_xor_sync(0xffffffffu, at, 1));
-        at = fadd(at, __shfl_xor_sync(0xffffffffu, at, 2));
-        const float ov = part == 0 ? fmul(at, scale) : 0.f;
-        if (part == 0) osm[t][cl] = ov;
-        const float ss = wsum(fmul(ov, ov));
-        if (lane == 0) red[warp][t] = ss;
+        aj = fadd(aj, __shfl_xor_sync(0xffffffffu, aj, 1));
+        aj = fadd(aj, __shfl_xor_sync(0xffffffffu, aj, 2));
+        if (j == 0) pa[part][cl] = aj;
         if (t < T - 1) {
             float* sp = g.snap + (size_t) t * nv * HS * HS + (st - g.S);
 #pragma unroll
-            for (int r = 0; r < 32; ++r) __stcs(sp + (size_t) r * HS, s[r]);
+            for (int i = 0; i < 8; ++i) __stcs(sp + (size_t) 4 * i * HS, s[i]);
         }
+        __syncthreads();
+        if (tid < GDN_QC) osm[t][tid] = fmul(fadd(fadd(pa[0][tid], pa[1][tid]), fadd(pa[2][tid], pa[3][tid])), scale);
     }
 #pragma unroll
-    for (int r = 0; r < 32; ++r) st[(size_t) r * HS] = s[r];
+    for (int i = 0; i < 8; ++i) st[(size_t) 4 * i * HS] = s[i];
     __syncthreads();
-    if (tid < T) {
+    if (tid < T) {   // the row's square sum: eight columns by a tree (a warp's butterfly over them), the four eights in order
         float v = 0.f;
 #pragma unroll
-        for (int w = 0; w < GDN_THREADS / 32; ++w) v = fadd(v, red[w][tid]);
+        for (int w = 0; w < 4; ++w) {
+            float c[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) c[k] = fmul(osm[tid][8 * w + k], osm[tid][8 * w + k]);
+            v = fadd(v, fadd(fadd(fadd(c[0], c[4]), fadd(c[2], c[6])), fadd(fadd(c[1], c[5]), fadd(c[3], c[7]))));
+        }
         sqs[tid] = v;
     }
     // ---- gated RMS norm over the head's 128 outputs: the head's four blocks are one thread-block cluster and read each
@@ -162,7 +157,7 @@ __global__ void __cluster_dims__(GDN_Q, 1, 1) __launch_bounds__(GDN_THREADS) k_g
     const float* rsq[GDN_Q];
 #pragma unroll
     for (int r = 0; r < GDN_Q; ++r) rsq[r] = cluster.map_shared_rank(sqs, r);
-    for (int t = warp; t < T; t += GDN_THREADS / 32) {
+    for (int t = warp; t < T; t += GDN_WARPS) {
         const float ms = fdiv(fadd(fadd(fadd(rsq[0][t], rsq[1][t]), rsq[2][t]), rsq[3][t]), (float) HS);
         const int c = qq * GDN_QC + lane;
         const float v = osm[t][lane];

@@ -42,35 +42,33 @@ __global__ void __launch_bounds__(RR_THREADS) k_router_route(const RouterArgs a,
     extern __shared__ __align__(16) float xs_sm[];   // the window's rows of x, read once per block (when they fit)
     __shared__ float rsum[FNX_MAXT][RR_THREADS / 32];
     const float* xs = a.x;
-    if (x_in_smem) {
+    if (x_in_smem) {   // asynchronous 16-byte copies: all of a thread's pieces in flight at once, beside the first weights
         const int n4 = a.T * a.n / 4;
-        for (int i0 = 0; i0 < n4; i0 += RR_THREADS * 8) {   // eight loads in flight per thread before the stores
-            float4 v[8];
-#pragma unroll
-            for (int k = 0; k < 8; ++k) {
-                const int i = i0 + k * RR_THREADS + e;
-                if (i < n4) v[k] = __ldg(reinterpret_cast<const float4*>(a.x) + i);
-            }
-#pragma unroll
-            for (int k = 0; k < 8; ++k) {
-                const int i = i0 + k * RR_THREADS + e;
-                if (i < n4) reinterpret_cast<float4*>(xs_sm)[i] = v[k];
-            }
-        }
+        for (int i = e; i < n4; i += RR_THREADS)
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((unsigned) __cvta_generic_to_shared(xs_sm + 4 * (size_t) i)),
+                         "l"(a.x + 4 * (size_t) i));
+        asm volatile("cp.async.commit_group;");
         xs = xs_sm;
-        __syncthreads();
     }
+    bool staged = !x_in_smem;
     // a block takes rows b, b + grid, ... four at a time, two warps a row (column halves)
     for (int row0 = blockIdx.x * RR_ROWS; row0 < L; row0 += gridDim.x * RR_ROWS) {
         const int row = row0 + rw;
+        // the row half's weights held in registers (up to 16 float4 a lane: n <= 4096), the rows of x four at a time
+        // so that their loads and sums overlap; each logit's summation order is unchanged
+        float4 wv[16];
         if (row < L) {
-            // the row half's weights held in registers (up to 16 float4 a lane: n <= 4096), the rows of x four at a time
-            // so that their loads and sums overlap; each logit's summation order is unchanged
             const float4* w4 = reinterpret_cast<const float4*>(a.W + (size_t) row * a.n) + half * nc * 32;
-            float4 wv[16];
 #pragma unroll
             for (int i = 0; i < 16; ++i)
                 if (i < nc) wv[i] = __ldg(w4 + i * 32 + lane);
+        }
+        if (!staged) {   // block-uniform: the rows of x have landed
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+            __syncthreads();
+            staged = true;
+        }
+        if (row < L) {
             for (int t = 0; t < a.T; t += RR_TG) {
                 float s[RR_TG];
                 const float4* x4[RR_TG];
@@ -99,6 +97,7 @@ __global__ void __launch_bounds__(RR_THREADS) k_router_route(const RouterArgs a,
         }
         __syncthreads();
     }
+    if (!staged) asm volatile("cp.async.wait_group 0;" ::: "memory");   // a block without rows: nothing left in flight at exit
     __shared__ bool last;
     __threadfence();
     __syncthreads();
@@ -110,83 +109,85 @@ __global__ void __launch_bounds__(RR_THREADS) k_router_route(const RouterArgs a,
 }
 
 // top-k per row by logit (ties: the lower index), weights exp(l - l_top) / sum in pick order; jobs: one per distinct
-// expert numbered by its first pick in pair order p = t topk + k, a job's rows in pair order.  The pair-against-pair
-// matches are warp ballots: pair p's expert against 32 pairs at a time.
+// expert numbered by its first pick in pair order p = t topk + k, a job's rows in pair order.
+//
+// A pick is two warp-wide integer reductions: the logits become order-preserving 32-bit keys (-0 folded into +0, which
+// compares equal), the largest key is a redux max and, among the lanes that hold it, the lowest expert index a redux
+// min; a taken expert's key drops to 0, below every number's key.  The picks of one row are distinct experts, so a
+// 16-bit mask of rows per expert gives a pair its place inside the job (rows below it) and the job's row count, and an
+// atomic minimum gives the expert's first pair.
+__device__ __forceinline__ unsigned logit_key(float v) {
+    const unsigned b = __float_as_uint(fadd(v, 0.f));
+    return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+__device__ __forceinline__ float key_logit(unsigned k) { return __uint_as_float((k & 0x80000000u) ? (k ^ 0x80000000u) : ~k); }
+
 __device__ void route_tail(const RouterArgs& a) {
     const int e = threadIdx.x, warp = e >> 5, lane = e & 31, L = a.nexp + 1, P = a.T * a.topk, per = a.nexp / 32;
-    constexpr int NW = RR_THREADS / 32, PW = FNX_MAXT * 16 / 32;   // warps; 32-pair words
+    constexpr int NW = RR_THREADS / 32, PW = FNX_MAXT * 16 / 32, MAXE = 512;   // warps; 32-pair words; experts (16 a lane)
     __shared__ int ex[FNX_MAXT * 16];
-    __shared__ int firstp[FNX_MAXT * 16], slot[FNX_MAXT * 16], count[FNX_MAXT * 16];
+    __shared__ unsigned rowmask[MAXE];
+    __shared__ int firstpair[MAXE];
     __shared__ unsigned firstmask[PW];
     if (e < PW) firstmask[e] = 0u;
+    for (int i = e; i < a.nexp; i += RR_THREADS) rowmask[i] = 0u, firstpair[i] = P;
     for (int t = warp; t < a.T; t += NW) {
-        float v[16];
+        unsigned key[16];
 #pragma unroll
-        for (int i = 0; i < 16; ++i) v[i] = i < per ? __ldcg(a.logits + (size_t) t * L + lane + 32 * i) : -INFINITY;
-        unsigned taken = 0;
-        float top0 = 0.f, z = 0.f, wk = 0.f;
+        for (int i = 0; i < 16; ++i) key[i] = i < per ? logit_key(__ldcg(a.logits + (size_t) t * L + lane + 32 * i)) : 0u;
+        float mine = 0.f, top0 = 0.f;   // lane k keeps pick k's logit
         for (int k = 0; k < a.topk; ++k) {
-            float bv = -INFINITY;
-            int bi = a.nexp;
+            unsigned m = key[0];
 #pragma unroll
-            for (int i = 0; i < 16; ++i)
-                if (i < per && !(taken >> i & 1u) && v[i] > bv) {
-                    bv = v[i];
-                    bi = lane + 32 * i;
-                }
+            for (int i = 1; i < 16; ++i) m = max(m, key[i]);
+            const unsigned M = __reduce_max_sync(0xffffffffu, m);
+            unsigned hit = 0u;
 #pragma unroll
-            for (int o = 16; o; o >>= 1) {
-                const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-                const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-                if (ov > bv || (ov == bv && oi < bi)) {
-                    bv = ov;
-                    bi = oi;
-                }
+            for (int i = 0; i < 16; ++i) hit |= (unsigned) (key[i] == M) << i;
+            const unsigned cand = hit ? (unsigned) (lane + 32 * (__ffs(hit) - 1)) : 0xffffffffu;
+            const int bi = (int) __reduce_min_sync(0xffffffffu, cand);
+            if ((bi & 31) == lane) {
+#pragma unroll
+                for (int i = 0; i < 16; ++i)
+                    if (i == (bi >> 5)) key[i] = 0u;
             }
-            if ((bi & 31) == lane && bi < a.nexp) taken |= 1u << (bi >> 5);
+            const float bv = key_logit(M);
             if (k == 0) top0 = bv;
-            const float ek = ex_expf(fsub(bv, top0));
-            z = fadd(z, ek);
             if (lane == k) {
-                wk = ek;
+                mine = bv;
                 a.topi[t * a.topk + k] = bi;
                 ex[t * a.topk + k] = bi;
             }
         }
-        if (lane < a.topk) a.topw[t * a.topk + lane] = fdiv(wk, z);
-    }
-    __syncthreads();
-    const int words = (P + 31) / 32;
-    for (int p = warp; p < P; p += NW) {
-        const int my = ex[p];
-        int fp = P, below = 0, cnt = 0;
-        for (int k = 0; k < words; ++k) {
-            const int q = 32 * k + lane;
-            const unsigned bal = __ballot_sync(0xffffffffu, q < P && ex[q] == my);
-            if (bal && fp == P) fp = 32 * k + __ffs(bal) - 1;
-            cnt += __popc(bal);
-            if (32 * k + 31 < p) below += __popc(bal);
-            else if (32 * k <= p) below += __popc(bal & ((1u << (p - 32 * k)) - 1u));
-        }
-        if (lane == 0) {
-            firstp[p] = fp, slot[p] = below, count[p] = cnt;
-            if (fp == p) atomicOr(&firstmask[p >> 5], 1u << (p & 31));
-        }
+        const float ek = ex_expf(fsub(mine, top0));
+        float z = 0.f;
+        for (int k = 0; k < a.topk; ++k) z = fadd(z, __shfl_sync(0xffffffffu, ek, k));
+        if (lane < a.topk) a.topw[t * a.topk + lane] = fdiv(ek, z);
     }
     __syncthreads();
     for (int p = e; p < P; p += RR_THREADS) {
-        const int fp = firstp[p];
+        atomicOr(&rowmask[ex[p]], 1u << (p / a.topk));
+        atomicMin(&firstpair[ex[p]], p);
+    }
+    __syncthreads();
+    for (int p = e; p < P; p += RR_THREADS)
+        if (firstpair[ex[p]] == p) atomicOr(&firstmask[p >> 5], 1u << (p & 31));
+    __syncthreads();
+    const int words = (P + 31) / 32;
+    for (int p = e; p < P; p += RR_THREADS) {
+        const int x = ex[p], fp = firstpair[x], t = p / a.topk;
         int j = 0;   // jobs that start before this pair's expert's first pair
         for (int k = 0; k < words; ++k) {
             if (32 * k + 31 < fp) j += __popc(firstmask[k]);
             else if (32 * k <= fp) j += __popc(firstmask[k] & ((1u << (fp - 32 * k)) - 1u));
         }
-        const int s = slot[p];
-        a.gu[j].y[s] = p / a.topk;
+        const unsigned rows = rowmask[x];
+        const int s = __popc(rows & ((1u << t) - 1u));
+        a.gu[j].y[s] = t;
         a.gu[j].out[s] = a.dn[j].y[s] = a.dn[j].out[s] = p;
         if (fp == p) {
-            a.gu[j].w = a.dn[j].w = ex[p];
-            a.gu[j].n = a.dn[j].n = count[p];
+            a.gu[j].w = a.dn[j].w = x;
+            a.gu[j].n = a.dn[j].n = __popc(rows);
         }
     }
     if (e == 0) {

@@ -27,6 +27,24 @@ struct Trace {
 };
 static Trace g_trace;
 
+// a second stream beside the window's own, given by the caller (fnx_window_side_stream): the shared expert runs on it
+// beside the router and the routed experts, the alpha/beta projection beside qkvz (the reference forks its st2 the same
+// way, src/engine.cu:939-946, 1021-1026).  Fork and join are event records and waits: capture-safe.
+struct Side {
+    cudaStream_t st = nullptr;
+    cudaEvent_t fork = nullptr, join = nullptr;
+};
+static thread_local Side g_side;
+static bool side_fork(void* st) {
+    if (!g_side.st || g_trace.on) return false;   // a traced window stays on one stream: its events time single calls
+    return cudaEventRecord(g_side.fork, (cudaStream_t) st) == cudaSuccess && cudaStreamWaitEvent(g_side.st, g_side.fork, 0) == cudaSuccess;
+}
+static int side_join(void* st) {
+    if (cudaEventRecord(g_side.join, g_side.st) != cudaSuccess || cudaStreamWaitEvent((cudaStream_t) st, g_side.join, 0) != cudaSuccess)
+        return fail("window: side stream join: %s", cudaGetErrorString(cudaGetLastError()));
+    return 0;
+}
+
 struct Traced {
     int slot = -1;
     cudaStream_t st;
@@ -221,8 +239,10 @@ int fnx_window_stage(const FnxStackCfg* cfg, const FnxLayer* layers, const FnxHe
     if (sg.part == 0 && L.kind == 0) {   // Gated DeltaNet mixer
         const int rows = (2 * c.nk + 2 * c.nv) * FNX_HS;
         TRK("rms_norm", 1, fnx_rms_norm_rows(x, pending, L.norm1, xn, xq, T, c.n, c.eps, st));
+        const bool forked = side_fork(st);
+        TRK("ab", 1, fnx_gemv_f32(L.ab, xn, (float*) (b + w.ab), 2 * c.nv, c.n, T, forked ? (void*) g_side.st : st));
         TRK("qkvz", 1, fnx_q8s_gemv(L.qkvz, rows, c.n, xq, (float*) (b + w.qkvz), rows, T, st));
-        TRK("ab", 1, fnx_gemv_f32(L.ab, xn, (float*) (b + w.ab), 2 * c.nv, c.n, T, st));
+        if (forked) TRY(side_join(st));
         TRK("gdn_core", 1, fnx_gdn_core((const float*) (b + w.qkvz), (const float*) (b + w.ab), L.hist, L.conv, L.dt, L.a, L.ssm_norm, L.S,
                                         b + w.yq, ctl, (float*) (b + w.gdn_scratch), L.snap, L.hsnap, c.nk, c.nv, L.vmap, T, c.eps, st, nullptr));
         TRK("ssm_out", 1, fnx_q8s_gemv(L.ssm_out, c.n, c.nv * FNX_HS, b + w.yq, bo, c.n, T, st));
@@ -267,12 +287,20 @@ int fnx_window_stage(const FnxStackCfg* cfg, const FnxLayer* layers, const FnxHe
     const int P = T * c.topk;
     float* rl = (float*) (b + w.rlogits);
     TRK("rms_norm", 1, fnx_rms_norm_rows(x, pending, L.norm2, xn, xq, T, c.n, c.eps, st));
+    const bool forked = side_fork(st);   // the shared expert beside the router and the routed experts
+    if (forked)
+        TRY(fnx_shared_expert(L.sh_gate_up, L.sh_down, xq, T, c.n, c.ff, (float*) (b + w.sh_gu), b + w.shq, (float*) (b + w.sh), g_side.st));
     TRK("router_route", 1, fnx_router_route(L.router, xn, rl, T, c.n, c.nexp, c.topk, (int*) (b + w.topi), (float*) (b + w.topw),
                                             (FnxJob*) (b + w.jobs_gu), (FnxJob*) (b + w.jobs_dn), (int*) (b + w.njobs), b + w.rscratch, st));
     TRK("moe_gate_up", 1, fnx_moe_gate_up(&L.gate_up, (const FnxJob*) (b + w.jobs_gu), (const int*) (b + w.njobs), P, xq, (float*) (b + w.gu), st));
     TRK("moe_down", 2, fnx_moe_down(&L.down, (const FnxJob*) (b + w.jobs_dn), (const int*) (b + w.njobs), P, (const float*) (b + w.gu), P,
                                     b + w.hq, (float*) (b + w.part), st));
-    TRK("shared_expert", 3, fnx_shared_expert(L.sh_gate_up, L.sh_down, xq, T, c.n, c.ff, (float*) (b + w.sh_gu), b + w.shq, (float*) (b + w.sh), st));
+    if (forked) {
+        g_trace.kernels += 3;
+        TRY(side_join(st));
+    } else {
+        TRK("shared_expert", 3, fnx_shared_expert(L.sh_gate_up, L.sh_down, xq, T, c.n, c.ff, (float*) (b + w.sh_gu), b + w.shq, (float*) (b + w.sh), st));
+    }
     TRK("moe_combine", 1, fnx_moe_combine((const float*) (b + w.part), (const float*) (b + w.topw), (const float*) (b + w.sh), rl, c.nexp, bo,
                                           T, c.n, c.topk, st));
     return 0;
@@ -299,6 +327,15 @@ int fnx_window_commit(const FnxStackCfg* cfg, const FnxLayer* layers, void* ws, 
     if (cudaMemcpyAsync(dj, hj, (size_t) nj * sizeof(FnxCopyJob), cudaMemcpyHostToDevice, strm(st)) != cudaSuccess)
         return fail("commit: job table upload: %s", cudaGetErrorString(cudaGetLastError()));
     return fnx_copy_many(dj, nj, st);
+}
+
+// the side stream and the two events the forks use (null stream: everything on the window's stream)
+int fnx_window_side_stream(void* st2, void* ev_fork, void* ev_join) {
+    if (st2 && (!ev_fork || !ev_join)) return fail("window_side_stream: a side stream needs its fork and join events");
+    g_side.st = (cudaStream_t) st2;
+    g_side.fork = (cudaEvent_t) ev_fork;
+    g_side.join = (cudaEvent_t) ev_join;
+    return 0;
 }
 
 // ---- per-call trace of windows enqueued outside a graph

@@ -99,6 +99,7 @@ _SIGS = {
     "fnx_math_probe": [_i, _p, _p, _z, _p],
     "fnx_embed_rows": [_p, _p, _p, _i, _i, _p],
     "fnx_window_init": [_p, _p, _p],
+    "fnx_window_side_stream": [_p, _p, _p],
     "fnx_window_stage": [_p, _p, _p, _p, _i, _i, _p],
     "fnx_window_commit": [_p, _p, _p, _i, _i, _i, _p, _p],
     "fnx_top_merge": [_p, _p, _i, _i, _p, _p],

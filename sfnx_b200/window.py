@@ -237,7 +237,7 @@ class WindowRunner:
     """One window of T rows as a CUDA graph on its own stream: embedding rows from the token ids, every stage, and
     between stages the collectives of the process group (NCCL) when there is more than one GPU."""
 
-    def __init__(self, stack, T, group=None, graph=True):
+    def __init__(self, stack, T, group=None, graph=True, overlap=True):
         import torch.distributed as dist
 
         self.stack, self.T, self.group = stack, T, group
@@ -271,6 +271,11 @@ class WindowRunner:
         self.commits = 0
         self.launches = 0
         self.graph = None
+        # a side stream for the window's independent branches (the library forks and joins with these events)
+        self.side = torch.cuda.Stream() if overlap else None
+        self.ev_fork, self.ev_join = torch.cuda.Event(), torch.cuda.Event()
+        self.ev_fork.record(self.stream)   # torch makes an event's handle at its first record
+        self.ev_join.record(self.stream)
         with torch.cuda.stream(self.stream):
             for _ in range(2):   # warm-up: shared-memory opt-ins, NCCL channels
                 self._enqueue()
@@ -284,6 +289,10 @@ class WindowRunner:
 
     def _enqueue(self):
         st, stack, T = torch.cuda.current_stream().cuda_stream, self.stack, self.T
+        if self.side is not None:
+            L.call("fnx_window_side_stream", self.side.cuda_stream, self.ev_fork.cuda_event, self.ev_join.cuda_event)
+        else:
+            L.call("fnx_window_side_stream", None, None, None)
         L.call("fnx_embed_rows", stack.embed.data_ptr(), self.ids.data_ptr(), self.x.data_ptr(), T, stack.shape.n, st)
         for i in range(self.nstages):
             L.call("fnx_window_stage", C.byref(stack.cfg), stack.layers, C.byref(stack.head), stack.ws.data_ptr(), T, i, st)
