@@ -32,7 +32,7 @@ struct GdnArgs {
     float* y32;
 };
 
-__global__ void __cluster_dims__(GDN_Q, 1, 1) __launch_bounds__(GDN_THREADS) k_gdn_core(const GdnArgs g) {
+__global__ void __cluster_dims__(GDN_Q, 1, 1) __launch_bounds__(GDN_THREADS, 2) k_gdn_core(const GdnArgs g) {
     namespace cg = cooperative_groups;
     const int lv = blockIdx.x / GDN_Q, qq = blockIdx.x % GDN_Q, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int vm = g.vmap[lv], kh = vm & 255, writes_hist = vm >> 8, nk = g.nk, nv = g.nv, T = g.T;
@@ -61,29 +61,47 @@ __global__ void __cluster_dims__(GDN_Q, 1, 1) __launch_bounds__(GDN_THREADS) k_g
     for (int i = 0; i < 8; ++i) s[i] = __ldcs(st + (size_t) 4 * i * HS);
     // ---- causal conv (width 4) + silu: the key head's q and k channels, this block's 32 v channels; one item per
     // (row, channel), its four taps read from the window's rows or, before row 0, from the history
-    constexpr int NCH = 2 * HS + GDN_QC;
-    for (int it = tid; it < T * NCH; it += GDN_THREADS) {
-        const int t = it / NCH, e = it % NCH;
-        const int pt = e < HS ? 0 : e < 2 * HS ? 1 : 2, i = pt < 2 ? e - pt * HS : e - 2 * HS;
-        const int c = pt == 0 ? kh * HS + i : pt == 1 ? nk * HS + kh * HS + i : 2 * nk * HS + lv * HS + qq * GDN_QC + i;
-        const bool wh = pt == 2 || (writes_hist && qq == 0);
-        const float4 w = *reinterpret_cast<const float4*>(g.convw + (size_t) c * 4);
-        float in[4];
+    constexpr int NCH = 2 * HS + GDN_QC, CI = 3;   // items in flight per thread
+#pragma unroll 1
+    for (int it0 = tid; it0 < T * NCH; it0 += CI * GDN_THREADS) {
+        float in[CI][4];   // a batch's loads go out before its first sum
+        float4 cw[CI];
+        auto channel = [&](int e, int& pt, int& i) {
+            pt = e < HS ? 0 : e < 2 * HS ? 1 : 2, i = pt < 2 ? e - pt * HS : e - 2 * HS;
+            return pt == 0 ? kh * HS + i : pt == 1 ? nk * HS + kh * HS + i : 2 * nk * HS + lv * HS + qq * GDN_QC + i;
+        };
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
-            const int tt = t - 3 + k;
-            in[k] = tt >= 0 ? g.qkvz[(size_t) tt * row_stride + c] : hin[(size_t) (tt + 3) * ch + c];
+        for (int m = 0; m < CI; ++m) {
+            const int it = it0 + m * GDN_THREADS;
+            if (it < T * NCH) {
+                int pt, i;
+                const int t = it / NCH, c = channel(it % NCH, pt, i);
+                cw[m] = *reinterpret_cast<const float4*>(g.convw + (size_t) c * 4);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const int tt = t - 3 + k;
+                    in[m][k] = tt >= 0 ? g.qkvz[(size_t) tt * row_stride + c] : hin[(size_t) (tt + 3) * ch + c];
+                }
+            }
         }
-        float x = fmul(w.x, in[0]);
-        x = ffma(w.y, in[1], x);
-        x = ffma(w.z, in[2], x);
-        x = ffma(w.w, in[3], x);
-        const float y = ex_silu(x);
-        if (pt < 2) xs[pt][t][i % 32][i / 32] = y;
-        else vs[t][i] = y;
-        if (wh) {   // the history if only rows 0..t are kept; after the last row, the new history
-            float* h = t + 1 < T ? g.hsnap + (size_t) t * 3 * ch : hout;
-            h[c] = in[1], h[(size_t) ch + c] = in[2], h[(size_t) 2 * ch + c] = in[3];
+#pragma unroll
+        for (int m = 0; m < CI; ++m) {
+            const int it = it0 + m * GDN_THREADS;
+            if (it < T * NCH) {
+                int pt, i;
+                const int t = it / NCH, c = channel(it % NCH, pt, i);
+                float x = fmul(cw[m].x, in[m][0]);
+                x = ffma(cw[m].y, in[m][1], x);
+                x = ffma(cw[m].z, in[m][2], x);
+                x = ffma(cw[m].w, in[m][3], x);
+                const float y = ex_silu(x);
+                if (pt < 2) xs[pt][t][i % 32][i / 32] = y;
+                else vs[t][i] = y;
+                if (pt == 2 || (writes_hist && qq == 0)) {   // the history if only rows 0..t are kept; after the last row, the new one
+                    float* h = t + 1 < T ? g.hsnap + (size_t) t * 3 * ch : hout;
+                    h[c] = in[m][1], h[(size_t) ch + c] = in[m][2], h[(size_t) 2 * ch + c] = in[m][3];
+                }
+            }
         }
     }
     __syncthreads();

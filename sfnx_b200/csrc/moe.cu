@@ -255,9 +255,12 @@ __device__ __forceinline__ void q4k_scale_min(const uint4& h, int j, float& sc, 
         m = (float) ((q4k_sbyte(h, j + 4) >> 4) | ((q4k_sbyte(h, j) >> 6) << 4));
     }
 }
-__device__ __forceinline__ uint4 ldg_stream(const void* p) {   // read-once weights: do not keep them in L1
+// Read-once weights.  A lane's 16-byte pieces are halves of 32-byte sectors whose other halves the next load of the same
+// lanes takes (a Q4_K superblock is 4.5 sectors long), so the lines do go through L1, first to leave: with L1 bypassed
+// every sector crossed the L2 -> SM path twice.
+__device__ __forceinline__ uint4 ldg_stream(const void* p) {
     uint4 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    asm volatile("ld.global.nc.L1::evict_first.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
     return v;
 }
 
@@ -298,9 +301,12 @@ __global__ void __launch_bounds__(GU_THREADS, 2) k_moe_gu_q4k(const uint8_t* __r
             int sum = 0;
 #pragma unroll
             for (int k = 0; k < 8; ++k) sum = __dp4a(0x01010101, (int) w[1 + k], sum);
-            uint4* dst = reinterpret_cast<uint4*>(aq + (size_t) j * n + b * 32);
-            dst[0] = make_uint4(w[1], w[2], w[3], w[4]);
-            dst[1] = make_uint4(w[5], w[6], w[7], w[8]);
+            // 16-byte pieces swizzled inside each 64 bytes by the 64-byte group's index / 2: the eight lanes of a row
+            // group read pieces 64 bytes apart, which would otherwise share two bank groups four ways
+            uint4* dst = reinterpret_cast<uint4*>(aq + (size_t) j * n);
+            const int u0 = 2 * b, sw = (u0 >> 3) & 3;
+            dst[(u0 & ~3) | ((u0 & 3) ^ sw)] = make_uint4(w[1], w[2], w[3], w[4]);
+            dst[(u0 & ~3) | (((u0 & 3) + 1) ^ sw)] = make_uint4(w[5], w[6], w[7], w[8]);
             float* gq = reinterpret_cast<float*>(ag + (size_t) j * (nb / 2) + (b >> 1));
             gq[b & 1] = h2f((uint16_t) (w[0] & 0xffff));
             gq[2 + (b & 1)] = (float) sum;
@@ -333,7 +339,8 @@ __global__ void __launch_bounds__(GU_THREADS, 2) k_moe_gu_q4k(const uint8_t* __r
             for (int r = 0; r < GU_TC; ++r) {
                 if (r >= cn) break;
                 const uint4* ap = reinterpret_cast<const uint4*>(aq + (size_t) r * n + yb * 32);
-                const uint4 a0 = ap[0], a1 = ap[1], a2 = ap[2], a3 = ap[3];
+                const int sw = (g >> 1) & 3;   // the staging's swizzle
+                const uint4 a0 = ap[sw], a1 = ap[1 ^ sw], a2 = ap[2 ^ sw], a3 = ap[3 ^ sw];
                 const float4 sg = ag[(size_t) r * (nb / 2) + (yb >> 1)];   // d8l, d8h, (float) sl, (float) sh
                 const unsigned al[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
                 const unsigned ah[8] = {a2.x, a2.y, a2.z, a2.w, a3.x, a3.y, a3.z, a3.w};
