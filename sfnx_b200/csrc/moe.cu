@@ -242,18 +242,24 @@ __device__ __forceinline__ void job_act_stage(const JobAct& a, const uint8_t* __
 // lanes combined by xor 4, 2, 1.
 constexpr int GU_THREADS = 256;
 
-__device__ __forceinline__ unsigned q4k_sbyte(const uint4& h, int k) {
-    const unsigned word = k < 4 ? h.y : k < 8 ? h.z : h.w;
-    return (word >> (8 * (k & 3))) & 0xFFu;
+// The 6-bit scales and mins of sub-blocks 2 jg and 2 jg + 1 out of the 12 packed bytes (h.y, h.z, h.w), both at once
+// as byte pairs: sub-blocks 0..3 have their scale in bytes 0..3 and their min in bytes 4..7 (low 6 bits); sub-blocks
+// 4..7 have the low 4 bits in bytes 8..11 (scale: low nibble, min: high nibble) and the high 2 bits in the top of
+// bytes 0..3 (scale) and 4..7 (min).
+__device__ __forceinline__ void q4k_scale_min_pair(const uint4& h, int jg, float& sc0, float& m0, float& sc1, float& m1) {
+    const int sh = 16 * (jg & 1);
+    const unsigned y = h.y >> sh, z = h.z >> sh, w = h.w >> sh;
+    const unsigned sc_lo = y & 0x3F3Fu, m_lo = z & 0x3F3Fu;
+    const unsigned sc_hi = (w & 0x0F0Fu) | ((y >> 2) & 0x3030u), m_hi = ((w >> 4) & 0x0F0Fu) | ((z >> 2) & 0x3030u);
+    const unsigned sc = jg & 2 ? sc_hi : sc_lo, m = jg & 2 ? m_hi : m_lo;
+    sc0 = (float) (sc & 0xFFu), sc1 = (float) (sc >> 8);
+    m0 = (float) (m & 0xFFu), m1 = (float) (m >> 8);
 }
-__device__ __forceinline__ void q4k_scale_min(const uint4& h, int j, float& sc, float& m) {
-    if (j < 4) {
-        sc = (float) (q4k_sbyte(h, j) & 63);
-        m = (float) (q4k_sbyte(h, j + 4) & 63);
-    } else {
-        sc = (float) ((q4k_sbyte(h, j + 4) & 0xF) | ((q4k_sbyte(h, j - 4) >> 6) << 4));
-        m = (float) ((q4k_sbyte(h, j + 4) >> 4) | ((q4k_sbyte(h, j) >> 6) << 4));
-    }
+// bytes of a taken as unsigned, of b as signed
+__device__ __forceinline__ int dp4a_us(unsigned a, unsigned b, int c) {
+    int d;
+    asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
 }
 // Read-once weights.  A lane's 16-byte pieces are halves of 32-byte sectors whose other halves the next load of the same
 // lanes takes (a Q4_K superblock is 4.5 sectors long), so the lines do go through L1, first to leave: with L1 bypassed
@@ -264,10 +270,18 @@ __device__ __forceinline__ uint4 ldg_stream(const void* p) {
     return v;
 }
 
-// What bounds this kernel is the shared-memory data pipe (the activations every lane reads), not HBM: so a lane keeps the
-// activations of its group in registers and applies them to GU_R rows, and the rows of a job are taken GU_TC at a time
-// (three jobs in four have one row, one in a hundred more than three).
-constexpr int GU_TC = 2, GU_R = 4, GU_MAGIC = 0x4B400000, GU_RPB = GU_THREADS / 8 * GU_R;
+// Expert gate|up rows against the rows of x routed to the expert.  Each weight byte is used once and the work per byte
+// is small, so what bounds the kernel is how many loads a multiprocessor keeps in flight: a lane group (8 lanes) owns
+// GU_R consecutive rows and takes them two at a time, the 16-byte pieces of the step after the one being summed
+// already on their way in a second set of registers (through a cp.async ring in shared memory instead, the ring's
+// writes and reads saturated the shared-memory pipe).  A lane reads the activations of its column group from shared
+// memory once per step and applies them to both rows; the rows of a job are taken GU_TC at a time (three jobs in four
+// have one row, one in a hundred more than three) and the pipeline runs on across those passes.
+constexpr int GU_TC = 2, GU_R = 4, GU_RS = 2, GU_MAGIC = 0x4B400000, GU_RPB = GU_THREADS / 8 * GU_R;
+
+struct GuStep {   // one step's weights of a lane: two rows' header and 32 bytes of nibbles
+    uint4 hdr[GU_RS], q0[GU_RS], q1[GU_RS];
+};
 
 template <int GPL>
 __global__ void __launch_bounds__(GU_THREADS, 2) k_moe_gu_q4k(const uint8_t* __restrict__ A, size_t sa, int nrows, int n,
@@ -279,18 +293,85 @@ __global__ void __launch_bounds__(GU_THREADS, 2) k_moe_gu_q4k(const uint8_t* __r
     __shared__ FnxJob jb;
     if (threadIdx.x < sizeof(FnxJob) / 4) reinterpret_cast<int*>(&jb)[threadIdx.x] = reinterpret_cast<const int*>(jobs + ji)[threadIdx.x];
     __syncthreads();
-    const int lane8 = threadIdx.x & 7, nb = n / 32;
+    const int lane8 = threadIdx.x & 7, nb = n / 32, jg = lane8 & 3;
     int8_t* aq = reinterpret_cast<int8_t*>(smem);                              // [GU_TC][n]
     float4* ag = reinterpret_cast<float4*>(smem + (size_t) GU_TC * n);         // [GU_TC][n / 64]: d8 low, d8 high, sum low, sum high
     const size_t row_b = (size_t) n / 256 * 144;
     const int row0 = blockIdx.x * GU_RPB + (threadIdx.x >> 3) * GU_R;          // this lane group's GU_R consecutive rows
     const uint8_t* wrow = A + (size_t) jb.w * sa + (size_t) min(row0, nrows - 1) * row_b;
-    size_t roff[GU_R];
+    unsigned roff[GU_R];
 #pragma unroll
-    for (int rr = 0; rr < GU_R; ++rr) roff[rr] = (size_t) (min(row0 + rr, nrows - 1) - min(row0, nrows - 1)) * row_b;
+    for (int rr = 0; rr < GU_R; ++rr) roff[rr] = (unsigned) ((min(row0 + rr, nrows - 1) - min(row0, nrows - 1)) * row_b);
+    // step s of a pass: rows 2 (s / GPL), +1 of the lane group, column group lane8 + 8 (s % GPL)
+    constexpr int NS = GU_R / GU_RS * GPL;
+    auto load = [&](GuStep& w, int s) {
+        const int h = s / GPL, g = lane8 + (s % GPL) * 8;
+#pragma unroll
+        for (int rr = 0; rr < GU_RS; ++rr) {
+            const uint8_t* blk = wrow + (h ? roff[GU_RS + rr] : roff[rr]) + (size_t) (g >> 2) * 144;
+            w.hdr[rr] = ldg_stream(blk);
+            w.q0[rr] = ldg_stream(blk + 16 + 32 * jg);
+            w.q1[rr] = ldg_stream(blk + 32 + 32 * jg);
+        }
+    };
+    float tmp[GU_RS][GU_TC];
+    int cn = 0, c0 = 0;
+    auto sums = [&](const GuStep& w, int s) {
+        const int h = s / GPL, i = s % GPL, g = lane8 + i * 8, yb = (g >> 2) * 8 + jg * 2, sw = (g >> 1) & 3;   // sw: the staging's swizzle
+        if (i == 0) {
+#pragma unroll
+            for (int rr = 0; rr < GU_RS; ++rr)
+#pragma unroll
+                for (int r = 0; r < GU_TC; ++r) tmp[rr][r] = 0.f;
+        }
+        float d[GU_RS], dmin[GU_RS], sc0[GU_RS], m0[GU_RS], sc1[GU_RS], m1[GU_RS];
+#pragma unroll
+        for (int rr = 0; rr < GU_RS; ++rr) {
+            d[rr] = h2f((uint16_t) (w.hdr[rr].x & 0xffff)), dmin[rr] = h2f((uint16_t) (w.hdr[rr].x >> 16));
+            q4k_scale_min_pair(w.hdr[rr], jg, sc0[rr], m0[rr], sc1[rr], m1[rr]);
+        }
+#pragma unroll
+        for (int r = 0; r < GU_TC; ++r) {
+            if (r >= cn) break;
+            const uint4* ap = reinterpret_cast<const uint4*>(aq + (size_t) r * n + yb * 32);
+            const uint4 a0 = ap[sw], a1 = ap[1 ^ sw], a2 = ap[2 ^ sw], a3 = ap[3 ^ sw];
+            const float4 sg = ag[(size_t) r * (nb / 2) + (yb >> 1)];   // d8l, d8h, (float) sl, (float) sh
+            const unsigned al[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+            const unsigned ah[8] = {a2.x, a2.y, a2.z, a2.w, a3.x, a3.y, a3.z, a3.w};
+#pragma unroll
+            for (int rr = 0; rr < GU_RS; ++rr) {
+                const unsigned qw[8] = {w.q0[rr].x, w.q0[rr].y, w.q0[rr].z, w.q0[rr].w, w.q1[rr].x, w.q1[rr].y, w.q1[rr].z, w.q1[rr].w};
+                int dl = GU_MAGIC, dh = GU_MAGIC;   // started at the bits of 1.5 * 2^23: as floats minus that, (float) dot
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {   // the high nibbles stay where they are: their dot is 16 x the sub-block's, exactly
+                    dl = dp4a_us(qw[k] & 0x0F0F0F0Fu, al[k], dl);
+                    dh = dp4a_us(qw[k] & 0xF0F0F0F0u, ah[k], dh);
+                }
+                const float fl = fsub(__int_as_float(dl), 12582912.0f);
+                const float fh = fmul(fsub(__int_as_float(dh), 12582912.0f), 0.0625f);
+                const float pos = fmul(d[rr], fadd(fmul(sg.x, fmul(sc0[rr], fl)), fmul(sg.y, fmul(sc1[rr], fh))));
+                const float neg = fmul(dmin[rr], fadd(fmul(sg.x, fmul(m0[rr], sg.z)), fmul(sg.y, fmul(m1[rr], sg.w))));
+                tmp[rr][r] = fadd(tmp[rr][r], fsub(pos, neg));
+            }
+        }
+        if (i == GPL - 1) {
+#pragma unroll
+            for (int rr = 0; rr < GU_RS; ++rr)
+#pragma unroll
+                for (int r = 0; r < GU_TC; ++r) {
+                    if (r >= cn) break;
+                    const float v = sum8(tmp[rr][r]);
+                    const int row = row0 + h * GU_RS + rr;
+                    if (lane8 == 0 && row < nrows) out[(size_t) jb.out[c0 + r] * nrows + row] = v;
+                }
+        }
+    };
+    GuStep w0, w1;
+    load(w0, 0);   // the weights do not wait for the activations
 #pragma unroll 1
-    for (int c0 = 0; c0 < jb.n; c0 += GU_TC) {
-        const int cn = min(GU_TC, jb.n - c0);
+    for (c0 = 0; c0 < jb.n; c0 += GU_TC) {
+        cn = min(GU_TC, jb.n - c0);
+        const bool more = c0 + GU_TC < jb.n;
         if (c0) __syncthreads();
         for (int it = threadIdx.x; it < cn * nb; it += GU_THREADS) {
             const int j = it / nb, b = it % nb;
@@ -312,62 +393,13 @@ __global__ void __launch_bounds__(GU_THREADS, 2) k_moe_gu_q4k(const uint8_t* __r
             gq[2 + (b & 1)] = (float) sum;
         }
         __syncthreads();
-        float tmp[GU_R][GU_TC];
-#pragma unroll
-        for (int rr = 0; rr < GU_R; ++rr)
-#pragma unroll
-            for (int r = 0; r < GU_TC; ++r) tmp[rr][r] = 0.f;
 #pragma unroll 1
-        for (int i = 0; i < GPL; ++i) {
-            const int g = lane8 + i * 8, jg = g & 3, yb = (g >> 2) * 8 + jg * 2;
-            uint4 hdr[GU_R], q0[GU_R], q1[GU_R];
-#pragma unroll
-            for (int rr = 0; rr < GU_R; ++rr) {
-                const uint8_t* blk = wrow + roff[rr] + (size_t) (g >> 2) * 144;
-                hdr[rr] = ldg_stream(blk);
-                q0[rr] = ldg_stream(blk + 16 + 32 * jg);
-                q1[rr] = ldg_stream(blk + 32 + 32 * jg);
-            }
-            float d[GU_R], dmin[GU_R], sc0[GU_R], m0[GU_R], sc1[GU_R], m1[GU_R];
-#pragma unroll
-            for (int rr = 0; rr < GU_R; ++rr) {
-                d[rr] = h2f((uint16_t) (hdr[rr].x & 0xffff)), dmin[rr] = h2f((uint16_t) (hdr[rr].x >> 16));
-                q4k_scale_min(hdr[rr], 2 * jg, sc0[rr], m0[rr]);
-                q4k_scale_min(hdr[rr], 2 * jg + 1, sc1[rr], m1[rr]);
-            }
-#pragma unroll
-            for (int r = 0; r < GU_TC; ++r) {
-                if (r >= cn) break;
-                const uint4* ap = reinterpret_cast<const uint4*>(aq + (size_t) r * n + yb * 32);
-                const int sw = (g >> 1) & 3;   // the staging's swizzle
-                const uint4 a0 = ap[sw], a1 = ap[1 ^ sw], a2 = ap[2 ^ sw], a3 = ap[3 ^ sw];
-                const float4 sg = ag[(size_t) r * (nb / 2) + (yb >> 1)];   // d8l, d8h, (float) sl, (float) sh
-                const unsigned al[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
-                const unsigned ah[8] = {a2.x, a2.y, a2.z, a2.w, a3.x, a3.y, a3.z, a3.w};
-#pragma unroll
-                for (int rr = 0; rr < GU_R; ++rr) {
-                    const unsigned qw[8] = {q0[rr].x, q0[rr].y, q0[rr].z, q0[rr].w, q1[rr].x, q1[rr].y, q1[rr].z, q1[rr].w};
-                    int dl = GU_MAGIC, dh = GU_MAGIC;   // started at the bits of 1.5 * 2^23: as floats minus that, (float) dot
-#pragma unroll
-                    for (int w = 0; w < 8; ++w) {
-                        dl = __dp4a((int) (qw[w] & 0x0F0F0F0Fu), (int) al[w], dl);
-                        dh = __dp4a((int) ((qw[w] >> 4) & 0x0F0F0F0Fu), (int) ah[w], dh);
-                    }
-                    const float fl = fsub(__int_as_float(dl), 12582912.0f), fh = fsub(__int_as_float(dh), 12582912.0f);
-                    const float pos = fmul(d[rr], fadd(fmul(sg.x, fmul(sc0[rr], fl)), fmul(sg.y, fmul(sc1[rr], fh))));
-                    const float neg = fmul(dmin[rr], fadd(fmul(sg.x, fmul(m0[rr], sg.z)), fmul(sg.y, fmul(m1[rr], sg.w))));
-                    tmp[rr][r] = fadd(tmp[rr][r], fsub(pos, neg));
-                }
-            }
+        for (int s = 0; s < NS; s += 2) {   // NS is even
+            load(w1, s + 1);
+            sums(w0, s);
+            if (s + 2 < NS || more) load(w0, s + 2 < NS ? s + 2 : 0);
+            sums(w1, s + 1);
         }
-#pragma unroll
-        for (int rr = 0; rr < GU_R; ++rr)
-#pragma unroll
-            for (int r = 0; r < GU_TC; ++r) {
-                if (r >= cn) break;
-                const float v = sum8(tmp[rr][r]);
-                if (lane8 == 0 && row0 + rr < nrows) out[(size_t) jb.out[c0 + r] * nrows + row0 + rr] = v;
-            }
     }
 }
 
@@ -552,8 +584,8 @@ int fnx_moe_gate_up(const FnxExperts* A, const FnxJob* jobs, const int* njobs, i
     const int n = A->ncols, nrows = A->nrows, maxrows = FNX_MAXT;
     if (A->type == FNX_Q4_K) {
         FNX_REQUIRE(n % 512 == 0 && n / 512 >= 1 && n / 512 <= 8, "moe gate|up q4_K: %d columns (multiples of 512 up to 4096)", n);
-        // blocks of 128 rows with direct 16-byte loads (measured faster than staging the panels through
-        // shared memory with bulk copies: each weight byte is used once and the consumer is instruction-bound)
+        // blocks of 128 rows with direct 16-byte loads one step ahead (measured faster than staging the weights through
+        // shared memory, by cp.async rings or bulk copies: there every operand crosses the shared-memory pipe)
         static const bool staged = getenv("FNX_GU_TMA") != nullptr;   // a tuning knob: the TMA-staged persistent kernel instead
         if (staged && gu_q4k_tma_smem(n) + 1024 <= 227 * 1024 && ((uintptr_t) A->a % 16) == 0 && A->stride % 16 == 0)
             return gu_q4k_tma_launch((const uint8_t*) A->a, A->stride, nrows, n, jobs, njobs, (const uint8_t*) xq, gu, strm(st));
