@@ -288,10 +288,11 @@ __global__ void __launch_bounds__(GU_THREADS, 2) k_moe_gu_q4k(const uint8_t* __r
                                                           const FnxJob* __restrict__ jobs, const int* __restrict__ njobs,
                                                           const uint8_t* __restrict__ xq, float* __restrict__ out) {
     const int ji = blockIdx.y;
-    if (ji >= *njobs) return;
     extern __shared__ __align__(16) unsigned char smem[];
     __shared__ FnxJob jb;
+    const int nj = *njobs;   // read beside the job, not before it (the job array has a slot for every block row)
     if (threadIdx.x < sizeof(FnxJob) / 4) reinterpret_cast<int*>(&jb)[threadIdx.x] = reinterpret_cast<const int*>(jobs + ji)[threadIdx.x];
+    if (ji >= nj) return;
     __syncthreads();
     const int lane8 = threadIdx.x & 7, nb = n / 32, jg = lane8 & 3;
     int8_t* aq = reinterpret_cast<int8_t*>(smem);                              // [GU_TC][n]
@@ -426,108 +427,133 @@ __global__ void __launch_bounds__(256) k_swiglu_q8(const float* __restrict__ gu,
 // added in ascending order (reference src/moe.cuh:330-344).
 constexpr int DN_THREADS = 256;
 
-constexpr int DN_TC = 2, DN_UPT = 3;   // activation rows a pass; weight rows a thread (its loads all in flight)
+constexpr int DN_TC = 2, DN_UPT = 3, DN_K = 4;   // activation rows a pass; weight rows a thread; row groups a block
 
-// Thread (u, r) takes 32-column unit u of rows r, r + RP, r + 2 RP of the block (RP = 256 / units-per-row rows a pass), so
-// the activations of its unit are read from shared memory once per activation row and used for three weight rows: the
-// kernel is bound by the shared-memory data pipe otherwise.  Lanes run over consecutive units of consecutive rows, so
-// every plane is read in contiguous 16-, 8- and 2-byte pieces.
-__global__ void __launch_bounds__(DN_THREADS, 4) k_moe_down_q6p(const uint4* __restrict__ QL, const uint2* __restrict__ QH,
+// Thread (u, r) takes 32-column unit u of rows r, r + RP, r + 2 RP of a row group (RP = 256 / units-per-row rows a pass),
+// so the activations of its unit are read from shared memory once per activation row and used for three weight rows:
+// the kernel is bound by the shared-memory data pipe otherwise.  Lanes run over consecutive units of consecutive rows,
+// so every plane is read in contiguous 16-, 8- and 2-byte pieces.  A block stages the job's activation rows once and
+// walks DN_K row groups, the next group's weights on their way while this group's are summed: a block's life is a
+// chain of dependent global reads (job, weights, activations) and short sums, so the reads are issued as early as
+// their addresses are known.
+struct DnRaw {
+    uint4 ql[DN_UPT];
+    uint2 qh[DN_UPT];
+    unsigned scw[DN_UPT], dh[DN_UPT];
+};
+
+__global__ void __launch_bounds__(DN_THREADS, 3) k_moe_down_q6p(const uint4* __restrict__ QL, const uint2* __restrict__ QH,
                                                                const uint16_t* __restrict__ SC, const uint16_t* __restrict__ D,
                                                                size_t expert_units, int nrows, int ffs, const FnxJob* __restrict__ jobs,
                                                                const int* __restrict__ njobs, const int8_t* __restrict__ hq,
                                                                const float* __restrict__ hd, float* __restrict__ out) {
     const int ji = blockIdx.y;
-    if (ji >= *njobs) return;
     extern __shared__ __align__(16) unsigned char smem[];
     __shared__ FnxJob jb;
+    const int nj = *njobs;   // read beside the job, not before it (the job array has a slot for every block row)
     if (threadIdx.x < sizeof(FnxJob) / 4) reinterpret_cast<int*>(&jb)[threadIdx.x] = reinterpret_cast<const int*>(jobs + ji)[threadIdx.x];
+    if (ji >= nj) return;
     __syncthreads();
     const int nu = ffs / 32, RP = DN_THREADS / nu, rpb = RP * DN_UPT, pu = nu + 1;   // pu: padded units a row in `part`
-    uint4* sq = reinterpret_cast<uint4*>(smem);                                   // [DN_TC][2 halves][nu] 16 bytes each
-    float* sd = reinterpret_cast<float*>(sq + (size_t) DN_TC * 2 * nu);           // [DN_TC][nu]
-    int2* ss = reinterpret_cast<int2*>(sd + (size_t) DN_TC * nu);                 // [DN_TC][nu]: 32 x the sums of each half
-    float* part = reinterpret_cast<float*>(ss + (size_t) DN_TC * nu);             // [DN_TC][rpb][pu]
-    const int row0 = blockIdx.x * rpb, u = threadIdx.x % nu, r = threadIdx.x / nu;
+    const int jn = min(jb.n, FNX_MAXT);
+    uint4* sq = reinterpret_cast<uint4*>(smem);                                   // [jn][2 halves][nu] 16 bytes each
+    float* sd = reinterpret_cast<float*>(sq + (size_t) FNX_MAXT * 2 * nu);        // [jn][nu]
+    int2* ss = reinterpret_cast<int2*>(sd + (size_t) FNX_MAXT * nu);              // [jn][nu]: 32 x the sums of each half
+    float* part = reinterpret_cast<float*>(ss + (size_t) FNX_MAXT * nu);          // [2][DN_TC][rpb][pu]
+    const int rowB = blockIdx.x * rpb * DN_K, u = threadIdx.x % nu, r = threadIdx.x / nu;
     const bool active = r < RP;
-    const size_t ebase = (size_t) jb.w * expert_units + (size_t) row0 * nu;
-    // this thread's units: the weights are read once and kept for every pass over the job's rows
-    unsigned v[DN_UPT][8];
-    float d[DN_UPT];
-    int sc0[DN_UPT], sc1[DN_UPT];
-    {
-        uint4 ql[DN_UPT];
-        uint2 qh[DN_UPT];
-        unsigned scw[DN_UPT];
+    auto load = [&](DnRaw& w, int row0) {
 #pragma unroll
         for (int k = 0; k < DN_UPT; ++k) {
             const int row = min(row0 + k * RP + min(r, RP - 1), nrows - 1);
             const size_t g = (size_t) jb.w * expert_units + (size_t) row * nu + u;
-            ql[k] = ldg_stream(QL + g);
-            qh[k] = __ldg(QH + g);
-            scw[k] = SC[g];
-            d[k] = h2f(D[g]);
+            w.ql[k] = ldg_stream(QL + g);
+            w.qh[k] = __ldg(QH + g);
+            w.scw[k] = SC[g];
+            w.dh[k] = D[g];
         }
+    };
+    DnRaw raw;
+    load(raw, rowB);
+    for (int it = threadIdx.x; it < jn * nu; it += DN_THREADS) {
+        const int j = it / nu, uu = it % nu;
+        sd[it] = hd[(size_t) jb.y[j] * nu + uu];
+        const uint4* hp = reinterpret_cast<const uint4*>(hq + (size_t) jb.y[j] * ffs + uu * 32);
+        const uint4 h0 = hp[0], h1 = hp[1];
+        sq[(size_t) (j * 2) * nu + uu] = h0;        // the two halves in planes of their own: a warp's 16-byte reads
+        sq[(size_t) (j * 2 + 1) * nu + uu] = h1;    // are contiguous
+        int s0 = __dp4a(0x01010101, (int) h0.x, 0), s1 = __dp4a(0x01010101, (int) h1.x, 0);
+        s0 = __dp4a(0x01010101, (int) h0.y, s0), s1 = __dp4a(0x01010101, (int) h1.y, s1);
+        s0 = __dp4a(0x01010101, (int) h0.z, s0), s1 = __dp4a(0x01010101, (int) h1.z, s1);
+        s0 = __dp4a(0x01010101, (int) h0.w, s0), s1 = __dp4a(0x01010101, (int) h1.w, s1);
+        ss[it] = make_int2(32 * s0, 32 * s1);
+    }
+    __syncthreads();
+    int buf = 0;
+#pragma unroll 1
+    for (int kk = 0; kk < DN_K; ++kk) {
+        const int row0 = rowB + kk * rpb;
+        if (row0 >= nrows) break;
+        // this group's weights: codes 0..63 (the -32 goes through ss), kept for every pass over the job's rows
+        unsigned v[DN_UPT][8];
+        float d[DN_UPT];
+        int sc0[DN_UPT], sc1[DN_UPT];
 #pragma unroll
         for (int k = 0; k < DN_UPT; ++k) {
-            sc0[k] = (int) (int8_t) (scw[k] & 0xff), sc1[k] = (int) (int8_t) (scw[k] >> 8);
-            const unsigned lw[4] = {ql[k].x, ql[k].y, ql[k].z, ql[k].w};
+            d[k] = h2f((uint16_t) raw.dh[k]);
+            sc0[k] = (int) (int8_t) (raw.scw[k] & 0xff), sc1[k] = (int) (int8_t) (raw.scw[k] >> 8);
+            const unsigned lw[4] = {raw.ql[k].x, raw.ql[k].y, raw.ql[k].z, raw.ql[k].w};
 #pragma unroll
             for (int w = 0; w < 4; ++w) {
-                v[k][w] = (lw[w] & 0x0F0F0F0Fu) | (((qh[k].x >> (2 * w)) & 0x03030303u) << 4);          // codes 0..63; the -32
-                v[k][4 + w] = ((lw[w] >> 4) & 0x0F0F0F0Fu) | (((qh[k].y >> (2 * w)) & 0x03030303u) << 4);   // goes through ss
+                v[k][w] = (lw[w] & 0x0F0F0F0Fu) | (((raw.qh[k].x >> (2 * w)) & 0x03030303u) << 4);
+                v[k][4 + w] = ((lw[w] >> 4) & 0x0F0F0F0Fu) | (((raw.qh[k].y >> (2 * w)) & 0x03030303u) << 4);
             }
         }
-    }
-    (void) ebase;
+        if (kk + 1 < DN_K && row0 + rpb < nrows) load(raw, row0 + rpb);
+        const int live_rows = min(rpb, nrows - row0);
 #pragma unroll 1
-    for (int c0 = 0; c0 < jb.n; c0 += DN_TC) {
-        const int cn = min(DN_TC, jb.n - c0);
-        if (c0) __syncthreads();
-        for (int it = threadIdx.x; it < cn * nu; it += DN_THREADS) {
-            const int j = it / nu, uu = it % nu;
-            sd[it] = hd[(size_t) jb.y[c0 + j] * nu + uu];
-            const uint4* hp = reinterpret_cast<const uint4*>(hq + (size_t) jb.y[c0 + j] * ffs + uu * 32);
-            const uint4 h0 = hp[0], h1 = hp[1];
-            sq[(size_t) (j * 2) * nu + uu] = h0;        // the two halves in planes of their own: a warp's 16-byte reads
-            sq[(size_t) (j * 2 + 1) * nu + uu] = h1;    // are contiguous
-            int s0 = __dp4a(0x01010101, (int) h0.x, 0), s1 = __dp4a(0x01010101, (int) h1.x, 0);
-            s0 = __dp4a(0x01010101, (int) h0.y, s0), s1 = __dp4a(0x01010101, (int) h1.y, s1);
-            s0 = __dp4a(0x01010101, (int) h0.z, s0), s1 = __dp4a(0x01010101, (int) h1.z, s1);
-            s0 = __dp4a(0x01010101, (int) h0.w, s0), s1 = __dp4a(0x01010101, (int) h1.w, s1);
-            ss[it] = make_int2(32 * s0, 32 * s1);
-        }
-        __syncthreads();
-        if (active) {
+        for (int c0 = 0; c0 < jn; c0 += DN_TC) {
+            const int cn = min(DN_TC, jn - c0);
+            float* pt = part + (size_t) buf * DN_TC * rpb * pu;
+            if (active) {
 #pragma unroll
-            for (int j = 0; j < DN_TC; ++j) {
-                if (j >= cn) break;
-                const uint4 a0 = sq[(size_t) (j * 2) * nu + u], a1 = sq[(size_t) (j * 2 + 1) * nu + u];
-                const int2 bias = ss[j * nu + u];   // sum (code - 32) a = sum code a - 32 sum a, exactly
-                const float dj = sd[j * nu + u];
+                for (int j = 0; j < DN_TC; ++j) {
+                    if (j >= cn) break;
+                    const int jj = c0 + j;
+                    const uint4 a0 = sq[(size_t) (jj * 2) * nu + u], a1 = sq[(size_t) (jj * 2 + 1) * nu + u];
+                    const int2 bias = ss[jj * nu + u];   // sum (code - 32) a = sum code a - 32 sum a, exactly
+                    const float dj = sd[jj * nu + u];
 #pragma unroll
-                for (int k = 0; k < DN_UPT; ++k) {
-                    int is0 = __dp4a((int) v[k][0], (int) a0.x, -bias.x);
-                    is0 = __dp4a((int) v[k][1], (int) a0.y, is0);
-                    is0 = __dp4a((int) v[k][2], (int) a0.z, is0);
-                    is0 = __dp4a((int) v[k][3], (int) a0.w, is0);
-                    int is1 = __dp4a((int) v[k][4], (int) a1.x, -bias.y);
-                    is1 = __dp4a((int) v[k][5], (int) a1.y, is1);
-                    is1 = __dp4a((int) v[k][6], (int) a1.z, is1);
-                    is1 = __dp4a((int) v[k][7], (int) a1.w, is1);
-                    const int I = sc0[k] * is0 + sc1[k] * is1;
-                    part[((size_t) j * rpb + k * RP + r) * pu + u] = fmul(d[k], fmul(dj, (float) I));
+                    for (int k = 0; k < DN_UPT; ++k) {
+                        int is0 = __dp4a((int) v[k][0], (int) a0.x, -bias.x);
+                        is0 = __dp4a((int) v[k][1], (int) a0.y, is0);
+                        is0 = __dp4a((int) v[k][2], (int) a0.z, is0);
+                        is0 = __dp4a((int) v[k][3], (int) a0.w, is0);
+                        int is1 = __dp4a((int) v[k][4], (int) a1.x, -bias.y);
+                        is1 = __dp4a((int) v[k][5], (int) a1.y, is1);
+                        is1 = __dp4a((int) v[k][6], (int) a1.z, is1);
+                        is1 = __dp4a((int) v[k][7], (int) a1.w, is1);
+                        const int I = sc0[k] * is0 + sc1[k] * is1;
+                        pt[((size_t) j * rpb + k * RP + r) * pu + u] = fmul(d[k], fmul(dj, (float) I));
+                    }
                 }
             }
-        }
-        __syncthreads();
-        const int live_rows = min(rpb, nrows - row0);
-        for (int e = threadIdx.x; e < cn * live_rows; e += DN_THREADS) {
-            const int j = e / live_rows, rr = e % live_rows;
-            const float* pr = part + ((size_t) j * rpb + rr) * pu;
-            float s = 0.f;
-            for (int k = 0; k < nu; ++k) s = fadd(s, pr[k]);
-            out[(size_t) jb.out[c0 + j] * nrows + row0 + rr] = s;
+            __syncthreads();   // the one barrier of a pass: the next pass writes the other half of `part`
+            for (int e = threadIdx.x; e < cn * live_rows; e += DN_THREADS) {
+                const int j = e / live_rows, rr = e % live_rows;
+                const float* pr = pt + ((size_t) j * rpb + rr) * pu;
+                float s = 0.f;
+                for (int k0 = 0; k0 < nu; k0 += 8) {   // the loads of eight units ahead of their ordered sums
+                    float t[8];
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) t[k] = pr[min(k0 + k, nu - 1)];
+#pragma unroll
+                    for (int k = 0; k < 8; ++k)
+                        if (k0 + k < nu) s = fadd(s, t[k]);
+                }
+                out[(size_t) jb.out[c0 + j] * nrows + row0 + rr] = s;
+            }
+            buf ^= 1;
         }
     }
 }
@@ -620,9 +646,9 @@ int fnx_moe_down(const FnxExperts* A, const FnxJob* jobs, const int* njobs, int 
         const int nu = ffs / 32;
         FNX_REQUIRE(nu <= DN_THREADS, "moe_down: ff width %d too wide for a block", ffs);
         const int rpb = DN_THREADS / nu * DN_UPT;
-        const size_t sm = (size_t) DN_TC * nu * (32 + 4 + 8) + (size_t) DN_TC * rpb * (nu + 1) * 4;
+        const size_t sm = (size_t) FNX_MAXT * nu * (32 + 4 + 8) + (size_t) 2 * DN_TC * rpb * (nu + 1) * 4;
         if (smem_optin(k_moe_down_q6p, sm, "moe_down q6_K")) return 1;
-        const dim3 grid((nrows + rpb - 1) / rpb, njobs_max);
+        const dim3 grid((nrows + rpb * DN_K - 1) / (rpb * DN_K), njobs_max);
         k_moe_down_q6p<<<grid, DN_THREADS, sm, strm(st)>>>((const uint4*) A->a, (const uint2*) A->b, (const uint16_t*) A->c,
                                                         (const uint16_t*) A->d, A->stride, nrows, ffs, jobs, njobs, h8, hd, part);
         return launch_ok("moe_down q6_K");
