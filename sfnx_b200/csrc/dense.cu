@@ -2,6 +2,9 @@
 // qkvz, wq/wk/wv/wo, ssm_out, the shared expert), and the small f32 GEMV (alpha/beta).  Replaces reference
 // src/dense.cuh and src/kernels.cu:184-227 with the same order of every sum: a lane takes 16 columns at
 // c = 16 lane + 512 k, acc = fma(dw da, (float) isum16, acc) in ascending k, lanes combined by xor 16..1.
+#include <algorithm>
+#include <cstdlib>
+
 #include "common.cuh"
 #include "exact_math.cuh"
 
@@ -118,6 +121,35 @@ __device__ __forceinline__ void mma_s8_16816(int (&d)[4], unsigned a0, unsigned 
                  : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
                  : "r"(a0), "r"(a1), "r"(b0), "r"(QM_MAGIC));
 }
+// two f32 in a 64-bit register, each half rounded as its scalar operation would be (Blackwell's packed f32 pipe): the
+// scaling and adding of the accumulator fragments takes half the instructions and keeps every bit
+typedef unsigned long long f32x2;
+__device__ __forceinline__ f32x2 pack2(float lo, float hi) {
+    f32x2 r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ f32x2 pack2i(int lo, int hi) {
+    f32x2 r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpack2(f32x2 v, float& lo, float& hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
+__device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
+    f32x2 d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ f32x2 add2(f32x2 a, f32x2 b) {
+    f32x2 d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ f32x2 mul2(f32x2 a, f32x2 b) {
+    f32x2 d;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
 __device__ __forceinline__ unsigned ldg_u32(const void* p) {
     unsigned v;
     asm volatile("ld.global.nc.u32 %0, [%1];" : "=r"(v) : "l"(p));
@@ -177,13 +209,14 @@ __global__ void __launch_bounds__(QM_THREADS, 2) k_q8s_mma(const QSegs sg, int c
         sd[it] = d;
     }
     __syncthreads();
-    float acc[QM_MT][4][NT][4];
+    f32x2 acc[QM_MT][4][NT][2];   // [..][h]: row 8 h + lane / 4 of the tile, activation rows 2 (lane % 4), + 1
 #pragma unroll
     for (int mt = 0; mt < QM_MT; ++mt)
 #pragma unroll
         for (int v = 0; v < 4; ++v)
 #pragma unroll
-            for (int nt = 0; nt < NT; ++nt) acc[mt][v][nt][0] = acc[mt][v][nt][1] = acc[mt][v][nt][2] = acc[mt][v][nt][3] = 0.f;
+            for (int nt = 0; nt < NT; ++nt) acc[mt][v][nt][0] = acc[mt][v][nt][1] = 0ull;
+    const f32x2 unmagic = pack2(-12582912.0f, -12582912.0f);
     // the warp's weights: its 64 columns of the block's 32 rows per step (2 KB) come through a two-stage ring of its own,
     // filled with 16-byte cp.async (4 lanes cover a row's 64 contiguous bytes) one step ahead of the MMAs; rows are padded
     // to 80 bytes so that the fragment reads (row lane / 4, 4 bytes at 4 (lane % 4)) hit 32 different banks
@@ -225,17 +258,18 @@ __global__ void __launch_bounds__(QM_THREADS, 2) k_q8s_mma(const QSegs sg, int c
 #pragma unroll
         for (int bb = 0; bb < 2; ++bb) {   // the two 32-column blocks of the warp's 64 columns
             const int b = (cb >> 5) + bb;
-            float w[QM_MT][2][NT][2];   // fl(dw da) of (row, activation row) for this block
-            float da[NT][2];
+            f32x2 w[QM_MT][2][NT];   // fl(dw da) of (row, activation row pair) for this block
+            f32x2 da[NT];
 #pragma unroll
-            for (int nt = 0; nt < NT; ++nt) da[nt][0] = sd[(8 * nt + 2 * q) * nb + b], da[nt][1] = sd[(8 * nt + 2 * q + 1) * nb + b];
+            for (int nt = 0; nt < NT; ++nt) da[nt] = pack2(sd[(8 * nt + 2 * q) * nb + b], sd[(8 * nt + 2 * q + 1) * nb + b]);
 #pragma unroll
             for (int mt = 0; mt < QM_MT; ++mt)
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
                     const float dw = sw[(16 * mt + 8 * h + r8) * (nb + 1) + b];
+                    const f32x2 dw2 = pack2(dw, dw);
 #pragma unroll
-                    for (int nt = 0; nt < NT; ++nt) w[mt][h][nt][0] = fmul(dw, da[nt][0]), w[mt][h][nt][1] = fmul(dw, da[nt][1]);
+                    for (int nt = 0; nt < NT; ++nt) w[mt][h][nt] = mul2(dw2, da[nt]);
                 }
 #pragma unroll
             for (int vv = 0; vv < 2; ++vv) {
@@ -249,9 +283,8 @@ __global__ void __launch_bounds__(QM_THREADS, 2) k_q8s_mma(const QSegs sg, int c
                     for (int nt = 0; nt < NT; ++nt) {
                         int d[4];
                         mma_s8_16816(d, a[mt][v][0], a[mt][v][1], bf[nt]);
-#pragma unroll
-                        for (int i = 0; i < 4; ++i)
-                            acc[mt][v][nt][i] = ffma(w[mt][i >> 1][nt][i & 1], fsub(__int_as_float(d[i]), 12582912.0f), acc[mt][v][nt][i]);
+                        acc[mt][v][nt][0] = fma2(w[mt][0][nt], add2(pack2i(d[0], d[1]), unmagic), acc[mt][v][nt][0]);
+                        acc[mt][v][nt][1] = fma2(w[mt][1][nt], add2(pack2i(d[2], d[3]), unmagic), acc[mt][v][nt][1]);
                     }
             }
         }
@@ -266,21 +299,219 @@ __global__ void __launch_bounds__(QM_THREADS, 2) k_q8s_mma(const QSegs sg, int c
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-                for (int i = 0; i < 4; ++i)
-                    red[(size_t) (4 * warp + v) * OUTS + (16 * mt + 8 * (i >> 1) + r8) * TO + 8 * nt + 2 * q + (i & 1)] = acc[mt][v][nt][i];
+                for (int h = 0; h < 2; ++h)
+                    *reinterpret_cast<f32x2*>(red + (size_t) (4 * warp + v) * OUTS + (16 * mt + 8 * h + r8) * TO + 8 * nt + 2 * q) =
+                        acc[mt][v][nt][h];
     __syncthreads();
-    for (int o = tid; o < OUTS; o += QM_THREADS) {
-        float p[32];
+    for (int o = 2 * tid; o < OUTS; o += 2 * QM_THREADS) {   // two neighbouring activation rows of a weight row a thread
+        f32x2 p[32];
 #pragma unroll
-        for (int l = 0; l < 32; ++l) p[l] = red[(size_t) l * OUTS + o];
+        for (int l = 0; l < 32; ++l) p[l] = *reinterpret_cast<const f32x2*>(red + (size_t) l * OUTS + o);
 #pragma unroll
         for (int w2 = 16; w2; w2 >>= 1)
 #pragma unroll
             for (int l = 0; l < 16; ++l)
-                if (l < w2) p[l] = fadd(p[l], p[l + w2]);
+                if (l < w2) p[l] = add2(p[l], p[l + w2]);
         const int row = row0 + o / TO, t = o % TO;
-        if (row < rows && t < T) out[(size_t) t * out_stride + row] = p[0];
+        float v0, v1;
+        unpack2(p[0], v0, v1);
+        if (row < rows && t < T) out[(size_t) t * out_stride + row] = v0;
+        if (row < rows && t + 1 < T) out[(size_t) (t + 1) * out_stride + row] = v1;
     }
+}
+
+// ---------------------------------------------------------------- the same sums, weights streamed by persistent blocks
+// One block of 16 warps per multiprocessor stages the activations once and walks row tiles (16 MT rows) until the
+// matrix is done.  With WPT = 8 the block is two groups of 8 warps on tiles of their own (their only shared state is
+// the activations); with WPT = 16 (wide matrices, whose activations leave less room) one group.  Warp w of a group owns
+// the 32-column pieces at 32 w and (WPT = 8) 256 + 32 w of every 512 columns, i.e. lanes 2 w, 2 w + 1 and their
+// partners 16 up in the row's xor tree, so the tree's first level is an add inside the warp and 16 lane sums per
+// output meet in shared memory instead of 32.  A warp's pieces of the tile (full 32-byte sectors, with the f16 block
+// scales as 4-byte words beside them) flow through a cp.async ring of QS_S stages that runs on across tiles, so a
+// multiprocessor always has about two steps of every warp in flight.
+constexpr int QS_THREADS = 512, QS_S = 3;
+
+__device__ __forceinline__ void cp_async16(void* dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((unsigned) __cvta_generic_to_shared(dst)), "l"(src));
+}
+__device__ __forceinline__ void cp_async4(void* dst, const void* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((unsigned) __cvta_generic_to_shared(dst)), "l"(src));
+}
+
+struct QTile {   // what a tile index means: its matrix, first row and output
+    const int8_t* wq;
+    const uint16_t* wd;
+    int rows, row0;
+};
+__device__ __forceinline__ QTile q_tile(const QSegs& sg, int tile, int tile_rows) {
+    const int seg = tile < sg.blk_end[0] ? 0 : tile < sg.blk_end[1] ? 1 : 2;
+    QTile t;
+    t.wq = seg == 0 ? sg.q[0] : seg == 1 ? sg.q[1] : sg.q[2];
+    t.wd = seg == 0 ? sg.d[0] : seg == 1 ? sg.d[1] : sg.d[2];
+    t.rows = seg == 0 ? sg.rows[0] : seg == 1 ? sg.rows[1] : sg.rows[2];
+    t.row0 = (tile - (seg == 0 ? 0 : seg == 1 ? sg.blk_end[0] : sg.blk_end[1])) * tile_rows;
+    return t;
+}
+
+template <int NT, int MT, int WPT>
+__global__ void __launch_bounds__(QS_THREADS, 1) k_q8s_stream(const QSegs sg, int cols, const uint8_t* __restrict__ yq,
+                                                             const int8_t* __restrict__ pq, const float* __restrict__ pd, int T, int ntiles,
+                                                             unsigned ring_off, unsigned red_off) {
+    constexpr int G = 16 / WPT, NP = 16 / WPT, CW = 32 * NP, RL = CW + 16, ROWS = 16 * MT, TO = 8 * NT, NL = WPT == 8 ? 16 : 32;
+    extern __shared__ __align__(16) unsigned char smem[];
+    const int nb = cols / 32, lda = cols + QM_APAD, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, q = lane & 3, r8 = lane >> 2;
+    const int g = warp / WPT, wg = warp % WPT, gtid = tid - g * WPT * 32, par = wg & 1, nsteps = (cols + 511) / 512;
+    int8_t* sq = reinterpret_cast<int8_t*>(smem);                          // [8 NT][cols + pad], rows >= T zero
+    float* sd = reinterpret_cast<float*>(smem + (size_t) 8 * NT * lda);    // [8 NT][nb]
+    unsigned char* ringw = smem + ring_off + (size_t) warp * QS_S * ROWS * RL;
+    float* red = reinterpret_cast<float*>(smem + red_off) + (size_t) g * NL * 16 * TO;   // [NL][16 rows][TO], a 16-row pass at a time
+    const int gstride = gridDim.x * G;
+    // ---- the copies run ahead of the sums by QS_S - 1 steps, across tile boundaries
+    int pf_tile = blockIdx.x * G + g, pf_k = 0, pf_slot = 0;
+    QTile pf = q_tile(sg, min(pf_tile, ntiles - 1), ROWS);
+    auto issue = [&]() {
+        if (pf_tile < ntiles) {
+            unsigned char* rs = ringw + (size_t) pf_slot * ROWS * RL;
+#pragma unroll
+            for (int i = 0; i < MT * NP; ++i) {   // 16-byte pieces: 2 NP a row
+                const int j = lane + 32 * i, row = j / (2 * NP), p16 = j % (2 * NP);
+                const int c = 512 * pf_k + 32 * wg + 256 * (p16 >> 1);
+                if (c < cols) cp_async16(rs + row * RL + 16 * p16, pf.wq + (size_t) min(pf.row0 + row, pf.rows - 1) * cols + c + 16 * (p16 & 1));
+            }
+#pragma unroll
+            for (int i = 0; i < (ROWS * NP + 31) / 32; ++i) {   // the pieces' block scales: the aligned f16 pair that holds each
+                const int j = lane + 32 * i, row = j / NP, pi = j % NP, b = 16 * pf_k + wg + 8 * pi;
+                if (j < ROWS * NP && 32 * b < cols)
+                    cp_async4(rs + row * RL + CW + 4 * pi, pf.wd + (size_t) min(pf.row0 + row, pf.rows - 1) * nb + (b & ~1));
+            }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        pf_slot = pf_slot + 1 == QS_S ? 0 : pf_slot + 1;
+        if (++pf_k == nsteps) {
+            pf_k = 0, pf_tile += gstride;
+            if (pf_tile < ntiles) pf = q_tile(sg, pf_tile, ROWS);
+        }
+    };
+#pragma unroll
+    for (int i = 0; i < QS_S - 1; ++i) issue();   // the weights do not wait for the activations
+    for (int it = tid; it < 8 * NT * nb; it += QS_THREADS) {
+        const int t = it / nb, b = it % nb;
+        uint4 v0 = make_uint4(0, 0, 0, 0), v1 = v0;
+        float d = 0.f;
+        if (t < T) {
+            if (yq) {
+                const unsigned* src = reinterpret_cast<const unsigned*>(yq + (size_t) it * 36);
+                d = h2f((uint16_t) (src[0] & 0xffff));
+                v0 = make_uint4(src[1], src[2], src[3], src[4]);
+                v1 = make_uint4(src[5], src[6], src[7], src[8]);
+            } else {
+                const uint4* src = reinterpret_cast<const uint4*>(pq + (size_t) t * cols + b * 32);
+                v0 = src[0], v1 = src[1];
+                d = pd[it];
+            }
+        }
+        uint4* dst = reinterpret_cast<uint4*>(sq + (size_t) t * lda + b * 32);
+        dst[0] = v0, dst[1] = v1;
+        sd[it] = d;
+    }
+    __syncthreads();
+    const f32x2 unmagic = pack2(-12582912.0f, -12582912.0f);
+    int slot = 0;
+#pragma unroll 1
+    for (int tile = blockIdx.x * G + g; tile < ntiles; tile += gstride) {
+        f32x2 acc[MT][2 * NP][NT][2];   // [..][h]: row 8 h + lane / 4 of the 16-row tile, activation rows 2 (lane % 4), + 1
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+            for (int v = 0; v < 2 * NP; ++v)
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) acc[mt][v][nt][0] = acc[mt][v][nt][1] = 0ull;
+#pragma unroll 1
+        for (int k = 0; k < nsteps; ++k) {
+            issue();   // into the stage read one step ago
+            asm volatile("cp.async.wait_group %0;" ::"n"(QS_S - 1) : "memory");
+            __syncwarp();
+            const unsigned char* rs = ringw + (size_t) slot * ROWS * RL;
+#pragma unroll
+            for (int pi = 0; pi < NP; ++pi) {
+                const int cbp = 512 * k + 32 * wg + 256 * pi, b = cbp >> 5;
+                if (cbp < cols) {   // the same for the whole warp
+                    f32x2 w[MT][2][NT];   // fl(dw da) of (row, activation row pair) for this block
+                    f32x2 da[NT];
+#pragma unroll
+                    for (int nt = 0; nt < NT; ++nt) da[nt] = pack2(sd[(8 * nt + 2 * q) * nb + b], sd[(8 * nt + 2 * q + 1) * nb + b]);
+#pragma unroll
+                    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+                        for (int h = 0; h < 2; ++h) {
+                            const float dw = h2f(*reinterpret_cast<const uint16_t*>(rs + (16 * mt + 8 * h + r8) * RL + CW + 4 * pi + 2 * par));
+                            const f32x2 dw2 = pack2(dw, dw);
+#pragma unroll
+                            for (int nt = 0; nt < NT; ++nt) w[mt][h][nt] = mul2(dw2, da[nt]);
+                        }
+#pragma unroll
+                    for (int half = 0; half < 2; ++half) {
+                        const int v = 2 * pi + half, c = cbp + 16 * half;
+                        unsigned bf[NT];
+#pragma unroll
+                        for (int nt = 0; nt < NT; ++nt) bf[nt] = *reinterpret_cast<const unsigned*>(sq + (size_t) (8 * nt + r8) * lda + c + 4 * q);
+#pragma unroll
+                        for (int mt = 0; mt < MT; ++mt) {
+                            const unsigned a0 = *reinterpret_cast<const unsigned*>(rs + (16 * mt + r8) * RL + 16 * v + 4 * q);
+                            const unsigned a1 = *reinterpret_cast<const unsigned*>(rs + (16 * mt + 8 + r8) * RL + 16 * v + 4 * q);
+#pragma unroll
+                            for (int nt = 0; nt < NT; ++nt) {
+                                int d[4];
+                                mma_s8_16816(d, a0, a1, bf[nt]);
+                                acc[mt][v][nt][0] = fma2(w[mt][0][nt], add2(pack2i(d[0], d[1]), unmagic), acc[mt][v][nt][0]);
+                                acc[mt][v][nt][1] = fma2(w[mt][1][nt], add2(pack2i(d[2], d[3]), unmagic), acc[mt][v][nt][1]);
+                            }
+                        }
+                    }
+                }
+            }
+            __syncwarp();   // every lane has read this stage before the next step's copies land in it
+            slot = slot + 1 == QS_S ? 0 : slot + 1;
+        }
+        // ---- the lane sums meet in shared memory, 16 rows at a time, and a thread adds two neighbouring outputs' trees
+        const int seg = tile < sg.blk_end[0] ? 0 : tile < sg.blk_end[1] ? 1 : 2;
+        float* __restrict__ out = seg == 0 ? sg.out[0] : seg == 1 ? sg.out[1] : sg.out[2];
+        const int out_stride = seg == 0 ? sg.stride[0] : seg == 1 ? sg.stride[1] : sg.stride[2];
+        const int rows = seg == 0 ? sg.rows[0] : seg == 1 ? sg.rows[1] : sg.rows[2];
+        const int row0 = (tile - (seg == 0 ? 0 : seg == 1 ? sg.blk_end[0] : sg.blk_end[1])) * ROWS;
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) {
+            asm volatile("bar.sync %0, %1;" ::"r"(1 + g), "r"(WPT * 32) : "memory");   // the pass before has been read
+#pragma unroll
+            for (int half = 0; half < 2; ++half)
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        const f32x2 val = NP == 2 ? add2(acc[mt][half][nt][h], acc[mt][NP == 2 ? 2 + half : half][nt][h]) : acc[mt][half][nt][h];
+                        const int row = 8 * h + r8, t = (8 * nt + 2 * q) ^ (NT == 2 ? ((row >> 1) & 1) << 3 : 0);   // swizzled against bank conflicts
+                        *reinterpret_cast<f32x2*>(red + ((size_t) (2 * wg + half) * 16 + row) * TO + t) = val;
+                    }
+            asm volatile("bar.sync %0, %1;" ::"r"(1 + g), "r"(WPT * 32) : "memory");
+            for (int o = 2 * gtid; o < 16 * TO; o += 2 * WPT * 32) {
+                const int row = o / TO, t = o % TO, ts = t ^ (NT == 2 ? ((row >> 1) & 1) << 3 : 0);
+                f32x2 p[NL];
+#pragma unroll
+                for (int l = 0; l < NL; ++l) p[l] = *reinterpret_cast<const f32x2*>(red + ((size_t) l * 16 + row) * TO + ts);
+#pragma unroll
+                for (int w2 = NL / 2; w2; w2 >>= 1)
+#pragma unroll
+                    for (int l = 0; l < NL / 2; ++l)
+                        if (l < w2) p[l] = add2(p[l], p[l + w2]);
+                float v0, v1;
+                unpack2(p[0], v0, v1);
+                const int orow = row0 + 16 * mt + row;
+                if (orow < rows && t < T) out[(size_t) t * out_stride + orow] = v0;
+                if (orow < rows && t + 1 < T) out[(size_t) (t + 1) * out_stride + orow] = v1;
+            }
+        }
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
 }
 
 // f32 GEMV, a block of 4 warps per row, warp p the p-th quarter of the float4 chunks (reference
@@ -344,6 +575,58 @@ __global__ void __launch_bounds__(256) k_swiglu_rows(const float* __restrict__ g
 }
 
 // the tensor-core kernel over 1..3 matrices; -1 when its shared memory does not fit (the caller falls back)
+static int sm_count() {
+    static int n[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    if (!n[dev] && cudaDeviceGetAttribute(&n[dev], cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) n[dev] = 148;
+    return n[dev];
+}
+
+// the persistent streaming kernel; -1 when the shape does not fit it
+int q8s_stream_launch(const FnxQ8S* w, const int* rows, float* const* out, const int* out_stride, int nseg, int cols, const void* yq,
+                      const int8_t* pq, const float* pd, int T, cudaStream_t st, const char* what) {
+    if (cols % 64) return -1;
+    for (int s = 0; s < nseg; ++s)
+        if ((uintptr_t) w[s].q % 16 || (uintptr_t) w[s].d % 4) return -1;   // 16-byte pieces, 4-byte scale pairs
+    const int NT = T <= 8 ? 1 : 2, TO = 8 * NT, nsm = sm_count();
+    const size_t act = ((size_t) 8 * NT * (cols + QM_APAD) + (size_t) 8 * NT * (cols / 32) * 4 + 15) & ~(size_t) 15, cap = 226 * 1024;
+    long rows_all = 0, tiles32 = 0;
+    for (int s = 0; s < nseg; ++s) rows_all += rows[s], tiles32 += (rows[s] + 31) / 32;
+    // two groups of 8 warps when their rings fit beside the activations, else one group of 16; 32-row tiles when there
+    // are enough of them to keep every group busy for a few rounds
+    int WPT = 8, MT = tiles32 >= 3L * 2 * nsm ? 2 : 1;
+    auto bytes = [&](int wpt, int mt) {
+        const int np = 16 / wpt, nl = wpt == 8 ? 16 : 32, g = 16 / wpt;
+        return act + (size_t) 16 * QS_S * 16 * mt * (32 * np + 16) + (size_t) g * nl * 16 * TO * 4;
+    };
+    if (bytes(8, MT) > cap) MT = 1;
+    if (bytes(8, MT) > cap) WPT = 16;
+    if (bytes(WPT, MT) > cap) return -1;
+    const int tile_rows = 16 * MT, G = 16 / WPT;
+    QSegs sg{};
+    int ntiles = 0;
+    for (int s = 0; s < 3; ++s) {
+        const int k = s < nseg ? s : nseg - 1;
+        sg.q[s] = w[k].q, sg.d[s] = w[k].d, sg.out[s] = out[k], sg.stride[s] = out_stride[k], sg.rows[s] = rows[k];
+        if (s < nseg) ntiles += (rows[s] + tile_rows - 1) / tile_rows;
+        sg.blk_end[s] = ntiles;
+    }
+    const int grid = std::min(nsm, (ntiles + G - 1) / G);
+    const size_t smm = bytes(WPT, MT);
+    const unsigned ring_off = (unsigned) act, red_off = (unsigned) (act + (size_t) 16 * QS_S * tile_rows * (32 * (16 / WPT) + 16));
+#define QS_CASE(NTv, MTv, WPTv)                                                                                                   \
+    if (NT == NTv && MT == MTv && WPT == WPTv) {                                                                                  \
+        if (cudaFuncSetAttribute(k_q8s_stream<NTv, MTv, WPTv>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smm) != cudaSuccess) \
+            return fail("%s: shared memory opt-in failed", what);                                                                 \
+        k_q8s_stream<NTv, MTv, WPTv><<<grid, QS_THREADS, smm, st>>>(sg, cols, (const uint8_t*) yq, pq, pd, T, ntiles, ring_off, red_off); \
+        return launch_ok(what);                                                                                                   \
+    }
+    QS_CASE(1, 1, 8) QS_CASE(1, 2, 8) QS_CASE(2, 1, 8) QS_CASE(2, 2, 8) QS_CASE(1, 1, 16) QS_CASE(2, 1, 16)
+#undef QS_CASE
+    return -1;
+}
+
 int q8s_mma_launch(const FnxQ8S* w, const int* rows, float* const* out, const int* out_stride, int nseg, int cols, const void* yq,
                    const int8_t* pq, const float* pd, int T, cudaStream_t st, const char* what) {
     const int NT = T <= 8 ? 1 : 2;
@@ -384,7 +667,10 @@ int q8s_launch(FnxQ8S w, int rows, int cols, const void* yq, const int8_t* pq, c
         const FnxQ8S ws[1] = {w};
         const int rs[1] = {rows}, strides[1] = {out_stride};
         float* outs[1] = {out};
-        const int rc = q8s_mma_launch(ws, rs, outs, strides, 1, cols, yq, pq, pd, T, st, what);
+        static const bool tiled = getenv("FNX_DENSE_TILED") != nullptr;   // a tuning knob: the one-tile-a-block kernel instead
+        int rc = tiled ? -1 : q8s_stream_launch(ws, rs, outs, strides, 1, cols, yq, pq, pd, T, st, what);
+        if (rc >= 0) return rc;
+        rc = q8s_mma_launch(ws, rs, outs, strides, 1, cols, yq, pq, pd, T, st, what);
         if (rc >= 0) return rc;
     }
     // enough blocks to fill the GPU twice over, at most 128 rows each so the staged activations are amortised
@@ -423,7 +709,10 @@ int fnx_q8s_gemv_segs(const FnxQ8S* w, const int* rows, float* const* out, const
     FNX_REQUIRE(n >= 1 && n <= 3, "q8s_gemv_segs: %d matrices (1..3)", n);
     FNX_REQUIRE(T >= 1 && T <= FNX_MAXT, "q8s_gemv_segs: T %d outside 1..%d", T, FNX_MAXT);
     if (cols % 64 == 0) {
-        const int rc = q8s_mma_launch(w, rows, out, out_stride, n, cols, y, nullptr, nullptr, T, strm(st), "q8s_gemv_segs");
+        static const bool tiled = getenv("FNX_DENSE_TILED") != nullptr;
+        int rc = tiled ? -1 : q8s_stream_launch(w, rows, out, out_stride, n, cols, y, nullptr, nullptr, T, strm(st), "q8s_gemv_segs");
+        if (rc >= 0) return rc;
+        rc = q8s_mma_launch(w, rows, out, out_stride, n, cols, y, nullptr, nullptr, T, strm(st), "q8s_gemv_segs");
         if (rc >= 0) return rc;
     }
     for (int s = 0; s < n; ++s)
