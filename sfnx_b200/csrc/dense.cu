@@ -353,43 +353,67 @@ __device__ __forceinline__ QTile q_tile(const QSegs& sg, int tile, int tile_rows
     return t;
 }
 
+__device__ __forceinline__ void ldmatrix_x4(unsigned (&r)[4], unsigned addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x2(unsigned (&r)[2], unsigned addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(addr));
+}
+
 template <int NT, int MT, int WPT>
 __global__ void __launch_bounds__(QS_THREADS, 1) k_q8s_stream(const QSegs sg, int cols, const uint8_t* __restrict__ yq,
                                                              const int8_t* __restrict__ pq, const float* __restrict__ pd, int T, int ntiles,
                                                              unsigned ring_off, unsigned red_off) {
     constexpr int G = 16 / WPT, NP = 16 / WPT, CW = 32 * NP, RL = CW + 16, ROWS = 16 * MT, TO = 8 * NT, NL = WPT == 8 ? 16 : 32;
+    constexpr int NPC = MT * NP, NSC = (ROWS * NP + 31) / 32;   // 16-byte pieces and scale words a lane copies per step
     extern __shared__ __align__(16) unsigned char smem[];
     const int nb = cols / 32, lda = cols + QM_APAD, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, q = lane & 3, r8 = lane >> 2;
     const int g = warp / WPT, wg = warp % WPT, gtid = tid - g * WPT * 32, par = wg & 1, nsteps = (cols + 511) / 512;
     int8_t* sq = reinterpret_cast<int8_t*>(smem);                          // [8 NT][cols + pad], rows >= T zero
-    float* sd = reinterpret_cast<float*>(smem + (size_t) 8 * NT * lda);    // [8 NT][nb]
+    float* sd = reinterpret_cast<float*>(smem + (size_t) 8 * NT * lda);    // [nb][4][NT][2]: block, lane % 4, 8-row tile, row pair
     unsigned char* ringw = smem + ring_off + (size_t) warp * QS_S * ROWS * RL;
     float* red = reinterpret_cast<float*>(smem + red_off) + (size_t) g * NL * 16 * TO;   // [NL][16 rows][TO], a 16-row pass at a time
     const int gstride = gridDim.x * G;
-    // ---- the copies run ahead of the sums by QS_S - 1 steps, across tile boundaries
+    // ---- the copies run ahead of the sums by QS_S - 1 steps, across tile boundaries; a lane's pieces of a step sit at
+    // fixed offsets from the tile's first row, computed when the tile changes
     int pf_tile = blockIdx.x * G + g, pf_k = 0, pf_slot = 0;
-    QTile pf = q_tile(sg, min(pf_tile, ntiles - 1), ROWS);
+    const int8_t* pf_wq = nullptr;
+    const uint16_t* pf_wd = nullptr;
+    unsigned poff[NPC], soff[NSC];
+    auto pf_set = [&]() {
+        const QTile t = q_tile(sg, pf_tile, ROWS);
+        pf_wq = t.wq, pf_wd = t.wd;
+#pragma unroll
+        for (int i = 0; i < NPC; ++i) {
+            const int j = lane + 32 * i, row = j / (2 * NP), p16 = j % (2 * NP);
+            poff[i] = (unsigned) min(t.row0 + row, t.rows - 1) * (unsigned) cols + 32 * wg + 256 * (p16 >> 1) + 16 * (p16 & 1);
+        }
+#pragma unroll
+        for (int i = 0; i < NSC; ++i) {
+            const int j = min(lane + 32 * i, ROWS * NP - 1), row = j / NP, pi = j % NP;
+            soff[i] = (unsigned) min(t.row0 + row, t.rows - 1) * (unsigned) nb + ((wg + 8 * pi) & ~1);
+        }
+    };
+    if (pf_tile < ntiles) pf_set();
     auto issue = [&]() {
         if (pf_tile < ntiles) {
             unsigned char* rs = ringw + (size_t) pf_slot * ROWS * RL;
 #pragma unroll
-            for (int i = 0; i < MT * NP; ++i) {   // 16-byte pieces: 2 NP a row
+            for (int i = 0; i < NPC; ++i) {   // 16-byte pieces: 2 NP a row
                 const int j = lane + 32 * i, row = j / (2 * NP), p16 = j % (2 * NP);
-                const int c = 512 * pf_k + 32 * wg + 256 * (p16 >> 1);
-                if (c < cols) cp_async16(rs + row * RL + 16 * p16, pf.wq + (size_t) min(pf.row0 + row, pf.rows - 1) * cols + c + 16 * (p16 & 1));
+                if (512 * pf_k + 32 * wg + 256 * (p16 >> 1) < cols) cp_async16(rs + row * RL + 16 * p16, pf_wq + poff[i] + 512 * pf_k);
             }
 #pragma unroll
-            for (int i = 0; i < (ROWS * NP + 31) / 32; ++i) {   // the pieces' block scales: the aligned f16 pair that holds each
-                const int j = lane + 32 * i, row = j / NP, pi = j % NP, b = 16 * pf_k + wg + 8 * pi;
-                if (j < ROWS * NP && 32 * b < cols)
-                    cp_async4(rs + row * RL + CW + 4 * pi, pf.wd + (size_t) min(pf.row0 + row, pf.rows - 1) * nb + (b & ~1));
+            for (int i = 0; i < NSC; ++i) {   // the pieces' block scales: the aligned f16 pair that holds each
+                const int j = lane + 32 * i, row = j / NP, pi = j % NP;
+                if (j < ROWS * NP && 512 * pf_k + 32 * wg + 256 * pi < cols) cp_async4(rs + row * RL + CW + 4 * pi, pf_wd + soff[i] + 16 * pf_k);
             }
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
         pf_slot = pf_slot + 1 == QS_S ? 0 : pf_slot + 1;
         if (++pf_k == nsteps) {
             pf_k = 0, pf_tile += gstride;
-            if (pf_tile < ntiles) pf = q_tile(sg, pf_tile, ROWS);
+            if (pf_tile < ntiles) pf_set();
         }
     };
 #pragma unroll
@@ -412,10 +436,15 @@ __global__ void __launch_bounds__(QS_THREADS, 1) k_q8s_stream(const QSegs sg, in
         }
         uint4* dst = reinterpret_cast<uint4*>(sq + (size_t) t * lda + b * 32);
         dst[0] = v0, dst[1] = v1;
-        sd[it] = d;
+        sd[((b * 4 + ((t & 7) >> 1)) * NT + (t >> 3)) * 2 + (t & 1)] = d;
     }
     __syncthreads();
     const f32x2 unmagic = pack2(-12582912.0f, -12582912.0f);
+    // ldmatrix row addresses of this lane: 8 x 16-byte matrices; lanes 8 m .. 8 m + 7 give matrix m's rows
+    const unsigned a_lane = (unsigned) ((8 * ((lane >> 3) & 1) + (lane & 7)) * RL + 16 * (lane >> 4));   // rows 0-7 | 8-15, then 16 columns on
+    const unsigned b_lane = NT == 2 ? (unsigned) ((8 * ((lane >> 3) & 1) + (lane & 7)) * lda + 16 * (lane >> 4))
+                                    : (unsigned) ((lane & 7) * lda + 16 * ((lane >> 3) & 1));
+    const unsigned sq_s = (unsigned) __cvta_generic_to_shared(sq) + b_lane, ring_s = (unsigned) __cvta_generic_to_shared(ringw) + a_lane;
     int slot = 0;
 #pragma unroll 1
     for (int tile = blockIdx.x * G + g; tile < ntiles; tile += gstride) {
@@ -432,41 +461,47 @@ __global__ void __launch_bounds__(QS_THREADS, 1) k_q8s_stream(const QSegs sg, in
             asm volatile("cp.async.wait_group %0;" ::"n"(QS_S - 1) : "memory");
             __syncwarp();
             const unsigned char* rs = ringw + (size_t) slot * ROWS * RL;
+            const unsigned rs_s = ring_s + slot * ROWS * RL;
 #pragma unroll
             for (int pi = 0; pi < NP; ++pi) {
                 const int cbp = 512 * k + 32 * wg + 256 * pi, b = cbp >> 5;
                 if (cbp < cols) {   // the same for the whole warp
-                    f32x2 w[MT][2][NT];   // fl(dw da) of (row, activation row pair) for this block
+                    unsigned bf[2][NT];   // [16-column half][8-row tile]
                     f32x2 da[NT];
+                    if (NT == 2) {
+                        unsigned r[4];
+                        ldmatrix_x4(r, sq_s + cbp);
+                        bf[0][0] = r[0], bf[0][NT - 1] = r[1], bf[1][0] = r[2], bf[1][NT - 1] = r[3];
+                        const ulonglong2 dd = *reinterpret_cast<const ulonglong2*>(sd + (size_t) (b * 4 + q) * 4);
+                        da[0] = dd.x, da[NT - 1] = dd.y;
+                    } else {
+                        unsigned r[2];
+                        ldmatrix_x2(r, sq_s + cbp);
+                        bf[0][0] = r[0], bf[1][0] = r[1];
+                        da[0] = *reinterpret_cast<const f32x2*>(sd + (size_t) (b * 4 + q) * 2);
+                    }
 #pragma unroll
-                    for (int nt = 0; nt < NT; ++nt) da[nt] = pack2(sd[(8 * nt + 2 * q) * nb + b], sd[(8 * nt + 2 * q + 1) * nb + b]);
-#pragma unroll
-                    for (int mt = 0; mt < MT; ++mt)
+                    for (int mt = 0; mt < MT; ++mt) {
+                        unsigned a[4];   // a0, a1 of the first half, then of the second
+                        ldmatrix_x4(a, rs_s + (16 * mt) * RL + 32 * pi);
+                        f32x2 w[2][NT];   // fl(dw da) of (row, activation row pair) for this block
 #pragma unroll
                         for (int h = 0; h < 2; ++h) {
                             const float dw = h2f(*reinterpret_cast<const uint16_t*>(rs + (16 * mt + 8 * h + r8) * RL + CW + 4 * pi + 2 * par));
                             const f32x2 dw2 = pack2(dw, dw);
 #pragma unroll
-                            for (int nt = 0; nt < NT; ++nt) w[mt][h][nt] = mul2(dw2, da[nt]);
+                            for (int nt = 0; nt < NT; ++nt) w[h][nt] = mul2(dw2, da[nt]);
                         }
 #pragma unroll
-                    for (int half = 0; half < 2; ++half) {
-                        const int v = 2 * pi + half, c = cbp + 16 * half;
-                        unsigned bf[NT];
-#pragma unroll
-                        for (int nt = 0; nt < NT; ++nt) bf[nt] = *reinterpret_cast<const unsigned*>(sq + (size_t) (8 * nt + r8) * lda + c + 4 * q);
-#pragma unroll
-                        for (int mt = 0; mt < MT; ++mt) {
-                            const unsigned a0 = *reinterpret_cast<const unsigned*>(rs + (16 * mt + r8) * RL + 16 * v + 4 * q);
-                            const unsigned a1 = *reinterpret_cast<const unsigned*>(rs + (16 * mt + 8 + r8) * RL + 16 * v + 4 * q);
+                        for (int half = 0; half < 2; ++half)
 #pragma unroll
                             for (int nt = 0; nt < NT; ++nt) {
+                                const int v = 2 * pi + half;
                                 int d[4];
-                                mma_s8_16816(d, a0, a1, bf[nt]);
-                                acc[mt][v][nt][0] = fma2(w[mt][0][nt], add2(pack2i(d[0], d[1]), unmagic), acc[mt][v][nt][0]);
-                                acc[mt][v][nt][1] = fma2(w[mt][1][nt], add2(pack2i(d[2], d[3]), unmagic), acc[mt][v][nt][1]);
+                                mma_s8_16816(d, a[2 * half], a[2 * half + 1], bf[half][nt]);
+                                acc[mt][v][nt][0] = fma2(w[0][nt], add2(pack2i(d[0], d[1]), unmagic), acc[mt][v][nt][0]);
+                                acc[mt][v][nt][1] = fma2(w[1][nt], add2(pack2i(d[2], d[3]), unmagic), acc[mt][v][nt][1]);
                             }
-                        }
                     }
                 }
             }
@@ -595,14 +630,25 @@ int q8s_stream_launch(const FnxQ8S* w, const int* rows, float* const* out, const
     for (int s = 0; s < nseg; ++s) rows_all += rows[s], tiles32 += (rows[s] + 31) / 32;
     // two groups of 8 warps when their rings fit beside the activations, else one group of 16; 32-row tiles when there
     // are enough of them to keep every group busy for a few rounds
-    int WPT = 8, MT = tiles32 >= 3L * 2 * nsm ? 2 : 1;
     auto bytes = [&](int wpt, int mt) {
         const int np = 16 / wpt, nl = wpt == 8 ? 16 : 32, g = 16 / wpt;
         return act + (size_t) 16 * QS_S * 16 * mt * (32 * np + 16) + (size_t) g * nl * 16 * TO * 4;
     };
-    if (bytes(8, MT) > cap) MT = 1;
-    if (bytes(8, MT) > cap) WPT = 16;
-    if (bytes(WPT, MT) > cap) return -1;
+    // how well a choice fills the machine: tiles over (groups x rounds); 32-row tiles cost fewer instructions a byte,
+    // so they win ties, and one group of 16 warps on a tile fills more multiprocessors when tiles are few
+    auto fill = [&](int wpt, int mt) {
+        if ((wpt == 16 && mt == 2) || bytes(wpt, mt) > cap) return -1.0;
+        long tiles = 0;
+        for (int s = 0; s < nseg; ++s) tiles += (rows[s] + 16 * mt - 1) / (16 * mt);
+        const long groups = (long) nsm * (16 / wpt), rounds = (tiles + groups - 1) / groups;
+        return (double) tiles / (double) (groups * rounds);
+    };
+    int WPT = 8, MT = 2;
+    double best = fill(8, 2);
+    if (fill(8, 1) > best + 0.08) best = fill(8, 1), MT = 1;
+    if (fill(16, 1) > best + 0.08) best = fill(16, 1), WPT = 16, MT = 1;
+    if (best < 0) return -1;
+    if ((size_t) rows_all * cols >= ((size_t) 1 << 32)) return -1;   // 32-bit piece offsets
     const int tile_rows = 16 * MT, G = 16 / WPT;
     QSegs sg{};
     int ntiles = 0;
