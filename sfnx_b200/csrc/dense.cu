@@ -375,14 +375,28 @@ __global__ void __launch_bounds__(QS_THREADS, 1) k_q8s_stream(const QSegs sg, in
     float* red = reinterpret_cast<float*>(smem + red_off) + (size_t) g * NL * 16 * TO;   // [NL][16 rows][TO], a 16-row pass at a time
     const int gstride = gridDim.x * G;
     // ---- the copies run ahead of the sums by QS_S - 1 steps, across tile boundaries; a lane's pieces of a step sit at
-    // fixed offsets from the tile's first row, computed when the tile changes
-    int pf_tile = blockIdx.x * G + g, pf_k = 0, pf_slot = 0;
-    const int8_t* pf_wq = nullptr;
-    const uint16_t* pf_wd = nullptr;
-    unsigned poff[NPC], soff[NSC];
+    // fixed offsets from the tile's first row, computed when the tile changes, and at fixed places of a ring stage
+    constexpr unsigned STAGE = ROWS * RL;
+    const unsigned ring_s0 = (unsigned) __cvta_generic_to_shared(ringw);
+    const bool whole = cols % 512 == 0;   // every piece of every step exists
+    int pf_tile = blockIdx.x * G + g, pf_k = 0;
+    unsigned pf_stage = ring_s0;
+    const int8_t* pf_q = nullptr;      // the tile's matrix, advanced by the step
+    const uint16_t* pf_d = nullptr;
+    unsigned poff[NPC], soff[NSC], pdst[NPC], sdst[NSC];
+#pragma unroll
+    for (int i = 0; i < NPC; ++i) {
+        const int j = lane + 32 * i, row = j / (2 * NP), p16 = j % (2 * NP);
+        pdst[i] = row * RL + 16 * p16;
+    }
+#pragma unroll
+    for (int i = 0; i < NSC; ++i) {
+        const int j = min(lane + 32 * i, ROWS * NP - 1), row = j / NP, pi = j % NP;
+        sdst[i] = row * RL + CW + 4 * pi;
+    }
     auto pf_set = [&]() {
         const QTile t = q_tile(sg, pf_tile, ROWS);
-        pf_wq = t.wq, pf_wd = t.wd;
+        pf_q = t.wq, pf_d = t.wd;
 #pragma unroll
         for (int i = 0; i < NPC; ++i) {
             const int j = lane + 32 * i, row = j / (2 * NP), p16 = j % (2 * NP);
@@ -397,20 +411,18 @@ __global__ void __launch_bounds__(QS_THREADS, 1) k_q8s_stream(const QSegs sg, in
     if (pf_tile < ntiles) pf_set();
     auto issue = [&]() {
         if (pf_tile < ntiles) {
-            unsigned char* rs = ringw + (size_t) pf_slot * ROWS * RL;
 #pragma unroll
-            for (int i = 0; i < NPC; ++i) {   // 16-byte pieces: 2 NP a row
-                const int j = lane + 32 * i, row = j / (2 * NP), p16 = j % (2 * NP);
-                if (512 * pf_k + 32 * wg + 256 * (p16 >> 1) < cols) cp_async16(rs + row * RL + 16 * p16, pf_wq + poff[i] + 512 * pf_k);
-            }
+            for (int i = 0; i < NPC; ++i)   // 16-byte pieces: 2 NP a row
+                if (whole || 512 * pf_k + 32 * wg + 256 * (((lane + 32 * i) % (2 * NP)) >> 1) < cols)
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(pf_stage + pdst[i]), "l"(pf_q + poff[i]));
 #pragma unroll
-            for (int i = 0; i < NSC; ++i) {   // the pieces' block scales: the aligned f16 pair that holds each
-                const int j = lane + 32 * i, row = j / NP, pi = j % NP;
-                if (j < ROWS * NP && 512 * pf_k + 32 * wg + 256 * pi < cols) cp_async4(rs + row * RL + CW + 4 * pi, pf_wd + soff[i] + 16 * pf_k);
-            }
+            for (int i = 0; i < NSC; ++i)   // the pieces' block scales: the aligned f16 pair that holds each
+                if (lane + 32 * i < ROWS * NP && (whole || 512 * pf_k + 32 * wg + 256 * ((lane + 32 * i) % NP) < cols))
+                    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(pf_stage + sdst[i]), "l"(pf_d + soff[i]));
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
-        pf_slot = pf_slot + 1 == QS_S ? 0 : pf_slot + 1;
+        pf_stage = pf_stage + STAGE == ring_s0 + QS_S * STAGE ? ring_s0 : pf_stage + STAGE;
+        pf_q += 512, pf_d += 16;
         if (++pf_k == nsteps) {
             pf_k = 0, pf_tile += gstride;
             if (pf_tile < ntiles) pf_set();
@@ -444,8 +456,9 @@ __global__ void __launch_bounds__(QS_THREADS, 1) k_q8s_stream(const QSegs sg, in
     const unsigned a_lane = (unsigned) ((8 * ((lane >> 3) & 1) + (lane & 7)) * RL + 16 * (lane >> 4));   // rows 0-7 | 8-15, then 16 columns on
     const unsigned b_lane = NT == 2 ? (unsigned) ((8 * ((lane >> 3) & 1) + (lane & 7)) * lda + 16 * (lane >> 4))
                                     : (unsigned) ((lane & 7) * lda + 16 * ((lane >> 3) & 1));
-    const unsigned sq_s = (unsigned) __cvta_generic_to_shared(sq) + b_lane, ring_s = (unsigned) __cvta_generic_to_shared(ringw) + a_lane;
-    int slot = 0;
+    const unsigned sq_s = (unsigned) __cvta_generic_to_shared(sq) + b_lane;
+    const unsigned dw_lane = (unsigned) (r8 * RL + CW + 2 * par);   // this lane's row's scales in a stage
+    unsigned stage = ring_s0;
 #pragma unroll 1
     for (int tile = blockIdx.x * G + g; tile < ntiles; tile += gstride) {
         f32x2 acc[MT][2 * NP][NT][2];   // [..][h]: row 8 h + lane / 4 of the 16-row tile, activation rows 2 (lane % 4), + 1
@@ -460,8 +473,7 @@ __global__ void __launch_bounds__(QS_THREADS, 1) k_q8s_stream(const QSegs sg, in
             issue();   // into the stage read one step ago
             asm volatile("cp.async.wait_group %0;" ::"n"(QS_S - 1) : "memory");
             __syncwarp();
-            const unsigned char* rs = ringw + (size_t) slot * ROWS * RL;
-            const unsigned rs_s = ring_s + slot * ROWS * RL;
+            const unsigned rs_s = stage + a_lane, rs_d = stage + dw_lane;
 #pragma unroll
             for (int pi = 0; pi < NP; ++pi) {
                 const int cbp = 512 * k + 32 * wg + 256 * pi, b = cbp >> 5;
@@ -487,7 +499,9 @@ __global__ void __launch_bounds__(QS_THREADS, 1) k_q8s_stream(const QSegs sg, in
                         f32x2 w[2][NT];   // fl(dw da) of (row, activation row pair) for this block
 #pragma unroll
                         for (int h = 0; h < 2; ++h) {
-                            const float dw = h2f(*reinterpret_cast<const uint16_t*>(rs + (16 * mt + 8 * h + r8) * RL + CW + 4 * pi + 2 * par));
+                            unsigned short dwh;
+                            asm volatile("ld.shared.u16 %0, [%1];" : "=h"(dwh) : "r"(rs_d + (16 * mt + 8 * h) * RL + 4 * pi));
+                            const float dw = h2f(dwh);
                             const f32x2 dw2 = pack2(dw, dw);
 #pragma unroll
                             for (int nt = 0; nt < NT; ++nt) w[h][nt] = mul2(dw2, da[nt]);
@@ -506,7 +520,7 @@ __global__ void __launch_bounds__(QS_THREADS, 1) k_q8s_stream(const QSegs sg, in
                 }
             }
             __syncwarp();   // every lane has read this stage before the next step's copies land in it
-            slot = slot + 1 == QS_S ? 0 : slot + 1;
+            stage = stage + STAGE == ring_s0 + QS_S * STAGE ? ring_s0 : stage + STAGE;
         }
         // ---- the lane sums meet in shared memory, 16 rows at a time, and a thread adds two neighbouring outputs' trees
         const int seg = tile < sg.blk_end[0] ? 0 : tile < sg.blk_end[1] ? 1 : 2;
@@ -634,8 +648,7 @@ int q8s_stream_launch(const FnxQ8S* w, const int* rows, float* const* out, const
         const int np = 16 / wpt, nl = wpt == 8 ? 16 : 32, g = 16 / wpt;
         return act + (size_t) 16 * QS_S * 16 * mt * (32 * np + 16) + (size_t) g * nl * 16 * TO * 4;
     };
-    // how well a choice fills the machine: tiles over (groups x rounds); 32-row tiles cost fewer instructions a byte,
-    // so they win ties, and one group of 16 warps on a tile fills more multiprocessors when tiles are few
+    // how well a choice fills the machine: tiles over (groups x rounds)
     auto fill = [&](int wpt, int mt) {
         if ((wpt == 16 && mt == 2) || bytes(wpt, mt) > cap) return -1.0;
         long tiles = 0;
@@ -643,11 +656,13 @@ int q8s_stream_launch(const FnxQ8S* w, const int* rows, float* const* out, const
         const long groups = (long) nsm * (16 / wpt), rounds = (tiles + groups - 1) / groups;
         return (double) tiles / (double) (groups * rounds);
     };
+    // relative instructions a byte of the shapes (measured): smaller tiles repeat the activation-side work more often
+    const double f82 = fill(8, 2), f81 = fill(8, 1) / 1.3, f161 = fill(16, 1) / 1.5;
     int WPT = 8, MT = 2;
-    double best = fill(8, 2);
-    if (fill(8, 1) > best + 0.08) best = fill(8, 1), MT = 1;
-    if (fill(16, 1) > best + 0.08) best = fill(16, 1), WPT = 16, MT = 1;
-    if (best < 0) return -1;
+    double best = f82;
+    if (f81 > best) best = f81, MT = 1;
+    if (f161 > best) best = f161, WPT = 16, MT = 1;
+    if (best <= 0) return -1;
     if ((size_t) rows_all * cols >= ((size_t) 1 << 32)) return -1;   // 32-bit piece offsets
     const int tile_rows = 16 * MT, G = 16 / WPT;
     QSegs sg{};
