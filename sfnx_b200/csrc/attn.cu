@@ -56,6 +56,8 @@ __device__ void norm_rope(float* x, const float* w, int pos, float eps, const Ro
 __global__ void k_attn_prep_append(float* qg, float* k, const float* v, const float* qn, const float* kn, uint16_t* kc, uint16_t* vc,
                                    FnxKvPages g, int card, int ncard, const int* pos0p, float eps, RopeFreqs rf, int nq, int nkv,
                                    int hd) {
+    pdl_wait();
+    pdl_go();
     const int t = blockIdx.y, h = blockIdx.x, i = threadIdx.x, p = *pos0p + t, j = p / 4;
     __shared__ float sh[32];
     if (h < nq) {
@@ -188,6 +190,8 @@ __global__ void k_attn_local(const float* __restrict__ acc_in, const AttPart* __
 // `first` (the head's owner): ((P[f+1] + P[f+2]) + ...) + P[f]; out[t][head - h0] = a / z * sigmoid(gate)
 __global__ void k_attn_finish(const float* __restrict__ parts, int nparts, int first, const float* __restrict__ qg,
                               float* __restrict__ out, int nq, int h0, int hd) {
+    pdl_wait();
+    pdl_go();
     const int h = h0 + blockIdx.x, t = blockIdx.y, i = threadIdx.x, T = gridDim.y;
     const size_t psz = (size_t) T * nq * (hd + 2), at = ((size_t) t * nq + h) * (hd + 2);
     const float* p1 = parts + (size_t) ((first + 1) % nparts) * psz + at;
@@ -222,8 +226,8 @@ int fnx_attn_prep_append(float* qg, float* k, const float* v, const float* q_nor
     RopeFreqs rf;
     rf.nrot = rope.nrot;
     for (int i = 0; i < rope.nrot / 2; ++i) rf.f[i] = powf(rope.base, -2.0f * (float) i / (float) rope.nrot);
-    k_attn_prep_append<<<dim3(nq + 2 * nkv, T), hd, 0, strm(st)>>>(qg, k, v, q_norm, k_norm, kc, vc, g, card, ncard, pos0, eps, rf, nq,
-                                                                  nkv, hd);
+    launch(0, k_attn_prep_append, dim3(nq + 2 * nkv, T), hd, 0, strm(st), qg, k, v, q_norm, k_norm, kc, vc, g, card, ncard, pos0, eps, rf,
+           nq, nkv, hd);
     return launch_ok("attn_prep_append");
 }
 
@@ -259,7 +263,7 @@ int fnx_attn_finish(const float* parts, int nparts, int first_part, const float*
                     int hd, void* st) {
     FNX_REQUIRE(nparts >= 1 && first_part >= 0 && first_part < nparts, "attn_finish: partial %d of %d", first_part, nparts);
     FNX_REQUIRE(nh >= 1 && h0 >= 0 && h0 + nh <= nq, "attn_finish: heads [%d, %d) of %d", h0, h0 + nh, nq);
-    k_attn_finish<<<dim3(nh, T), hd, 0, strm(st)>>>(parts, nparts, first_part, qg, out, nq, h0, hd);
+    launch(0, k_attn_finish, dim3(nh, T), hd, 0, strm(st), parts, nparts, first_part, qg, out, nq, h0, hd);
     return launch_ok("attn_finish");
 }
 }

@@ -67,6 +67,8 @@ __global__ void __launch_bounds__(256) k_attn_fast(const AfArgs a) {
     __half* Qhi = reinterpret_cast<__half*>(af_smem);
     __half* Qlo = Qhi + (size_t) Mpad * LD;
     __half* KV = Qlo + (size_t) Mpad * LD;   // [STAGES][K, V][32][LD]
+    pdl_wait();   // the rows appended by the kernel before are among the positions read
+    pdl_go();
     const int pos0 = *a.pos0;
     const int ctx_max = af_kv_owned(pos0 + a.T - 1, a.card, a.ncard);
     const int nchunks = (ctx_max + AF_CH - 1) / AF_CH, cps = (nchunks + a.nsplit - 1) / a.nsplit;
@@ -215,6 +217,8 @@ __global__ void __launch_bounds__(256) k_attn_fast(const AfArgs a) {
 
 // the splits of (row t, head h) merged into this GPU's partial: part[(t nq + h) (hd + 2)] = acc[hd], m, z
 __global__ void k_attn_fast_merge(const float* __restrict__ scratch, float* __restrict__ part, int nq, int nkv, int T, int nsplit, int hd) {
+    pdl_wait();
+    pdl_go();
     const int h = blockIdx.x, t = blockIdx.y, i = threadIdx.x, qpk = nq / nkv, kvl = h / qpk, m = (h % qpk) * T + t, M = T * qpk;
     const float* base = scratch + ((size_t) kvl * nsplit * M + m) * (hd + 2);
     const size_t step = (size_t) M * (hd + 2);
@@ -267,7 +271,7 @@ int fnx_attn_partial(const float* qg, const uint16_t* kc, const uint16_t* vc, Fn
     {                                                                                                             \
         if (cudaFuncSetAttribute(k_attn_fast<HD, ST>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) sm) != cudaSuccess) \
             return fail("attn: shared memory opt-in (%zu bytes) failed", sm);                                     \
-        k_attn_fast<HD, ST><<<grid, 2 * Mpad, sm, strm(st)>>>(a);                                                 \
+        launch(6, k_attn_fast<HD, ST>, grid, 2 * Mpad, sm, strm(st), a);                                            \
     }
     if (hd == 256 && stages == 3) AF_LAUNCH(256, 3)
     else if (hd == 256) AF_LAUNCH(256, 2)
@@ -275,7 +279,7 @@ int fnx_attn_partial(const float* qg, const uint16_t* kc, const uint16_t* vc, Fn
     else AF_LAUNCH(128, 2)
 #undef AF_LAUNCH
     if (launch_ok("attn scan")) return 1;
-    k_attn_fast_merge<<<dim3(nq, T), hd, 0, strm(st)>>>(scratch, part, nq, nkv, T, nsplit, hd);
+    launch(0, k_attn_fast_merge, dim3(nq, T), hd, 0, strm(st), scratch, part, nq, nkv, T, nsplit, hd);
     return launch_ok("attn merge");
 }
 }

@@ -429,7 +429,9 @@ __global__ void __launch_bounds__(QS_THREADS, 1) k_q8s_stream(const QSegs sg, in
         }
     };
 #pragma unroll
-    for (int i = 0; i < QS_S - 1; ++i) issue();   // the weights do not wait for the activations
+    for (int i = 0; i < QS_S - 1; ++i) issue();   // the weights wait neither for the activations nor for the kernel that makes them
+    pdl_wait();
+    pdl_go();
     for (int it = tid; it < 8 * NT * nb; it += QS_THREADS) {
         const int t = it / nb, b = it % nb;
         uint4 v0 = make_uint4(0, 0, 0, 0), v1 = v0;
@@ -575,6 +577,8 @@ __global__ void __launch_bounds__(128) k_gemv_f32(const float* __restrict__ W, c
 #pragma unroll
     for (int i = 0; i < 8; ++i)
         if (i < nc) wv[i] = __ldg(w4 + i * 32 + lane);
+    pdl_wait();   // the weights above are asked for while the kernel before still runs
+    pdl_go();
     float a[4];
     const float4* x4[4];
 #pragma unroll
@@ -613,6 +617,8 @@ __global__ void __launch_bounds__(128) k_gemv_f32(const float* __restrict__ W, c
 __global__ void __launch_bounds__(256) k_swiglu_rows(const float* __restrict__ gu, int ffs, int nrows, int8_t* __restrict__ hq,
                                                      float* __restrict__ hd) {
     const int nb = ffs / 32, q = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    pdl_wait();
+    pdl_go();
     if (q >= nrows * nb) return;
     const int e = q / nb, b = q % nb;
     const float* g = gu + (size_t) e * 2 * ffs;
@@ -680,7 +686,7 @@ int q8s_stream_launch(const FnxQ8S* w, const int* rows, float* const* out, const
     if (NT == NTv && MT == MTv && WPT == WPTv) {                                                                                  \
         if (cudaFuncSetAttribute(k_q8s_stream<NTv, MTv, WPTv>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smm) != cudaSuccess) \
             return fail("%s: shared memory opt-in failed", what);                                                                 \
-        k_q8s_stream<NTv, MTv, WPTv><<<grid, QS_THREADS, smm, st>>>(sg, cols, (const uint8_t*) yq, pq, pd, T, ntiles, ring_off, red_off); \
+        launch(1, k_q8s_stream<NTv, MTv, WPTv>, grid, QS_THREADS, smm, st, sg, cols, (const uint8_t*) yq, pq, pd, T, ntiles, ring_off, red_off); \
         return launch_ok(what);                                                                                                   \
     }
     QS_CASE(1, 1, 8) QS_CASE(1, 2, 8) QS_CASE(2, 1, 8) QS_CASE(2, 2, 8) QS_CASE(1, 1, 16) QS_CASE(2, 1, 16)
@@ -784,7 +790,7 @@ int fnx_q8s_gemv_segs(const FnxQ8S* w, const int* rows, float* const* out, const
 int fnx_gemv_f32(const float* W, const float* x, float* y, int rows, int n, int T, void* st) {
     FNX_REQUIRE(T >= 1 && T <= FNX_MAXT, "gemv_f32: T %d outside 1..%d", T, FNX_MAXT);
     FNX_REQUIRE(n > 0 && n % 512 == 0 && n <= 4096 && rows > 0, "gemv_f32: %d x %d (columns a multiple of 512 up to 4096)", rows, n);
-    k_gemv_f32<<<dim3(rows, (T + 3) / 4), 128, 0, strm(st)>>>(W, x, y, rows, n, T);
+    launch(7, k_gemv_f32, dim3(rows, (T + 3) / 4), 128, 0, strm(st), W, x, y, rows, n, T);
     return launch_ok("gemv_f32");
 }
 
@@ -794,7 +800,7 @@ int fnx_shared_expert(FnxQ8S gate_up, FnxQ8S down, const void* xq, int T, int n,
     if (q8s_launch(gate_up, 2 * ffs, n, xq, nullptr, nullptr, sh_gu, 2 * ffs, T, strm(st), "shared expert gate|up")) return 1;
     int8_t* h8 = (int8_t*) hq;
     float* hd = (float*) ((char*) hq + (size_t) T * ffs);
-    k_swiglu_rows<<<(T * (ffs / 32) + 7) / 8, 256, 0, strm(st)>>>(sh_gu, ffs, T, h8, hd);
+    launch(0, k_swiglu_rows, (T * (ffs / 32) + 7) / 8, 256, 0, strm(st), sh_gu, ffs, T, h8, hd);
     if (launch_ok("shared expert swiglu")) return 1;
     return q8s_launch(down, n, ffs, nullptr, h8, hd, out, n, T, strm(st), "shared expert down");
 }

@@ -37,6 +37,14 @@ __global__ void __cluster_dims__(GDN_Q, 1, 1) __launch_bounds__(GDN_THREADS, 2) 
     const int lv = blockIdx.x / GDN_Q, qq = blockIdx.x % GDN_Q, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int vm = g.vmap[lv], kh = vm & 255, writes_hist = vm >> 8, nk = g.nk, nv = g.nv, T = g.T;
     const int ch = (2 * nk + nv) * HS, row_stride = ch + nv * HS;
+    // the state's loads go out first: they depend on no kernel of this window and have the whole prologue to land
+    const int part = tid >> 7, cl = (tid >> 2) & 31, j = tid & 3, col = qq * GDN_QC + cl;
+    float* st = g.S + (size_t) lv * HS * HS + (size_t) (part * 32 + j) * HS + col;
+    float s[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) s[i] = __ldcs(st + (size_t) 4 * i * HS);
+    pdl_wait();
+    pdl_go();
     const unsigned parity = ((const unsigned*) g.ctl)[1] & 1u;
     const float* hin = g.hist + (size_t) parity * 3 * ch;
     float* hout = g.hist + (size_t) (parity ^ 1u) * 3 * ch;
@@ -53,12 +61,6 @@ __global__ void __cluster_dims__(GDN_Q, 1, 1) __launch_bounds__(GDN_THREADS, 2) 
         gates[tid][0] = ex_expf(fmul(sp, g.a[lv]));
         gates[tid][1] = fdiv(1.0f, fadd(1.0f, ex_expf(-abt[nv + lv])));
     }
-    // ---- the state's loads go out first: they have the whole prologue to land
-    const int part = tid >> 7, cl = (tid >> 2) & 31, j = tid & 3, col = qq * GDN_QC + cl;
-    float* st = g.S + (size_t) lv * HS * HS + (size_t) (part * 32 + j) * HS + col;
-    float s[8];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) s[i] = __ldcs(st + (size_t) 4 * i * HS);
     // ---- causal conv (width 4) + silu: the key head's q and k channels, this block's 32 v channels; one item per
     // (row, channel), its four taps read from the window's rows or, before row 0, from the history
     constexpr int NCH = 2 * HS + GDN_QC, CI = 3;   // items in flight per thread
@@ -209,7 +211,7 @@ int fnx_gdn_core(const float* qkvz, const float* ab, float* hist, const float* c
     FNX_REQUIRE(nk >= 1 && nk <= 255 && nv >= 1, "gdn_core: %d key heads, %d value heads", nk, nv);
     FNX_REQUIRE(T == 1 || (snap && hsnap), "gdn_core: a window of %d rows needs snap and hsnap", T);
     GdnArgs g{qkvz, ab, hist, convw, dt, a, nw, S, (uint8_t*) yq, ctl, scratch, snap, hsnap, nk, nv, vmap, T, eps, y32};
-    k_gdn_core<<<nv * GDN_Q, GDN_THREADS, 0, strm(st)>>>(g);
+    launch(5, k_gdn_core, nv * GDN_Q, GDN_THREADS, 0, strm(st), g);
     return launch_ok("gdn_core");
 }
 }

@@ -13,6 +13,8 @@ __global__ void __launch_bounds__(AM_THREADS) k_argmax(const float* __restrict__
                                                       unsigned* err) {
     const int t = blockIdx.y;
     const float* r = logits + (size_t) t * rows;
+    pdl_wait();
+    pdl_go();
     unsigned long long best = 0;
     bool bad = false;
     for (int i = blockIdx.x * AM_THREADS + threadIdx.x; i < rows; i += gridDim.x * AM_THREADS) {
@@ -39,6 +41,8 @@ __global__ void __launch_bounds__(AM_THREADS) k_argmax(const float* __restrict__
 // decodes the keys into (value, index + v0) and leaves them at zero for the next call
 __global__ void k_argmax_fin(unsigned long long* keys, int T, int v0, float* bv, int* bi) {
     const int t = threadIdx.x;
+    pdl_wait();
+    pdl_go();
     if (t >= T) return;
     const unsigned long long k = keys[t];
     bv[t] = fkey_inv((unsigned) (k >> 32));
@@ -182,9 +186,9 @@ int fnx_argmax(const float* logits, int rows, int T, int v0, float* best_v, int*
     FNX_REQUIRE(T >= 1 && T <= FNX_MAXT && rows >= 1, "argmax: T %d, %d logits a row", T, rows);
     int gx = (rows + AM_THREADS * 8 - 1) / (AM_THREADS * 8);
     gx = gx < 1 ? 1 : gx > 64 ? 64 : gx;
-    k_argmax<<<dim3(gx, T), AM_THREADS, 0, strm(st)>>>(logits, rows, keys, err);
+    launch(0, k_argmax, dim3(gx, T), AM_THREADS, 0, strm(st), logits, rows, keys, err);
     if (launch_ok("argmax")) return 1;
-    k_argmax_fin<<<1, 32, 0, strm(st)>>>(keys, T, v0, best_v, best_i);
+    launch(0, k_argmax_fin, 1, 32, 0, strm(st), keys, T, v0, best_v, best_i);
     return launch_ok("argmax fin");
 }
 

@@ -41,6 +41,17 @@ __global__ void __launch_bounds__(RR_THREADS) k_router_route(const RouterArgs a,
     const int L = a.nexp + 1, nc = a.n / 256;   // float4 chunks per lane
     extern __shared__ __align__(16) float xs_sm[];   // the window's rows of x, read once per block (when they fit)
     __shared__ float rsum[FNX_MAXT][RR_THREADS / 32];
+    // the first rows' weights are asked for before the kernel ahead in the stream has finished (they do not depend on it)
+    const int first0 = blockIdx.x * RR_ROWS;
+    float4 wv[16];   // a row half's weights held in registers (up to 16 float4 a lane: n <= 4096)
+    if (first0 + rw < L) {
+        const float4* w4 = reinterpret_cast<const float4*>(a.W + (size_t) (first0 + rw) * a.n) + half * nc * 32;
+#pragma unroll
+        for (int i = 0; i < 16; ++i)
+            if (i < nc) wv[i] = __ldg(w4 + i * 32 + lane);
+    }
+    pdl_wait();
+    pdl_go();
     const float* xs = a.x;
     if (x_in_smem) {   // asynchronous 16-byte copies: all of a thread's pieces in flight at once, beside the first weights
         const int n4 = a.T * a.n / 4;
@@ -54,10 +65,8 @@ __global__ void __launch_bounds__(RR_THREADS) k_router_route(const RouterArgs a,
     // a block takes rows b, b + grid, ... four at a time, two warps a row (column halves)
     for (int row0 = blockIdx.x * RR_ROWS; row0 < L; row0 += gridDim.x * RR_ROWS) {
         const int row = row0 + rw;
-        // the row half's weights held in registers (up to 16 float4 a lane: n <= 4096), the rows of x four at a time
-        // so that their loads and sums overlap; each logit's summation order is unchanged
-        float4 wv[16];
-        if (row < L) {
+        // the rows of x four at a time so that their loads and sums overlap; each logit's summation order is unchanged
+        if (row < L && row0 != first0) {
             const float4* w4 = reinterpret_cast<const float4*>(a.W + (size_t) row * a.n) + half * nc * 32;
 #pragma unroll
             for (int i = 0; i < 16; ++i)
@@ -290,6 +299,8 @@ __global__ void __launch_bounds__(GU_THREADS, 2) k_moe_gu_q4k(const uint8_t* __r
     const int ji = blockIdx.y;
     extern __shared__ __align__(16) unsigned char smem[];
     __shared__ FnxJob jb;
+    pdl_wait();              // the jobs come from the kernel before
+    pdl_go();
     const int nj = *njobs;   // read beside the job, not before it (the job array has a slot for every block row)
     if (threadIdx.x < sizeof(FnxJob) / 4) reinterpret_cast<int*>(&jb)[threadIdx.x] = reinterpret_cast<const int*>(jobs + ji)[threadIdx.x];
     if (ji >= nj) return;
@@ -411,6 +422,8 @@ __global__ void __launch_bounds__(GU_THREADS, 2) k_moe_gu_q4k(const uint8_t* __r
 __global__ void __launch_bounds__(256) k_swiglu_q8(const float* __restrict__ gu, int ffs, int nrows, int8_t* __restrict__ hq,
                                                    float* __restrict__ hd) {
     const int nb = ffs / 32, q = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    pdl_wait();
+    pdl_go();
     if (q >= nrows * nb) return;
     const int e = q / nb, b = q % nb;
     const float* g = gu + (size_t) e * 2 * ffs;
@@ -450,6 +463,8 @@ __global__ void __launch_bounds__(DN_THREADS, 3) k_moe_down_q6p(const uint4* __r
     const int ji = blockIdx.y;
     extern __shared__ __align__(16) unsigned char smem[];
     __shared__ FnxJob jb;
+    // the jobs are older than the kernel before this one (the SwiGLU of the pairs), so the job and this block's first
+    // weights are read while that kernel still runs
     const int nj = *njobs;   // read beside the job, not before it (the job array has a slot for every block row)
     if (threadIdx.x < sizeof(FnxJob) / 4) reinterpret_cast<int*>(&jb)[threadIdx.x] = reinterpret_cast<const int*>(jobs + ji)[threadIdx.x];
     if (ji >= nj) return;
@@ -475,6 +490,8 @@ __global__ void __launch_bounds__(DN_THREADS, 3) k_moe_down_q6p(const uint4* __r
     };
     DnRaw raw;
     load(raw, rowB);
+    pdl_wait();   // the pairs' h
+    pdl_go();
     for (int it = threadIdx.x; it < jn * nu; it += DN_THREADS) {
         const int j = it / nu, uu = it % nu;
         sd[it] = hd[(size_t) jb.y[j] * nu + uu];
@@ -563,6 +580,8 @@ __global__ void __launch_bounds__(256) k_moe_combine(const float* __restrict__ p
                                                      const float* __restrict__ sh, const float* __restrict__ logits, int nexp,
                                                      float* __restrict__ out, int n, int topk) {
     const int t = blockIdx.y, i = blockIdx.x * 256 + threadIdx.x;
+    pdl_wait();
+    pdl_go();
     if (i >= n) return;
     float s = 0.f;
     for (int k = 0; k < topk; ++k) s = ffma(topw[t * topk + k], part[((size_t) t * topk + k) * n + i], s);
@@ -599,7 +618,7 @@ int fnx_router_route(const float* W, const float* x, float* logits, int T, int n
     int grid = (nexp + 1 + RR_ROWS - 1) / RR_ROWS;
     if (fits && grid > 148) grid = 148;
     if (fits && smem_optin(k_router_route, xbytes, "router_route")) return 1;
-    k_router_route<<<grid, RR_THREADS, fits ? xbytes : 0, strm(st)>>>(a, fits);
+    launch(2, k_router_route, grid, RR_THREADS, fits ? xbytes : 0, strm(st), a, (int) fits);
     return launch_ok("router_route");
 }
 
@@ -621,7 +640,7 @@ int fnx_moe_gate_up(const FnxExperts* A, const FnxJob* jobs, const int* njobs, i
 #define GU_CASE(G)                                                                                                          \
     case G:                                                                                                                 \
         if (smem_optin(k_moe_gu_q4k<G>, sm, "moe gate|up q4_K")) return 1;                                                  \
-        k_moe_gu_q4k<G><<<grid, GU_THREADS, sm, strm(st)>>>(a, A->stride, nrows, n, jobs, njobs, (const uint8_t*) xq, gu); \
+        launch(3, k_moe_gu_q4k<G>, grid, GU_THREADS, sm, strm(st), a, A->stride, nrows, n, jobs, njobs, (const uint8_t*) xq, gu); \
         break;
         switch (n / 512) {
             GU_CASE(1) GU_CASE(2) GU_CASE(3) GU_CASE(4) GU_CASE(5) GU_CASE(6) GU_CASE(7) GU_CASE(8)
@@ -640,7 +659,7 @@ int fnx_moe_down(const FnxExperts* A, const FnxJob* jobs, const int* njobs, int 
     int8_t* h8 = (int8_t*) hq;
     float* hd = (float*) ((char*) hq + (size_t) npairs * ffs);
     FNX_REQUIRE(((size_t) npairs * ffs) % 16 == 0 && ffs % 16 == 0, "moe_down: h rows must be 16-byte multiples");
-    k_swiglu_q8<<<(npairs * (ffs / 32) + 7) / 8, 256, 0, strm(st)>>>(gu, ffs, npairs, h8, hd);
+    launch(0, k_swiglu_q8, (npairs * (ffs / 32) + 7) / 8, 256, 0, strm(st), gu, ffs, npairs, h8, hd);
     if (launch_ok("moe_down swiglu")) return 1;
     if (A->type == FNX_Q6_K) {
         const int nu = ffs / 32;
@@ -649,8 +668,8 @@ int fnx_moe_down(const FnxExperts* A, const FnxJob* jobs, const int* njobs, int 
         const size_t sm = (size_t) FNX_MAXT * nu * (32 + 4 + 8) + (size_t) 2 * DN_TC * rpb * (nu + 1) * 4;
         if (smem_optin(k_moe_down_q6p, sm, "moe_down q6_K")) return 1;
         const dim3 grid((nrows + rpb * DN_K - 1) / (rpb * DN_K), njobs_max);
-        k_moe_down_q6p<<<grid, DN_THREADS, sm, strm(st)>>>((const uint4*) A->a, (const uint2*) A->b, (const uint16_t*) A->c,
-                                                        (const uint16_t*) A->d, A->stride, nrows, ffs, jobs, njobs, h8, hd, part);
+        launch(4, k_moe_down_q6p, grid, DN_THREADS, sm, strm(st), (const uint4*) A->a, (const uint2*) A->b, (const uint16_t*) A->c,
+               (const uint16_t*) A->d, A->stride, nrows, ffs, jobs, njobs, (const int8_t*) h8, (const float*) hd, part);
         return launch_ok("moe_down q6_K");
     }
     return fail("moe_down: expert type %d not supported (Q6_K units)", A->type);
@@ -699,7 +718,7 @@ int fnx_moe_down_noalloc(const FnxExperts* A, const FnxJob* jobs, const int* njo
 int fnx_moe_combine(const float* part, const float* topw, const float* sh, const float* logits, int nexp, float* out, int T,
                     int n, int topk, void* st) {
     FNX_REQUIRE(T >= 1 && n >= 1, "moe_combine: empty");
-    k_moe_combine<<<dim3((n + 255) / 256, T), 256, 0, strm(st)>>>(part, topw, sh, logits, nexp, out, n, topk);
+    launch(0, k_moe_combine, dim3((n + 255) / 256, T), 256, 0, strm(st), part, topw, sh, logits, nexp, out, n, topk);
     return launch_ok("moe_combine");
 }
 }

@@ -1,4 +1,5 @@
 // Error reporting, activation quantisation, RMS norm, batched copies, load-time repacks, synthetic weights.
+#include <cstdlib>
 #include <cstring>
 
 #include "common.cuh"
@@ -17,6 +18,17 @@ int fail(const char* fmt, ...) {
     va_end(ap);
     return 1;
 }
+bool g_pdl_hold = false;
+bool pdl_on(int kind) {
+    static const bool off = getenv("FNX_NO_PDL") != nullptr;
+    // classes: 0 small row kernels, 1 dense streaming, 2 router, 3 expert gate|up, 4 expert down, 5 DeltaNet, 6 attention
+    // scan, 7 f32 GEMV.  Measured on the 8-layer benchmark window (ms per window; none 2.52): dense alone 2.39, router
+    // alone 2.43, gate|up alone 2.74 (its blocks take the registers of every multiprocessor while the router still runs
+    // and push the shared expert off its overlap), classes 0, 1, 2, 4, 5 together 2.32.
+    static const unsigned mask = getenv("FNX_PDL_MASK") ? (unsigned) strtoul(getenv("FNX_PDL_MASK"), nullptr, 0) : 0x37u;
+    return !off && !g_pdl_hold && (mask >> kind & 1u);
+}
+void pdl_hold(bool hold) { g_pdl_hold = hold; }
 int launch_ok(const char* what) {
     const cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return fail("%s: %s", what, cudaGetErrorString(e));
@@ -38,6 +50,8 @@ __device__ __forceinline__ void q8_1_store(float xi, uint8_t* blk, int lane) {
 
 __global__ void __launch_bounds__(256) k_quantize_q8_1(const float* __restrict__ x, uint8_t* __restrict__ q, int n) {
     const int row = blockIdx.y, b = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    pdl_wait();
+    pdl_go();
     if (b >= n / 32) return;
     q8_1_store(x[(size_t) row * n + b * 32 + lane], q + ((size_t) row * (n / 32) + b) * 36, lane);
 }
@@ -51,6 +65,8 @@ __global__ void __launch_bounds__(1024) k_rms_norm_rows(float* __restrict__ x, c
     __shared__ float sh[32];
     float* xr = x + (size_t) blockIdx.x * n;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    pdl_wait();
+    pdl_go();
     float s = 0.f;
     for (int i = tid; i < n; i += 1024) {
         float v = xr[i];
@@ -78,6 +94,8 @@ __global__ void __launch_bounds__(1024) k_rms_norm_rows(float* __restrict__ x, c
 
 // ---------------------------------------------------------------- batched copies (reference src/kernels.cu:1473-1485)
 __global__ void __launch_bounds__(256) k_copy_many(const FnxCopyJob* __restrict__ jobs) {
+    pdl_wait();
+    pdl_go();
     const FnxCopyJob j = jobs[blockIdx.y];
     float4* d = reinterpret_cast<float4*>(j.dst);
     const float4* s = reinterpret_cast<const float4*>(j.src);
@@ -267,20 +285,20 @@ int fnx_built_arch(void) { return 100; }
 int fnx_quantize_q8_1(const float* x, void* q, int n, int rows, void* st) {
     FNX_REQUIRE(n > 0 && n % 32 == 0 && rows >= 0, "quantize_q8_1: n %d must be a positive multiple of 32", n);
     if (!rows) return 0;
-    k_quantize_q8_1<<<dim3((n / 32 + 7) / 8, rows), 256, 0, strm(st)>>>(x, (uint8_t*) q, n);
+    launch(0, k_quantize_q8_1, dim3((n / 32 + 7) / 8, rows), 256, 0, strm(st), x, (uint8_t*) q, n);
     return launch_ok("quantize_q8_1");
 }
 
 int fnx_rms_norm_rows(float* x, const float* add, const float* w, float* y, void* q, int rows, int n, float eps, void* st) {
     FNX_REQUIRE(n > 0 && n % 32 == 0, "rms_norm_rows: n %d must be a positive multiple of 32", n);
     if (rows <= 0) return 0;
-    k_rms_norm_rows<<<rows, 1024, 0, strm(st)>>>(x, add, w, y, (uint8_t*) q, n, eps);
+    launch(0, k_rms_norm_rows, rows, 1024, 0, strm(st), x, add, w, y, (uint8_t*) q, n, eps);
     return launch_ok("rms_norm_rows");
 }
 
 int fnx_copy_many(const FnxCopyJob* jobs, int n, void* st) {
     if (n <= 0) return 0;
-    k_copy_many<<<dim3(74, n), 256, 0, strm(st)>>>(jobs);
+    launch(0, k_copy_many, dim3(74, n), 256, 0, strm(st), jobs);
     return launch_ok("copy_many");
 }
 

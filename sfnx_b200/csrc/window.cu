@@ -347,12 +347,14 @@ int fnx_trace_begin(void) {
     }
     g_trace.n = 0;
     g_trace.on = true;
+    pdl_hold(true);   // traced kernels run one after the other
     return 0;
 }
 // stops tracing; after the stream has drained, fills ms[i], layer[i] and name pointers for the traced calls (up to cap);
 // returns how many there were
 int fnx_trace_end(float* ms, int* layer, const char** names, int cap) {
     g_trace.on = false;
+    pdl_hold(false);
     int n = g_trace.n < cap ? g_trace.n : cap;
     for (int i = 0; i < n; ++i) {
         if (cudaEventSynchronize(g_trace.ev[2 * i + 1]) != cudaSuccess) return -1;
