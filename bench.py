@@ -38,6 +38,8 @@ def parse():
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--experts", type=int, default=512, help="routed experts (512 = the benchmark configuration; fewer for small profiling runs)")
     ap.add_argument("--vocab", type=int, default=151936, help="vocabulary (151936 = the benchmark configuration)")
+    ap.add_argument("--expert-type", default="q4k", choices=["q4k", "q8_0"],
+                    help="routed experts: q4k (Q4_K gate|up + Q6_K down, the benchmark configuration) or q8_0 (the all-Q8_0 configuration)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="enqueue every window call by call instead of replaying a CUDA graph")
     return ap.parse_args()
@@ -82,9 +84,9 @@ class ClockSampler:
 def algorithmic_bytes(shape, distinct_experts, ctx):
     """Bytes a window must move once (weights, K/V, state + checkpoints, logits), per kernel family, whole model."""
     n, ff = shape.n, shape.ff
-    gu = 2 * ff * (n // 256) * 144
-    dn = n * (ff // 256) * 210
     q8 = lambda r, c: r * c * 34 // 32  # noqa: E731
+    gu = 2 * ff * (n // 256) * 144 if shape.experts == "q4k" else q8(2 * ff, n)
+    dn = n * (ff // 256) * 210 if shape.experts == "q4k" else q8(n, ff)
     state = shape.nvh * 128 * 128 * 4
     b = {"moe_gate_up": gu, "moe_down": dn, "router": (shape.nexp + 1) * n * 4, "shared": q8(2 * ff, n) + q8(n, ff),
          "gdn_core": 17 * state, "qkvz": q8((2 * shape.nkh + 2 * shape.nvh) * 128, n), "ssm_out": q8(n, shape.nvh * 128),
@@ -118,7 +120,8 @@ def main():
     L.load()
     kinds = [1 if (i % 4) == 3 else 0 for i in range(args.layers)]
     T = L.MAXT
-    shape = StackShape(kinds=kinds, ctx=args.ctx, kv_slack=(args.warmup + args.steps + 2) * T, nexp=args.experts, vocab=args.vocab)
+    shape = StackShape(kinds=kinds, ctx=args.ctx, kv_slack=(args.warmup + args.steps + 2) * T, nexp=args.experts, vocab=args.vocab,
+                       experts=args.expert_type)
     t_build = time.time()
     stack = SyntheticStack(shape, ncard=world, card=rank, seed=args.seed, device="cuda:%d" % local)
     runner = WindowRunner(stack, T, group=group, graph=not args.no_graph)
@@ -258,7 +261,7 @@ def main():
     roof = None
     if gu_ms:
         ach = gu_bytes / (gu_ms * 1e-3) / 1e9
-        roof = {"kernel": "k_moe_gu_q4k", "bound": "hbm", "achieved": round(ach, 1), "peak": peak_gbs, "unit": "GB/s",
+        roof = {"kernel": "k_moe_gu_q4k" if shape.experts == "q4k" else "k_moe_gu_q8", "bound": "hbm", "achieved": round(ach, 1), "peak": peak_gbs, "unit": "GB/s",
                 # dram read + write bytes of one launch: ncu on a 128-expert case measured 1.00 x the algorithmic bytes
                 # read (each selected expert's rows once) + the output rows written; scaled to this launch by D
                 "frac": round(ach / peak_gbs, 4), "traffic": int(gu_bytes + T * shape.topk * 2 * (shape.ff // world) * 4),
@@ -272,7 +275,7 @@ def main():
         "scaling": "strong", "vs_baseline": None, "dtype": "int8 x int4/int6/int8 dot products, f32 accumulate", "data": "synthetic",
         "config": {"workload": "cfg2: %d-layer stack (%d DeltaNet + %d attention), batch 1, ctx %d, T=16 rows (1 committed + 15 drafts), "
                                "greedy acceptance, Bernoulli(0.8) drafts" % (len(kinds), kinds.count(0), kinds.count(1), args.ctx),
-                   "hidden": shape.n, "experts": shape.nexp, "topk": shape.topk, "ff": shape.ff, "vocab": shape.vocab,
+                   "hidden": shape.n, "experts": shape.nexp, "expert_type": shape.experts, "topk": shape.topk, "ff": shape.ff, "vocab": shape.vocab,
                    "l2": "inputs larger than L2: %.1f GB of weights and K/V streamed per window" % (stack.weight_bytes() / 1e9),
                    "parallelism": "tp%d (FF blocks / value heads / KV positions / vocabulary)" % world},
         "accepted_per_window": round(accepted / args.steps, 3),
@@ -281,7 +284,7 @@ def main():
         "gpu_launches": int(kernels_per_window * args.steps), "kernels_per_window": int(kernels_per_window),
         "clocks": clk, "roofline": roof, "kernel_us": breakdown, "build_s": round(t_build, 1),
     }
-    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+    if rank == 0 and world == 1 and not args.no_cpu_baseline and shape.experts == "q4k":
         import bench_reference
 
         result["cpu_baseline"] = bench_reference.cpu_baseline(stack, runner, rec[args.warmup], shape, accepted / args.steps)

@@ -415,6 +415,92 @@ __global__ void __launch_bounds__(GU_THREADS, 2) k_moe_gu_q4k(const uint8_t* __r
     }
 }
 
+// ================================================================ gate|up, split Q8_0 experts (reference src/moe.cuh:258-272
+// with the in-tree Q8_0 order of src/dense.cuh:86-138)
+// A row's result is the dense row dot: lane l adds fl(dw da) (float) isum16 over the 16-column pieces at
+// c = 16 l + 512 k in ascending k, the 32 lanes meet by xor 16..1.  A warp takes G8_R rows at a time (their 16-byte
+// loads of one step in flight together, the next step's behind them) against the job's rows, GU_TC at a time, staged in
+// shared memory as an int8 plane and float scales.  With 1-2 rows per job the integer dots are a few dp4a: no tensor
+// cores here.
+constexpr int G8_R = 4, G8_RPB = GU_THREADS / 32 * 16;
+
+__global__ void __launch_bounds__(GU_THREADS, 3) k_moe_gu_q8(const int8_t* __restrict__ WQ, size_t sq, const uint16_t* __restrict__ WD,
+                                                            size_t sd, int nrows, int n, const FnxJob* __restrict__ jobs,
+                                                            const int* __restrict__ njobs, const uint8_t* __restrict__ xq,
+                                                            float* __restrict__ out) {
+    const int ji = blockIdx.y;
+    extern __shared__ __align__(16) unsigned char smem[];
+    __shared__ FnxJob jb;
+    pdl_wait();
+    pdl_go();
+    const int nj = *njobs;
+    if (threadIdx.x < sizeof(FnxJob) / 4) reinterpret_cast<int*>(&jb)[threadIdx.x] = reinterpret_cast<const int*>(jobs + ji)[threadIdx.x];
+    if (ji >= nj) return;
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nb = n / 32;
+    int8_t* aq = reinterpret_cast<int8_t*>(smem);                       // [GU_TC][n]
+    float* ad = reinterpret_cast<float*>(smem + (size_t) GU_TC * n);    // [GU_TC][nb]
+    const int8_t* wq = WQ + (size_t) jb.w * sq;
+    const uint16_t* wd = WD + (size_t) jb.w * sd;
+#pragma unroll 1
+    for (int c0 = 0; c0 < jb.n; c0 += GU_TC) {
+        const int cn = min(GU_TC, jb.n - c0);
+        if (c0) __syncthreads();
+        for (int it = threadIdx.x; it < cn * nb; it += GU_THREADS) {
+            const int j = it / nb, b = it % nb;
+            const unsigned* src = reinterpret_cast<const unsigned*>(xq + ((size_t) jb.y[c0 + j] * nb + b) * 36);
+            uint4* dst = reinterpret_cast<uint4*>(aq + (size_t) j * n + b * 32);
+            dst[0] = make_uint4(src[1], src[2], src[3], src[4]);
+            dst[1] = make_uint4(src[5], src[6], src[7], src[8]);
+            ad[it] = h2f((uint16_t) (src[0] & 0xffff));
+        }
+        __syncthreads();
+#pragma unroll 1
+        for (int r0 = blockIdx.x * G8_RPB + warp * 16; r0 < blockIdx.x * G8_RPB + warp * 16 + 16; r0 += G8_R) {
+            if (r0 >= nrows) break;
+            float acc[G8_R][GU_TC];
+#pragma unroll
+            for (int r = 0; r < G8_R; ++r)
+#pragma unroll
+                for (int t = 0; t < GU_TC; ++t) acc[r][t] = 0.f;
+#pragma unroll 2
+            for (int c = lane * 16; c < n; c += 512) {
+                const int b = c >> 5;
+                uint4 w[G8_R];
+                float dw[G8_R];
+#pragma unroll
+                for (int r = 0; r < G8_R; ++r) {
+                    const size_t row = (size_t) min(r0 + r, nrows - 1);
+                    w[r] = ldg_stream(wq + row * n + c);
+                    dw[r] = h2f(__ldg(wd + row * nb + b));
+                }
+#pragma unroll
+                for (int t = 0; t < GU_TC; ++t) {
+                    if (t >= cn) break;
+                    const uint4 a = *reinterpret_cast<const uint4*>(aq + (size_t) t * n + c);
+                    const float da = ad[t * nb + b];
+#pragma unroll
+                    for (int r = 0; r < G8_R; ++r) {
+                        int sI = __dp4a((int) w[r].x, (int) a.x, GU_MAGIC);   // see GU_MAGIC: no convert instruction
+                        sI = __dp4a((int) w[r].y, (int) a.y, sI);
+                        sI = __dp4a((int) w[r].z, (int) a.z, sI);
+                        sI = __dp4a((int) w[r].w, (int) a.w, sI);
+                        acc[r][t] = ffma(fmul(dw[r], da), fsub(__int_as_float(sI), 12582912.0f), acc[r][t]);
+                    }
+                }
+            }
+#pragma unroll
+            for (int r = 0; r < G8_R; ++r)
+#pragma unroll
+                for (int t = 0; t < GU_TC; ++t) {
+                    if (t >= cn) break;
+                    const float v = wsum(acc[r][t]);
+                    if (lane == 0 && r0 + r < nrows) out[(size_t) jb.out[c0 + t] * nrows + r0 + r] = v;
+                }
+        }
+    }
+}
+
 // ================================================================ h = silu(gate) * up as int8 + scales
 // a warp per (row, 32 columns) of gu rows [gate (ffs) | up (ffs)]: the q8_1 rounding with the scale kept as the float
 // of its f16 value (reference src/moe.cuh:284-295, src/dense.cuh:187-194).  hq: int8 [rows][ffs], then float
@@ -450,11 +536,14 @@ constexpr int DN_TC = 2, DN_UPT = 3, DN_K = 4;   // activation rows a pass; weig
 // chain of dependent global reads (job, weights, activations) and short sums, so the reads are issued as early as
 // their addresses are known.
 struct DnRaw {
-    uint4 ql[DN_UPT];
+    uint4 ql[DN_UPT], qx[DN_UPT];   // qx: the second 16 bytes of a Q8_0 unit
     uint2 qh[DN_UPT];
     unsigned scw[DN_UPT], dh[DN_UPT];
 };
 
+// Q8: the same walk over split Q8_0 experts (reference src/moe.cuh:299-345 with the Q8_0 unit value of src/dense.cuh):
+// a unit is 32 int8 values (QL: two 16-byte pieces) and an f16 scale (D); unit value (dw d8) (float) isum.
+template <bool Q8>
 __global__ void __launch_bounds__(DN_THREADS, 3) k_moe_down_q6p(const uint4* __restrict__ QL, const uint2* __restrict__ QH,
                                                                const uint16_t* __restrict__ SC, const uint16_t* __restrict__ D,
                                                                size_t expert_units, int nrows, int ffs, const FnxJob* __restrict__ jobs,
@@ -482,9 +571,14 @@ __global__ void __launch_bounds__(DN_THREADS, 3) k_moe_down_q6p(const uint4* __r
         for (int k = 0; k < DN_UPT; ++k) {
             const int row = min(row0 + k * RP + min(r, RP - 1), nrows - 1);
             const size_t g = (size_t) jb.w * expert_units + (size_t) row * nu + u;
-            w.ql[k] = ldg_stream(QL + g);
-            w.qh[k] = __ldg(QH + g);
-            w.scw[k] = SC[g];
+            if (Q8) {
+                w.ql[k] = ldg_stream(QL + 2 * g);
+                w.qx[k] = ldg_stream(QL + 2 * g + 1);
+            } else {
+                w.ql[k] = ldg_stream(QL + g);
+                w.qh[k] = __ldg(QH + g);
+                w.scw[k] = SC[g];
+            }
             w.dh[k] = D[g];
         }
     };
@@ -518,12 +612,19 @@ __global__ void __launch_bounds__(DN_THREADS, 3) k_moe_down_q6p(const uint4* __r
 #pragma unroll
         for (int k = 0; k < DN_UPT; ++k) {
             d[k] = h2f((uint16_t) raw.dh[k]);
-            sc0[k] = (int) (int8_t) (raw.scw[k] & 0xff), sc1[k] = (int) (int8_t) (raw.scw[k] >> 8);
             const unsigned lw[4] = {raw.ql[k].x, raw.ql[k].y, raw.ql[k].z, raw.ql[k].w};
+            if (Q8) {
+                const unsigned xw[4] = {raw.qx[k].x, raw.qx[k].y, raw.qx[k].z, raw.qx[k].w};
+                sc0[k] = sc1[k] = 1;
 #pragma unroll
-            for (int w = 0; w < 4; ++w) {
-                v[k][w] = (lw[w] & 0x0F0F0F0Fu) | (((raw.qh[k].x >> (2 * w)) & 0x03030303u) << 4);
-                v[k][4 + w] = ((lw[w] >> 4) & 0x0F0F0F0Fu) | (((raw.qh[k].y >> (2 * w)) & 0x03030303u) << 4);
+                for (int w = 0; w < 4; ++w) v[k][w] = lw[w], v[k][4 + w] = xw[w];
+            } else {
+                sc0[k] = (int) (int8_t) (raw.scw[k] & 0xff), sc1[k] = (int) (int8_t) (raw.scw[k] >> 8);
+#pragma unroll
+                for (int w = 0; w < 4; ++w) {
+                    v[k][w] = (lw[w] & 0x0F0F0F0Fu) | (((raw.qh[k].x >> (2 * w)) & 0x03030303u) << 4);
+                    v[k][4 + w] = ((lw[w] >> 4) & 0x0F0F0F0Fu) | (((raw.qh[k].y >> (2 * w)) & 0x03030303u) << 4);
+                }
             }
         }
         if (kk + 1 < DN_K && row0 + rpb < nrows) load(raw, row0 + rpb);
@@ -538,7 +639,8 @@ __global__ void __launch_bounds__(DN_THREADS, 3) k_moe_down_q6p(const uint4* __r
                     if (j >= cn) break;
                     const int jj = c0 + j;
                     const uint4 a0 = sq[(size_t) (jj * 2) * nu + u], a1 = sq[(size_t) (jj * 2 + 1) * nu + u];
-                    const int2 bias = ss[jj * nu + u];   // sum (code - 32) a = sum code a - 32 sum a, exactly
+                    int2 bias = ss[jj * nu + u];   // sum (code - 32) a = sum code a - 32 sum a, exactly
+                    if (Q8) bias = make_int2(0, 0);
                     const float dj = sd[jj * nu + u];
 #pragma unroll
                     for (int k = 0; k < DN_UPT; ++k) {
@@ -550,8 +652,8 @@ __global__ void __launch_bounds__(DN_THREADS, 3) k_moe_down_q6p(const uint4* __r
                         is1 = __dp4a((int) v[k][5], (int) a1.y, is1);
                         is1 = __dp4a((int) v[k][6], (int) a1.z, is1);
                         is1 = __dp4a((int) v[k][7], (int) a1.w, is1);
-                        const int I = sc0[k] * is0 + sc1[k] * is1;
-                        pt[((size_t) j * rpb + k * RP + r) * pu + u] = fmul(d[k], fmul(dj, (float) I));
+                        const int I = Q8 ? is0 + is1 : sc0[k] * is0 + sc1[k] * is1;
+                        pt[((size_t) j * rpb + k * RP + r) * pu + u] = Q8 ? fmul(fmul(d[k], dj), (float) I) : fmul(d[k], fmul(dj, (float) I));
                     }
                 }
             }
@@ -648,7 +750,17 @@ int fnx_moe_gate_up(const FnxExperts* A, const FnxJob* jobs, const int* njobs, i
 #undef GU_CASE
         return launch_ok("moe gate|up q4_K");
     }
-    return fail("moe_gate_up: expert type %d not supported (Q4_K)", A->type);
+    if (A->type == FNX_Q8_0) {
+        FNX_REQUIRE(n % 32 == 0 && ((uintptr_t) A->a % 16) == 0 && A->stride % 16 == 0 && n % 16 == 0,
+                    "moe gate|up q8_0: %d columns, planes 16-byte aligned", n);
+        const dim3 grid((nrows + G8_RPB - 1) / G8_RPB, njobs_max);
+        const size_t sm = (size_t) GU_TC * (n + (n / 32) * 4);
+        if (smem_optin(k_moe_gu_q8, sm, "moe gate|up q8_0")) return 1;
+        launch(3, k_moe_gu_q8, grid, GU_THREADS, sm, strm(st), (const int8_t*) A->a, A->stride, (const uint16_t*) A->b, A->stride_b / 2, nrows, n,
+               jobs, njobs, (const uint8_t*) xq, gu);
+        return launch_ok("moe gate|up q8_0");
+    }
+    return fail("moe_gate_up: expert type %d not supported (Q4_K, Q8_0)", A->type);
 }
 
 int fnx_moe_down(const FnxExperts* A, const FnxJob* jobs, const int* njobs, int njobs_max, const float* gu, int npairs, void* hq,
@@ -666,13 +778,26 @@ int fnx_moe_down(const FnxExperts* A, const FnxJob* jobs, const int* njobs, int 
         FNX_REQUIRE(nu <= DN_THREADS, "moe_down: ff width %d too wide for a block", ffs);
         const int rpb = DN_THREADS / nu * DN_UPT;
         const size_t sm = (size_t) FNX_MAXT * nu * (32 + 4 + 8) + (size_t) 2 * DN_TC * rpb * (nu + 1) * 4;
-        if (smem_optin(k_moe_down_q6p, sm, "moe_down q6_K")) return 1;
+        if (smem_optin(k_moe_down_q6p<false>, sm, "moe_down q6_K")) return 1;
         const dim3 grid((nrows + rpb * DN_K - 1) / (rpb * DN_K), njobs_max);
-        launch(4, k_moe_down_q6p, grid, DN_THREADS, sm, strm(st), (const uint4*) A->a, (const uint2*) A->b, (const uint16_t*) A->c,
+        launch(4, k_moe_down_q6p<false>, grid, DN_THREADS, sm, strm(st), (const uint4*) A->a, (const uint2*) A->b, (const uint16_t*) A->c,
                (const uint16_t*) A->d, A->stride, nrows, ffs, jobs, njobs, (const int8_t*) h8, (const float*) hd, part);
         return launch_ok("moe_down q6_K");
     }
-    return fail("moe_down: expert type %d not supported (Q6_K units)", A->type);
+    if (A->type == FNX_Q8_0) {   // expert e: values at a + e stride (nrows x ffs int8), scales at b + e stride_b
+        const int nu = ffs / 32;
+        FNX_REQUIRE(nu <= DN_THREADS, "moe_down: ff width %d too wide for a block", ffs);
+        FNX_REQUIRE(((uintptr_t) A->a % 16) == 0 && A->stride == (size_t) nrows * ffs && A->stride_b == (size_t) nrows * nu * 2,
+                    "moe_down q8_0: experts must be dense planes of %d x %d", nrows, ffs);
+        const int rpb = DN_THREADS / nu * DN_UPT;
+        const size_t sm = (size_t) FNX_MAXT * nu * (32 + 4 + 8) + (size_t) 2 * DN_TC * rpb * (nu + 1) * 4;
+        if (smem_optin(k_moe_down_q6p<true>, sm, "moe_down q8_0")) return 1;
+        const dim3 grid((nrows + rpb * DN_K - 1) / (rpb * DN_K), njobs_max);
+        launch(4, k_moe_down_q6p<true>, grid, DN_THREADS, sm, strm(st), (const uint4*) A->a, (const uint2*) nullptr, (const uint16_t*) nullptr,
+               (const uint16_t*) A->b, (size_t) nrows * nu, nrows, ffs, jobs, njobs, (const int8_t*) h8, (const float*) hd, part);
+        return launch_ok("moe_down q8_0");
+    }
+    return fail("moe_down: expert type %d not supported (Q6_K units, Q8_0)", A->type);
 }
 
 // ---- the down projection for callers that cannot allocate device memory

@@ -34,6 +34,7 @@ class StackShape:
     eps: float = 1e-6
     rope_base: float = 1e7
     sigma: float = 0.02
+    experts: str = "q4k"   # routed experts: "q4k" (Q4_K gate|up, Q6_K down) or "q8_0" (both Q8_0)
 
 
 def _seed(base, layer, name):
@@ -173,6 +174,9 @@ class SyntheticStack:
         # FFN
         self.named[(l, "router")] = self._t(self._normal(l, "router", (s.nexp + 1, s.n), s.sigma))
         Lr.router = self.named[(l, "router")].data_ptr()
+        if s.experts == "q8_0":
+            self._build_experts_q8(l)
+            return
         row_b = s.n // 256 * 144
         gu = self._blocks(l, "gate_up", L.Q4_K, s.nexp * 2 * s.ff * s.n).view(s.nexp, 2, s.ff, row_b)
         gu = self._t(gu[:, :, self.ff0:self.ff0 + self.ffs].reshape(s.nexp, 2 * self.ffs * row_b))
@@ -188,11 +192,40 @@ class SyntheticStack:
         self.named[(l, "gate_up")] = gu
         self.named[(l, "down")] = (QL.view(s.nexp, s.n, nu, 16), QH.view(s.nexp, s.n, nu, 8), SC.view(s.nexp, s.n, nu, 2), D.view(s.nexp, s.n, nu))
         Lr.down = L.Experts(L.Q6_K, s.n, self.ffs, QL.data_ptr(), QH.data_ptr(), SC.data_ptr(), D.data_ptr(), s.n * nu, 0)
+        self._build_shared(l)
+        torch.cuda.synchronize()
+        del dn
+
+    def _build_shared(self, l):
+        s, Lr = self.shape, self.layers[l]
         ffr = list(range(self.ff0, self.ff0 + self.ffs))
         Lr.sh_gate_up = self._q8s(l, "sh_gate_up", 2 * s.ff, s.n, rows_idx=self._idx(ffr + [s.ff + r for r in ffr]))
         Lr.sh_down = self._q8s(l, "sh_down", s.n, s.ff, cols_idx=self._idx(list(range(self.ff0 // 32, (self.ff0 + self.ffs) // 32))))
+
+    def _build_experts_q8(self, l):
+        """Routed experts in split Q8_0: gate|up [nexp][2 ffs][n], down [nexp][n][ffs], this GPU's FF range of each."""
+        s, Lr = self.shape, self.layers[l]
+        nb, fb0, fbs = s.n // 32, self.ff0 // 32, self.ffs // 32
+        b = self._blocks(l, "gate_up", L.Q8_0, s.nexp * 2 * s.ff * s.n)
+        q = torch.empty((s.nexp * 2 * s.ff, s.n), dtype=torch.int8, device=self.dev)
+        d = torch.empty((s.nexp * 2 * s.ff, nb), dtype=torch.int16, device=self.dev)
+        L.call("fnx_repack_q8_0_split", b.data_ptr(), q.data_ptr(), d.data_ptr(), s.nexp * 2 * s.ff, s.n, L.stream())
+        gq = self._t(q.view(s.nexp, 2, s.ff, s.n)[:, :, self.ff0:self.ff0 + self.ffs].reshape(s.nexp, 2 * self.ffs, s.n))
+        gd = self._t(d.view(s.nexp, 2, s.ff, nb)[:, :, self.ff0:self.ff0 + self.ffs].reshape(s.nexp, 2 * self.ffs, nb))
+        del b, q, d
+        Lr.gate_up = L.Experts(L.Q8_0, 2 * self.ffs, s.n, gq.data_ptr(), gd.data_ptr(), None, None, 2 * self.ffs * s.n, 2 * self.ffs * nb * 2)
+        b = self._blocks(l, "down", L.Q8_0, s.nexp * s.n * s.ff)
+        q = torch.empty((s.nexp * s.n, s.ff), dtype=torch.int8, device=self.dev)
+        d = torch.empty((s.nexp * s.n, s.ff // 32), dtype=torch.int16, device=self.dev)
+        L.call("fnx_repack_q8_0_split", b.data_ptr(), q.data_ptr(), d.data_ptr(), s.nexp * s.n, s.ff, L.stream())
+        dq = self._t(q.view(s.nexp, s.n, s.ff)[:, :, self.ff0:self.ff0 + self.ffs].contiguous())
+        dd = self._t(d.view(s.nexp, s.n, s.ff // 32)[:, :, fb0:fb0 + fbs].contiguous())
+        del b, q, d
+        Lr.down = L.Experts(L.Q8_0, s.n, self.ffs, dq.data_ptr(), dd.data_ptr(), None, None, s.n * self.ffs, s.n * fbs * 2)
+        self.named[(l, "gate_up")] = (gq, gd)
+        self.named[(l, "down")] = (dq, dd)
+        self._build_shared(l)
         torch.cuda.synchronize()
-        del dn
 
     # ---- state
     def save_state(self):

@@ -31,6 +31,25 @@ def moe_weights(n, nexp, ffs, seed=0, sigma=0.02):
     return w
 
 
+def moe_weights_q8(n, nexp, ffs, seed=0, sigma=0.02):
+    """The same layer with the routed experts in split Q8_0 (the all-Q8_0 configuration): gate|up [nexp][2 ffs][n] and
+    down [nexp][n][ffs] as int8 planes + f16 block scales."""
+    rng = np.random.default_rng(seed)
+    w = {"n": n, "nexp": nexp, "ffs": ffs, "experts": "q8_0"}
+    w["router"] = (rng.standard_normal((nexp + 1, n)) * sigma).astype(np.float32)
+    gu = (rng.standard_normal((nexp * 2 * ffs, n)) * sigma).astype(np.float32)
+    q, d = O.q8_0_to_split(O.quantize_q8_0(gu), nexp * 2 * ffs, n)
+    w["gu_q8"] = (q.reshape(nexp, 2 * ffs, n), d.reshape(nexp, 2 * ffs, n // 32))
+    dn = (rng.standard_normal((nexp * n, ffs)) * sigma).astype(np.float32)
+    q, d = O.q8_0_to_split(O.quantize_q8_0(dn), nexp * n, ffs)
+    w["dn_q8"] = (q.reshape(nexp, n, ffs), d.reshape(nexp, n, ffs // 32))
+    sgu = (rng.standard_normal((2 * ffs, n)) * sigma).astype(np.float32)
+    sdn = (rng.standard_normal((n, ffs)) * sigma).astype(np.float32)
+    w["sh_gu"] = O.q8_0_to_split(O.quantize_q8_0(sgu), 2 * ffs, n)
+    w["sh_dn"] = O.q8_0_to_split(O.quantize_q8_0(sdn), n, ffs)
+    return w
+
+
 def moe_oracle(w, x, topk=10):
     """The whole FFN half on the CPU oracle; returns every intermediate."""
     n, ffs = w["n"], w["ffs"]
@@ -38,8 +57,12 @@ def moe_oracle(w, x, topk=10):
     r = {}
     r["xq"] = O.quantize_q8_1(x)
     r["logits"], r["topi"], r["topw"], r["jobs_gu"], r["jobs_dn"], r["njobs"] = O.router_route(w["router"], x, topk)
-    r["gu"] = O.moe_gate_up_q4k(w["gu_q4k"], w["gu_q4k"].shape[1], r["jobs_gu"], r["njobs"], r["xq"], n, 2 * ffs, T * topk)
-    r["part"] = O.moe_down_q6p(w["dn_planes"], r["jobs_dn"], r["njobs"], r["gu"], n, ffs, T * topk)
+    if w.get("experts") == "q8_0":
+        r["gu"] = O.moe_gate_up_q8(w["gu_q8"][0], w["gu_q8"][1], r["jobs_gu"], r["njobs"], r["xq"], T, T * topk)
+        r["part"] = O.moe_down_q8(w["dn_q8"][0], w["dn_q8"][1], r["jobs_dn"], r["njobs"], r["gu"], T * topk)
+    else:
+        r["gu"] = O.moe_gate_up_q4k(w["gu_q4k"], w["gu_q4k"].shape[1], r["jobs_gu"], r["njobs"], r["xq"], n, 2 * ffs, T * topk)
+        r["part"] = O.moe_down_q6p(w["dn_planes"], r["jobs_dn"], r["njobs"], r["gu"], n, ffs, T * topk)
     r["sh_gu"], r["sh"] = O.shared_expert(w["sh_gu"][0], w["sh_gu"][1], w["sh_dn"][0], w["sh_dn"][1], r["xq"], T)
     r["out"] = O.moe_combine(r["part"], r["topw"], r["sh"], r["logits"], T, n, topk)
     return r

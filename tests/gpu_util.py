@@ -51,6 +51,13 @@ def experts_q6p(planes, nrows, ffs):
     return e, (QL, QH, SC, D)
 
 
+def experts_q8(planes, nrows, ncols):
+    """([nexp][nrows][ncols] int8, [nexp][nrows][ncols / 32] f16 bits) -> FnxExperts of type Q8_0."""
+    q, d = dev(planes[0]), dev(planes[1])
+    e = L.Experts(L.Q8_0, nrows, ncols, q.data_ptr(), d.data_ptr(), None, None, nrows * ncols, nrows * (ncols // 32) * 2)
+    return e, (q, d)
+
+
 def run_moe(w, x, topk=10, keep=None):
     """The FFN half through the C ABI on device copies of the case's weights; returns intermediates as numpy."""
     n, nexp, ffs = w["n"], w["nexp"], w["ffs"]
@@ -65,8 +72,12 @@ def run_moe(w, x, topk=10, keep=None):
     njobs, scratch = zeros(2, torch.int32), zeros(16, torch.uint8)
     L.call("fnx_router_route", router.data_ptr(), dx.data_ptr(), logits.data_ptr(), T, n, nexp, topk, topi.data_ptr(), topw.data_ptr(),
            jgu.data_ptr(), jdn.data_ptr(), njobs.data_ptr(), scratch.data_ptr(), st)
-    egu, k1 = experts_q4k(w["gu_q4k"], 2 * ffs, n)
-    edn, k2 = experts_q6p(w["dn_planes"], n, ffs)
+    if w.get("experts") == "q8_0":
+        egu, k1 = experts_q8(w["gu_q8"], 2 * ffs, n)
+        edn, k2 = experts_q8(w["dn_q8"], n, ffs)
+    else:
+        egu, k1 = experts_q4k(w["gu_q4k"], 2 * ffs, n)
+        edn, k2 = experts_q6p(w["dn_planes"], n, ffs)
     gu = zeros((P, 2 * ffs))
     L.call("fnx_moe_gate_up", C.byref(egu), jgu.data_ptr(), njobs.data_ptr(), P, xq.data_ptr(), gu.data_ptr(), st)
     hq = zeros(L.load().fnx_moe_h_bytes(P, ffs), torch.uint8)

@@ -71,3 +71,25 @@ def test_moe_benchmark_shape_hidden_3072():
     rng = np.random.default_rng(24)
     w = cases.moe_weights(n=3072, nexp=32, ffs=768, seed=4)
     _check(w, rng.standard_normal((16, 3072)).astype(np.float32), topk=10)
+
+
+def test_moe_q8_0_experts():
+    """The all-Q8_0 configuration's routed experts: gate|up in the dense row-dot order, down in 32-column units; small and
+    ragged shapes (FF slice 96), one row, tied routing, rows routed alike, and a job of 16 rows."""
+    rng = np.random.default_rng(25)
+    w = cases.moe_weights_q8(n=1024, nexp=32, ffs=96, seed=5)
+    w["router"][9] = w["router"][4]
+    _check(w, rng.standard_normal((1, 1024)).astype(np.float32), topk=10)
+    x = rng.standard_normal((16, 1024)).astype(np.float32)
+    x[3] = x[1]
+    x[2] = 0
+    _check(w, x, topk=10)
+    w = cases.moe_weights_q8(n=512, nexp=32, ffs=128, seed=6)
+    got = _check(w, np.repeat(rng.standard_normal((1, 512)).astype(np.float32), 16, axis=0), topk=10)
+    assert got["njobs"] == 10
+
+
+def test_moe_q8_0_experts_benchmark_shape():
+    rng = np.random.default_rng(26)
+    w = cases.moe_weights_q8(n=3072, nexp=32, ffs=768, seed=7)
+    _check(w, rng.standard_normal((16, 3072)).astype(np.float32), topk=10)

@@ -77,9 +77,14 @@ class OracleStack:
                 bo = O.q8s_gemv(*_q8s(h, (l, "wo")), O.quantize_q8_1(att.reshape(T, -1)), T)
             x = x + bo
             xn = O.rms_norm_rows(x, ones, s.eps)
-            w = {"n": n, "nexp": s.nexp, "ffs": self.ffs, "router": h[(l, "router")], "gu_q4k": h[(l, "gate_up")],
-                 "dn_planes": (h[(l, "down")][0], h[(l, "down")][1], h[(l, "down")][2].view(np.int8), h[(l, "down")][3].view(np.uint16)),
-                 "sh_gu": _q8s(h, (l, "sh_gate_up")), "sh_dn": _q8s(h, (l, "sh_down"))}
+            w = {"n": n, "nexp": s.nexp, "ffs": self.ffs, "router": h[(l, "router")], "sh_gu": _q8s(h, (l, "sh_gate_up")),
+                 "sh_dn": _q8s(h, (l, "sh_down"))}
+            if s.experts == "q8_0":
+                w["experts"] = "q8_0"
+                w["gu_q8"], w["dn_q8"] = _q8s(h, (l, "gate_up")), _q8s(h, (l, "down"))
+            else:
+                w["gu_q4k"] = h[(l, "gate_up")]
+                w["dn_planes"] = (h[(l, "down")][0], h[(l, "down")][1], h[(l, "down")][2].view(np.int8), h[(l, "down")][3].view(np.uint16))
             pending = cases.moe_oracle(w, xn, s.topk)["out"]
         x = x + pending
         xq = O.quantize_q8_1(O.rms_norm_rows(x, ones, s.eps))
@@ -94,11 +99,11 @@ class OracleStack:
             O.gdn_rollback(self.state[(l, "S")], self.state[(l, "hist")], snap, hsnap, np.array([0, tag], np.int32), self.nk, self.nv, T, n)
 
 
-def _make(kinds, seed):
+def _make(kinds, seed, experts="q4k"):
     from sfnx_b200.window import StackShape, SyntheticStack, WindowRunner
 
     shape = StackShape(n=512, nexp=32, topk=4, ff=256, nkh=2, nvh=4, nq=4, nkv=2, hd=128, nrot=64, vocab=2048, kinds=kinds, ctx=300,
-                       kv_slack=256)
+                       kv_slack=256, experts=experts)
     stack = SyntheticStack(shape, seed=seed, device="cuda:0")
     return shape, stack, WindowRunner(stack, 16, graph=True), OracleStack(stack)
 
@@ -154,6 +159,14 @@ def test_window_deltanet_stack_bit_exact():
     shape, stack, runner, orc = _make([0, 0], seed=5)
     _, total = _run_windows(shape, stack, runner, orc, nwin=4, seed=1, exact=True)
     assert 4 <= total <= 64
+
+
+def test_window_q8_0_experts_bit_exact(monkeypatch):
+    """The all-Q8_0 configuration's expert path inside whole windows (DeltaNet + exact-order attention)."""
+    monkeypatch.setenv("FNX_ATTN_EXACT", "1")
+    shape, stack, runner, orc = _make([0, 1], seed=8, experts="q8_0")
+    _, total = _run_windows(shape, stack, runner, orc, nwin=3, seed=3, exact=True)
+    assert 3 <= total <= 48
 
 
 def test_window_mixed_stack_exact_attention_bit_exact(monkeypatch):
