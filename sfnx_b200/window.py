@@ -270,7 +270,7 @@ class WindowRunner:
     """One window of T rows as a CUDA graph on its own stream: embedding rows from the token ids, every stage, and
     between stages the collectives of the process group (NCCL) when there is more than one GPU."""
 
-    def __init__(self, stack, T, group=None, graph=True, overlap=True):
+    def __init__(self, stack, T, group=None, graph=True, overlap=True, sampled=False):
         import torch.distributed as dist
 
         self.stack, self.T, self.group = stack, T, group
@@ -299,6 +299,15 @@ class WindowRunner:
         self.h_v = torch.zeros((stack.ncard, T), dtype=torch.float32).pin_memory()
         self.h_i = torch.zeros((stack.ncard, T), dtype=torch.int32).pin_memory()
         self.h_err = torch.zeros(1, dtype=torch.int32).pin_memory()
+        # sampled acceptance: every GPU's 64 best (value, token) of each row of its vocabulary range, merged on the host
+        self.sampled = sampled
+        if sampled:
+            self.cand_v = torch.zeros((T, L.TOPK_N), dtype=torch.float32, device=stack.dev)
+            self.cand_i = torch.zeros((T, L.TOPK_N), dtype=torch.int32, device=stack.dev)
+            self.all_cv = torch.zeros((stack.ncard, T, L.TOPK_N), dtype=torch.float32, device=stack.dev)
+            self.all_ci = torch.zeros((stack.ncard, T, L.TOPK_N), dtype=torch.int32, device=stack.dev)
+            self.h_cv = torch.zeros((stack.ncard, T, L.TOPK_N), dtype=torch.float32).pin_memory()
+            self.h_ci = torch.zeros((stack.ncard, T, L.TOPK_N), dtype=torch.int32).pin_memory()
         self.job_bytes = len(s.kinds) * 2 * C.sizeof(L.CopyJob)
         self.h_jobs = torch.zeros(64 * self.job_bytes, dtype=torch.uint8).pin_memory()   # a ring of job tables
         self.commits = 0
@@ -336,12 +345,21 @@ class WindowRunner:
             elif self.after[i] == 2:
                 per = self.partials.numel() // stack.ncard
                 self.dist.all_gather_into_tensor(self.partials, self.partials[stack.card * per:(stack.card + 1) * per], group=self.group)
+        if self.sampled:   # no penalties: the candidates of the plain logits (reference Engine::top_tokens)
+            L.call("fnx_top_tokens", self.logits.data_ptr(), stack.vrows, T, stack.v0, None, None, None, 0, None, self.cand_v.data_ptr(),
+                   self.cand_i.data_ptr(), self.err.data_ptr(), st)
         if self.dist is None:
             self.all_v[0].copy_(self.best_v)
             self.all_i[0].copy_(self.best_i)
+            if self.sampled:
+                self.all_cv[0].copy_(self.cand_v)
+                self.all_ci[0].copy_(self.cand_i)
         else:
             self.dist.all_gather_into_tensor(self.all_v.view(-1), self.best_v, group=self.group)
             self.dist.all_gather_into_tensor(self.all_i.view(-1), self.best_i, group=self.group)
+            if self.sampled:
+                self.dist.all_gather_into_tensor(self.all_cv.view(-1), self.cand_v.view(-1), group=self.group)
+                self.dist.all_gather_into_tensor(self.all_ci.view(-1), self.cand_i.view(-1), group=self.group)
 
     def launch(self):
         """Enqueues one window on the runner's stream (the caller has set ids and ctl)."""
@@ -374,6 +392,29 @@ class WindowRunner:
 
     def merge_best(self):
         return merge_best(self.h_v, self.h_i)
+
+    def window_sampled(self, rows, pos0, tag, rng, temperature=1.0, top_p=1.0, min_p=0.0, top_k=0):
+        """One window with rejection-sampling acceptance against the fixed (one-hot) drafts rows[1:]: runs the window,
+        reads back every GPU's 64 candidates per row, merges them and runs the reference's acceptance loop
+        (src/session.cpp:469-510) with the caller's random stream (fnx_rng_new).  Returns (the emitted tokens, their
+        number); the caller commits that many rows."""
+        assert self.sampled, "build the runner with sampled=True"
+        T, lib = self.T, L.load()
+        self.window(rows, pos0, tag)
+        with torch.cuda.stream(self.stream):
+            self.h_cv.copy_(self.all_cv, non_blocking=True)
+            self.h_ci.copy_(self.all_ci, non_blocking=True)
+        self.stream.synchronize()
+        mv = (C.c_float * (T * L.TOPK_N))()
+        mi = (C.c_int * (T * L.TOPK_N))()
+        if lib.fnx_top_merge(self.h_cv.data_ptr(), self.h_ci.data_ptr(), self.stack.ncard, T, mv, mi) != 0:
+            raise L.FnxError(lib.fnx_last_error().decode())
+        sp = L.Sampling(temperature, top_p, min_p, top_k)
+        rc, out = (C.c_int * T)(*[int(r) for r in rows]), (C.c_int * T)()
+        n = lib.fnx_accept_sampled(rc, T, mv, mi, C.byref(sp), rng, out)
+        if n < 0:
+            raise L.FnxError(lib.fnx_last_error().decode())
+        return list(out[:n]), n
 
     def commit(self, n, tag):
         """Keep the first n rows of the last window: the DeltaNet layers' states and histories back to row n - 1."""

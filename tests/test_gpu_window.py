@@ -182,3 +182,45 @@ def test_window_mixed_stack_fast_attention_within_exactness_bar(monkeypatch):
     (kls, agree), total = _run_windows(shape, stack, runner, orc, nwin=6, seed=2, exact=False)
     assert np.mean(kls) <= KL_BAR, kls
     assert np.mean(agree) >= 0.9833 - 0.015, agree
+
+
+def test_window_sampled_acceptance_matches_oracle():
+    """Rejection sampling against one-hot drafts: the window's 64 candidates per row and the emitted tokens equal the
+    oracle's (its top-64 of the oracle's logits and its acceptance loop with the same random stream), window after
+    window through the rollbacks."""
+    import torch
+
+    from sfnx_b200 import lib as L
+    from sfnx_b200.window import StackShape, SyntheticStack, WindowRunner
+
+    shape = StackShape(n=512, nexp=32, topk=4, ff=256, nkh=2, nvh=4, nq=4, nkv=2, hd=128, nrot=64, vocab=2048, kinds=[0, 0], ctx=300,
+                       kv_slack=256)
+    stack = SyntheticStack(shape, seed=9, device="cuda:0")
+    runner, orc = WindowRunner(stack, 16, graph=True, sampled=True), OracleStack(stack)
+    rng_dev, rng_ref = L.load().fnx_rng_new(1234), O.mt_new(1234)
+    rs = np.random.default_rng(4)
+    none = np.zeros((16, 1), np.int32)
+    pos, tag, x, total = shape.ctx, 1, 11, 0
+    for w in range(4):
+        rows = [x] + [int(v) for v in rs.integers(0, shape.vocab, 15)]
+        if w > 0:   # drafts that follow the model's greedy tokens for a while, so that some are accepted
+            saved = {k: v.copy() for k, v in orc.state.items()}
+            for j in range(int(rs.integers(1, 5))):
+                _, guess = orc.window(rows, pos, tag)
+                orc.state = {k: v.copy() for k, v in saved.items()}
+                rows[j + 1] = guess[j]
+            orc.state = saved
+        ref_logits, _ = orc.window(rows, pos, tag)
+        cv, ci, err = O.top_tokens(ref_logits.copy(), 0, none, none, np.zeros(16, np.int32), np.zeros(3, np.float32))
+        assert err == 0
+        n_ref, toks_ref = O.accept_sampled(rows, cv, ci, rng_ref, temperature=1.0)
+        toks, n = runner.window_sampled(rows, pos, tag, rng_dev, temperature=1.0)
+        assert np.array_equal(runner.h_ci[0].numpy(), ci) and np.array_equal(runner.h_cv[0].numpy().view(np.uint32), cv.view(np.uint32))
+        assert n == n_ref and toks == toks_ref.tolist(), (w, n, n_ref)
+        runner.commit(n, tag)
+        orc.commit(n)
+        torch.cuda.synchronize()
+        total += n
+        pos, tag, x = pos + n, tag + 1, toks[-1]
+    L.load().fnx_rng_free(rng_dev)
+    assert 4 <= total <= 64
