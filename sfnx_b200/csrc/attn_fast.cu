@@ -73,16 +73,6 @@ __global__ void __launch_bounds__(256) k_attn_fast(const AfArgs a) {
     const int ctx_max = af_kv_owned(pos0 + a.T - 1, a.card, a.ncard);
     const int nchunks = (ctx_max + AF_CH - 1) / AF_CH, cps = (nchunks + a.nsplit - 1) / a.nsplit;
     const int c_begin = split * cps, nc = max(0, min(nchunks, c_begin + cps) - c_begin);
-    // the query rows, split into high and low halves: row m = hh T + t is row t of head kvl qpk + hh
-    for (int idx = tid; idx < Mpad * (HD / 2); idx += nthreads) {
-        const int m = idx / (HD / 2), d = (idx % (HD / 2)) * 2;
-        float2 x = make_float2(0.f, 0.f);
-        if (m < M) x = *reinterpret_cast<const float2*>(a.qg + ((size_t) (m % a.T) * a.nq + kvl * qpk + m / a.T) * 2 * HD + d);
-        unsigned hi, lo;
-        split2(x.x, x.y, hi, lo);
-        *reinterpret_cast<unsigned*>(Qhi + (size_t) m * LD + d) = hi;
-        *reinterpret_cast<unsigned*>(Qlo + (size_t) m * LD + d) = lo;
-    }
     auto load_chunk = [&](int c, int stage) {
         __half* Ks = KV + (size_t) stage * 2 * AF_CH * LD;
         __half* Vs = Ks + (size_t) AF_CH * LD;
@@ -107,6 +97,27 @@ __global__ void __launch_bounds__(256) k_attn_fast(const AfArgs a) {
     for (int s = 0; s < STAGES - 1; ++s) {
         if (s < nc) load_chunk(c_begin + s, s);
         cp_async_commit();
+    }
+    // (the first K/V chunks are on their way while the queries are staged)
+    // the query rows, split into high and low halves: row m = hh T + t is row t of head kvl qpk + hh
+    for (int idx0 = tid; idx0 < Mpad * (HD / 2); idx0 += 8 * nthreads) {   // eight loads in flight a thread
+        float2 x[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int idx = idx0 + u * nthreads, m = idx / (HD / 2), d = (idx % (HD / 2)) * 2;
+            x[u] = make_float2(0.f, 0.f);
+            if (idx < Mpad * (HD / 2) && m < M)
+                x[u] = *reinterpret_cast<const float2*>(a.qg + ((size_t) (m % a.T) * a.nq + kvl * qpk + m / a.T) * 2 * HD + d);
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int idx = idx0 + u * nthreads, m = idx / (HD / 2), d = (idx % (HD / 2)) * 2;
+            if (idx >= Mpad * (HD / 2)) break;
+            unsigned hi, lo;
+            split2(x[u].x, x[u].y, hi, lo);
+            *reinterpret_cast<unsigned*>(Qhi + (size_t) m * LD + d) = hi;
+            *reinterpret_cast<unsigned*>(Qlo + (size_t) m * LD + d) = lo;
+        }
     }
 #pragma unroll 1
     for (int i = 0; i < nc; ++i) {
