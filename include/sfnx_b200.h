@@ -177,6 +177,25 @@ int fnx_attn_splits(int nkv);
 int fnx_attn_finish(const float* parts, int nparts, int first_part, const float* qg, float* out, int T, int nq, int h0, int nh,
                     int hd, void* st);
 
+/* ---- sum across GPUs */
+/* all-reduce(sum) of x[rows][row_len] in the reference ring's order, chunk c = float pairs [c NP / n, (c + 1) NP / n) of
+ * every row (NP = row_len / 2) summed as ((x_c + x_{c+1}) + ...) + x_{c+n-1} (reference src/kernels.hpp:321-353 ring_sum / Ring, src/kernels.cu:755-868
+ * k_ring, fp32 payload), over memory the GPUs of one box can read and write directly:
+ *   slot[p][r]  GPU r's slot of parity p (rows * row_len floats), as addressed from this GPU
+ *   pad[r]      GPU r's flag words (nrank of them, zeroed once), as addressed from this GPU
+ *   state       three words of this GPU's own memory, zeroed once
+ *   spin_limit  polls a wait may take before it gives up and sets bit 1 of *err
+ * x is summed in place; every GPU gets the same bits.  Capture-safe; nrank == 1 does nothing. */
+enum { FNX_RING_MAX = 8 };
+typedef struct FnxRing {
+    int nrank, rank;
+    float* slot[2][FNX_RING_MAX];
+    unsigned* pad[FNX_RING_MAX];
+    unsigned* state;
+    unsigned spin_limit;
+} FnxRing;
+int fnx_ring_sum(float* x, int rows, int row_len, const FnxRing* ring, unsigned* err, void* st);
+
 /* ---- head */
 /* reference src/kernels.hpp:384 argmax (src/kernels.cu:870-908); keys: FNX_MAXT words zeroed once */
 int fnx_argmax(const float* logits, int rows, int T, int v0, float* best_v, int* best_i, unsigned long long* keys, unsigned* err,

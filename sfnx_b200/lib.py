@@ -64,6 +64,14 @@ class Sampling(C.Structure):
     _fields_ = [("temperature", C.c_float), ("top_p", C.c_float), ("min_p", C.c_float), ("top_k", C.c_int)]
 
 
+RING_MAX = 8
+
+
+class Ring(C.Structure):
+    _fields_ = [("nrank", C.c_int), ("rank", C.c_int), ("slot", (C.c_void_p * RING_MAX) * 2), ("pad", C.c_void_p * RING_MAX),
+                ("state", C.c_void_p), ("spin_limit", C.c_uint)]
+
+
 class CopyJob(C.Structure):
     _fields_ = [("dst", C.c_void_p), ("src", C.c_void_p), ("bytes", C.c_size_t)]
 
@@ -103,6 +111,7 @@ _SIGS = {
     "fnx_window_stage": [_p, _p, _p, _p, _i, _i, _p],
     "fnx_window_commit": [_p, _p, _p, _i, _i, _i, _p, _p],
     "fnx_top_merge": [_p, _p, _i, _i, _p, _p],
+    "fnx_ring_sum": [_p, _i, _i, C.POINTER(Ring), _p, _p],
 }
 _OTHER = {
     "fnx_last_error": (C.c_char_p, []),

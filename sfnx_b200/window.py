@@ -7,6 +7,8 @@ docs/config.md:62-71): experts by FF width in 32-value blocks, DeltaNet by value
 the vocabulary in contiguous ranges; the router, the norms and the embeddings are copied.
 """
 import ctypes as C
+import os
+import sys
 from dataclasses import dataclass, field
 
 import torch
@@ -308,6 +310,12 @@ class WindowRunner:
             self.all_ci = torch.zeros((stack.ncard, T, L.TOPK_N), dtype=torch.int32, device=stack.dev)
             self.h_cv = torch.zeros((stack.ncard, T, L.TOPK_N), dtype=torch.float32).pin_memory()
             self.h_ci = torch.zeros((stack.ncard, T, L.TOPK_N), dtype=torch.int32).pin_memory()
+        # the sum across GPUs after each half layer: the library's own peer-memory sum in the reference ring's order
+        # (fnx_ring_sum) over torch's symmetric memory, or NCCL's all-reduce (FNX_RING=nccl, or when peer memory cannot
+        # be set up)
+        self.ring = None
+        if self.dist is not None and os.environ.get("FNX_RING", "peer") != "nccl":
+            self.ring = self._make_ring(T * s.n)
         self.job_bytes = len(s.kinds) * 2 * C.sizeof(L.CopyJob)
         self.h_jobs = torch.zeros(64 * self.job_bytes, dtype=torch.uint8).pin_memory()   # a ring of job tables
         self.commits = 0
@@ -329,6 +337,38 @@ class WindowRunner:
                 self.graph = g
         torch.cuda.synchronize()
 
+    def _make_ring(self, count):
+        """Two slots of `count` floats and 64 flag words that every GPU of the group can address, and this GPU's view of
+        them (FnxRing).  Returns None (NCCL is used) when symmetric memory is not available."""
+        try:
+            import torch.distributed._symmetric_memory as symm
+
+            group = self.group if self.group is not None else self.dist.group.WORLD
+            if hasattr(symm, "enable_symm_mem_for_group"):
+                try:
+                    symm.enable_symm_mem_for_group(group.group_name)
+                except Exception:   # newer releases need no enabling
+                    pass
+            buf = symm.empty(2 * count + 64, dtype=torch.float32, device=self.stack.dev)
+            buf.zero_()
+            torch.cuda.synchronize()
+            hdl = symm.rendezvous(buf, group)
+            ptrs = [int(p) for p in hdl.buffer_ptrs]
+            self.dist.barrier(group=self.group)   # every slot and flag is zero before anyone can signal
+        except Exception as e:   # noqa: BLE001
+            sys.stderr.write("peer-memory ring not available (%s): sums across GPUs go through NCCL\n" % (e,))
+            return None
+        ring = L.Ring()
+        ring.nrank, ring.rank = self.stack.ncard, self.stack.card
+        for r in range(self.stack.ncard):
+            ring.slot[0][r], ring.slot[1][r] = ptrs[r], ptrs[r] + count * 4
+            ring.pad[r] = ptrs[r] + 2 * count * 4
+        self.ring_state = torch.zeros(4, dtype=torch.int32, device=self.stack.dev)
+        ring.state = self.ring_state.data_ptr()
+        ring.spin_limit = 1 << 20   # about a second of polling before a missing peer is reported
+        self.ring_keep = (buf, hdl)
+        return ring
+
     def _enqueue(self):
         st, stack, T = torch.cuda.current_stream().cuda_stream, self.stack, self.T
         if self.side is not None:
@@ -341,7 +381,10 @@ class WindowRunner:
             if self.dist is None:
                 continue
             if self.after[i] == 1:
-                self.dist.all_reduce(self.bo, group=self.group)
+                if self.ring is not None:
+                    L.call("fnx_ring_sum", self.bo.data_ptr(), T, stack.shape.n, C.byref(self.ring), self.err.data_ptr(), st)
+                else:
+                    self.dist.all_reduce(self.bo, group=self.group)
             elif self.after[i] == 2:
                 per = self.partials.numel() // stack.ncard
                 self.dist.all_gather_into_tensor(self.partials, self.partials[stack.card * per:(stack.card + 1) * per], group=self.group)
