@@ -95,20 +95,50 @@ def algorithmic_bytes(shape, distinct_experts, ctx):
     return b
 
 
+def workload_config(shape, kinds, ctx, world):
+    """The `config` object of the result line: the same for this arm and for the CPU arm."""
+    b = algorithmic_bytes(shape, 0, ctx)
+    experts_all = shape.nexp * (b["moe_gate_up"] + b["moe_down"])
+    resident = (len(kinds) * (experts_all + b["router"] + b["shared"]) + kinds.count(0) * (b["qkvz"] + b["ssm_out"] + b["gdn_core"]) +
+                kinds.count(1) * (b["wq"] + b["wkv"] + b["wo"] + b["attn_kv"]) + b["head"])
+    d_exp = shape.nexp * (1.0 - (1.0 - shape.topk / shape.nexp) ** 16)   # expected distinct experts of 16 rows
+    window = (len(kinds) * (d_exp * (b["moe_gate_up"] + b["moe_down"]) + b["router"] + b["shared"]) +
+              kinds.count(0) * (b["qkvz"] + b["ssm_out"] + b["gdn_core"]) + kinds.count(1) * (b["wq"] + b["wkv"] + b["wo"] + b["attn_kv"]) + b["head"])
+    return {"workload": "cfg2: %d-layer stack (%d DeltaNet + %d attention), batch 1, ctx %d, T=16 rows (1 committed + 15 drafts), "
+                        "greedy acceptance, Bernoulli(0.8) drafts" % (len(kinds), kinds.count(0), kinds.count(1), ctx),
+            "hidden": shape.n, "experts": shape.nexp, "expert_type": shape.experts, "topk": shape.topk, "ff": shape.ff, "vocab": shape.vocab,
+            "l2": "inputs larger than L2, no flush: %.1f GB of weights, state and K/V resident, about %.1f GB of them read per window "
+                  "(126 MB of L2)" % (resident / 1e9, window / 1e9),
+            "parallelism": "tp%d (FF blocks / value heads / KV positions / vocabulary)" % world}
+
+
+_REAL_STDOUT = None
+
+
+def emit(line):
+    """The result line, on the process's original stdout."""
+    os.write(_REAL_STDOUT if _REAL_STDOUT is not None else 1, (line + "\n").encode())
+
+
 def main():
     args = parse()
     import numpy as np
     import torch
     import torch.distributed as dist
 
-    os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")   # NCCL's version / debug lines stay off stdout: one JSON line there
+    # stdout carries the one JSON line and nothing else: whatever libraries print there (NCCL's version line) goes to
+    # stderr, and the line is written to the saved descriptor at the end
+    global _REAL_STDOUT
+    sys.stdout.flush()
+    _REAL_STDOUT = os.dup(1)
+    os.dup2(2, 1)
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
         import bench_reference
 
-        return bench_reference.main(args, rank, world)
+        return bench_reference.main(args, rank, world, emit, workload_config)
     assert world == args.gpus, "launch with torch.distributed.run --nproc-per-node %d for --gpus %d" % (args.gpus, args.gpus)
     torch.cuda.set_device(local)
     group = None
@@ -274,11 +304,7 @@ def main():
         "metric": "accepted tok/s @ draft len 16", "value": round(accepted / (dev_ms * 1e-3), 2), "unit": "tok/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(dev_ms / args.steps, 4), "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "int8 x int4/int6/int8 dot products, f32 accumulate", "data": "synthetic",
-        "config": {"workload": "cfg2: %d-layer stack (%d DeltaNet + %d attention), batch 1, ctx %d, T=16 rows (1 committed + 15 drafts), "
-                               "greedy acceptance, Bernoulli(0.8) drafts" % (len(kinds), kinds.count(0), kinds.count(1), args.ctx),
-                   "hidden": shape.n, "experts": shape.nexp, "expert_type": shape.experts, "topk": shape.topk, "ff": shape.ff, "vocab": shape.vocab,
-                   "l2": "inputs larger than L2: %.1f GB of weights and K/V streamed per window" % (stack.weight_bytes() / 1e9),
-                   "parallelism": "tp%d (FF blocks / value heads / KV positions / vocabulary)" % world},
+        "config": workload_config(shape, kinds, args.ctx, world),
         "accepted_per_window": round(accepted / args.steps, 3),
         "e2e": {"value": round(e2e_accepted / (e2e_ms * 1e-3), 2), "unit": "tok/s", "ms_per_step": round(e2e_ms / args.steps, 4),
                 "h2d_bytes_per_step": runner.h2d_bytes + runner.job_bytes, "d2h_bytes_per_step": runner.d2h_bytes},
@@ -290,7 +316,7 @@ def main():
 
         result["cpu_baseline"] = bench_reference.cpu_baseline(stack, runner, rec[args.warmup], shape, accepted / args.steps)
     if rank == 0:
-        print(json.dumps(result))
+        emit(json.dumps(result))
     sys.stdout.flush()
     if world > 1:
         # leave without tearing the communicator down: its destruction can wait for ever on the captured graphs' kernels

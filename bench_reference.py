@@ -103,7 +103,7 @@ def cpu_baseline(stack, runner, step, shape, accepted_per_window):
             "window_s": round(w, 3), "pieces_s": {k: round(v, 4) for k, v in t.items()}}
 
 
-def main(args, rank, world):
+def main(args, rank, world, emit=print, workload_config=None):
     """`bench.py --impl reference`: rank 0 alone runs (the other ranks exit 0 without work)."""
     if rank != 0:
         return 0
@@ -127,12 +127,11 @@ def main(args, rank, world):
             times.append(window_seconds(t, full.kinds))
     w = sum(times) / len(times)
     val = round(accepted / w, 4)
-    print(json.dumps({
+    emit(json.dumps({
         "impl": "reference", "metric": "accepted tok/s @ draft len 16", "value": val, "unit": "tok/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(w * 1e3, 2), "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "int8 x int4/int6/int8 dot products, f32 accumulate", "data": "synthetic",
-        "config": {"workload": "cfg2: %d-layer stack (%d DeltaNet + %d attention), batch 1, ctx %d, T=16 rows, greedy acceptance, "
-                               "expected %.2f tokens per window" % (len(kinds), kinds.count(0), kinds.count(1), args.ctx, accepted)},
+        "config": workload_config(full, kinds, args.ctx, max(1, args.gpus)),
         "cpu_baseline": {"value": val, "unit": "tok/s", "cores": cores, "kind": "port",
                          "sample": "each step: CPU oracle on one FFN half, one DeltaNet mixer, one attention mixer and the head, scaled "
                                    "by the layer counts"},

@@ -344,11 +344,6 @@ class WindowRunner:
             import torch.distributed._symmetric_memory as symm
 
             group = self.group if self.group is not None else self.dist.group.WORLD
-            if hasattr(symm, "enable_symm_mem_for_group"):
-                try:
-                    symm.enable_symm_mem_for_group(group.group_name)
-                except Exception:   # newer releases need no enabling
-                    pass
             buf = symm.empty(2 * count + 64, dtype=torch.float32, device=self.stack.dev)
             buf.zero_()
             torch.cuda.synchronize()
