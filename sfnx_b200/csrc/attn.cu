@@ -232,8 +232,8 @@ int fnx_attn_prep_append(float* qg, float* k, const float* v, const float* q_nor
 }
 
 size_t fnx_attn_scratch_floats(int nq, int hd, int T) {   // the larger of the exact scan's 16 splits and the fast scan's (at most 148)
-    const size_t exact = (size_t) T * nq * ATT_SPLITS * (hd + 2), fast = (size_t) T * nq * 148 * (hd + 2);
-    return exact > fast ? exact : fast;
+    const size_t exact = (size_t) T * nq * ATT_SPLITS * (hd + 2), fast = (size_t) T * nq * 148 * (hd + 2) + (size_t) 8 * 32768;
+    return exact > fast ? exact : fast;   // fast: at most 148 splits' partials, then the queries' tensor-core image (8 KV heads)
 }
 
 int fnx_attn_partial_exact(const float* qg, const uint16_t* kc, const uint16_t* vc, FnxKvPages g, float* part, int card, int ncard, int T,

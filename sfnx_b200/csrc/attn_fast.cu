@@ -8,8 +8,11 @@
 // scratch and a second kernel merges the splits into the per-GPU partial the cross-GPU merge takes.
 // The sums are not in the reference's order (src/kernels.cu:497-606): results agree with the exact-order scan to f32
 // rounding, not bit for bit.
+#include <cstdlib>
+
 #include "common.cuh"
 #include "exact_math.cuh"
+#include "moe_internal.cuh"
 
 namespace fnxk {
 
@@ -273,6 +276,17 @@ int fnx_attn_partial(const float* qg, const uint16_t* kc, const uint16_t* vc, Fn
     FNX_REQUIRE(nkv >= 1 && nq % nkv == 0 && T * (nq / nkv) <= 128, "attn: %d query heads over %d KV heads, %d rows", nq, nkv, T);
     FNX_REQUIRE(ncard >= 1 && card >= 0 && card < ncard, "attn: GPU %d of %d", card, ncard);
     const int M = T * (nq / nkv), Mpad = (M + 15) / 16 * 16, nsplit = fnx_attn_splits(nkv);
+    // head dimension 256: S = Q K^T on tcgen05 with the scores in tensor memory (attn_umma.cu); FNX_ATTN_MMA=1 keeps the
+    // mma.sync scan below, which also serves the other shapes
+    static const bool legacy = getenv("FNX_ATTN_MMA") != nullptr;
+    if (hd == 256 && !legacy) {
+        const int rc = attn_umma_launch(qg, kc, vc, g, scratch, card, ncard, T, pos0, nq, nkv, nsplit, strm(st));
+        if (rc > 0) return 1;
+        if (rc == 0) {
+            launch(0, k_attn_fast_merge, dim3(nq, T), hd, 0, strm(st), scratch, part, nq, nkv, T, nsplit, hd);
+            return launch_ok("attn merge");
+        }
+    }
     AfArgs a{qg, kc, vc, g, scratch, nq, nkv, T, card, ncard, nsplit, pos0};
     const int LD = hd + AF_PAD;
     const int stages = ((size_t) (2 * Mpad + 3 * 2 * AF_CH) * LD * 2 <= 227 * 1024) ? 3 : 2;

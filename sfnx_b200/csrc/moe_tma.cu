@@ -156,6 +156,14 @@ int gu_q4k_tma_launch(const uint8_t* A, size_t sa, int nrows, int n, const FnxJo
     return launch_ok("moe gate|up q4_K (staged)");
 }
 
+unsigned* device_fault_word() {
+    static unsigned* ptr[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    if (!ptr[dev] && cudaGetSymbolAddress((void**) &ptr[dev], g_fault) != cudaSuccess) ptr[dev] = nullptr;
+    return ptr[dev];
+}
+
 }  // namespace fnxk
 
 extern "C" unsigned fnx_device_fault(void) {
