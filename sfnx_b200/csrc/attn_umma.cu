@@ -125,21 +125,36 @@ __global__ void __launch_bounds__(AU_THREADS) k_attn_umma(const AuArgs a) {
         for (int i = tid; i < M * (HD + 2); i += nthreads) out[i] = (i % (HD + 2)) == HD ? -INFINITY : 0.f;
         return;
     }
-    // ---- the copies: a thread always moves the same 16-byte column piece (seg) of rows warp, warp + 8, .. of a chunk
+    // ---- the copies: a thread always moves the same 16-byte column piece (seg) of rows warp, warp + 8, .. of a chunk, so
+    // its shared-memory offsets are fixed and (without a page table) its global addresses advance by a constant
     const int seg = lane, rowb = warp;
-    auto load_rows = [&](const uint16_t* cache, int c, unsigned char* dst_base, bool swizzled) {
+    const size_t row_elems = (size_t) a.nkv * HD;
+    unsigned kdst[AU_CH / 8], vdst[AU_CH / 8];
+#pragma unroll
+    for (int k = 0; k < AU_CH / 8; ++k) {
+        const int row = rowb + 8 * k;
+        kdst[k] = (seg >> 3) * (AU_CH * 128) + row * 128 + (((seg & 7) ^ (row & 7)) << 4);
+        vdst[k] = row * AU_LDV * 2 + seg * 16;
+    }
+    auto load_rows = [&](const uint16_t* cache, int c, unsigned dst_base, const unsigned (&dst)[AU_CH / 8]) {
+        if (!a.g.pt && (c + 1) * AU_CH <= ctx_max) {   // a whole chunk of contiguous rows
+            const uint16_t* src = cache + ((size_t) c * AU_CH + rowb) * row_elems + (size_t) kvl * HD + seg * 8;
+#pragma unroll
+            for (int k = 0; k < AU_CH / 8; ++k)
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst_base + dst[k]), "l"(src + (size_t) 8 * k * row_elems));
+            return;
+        }
 #pragma unroll
         for (int k = 0; k < AU_CH / 8; ++k) {
-            const int row = rowb + 8 * k, pos = c * AU_CH + row;
+            const int pos = c * AU_CH + rowb + 8 * k;
             const bool valid = pos < ctx_max;
             const uint16_t* src = cache + au_row_at(a.g, valid ? pos : 0, a.nkv) + (size_t) kvl * HD + seg * 8;
-            unsigned char* dst = swizzled ? dst_base + (seg >> 3) * (AU_CH * 128) + row * 128 + (((seg & 7) ^ (row & 7)) << 4)
-                                          : dst_base + (size_t) row * AU_LDV * 2 + seg * 16;
-            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(au_s32(dst)), "l"(src), "r"(valid ? 16 : 0));   // invalid rows: zeros
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst_base + dst[k]), "l"(src), "r"(valid ? 16 : 0));   // invalid rows: zeros
         }
     };
-    auto load_k = [&](int c, int stage) { load_rows(a.kc, c, Kst + (size_t) stage * AU_KBYTES, true); };
-    auto load_v = [&](int c, int stage) { load_rows(a.vc, c, reinterpret_cast<unsigned char*>(Vst) + (size_t) stage * AU_VBYTES, false); };
+    const unsigned ks_s = au_s32(Kst), vs_s = au_s32(Vst);
+    auto load_k = [&](int c, int stage) { load_rows(a.kc, c, ks_s + stage * AU_KBYTES, kdst); };
+    auto load_v = [&](int c, int stage) { load_rows(a.vc, c, vs_s + stage * AU_VBYTES, vdst); };
     load_k(c_begin, 0);
     load_v(c_begin, 0);
     if (nc > 1) load_k(c_begin + 1, 1);
