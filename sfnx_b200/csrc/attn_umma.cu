@@ -417,7 +417,6 @@ __global__ void __launch_bounds__(AU_THREADS) k_attn_umma2(const AuArgs a) {
     load_k(0);
     load_v(0);
     if (nc > 1) load_k(1);
-    if (nc > 2) load_k(2);
     {   // the queries' image, made by k_attn_qsplit
         const unsigned char* img = a.qsplit + (size_t) kvl * 2 * AU_QBYTES;
         for (int i = tid; i < 2 * AU_QBYTES / 16; i += nthreads)
@@ -472,28 +471,24 @@ __global__ void __launch_bounds__(AU_THREADS) k_attn_umma2(const AuArgs a) {
     };
     asm volatile("cp.async.wait_group 0;" ::: "memory");
     sync_all();
-    // The tensor core runs two chunks ahead of the row warps: S(c) is issued at the end of chunk c - 2, so that K(c), copied
-    // at chunk c - 3, has had two chunks' time to arrive, and the 32 MMAs of a score tile overlap the row warps' work.
     const bool issuer = tid == 3 * 32;   // warp 3, lane 0
-    if (issuer) {
-        issue_scores(0);
-        if (nc > 1) issue_scores(1);
-    }
+    if (issuer) issue_scores(0);
     bool alive = true;   // false after a wait ran out
 #pragma unroll 1
     for (int i = 0; i < nc; ++i) {
         const int buf = i & 1;
+        if (i + 2 < nc) load_k(i + 2);   // its stage held chunk i - 1, whose scores were read a chunk ago
+        asm volatile("cp.async.commit_group;");
+        if (issuer && i + 1 < nc) issue_scores(i + 1);   // the next chunk's scores while this chunk's are used
         float sacc[4][4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) sacc[j][0] = sacc[j][1] = sacc[j][2] = sacc[j][3] = -INFINITY;
-        if (worker || copier) {
-            bool ok = alive && au_wait(&mbar_s[buf], (i >> 1) & 1, a.fault);   // S(i) is complete: K(i)'s stage is free
+        if (worker) {
+            bool ok = alive && au_wait(&mbar_s[buf], (i >> 1) & 1, a.fault);
             ok = __all_sync(0xffffffffu, ok);
             alive = alive && ok;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            if (i + 3 < nc) load_k(i + 3);
-            asm volatile("cp.async.commit_group;");
-            if (ok && worker) {
+            if (ok) {
                 unsigned r[16];
                 asm volatile("tcgen05.ld.sync.aligned.16x256b.x4.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
                              : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
@@ -590,14 +585,10 @@ __global__ void __launch_bounds__(AU_THREADS) k_attn_umma2(const AuArgs a) {
             z0 = z0 * f0 + ps0;
             z1 = z1 * f1 + ps1;
         }
-        // ---- P is written, V(i) and K(i + 2) (copied a chunk ago) have landed: this chunk's output MMAs, then the scores
-        // of the chunk after the next
-        asm volatile("cp.async.wait_group 2;" ::: "memory");   // all but K(i + 3) and V(i + 1), just asked for
+        // ---- P is written, V(i) (copied a chunk ago) and K(i + 1) have landed: the output MMAs of this chunk
+        asm volatile("cp.async.wait_group 1;" ::: "memory");   // all but V(i + 1), just asked for
         sync_all();
-        if (issuer) {
-            issue_output(i);
-            if (i + 2 < nc) issue_scores(i + 2);
-        }
+        if (issuer) issue_output(i);
     }
     // ---- this split's partial: the accumulator out of tensor memory, m_ref, z per row
     {

@@ -102,9 +102,10 @@ def gdn_oracle(c):
 
 
 # ---------------------------------------------------------------- attention
-def attn_case(T, ctx, nq=24, nkv=4, hd=256, ncard=1, seed=0):
+def attn_case(T, ctx, nq=24, nkv=4, hd=256, ncard=1, seed=0, ramp=None):
     """A K/V cache of ctx positions N(0, 1) rounded to f16, split by position over ncard GPUs, and a window of T rows at
-    positions ctx .. ctx + T - 1."""
+    positions ctx .. ctx + T - 1.  With `ramp` the cached keys grow from 0.5x at position 0 to ramp x at the last one, so
+    that a row's largest score keeps rising along the scan."""
     rng = np.random.default_rng(seed)
     c = {"T": T, "ctx": ctx, "nq": nq, "nkv": nkv, "hd": hd, "ncard": ncard, "pos0": ctx}
     c["qg"] = rng.standard_normal((T, nq, 2 * hd)).astype(np.float32)
@@ -113,7 +114,10 @@ def attn_case(T, ctx, nq=24, nkv=4, hd=256, ncard=1, seed=0):
     c["qn"] = (1 + 0.1 * rng.standard_normal(hd)).astype(np.float32)
     c["kn"] = (1 + 0.1 * rng.standard_normal(hd)).astype(np.float32)
     rows = ((ctx + T + 3) // 4 + ncard - 1) // ncard * 4
-    full_k = rng.standard_normal((ctx, nkv, hd)).astype(np.float16)
+    full_k = rng.standard_normal((ctx, nkv, hd))
+    if ramp is not None:
+        full_k *= np.linspace(0.5, ramp, ctx)[:, None, None]
+    full_k = full_k.astype(np.float16)
     full_v = rng.standard_normal((ctx, nkv, hd)).astype(np.float16)
     c["kc"], c["vc"] = [], []
     for card in range(ncard):

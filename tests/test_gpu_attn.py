@@ -71,3 +71,18 @@ def test_attention_fast_scan(T, ctx, ncard, hd):
         zr, zg = ref["part"][card][..., hd + 1], got["part"][card][..., hd + 1]
         mr, mg = ref["part"][card][..., hd], got["part"][card][..., hd]
         assert np.allclose(zg * np.exp(mg - mr), zr, rtol=1e-4)
+
+
+@pytest.mark.parametrize("T,ctx,ramp", [(16, 3000, 8.0), (16, 700, 20.0), (3, 5000, 12.0)])
+def test_attention_fast_scan_rising_scores(T, ctx, ramp):
+    """Keys that grow along the cache: every row's largest score rises by far more than the scan's rescaling threshold
+    between the first and the last chunk, so the accumulated output is rescaled several times on the way."""
+    c = cases.attn_case(T=T, ctx=ctx, seed=90 + T, ramp=ramp)
+    ref = cases.attn_oracle(c)
+    got = _run(c, "fnx_attn_partial")
+    assert np.isfinite(got["out"]).all()
+    assert (ref["part"][0][..., 256] > 16).all(), "the case does not reach the rescaling path"
+    # scores reach 30 to 70 here, where one f32 rounding of a score moves its weight by 4e-6 relative: the bound is
+    # stated against the largest output, 2e-5 of it
+    err, top = np.abs(got["out"] - ref["out"]), np.abs(ref["out"]).max()
+    assert err.max() <= 2e-5 * top, (err.max(), top)
