@@ -37,6 +37,15 @@ typedef struct FnxJob {
     int out[FNX_MAXT]; /* output rows */
 } FnxJob;
 
+/* the prompt path's expert jobs, up to FNX_PF_JOB rows of one expert: reference src/kernels.hpp:25-32 (PF_JOB, BigJob) */
+#define FNX_PF_JOB 64
+typedef struct FnxBigJob {
+    int w;               /* expert */
+    int n;               /* rows of the job */
+    int y[FNX_PF_JOB];   /* activation rows */
+    int out[FNX_PF_JOB]; /* output rows */
+} FnxBigJob;
+
 /* a Q8_0 matrix in the split layout: int8 values [rows][cols], f16 scales [rows][cols / 32]
  * (reference src/model.hpp:71-87, Q8S) */
 typedef struct FnxQ8S {
@@ -136,6 +145,18 @@ int fnx_moe_down(const FnxExperts* A, const FnxJob* jobs, const int* njobs, int 
 #define FNX_DOWN_NOALLOC_BYTES (288 * 1024) /* 256 pairs x ff 1024: 256 KiB of int8 h + 32 KiB of scales */
 int fnx_moe_down_noalloc(const FnxExperts* A, const FnxJob* jobs, const int* njobs, int njobs_max, const float* gu, int npairs,
                          float* part, void* st);
+/* ---- routed experts over many rows, on the tensor cores (the reference's prompt path)
+ * reference src/kernels.hpp:289-292 moe_gate_up_mma, swiglu_h16, moe_down_mma (src/moe_mma.cu:28-59, src/moe_mma.cuh:63-388):
+ * out[jobs[j].out[s]][r] = sum_k f16(W_e[r][k]) * x[jobs[j].y[s]][k] for every job j < *njobs (device) and row s of it; every
+ * weight dequantised to f16 with one rounding (Q4_K: q * f16(d sc) - f16(dmin m) as one half fma; Q8_0: q * d; Q6_K in
+ * 32-column units: (q - 32) * f16(d sc)), x rows of A->ncols f16 values, fp32 sums on tcgen05 tensor cores (the order
+ * of a sum's terms is the hardware's).  A->ncols in units of 32.  njobs_cap: the most jobs there can be (grid rows). */
+int fnx_moe_gate_up_mma(const FnxExperts* A, const FnxBigJob* jobs, const int* njobs, int njobs_cap, const uint16_t* xh, float* gu,
+                        void* st);
+/* h16[p][i] = f16(silu(gu[p][i]) * gu[p][ffs + i]) for P rows of [gate | up] */
+int fnx_swiglu_h16(const float* gu, int ffs, int P, uint16_t* h16, void* st);
+int fnx_moe_down_mma(const FnxExperts* A, const FnxBigJob* jobs, const int* njobs, int njobs_cap, const uint16_t* h16, float* part,
+                     void* st);
 /* reference src/kernels.hpp:307 swiglu_stacked_q8_1 + src/dense.cuh:162-198 (the shared expert): T rows of
  * [gate | up] -> h as int8 + f16-rounded scales, then the Q8_0 down into out[t][n] */
 int fnx_shared_expert(FnxQ8S gate_up, FnxQ8S down, const void* xq, int T, int n, int ffs, float* sh_gu, void* hq, float* out,

@@ -23,6 +23,10 @@ class Job(C.Structure):
 JOB_DTYPE = np.dtype([("w", "<i4"), ("n", "<i4"), ("y", "<i4", (MAXT,)), ("out", "<i4", (MAXT,))])
 
 
+PF_JOB = 64
+BIGJOB_DTYPE = np.dtype([("w", "<i4"), ("n", "<i4"), ("y", "<i4", (PF_JOB,)), ("out", "<i4", (PF_JOB,))])
+
+
 class KvPages(C.Structure):
     _fields_ = [("pt", C.c_void_p), ("page", C.c_size_t), ("rows", C.c_int)]
 
@@ -198,6 +202,43 @@ def moe_down_q8(wq, wd, jobs, njobs, gu, nout):
     lib().orc_moe_down_q8(P(wq), C.c_size_t(nrows * ffs), P(wd), C.c_size_t(nrows * ffs // 32), P(jobs), njobs, P(_f32(gu)),
                           P(part), nrows, ffs)
     return part
+
+
+def mma_weights_q4k(A, rows, n):
+    """f16 weights (bit patterns) of `rows` Q4_K rows of n columns, several experts stacked as rows."""
+    w = np.zeros((rows, n), np.uint16)
+    lib().orc_mma_weights_q4k(P(A), rows, n, P(w))
+    return w
+
+
+def mma_weights_q8(wq, wd):
+    rows, n = wq.reshape(-1, wq.shape[-1]).shape
+    w = np.zeros((rows, n), np.uint16)
+    lib().orc_mma_weights_q8(P(wq), P(wd), rows, n, P(w))
+    return w
+
+
+def mma_weights_q6p(planes, rows, n):
+    QL, QH, SC, D = planes
+    w = np.zeros((rows, n), np.uint16)
+    lib().orc_mma_weights_q6p(P(QL), P(QH), P(SC), P(D), rows, n, P(w))
+    return w
+
+
+def moe_mma(w, jobs, njobs, x, nrows, nout):
+    """w: f16 bits [experts * nrows][n]; x: f16 bits [rows][n]; returns (sums, sums of |products|) as float64 [nout][nrows]."""
+    n = w.shape[-1]
+    out = np.zeros((nout, nrows), np.float64)
+    mag = np.zeros((nout, nrows), np.float64)
+    lib().orc_moe_mma(P(w), P(jobs), njobs, P(x), nrows, n, P(out), P(mag))
+    return out, mag
+
+
+def swiglu_h16(gu, ffs):
+    gu = _f32(gu)
+    h = np.zeros((gu.shape[0], ffs), np.uint16)
+    lib().orc_swiglu_h16(P(gu), ffs, gu.shape[0], P(h))
+    return h
 
 
 def shared_expert(guq, gud, dnq, dnd, xq, T):

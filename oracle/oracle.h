@@ -23,6 +23,14 @@ typedef struct { /* reference src/kernels.hpp:18-23 */
     int out[ORC_MAXT];
 } OrcJob;
 
+#define ORC_PF_JOB 64
+typedef struct { /* reference src/kernels.hpp:25-32 (BigJob): up to 64 rows of one expert */
+    int w;
+    int n;
+    int y[ORC_PF_JOB];
+    int out[ORC_PF_JOB];
+} OrcBigJob;
+
 typedef struct { /* reference src/kernels.hpp:160-165; pt null: one contiguous run of local rows */
     const int* pt;
     size_t page; /* halves per page */
@@ -74,6 +82,12 @@ void orc_shared_expert(const int8_t* guq, const o_half* gud, const int8_t* dnq, 
                        int n, int ffs, float* sh_gu, float* out);
 void orc_moe_combine(const float* part, const float* topw, const float* sh, const float* logits, int logit_stride, int sh_col,
                      float* out, int T, int n, int topk);
+/* the prompt path's experts: f16 weights with one rounding, sums in double (omma.c) */
+void orc_mma_weights_q4k(const uint8_t* A, int rows, int n, o_half* w);
+void orc_mma_weights_q8(const int8_t* wq, const o_half* wd, int rows, int n, o_half* w);
+void orc_mma_weights_q6p(const uint8_t* QL, const uint8_t* QH, const int8_t* SC, const o_half* D, int rows, int n, o_half* w);
+void orc_moe_mma(const o_half* w, const OrcBigJob* jobs, int njobs, const o_half* x, int nrows, int n, double* out, double* mag);
+void orc_swiglu_h16(const float* gu, int ffs, int P, o_half* h);
 void orc_rms_norm_rows(const float* x, const float* w, float* y, int rows, int n, float eps);
 
 /* Gated DeltaNet */

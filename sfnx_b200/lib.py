@@ -88,6 +88,9 @@ _SIGS = {
     "fnx_router_route": [_p, _p, _p, _i, _i, _i, _i, _p, _p, _p, _p, _p, _p, _p],
     "fnx_moe_gate_up": [C.POINTER(Experts), _p, _p, _i, _p, _p, _p],
     "fnx_moe_down": [C.POINTER(Experts), _p, _p, _i, _p, _i, _p, _p, _p],
+    "fnx_moe_gate_up_mma": [C.POINTER(Experts), _p, _p, _i, _p, _p, _p],
+    "fnx_swiglu_h16": [_p, _i, _i, _p, _p],
+    "fnx_moe_down_mma": [C.POINTER(Experts), _p, _p, _i, _p, _p, _p],
     "fnx_moe_down_noalloc": [C.POINTER(Experts), _p, _p, _i, _p, _i, _p, _p],
     "fnx_shared_expert": [Q8S, Q8S, _p, _i, _i, _i, _p, _p, _p, _p],
     "fnx_moe_combine": [_p, _p, _p, _p, _i, _p, _i, _i, _i, _p],

@@ -50,6 +50,23 @@ def moe_weights_q8(n, nexp, ffs, seed=0, sigma=0.02):
     return w
 
 
+def big_jobs(ntok, nexp, topk, seed=0, cap=64):
+    """The prompt path's jobs: every token picks topk distinct experts, pair p = t topk + k; an expert's pairs in pair
+    order, cut into jobs of at most `cap` rows (reference src/kernels.hpp:25-32).  Returns (jobs, pairs)."""
+    rng = np.random.default_rng(seed)
+    picks = np.stack([rng.permutation(nexp)[:topk] for _ in range(ntok)])
+    jobs = []
+    for e in range(nexp):
+        t, k = np.nonzero(picks == e)
+        for i in range(0, len(t), cap):
+            jobs.append((e, t[i:i + cap], t[i:i + cap] * topk + k[i:i + cap]))
+    out = np.zeros(len(jobs), O.BIGJOB_DTYPE)
+    for j, (e, y, o) in enumerate(jobs):
+        out[j]["w"], out[j]["n"] = e, len(y)
+        out[j]["y"][:len(y)], out[j]["out"][:len(y)] = y, o
+    return out, ntok * topk
+
+
 def moe_oracle(w, x, topk=10):
     """The whole FFN half on the CPU oracle; returns every intermediate."""
     n, ffs = w["n"], w["ffs"]
