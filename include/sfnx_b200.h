@@ -115,6 +115,10 @@ int fnx_q8s_gemv(FnxQ8S w, int rows, int cols, const void* y, float* out, int ou
  * launch; each output as fnx_q8s_gemv of that matrix alone gives it */
 int fnx_q8s_gemv_segs(const FnxQ8S* w, const int* rows, float* const* out, const int* out_stride, int n, int cols, const void* y, int T,
                       void* st);
+/* reference src/kernels.hpp:369-372 q8s_gemv_f32: fnx_q8s_gemv(w, rows, cols, y, out, rows) and fnx_gemv_f32(W, x, yf, rf, cols)
+ * behind one call, the same values (two launches in stream order here) */
+int fnx_q8s_gemv_f32(FnxQ8S w, int rows, int cols, const void* y, float* out, const float* W, const float* x, float* yf, int rf, int T,
+                     void* st);
 /* reference src/kernels.hpp:49 gemv_f32 (src/kernels.cu:184-227, the block-per-row form): y[t][r] = W[r] . x[t] */
 int fnx_gemv_f32(const float* W, const float* x, float* y, int rows, int n, int T, void* st);
 
@@ -128,6 +132,10 @@ int fnx_router_route(const float* W, const float* x, float* logits, int T, int n
 /* reference src/kernels.hpp:281-282 moe_gate_up (src/moe_q4k.cuh:91-154; src/moe.cuh:258-272): gu[out][2 ffs] =
  * [gate | up] rows of each job's expert over its q8_1 rows of xq (rows of A.ncols) */
 int fnx_moe_gate_up(const FnxExperts* A, const FnxJob* jobs, const int* njobs, int njobs_max, const void* xq, float* gu, void* st);
+/* reference src/kernels.hpp:43-45 mmvq (src/kernels.cu:935-968): out[jobs[j].out[s]][r] = W[jobs[j].w][r] . y[jobs[j].y[s]] over
+ * q8_1 rows y; Q4_K and split-Q8_0 matrices, with fnx_moe_gate_up's arithmetic (the reference's other types run through
+ * ggml's dot products); out_stride = W->nrows */
+int fnx_mmvq(const FnxExperts* W, const FnxJob* jobs, const int* njobs, int njobs_max, const void* y, float* out, int out_stride, void* st);
 /* reference src/kernels.hpp:305 moe_down (src/moe.cuh:284-345): part[out][n] from h = silu(gate) * up of the gu rows.
  * hq: fnx_moe_h_bytes(pairs, ffs) bytes of scratch for the pairs' quantised h (the reference keeps it in a
  * __device__ global, src/moe.cuh:281) */
@@ -172,6 +180,23 @@ size_t fnx_gdn_scratch_floats(int nv);
 int fnx_gdn_core(const float* qkvz, const float* ab, float* hist, const float* convw, const float* dt, const float* a,
                  const float* nw, float* S, void* yq, const int* ctl, float* scratch, float* snap, float* hsnap, int nk, int nv,
                  const int* vmap, int T, float eps, void* st, float* y32);
+/* reference src/kernels.hpp:94-111 GdnLanes, gdn_core_lanes, gdn_core_segs: several sequences ("lanes") in one launch.
+ * Device arrays give segment s's state, conv history (this layer's) and ctl; its rows are window rows row0[s] ..
+ * row0[s] + T - 1 of qkvz, ab and yq, and its snapshots (snap, hsnap as fnx_gdn_core's) are written from window row
+ * row0[s] on.  Each segment's rows chain through its lane's state exactly as a window of T rows on that lane alone.
+ * fnx_gdn_core_lanes: T rows, one lane each (row0 null, no snapshots). */
+typedef struct FnxGdnLanes {
+    float* const* S;
+    float* const* hist;
+    const int* const* ctl;
+    const int* row0;
+    float* snap;
+    float* hsnap;
+} FnxGdnLanes;
+int fnx_gdn_core_segs(const float* qkvz, const float* ab, const float* convw, const float* dt, const float* a, const float* nw, void* yq,
+                      float* scratch, int nk, int nv, const int* vmap, const FnxGdnLanes* gl, int nseg, int T, float eps, void* st);
+int fnx_gdn_core_lanes(const float* qkvz, const float* ab, const float* convw, const float* dt, const float* a, const float* nw, void* yq,
+                       float* scratch, int nk, int nv, const int* vmap, const FnxGdnLanes* gl, int T, float eps, void* st);
 /* reference src/kernels.hpp:380 copy_many (src/kernels.cu:1473-1485): the rollback's batched copies */
 int fnx_copy_many(const FnxCopyJob* jobs, int n, void* st);
 

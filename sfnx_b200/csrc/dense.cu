@@ -794,6 +794,14 @@ int fnx_gemv_f32(const float* W, const float* x, float* y, int rows, int n, int 
     return launch_ok("gemv_f32");
 }
 
+int fnx_q8s_gemv_f32(FnxQ8S w, int rows, int cols, const void* y, float* out, const float* W, const float* x, float* yf, int rf, int T,
+                     void* st) {
+    // the reference fuses the two into one launch to save a launch's latency on a V100; here they are two launches in
+    // stream order (the window itself runs the f32 one on a side stream beside the quantised one), the same values
+    if (fnx_q8s_gemv(w, rows, cols, y, out, rows, T, st)) return 1;
+    return fnx_gemv_f32(W, x, yf, rf, cols, T, st);
+}
+
 int fnx_shared_expert(FnxQ8S gate_up, FnxQ8S down, const void* xq, int T, int n, int ffs, float* sh_gu, void* hq, float* out,
                       void* st) {
     FNX_REQUIRE(ffs > 0 && ffs % 32 == 0 && ((size_t) T * ffs) % 16 == 0, "shared_expert: ff width %d", ffs);

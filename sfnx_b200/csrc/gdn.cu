@@ -30,6 +30,12 @@ struct GdnArgs {
     int T;
     float eps;
     float* y32;
+    // several sequences in one launch (grid row = segment): segment s's state, conv history and ctl, its rows from window
+    // row row0[s] (row s when row0 is null); null lS: one sequence, the fields above
+    float* const* lS;
+    float* const* lhist;
+    const int* const* lctl;
+    const int* row0;
 };
 
 __global__ void __cluster_dims__(GDN_Q, 1, 1) __launch_bounds__(GDN_THREADS, 2) k_gdn_core(const GdnArgs g) {
@@ -37,17 +43,29 @@ __global__ void __cluster_dims__(GDN_Q, 1, 1) __launch_bounds__(GDN_THREADS, 2) 
     const int lv = blockIdx.x / GDN_Q, qq = blockIdx.x % GDN_Q, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int vm = g.vmap[lv], kh = vm & 255, writes_hist = vm >> 8, nk = g.nk, nv = g.nv, T = g.T;
     const int ch = (2 * nk + nv) * HS, row_stride = ch + nv * HS;
+    // a segment's own state, history and rows (the pointer arrays are older than the window)
+    float *S = g.S, *hist = g.hist;
+    const int* ctl = g.ctl;
+    int r0 = 0;
+    if (g.lS) {
+        const int seg = blockIdx.y;
+        S = g.lS[seg], hist = g.lhist[seg], ctl = g.lctl[seg], r0 = g.row0 ? g.row0[seg] : seg;
+    }
+    const float* qkvz = g.qkvz + (size_t) r0 * row_stride;
+    const float* ab = g.ab + (size_t) r0 * 2 * nv;
+    float* snap = g.snap ? g.snap + (size_t) r0 * nv * HS * HS : nullptr;
+    float* hsnap = g.hsnap ? g.hsnap + (size_t) r0 * 3 * ch : nullptr;
     // the state's loads go out first: they depend on no kernel of this window and have the whole prologue to land
     const int part = tid >> 7, cl = (tid >> 2) & 31, j = tid & 3, col = qq * GDN_QC + cl;
-    float* st = g.S + (size_t) lv * HS * HS + (size_t) (part * 32 + j) * HS + col;
+    float* st = S + (size_t) lv * HS * HS + (size_t) (part * 32 + j) * HS + col;
     float s[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) s[i] = __ldcs(st + (size_t) 4 * i * HS);
     pdl_wait();
     pdl_go();
-    const unsigned parity = ((const unsigned*) g.ctl)[1] & 1u;
-    const float* hin = g.hist + (size_t) parity * 3 * ch;
-    float* hout = g.hist + (size_t) (parity ^ 1u) * 3 * ch;
+    const unsigned parity = ((const unsigned*) ctl)[1] & 1u;
+    const float* hin = hist + (size_t) parity * 3 * ch;
+    float* hout = hist + (size_t) (parity ^ 1u) * 3 * ch;
     __shared__ float xs[2][FNX_MAXT][32][4];   // q, k after conv, silu, L2 norm: element i at [i % 32][i / 32]
     __shared__ float vs[FNX_MAXT][GDN_QC];
     __shared__ float gates[FNX_MAXT][2];
@@ -55,7 +73,7 @@ __global__ void __cluster_dims__(GDN_Q, 1, 1) __launch_bounds__(GDN_THREADS, 2) 
     __shared__ float osm[FNX_MAXT][GDN_QC];          // this block's outputs and, per row, their square sum
     __shared__ float sqs[FNX_MAXT];
     if (tid < T) {
-        const float* abt = g.ab + (size_t) tid * 2 * nv;
+        const float* abt = ab + (size_t) tid * 2 * nv;
         const float x = fadd(abt[lv], g.dt[lv]);
         const float sp = x > 20.0f ? x : ex_log1pf_pos(ex_expf(x));
         gates[tid][0] = ex_expf(fmul(sp, g.a[lv]));
@@ -82,7 +100,7 @@ __global__ void __cluster_dims__(GDN_Q, 1, 1) __launch_bounds__(GDN_THREADS, 2) 
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {
                     const int tt = t - 3 + k;
-                    in[m][k] = tt >= 0 ? g.qkvz[(size_t) tt * row_stride + c] : hin[(size_t) (tt + 3) * ch + c];
+                    in[m][k] = tt >= 0 ? qkvz[(size_t) tt * row_stride + c] : hin[(size_t) (tt + 3) * ch + c];
                 }
             }
         }
@@ -100,7 +118,7 @@ __global__ void __cluster_dims__(GDN_Q, 1, 1) __launch_bounds__(GDN_THREADS, 2) 
                 if (pt < 2) xs[pt][t][i % 32][i / 32] = y;
                 else vs[t][i] = y;
                 if (pt == 2 || (writes_hist && qq == 0)) {   // the history if only rows 0..t are kept; after the last row, the new one
-                    float* h = t + 1 < T ? g.hsnap + (size_t) t * 3 * ch : hout;
+                    float* h = t + 1 < T ? hsnap + (size_t) t * 3 * ch : hout;
                     h[c] = in[m][1], h[(size_t) ch + c] = in[m][2], h[(size_t) 2 * ch + c] = in[m][3];
                 }
             }
@@ -148,7 +166,7 @@ __global__ void __cluster_dims__(GDN_Q, 1, 1) __launch_bounds__(GDN_THREADS, 2) 
         aj = fadd(aj, __shfl_xor_sync(0xffffffffu, aj, 2));
         if (j == 0) pa[part][cl] = aj;
         if (t < T - 1) {
-            float* sp = g.snap + (size_t) t * nv * HS * HS + (st - g.S);
+            float* sp = snap + (size_t) t * nv * HS * HS + (st - S);
 #pragma unroll
             for (int i = 0; i < 8; ++i) __stcs(sp + (size_t) 4 * i * HS, s[i]);
         }
@@ -181,12 +199,12 @@ __global__ void __cluster_dims__(GDN_Q, 1, 1) __launch_bounds__(GDN_THREADS, 2) 
         const float ms = fdiv(fadd(fadd(fadd(rsq[0][t], rsq[1][t]), rsq[2][t]), rsq[3][t]), (float) HS);
         const int c = qq * GDN_QC + lane;
         const float v = osm[t][lane];
-        const float z = g.qkvz[(size_t) t * row_stride + ch + lv * HS + c];
+        const float z = qkvz[(size_t) t * row_stride + ch + lv * HS + c];
         const float xi = fdiv(fmul(fmul(v, ex_rsqrt(fadd(ms, g.eps))), g.nw[c]), fadd(1.0f, ex_expf(-z)));
-        if (g.y32) g.y32[(size_t) t * nv * HS + lv * HS + c] = xi;
+        if (g.y32) g.y32[(size_t) (r0 + t) * nv * HS + lv * HS + c] = xi;
         const float amax = wmax(fabsf(xi)), sm = wsum(xi);
         const float d = fdiv(amax, 127.0f);
-        uint8_t* blk = g.yq + ((size_t) t * (nv * HS / 32) + lv * 4 + qq) * 36;
+        uint8_t* blk = g.yq + ((size_t) (r0 + t) * (nv * HS / 32) + lv * 4 + qq) * 36;
         reinterpret_cast<int8_t*>(blk + 4)[lane] = amax == 0.0f ? 0 : (int8_t) roundf(fdiv(xi, d));
         if (lane == 0) {
             reinterpret_cast<uint16_t*>(blk)[0] = f2h(d);
@@ -210,8 +228,26 @@ int fnx_gdn_core(const float* qkvz, const float* ab, float* hist, const float* c
     FNX_REQUIRE(T >= 1 && T <= FNX_MAXT, "gdn_core: T %d outside 1..%d", T, FNX_MAXT);
     FNX_REQUIRE(nk >= 1 && nk <= 255 && nv >= 1, "gdn_core: %d key heads, %d value heads", nk, nv);
     FNX_REQUIRE(T == 1 || (snap && hsnap), "gdn_core: a window of %d rows needs snap and hsnap", T);
-    GdnArgs g{qkvz, ab, hist, convw, dt, a, nw, S, (uint8_t*) yq, ctl, scratch, snap, hsnap, nk, nv, vmap, T, eps, y32};
+    GdnArgs g{qkvz, ab, hist, convw, dt, a, nw, S, (uint8_t*) yq, ctl, scratch, snap, hsnap, nk, nv, vmap, T, eps, y32, nullptr, nullptr, nullptr, nullptr};
     launch(5, k_gdn_core, nv * GDN_Q, GDN_THREADS, 0, strm(st), g);
     return launch_ok("gdn_core");
+}
+
+int fnx_gdn_core_segs(const float* qkvz, const float* ab, const float* convw, const float* dt, const float* a, const float* nw, void* yq,
+                      float* scratch, int nk, int nv, const int* vmap, const FnxGdnLanes* gl, int nseg, int T, float eps, void* st) {
+    FNX_REQUIRE(T >= 1 && T <= FNX_MAXT && nseg >= 1 && nseg <= 65535, "gdn_core_segs: %d segments of %d rows", nseg, T);
+    FNX_REQUIRE(nk >= 1 && nk <= 255 && nv >= 1, "gdn_core_segs: %d key heads, %d value heads", nk, nv);
+    FNX_REQUIRE(gl && gl->S && gl->hist && gl->ctl, "gdn_core_segs: no lanes");
+    FNX_REQUIRE(T == 1 || (gl->snap && gl->hsnap && gl->row0), "gdn_core_segs: segments of %d rows need row0, snap and hsnap", T);
+    GdnArgs g{qkvz, ab, nullptr, convw, dt, a, nw, nullptr, (uint8_t*) yq, nullptr, scratch, gl->snap, gl->hsnap, nk, nv, vmap, T, eps, nullptr,
+              gl->S, gl->hist, gl->ctl, gl->row0};
+    launch(5, k_gdn_core, dim3(nv * GDN_Q, nseg), GDN_THREADS, 0, strm(st), g);
+    return launch_ok("gdn_core_segs");
+}
+
+int fnx_gdn_core_lanes(const float* qkvz, const float* ab, const float* convw, const float* dt, const float* a, const float* nw, void* yq,
+                       float* scratch, int nk, int nv, const int* vmap, const FnxGdnLanes* gl, int T, float eps, void* st) {
+    FNX_REQUIRE(T >= 1 && gl && !gl->row0, "gdn_core_lanes: %d rows, one lane each (no row0)", T);
+    return fnx_gdn_core_segs(qkvz, ab, convw, dt, a, nw, yq, scratch, nk, nv, vmap, gl, T, 1, eps, st);
 }
 }

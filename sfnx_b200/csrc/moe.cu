@@ -741,6 +741,12 @@ int fnx_moe_gate_up(const FnxExperts* A, const FnxJob* jobs, const int* njobs, i
     return fail("moe_gate_up: expert type %d not supported (Q4_K, Q8_0)", A->type);
 }
 
+int fnx_mmvq(const FnxExperts* W, const FnxJob* jobs, const int* njobs, int njobs_max, const void* y, float* out, int out_stride, void* st) {
+    FNX_REQUIRE(W && out_stride == W->nrows, "mmvq: output rows of %d values only (the matrix's rows)", W ? W->nrows : 0);
+    FNX_REQUIRE(W->type == FNX_Q4_K || W->type == FNX_Q8_0, "mmvq: weight type %d not handled (Q4_K, Q8_0)", W->type);
+    return fnx_moe_gate_up(W, jobs, njobs, njobs_max, y, out, st);
+}
+
 int fnx_moe_down(const FnxExperts* A, const FnxJob* jobs, const int* njobs, int njobs_max, const float* gu, int npairs, void* hq,
                  float* part, void* st) {
     FNX_REQUIRE(A && njobs_max >= 1 && npairs >= 1, "moe_down: no experts, jobs or pairs");

@@ -33,6 +33,10 @@ class Experts(C.Structure):
                 ("c", C.c_void_p), ("d", C.c_void_p), ("stride", C.c_size_t), ("stride_b", C.c_size_t)]
 
 
+class GdnLanes(C.Structure):
+    _fields_ = [("S", C.c_void_p), ("hist", C.c_void_p), ("ctl", C.c_void_p), ("row0", C.c_void_p), ("snap", C.c_void_p), ("hsnap", C.c_void_p)]
+
+
 class KvPages(C.Structure):
     _fields_ = [("pt", C.c_void_p), ("page", C.c_size_t), ("rows", C.c_int), ("cap", C.c_int)]
 
@@ -88,6 +92,8 @@ _SIGS = {
     "fnx_router_route": [_p, _p, _p, _i, _i, _i, _i, _p, _p, _p, _p, _p, _p, _p],
     "fnx_moe_gate_up": [C.POINTER(Experts), _p, _p, _i, _p, _p, _p],
     "fnx_moe_down": [C.POINTER(Experts), _p, _p, _i, _p, _i, _p, _p, _p],
+    "fnx_mmvq": [C.POINTER(Experts), _p, _p, _i, _p, _p, _i, _p],
+    "fnx_q8s_gemv_f32": [Q8S, _i, _i, _p, _p, _p, _p, _p, _i, _i, _p],
     "fnx_moe_gate_up_mma": [C.POINTER(Experts), _p, _p, _i, _p, _p, _p],
     "fnx_swiglu_h16": [_p, _i, _i, _p, _p],
     "fnx_moe_down_mma": [C.POINTER(Experts), _p, _p, _i, _p, _p, _p],
@@ -95,6 +101,8 @@ _SIGS = {
     "fnx_shared_expert": [Q8S, Q8S, _p, _i, _i, _i, _p, _p, _p, _p],
     "fnx_moe_combine": [_p, _p, _p, _p, _i, _p, _i, _i, _i, _p],
     "fnx_gdn_core": [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _p, _i, _f, _p, _p],
+    "fnx_gdn_core_segs": [_p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _p, C.POINTER(GdnLanes), _i, _i, _f, _p],
+    "fnx_gdn_core_lanes": [_p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _p, C.POINTER(GdnLanes), _i, _f, _p],
     "fnx_copy_many": [_p, _i, _p],
     "fnx_attn_prep_append": [_p, _p, _p, _p, _p, _p, _p, KvPages, _i, _i, _i, _p, _f, Rope, _i, _i, _i, _p],
     "fnx_attn_partial": [_p, _p, _p, KvPages, _p, _i, _i, _i, _p, _i, _i, _i, _p, _p],

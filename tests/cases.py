@@ -51,20 +51,10 @@ def moe_weights_q8(n, nexp, ffs, seed=0, sigma=0.02):
 
 
 def big_jobs(ntok, nexp, topk, seed=0, cap=64):
-    """The prompt path's jobs: every token picks topk distinct experts, pair p = t topk + k; an expert's pairs in pair
-    order, cut into jobs of at most `cap` rows (reference src/kernels.hpp:25-32).  Returns (jobs, pairs)."""
-    rng = np.random.default_rng(seed)
-    picks = np.stack([rng.permutation(nexp)[:topk] for _ in range(ntok)])
-    jobs = []
-    for e in range(nexp):
-        t, k = np.nonzero(picks == e)
-        for i in range(0, len(t), cap):
-            jobs.append((e, t[i:i + cap], t[i:i + cap] * topk + k[i:i + cap]))
-    out = np.zeros(len(jobs), O.BIGJOB_DTYPE)
-    for j, (e, y, o) in enumerate(jobs):
-        out[j]["w"], out[j]["n"] = e, len(y)
-        out[j]["y"][:len(y)], out[j]["out"][:len(y)] = y, o
-    return out, ntok * topk
+    """The prompt path's jobs (the package's own generator, so that the tests and its microbenchmark route alike)."""
+    from sfnx_b200.moe_mma_bench import big_jobs as make
+
+    return make(ntok, nexp, topk, seed=seed, cap=cap)
 
 
 def moe_oracle(w, x, topk=10):
@@ -140,11 +130,10 @@ def attn_case(T, ctx, nq=24, nkv=4, hd=256, ncard=1, seed=0, ramp=None):
     for card in range(ncard):
         kc = np.zeros((rows, nkv, hd), np.float16)
         vc = np.zeros((rows, nkv, hd), np.float16)
-        for p in range(ctx):
-            j = p // 4
-            if j % ncard == card:
-                kc[(j // ncard) * 4 + p % 4] = full_k[p]
-                vc[(j // ncard) * 4 + p % 4] = full_v[p]
+        p = np.arange(ctx)
+        mine = (p // 4) % ncard == card
+        at = (p // 4 // ncard) * 4 + p % 4
+        kc[at[mine]], vc[at[mine]] = full_k[mine], full_v[mine]
         c["kc"].append(kc.view(np.uint16))
         c["vc"].append(vc.view(np.uint16))
     c["eps"] = 1e-6

@@ -57,7 +57,7 @@ def test_attention_exact(T, ctx, ncard, hd):
 
 
 @pytest.mark.parametrize("T,ctx,ncard,hd", [(16, 3000, 1, 256), (16, 70, 1, 256), (7, 1500, 2, 256), (5, 515, 4, 128), (1, 0, 1, 256),
-                                            (16, 40000, 1, 256)])
+                                            (16, 40000, 1, 256), (2, 262144, 1, 256), (3, 70000, 8, 256)])
 def test_attention_fast_scan(T, ctx, ncard, hd):
     """The one-pass tensor-core scan against the oracle: the same partial format and merge, values equal to f32 rounding
     (its sums run in another order; queries and weights enter the f16 MMAs as high + low halves)."""

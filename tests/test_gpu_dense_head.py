@@ -55,6 +55,25 @@ def test_q8s_gemv(rows, cols, T):
     assert np.array_equal(G.host(out).view(np.uint32), ref.view(np.uint32))
 
 
+def test_q8s_gemv_f32_pair(oracle):
+    """The quantised projection and the small f32 one behind one call (the DeltaNet layer's qkvz and alpha|beta): each
+    output as its own entry point gives it."""
+    from sfnx_b200 import lib as L
+    from tests import gpu_util as G
+
+    rows, cols, T, rf = 4100, 3072, 16, 96
+    wq, wd, yq = _q8s_case(rows, cols, T, 77)
+    rng = np.random.default_rng(78)
+    W = (rng.standard_normal((rf, cols)) * 0.02).astype(np.float32)
+    x = rng.standard_normal((T, cols)).astype(np.float32)
+    w, keep = G.q8s((wq, wd))
+    dy, dW, dx, out, yf = G.dev(yq), G.dev(W), G.dev(x), G.zeros((T, rows)), G.zeros((T, rf))
+    L.call("fnx_q8s_gemv_f32", w, rows, cols, dy.data_ptr(), out.data_ptr(), dW.data_ptr(), dx.data_ptr(), yf.data_ptr(), rf, T, L.stream())
+    G.sync()
+    assert np.array_equal(G.host(out).view(np.uint32), cases.O.q8s_gemv(wq, wd, yq, T).view(np.uint32))
+    assert np.array_equal(G.host(yf).view(np.uint32), oracle.gemv_f32(W, x, 4).view(np.uint32))
+
+
 def test_gemv_f32_and_rms_norm(oracle):
     from sfnx_b200 import lib as L
     from tests import gpu_util as G

@@ -59,3 +59,71 @@ def test_gdn_benchmark_shape_with_rollback():
             L.call("fnx_copy_many", dj.data_ptr(), 2, L.stream())
         G.sync()
         assert np.array_equal(G.host(dS), S) and np.array_equal(G.host(dh), hist), n
+
+
+def _lanes_run(cs, T, with_snap):
+    """Several sequences through one launch: lane s's rows are window rows s T .. s T + T - 1 (weights shared, taken
+    from the first case)."""
+    import torch
+
+    from sfnx_b200 import lib as L
+    from tests import gpu_util as G
+
+    c0, nseg = cs[0], len(cs)
+    nk, nv, ch = c0["nk"], c0["nv"], c0["ch"]
+    qkvz, ab = G.dev(np.concatenate([c["qkvz"] for c in cs])), G.dev(np.concatenate([c["ab"] for c in cs]))
+    w = {k: G.dev(c0[k]) for k in ("convw", "dt", "a", "nw", "vmap")}
+    S, hist, ctl = [G.dev(c["S"]) for c in cs], [G.dev(c["hist"]) for c in cs], [G.dev(c["ctl"]) for c in cs]
+    ptrs = lambda ts: G.dev(np.array([t.data_ptr() for t in ts], np.uint64))
+    pS, ph, pc = ptrs(S), ptrs(hist), ptrs(ctl)
+    rows = nseg * T
+    yq = G.zeros(rows * (nv * 128 // 32) * 36, torch.uint8)
+    scratch = G.zeros(L.load().fnx_gdn_scratch_floats(nv))
+    if with_snap:
+        row0 = G.dev(np.arange(nseg, dtype=np.int32) * T)
+        snap, hsnap = G.zeros((rows, nv, 128, 128)), G.zeros((rows, 3, ch))
+        gl = L.GdnLanes(pS.data_ptr(), ph.data_ptr(), pc.data_ptr(), row0.data_ptr(), snap.data_ptr(), hsnap.data_ptr())
+        L.call("fnx_gdn_core_segs", qkvz.data_ptr(), ab.data_ptr(), w["convw"].data_ptr(), w["dt"].data_ptr(), w["a"].data_ptr(),
+               w["nw"].data_ptr(), yq.data_ptr(), scratch.data_ptr(), nk, nv, w["vmap"].data_ptr(), C.byref(gl), nseg, T, c0["eps"], L.stream())
+    else:
+        snap = hsnap = None
+        gl = L.GdnLanes(pS.data_ptr(), ph.data_ptr(), pc.data_ptr(), None, None, None)
+        L.call("fnx_gdn_core_lanes", qkvz.data_ptr(), ab.data_ptr(), w["convw"].data_ptr(), w["dt"].data_ptr(), w["a"].data_ptr(),
+               w["nw"].data_ptr(), yq.data_ptr(), scratch.data_ptr(), nk, nv, w["vmap"].data_ptr(), C.byref(gl), nseg, c0["eps"], L.stream())
+    G.sync()
+    return {"S": [G.host(t) for t in S], "hist": [G.host(t) for t in hist], "yq": G.host(yq).reshape(rows, -1),
+            "snap": G.host(snap) if with_snap else None, "hsnap": G.host(hsnap) if with_snap else None}
+
+
+def _lane_cases(nseg, T, nk, nv, seed):
+    cs = [cases.gdn_case(T=T, nk=nk, nv=nv, seed=seed + s) for s in range(nseg)]
+    for s, c in enumerate(cs):   # one layer's weights; every lane its own state, history, position and parity
+        for k in ("convw", "dt", "a", "nw", "vmap"):
+            c[k] = cs[0][k]
+        c["ctl"] = np.array([100 * s + 7, 4 + s], np.int32)
+    return cs
+
+
+def test_gdn_segments_of_several_sequences():
+    """Three sequences x 5 rows in one launch: each lane's outputs, state, history and checkpoints as a window of 5 rows
+    on that lane alone gives them (batched lanes = alone)."""
+    T, cs = 5, _lane_cases(3, 5, 2, 6, seed=70)
+    got = _lanes_run(cs, T, with_snap=True)
+    for s, c in enumerate(cs):
+        ref = cases.gdn_oracle(c)
+        assert np.array_equal(got["yq"][s * T:(s + 1) * T], ref["yq"]), s
+        assert np.array_equal(got["S"][s].view(np.uint32), ref["S"].view(np.uint32)), s
+        assert np.array_equal(got["hist"][s], ref["hist"]), s
+        assert np.array_equal(got["snap"][s * T:s * T + T - 1].view(np.uint32), ref["snap"][:T - 1].view(np.uint32)), s
+        assert np.array_equal(got["hsnap"][s * T:s * T + T - 1], ref["hsnap"][:T - 1]), s
+
+
+def test_gdn_one_row_per_lane():
+    """Six lanes, one row each (a batched decode step)."""
+    cs = _lane_cases(6, 1, 2, 4, seed=80)
+    got = _lanes_run(cs, 1, with_snap=False)
+    for s, c in enumerate(cs):
+        ref = cases.gdn_oracle(c)
+        assert np.array_equal(got["yq"][s:s + 1], ref["yq"]), s
+        assert np.array_equal(got["S"][s].view(np.uint32), ref["S"].view(np.uint32)), s
+        assert np.array_equal(got["hist"][s], ref["hist"]), s

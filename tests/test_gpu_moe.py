@@ -93,3 +93,26 @@ def test_moe_q8_0_experts_benchmark_shape():
     rng = np.random.default_rng(26)
     w = cases.moe_weights_q8(n=3072, nexp=32, ffs=768, seed=7)
     _check(w, rng.standard_normal((16, 3072)).astype(np.float32), topk=10)
+
+
+def test_mmvq_is_the_job_matvec():
+    """mmvq over a job list: the same entry as the experts' gate|up for the types it takes, refused for the others."""
+    import ctypes as C
+
+    from sfnx_b200 import lib as L
+    from tests import gpu_util as G
+
+    rng = np.random.default_rng(29)
+    w = cases.moe_weights(n=512, nexp=16, ffs=128, seed=9)
+    x = rng.standard_normal((7, 512)).astype(np.float32)
+    ref = cases.moe_oracle(w, x, topk=4)
+    nj, P = ref["njobs"], 7 * 4
+    ex, keep = G.experts_q4k(w["gu_q4k"], 256, 512)
+    dj, dn = G.dev(ref["jobs_gu"].view(np.uint8).reshape(-1)), G.dev(np.array([nj, 0], np.int32))
+    dxq, out = G.dev(ref["xq"]), G.zeros((P, 256))
+    L.call("fnx_mmvq", C.byref(ex), dj.data_ptr(), dn.data_ptr(), P, dxq.data_ptr(), out.data_ptr(), 256, L.stream())
+    G.sync()
+    assert np.array_equal(_bits(G.host(out)), _bits(ref["gu"]))
+    assert L.load().fnx_mmvq(C.byref(ex), dj.data_ptr(), dn.data_ptr(), P, dxq.data_ptr(), out.data_ptr(), 300, L.stream()) != 0
+    e6, keep6 = G.experts_q6p(w["dn_planes"], 512, 128)
+    assert L.load().fnx_mmvq(C.byref(e6), dj.data_ptr(), dn.data_ptr(), P, dxq.data_ptr(), out.data_ptr(), 512, L.stream()) != 0

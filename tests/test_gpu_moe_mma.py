@@ -87,7 +87,7 @@ def test_f16_weights_bit_exact_through_one_hot_rows(kind):
         assert np.array_equal(got.astype(np.float32).view(np.uint32), ref.astype(np.float32).view(np.uint32)), which
 
 
-@pytest.mark.parametrize("kind,n,ffs,nexp,ntok,topk", [("q4k", 512, 256, 8, 100, 4), ("q8_0", 1024, 96, 6, 70, 3), ("q4k", 3072, 768, 4, 150, 2),
+@pytest.mark.parametrize("kind,n,ffs,nexp,ntok,topk", [("q4k", 512, 256, 8, 150, 4), ("q8_0", 1024, 96, 6, 70, 3), ("q4k", 3072, 768, 4, 150, 2),
                                                       ("q4k", 256, 64, 5, 1, 2)])
 def test_gate_up_swiglu_down(kind, n, ffs, nexp, ntok, topk):
     """gate|up -> SwiGLU -> down over jobs of 1 to 64 rows (ragged job sizes, row tiles past the matrix's last row, FF slice
