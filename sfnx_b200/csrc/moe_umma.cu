@@ -7,14 +7,15 @@
 // half product q * d, :184-216; Q6_K in 32-column units, which the reference's prompt path does not take, by the same
 // rule: one half product (q - 32) * f16(d sc)), activations f16, products summed in fp32.
 //
-// A CTA takes one job and 128 of the expert's rows.  Those rows are the M side of tcgen05.mma (kind::f16, cta_group::1,
-// M 128), the job's activation rows the N side (16 to 64), and the 128 x N fp32 result sits in tensor memory.  Eight
-// producer warps turn 64 columns at a time into the A operand (128 rows x 128 bytes, K-major, 128-byte swizzle) in one
-// of four shared-memory stages, next to the job's activation rows for those columns (the B operand, same form); raw
-// weight bytes are fetched two steps ahead into registers.  A ninth warp waits for a stage to be full, issues its four
-// MMAs (K 16 each) and lets tcgen05.commit hand the stage back.  Two CTAs share an SM (97 KB of shared memory and 64
-// columns of tensor memory each), so one streams while the other starts or drains.  Every wait is bounded and feeds the
-// device fault word.
+// A CTA takes 128 of an expert's rows and one or two of the expert's jobs (consecutive jobs of one expert are paired, so
+// that their weights are dequantised once).  The rows are the M side of tcgen05.mma (kind::f16, cta_group::1, M 128),
+// the jobs' activation rows the N side (16 to 128), and the 128 x N fp32 result sits in tensor memory.  Eight producer
+// warps turn 64 columns at a time into the A operand (128 rows x 128 bytes, K-major, 128-byte swizzle) in one of three
+// shared-memory stages, next to the jobs' activation rows for those columns (the B operand, same form, by cp.async);
+// raw weight bytes are fetched a step ahead into registers (a Q4_K super-block, four stages' worth, at a time).  A
+// ninth warp waits for a stage to be full, issues its four MMAs (K 16 each) and lets tcgen05.commit hand the stage
+// back.  Two CTAs share an SM (97 KB of shared memory and 128 columns of tensor memory each), so one streams while the
+// other starts or drains.  Every wait is bounded and feeds the device fault word.
 #include <algorithm>
 
 #include "common.cuh"
@@ -23,8 +24,8 @@
 
 namespace fnxk {
 
-constexpr int MU_BM = 128, MU_KC = 64, MU_NS = 4, MU_PROD = 256, MU_THREADS = MU_PROD + 32;
-constexpr int MU_ABYTES = MU_BM * 128, MU_BBYTES = FNX_PF_JOB * 128, MU_STAGE = MU_ABYTES + MU_BBYTES;
+constexpr int MU_BM = 128, MU_KC = 64, MU_NS = 3, MU_PROD = 256, MU_THREADS = MU_PROD + 32, MU_PAIR = 2, MU_NMAX = MU_PAIR * FNX_PF_JOB;
+constexpr int MU_ABYTES = MU_BM * 128, MU_BBYTES = MU_NMAX * 128, MU_STAGE = MU_ABYTES + MU_BBYTES;
 constexpr size_t MU_SMEM = (size_t) MU_NS * MU_STAGE + 1024;
 
 __device__ __forceinline__ unsigned mu_s32(const void* p) { return (unsigned) __cvta_generic_to_shared(p); }
@@ -179,14 +180,26 @@ __device__ __forceinline__ void mu_dequant(const MuRaw<FNX_Q6_K>& r, int, unsign
 template <int TYPE>
 __global__ void __launch_bounds__(MU_THREADS, 2) k_moe_umma(const MuArgs a) {
     const int ji = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    if (ji >= *a.njobs) return;
+    const int njobs = *a.njobs;
+    if (ji >= njobs) return;
+    // Consecutive jobs of one expert share the dequantised weights: the jobs of an expert are taken two at a time, the
+    // first of a pair does both (its rows in columns 0..63 of the result, the partner's from column 64), the second
+    // leaves at once.  A pair is counted from the expert's first job.
+    const int expert = a.jobs[ji].w;
+    int first = ji;
+    while (first > 0 && a.jobs[first - 1].w == expert) --first;
+    if ((ji - first) & 1) return;
+    const bool paired = ji + 1 < njobs && a.jobs[ji + 1].w == expert;
     extern __shared__ __align__(1024) unsigned char mu_smem[];
     // the swizzle is a function of the shared-memory address: operand tiles start on 1024-byte boundaries
     unsigned char* stages = mu_smem + ((1024u - (mu_s32(mu_smem) & 1023u)) & 1023u);
-    __shared__ FnxBigJob jb;
+    __shared__ FnxBigJob jb, jb2;
     __shared__ __align__(8) unsigned long long full[MU_NS], empty[MU_NS], done;
     __shared__ unsigned tmem_base;
-    for (int i = tid; i < (int) (sizeof(FnxBigJob) / 4); i += MU_THREADS) reinterpret_cast<int*>(&jb)[i] = reinterpret_cast<const int*>(a.jobs + ji)[i];
+    for (int i = tid; i < (int) (sizeof(FnxBigJob) / 4); i += MU_THREADS) {
+        reinterpret_cast<int*>(&jb)[i] = reinterpret_cast<const int*>(a.jobs + ji)[i];
+        reinterpret_cast<int*>(&jb2)[i] = paired ? reinterpret_cast<const int*>(a.jobs + ji + 1)[i] : 0;
+    }
     if (tid == 0) {
         for (int s = 0; s < MU_NS; ++s) {
             asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(mu_s32(&full[s])), "r"(MU_PROD));
@@ -195,15 +208,17 @@ __global__ void __launch_bounds__(MU_THREADS, 2) k_moe_umma(const MuArgs a) {
         asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(mu_s32(&done)));
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == MU_PROD / 32) {   // 64 columns of tensor memory: the 128 x 64 fp32 result
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(mu_s32(&tmem_base)), "r"(64));
+    if (warp == MU_PROD / 32) {   // 128 columns of tensor memory: the 128 x (64 + 64) fp32 result
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(mu_s32(&tmem_base)), "r"(MU_NMAX));
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     // a last step of 32 columns (an FF slice of 96) fills half a stage: two MMAs instead of four
-    const int n = min(max(jb.n, 0), FNX_PF_JOB), nt = (n + 15) / 16, nk = (a.ncols + MU_KC - 1) / MU_KC, row0 = blockIdx.x * MU_BM;
+    const int n = min(max(jb.n, 0), FNX_PF_JOB), n2 = paired ? min(max(jb2.n, 0), FNX_PF_JOB) : 0;
+    const int ncol = paired ? FNX_PF_JOB + 16 * ((n2 + 15) / 16) : 16 * ((n + 15) / 16);   // N of the MMAs
+    const int nk = (a.ncols + MU_KC - 1) / MU_KC, row0 = blockIdx.x * MU_BM;
     const unsigned st_s = mu_s32(stages);
     bool alive = true;   // false after a wait ran out
     if (warp < MU_PROD / 32) {
@@ -214,18 +229,25 @@ __global__ void __launch_bounds__(MU_THREADS, 2) k_moe_umma(const MuArgs a) {
         using Raw = MuRaw<TYPE>;
         const int row = 16 * warp + (lane & 15), half = lane >> 4;
         const int wrow = min(row0 + row, a.nrows - 1);   // rows past the matrix repeat the last one; never written out
-        const int xj0 = tid >> 3, xj1 = xj0 + 32, xc = tid & 7;
-        const uint16_t* xp0 = xj0 < n ? a.x + (size_t) jb.y[xj0] * a.ncols + xc * 8 : nullptr;
-        const uint16_t* xp1 = xj1 < n ? a.x + (size_t) jb.y[xj1] * a.ncols + xc * 8 : nullptr;
-        const unsigned xd0 = MU_ABYTES + xj0 * 128 + ((xc ^ (xj0 & 7)) << 4), xd1 = MU_ABYTES + xj1 * 128 + ((xc ^ (xj1 & 7)) << 4);
+        const int xc = tid & 7;
+        const uint16_t* xp[MU_NMAX / 32];   // B rows tid / 8 + 32 i: rows 0..63 the job's, 64..127 its partner's
+        unsigned xd[MU_NMAX / 32];
+#pragma unroll
+        for (int i = 0; i < MU_NMAX / 32; ++i) {
+            const int j = (tid >> 3) + 32 * i, jj = j & (FNX_PF_JOB - 1);
+            const bool has = j < FNX_PF_JOB ? jj < n : jj < n2;
+            xp[i] = has ? a.x + (size_t) (j < FNX_PF_JOB ? jb.y[jj] : jb2.y[jj]) * a.ncols + xc * 8 : nullptr;
+            xd[i] = MU_ABYTES + j * 128 + ((xc ^ (j & 7)) << 4);
+        }
         auto xcopy = [&](int k) {   // the job's rows for step k, once its stage is free
             if (k < nk) {
                 const int s = k % MU_NS;
                 if (k >= MU_NS && alive) alive = mu_wait(&empty[s], (unsigned) ((k / MU_NS - 1) & 1), a.fault);
                 const unsigned tile = st_s + s * MU_STAGE;
                 const bool in = 8 * xc < a.ncols - k * MU_KC;
-                if (xp0 && in) asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(tile + xd0), "l"(xp0 + k * MU_KC));
-                if (xp1 && in) asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(tile + xd1), "l"(xp1 + k * MU_KC));
+#pragma unroll
+                for (int i = 0; i < MU_NMAX / 32; ++i)
+                    if (xp[i] && in) asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(tile + xd[i]), "l"(xp[i] + k * MU_KC));
             }
             asm volatile("cp.async.commit_group;");
         };
@@ -239,16 +261,16 @@ __global__ void __launch_bounds__(MU_THREADS, 2) k_moe_umma(const MuArgs a) {
         };
         const int nsteps = (nk + Raw::STEPS - 1) / Raw::STEPS;
         Raw r0, r1;
-        r0.fetch(a, jb.w, wrow, half, 0);
+        r0.fetch(a, expert, wrow, half, 0);
         xcopy(0);
 #pragma unroll 1
         for (int sidx = 0; sidx < nsteps; sidx += 2) {
-            if (sidx + 1 < nsteps) r1.fetch(a, jb.w, wrow, half, sidx + 1);
+            if (sidx + 1 < nsteps) r1.fetch(a, expert, wrow, half, sidx + 1);
 #pragma unroll
             for (int j = 0; j < Raw::STEPS; ++j)
                 if (sidx * Raw::STEPS + j < nk) produce(r0, j, sidx * Raw::STEPS + j);
             if (sidx + 1 < nsteps) {
-                if (sidx + 2 < nsteps) r0.fetch(a, jb.w, wrow, half, sidx + 2);
+                if (sidx + 2 < nsteps) r0.fetch(a, expert, wrow, half, sidx + 2);
 #pragma unroll
                 for (int j = 0; j < Raw::STEPS; ++j)
                     if ((sidx + 1) * Raw::STEPS + j < nk) produce(r1, j, (sidx + 1) * Raw::STEPS + j);
@@ -257,7 +279,7 @@ __global__ void __launch_bounds__(MU_THREADS, 2) k_moe_umma(const MuArgs a) {
         asm volatile("cp.async.wait_group 0;" ::: "memory");
     } else {
         // ---- the issuing warp: stage k's four MMAs once it is full; the commit frees the stage
-        const unsigned idesc = (1u << 4) | ((unsigned) (16 * nt >> 3) << 17) | ((128u >> 4) << 24);   // D f32, A and B f16 K-major
+        const unsigned idesc = (1u << 4) | ((unsigned) (ncol >> 3) << 17) | ((128u >> 4) << 24);   // D f32, A and B f16 K-major
 #pragma unroll 1
         for (int k = 0; k < nk; ++k) {
             const int s = k % MU_NS;
@@ -281,7 +303,7 @@ __global__ void __launch_bounds__(MU_THREADS, 2) k_moe_umma(const MuArgs a) {
         bool ok = alive && mu_wait(&done, 0u, a.fault);
         ok = __all_sync(0xffffffffu, ok);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const int row = row0 + 32 * (warp & 3) + lane, cols = 8 * nt, c0 = (warp >> 2) * cols;
+        const int row = row0 + 32 * (warp & 3) + lane, cols = ncol / 2, c0 = (warp >> 2) * cols;
         if (ok)
             for (int c = c0; c < c0 + cols; c += 8) {
                 unsigned v[8];
@@ -290,13 +312,16 @@ __global__ void __launch_bounds__(MU_THREADS, 2) k_moe_umma(const MuArgs a) {
                              : "r"(tmem_base + ((unsigned) (32 * (warp & 3)) << 16) + (unsigned) c));
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-                for (int i = 0; i < 8; ++i)
-                    if (c + i < n && row < a.nrows) a.out[(size_t) jb.out[c + i] * a.nrows + row] = __uint_as_float(v[i]);
+                for (int i = 0; i < 8; ++i) {
+                    const int col = c + i, jj = col & (FNX_PF_JOB - 1);
+                    const bool second = paired && col >= FNX_PF_JOB;
+                    if (jj < (second ? n2 : n) && row < a.nrows) a.out[(size_t) (second ? jb2.out[jj] : jb.out[jj]) * a.nrows + row] = __uint_as_float(v[i]);
+                }
             }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
-    if (warp == MU_PROD / 32) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(64));
+    if (warp == MU_PROD / 32) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(MU_NMAX));
 }
 
 // h = silu(gate) * up of the stacked rows, rounded to f16 (reference src/moe_mma.cuh:381-388)

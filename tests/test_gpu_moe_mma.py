@@ -88,10 +88,11 @@ def test_f16_weights_bit_exact_through_one_hot_rows(kind):
 
 
 @pytest.mark.parametrize("kind,n,ffs,nexp,ntok,topk", [("q4k", 512, 256, 8, 150, 4), ("q8_0", 1024, 96, 6, 70, 3), ("q4k", 3072, 768, 4, 150, 2),
-                                                      ("q4k", 256, 64, 5, 1, 2)])
+                                                      ("q4k", 256, 64, 5, 1, 2), ("q8_0", 256, 64, 2, 330, 2)])
 def test_gate_up_swiglu_down(kind, n, ffs, nexp, ntok, topk):
     """gate|up -> SwiGLU -> down over jobs of 1 to 64 rows (ragged job sizes, row tiles past the matrix's last row, FF slice
-    96), each step against the oracle fed with the GPU's previous step."""
+    96; experts with one, two and six jobs: consecutive jobs of an expert are taken in pairs), each step against the
+    oracle fed with the GPU's previous step."""
     from oracle import binding as O
 
     w = (cases.moe_weights if kind == "q4k" else cases.moe_weights_q8)(n=n, nexp=nexp, ffs=ffs, seed=32)
