@@ -219,6 +219,16 @@ int fnx_attn_partial(const float* qg, const uint16_t* kc, const uint16_t* vc, Fn
                      const int* pos0, int nq, int nkv, int hd, float* scratch, void* st);
 int fnx_attn_partial_exact(const float* qg, const uint16_t* kc, const uint16_t* vc, FnxKvPages g, float* part, int card, int ncard,
                            int T, const int* pos0, int nq, int nkv, int hd, float* scratch, void* st);
+/* reference src/kernels.hpp:182-193 LaneRows, :232-235 attn_part_lanes (src/kernels.cu:1262-1281): the partials of a
+ * batched window's T rows, each of a lane (sequence) of its own: row t at position *pos[t] on the page table pt[t] (device
+ * arrays of device pointers; pt null: g's table for every row).  The reference's order of sums, as
+ * fnx_attn_partial_exact; merged by fnx_attn_finish as any other partials. */
+typedef struct FnxLaneRows {
+    const int* const* pos;
+    const int* const* pt;
+} FnxLaneRows;
+int fnx_attn_part_lanes(const float* qg, const uint16_t* kc, const uint16_t* vc, FnxKvPages g, FnxLaneRows lr, float* part, int card, int ncard,
+                        int T, int nq, int nkv, int hd, float* scratch, void* st);
 int fnx_attn_splits(int nkv);
 int fnx_attn_finish(const float* parts, int nparts, int first_part, const float* qg, float* out, int T, int nq, int h0, int nh,
                     int hd, void* st);
@@ -318,6 +328,32 @@ int fnx_window_commit(const FnxStackCfg* cfg, const FnxLayer* layers, void* ws, 
  * alpha/beta projection beside qkvz; the reference's st2, src/engine.cu:939-946), with the two events (cudaEvent_t) the
  * forks and joins record; set per host thread, null to stay on one stream.  Capture-safe. */
 int fnx_window_side_stream(void* st2, void* ev_fork, void* ev_join);
+
+/* A window of several sequences ("lanes"; reference src/engine.cu:1137-1216 enqueue_rows / src/engine_common.cu:1136-1195
+ * commit_rows): nseg lanes x `rows` window rows each, at most FNX_MAXT rows in all; lane s's rows are window rows
+ * s rows .. s rows + rows - 1.  Everything shared (norms, projections, router, experts, head) runs over all rows as in a
+ * window of one sequence; the DeltaNet core chains each lane's rows through that lane's state (fnx_gdn_core_segs), the K/V
+ * rows are appended lane by lane and every row's attention partial is taken on its lane's position and pages
+ * (fnx_attn_part_lanes, the reference's order of sums).  Each lane's results are those of a window of its rows alone.
+ * The layers' S / hist fields are not used; kc / vc are the layer's paged pool. */
+typedef struct FnxWindowLanes {
+    int nseg, rows;
+    const int* const* ctl;      /* device [nseg]: lane s's (position of its first row, tag) words */
+    const int* row0;            /* device [nseg]: s * rows */
+    const int* const* row_pos;  /* device [nseg * rows]: row t's position word */
+    const int* const* row_pt;   /* device [nseg * rows]: row t's lane's page table */
+    const int* const* ctl_host; /* host [nseg]: the same device pointers as ctl */
+    const int* const* pt_host;  /* host [nseg]: the lanes' page tables (device pointers) */
+    float* const* const* S;     /* host [nlayers]: device array [nseg] of the lanes' states (DeltaNet layers) */
+    float* const* const* hist;  /* host [nlayers]: device array [nseg] of the lanes' conv histories */
+    float* const* const* S_host;    /* host [nlayers] of host arrays [nseg]: the same pointers, for the commit */
+    float* const* const* hist_host;
+} FnxWindowLanes;
+int fnx_window_stage_lanes(const FnxStackCfg* cfg, const FnxLayer* layers, const FnxHead* head, void* ws, const FnxWindowLanes* lanes, int stage,
+                           void* st);
+/* keeps the first n[s] rows of lane s (tags[s]: the lane's window tag, whose low bit says which history half was read) */
+int fnx_window_commit_lanes(const FnxStackCfg* cfg, const FnxLayer* layers, void* ws, const FnxWindowLanes* lanes, const int* n, const int* tags,
+                            void* host_jobs, void* st);
 
 /* per-call timing of windows enqueued outside a graph (the reference's engine keeps per-window timers,
  * src/engine.hpp:182-187): between fnx_trace_begin and fnx_trace_end every C ABI call of fnx_window_stage is bracketed by

@@ -93,10 +93,12 @@ template <int HD>
 __global__ void __launch_bounds__(HD) k_attn_part(const float* __restrict__ qg, const uint16_t* __restrict__ kc,
                                                   const uint16_t* __restrict__ vc, FnxKvPages g, float* __restrict__ acc_out,
                                                   AttPart* __restrict__ mz_out, int nq, int nkv, const int* __restrict__ pos0p, int card,
-                                                  int ncard) {
+                                                  int ncard, FnxLaneRows lr) {
     const int s = blockIdx.x, t = blockIdx.y, kvl = blockIdx.z, i = threadIdx.x, lane = i & 31, warp = i >> 5;
     const int qpk = nq / nkv, h0 = kvl * qpk;
-    const int ctx = kv_owned(*pos0p + t, card, ncard);
+    // a row of a lane of its own: the lane's position word and page table (reference src/kernels.hpp:189-193)
+    if (lr.pt) g.pt = lr.pt[t];
+    const int ctx = kv_owned(lr.pos ? *lr.pos[t] : *pos0p + t, card, ncard);
     const int len = ((ctx + ATT_SPLITS - 1) / ATT_SPLITS + ATT_CH - 1) / ATT_CH * ATT_CH;
     const int p0 = s * len, p1 = min(ctx, p0 + len);
     extern __shared__ __align__(16) float att_sm[];
@@ -236,8 +238,8 @@ size_t fnx_attn_scratch_floats(int nq, int hd, int T) {   // the larger of the e
     return exact > fast ? exact : fast;   // fast: at most 148 splits' partials, then the queries' tensor-core image (8 KV heads)
 }
 
-int fnx_attn_partial_exact(const float* qg, const uint16_t* kc, const uint16_t* vc, FnxKvPages g, float* part, int card, int ncard, int T,
-                     const int* pos0, int nq, int nkv, int hd, float* scratch, void* st) {
+static int attn_partial_rows(const float* qg, const uint16_t* kc, const uint16_t* vc, FnxKvPages g, float* part, int card, int ncard, int T,
+                             const int* pos0, FnxLaneRows lr, int nq, int nkv, int hd, float* scratch, void* st) {
     FNX_REQUIRE(T >= 1 && T <= FNX_MAXT, "attn: T %d outside 1..%d", T, FNX_MAXT);
     FNX_REQUIRE(hd == 256 || hd == 128, "attn: head dim %d (128 or 256)", hd);
     FNX_REQUIRE(nkv >= 1 && nq % nkv == 0 && nq / nkv <= ATT_MAXQPK, "attn: %d query heads over %d KV heads", nq, nkv);
@@ -249,14 +251,25 @@ int fnx_attn_partial_exact(const float* qg, const uint16_t* kc, const uint16_t* 
     const dim3 grid(ATT_SPLITS, T, nkv);
     if (hd == 256) {
         if (sm > 48 * 1024) cudaFuncSetAttribute(k_attn_part<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) sm);
-        k_attn_part<256><<<grid, 256, sm, strm(st)>>>(qg, kc, vc, g, acc, mz, nq, nkv, pos0, card, ncard);
+        k_attn_part<256><<<grid, 256, sm, strm(st)>>>(qg, kc, vc, g, acc, mz, nq, nkv, pos0, card, ncard, lr);
     } else {
         if (sm > 48 * 1024) cudaFuncSetAttribute(k_attn_part<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) sm);
-        k_attn_part<128><<<grid, 128, sm, strm(st)>>>(qg, kc, vc, g, acc, mz, nq, nkv, pos0, card, ncard);
+        k_attn_part<128><<<grid, 128, sm, strm(st)>>>(qg, kc, vc, g, acc, mz, nq, nkv, pos0, card, ncard, lr);
     }
     if (launch_ok("attn partial")) return 1;
     k_attn_local<<<dim3(nq, T), hd, 0, strm(st)>>>(acc, mz, part, nq, hd);
     return launch_ok("attn local");
+}
+
+int fnx_attn_partial_exact(const float* qg, const uint16_t* kc, const uint16_t* vc, FnxKvPages g, float* part, int card, int ncard, int T,
+                           const int* pos0, int nq, int nkv, int hd, float* scratch, void* st) {
+    return attn_partial_rows(qg, kc, vc, g, part, card, ncard, T, pos0, FnxLaneRows{nullptr, nullptr}, nq, nkv, hd, scratch, st);
+}
+
+int fnx_attn_part_lanes(const float* qg, const uint16_t* kc, const uint16_t* vc, FnxKvPages g, FnxLaneRows lr, float* part, int card, int ncard,
+                        int T, int nq, int nkv, int hd, float* scratch, void* st) {
+    FNX_REQUIRE(lr.pos, "attn_part_lanes: no position words");
+    return attn_partial_rows(qg, kc, vc, g, part, card, ncard, T, nullptr, lr, nq, nkv, hd, scratch, st);
 }
 
 int fnx_attn_finish(const float* parts, int nparts, int first_part, const float* qg, float* out, int T, int nq, int h0, int nh,

@@ -111,7 +111,7 @@ static Ws carve(const FnxStackCfg& c) {
     w.err = take(16);
     w.ctl = take(16);
     w.gdn_scratch = take(fnx_gdn_scratch_floats(c.nv) * 4);
-    w.copy_jobs = take((size_t) c.nlayers * 2 * sizeof(FnxCopyJob));
+    w.copy_jobs = take((size_t) c.nlayers * 2 * FNX_MAXT * sizeof(FnxCopyJob));   // up to a lane a row
     w.total = o;
     return w;
 }
@@ -208,7 +208,9 @@ int fnx_window_plan(const FnxStackCfg* cfg, const FnxLayer* layers, int* after, 
     return plan(*cfg, layers, nullptr, after, max);
 }
 
-int fnx_window_stage(const FnxStackCfg* cfg, const FnxLayer* layers, const FnxHead* head, void* ws, int T, int stage, void* st) {
+// one stage; lanes null: the rows are one sequence's
+static int window_stage(const FnxStackCfg* cfg, const FnxLayer* layers, const FnxHead* head, void* ws, int T, int stage, const FnxWindowLanes* lanes,
+                        void* st) {
     TRY(check_cfg(cfg));
     FNX_REQUIRE(T >= 1 && T <= FNX_MAXT, "window: T %d outside 1..%d", T, FNX_MAXT);
     const FnxStackCfg& c = *cfg;
@@ -243,8 +245,13 @@ int fnx_window_stage(const FnxStackCfg* cfg, const FnxLayer* layers, const FnxHe
         TRK("ab", 1, fnx_gemv_f32(L.ab, xn, (float*) (b + w.ab), 2 * c.nv, c.n, T, forked ? (void*) g_side.st : st));
         TRK("qkvz", 1, fnx_q8s_gemv(L.qkvz, rows, c.n, xq, (float*) (b + w.qkvz), rows, T, st));
         if (forked) TRY(side_join(st));
-        TRK("gdn_core", 1, fnx_gdn_core((const float*) (b + w.qkvz), (const float*) (b + w.ab), L.hist, L.conv, L.dt, L.a, L.ssm_norm, L.S,
-                                        b + w.yq, ctl, (float*) (b + w.gdn_scratch), L.snap, L.hsnap, c.nk, c.nv, L.vmap, T, c.eps, st, nullptr));
+        if (lanes) {   // every lane's rows chain through that lane's state, all lanes in one launch
+            const FnxGdnLanes gl{lanes->S[sg.layer], lanes->hist[sg.layer], lanes->ctl, lanes->row0, L.snap, L.hsnap};
+            TRK("gdn_core", 1, fnx_gdn_core_segs((const float*) (b + w.qkvz), (const float*) (b + w.ab), L.conv, L.dt, L.a, L.ssm_norm, b + w.yq,
+                                                 (float*) (b + w.gdn_scratch), c.nk, c.nv, L.vmap, &gl, lanes->nseg, lanes->rows, c.eps, st));
+        } else
+            TRK("gdn_core", 1, fnx_gdn_core((const float*) (b + w.qkvz), (const float*) (b + w.ab), L.hist, L.conv, L.dt, L.a, L.ssm_norm, L.S,
+                                            b + w.yq, ctl, (float*) (b + w.gdn_scratch), L.snap, L.hsnap, c.nk, c.nv, L.vmap, T, c.eps, st, nullptr));
         TRK("ssm_out", 1, fnx_q8s_gemv(L.ssm_out, c.n, c.nv * FNX_HS, b + w.yq, bo, c.n, T, st));
         return 0;
     }
@@ -260,9 +267,24 @@ int fnx_window_stage(const FnxStackCfg* cfg, const FnxLayer* layers, const FnxHe
             TRK("wqkv", 1, fnx_q8s_gemv_segs(ws, rows3, outs, rows3, 3, c.n, xq, T, st));
         }
         const FnxRope rope{c.rope_base, c.nrot};
+        float* mine = (float*) (b + w.partials) + (size_t) c.card * T * c.nq * (c.hd + 2);
+        if (lanes) {
+            // norm, rotary and append lane by lane (the lane's position and pages), then every row's partial at once, each
+            // on its lane's position and pages, in the reference's order of sums (reference src/engine.cu:1186-1200)
+            for (int sI = 0; sI < lanes->nseg; ++sI) {
+                const size_t r0 = (size_t) sI * lanes->rows;
+                FnxKvPages pg = L.pages;
+                pg.pt = lanes->pt_host[sI];
+                TRK("attn_prep_append", 1, fnx_attn_prep_append(qg + r0 * c.nq * 2 * c.hd, k + r0 * c.nkv * c.hd, v + r0 * c.nkv * c.hd, L.q_norm, L.k_norm,
+                                                                L.kc, L.vc, pg, c.card, c.ncard, lanes->rows, lanes->ctl_host[sI], c.eps, rope, c.nq,
+                                                                c.nkv, c.hd, st));
+            }
+            TRK("attn_partial", 2, fnx_attn_part_lanes(qg, L.kc, L.vc, L.pages, FnxLaneRows{lanes->row_pos, lanes->row_pt}, mine, c.card, c.ncard, T,
+                                                       c.nq, c.nkv, c.hd, (float*) (b + w.att_scratch), st));
+            return 0;
+        }
         TRK("attn_prep_append", 1, fnx_attn_prep_append(qg, k, v, L.q_norm, L.k_norm, L.kc, L.vc, L.pages, c.card, c.ncard, T, ctl, c.eps,
                                                         rope, c.nq, c.nkv, c.hd, st));
-        float* mine = (float*) (b + w.partials) + (size_t) c.card * T * c.nq * (c.hd + 2);
         // FNX_ATTN_EXACT=1: the scan in the reference's order of sums (bit-reproducible against the CPU statement, several
         // times slower); default: the one-pass tensor-core scan
         const char* ex = getenv("FNX_ATTN_EXACT");
@@ -304,6 +326,48 @@ int fnx_window_stage(const FnxStackCfg* cfg, const FnxLayer* layers, const FnxHe
     TRK("moe_combine", 1, fnx_moe_combine((const float*) (b + w.part), (const float*) (b + w.topw), (const float*) (b + w.sh), rl, c.nexp, bo,
                                           T, c.n, c.topk, st));
     return 0;
+}
+
+int fnx_window_stage(const FnxStackCfg* cfg, const FnxLayer* layers, const FnxHead* head, void* ws, int T, int stage, void* st) {
+    return window_stage(cfg, layers, head, ws, T, stage, nullptr, st);
+}
+
+int fnx_window_stage_lanes(const FnxStackCfg* cfg, const FnxLayer* layers, const FnxHead* head, void* ws, const FnxWindowLanes* lanes, int stage,
+                           void* st) {
+    FNX_REQUIRE(lanes && lanes->nseg >= 1 && lanes->rows >= 1 && lanes->nseg * lanes->rows <= FNX_MAXT, "window: %d lanes of %d rows (at most %d rows)",
+                lanes ? lanes->nseg : 0, lanes ? lanes->rows : 0, FNX_MAXT);
+    FNX_REQUIRE(lanes->ctl && lanes->row0 && lanes->row_pos && lanes->row_pt && lanes->ctl_host && lanes->pt_host && lanes->S && lanes->hist,
+                "window: lanes without their tables");
+    return window_stage(cfg, layers, head, ws, lanes->nseg * lanes->rows, stage, lanes, st);
+}
+
+// keeps the first n[s] rows of lane s: its state and history from the checkpoints of window row s rows + n[s] - 1
+int fnx_window_commit_lanes(const FnxStackCfg* cfg, const FnxLayer* layers, void* ws, const FnxWindowLanes* lanes, const int* n, const int* tags,
+                            void* host_jobs, void* st) {
+    TRY(check_cfg(cfg));
+    FNX_REQUIRE(lanes && n && tags && lanes->S_host && lanes->hist_host, "commit: no lanes");
+    const FnxStackCfg& c = *cfg;
+    const Ws w = carve(c);
+    FnxCopyJob* hj = (FnxCopyJob*) host_jobs;
+    FNX_REQUIRE(hj, "commit: no host job table");
+    const size_t ch = (size_t) (2 * c.nk + c.nv) * FNX_HS, state = (size_t) c.nv * FNX_HS * FNX_HS;
+    int nj = 0;
+    for (int sI = 0; sI < lanes->nseg; ++sI) {
+        FNX_REQUIRE(n[sI] >= 1 && n[sI] <= lanes->rows, "commit: %d of lane %d's %d rows", n[sI], sI, lanes->rows);
+        if (n[sI] == lanes->rows) continue;
+        const size_t row = (size_t) sI * lanes->rows + n[sI] - 1;
+        const unsigned written = ((unsigned) tags[sI] & 1u) ^ 1u;
+        for (int l = 0; l < c.nlayers; ++l) {
+            if (layers[l].kind != 0) continue;
+            hj[nj++] = FnxCopyJob{lanes->S_host[l][sI], layers[l].snap + row * state, state * 4};
+            hj[nj++] = FnxCopyJob{lanes->hist_host[l][sI] + (size_t) written * 3 * ch, layers[l].hsnap + row * 3 * ch, 3 * ch * 4};
+        }
+    }
+    if (!nj) return 0;
+    FnxCopyJob* dj = (FnxCopyJob*) ((char*) ws + w.copy_jobs);
+    if (cudaMemcpyAsync(dj, hj, (size_t) nj * sizeof(FnxCopyJob), cudaMemcpyHostToDevice, strm(st)) != cudaSuccess)
+        return fail("commit: job table upload: %s", cudaGetErrorString(cudaGetLastError()));
+    return fnx_copy_many(dj, nj, st);
 }
 
 int fnx_window_commit(const FnxStackCfg* cfg, const FnxLayer* layers, void* ws, int T, int n, int tag, void* host_jobs, void* st) {

@@ -37,6 +37,10 @@ class GdnLanes(C.Structure):
     _fields_ = [("S", C.c_void_p), ("hist", C.c_void_p), ("ctl", C.c_void_p), ("row0", C.c_void_p), ("snap", C.c_void_p), ("hsnap", C.c_void_p)]
 
 
+class LaneRows(C.Structure):
+    _fields_ = [("pos", C.c_void_p), ("pt", C.c_void_p)]
+
+
 class KvPages(C.Structure):
     _fields_ = [("pt", C.c_void_p), ("page", C.c_size_t), ("rows", C.c_int), ("cap", C.c_int)]
 
@@ -58,6 +62,12 @@ class Layer(C.Structure):
                 ("wq", Q8S), ("wk", Q8S), ("wv", Q8S), ("wo", Q8S), ("q_norm", C.c_void_p), ("k_norm", C.c_void_p),
                 ("kc", C.c_void_p), ("vc", C.c_void_p), ("pages", KvPages),
                 ("router", C.c_void_p), ("gate_up", Experts), ("down", Experts), ("sh_gate_up", Q8S), ("sh_down", Q8S)]
+
+
+class WindowLanes(C.Structure):
+    _fields_ = [("nseg", C.c_int), ("rows", C.c_int), ("ctl", C.c_void_p), ("row0", C.c_void_p), ("row_pos", C.c_void_p), ("row_pt", C.c_void_p),
+                ("ctl_host", C.c_void_p), ("pt_host", C.c_void_p), ("S", C.c_void_p), ("hist", C.c_void_p), ("S_host", C.c_void_p),
+                ("hist_host", C.c_void_p)]
 
 
 class Head(C.Structure):
@@ -107,6 +117,7 @@ _SIGS = {
     "fnx_attn_prep_append": [_p, _p, _p, _p, _p, _p, _p, KvPages, _i, _i, _i, _p, _f, Rope, _i, _i, _i, _p],
     "fnx_attn_partial": [_p, _p, _p, KvPages, _p, _i, _i, _i, _p, _i, _i, _i, _p, _p],
     "fnx_attn_partial_exact": [_p, _p, _p, KvPages, _p, _i, _i, _i, _p, _i, _i, _i, _p, _p],
+    "fnx_attn_part_lanes": [_p, _p, _p, KvPages, LaneRows, _p, _i, _i, _i, _i, _i, _i, _p, _p],
     "fnx_attn_finish": [_p, _i, _i, _p, _p, _i, _i, _i, _i, _i, _p],
     "fnx_argmax": [_p, _i, _i, _i, _p, _p, _p, _p, _p],
     "fnx_penalize_row": [_p, _i, _p, _p, _p],
@@ -121,6 +132,8 @@ _SIGS = {
     "fnx_window_side_stream": [_p, _p, _p],
     "fnx_window_stage": [_p, _p, _p, _p, _i, _i, _p],
     "fnx_window_commit": [_p, _p, _p, _i, _i, _i, _p, _p],
+    "fnx_window_stage_lanes": [_p, _p, _p, _p, C.POINTER(WindowLanes), _i, _p],
+    "fnx_window_commit_lanes": [_p, _p, _p, C.POINTER(WindowLanes), _p, _p, _p, _p],
     "fnx_top_merge": [_p, _p, _i, _i, _p, _p],
     "fnx_ring_sum": [_p, _i, _i, C.POINTER(Ring), _p, _p],
 }

@@ -268,14 +268,85 @@ def vocab_slice(vocab, ncard, card):
     return v0, max(0, min(vocab, v0 + per) - v0)
 
 
+class LaneSet:
+    """The per-sequence side of a window of several sequences ("lanes": reference src/engine.hpp LaneDev): every lane's
+    DeltaNet states and conv histories (copies of the stack's, scaled a little apart), its run of pages of each attention
+    layer's K/V pool (the stack's cache cut into nseg equal runs of pages of `rpp` local rows), its (position, tag) words,
+    and the pointer tables the library's lanes entry points take (FnxWindowLanes)."""
+
+    def __init__(self, stack, nseg, rows, rpp=64):
+        assert nseg * rows <= L.MAXT
+        self.stack, self.nseg, self.rows, self.rpp = stack, nseg, rows, rpp
+        dev, s, T = stack.dev, stack.shape, nseg * rows
+        nl = len(s.kinds)
+        self.region = stack.kv_rows // nseg // rpp * rpp   # local rows of a lane's run of pages
+        assert self.region >= rpp, "the K/V pool is too small for %d lanes" % nseg
+        self.keep = []
+        ptr_dev = lambda ts: self._k(torch.tensor([t.data_ptr() for t in ts], dtype=torch.int64, device=dev))
+        ptr_host = lambda ps: self._k((C.c_void_p * len(ps))(*ps))
+        self.S, self.hist = {}, {}
+        S_dev, h_dev, S_host, h_host = [None] * nl, [None] * nl, [None] * nl, [None] * nl
+        gi = 0
+        for l, kind in enumerate(s.kinds):
+            if kind != 0:
+                continue
+            S0, h0 = stack.gdn_state[gi]
+            gi += 1
+            self.S[l] = [self._k((S0 * (1.0 + 0.05 * i)).contiguous()) for i in range(nseg)]
+            self.hist[l] = [self._k((h0 * (1.0 - 0.03 * i)).contiguous()) for i in range(nseg)]
+            S_dev[l], h_dev[l] = ptr_dev(self.S[l]).data_ptr(), ptr_dev(self.hist[l]).data_ptr()
+            S_host[l] = C.addressof(ptr_host([t.data_ptr() for t in self.S[l]]))
+            h_host[l] = C.addressof(ptr_host([t.data_ptr() for t in self.hist[l]]))
+        ppl = self.region // rpp   # pages per lane
+        self.pt = [self._k(torch.arange(i * ppl, (i + 1) * ppl, dtype=torch.int32, device=dev)) for i in range(nseg)]
+        self.ctl = self._k(torch.zeros((nseg, 2), dtype=torch.int32, device=dev))
+        self.row_pos = self._k(torch.zeros(T, dtype=torch.int32, device=dev))
+        self.row0 = self._k(torch.arange(nseg, dtype=torch.int32, device=dev) * rows)
+        ctl_ptrs = [self.ctl[i].data_ptr() for i in range(nseg)]
+        self.h_ctl = torch.zeros((nseg, 2), dtype=torch.int32).pin_memory()
+        self.h_row_pos = torch.zeros(T, dtype=torch.int32).pin_memory()
+        self.c = L.WindowLanes(
+            nseg, rows,
+            self._k(torch.tensor(ctl_ptrs, dtype=torch.int64, device=dev)).data_ptr(), self.row0.data_ptr(),
+            self._k(torch.tensor([self.row_pos[t:t + 1].data_ptr() for t in range(T)], dtype=torch.int64, device=dev)).data_ptr(),
+            self._k(torch.tensor([self.pt[t // rows].data_ptr() for t in range(T)], dtype=torch.int64, device=dev)).data_ptr(),
+            C.addressof(ptr_host(ctl_ptrs)), C.addressof(ptr_host([t.data_ptr() for t in self.pt])),
+            C.addressof(ptr_host(S_dev)), C.addressof(ptr_host(h_dev)), C.addressof(ptr_host(S_host)), C.addressof(ptr_host(h_host)))
+        # the attention layers' pools as pages of rpp local rows (a lane's table is filled in per call)
+        self.paged = L.KvPages(None, rpp * s.nkv * s.hd, rpp, 0)
+
+    def _k(self, x):
+        self.keep.append(x)
+        return x
+
+    def set_paged(self, on):
+        """Switches the stack's attention layers between the lanes' paged view of the K/V pool and the one-sequence view."""
+        for l, kind in enumerate(self.stack.shape.kinds):
+            if kind == 1:
+                self.stack.layers[l].pages = self.paged if on else L.KvPages(None, 0, 0, self.stack.kv_rows)
+
+    def positions(self, pos, tags):
+        """Lane i's window starts at position pos[i] with tag tags[i] (host lists)."""
+        for i in range(self.nseg):
+            self.h_ctl[i, 0], self.h_ctl[i, 1] = pos[i], tags[i]
+            for r in range(self.rows):
+                self.h_row_pos[i * self.rows + r] = pos[i] + r
+        self.ctl.copy_(self.h_ctl, non_blocking=True)
+        self.row_pos.copy_(self.h_row_pos, non_blocking=True)
+
+
 class WindowRunner:
     """One window of T rows as a CUDA graph on its own stream: embedding rows from the token ids, every stage, and
     between stages the collectives of the process group (NCCL) when there is more than one GPU."""
 
-    def __init__(self, stack, T, group=None, graph=True, overlap=True, sampled=False):
+    def __init__(self, stack, T, group=None, graph=True, overlap=True, sampled=False, lanes=None):
         import torch.distributed as dist
 
         self.stack, self.T, self.group = stack, T, group
+        self.lanes = lanes   # a LaneSet: the T rows are lanes.nseg sequences' rows (window_lanes, commit_lanes)
+        if lanes is not None:
+            assert T == lanes.nseg * lanes.rows
+            lanes.set_paged(True)
         self.dist = dist if stack.ncard > 1 else None
         cfg, s = stack.cfg, stack.shape
         lib = L.load()
@@ -372,7 +443,11 @@ class WindowRunner:
             L.call("fnx_window_side_stream", None, None, None)
         L.call("fnx_embed_rows", stack.embed.data_ptr(), self.ids.data_ptr(), self.x.data_ptr(), T, stack.shape.n, st)
         for i in range(self.nstages):
-            L.call("fnx_window_stage", C.byref(stack.cfg), stack.layers, C.byref(stack.head), stack.ws.data_ptr(), T, i, st)
+            if self.lanes is not None:
+                L.call("fnx_window_stage_lanes", C.byref(stack.cfg), stack.layers, C.byref(stack.head), stack.ws.data_ptr(), C.byref(self.lanes.c),
+                       i, st)
+            else:
+                L.call("fnx_window_stage", C.byref(stack.cfg), stack.layers, C.byref(stack.head), stack.ws.data_ptr(), T, i, st)
             if self.dist is None:
                 continue
             if self.after[i] == 1:
@@ -427,6 +502,37 @@ class WindowRunner:
         if int(self.h_err[0]) != 0:
             raise L.FnxError("window error word %d (bit 16: a non-finite logit)" % int(self.h_err[0]))
         return self.merge_best()
+
+    def window_lanes(self, rows, pos, tags):
+        """One window of several sequences: rows = the T token ids (lane i's rows at i * lanes.rows ..), pos[i] / tags[i]
+        lane i's first position and window tag.  Returns every row's argmax."""
+        T, ln = self.T, self.lanes
+        assert ln is not None, "build the runner with lanes=LaneSet(...)"
+        for p in pos:
+            if (p + ln.rows - 1) // 4 // self.stack.ncard * 4 + 4 > ln.region:
+                raise L.FnxError("a lane at position %d + %d rows is past its run of K/V pages (%d local rows)" % (p, ln.rows, ln.region))
+        self.h_ids[:T] = torch.as_tensor(rows, dtype=torch.int32)
+        with torch.cuda.stream(self.stream):
+            self.ids.copy_(self.h_ids, non_blocking=True)
+            ln.positions(pos, tags)
+            self.launch()
+            self.h_v.copy_(self.all_v, non_blocking=True)
+            self.h_i.copy_(self.all_i, non_blocking=True)
+            self.h_err.copy_(self.err, non_blocking=True)
+        self.stream.synchronize()
+        if int(self.h_err[0]) != 0:
+            raise L.FnxError("window error word %d (bit 16: a non-finite logit)" % int(self.h_err[0]))
+        return self.merge_best()
+
+    def commit_lanes(self, n, tags):
+        """Keep the first n[i] rows of lane i of the last window."""
+        ln = self.lanes
+        nn, tt = (C.c_int * ln.nseg)(*n), (C.c_int * ln.nseg)(*tags)
+        jobs = torch.zeros(len(self.stack.shape.kinds) * 2 * L.MAXT * C.sizeof(L.CopyJob), dtype=torch.uint8).pin_memory()
+        with torch.cuda.stream(self.stream):
+            L.call("fnx_window_commit_lanes", C.byref(self.stack.cfg), self.stack.layers, self.stack.ws.data_ptr(), C.byref(ln.c), nn, tt,
+                   jobs.data_ptr(), torch.cuda.current_stream().cuda_stream)
+        self.stream.synchronize()   # the job table is read by an asynchronous copy
 
     def merge_best(self):
         return merge_best(self.h_v, self.h_i)

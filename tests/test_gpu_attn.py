@@ -86,3 +86,45 @@ def test_attention_fast_scan_rising_scores(T, ctx, ramp):
     # stated against the largest output, 2e-5 of it
     err, top = np.abs(got["out"] - ref["out"]), np.abs(ref["out"]).max()
     assert err.max() <= 2e-5 * top, (err.max(), top)
+
+
+def test_attention_rows_of_several_sequences():
+    """A batched window: six rows of three sequences (2 + 1 + 3), each row at its lane's position on its lane's pages of one
+    paged pool; every row's partial as the exact scan of that lane alone gives it."""
+    import torch
+
+    from sfnx_b200 import lib as L
+    from tests import gpu_util as G
+
+    nq, nkv, hd, rpp = 24, 4, 256, 64   # local rows per page
+    lanes = [(2, 300, 71), (1, 37, 72), (3, 1000, 73)]
+    cs = [cases.attn_case(T=T, ctx=ctx, seed=seed) for T, ctx, seed in lanes]
+    refs = [cases.attn_oracle(c) for c in cs]
+    npages = [(r["kc"][0].shape[0] + rpp - 1) // rpp for r in refs]
+    rng = np.random.default_rng(74)
+    phys = rng.permutation(sum(npages) + 3)   # a few pages stay unused
+    pool_k = np.zeros((len(phys), rpp, nkv, hd), np.uint16)
+    pool_v = np.zeros_like(pool_k)
+    pts, at = [], 0
+    for r, n in zip(refs, npages):
+        pt = phys[at:at + n].astype(np.int32)
+        at += n
+        for j, pg in enumerate(pt):
+            rows = r["kc"][0][j * rpp:(j + 1) * rpp]
+            pool_k[pg, :len(rows)], pool_v[pg, :len(rows)] = rows, r["vc"][0][j * rpp:(j + 1) * rpp]
+        pts.append(G.dev(pt))
+    kc, vc = G.dev(pool_k), G.dev(pool_v)
+    qg = G.dev(np.concatenate([r["qg"] for r in refs]))
+    T = sum(T for T, _, _ in lanes)
+    pos = [G.dev(np.array([ctx + i], np.int32)) for (Tl, ctx, _) in lanes for i in range(Tl)]
+    row_pt = [pts[l] for l, (Tl, _, _) in enumerate(lanes) for _ in range(Tl)]
+    ppos = G.dev(np.array([t.data_ptr() for t in pos], np.uint64))
+    ppt = G.dev(np.array([t.data_ptr() for t in row_pt], np.uint64))
+    g = L.KvPages(None, rpp * nkv * hd, rpp, 0)
+    part = G.zeros((T, nq, hd + 2))
+    scratch = G.zeros(L.load().fnx_attn_scratch_floats(nq, hd, T))
+    L.call("fnx_attn_part_lanes", qg.data_ptr(), kc.data_ptr(), vc.data_ptr(), g, L.LaneRows(ppos.data_ptr(), ppt.data_ptr()), part.data_ptr(),
+           0, 1, T, nq, nkv, hd, scratch.data_ptr(), L.stream())
+    G.sync()
+    ref = np.concatenate([r["part"][0] for r in refs])
+    assert np.array_equal(G.host(part).view(np.uint32), ref.view(np.uint32))

@@ -224,3 +224,79 @@ def test_window_sampled_acceptance_matches_oracle():
         pos, tag, x = pos + n, tag + 1, toks[-1]
     L.load().fnx_rng_free(rng_dev)
     assert 4 <= total <= 64
+
+
+def test_window_of_several_sequences_equals_each_alone(monkeypatch):
+    """The reference's batch property (tools/batch_check.hpp: "batched lanes = alone"): three sequences x four rows in one
+    window of 12 rows give, bit for bit, the logits, DeltaNet states, conv histories and K/V rows that each sequence's
+    window of four rows gives alone, and cutting every lane back to its own accepted prefix gives the states the
+    one-sequence rollback gives."""
+    import torch
+
+    from sfnx_b200 import lib as L
+    from sfnx_b200.window import LaneSet, StackShape, SyntheticStack, WindowRunner
+
+    monkeypatch.setenv("FNX_ATTN_EXACT", "1")   # the one-sequence windows in the order of sums the lanes' scan uses
+    shape = StackShape(n=512, nexp=32, topk=4, ff=256, nkh=2, nvh=4, nq=4, nkv=2, hd=128, nrot=64, vocab=2048, kinds=(0, 1, 0, 1), ctx=300,
+                       kv_slack=256)
+    stack = SyntheticStack(shape, seed=11, device="cuda:0")
+    nseg, rows = 3, 4
+    lanes = LaneSet(stack, nseg, rows)
+    alone = WindowRunner(stack, rows, graph=False)
+    batched = WindowRunner(stack, nseg * rows, graph=False, lanes=lanes)
+    gdn = [l for l, k in enumerate(shape.kinds) if k == 0]
+    att = [l for l, k in enumerate(shape.kinds) if k == 1]
+    pool = {l: (stack.named[(l, "kc")], stack.named[(l, "vc")]) for l in att}
+    state0 = {(l, i): (lanes.S[l][i].clone(), lanes.hist[l][i].clone()) for l in gdn for i in range(nseg)}
+    pool0 = {l: (k.clone(), v.clone()) for l, (k, v) in pool.items()}
+
+    def restore():
+        for (l, i), (S, h) in state0.items():
+            lanes.S[l][i].copy_(S)
+            lanes.hist[l][i].copy_(h)
+        for l, (k, v) in pool0.items():
+            pool[l][0].copy_(k)
+            pool[l][1].copy_(v)
+        torch.cuda.synchronize()
+
+    rng = np.random.default_rng(12)
+    ids = [[int(v) for v in rng.integers(0, shape.vocab, rows)] for _ in range(nseg)]
+    pos, tags, keep = [40, 100, 77], [3, 8, 5], [2, 4, 1]
+    row_bytes = shape.nkv * shape.hd * 2
+    # ---- every lane alone: the stack's layers pointed at the lane's state and at its run of the K/V pool
+    restore()
+    lanes.set_paged(False)
+    want = []
+    for i in range(nseg):
+        for l in gdn:
+            stack.layers[l].S, stack.layers[l].hist = lanes.S[l][i].data_ptr(), lanes.hist[l][i].data_ptr()
+        for l in att:
+            stack.layers[l].kc = pool[l][0].data_ptr() + i * lanes.region * row_bytes
+            stack.layers[l].vc = pool[l][1].data_ptr() + i * lanes.region * row_bytes
+            stack.layers[l].pages = L.KvPages(None, 0, 0, lanes.region)
+        best = alone.window(ids[i], pos[i], tags[i])
+        logits = alone.logits.clone()
+        full = {l: (lanes.S[l][i].clone(), lanes.hist[l][i].clone()) for l in gdn}
+        alone.commit(keep[i], tags[i])
+        alone.stream.synchronize()
+        cut = {l: (lanes.S[l][i].clone(), lanes.hist[l][i].clone()) for l in gdn}
+        want.append((best, logits, full, cut))
+    pool_alone = {l: (k.clone(), v.clone()) for l, (k, v) in pool.items()}
+    # ---- the three together
+    restore()
+    for l in att:
+        stack.layers[l].kc, stack.layers[l].vc = pool[l][0].data_ptr(), pool[l][1].data_ptr()
+    lanes.set_paged(True)
+    best = batched.window_lanes([t for lane in ids for t in lane], pos, tags)
+    logits = batched.logits.clone()
+    for i in range(nseg):
+        assert list(best[i * rows:(i + 1) * rows]) == list(want[i][0]), i
+        assert torch.equal(logits[i * rows:(i + 1) * rows].view(torch.int32), want[i][1].view(torch.int32)), "lane %d logits" % i
+        for l in gdn:
+            assert torch.equal(lanes.S[l][i], want[i][2][l][0]) and torch.equal(lanes.hist[l][i], want[i][2][l][1]), (i, l)
+    for l in att:
+        assert torch.equal(pool[l][0], pool_alone[l][0]) and torch.equal(pool[l][1], pool_alone[l][1]), "appended K/V rows"
+    batched.commit_lanes(keep, tags)
+    for i in range(nseg):
+        for l in gdn:
+            assert torch.equal(lanes.S[l][i], want[i][3][l][0]) and torch.equal(lanes.hist[l][i], want[i][3][l][1]), ("cut", i, l)
