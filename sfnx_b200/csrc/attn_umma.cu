@@ -17,6 +17,7 @@
 #include "common.cuh"
 #include "exact_math.cuh"
 #include "moe_internal.cuh"
+#include "umma.cuh"
 
 namespace fnxk {
 
@@ -32,21 +33,11 @@ __device__ __forceinline__ size_t au_row_at(const FnxKvPages& g, int r, int nkv)
     if (!g.pt) return (size_t) r * nkv * AU_HD;
     return (size_t) g.pt[r / g.rows] * g.page + (size_t) (r % g.rows) * nkv * AU_HD;
 }
-__device__ __forceinline__ unsigned au_s32(const void* p) { return (unsigned) __cvta_generic_to_shared(p); }
-// K-major operand tile with the 128-byte swizzle: rows of 128 bytes, groups of 8 rows 1024 bytes apart
-__device__ __forceinline__ unsigned long long au_desc(unsigned addr) {
-    return (unsigned long long) ((addr & 0x3FFFF) >> 4) | (1ull << 16) | ((unsigned long long) (1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
-}
-__device__ __forceinline__ void au_mma(unsigned tmem, unsigned long long da, unsigned long long db, unsigned idesc, unsigned accumulate) {
-    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem), "l"(da),
-                 "l"(db), "r"(idesc), "r"(accumulate)
-                 : "memory");
-}
 __device__ __forceinline__ void au_ldsm4(unsigned& a, unsigned& b, unsigned& c, unsigned& d, const void* p) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(a), "=r"(b), "=r"(c), "=r"(d) : "r"(au_s32(p)));
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(a), "=r"(b), "=r"(c), "=r"(d) : "r"(um_s32(p)));
 }
 __device__ __forceinline__ void au_ldsm4t(unsigned& a, unsigned& b, unsigned& c, unsigned& d, const void* p) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(a), "=r"(b), "=r"(c), "=r"(d) : "r"(au_s32(p)));
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(a), "=r"(b), "=r"(c), "=r"(d) : "r"(um_s32(p)));
 }
 __device__ __forceinline__ void au_hmma(float (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0, unsigned b1) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
@@ -105,7 +96,7 @@ __global__ void __launch_bounds__(AU_THREADS) k_attn_umma(const AuArgs a) {
     const int qpk = a.nq / a.nkv, M = a.T * qpk;
     extern __shared__ __align__(1024) unsigned char au_smem[];
     // the swizzle is a function of the shared-memory address: operand tiles start on 1024-byte boundaries
-    unsigned char* Qhi = au_smem + ((1024u - (au_s32(au_smem) & 1023u)) & 1023u);   // 4 K-blocks x [128 rows x 128 B], swizzled
+    unsigned char* Qhi = au_smem + ((1024u - (um_s32(au_smem) & 1023u)) & 1023u);   // 4 K-blocks x [128 rows x 128 B], swizzled
     unsigned char* Qlo = Qhi + AU_QBYTES;
     unsigned char* Kst = Qlo + AU_QBYTES;               // [3 stages] 4 K-blocks x [32 rows x 128 B], swizzled
     __half* Vst = reinterpret_cast<__half*>(Kst + AU_KSTAGES * AU_KBYTES);   // [2 stages][32][LDV]
@@ -154,7 +145,7 @@ __global__ void __launch_bounds__(AU_THREADS) k_attn_umma(const AuArgs a) {
             asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst_base + dst[k]), "l"(src), "r"(valid ? 16 : 0));   // invalid rows: zeros
         }
     };
-    const unsigned ks_s = au_s32(Kst), vs_s = au_s32(Vst);
+    const unsigned ks_s = um_s32(Kst), vs_s = um_s32(Vst);
     auto load_k = [&](int c, int stage) { load_rows(a.kc, c, ks_s + stage * AU_KBYTES, kdst); };
     auto load_v = [&](int c, int stage) { load_rows(a.vc, c, vs_s + stage * AU_VBYTES, vdst); };
     load_k(c_begin, 0);
@@ -163,16 +154,16 @@ __global__ void __launch_bounds__(AU_THREADS) k_attn_umma(const AuArgs a) {
     {   // the queries' image, made by k_attn_qsplit
         const unsigned char* img = a.qsplit + (size_t) kvl * 2 * AU_QBYTES;
         for (int i = tid; i < 2 * AU_QBYTES / 16; i += nthreads)
-            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(au_s32(Qhi + (size_t) i * 16)), "l"(img + (size_t) i * 16));
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(um_s32(Qhi + (size_t) i * 16)), "l"(img + (size_t) i * 16));
     }
     asm volatile("cp.async.commit_group;");
     if (tid == 0) {
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(au_s32(&mbar[0])));
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(au_s32(&mbar[1])));
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(um_s32(&mbar[0])));
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(um_s32(&mbar[1])));
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 0) {   // 64 columns of tensor memory: two 128 x 32 fp32 score tiles
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(au_s32(&tmem_base)), "r"(64));
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(um_s32(&tmem_base)), "r"(64));
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
     }
     // the positions this thread's two rows may see, their running maxima and sums
@@ -188,17 +179,17 @@ __global__ void __launch_bounds__(AU_THREADS) k_attn_umma(const AuArgs a) {
     // on mbar[c & 1] tells the row warps that the tile is complete
     auto issue_scores = [&](int c) {
         const unsigned tb = tmem_base + (c & 1) * 32;
-        const unsigned long long dk = au_desc(au_s32(Kst + (size_t) (c % AU_KSTAGES) * AU_KBYTES));
-        const unsigned long long dh = au_desc(au_s32(Qhi)), dl = au_desc(au_s32(Qlo));
+        const unsigned long long dk = um_desc(um_s32(Kst + (size_t) (c % AU_KSTAGES) * AU_KBYTES));
+        const unsigned long long dh = um_desc(um_s32(Qhi)), dl = um_desc(um_s32(Qlo));
 #pragma unroll
         for (int kb = 0; kb < 4; ++kb)
 #pragma unroll
             for (int ks = 0; ks < 4; ++ks) {
                 const unsigned long long ob = (unsigned long long) ((kb * AU_CH * 128 + ks * 32) >> 4), oa = (unsigned long long) ((kb * AU_ROWS * 128 + ks * 32) >> 4);
-                au_mma(tb, dh + oa, dk + ob, idesc, kb | ks);
-                au_mma(tb, dl + oa, dk + ob, idesc, 1u);
+                um_mma(tb, dh + oa, dk + ob, idesc, kb | ks);
+                um_mma(tb, dl + oa, dk + ob, idesc, 1u);
             }
-        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(au_s32(&mbar[c & 1])) : "memory");
+        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(um_s32(&mbar[c & 1])) : "memory");
     };
     auto landed = [&] {   // this thread's copies are in shared memory and every thread's are visible to the tensor core
         asm volatile("cp.async.wait_group 0;" ::: "memory");
@@ -226,7 +217,7 @@ __global__ void __launch_bounds__(AU_THREADS) k_attn_umma(const AuArgs a) {
                 for (int spin = 0; spin < (1 << 22) && !ok; ++spin)
                     asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
                                  : "=r"(ok)
-                                 : "r"(au_s32(&mbar[buf])), "r"((i >> 1) & 1)
+                                 : "r"(um_s32(&mbar[buf])), "r"((i >> 1) & 1)
                                  : "memory");
                 if (!ok) {
                     alive = false;
@@ -346,27 +337,13 @@ __global__ void __launch_bounds__(AU_THREADS) k_attn_umma(const AuArgs a) {
 constexpr int AU2_KST = 3, AU2_VST = 2, AU2_PBYTES = AU_ROWS * 64;   // K, V stages; one P tile (hi or lo)
 constexpr unsigned AU2_COL_S = 256;   // tensor memory: O in columns 0..255, the two score tiles after it
 
-__device__ __forceinline__ unsigned long long au_desc_x(unsigned addr, unsigned lbo, unsigned sbo, unsigned layout) {
-    return (unsigned long long) ((addr & 0x3FFFF) >> 4) | ((unsigned long long) (lbo >> 4) << 16) | ((unsigned long long) (sbo >> 4) << 32) | (1ull << 46) |
-           ((unsigned long long) layout << 61);
-}
-__device__ __forceinline__ bool au_wait(unsigned long long* bar, unsigned parity, unsigned* fault) {
-    unsigned ok = 0;
-    for (int spin = 0; spin < (1 << 22) && !ok; ++spin)
-        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-                     : "=r"(ok)
-                     : "r"(au_s32(bar)), "r"(parity)
-                     : "memory");
-    if (!ok) atomicOr(fault, 1u);
-    return ok != 0;
-}
 
 __global__ void __launch_bounds__(AU_THREADS) k_attn_umma2(const AuArgs a) {
     constexpr int HD = AU_HD;
     const int split = blockIdx.x, kvl = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, nthreads = blockDim.x;
     const int qpk = a.nq / a.nkv, M = a.T * qpk;
     extern __shared__ __align__(1024) unsigned char au_smem[];
-    unsigned char* Qhi = au_smem + ((1024u - (au_s32(au_smem) & 1023u)) & 1023u);
+    unsigned char* Qhi = au_smem + ((1024u - (um_s32(au_smem) & 1023u)) & 1023u);
     unsigned char* Qlo = Qhi + AU_QBYTES;
     unsigned char* Kst = Qlo + AU_QBYTES;                       // [3] 4 K-blocks x [32 rows x 128 B], swizzled
     unsigned char* Vst = Kst + AU2_KST * AU_KBYTES;             // [2] the same form: 4 blocks of 64 dims x [32 rows x 128 B]
@@ -411,7 +388,7 @@ __global__ void __launch_bounds__(AU_THREADS) k_attn_umma2(const AuArgs a) {
                          "r"(valid ? 16 : 0));   // invalid rows: zeros
         }
     };
-    const unsigned ks_s = au_s32(Kst), vs_s = au_s32(Vst);
+    const unsigned ks_s = um_s32(Kst), vs_s = um_s32(Vst);
     auto load_k = [&](int c) { load_rows(a.kc, c_begin + c, ks_s + (c % AU2_KST) * AU_KBYTES); };
     auto load_v = [&](int c) { load_rows(a.vc, c_begin + c, vs_s + (c % AU2_VST) * AU_KBYTES); };
     load_k(0);
@@ -420,17 +397,17 @@ __global__ void __launch_bounds__(AU_THREADS) k_attn_umma2(const AuArgs a) {
     {   // the queries' image, made by k_attn_qsplit
         const unsigned char* img = a.qsplit + (size_t) kvl * 2 * AU_QBYTES;
         for (int i = tid; i < 2 * AU_QBYTES / 16; i += nthreads)
-            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(au_s32(Qhi + (size_t) i * 16)), "l"(img + (size_t) i * 16));
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(um_s32(Qhi + (size_t) i * 16)), "l"(img + (size_t) i * 16));
     }
     asm volatile("cp.async.commit_group;");
     if (tid == 0) {
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(au_s32(&mbar_s[0])));
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(au_s32(&mbar_s[1])));
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(au_s32(&mbar_o)));
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(um_s32(&mbar_s[0])));
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(um_s32(&mbar_s[1])));
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(um_s32(&mbar_o)));
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 0) {   // all 512 columns: O (256), two score tiles (64)
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(au_s32(&tmem_base)), "r"(512));
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(um_s32(&tmem_base)), "r"(512));
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
     }
     const int lim0 = worker && r0 < M ? au_kv_owned(pos0 + r0 % a.T, a.card, a.ncard) : 0;
@@ -441,27 +418,27 @@ __global__ void __launch_bounds__(AU_THREADS) k_attn_umma2(const AuArgs a) {
     const unsigned idesc_o = (1u << 4) | (1u << 16) | ((256u >> 3) << 17) | ((128u >> 4) << 24);   // O: N 256, B MN-major
     auto issue_scores = [&](int c) {
         const unsigned tb = tmem_base + AU2_COL_S + (c & 1) * 32;
-        const unsigned long long dk = au_desc(au_s32(Kst + (size_t) (c % AU2_KST) * AU_KBYTES));
-        const unsigned long long dh = au_desc(au_s32(Qhi)), dl = au_desc(au_s32(Qlo));
+        const unsigned long long dk = um_desc(um_s32(Kst + (size_t) (c % AU2_KST) * AU_KBYTES));
+        const unsigned long long dh = um_desc(um_s32(Qhi)), dl = um_desc(um_s32(Qlo));
 #pragma unroll
         for (int kb = 0; kb < 4; ++kb)
 #pragma unroll
             for (int ks = 0; ks < 4; ++ks) {
                 const unsigned long long ob = (unsigned long long) ((kb * AU_CH * 128 + ks * 32) >> 4), oa = (unsigned long long) ((kb * AU_ROWS * 128 + ks * 32) >> 4);
-                au_mma(tb, dh + oa, dk + ob, idesc_s, kb | ks);
-                au_mma(tb, dl + oa, dk + ob, idesc_s, 1u);
+                um_mma(tb, dh + oa, dk + ob, idesc_s, kb | ks);
+                um_mma(tb, dl + oa, dk + ob, idesc_s, 1u);
             }
-        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(au_s32(&mbar_s[c & 1])) : "memory");
+        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(um_s32(&mbar_s[c & 1])) : "memory");
     };
     auto issue_output = [&](int c) {   // O (+)= (Phi + Plo) V(c)
-        const unsigned long long dv = au_desc_x(au_s32(Vst + (size_t) (c % AU2_VST) * AU_KBYTES), AU_CH * 128, 1024, 2);
-        const unsigned long long dph = au_desc_x(au_s32(Pst), 16, 512, 4), dpl = au_desc_x(au_s32(Pst + AU2_PBYTES), 16, 512, 4);
+        const unsigned long long dv = um_desc_x(um_s32(Vst + (size_t) (c % AU2_VST) * AU_KBYTES), AU_CH * 128, 1024, 2);
+        const unsigned long long dph = um_desc_x(um_s32(Pst), 16, 512, 4), dpl = um_desc_x(um_s32(Pst + AU2_PBYTES), 16, 512, 4);
 #pragma unroll
         for (int ks = 0; ks < 2; ++ks) {
-            au_mma(tmem_base, dph + (unsigned long long) (ks * 32 >> 4), dv + (unsigned long long) (ks * 16 * 128 >> 4), idesc_o, c | ks);
-            au_mma(tmem_base, dpl + (unsigned long long) (ks * 32 >> 4), dv + (unsigned long long) (ks * 16 * 128 >> 4), idesc_o, 1u);
+            um_mma(tmem_base, dph + (unsigned long long) (ks * 32 >> 4), dv + (unsigned long long) (ks * 16 * 128 >> 4), idesc_o, c | ks);
+            um_mma(tmem_base, dpl + (unsigned long long) (ks * 32 >> 4), dv + (unsigned long long) (ks * 16 * 128 >> 4), idesc_o, 1u);
         }
-        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(au_s32(&mbar_o)) : "memory");
+        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(um_s32(&mbar_o)) : "memory");
     };
     auto sync_all = [&] {   // stores and landed copies of every thread visible to the tensor core, tensor-memory accesses ordered
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -484,7 +461,7 @@ __global__ void __launch_bounds__(AU_THREADS) k_attn_umma2(const AuArgs a) {
 #pragma unroll
         for (int j = 0; j < 4; ++j) sacc[j][0] = sacc[j][1] = sacc[j][2] = sacc[j][3] = -INFINITY;
         if (worker) {
-            bool ok = alive && au_wait(&mbar_s[buf], (i >> 1) & 1, a.fault);
+            bool ok = alive && um_wait(&mbar_s[buf], (i >> 1) & 1, a.fault);
             ok = __all_sync(0xffffffffu, ok);
             alive = alive && ok;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -524,7 +501,7 @@ __global__ void __launch_bounds__(AU_THREADS) k_attn_umma2(const AuArgs a) {
         if (up1) m1 = mx1;
         // ---- the accumulator and the P tile are free once the MMAs of the chunk before are done
         if (i > 0) {
-            bool ok = alive && au_wait(&mbar_o, (i - 1) & 1, a.fault);
+            bool ok = alive && um_wait(&mbar_o, (i - 1) & 1, a.fault);
             ok = __all_sync(0xffffffffu, ok);
             alive = alive && ok;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -592,7 +569,7 @@ __global__ void __launch_bounds__(AU_THREADS) k_attn_umma2(const AuArgs a) {
     }
     // ---- this split's partial: the accumulator out of tensor memory, m_ref, z per row
     {
-        bool ok = alive && au_wait(&mbar_o, (nc - 1) & 1, a.fault);
+        bool ok = alive && um_wait(&mbar_o, (nc - 1) & 1, a.fault);
         ok = __all_sync(0xffffffffu, ok);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         if (worker) {

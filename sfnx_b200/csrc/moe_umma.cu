@@ -21,6 +21,7 @@
 #include "common.cuh"
 #include "exact_math.cuh"
 #include "moe_internal.cuh"
+#include "umma.cuh"
 
 namespace fnxk {
 
@@ -28,28 +29,8 @@ constexpr int MU_BM = 128, MU_KC = 64, MU_NS = 3, MU_PROD = 256, MU_THREADS = MU
 constexpr int MU_ABYTES = MU_BM * 128, MU_BBYTES = MU_NMAX * 128, MU_STAGE = MU_ABYTES + MU_BBYTES;
 constexpr size_t MU_SMEM = (size_t) MU_NS * MU_STAGE + 1024;
 
-__device__ __forceinline__ unsigned mu_s32(const void* p) { return (unsigned) __cvta_generic_to_shared(p); }
-// K-major operand tile with the 128-byte swizzle: rows of 128 bytes, groups of 8 rows 1024 bytes apart
-__device__ __forceinline__ unsigned long long mu_desc(unsigned addr) {
-    return (unsigned long long) ((addr & 0x3FFFF) >> 4) | (1ull << 16) | ((unsigned long long) (1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
-}
-__device__ __forceinline__ void mu_mma(unsigned tmem, unsigned long long da, unsigned long long db, unsigned idesc, unsigned accumulate) {
-    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem), "l"(da),
-                 "l"(db), "r"(idesc), "r"(accumulate)
-                 : "memory");
-}
-__device__ __forceinline__ bool mu_wait(unsigned long long* bar, unsigned parity, unsigned* fault) {
-    unsigned ok = 0;
-    for (int spin = 0; spin < (1 << 22) && !ok; ++spin)
-        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-                     : "=r"(ok)
-                     : "r"(mu_s32(bar)), "r"(parity)
-                     : "memory");
-    if (!ok) atomicOr(fault, 1u);
-    return ok != 0;
-}
 __device__ __forceinline__ void mu_arrive(unsigned long long* bar) {
-    asm volatile("{\n\t.reg .b64 t;\n\tmbarrier.arrive.shared::cta.b64 t, [%0];\n\t}" ::"r"(mu_s32(bar)) : "memory");
+    asm volatile("{\n\t.reg .b64 t;\n\tmbarrier.arrive.shared::cta.b64 t, [%0];\n\t}" ::"r"(um_s32(bar)) : "memory");
 }
 
 // four bytes (each 0..255) as f16 pairs {b0, b1}, {b2, b3} less `bias`: 0x6400 | b is the f16 1024 + b exactly
@@ -192,7 +173,7 @@ __global__ void __launch_bounds__(MU_THREADS, 2) k_moe_umma(const MuArgs a) {
     const bool paired = ji + 1 < njobs && a.jobs[ji + 1].w == expert;
     extern __shared__ __align__(1024) unsigned char mu_smem[];
     // the swizzle is a function of the shared-memory address: operand tiles start on 1024-byte boundaries
-    unsigned char* stages = mu_smem + ((1024u - (mu_s32(mu_smem) & 1023u)) & 1023u);
+    unsigned char* stages = mu_smem + ((1024u - (um_s32(mu_smem) & 1023u)) & 1023u);
     __shared__ FnxBigJob jb, jb2;
     __shared__ __align__(8) unsigned long long full[MU_NS], empty[MU_NS], done;
     __shared__ unsigned tmem_base;
@@ -202,14 +183,14 @@ __global__ void __launch_bounds__(MU_THREADS, 2) k_moe_umma(const MuArgs a) {
     }
     if (tid == 0) {
         for (int s = 0; s < MU_NS; ++s) {
-            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(mu_s32(&full[s])), "r"(MU_PROD));
-            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(mu_s32(&empty[s])));
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(um_s32(&full[s])), "r"(MU_PROD));
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(um_s32(&empty[s])));
         }
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(mu_s32(&done)));
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(um_s32(&done)));
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == MU_PROD / 32) {   // 128 columns of tensor memory: the 128 x (64 + 64) fp32 result
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(mu_s32(&tmem_base)), "r"(MU_NMAX));
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(um_s32(&tmem_base)), "r"(MU_NMAX));
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -219,7 +200,7 @@ __global__ void __launch_bounds__(MU_THREADS, 2) k_moe_umma(const MuArgs a) {
     const int n = min(max(jb.n, 0), FNX_PF_JOB), n2 = paired ? min(max(jb2.n, 0), FNX_PF_JOB) : 0;
     const int ncol = paired ? FNX_PF_JOB + 16 * ((n2 + 15) / 16) : 16 * ((n + 15) / 16);   // N of the MMAs
     const int nk = (a.ncols + MU_KC - 1) / MU_KC, row0 = blockIdx.x * MU_BM;
-    const unsigned st_s = mu_s32(stages);
+    const unsigned st_s = um_s32(stages);
     bool alive = true;   // false after a wait ran out
     if (warp < MU_PROD / 32) {
         // ---- producers.  Weights: warp w owns rows 16 w .. + 15 of the tile, lanes 0..15 the first 32 columns of a step
@@ -242,7 +223,7 @@ __global__ void __launch_bounds__(MU_THREADS, 2) k_moe_umma(const MuArgs a) {
         auto xcopy = [&](int k) {   // the job's rows for step k, once its stage is free
             if (k < nk) {
                 const int s = k % MU_NS;
-                if (k >= MU_NS && alive) alive = mu_wait(&empty[s], (unsigned) ((k / MU_NS - 1) & 1), a.fault);
+                if (k >= MU_NS && alive) alive = um_wait(&empty[s], (unsigned) ((k / MU_NS - 1) & 1), a.fault);
                 const unsigned tile = st_s + s * MU_STAGE;
                 const bool in = 8 * xc < a.ncols - k * MU_KC;
 #pragma unroll
@@ -283,24 +264,24 @@ __global__ void __launch_bounds__(MU_THREADS, 2) k_moe_umma(const MuArgs a) {
 #pragma unroll 1
         for (int k = 0; k < nk; ++k) {
             const int s = k % MU_NS;
-            if (alive) alive = mu_wait(&full[s], (unsigned) ((k / MU_NS) & 1), a.fault);
+            if (alive) alive = um_wait(&full[s], (unsigned) ((k / MU_NS) & 1), a.fault);
             alive = __all_sync(0xffffffffu, alive);
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             if (lane == 0) {
-                const unsigned long long da = mu_desc(st_s + s * MU_STAGE), db = mu_desc(st_s + s * MU_STAGE + MU_ABYTES);
+                const unsigned long long da = um_desc(st_s + s * MU_STAGE), db = um_desc(st_s + s * MU_STAGE + MU_ABYTES);
 #pragma unroll
                 for (int ks = 0; ks < MU_KC / 16; ++ks)
-                    if (16 * ks < a.ncols - k * MU_KC) mu_mma(tmem_base, da + 2 * ks, db + 2 * ks, idesc, (unsigned) (k | ks));
-                asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(mu_s32(&empty[s])) : "memory");
+                    if (16 * ks < a.ncols - k * MU_KC) um_mma(tmem_base, da + 2 * ks, db + 2 * ks, idesc, (unsigned) (k | ks));
+                asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(um_s32(&empty[s])) : "memory");
             }
             __syncwarp();
         }
-        if (lane == 0) asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(mu_s32(&done)) : "memory");
+        if (lane == 0) asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(um_s32(&done)) : "memory");
     }
     // ---- the result out of tensor memory: warp w reads lanes 32 (w % 4) .. + 31 (its quarter), rows of the tile; warps
     // 0..3 take the first half of the job's rows, warps 4..7 the second; a warp's 32 lanes write 32 consecutive floats
     if (warp < MU_PROD / 32) {
-        bool ok = alive && mu_wait(&done, 0u, a.fault);
+        bool ok = alive && um_wait(&done, 0u, a.fault);
         ok = __all_sync(0xffffffffu, ok);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const int row = row0 + 32 * (warp & 3) + lane, cols = ncol / 2, c0 = (warp >> 2) * cols;
