@@ -213,7 +213,7 @@ def main():
     def device_step(i):
         with torch.cuda.stream(runner.stream):
             runner.ids[:T].copy_(d_ids[i], non_blocking=True)
-            runner.ctl.copy_(d_ctl[i], non_blocking=True)
+            runner.ctl_in.copy_(d_ctl[i], non_blocking=True)
             runner.launch()
         runner.commit(rec[i][3], rec[i][2])
 
@@ -263,7 +263,7 @@ def main():
         eager.h_ctl[0], eager.h_ctl[1] = p, tg
         with torch.cuda.stream(eager.stream):
             eager.ids.copy_(eager.h_ids, non_blocking=True)
-            eager.ctl.copy_(eager.h_ctl, non_blocking=True)
+            eager.ctl_in.copy_(eager.h_ctl, non_blocking=True)
         eager.stream.synchronize()
         lib.fnx_trace_begin()
         eager.launch()
@@ -337,7 +337,8 @@ def distinct_experts(stack, runner, step, T):
     counts = []
     with torch.cuda.stream(runner.stream):
         runner.ids[:T].copy_(torch.tensor(rows, dtype=torch.int32, device=stack.dev))
-        runner.ctl.copy_(torch.tensor([pos, tag], dtype=torch.int32, device=stack.dev))
+        runner.ctl_in.copy_(torch.tensor([pos, tag], dtype=torch.int32, device=stack.dev))
+        runner.ctl.copy_(runner.ctl_in)
         st = torch.cuda.current_stream().cuda_stream
         L.call("fnx_embed_rows", stack.embed.data_ptr(), runner.ids.data_ptr(), runner.x.data_ptr(), T, stack.shape.n, st)
         # the job count lives at a fixed place of the workspace; find it through the layout: run every stage and read it

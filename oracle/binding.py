@@ -56,6 +56,8 @@ def lib():
             build()
         _LIB = C.CDLL(so)
         _LIB.orc_q8s_row_dot.restype = C.c_float
+        _LIB.orc_d2h.restype = C.c_uint16
+        _LIB.orc_d2h.argtypes = [C.c_double]
         _LIB.orc_mt_unif.restype = C.c_double
         _LIB.orc_mt_next.restype = C.c_uint64
         _LIB.orc_argmax.restype = C.c_uint

@@ -31,6 +31,8 @@ static o_half d2h(double x) {
     return o_f2h(f);
 }
 
+o_half orc_d2h(double x) { return d2h(x); }
+
 /* the f16 weights of `rows` Q4_K rows of n columns */
 void orc_mma_weights_q4k(const uint8_t* A, int rows, int n, o_half* w) {
     const int nb = n / 256;

@@ -83,6 +83,7 @@ void orc_shared_expert(const int8_t* guq, const o_half* gud, const int8_t* dnq, 
 void orc_moe_combine(const float* part, const float* topw, const float* sh, const float* logits, int logit_stride, int sh_col,
                      float* out, int T, int n, int topk);
 /* the prompt path's experts: f16 weights with one rounding, sums in double (omma.c) */
+o_half orc_d2h(double x);
 void orc_mma_weights_q4k(const uint8_t* A, int rows, int n, o_half* w);
 void orc_mma_weights_q8(const int8_t* wq, const o_half* wd, int rows, int n, o_half* w);
 void orc_mma_weights_q6p(const uint8_t* QL, const uint8_t* QH, const int8_t* SC, const o_half* D, int rows, int n, o_half* w);

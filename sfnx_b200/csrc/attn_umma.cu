@@ -1,17 +1,16 @@
 // Position-split attention, the fast scan on Blackwell's fifth-generation tensor cores (head dimension 256).
 //
 // Same plan as attn_fast.cu (one CTA per KV head and range of owned positions, all T x (query heads per KV head) query
-// rows at once, K/V chunks of 32 positions through a cp.async ring, partial (acc, m, z) per split), but S = Q K^T is a
-// tcgen05.mma: the queries (split into high and low f16 halves, x = hi + lo) sit in shared memory as the A operand,
-// 128 rows x 256 dims in four K-blocks of 64 dims with the 128-byte swizzle, the chunk's K rows as the B operand in the
-// same form, and the 128 x 32 fp32 scores accumulate in tensor memory (32 MMAs of M 128, N 32, K 16: hi then lo).  One
-// thread issues them; tcgen05.commit signals an mbarrier.  Six warps then read the scores out of tensor memory with
+// rows at once, K/V chunks of 32 positions through a cp.async ring, partial (acc, m, z) per split), with both products
+// as tcgen05.mma.  S = Q K^T: the queries (split into high and low f16 halves, x = hi + lo) sit in shared memory as the A
+// operand, 128 rows x 256 dims in four K-blocks of 64 dims with the 128-byte swizzle, the chunk's K rows as the B operand
+// in the same form, and the 128 x 32 fp32 scores accumulate in tensor memory (32 MMAs of M 128, N 32, K 16: hi then lo).
+// One thread issues them; tcgen05.commit signals an mbarrier.  Six warps then read the scores out of tensor memory with
 // tcgen05.ld.16x256b, whose register layout is the accumulator fragment of mma.sync m16n8 (a warp reads the 16 rows it
-// owns: warp w may touch lanes 32 (w % 4) .. + 31 of tensor memory, so the 16-row tiles go to warps 0, 4, 1, 5, 2, 6 and
-// warps 3 and 7 only help with the copies); the online softmax step and O += P V stay as in the mma.sync scan (the
-// weights as high + low f16 halves, accumulators in registers, rescaled every chunk).
-// The legacy mma.sync path measured 2.2 us of 4.1 us per chunk in S = Q K^T; here those MMAs take a few hundred cycles.
-// Every wait on the mbarrier is bounded; on a timeout the fault word is set and the CTA finishes with what it has.
+// owns: warp w may touch lanes 32 (w % 4) .. + 31 of tensor memory, so the 16-row tiles go to warps 0, 4, 1, 5, 2, 6;
+// warp 3 issues the MMAs and warp 7 makes the copies).  O += P V is described further down.
+// The mma.sync scan measured 2.2 us of 4.1 us per chunk in S = Q K^T; here those MMAs take a few hundred cycles.
+// Every wait on an mbarrier is bounded; on a timeout the fault word is set and the CTA finishes with what it has.
 #include <cstdlib>
 
 #include "common.cuh"
@@ -21,8 +20,8 @@
 
 namespace fnxk {
 
-constexpr int AU_CH = 32, AU_HD = 256, AU_LDV = AU_HD + 8, AU_LDP = AU_CH + 8, AU_ROWS = 128, AU_KSTAGES = 3, AU_VSTAGES = 2;
-constexpr int AU_QBYTES = 4 * AU_ROWS * 128, AU_KBYTES = 4 * AU_CH * 128, AU_VBYTES = AU_CH * AU_LDV * 2, AU_THREADS = 256;
+constexpr int AU_CH = 32, AU_HD = 256, AU_ROWS = 128;
+constexpr int AU_QBYTES = 4 * AU_ROWS * 128, AU_KBYTES = 4 * AU_CH * 128, AU_THREADS = 256;
 
 __host__ __device__ inline int au_kv_owned(int p, int card, int ncard) {
     const int b = p / 4;
@@ -32,17 +31,6 @@ __host__ __device__ inline int au_kv_owned(int p, int card, int ncard) {
 __device__ __forceinline__ size_t au_row_at(const FnxKvPages& g, int r, int nkv) {
     if (!g.pt) return (size_t) r * nkv * AU_HD;
     return (size_t) g.pt[r / g.rows] * g.page + (size_t) (r % g.rows) * nkv * AU_HD;
-}
-__device__ __forceinline__ void au_ldsm4(unsigned& a, unsigned& b, unsigned& c, unsigned& d, const void* p) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(a), "=r"(b), "=r"(c), "=r"(d) : "r"(um_s32(p)));
-}
-__device__ __forceinline__ void au_ldsm4t(unsigned& a, unsigned& b, unsigned& c, unsigned& d, const void* p) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(a), "=r"(b), "=r"(c), "=r"(d) : "r"(um_s32(p)));
-}
-__device__ __forceinline__ void au_hmma(float (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0, unsigned b1) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 __device__ __forceinline__ void au_split(float x, __half& hi, __half& lo) {
     hi = __float2half_rn(x);
@@ -90,240 +78,6 @@ __global__ void __launch_bounds__(256) k_attn_qsplit(const AuArgs a) {
     *reinterpret_cast<unsigned*>(img + AU_QBYTES + off) = (unsigned) __half_as_ushort(l0) | ((unsigned) __half_as_ushort(l1) << 16);
 }
 
-__global__ void __launch_bounds__(AU_THREADS) k_attn_umma(const AuArgs a) {
-    constexpr int HD = AU_HD, NT = HD / 8;
-    const int split = blockIdx.x, kvl = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, nthreads = blockDim.x;
-    const int qpk = a.nq / a.nkv, M = a.T * qpk;
-    extern __shared__ __align__(1024) unsigned char au_smem[];
-    // the swizzle is a function of the shared-memory address: operand tiles start on 1024-byte boundaries
-    unsigned char* Qhi = au_smem + ((1024u - (um_s32(au_smem) & 1023u)) & 1023u);   // 4 K-blocks x [128 rows x 128 B], swizzled
-    unsigned char* Qlo = Qhi + AU_QBYTES;
-    unsigned char* Kst = Qlo + AU_QBYTES;               // [3 stages] 4 K-blocks x [32 rows x 128 B], swizzled
-    __half* Vst = reinterpret_cast<__half*>(Kst + AU_KSTAGES * AU_KBYTES);   // [2 stages][32][LDV]
-    __shared__ __align__(8) unsigned long long mbar[2];
-    __shared__ unsigned tmem_base;
-    pdl_wait();   // the rows appended by the kernel before are among the positions read
-    pdl_go();
-    const int pos0 = *a.pos0;
-    const int ctx_max = au_kv_owned(pos0 + a.T - 1, a.card, a.ncard);
-    const int nchunks = (ctx_max + AU_CH - 1) / AU_CH, cps = (nchunks + a.nsplit - 1) / a.nsplit;
-    const int c_begin = split * cps, nc = max(0, min(nchunks, c_begin + cps) - c_begin);
-    float* out = a.scratch + ((size_t) (kvl * a.nsplit + split) * M) * (HD + 2);
-    // warp w works on the 16-row tile 2 (w % 4) + w / 4 (tiles 0..5; warps 3 and 7 have none): its rows are lanes
-    // 32 (w % 4) + 16 (w / 4) .. + 15 of tensor memory, inside the quarter the warp may read
-    const int tile = (warp & 3) * 2 + (warp >> 2);
-    const bool worker = (warp & 3) != 3;
-    const int r0 = tile * 16 + (lane >> 2), r1 = r0 + 8;   // this thread's rows of its tile
-    if (nc == 0) {   // nothing owned in this range: an empty partial
-        for (int i = tid; i < M * (HD + 2); i += nthreads) out[i] = (i % (HD + 2)) == HD ? -INFINITY : 0.f;
-        return;
-    }
-    // ---- the copies: a thread always moves the same 16-byte column piece (seg) of rows warp, warp + 8, .. of a chunk, so
-    // its shared-memory offsets are fixed and (without a page table) its global addresses advance by a constant
-    const int seg = lane, rowb = warp;
-    const size_t row_elems = (size_t) a.nkv * HD;
-    unsigned kdst[AU_CH / 8], vdst[AU_CH / 8];
-#pragma unroll
-    for (int k = 0; k < AU_CH / 8; ++k) {
-        const int row = rowb + 8 * k;
-        kdst[k] = (seg >> 3) * (AU_CH * 128) + row * 128 + (((seg & 7) ^ (row & 7)) << 4);
-        vdst[k] = row * AU_LDV * 2 + seg * 16;
-    }
-    auto load_rows = [&](const uint16_t* cache, int c, unsigned dst_base, const unsigned (&dst)[AU_CH / 8]) {
-        if (!a.g.pt && (c + 1) * AU_CH <= ctx_max) {   // a whole chunk of contiguous rows
-            const uint16_t* src = cache + ((size_t) c * AU_CH + rowb) * row_elems + (size_t) kvl * HD + seg * 8;
-#pragma unroll
-            for (int k = 0; k < AU_CH / 8; ++k)
-                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst_base + dst[k]), "l"(src + (size_t) 8 * k * row_elems));
-            return;
-        }
-#pragma unroll
-        for (int k = 0; k < AU_CH / 8; ++k) {
-            const int pos = c * AU_CH + rowb + 8 * k;
-            const bool valid = pos < ctx_max;
-            const uint16_t* src = cache + au_row_at(a.g, valid ? pos : 0, a.nkv) + (size_t) kvl * HD + seg * 8;
-            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst_base + dst[k]), "l"(src), "r"(valid ? 16 : 0));   // invalid rows: zeros
-        }
-    };
-    const unsigned ks_s = um_s32(Kst), vs_s = um_s32(Vst);
-    auto load_k = [&](int c, int stage) { load_rows(a.kc, c, ks_s + stage * AU_KBYTES, kdst); };
-    auto load_v = [&](int c, int stage) { load_rows(a.vc, c, vs_s + stage * AU_VBYTES, vdst); };
-    load_k(c_begin, 0);
-    load_v(c_begin, 0);
-    if (nc > 1) load_k(c_begin + 1, 1);
-    {   // the queries' image, made by k_attn_qsplit
-        const unsigned char* img = a.qsplit + (size_t) kvl * 2 * AU_QBYTES;
-        for (int i = tid; i < 2 * AU_QBYTES / 16; i += nthreads)
-            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(um_s32(Qhi + (size_t) i * 16)), "l"(img + (size_t) i * 16));
-    }
-    asm volatile("cp.async.commit_group;");
-    if (tid == 0) {
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(um_s32(&mbar[0])));
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(um_s32(&mbar[1])));
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    if (warp == 0) {   // 64 columns of tensor memory: two 128 x 32 fp32 score tiles
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(um_s32(&tmem_base)), "r"(64));
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
-    }
-    // the positions this thread's two rows may see, their running maxima and sums
-    const int lim0 = worker && r0 < M ? au_kv_owned(pos0 + r0 % a.T, a.card, a.ncard) : 0;
-    const int lim1 = worker && r1 < M ? au_kv_owned(pos0 + r1 % a.T, a.card, a.ncard) : 0;
-    float m0 = -INFINITY, m1 = -INFINITY, z0 = 0.f, z1 = 0.f;
-    float o[NT][4];
-#pragma unroll
-    for (int nt = 0; nt < NT; ++nt) o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.f;
-    const float rs = 1.0f / sqrtf((float) HD);
-    const unsigned idesc = (1u << 4) | ((32u >> 3) << 17) | ((128u >> 4) << 24);   // D f32, A and B f16 K-major, N 32, M 128
-    // S(c) = (Qhi + Qlo) K(c)^T into score tile c & 1, by one thread of a warp that has no rows of its own; the arrival
-    // on mbar[c & 1] tells the row warps that the tile is complete
-    auto issue_scores = [&](int c) {
-        const unsigned tb = tmem_base + (c & 1) * 32;
-        const unsigned long long dk = um_desc(um_s32(Kst + (size_t) (c % AU_KSTAGES) * AU_KBYTES));
-        const unsigned long long dh = um_desc(um_s32(Qhi)), dl = um_desc(um_s32(Qlo));
-#pragma unroll
-        for (int kb = 0; kb < 4; ++kb)
-#pragma unroll
-            for (int ks = 0; ks < 4; ++ks) {
-                const unsigned long long ob = (unsigned long long) ((kb * AU_CH * 128 + ks * 32) >> 4), oa = (unsigned long long) ((kb * AU_ROWS * 128 + ks * 32) >> 4);
-                um_mma(tb, dh + oa, dk + ob, idesc, kb | ks);
-                um_mma(tb, dl + oa, dk + ob, idesc, 1u);
-            }
-        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(um_s32(&mbar[c & 1])) : "memory");
-    };
-    auto landed = [&] {   // this thread's copies are in shared memory and every thread's are visible to the tensor core
-        asm volatile("cp.async.wait_group 0;" ::: "memory");
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-        __syncthreads();
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    };
-    landed();
-    const bool issuer = tid == 3 * 32;   // warp 3, lane 0
-    if (issuer) issue_scores(0);
-    bool alive = true;   // false after a wait ran out
-#pragma unroll 1
-    for (int i = 0; i < nc; ++i) {
-        const int buf = i & 1;
-        // the copies two chunks (K) and one chunk (V) ahead; their stages were last read a chunk ago, before the barrier
-        if (i + 2 < nc) load_k(c_begin + i + 2, (i + 2) % AU_KSTAGES);
-        if (i + 1 < nc) load_v(c_begin + i + 1, buf ^ 1);
-        asm volatile("cp.async.commit_group;");
-        if (issuer && i + 1 < nc) issue_scores(i + 1);   // the next chunk's scores while this chunk's are used
-        if (worker) {
-            // ---- the chunk's scores of this warp's 16 rows, out of tensor memory in the mma.sync accumulator layout
-            unsigned ok = 0;
-            if (alive) {
-                for (int spin = 0; spin < (1 << 22) && !ok; ++spin)
-                    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-                                 : "=r"(ok)
-                                 : "r"(um_s32(&mbar[buf])), "r"((i >> 1) & 1)
-                                 : "memory");
-                if (!ok) {
-                    alive = false;
-                    atomicOr(a.fault, 1u);
-                }
-            }
-            ok = __all_sync(0xffffffffu, ok);   // the tensor-memory load below is one instruction of the whole warp
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            float sacc[4][4];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) sacc[j][0] = sacc[j][1] = sacc[j][2] = sacc[j][3] = -INFINITY;   // when the scores never came
-            if (ok) {
-                unsigned r[16];
-                asm volatile("tcgen05.ld.sync.aligned.16x256b.x4.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-                             : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-                               "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-                             : "r"(tmem_base + buf * 32 + ((unsigned) (tile * 16) << 16)));
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-                for (int j = 0; j < 4; ++j)
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) sacc[j][e] = __uint_as_float(r[4 * j + e]);
-            }
-            // ---- online softmax step per row (a row's 32 scores sit in the 4 lanes of a quad)
-            const int pc = (c_begin + i) * AU_CH + 2 * (lane & 3);
-            float mx0 = -INFINITY, mx1 = -INFINITY;
-#pragma unroll
-            for (int j = 0; j < 4; ++j)
-#pragma unroll
-                for (int e = 0; e < 2; ++e) {
-                    const int pcol = pc + 8 * j + e;
-                    sacc[j][e] = pcol < lim0 ? sacc[j][e] * rs : -INFINITY;
-                    sacc[j][2 + e] = pcol < lim1 ? sacc[j][2 + e] * rs : -INFINITY;
-                    mx0 = fmaxf(mx0, sacc[j][e]);
-                    mx1 = fmaxf(mx1, sacc[j][2 + e]);
-                }
-            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
-            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
-            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
-            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
-            const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
-            const float sc0 = m0 == -INFINITY ? 0.f : __expf(m0 - mn0), sc1 = m1 == -INFINITY ? 0.f : __expf(m1 - mn1);
-            float ps0 = 0.f, ps1 = 0.f;
-#pragma unroll
-            for (int j = 0; j < 4; ++j)
-#pragma unroll
-                for (int e = 0; e < 2; ++e) {
-                    sacc[j][e] = sacc[j][e] == -INFINITY ? 0.f : __expf(sacc[j][e] - mn0);
-                    sacc[j][2 + e] = sacc[j][2 + e] == -INFINITY ? 0.f : __expf(sacc[j][2 + e] - mn1);
-                    ps0 += sacc[j][e];
-                    ps1 += sacc[j][2 + e];
-                }
-            ps0 += __shfl_xor_sync(0xffffffffu, ps0, 1);
-            ps0 += __shfl_xor_sync(0xffffffffu, ps0, 2);
-            ps1 += __shfl_xor_sync(0xffffffffu, ps1, 1);
-            ps1 += __shfl_xor_sync(0xffffffffu, ps1, 2);
-            z0 = z0 * sc0 + ps0;
-            z1 = z1 * sc1 + ps1;
-            m0 = mn0;
-            m1 = mn1;
-#pragma unroll
-            for (int nt = 0; nt < NT; ++nt) {
-                o[nt][0] *= sc0;
-                o[nt][1] *= sc0;
-                o[nt][2] *= sc1;
-                o[nt][3] *= sc1;
-            }
-            // ---- O += P V, the weights as high + low f16 halves
-            const __half* Vs = Vst + (size_t) buf * AU_CH * AU_LDV;
-#pragma unroll
-            for (int kk = 0; kk < 2; ++kk) {
-                unsigned ph[4], pl[4];
-                au_split2(sacc[2 * kk][0], sacc[2 * kk][1], ph[0], pl[0]);
-                au_split2(sacc[2 * kk][2], sacc[2 * kk][3], ph[1], pl[1]);
-                au_split2(sacc[2 * kk + 1][0], sacc[2 * kk + 1][1], ph[2], pl[2]);
-                au_split2(sacc[2 * kk + 1][2], sacc[2 * kk + 1][3], ph[3], pl[3]);
-                const __half* vrow = Vs + (size_t) (16 * kk + (lane & 7) + 8 * ((lane >> 3) & 1)) * AU_LDV + 8 * (lane >> 4);
-#pragma unroll
-                for (int n2 = 0; n2 < NT / 2; ++n2) {
-                    unsigned b[4];
-                    au_ldsm4t(b[0], b[1], b[2], b[3], vrow + n2 * 16);
-                    au_hmma(o[2 * n2], ph[0], ph[1], ph[2], ph[3], b[0], b[1]);
-                    au_hmma(o[2 * n2], pl[0], pl[1], pl[2], pl[3], b[0], b[1]);
-                    au_hmma(o[2 * n2 + 1], ph[0], ph[1], ph[2], ph[3], b[2], b[3]);
-                    au_hmma(o[2 * n2 + 1], pl[0], pl[1], pl[2], pl[3], b[2], b[3]);
-                }
-            }
-        }
-        landed();   // the next chunks' K and V are in place, this chunk's stages and score tile are free
-    }
-    // ---- this split's partial: acc[HD], m, z per row
-    if (worker) {
-#pragma unroll
-        for (int nt = 0; nt < NT; ++nt) {
-            const int col = nt * 8 + 2 * (lane & 3);
-            if (r0 < M) *reinterpret_cast<float2*>(out + (size_t) r0 * (HD + 2) + col) = make_float2(o[nt][0], o[nt][1]);
-            if (r1 < M) *reinterpret_cast<float2*>(out + (size_t) r1 * (HD + 2) + col) = make_float2(o[nt][2], o[nt][3]);
-        }
-        if ((lane & 3) == 0) {
-            if (r0 < M) out[(size_t) r0 * (HD + 2) + HD] = m0, out[(size_t) r0 * (HD + 2) + HD + 1] = z0;
-            if (r1 < M) out[(size_t) r1 * (HD + 2) + HD] = m1, out[(size_t) r1 * (HD + 2) + HD + 1] = z1;
-        }
-    }
-    if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(64));
-}
-
 // ---------------------------------------------------------------- both products on the tensor cores
 // O += P V as tcgen05.mma too: the weights P of a chunk go to shared memory as the A operand (128 rows x 32 positions,
 // high and low f16 halves, 64-byte swizzle), the chunk's V rows are the B operand as they lie in memory (dims
@@ -357,7 +111,7 @@ __global__ void __launch_bounds__(AU_THREADS) k_attn_umma2(const AuArgs a) {
     const int nchunks = (ctx_max + AU_CH - 1) / AU_CH, cps = (nchunks + a.nsplit - 1) / a.nsplit;
     const int c_begin = split * cps, nc = max(0, min(nchunks, c_begin + cps) - c_begin);
     float* out = a.scratch + ((size_t) (kvl * a.nsplit + split) * M) * (HD + 2);
-    const int tile = (warp & 3) * 2 + (warp >> 2);   // see k_attn_umma: which 16 rows this warp may read and owns
+    const int tile = (warp & 3) * 2 + (warp >> 2);   // the 16 rows this warp owns: inside the quarter of tensor memory it may read
     const bool worker = (warp & 3) != 3;
     const int r0 = tile * 16 + (lane >> 2), r1 = r0 + 8, q4 = lane & 3;
     if (nc == 0) {
@@ -606,30 +360,21 @@ __global__ void __launch_bounds__(AU_THREADS) k_attn_umma2(const AuArgs a) {
 
 size_t attn_umma2_smem() { return (size_t) 2 * AU_QBYTES + (AU2_KST + AU2_VST) * AU_KBYTES + 2 * AU2_PBYTES + 1024; }
 
-size_t attn_umma_smem() { return (size_t) 2 * AU_QBYTES + AU_KSTAGES * AU_KBYTES + AU_VSTAGES * AU_VBYTES + 1024; }
-
 // the scan part of fnx_attn_partial for head dimension 256 and at most 96 query rows a KV head; -1 when it does not apply
 int attn_umma_launch(const float* qg, const uint16_t* kc, const uint16_t* vc, FnxKvPages g, float* scratch, int card, int ncard, int T,
                      const int* pos0, int nq, int nkv, int nsplit, cudaStream_t st) {
     const int M = T * (nq / nkv);
     unsigned* fault = device_fault_word();
     if (M > 96 || nkv > 8 || !fault) return -1;
-    const size_t sm = attn_umma_smem();
-    if (cudaFuncSetAttribute(k_attn_umma, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) sm) != cudaSuccess) return -1;
     // the queries' image sits in the scratch after the splits' partials (fnx_attn_scratch_floats leaves room for it)
     unsigned char* qsplit = reinterpret_cast<unsigned char*>(scratch + (size_t) nkv * nsplit * M * (AU_HD + 2));
     if ((uintptr_t) qsplit % 16) return -1;
     AuArgs a{qg, kc, vc, g, scratch, qsplit, nq, nkv, T, card, ncard, nsplit, pos0, fault};
     launch(0, k_attn_qsplit, (nkv * AU_ROWS * (AU_HD / 2) + 255) / 256, 256, 0, st, a);
     if (launch_ok("attn query split")) return 1;
-    static const bool pv_legacy = getenv("FNX_ATTN_PV_MMA") != nullptr;   // a tuning knob: O += P V on mma.sync (k_attn_umma)
-    if (!pv_legacy) {
-        const size_t sm2 = attn_umma2_smem();
-        if (cudaFuncSetAttribute(k_attn_umma2, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) sm2) != cudaSuccess) return -1;
-        launch(6, k_attn_umma2, dim3(nsplit, nkv), AU_THREADS, sm2, st, a);
-        return launch_ok("attn scan (tcgen05)");
-    }
-    launch(6, k_attn_umma, dim3(nsplit, nkv), AU_THREADS, sm, st, a);
+    const size_t sm2 = attn_umma2_smem();
+    if (cudaFuncSetAttribute(k_attn_umma2, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) sm2) != cudaSuccess) return -1;
+    launch(6, k_attn_umma2, dim3(nsplit, nkv), AU_THREADS, sm2, st, a);
     return launch_ok("attn scan (tcgen05)");
 }
 

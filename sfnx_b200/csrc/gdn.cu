@@ -139,8 +139,11 @@ __global__ void __cluster_dims__(GDN_Q, 1, 1) __launch_bounds__(GDN_THREADS, 2) 
         for (int gI = 0; gI < 4; ++gI) xs[0][t][lane][gI] = fmul(qv[gI], rq), xs[1][t][lane][gI] = fmul(kv[gI], rk);
     }
     __syncthreads();
-    // ---- the delta rule over the rows
+    // ---- the delta rule over the rows.  A column's four parts sit in warps w, w + 4, w + 8, w + 12 (w = the column's
+    // eighth of the block's 32), so the exchange of their sums needs only those four warps to meet: a named barrier per
+    // group of four warps instead of the whole block's
     const float scale = ex_rsqrt((float) HS);
+    auto group_sync = [&] { asm volatile("bar.sync %0, 128;" ::"r"(1 + (warp & 3)) : "memory"); };
 #pragma unroll 1
     for (int t = 0; t < T; ++t) {
         const float gv = gates[t][0], bv = gates[t][1];
@@ -153,7 +156,7 @@ __global__ void __cluster_dims__(GDN_Q, 1, 1) __launch_bounds__(GDN_THREADS, 2) 
         kj = fadd(kj, __shfl_xor_sync(0xffffffffu, kj, 1));   // (k0 + k1), (k2 + k3)
         kj = fadd(kj, __shfl_xor_sync(0xffffffffu, kj, 2));
         if (j == 0) pk[part][cl] = kj;
-        __syncthreads();
+        group_sync();
         const float kvd = fadd(fadd(pk[0][cl], pk[1][cl]), fadd(pk[2][cl], pk[3][cl]));
         const float delta = fmul(ffma(-gv, kvd, vs[t][cl]), bv);
         float aj = 0.f;
@@ -170,8 +173,8 @@ __global__ void __cluster_dims__(GDN_Q, 1, 1) __launch_bounds__(GDN_THREADS, 2) 
 #pragma unroll
             for (int i = 0; i < 8; ++i) __stcs(sp + (size_t) 4 * i * HS, s[i]);
         }
-        __syncthreads();
-        if (tid < GDN_QC) osm[t][tid] = fmul(fadd(fadd(pa[0][tid], pa[1][tid]), fadd(pa[2][tid], pa[3][tid])), scale);
+        group_sync();
+        if (part == 0 && j == 0) osm[t][cl] = fmul(fadd(fadd(pa[0][cl], pa[1][cl]), fadd(pa[2][cl], pa[3][cl])), scale);
     }
 #pragma unroll
     for (int i = 0; i < 8; ++i) st[(size_t) 4 * i * HS] = s[i];

@@ -355,7 +355,10 @@ class WindowRunner:
         assert 0 < self.nstages <= 1024, lib.fnx_last_error()
         self.after = list(after[: self.nstages])
         self.stream = torch.cuda.Stream()
-        self.ids = torch.zeros(L.MAXT, dtype=torch.int32, device=stack.dev)
+        # what a window takes from the host, one buffer and one copy: the token ids, then (position, tag); the window's
+        # first node copies the pair into the workspace's control words
+        self.d_in = torch.zeros(L.MAXT + 2, dtype=torch.int32, device=stack.dev)
+        self.ids, self.ctl_in = self.d_in[:L.MAXT], self.d_in[L.MAXT:]
         self.x = stack.buf(0, torch.float32, T * s.n)
         self.bo = stack.buf(1, torch.float32, T * s.n)
         self.partials = stack.buf(2, torch.float32, stack.ncard * T * s.nq * (s.hd + 2))
@@ -364,14 +367,18 @@ class WindowRunner:
         self.err = stack.buf(5, torch.int32, 1)
         self.ctl = stack.buf(6, torch.int32, 2)
         self.logits = stack.buf(7, torch.float32, T * stack.vrows).view(T, stack.vrows)
-        # what the host reads back: every GPU's (value, index) per row and the error word
-        self.all_v = torch.zeros((stack.ncard, T), dtype=torch.float32, device=stack.dev)
-        self.all_i = torch.zeros((stack.ncard, T), dtype=torch.int32, device=stack.dev)
-        self.h_ids = torch.zeros(L.MAXT, dtype=torch.int32).pin_memory()
-        self.h_ctl = torch.zeros(2, dtype=torch.int32).pin_memory()
-        self.h_v = torch.zeros((stack.ncard, T), dtype=torch.float32).pin_memory()
-        self.h_i = torch.zeros((stack.ncard, T), dtype=torch.int32).pin_memory()
-        self.h_err = torch.zeros(1, dtype=torch.int32).pin_memory()
+        # what the host reads back, one buffer and one copy: every GPU's (value, index) per row and the error word
+        nb = stack.ncard * T
+        self.d_out = torch.zeros(2 * nb + 1, dtype=torch.int32, device=stack.dev)
+        self.all_v = self.d_out[:nb].view(torch.float32).view(stack.ncard, T)
+        self.all_i = self.d_out[nb:2 * nb].view(stack.ncard, T)
+        self.h_in = torch.zeros(L.MAXT + 2, dtype=torch.int32).pin_memory()
+        self.h_ids, self.h_ctl = self.h_in[:L.MAXT], self.h_in[L.MAXT:]
+        self.h_out = torch.zeros(2 * nb + 1, dtype=torch.int32).pin_memory()
+        self.h_v = self.h_out[:nb].view(torch.float32).view(stack.ncard, T)
+        self.h_i = self.h_out[nb:2 * nb].view(stack.ncard, T)
+        self.h_err = self.h_out[2 * nb:]
+        self.h_in_np, self.h_v_np, self.h_i_np = self.h_in.numpy(), self.h_v.numpy(), self.h_i.numpy()   # the same memory
         # sampled acceptance: every GPU's 64 best (value, token) of each row of its vocabulary range, merged on the host
         self.sampled = sampled
         if sampled:
@@ -441,6 +448,7 @@ class WindowRunner:
             L.call("fnx_window_side_stream", self.side.cuda_stream, self.ev_fork.cuda_event, self.ev_join.cuda_event)
         else:
             L.call("fnx_window_side_stream", None, None, None)
+        self.ctl.copy_(self.ctl_in)
         L.call("fnx_embed_rows", stack.embed.data_ptr(), self.ids.data_ptr(), self.x.data_ptr(), T, stack.shape.n, st)
         for i in range(self.nstages):
             if self.lanes is not None:
@@ -473,6 +481,7 @@ class WindowRunner:
             if self.sampled:
                 self.dist.all_gather_into_tensor(self.all_cv.view(-1), self.cand_v.view(-1), group=self.group)
                 self.dist.all_gather_into_tensor(self.all_ci.view(-1), self.cand_i.view(-1), group=self.group)
+        self.d_out[-1:].copy_(self.err)
 
     def launch(self):
         """Enqueues one window on the runner's stream (the caller has set ids and ctl)."""
@@ -489,18 +498,20 @@ class WindowRunner:
         if pos0 + T > self.stack.shape.ctx + self.stack.shape.kv_slack:
             raise L.FnxError("window at position %d + %d rows is past the K/V cache (%d positions)" %
                              (pos0, T, self.stack.shape.ctx + self.stack.shape.kv_slack))
-        self.h_ids[:T] = torch.as_tensor(rows, dtype=torch.int32)
-        self.h_ctl[0], self.h_ctl[1] = pos0, tag
+        self.h_in_np[:T] = rows
+        self.h_in_np[L.MAXT], self.h_in_np[L.MAXT + 1] = pos0, tag
+        return self._run()
+
+    def _run(self):
+        """Uploads the host's ids and control words, runs the window, reads the result back and merges it."""
         with torch.cuda.stream(self.stream):
-            self.ids.copy_(self.h_ids, non_blocking=True)
-            self.ctl.copy_(self.h_ctl, non_blocking=True)
+            self.d_in.copy_(self.h_in, non_blocking=True)
             self.launch()
-            self.h_v.copy_(self.all_v, non_blocking=True)
-            self.h_i.copy_(self.all_i, non_blocking=True)
-            self.h_err.copy_(self.err, non_blocking=True)
+            self.h_out.copy_(self.d_out, non_blocking=True)
         self.stream.synchronize()
-        if int(self.h_err[0]) != 0:
-            raise L.FnxError("window error word %d (bit 16: a non-finite logit)" % int(self.h_err[0]))
+        err = int(self.h_err[0])
+        if err != 0:
+            raise L.FnxError("window error word %d (bit 16: a non-finite logit)" % err)
         return self.merge_best()
 
     def window_lanes(self, rows, pos, tags):
@@ -511,18 +522,10 @@ class WindowRunner:
         for p in pos:
             if (p + ln.rows - 1) // 4 // self.stack.ncard * 4 + 4 > ln.region:
                 raise L.FnxError("a lane at position %d + %d rows is past its run of K/V pages (%d local rows)" % (p, ln.rows, ln.region))
-        self.h_ids[:T] = torch.as_tensor(rows, dtype=torch.int32)
+        self.h_in_np[:T] = rows
         with torch.cuda.stream(self.stream):
-            self.ids.copy_(self.h_ids, non_blocking=True)
             ln.positions(pos, tags)
-            self.launch()
-            self.h_v.copy_(self.all_v, non_blocking=True)
-            self.h_i.copy_(self.all_i, non_blocking=True)
-            self.h_err.copy_(self.err, non_blocking=True)
-        self.stream.synchronize()
-        if int(self.h_err[0]) != 0:
-            raise L.FnxError("window error word %d (bit 16: a non-finite logit)" % int(self.h_err[0]))
-        return self.merge_best()
+        return self._run()
 
     def commit_lanes(self, n, tags):
         """Keep the first n[i] rows of lane i of the last window."""
@@ -535,7 +538,9 @@ class WindowRunner:
         self.stream.synchronize()   # the job table is read by an asynchronous copy
 
     def merge_best(self):
-        return merge_best(self.h_v, self.h_i)
+        if self.stack.ncard == 1:
+            return self.h_i_np[0].tolist()
+        return merge_best(self.h_v_np, self.h_i_np)
 
     def window_sampled(self, rows, pos0, tag, rng, temperature=1.0, top_p=1.0, min_p=0.0, top_k=0):
         """One window with rejection-sampling acceptance against the fixed (one-hot) drafts rows[1:]: runs the window,
@@ -568,9 +573,8 @@ class WindowRunner:
         self.commits += 1
         if slot == 0 and self.commits > 1:
             self.stream.synchronize()
-        with torch.cuda.stream(self.stream):
-            L.call("fnx_window_commit", C.byref(self.stack.cfg), self.stack.layers, self.stack.ws.data_ptr(), self.T, n, tag,
-                   self.h_jobs.data_ptr() + slot * self.job_bytes, torch.cuda.current_stream().cuda_stream)
+        L.call("fnx_window_commit", C.byref(self.stack.cfg), self.stack.layers, self.stack.ws.data_ptr(), self.T, n, tag,
+               self.h_jobs.data_ptr() + slot * self.job_bytes, self.stream.cuda_stream)
 
-    h2d_bytes = property(lambda self: self.T * 4 + 8)
+    h2d_bytes = property(lambda self: (L.MAXT + 2) * 4)
     d2h_bytes = property(lambda self: self.stack.ncard * self.T * 8 + 4)
