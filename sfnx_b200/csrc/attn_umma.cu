@@ -1,15 +1,16 @@
 // Position-split attention, the fast scan on Blackwell's fifth-generation tensor cores (head dimension 256).
 //
 // Same plan as attn_fast.cu (one CTA per KV head and range of owned positions, all T x (query heads per KV head) query
-// rows at once, K/V chunks of 32 positions through a cp.async ring, partial (acc, m, z) per split), with both products
-// as tcgen05.mma.  S = Q K^T: the queries (split into high and low f16 halves, x = hi + lo) sit in shared memory as the A
-// operand, 128 rows x 256 dims in four K-blocks of 64 dims with the 128-byte swizzle, the chunk's K rows as the B operand
-// in the same form, and the 128 x 32 fp32 scores accumulate in tensor memory (32 MMAs of M 128, N 32, K 16: hi then lo).
-// One thread issues them; tcgen05.commit signals an mbarrier.  Six warps then read the scores out of tensor memory with
-// tcgen05.ld.16x256b, whose register layout is the accumulator fragment of mma.sync m16n8 (a warp reads the 16 rows it
-// owns: warp w may touch lanes 32 (w % 4) .. + 31 of tensor memory, so the 16-row tiles go to warps 0, 4, 1, 5, 2, 6;
-// warp 3 issues the MMAs and warp 7 makes the copies).  O += P V is described further down.
-// The mma.sync scan measured 2.2 us of 4.1 us per chunk in S = Q K^T; here those MMAs take a few hundred cycles.
+// rows at once, K/V chunks through cp.async, partial (acc, m, z) per split), with both products as tcgen05.mma and
+// chunks of 64 positions.  S = Q K^T: the queries (split into high and low f16 halves, x = hi + lo) sit in shared memory
+// as the A operand, rows x 256 dims in four K-blocks of 64 dims with the 128-byte swizzle, the chunk's K rows as the B
+// operand in the same form, and the 128 x 64 fp32 scores accumulate in tensor memory (32 MMAs of M 128, N 64, K 16: hi
+// then lo).  One thread issues them; tcgen05.commit signals an mbarrier.  Six warps then read the scores out of tensor
+// memory with tcgen05.ld.16x256b, whose register layout is the accumulator fragment of mma.sync m16n8 (a warp reads the
+// 16 rows it owns: warp w may touch lanes 32 (w % 4) .. + 31 of tensor memory, so the 16-row tiles go to warps 0, 4, 1,
+// 5, 2, 6; warp 3 issues the MMAs and warp 7 makes the copies).  O += P V is described further down.
+// The mma.sync scan measured 2.2 us of 4.1 us per 32 positions in S = Q K^T alone; here a chunk of 64 takes about 2.4 us
+// in all, most of it the row warps' softmax step (six warps cannot hide their own latencies).
 // Every wait on an mbarrier is bounded; on a timeout the fault word is set and the CTA finishes with what it has.
 #include <cstdlib>
 
@@ -20,8 +21,8 @@
 
 namespace fnxk {
 
-constexpr int AU_CH = 32, AU_HD = 256, AU_ROWS = 128;
-constexpr int AU_QBYTES = 4 * AU_ROWS * 128, AU_KBYTES = 4 * AU_CH * 128, AU_THREADS = 256;
+constexpr int AU_HD = 256, AU_ROWS = 128;   // AU_ROWS: rows of the queries' image in global memory (and M of the MMAs)
+constexpr int AU_QBYTES = 4 * AU_ROWS * 128, AU_THREADS = 256;
 
 __host__ __device__ inline int au_kv_owned(int p, int card, int ncard) {
     const int b = p / 4;
@@ -79,305 +80,36 @@ __global__ void __launch_bounds__(256) k_attn_qsplit(const AuArgs a) {
 }
 
 // ---------------------------------------------------------------- both products on the tensor cores
-// O += P V as tcgen05.mma too: the weights P of a chunk go to shared memory as the A operand (128 rows x 32 positions,
-// high and low f16 halves, 64-byte swizzle), the chunk's V rows are the B operand as they lie in memory (dims
+// O += P V as tcgen05.mma too: the weights P of a chunk go to shared memory as the A operand (96 rows x 64 positions,
+// high and low f16 halves, 128-byte swizzle), the chunk's V rows are the B operand as they lie in memory (dims
 // contiguous: "MN-major", 128-byte swizzle, the same shared-memory form as K), and the 128 x 256 fp32 output accumulates
-// in tensor memory over the whole range (4 MMAs of M 128, N 256, K 16 per chunk: hi and lo halves of P, two 16-position
+// in tensor memory over the whole range (8 MMAs of M 128, N 256, K 16 per chunk: hi and lo halves of P, four 16-position
 // steps).  The row warps therefore hold no accumulators; they read each chunk's scores, take the softmax step and write
 // P.  Rescaling the accumulator every chunk would mean a round trip through tensor memory, so the exponentials use a
 // reference maximum that is only raised (and the accumulator only rescaled, tcgen05.ld / scale / tcgen05.st) when a row's
 // maximum has grown by more than 8: the weights stay below e^8, well inside f16, and (acc, m_ref, z) is an exact
 // partial for any reference.
-constexpr int AU2_KST = 3, AU2_VST = 2, AU2_PBYTES = AU_ROWS * 64;   // K, V stages; one P tile (hi or lo)
+//
+// Why chunks of 64: the row warps are few (six warps for 96 rows: a warp may read only its quarter of tensor memory), so
+// what a chunk costs them is largely latency that does not grow with the chunk (waits, barriers, the round trip of
+// tcgen05.ld, shuffles), and an MMA of N 64 costs the issuing thread little more than one of N 32 (the A operand's 4 KB
+// from shared memory bounds both): 80 -> 66 us per launch at 32,768 positions against chunks of 32.  Shared memory is
+// what a chunk of 64 needs more of: the queries' image keeps only its 96 real rows per K-block (the MMAs of M 128 read
+// the 32 rows past a block from whatever follows, into accumulator rows nobody reads), K and V share three buffers (see
+// the kernel), and the P tile is 96 rows x 128 bytes per half.
 constexpr unsigned AU2_COL_S = 256;   // tensor memory: O in columns 0..255, the two score tiles after it
-
-
-__global__ void __launch_bounds__(AU_THREADS) k_attn_umma2(const AuArgs a) {
-    constexpr int HD = AU_HD;
-    const int split = blockIdx.x, kvl = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, nthreads = blockDim.x;
-    const int qpk = a.nq / a.nkv, M = a.T * qpk;
-    extern __shared__ __align__(1024) unsigned char au_smem[];
-    unsigned char* Qhi = au_smem + ((1024u - (um_s32(au_smem) & 1023u)) & 1023u);
-    unsigned char* Qlo = Qhi + AU_QBYTES;
-    unsigned char* Kst = Qlo + AU_QBYTES;                       // [3] 4 K-blocks x [32 rows x 128 B], swizzled
-    unsigned char* Vst = Kst + AU2_KST * AU_KBYTES;             // [2] the same form: 4 blocks of 64 dims x [32 rows x 128 B]
-    unsigned char* Pst = Vst + AU2_VST * AU_KBYTES;             // hi, lo: [128 rows x 64 B], 64-byte swizzle
-    __shared__ __align__(8) unsigned long long mbar_s[2], mbar_o;
-    __shared__ unsigned tmem_base;
-    pdl_wait();   // the rows appended by the kernel before are among the positions read
-    pdl_go();
-    const int pos0 = *a.pos0;
-    const int ctx_max = au_kv_owned(pos0 + a.T - 1, a.card, a.ncard);
-    const int nchunks = (ctx_max + AU_CH - 1) / AU_CH, cps = (nchunks + a.nsplit - 1) / a.nsplit;
-    const int c_begin = split * cps, nc = max(0, min(nchunks, c_begin + cps) - c_begin);
-    float* out = a.scratch + ((size_t) (kvl * a.nsplit + split) * M) * (HD + 2);
-    const int tile = (warp & 3) * 2 + (warp >> 2);   // the 16 rows this warp owns: inside the quarter of tensor memory it may read
-    const bool worker = (warp & 3) != 3;
-    const int r0 = tile * 16 + (lane >> 2), r1 = r0 + 8, q4 = lane & 3;
-    if (nc == 0) {
-        for (int i = tid; i < M * (HD + 2); i += nthreads) out[i] = (i % (HD + 2)) == HD ? -INFINITY : 0.f;
-        return;
-    }
-    // ---- the copies (K and V rows take the same shared-memory form) are the work of warp 7, which owns no rows: a lane
-    // moves the 16-byte column piece `lane` of all 32 rows of a chunk, so the row warps spend nothing on them
-    const bool copier = warp == 7;
-    const int seg = lane;
-    const size_t row_elems = (size_t) a.nkv * HD;
-    auto load_rows = [&](const uint16_t* cache, int c, unsigned dst_base) {
-        if (!copier) return;
-        const unsigned dcol = dst_base + (seg >> 3) * (AU_CH * 128);
-        if (!a.g.pt && (c + 1) * AU_CH <= ctx_max) {   // a whole chunk of contiguous rows
-            const uint16_t* src = cache + (size_t) c * AU_CH * row_elems + (size_t) kvl * HD + seg * 8;
-#pragma unroll 8
-            for (int row = 0; row < AU_CH; ++row)
-                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dcol + row * 128 + (((seg & 7) ^ (row & 7)) << 4)), "l"(src + (size_t) row * row_elems));
-            return;
-        }
-#pragma unroll 4
-        for (int row = 0; row < AU_CH; ++row) {
-            const int pos = c * AU_CH + row;
-            const bool valid = pos < ctx_max;
-            const uint16_t* src = cache + au_row_at(a.g, valid ? pos : 0, a.nkv) + (size_t) kvl * HD + seg * 8;
-            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dcol + row * 128 + (((seg & 7) ^ (row & 7)) << 4)), "l"(src),
-                         "r"(valid ? 16 : 0));   // invalid rows: zeros
-        }
-    };
-    const unsigned ks_s = um_s32(Kst), vs_s = um_s32(Vst);
-    auto load_k = [&](int c) { load_rows(a.kc, c_begin + c, ks_s + (c % AU2_KST) * AU_KBYTES); };
-    auto load_v = [&](int c) { load_rows(a.vc, c_begin + c, vs_s + (c % AU2_VST) * AU_KBYTES); };
-    load_k(0);
-    load_v(0);
-    if (nc > 1) load_k(1);
-    {   // the queries' image, made by k_attn_qsplit
-        const unsigned char* img = a.qsplit + (size_t) kvl * 2 * AU_QBYTES;
-        for (int i = tid; i < 2 * AU_QBYTES / 16; i += nthreads)
-            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(um_s32(Qhi + (size_t) i * 16)), "l"(img + (size_t) i * 16));
-    }
-    asm volatile("cp.async.commit_group;");
-    if (tid == 0) {
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(um_s32(&mbar_s[0])));
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(um_s32(&mbar_s[1])));
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(um_s32(&mbar_o)));
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    if (warp == 0) {   // all 512 columns: O (256), two score tiles (64)
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(um_s32(&tmem_base)), "r"(512));
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
-    }
-    const int lim0 = worker && r0 < M ? au_kv_owned(pos0 + r0 % a.T, a.card, a.ncard) : 0;
-    const int lim1 = worker && r1 < M ? au_kv_owned(pos0 + r1 % a.T, a.card, a.ncard) : 0;
-    float m0 = -INFINITY, m1 = -INFINITY, z0 = 0.f, z1 = 0.f;   // reference maxima and sums of this thread's two rows
-    const float rs = 1.0f / sqrtf((float) HD);
-    const unsigned idesc_s = (1u << 4) | ((32u >> 3) << 17) | ((128u >> 4) << 24);               // S: N 32, both operands K-major
-    const unsigned idesc_o = (1u << 4) | (1u << 16) | ((256u >> 3) << 17) | ((128u >> 4) << 24);   // O: N 256, B MN-major
-    auto issue_scores = [&](int c) {
-        const unsigned tb = tmem_base + AU2_COL_S + (c & 1) * 32;
-        const unsigned long long dk = um_desc(um_s32(Kst + (size_t) (c % AU2_KST) * AU_KBYTES));
-        const unsigned long long dh = um_desc(um_s32(Qhi)), dl = um_desc(um_s32(Qlo));
-#pragma unroll
-        for (int kb = 0; kb < 4; ++kb)
-#pragma unroll
-            for (int ks = 0; ks < 4; ++ks) {
-                const unsigned long long ob = (unsigned long long) ((kb * AU_CH * 128 + ks * 32) >> 4), oa = (unsigned long long) ((kb * AU_ROWS * 128 + ks * 32) >> 4);
-                um_mma(tb, dh + oa, dk + ob, idesc_s, kb | ks);
-                um_mma(tb, dl + oa, dk + ob, idesc_s, 1u);
-            }
-        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(um_s32(&mbar_s[c & 1])) : "memory");
-    };
-    auto issue_output = [&](int c) {   // O (+)= (Phi + Plo) V(c)
-        const unsigned long long dv = um_desc_x(um_s32(Vst + (size_t) (c % AU2_VST) * AU_KBYTES), AU_CH * 128, 1024, 2);
-        const unsigned long long dph = um_desc_x(um_s32(Pst), 16, 512, 4), dpl = um_desc_x(um_s32(Pst + AU2_PBYTES), 16, 512, 4);
-#pragma unroll
-        for (int ks = 0; ks < 2; ++ks) {
-            um_mma(tmem_base, dph + (unsigned long long) (ks * 32 >> 4), dv + (unsigned long long) (ks * 16 * 128 >> 4), idesc_o, c | ks);
-            um_mma(tmem_base, dpl + (unsigned long long) (ks * 32 >> 4), dv + (unsigned long long) (ks * 16 * 128 >> 4), idesc_o, 1u);
-        }
-        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(um_s32(&mbar_o)) : "memory");
-    };
-    auto sync_all = [&] {   // stores and landed copies of every thread visible to the tensor core, tensor-memory accesses ordered
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-        __syncthreads();
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    };
-    asm volatile("cp.async.wait_group 0;" ::: "memory");
-    sync_all();
-    const bool issuer = tid == 3 * 32;   // warp 3, lane 0
-    if (issuer) issue_scores(0);
-    bool alive = true;   // false after a wait ran out
-#pragma unroll 1
-    for (int i = 0; i < nc; ++i) {
-        const int buf = i & 1;
-        if (i + 2 < nc) load_k(i + 2);   // its stage held chunk i - 1, whose scores were read a chunk ago
-        asm volatile("cp.async.commit_group;");
-        if (issuer && i + 1 < nc) issue_scores(i + 1);   // the next chunk's scores while this chunk's are used
-        float sacc[4][4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) sacc[j][0] = sacc[j][1] = sacc[j][2] = sacc[j][3] = -INFINITY;
-        if (worker) {
-            bool ok = alive && um_wait(&mbar_s[buf], (i >> 1) & 1, a.fault);
-            ok = __all_sync(0xffffffffu, ok);
-            alive = alive && ok;
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            if (ok) {
-                unsigned r[16];
-                asm volatile("tcgen05.ld.sync.aligned.16x256b.x4.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-                             : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-                               "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-                             : "r"(tmem_base + AU2_COL_S + buf * 32 + ((unsigned) (tile * 16) << 16)));
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-                for (int j = 0; j < 4; ++j)
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) sacc[j][e] = __uint_as_float(r[4 * j + e]);
-            }
-        }
-        // ---- the chunk's maxima; a row's reference is raised when its maximum has grown by more than 8
-        const int pc = (c_begin + i) * AU_CH + 2 * q4;
-        float mx0 = -INFINITY, mx1 = -INFINITY;
-#pragma unroll
-        for (int j = 0; j < 4; ++j)
-#pragma unroll
-            for (int e = 0; e < 2; ++e) {
-                const int pcol = pc + 8 * j + e;
-                sacc[j][e] = pcol < lim0 ? sacc[j][e] * rs : -INFINITY;
-                sacc[j][2 + e] = pcol < lim1 ? sacc[j][2 + e] * rs : -INFINITY;
-                mx0 = fmaxf(mx0, sacc[j][e]);
-                mx1 = fmaxf(mx1, sacc[j][2 + e]);
-            }
-        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
-        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
-        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
-        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
-        const bool up0 = mx0 > m0 + 8.0f || (m0 == -INFINITY && mx0 != -INFINITY), up1 = mx1 > m1 + 8.0f || (m1 == -INFINITY && mx1 != -INFINITY);
-        const float f0 = !up0 ? 1.0f : m0 == -INFINITY ? 0.f : __expf(m0 - mx0), f1 = !up1 ? 1.0f : m1 == -INFINITY ? 0.f : __expf(m1 - mx1);
-        if (up0) m0 = mx0;
-        if (up1) m1 = mx1;
-        // ---- the accumulator and the P tile are free once the MMAs of the chunk before are done
-        if (i > 0) {
-            bool ok = alive && um_wait(&mbar_o, (i - 1) & 1, a.fault);
-            ok = __all_sync(0xffffffffu, ok);
-            alive = alive && ok;
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        }
-        if (i + 1 < nc) load_v(i + 1);   // its stage held chunk i - 1
-        asm volatile("cp.async.commit_group;");
-        if (worker) {
-            // rows of this warp whose reference went up (and had something accumulated): O row *= f, 32 columns at a time
-            if (i > 0 && __any_sync(0xffffffffu, f0 != 1.0f || f1 != 1.0f)) {
-#pragma unroll 1
-                for (int cb = 0; cb < HD / 32; ++cb) {
-                    unsigned r[16];
-                    const unsigned ta = tmem_base + cb * 32 + ((unsigned) (tile * 16) << 16);
-                    asm volatile("tcgen05.ld.sync.aligned.16x256b.x4.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-                                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-                                   "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-                                 : "r"(ta));
-                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        r[4 * j] = __float_as_uint(__uint_as_float(r[4 * j]) * f0), r[4 * j + 1] = __float_as_uint(__uint_as_float(r[4 * j + 1]) * f0);
-                        r[4 * j + 2] = __float_as_uint(__uint_as_float(r[4 * j + 2]) * f1), r[4 * j + 3] = __float_as_uint(__uint_as_float(r[4 * j + 3]) * f1);
-                    }
-                    asm volatile("tcgen05.st.sync.aligned.16x256b.x4.b32 [%16], {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15};" ::"r"(r[0]), "r"(r[1]),
-                                 "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]),
-                                 "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(ta)
-                                 : "memory");
-                }
-                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-            }
-            // ---- the weights against the references, their sums, and the P tile (hi and lo halves, 64-byte swizzle)
-            float ps0 = 0.f, ps1 = 0.f;
-            unsigned char* prow0 = Pst + r0 * 64 + 4 * q4;
-            unsigned char* prow1 = Pst + r1 * 64 + 4 * q4;
-            const int sw0 = (r0 >> 1) & 3, sw1 = (r1 >> 1) & 3;
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                float p[4];
-#pragma unroll
-                for (int e = 0; e < 2; ++e) {
-                    p[e] = sacc[j][e] == -INFINITY ? 0.f : __expf(sacc[j][e] - m0);
-                    p[2 + e] = sacc[j][2 + e] == -INFINITY ? 0.f : __expf(sacc[j][2 + e] - m1);
-                }
-                ps0 += p[0] + p[1];
-                ps1 += p[2] + p[3];
-                unsigned h0, l0, h1, l1;
-                au_split2(p[0], p[1], h0, l0);
-                au_split2(p[2], p[3], h1, l1);
-                *reinterpret_cast<unsigned*>(prow0 + ((j ^ sw0) << 4)) = h0;
-                *reinterpret_cast<unsigned*>(prow0 + AU2_PBYTES + ((j ^ sw0) << 4)) = l0;
-                *reinterpret_cast<unsigned*>(prow1 + ((j ^ sw1) << 4)) = h1;
-                *reinterpret_cast<unsigned*>(prow1 + AU2_PBYTES + ((j ^ sw1) << 4)) = l1;
-            }
-            ps0 += __shfl_xor_sync(0xffffffffu, ps0, 1);
-            ps0 += __shfl_xor_sync(0xffffffffu, ps0, 2);
-            ps1 += __shfl_xor_sync(0xffffffffu, ps1, 1);
-            ps1 += __shfl_xor_sync(0xffffffffu, ps1, 2);
-            z0 = z0 * f0 + ps0;
-            z1 = z1 * f1 + ps1;
-        }
-        // ---- P is written, V(i) (copied a chunk ago) and K(i + 1) have landed: the output MMAs of this chunk
-        asm volatile("cp.async.wait_group 1;" ::: "memory");   // all but V(i + 1), just asked for
-        sync_all();
-        if (issuer) issue_output(i);
-    }
-    // ---- this split's partial: the accumulator out of tensor memory, m_ref, z per row
-    {
-        bool ok = alive && um_wait(&mbar_o, (nc - 1) & 1, a.fault);
-        ok = __all_sync(0xffffffffu, ok);
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        if (worker) {
-#pragma unroll 1
-            for (int cb = 0; cb < HD / 32; ++cb) {
-                unsigned r[16];
-#pragma unroll
-                for (int e = 0; e < 16; ++e) r[e] = 0u;
-                if (ok) {
-                    asm volatile("tcgen05.ld.sync.aligned.16x256b.x4.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-                                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-                                   "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-                                 : "r"(tmem_base + cb * 32 + ((unsigned) (tile * 16) << 16)));
-                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                }
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const int col = cb * 32 + j * 8 + 2 * q4;
-                    if (r0 < M) *reinterpret_cast<float2*>(out + (size_t) r0 * (HD + 2) + col) = make_float2(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]));
-                    if (r1 < M) *reinterpret_cast<float2*>(out + (size_t) r1 * (HD + 2) + col) = make_float2(__uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
-                }
-            }
-            if (q4 == 0) {
-                if (r0 < M) out[(size_t) r0 * (HD + 2) + HD] = m0, out[(size_t) r0 * (HD + 2) + HD + 1] = z0;
-                if (r1 < M) out[(size_t) r1 * (HD + 2) + HD] = m1, out[(size_t) r1 * (HD + 2) + HD + 1] = z1;
-            }
-        }
-    }
-    asm volatile("cp.async.wait_group 0;" ::: "memory");
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();
-    if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512));
-}
-
-// The same scan in chunks of 64 positions.  The row warps are few (six warps for 96 rows: a warp may read only its quarter
-// of tensor memory), so what a chunk costs them is mostly latency that does not grow with the chunk: waits, barriers, the
-// round trip of tcgen05.ld, shuffles.  Twice the positions per chunk halves that per position, and an MMA of N 64 costs the
-// issuing thread what one of N 32 does (the A operand's 4 KB from shared memory bounds both).  Shared memory is what a
-// chunk of 64 needs more of: the queries' image keeps only its 96 real rows per K-block (the MMAs of M 128 read the 32
-// rows past a block from whatever follows, into accumulator rows nobody reads), K has two stages and V one (its lines
-// asked into L2 a chunk ahead), and the P tile is 96 rows x 128 bytes per half with the 128-byte swizzle.
 constexpr int A3_CH = 64, A3_QROWS = 96, A3_QBLK = A3_QROWS * 128, A3_QBYTES = 4 * A3_QBLK, A3_KBLK = A3_CH * 128, A3_KBYTES = 4 * A3_KBLK;
-constexpr int A3_KST = 2, A3_PBYTES = A3_QROWS * 128, A3_PAD = 4096;   // the pad: what an MMA reads past the last P row
+constexpr int A3_NBUF = 3, A3_PBYTES = A3_QROWS * 128, A3_PAD = 4096;   // the pad: what an MMA reads past the last P row
 
-__global__ void __launch_bounds__(AU_THREADS) k_attn_umma3(const AuArgs a) {
+__global__ void __launch_bounds__(AU_THREADS) k_attn_umma(const AuArgs a) {
     constexpr int HD = AU_HD;
     const int split = blockIdx.x, kvl = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, nthreads = blockDim.x;
     const int qpk = a.nq / a.nkv, M = a.T * qpk;
     extern __shared__ __align__(1024) unsigned char au_smem[];
     unsigned char* Qhi = au_smem + ((1024u - (um_s32(au_smem) & 1023u)) & 1023u);
     unsigned char* Qlo = Qhi + A3_QBYTES;                       // each: 4 K-blocks x [96 rows x 128 B], swizzled
-    unsigned char* Kst = Qlo + A3_QBYTES;                       // [2] 4 K-blocks x [64 rows x 128 B], swizzled
-    unsigned char* Vst = Kst + A3_KST * A3_KBYTES;              // [1] the same form: 4 blocks of 64 dims x [64 rows x 128 B]
-    unsigned char* Pst = Vst + A3_KBYTES;                       // hi, lo: [96 rows x 128 B], 128-byte swizzle; then the pad
+    unsigned char* KVst = Qlo + A3_QBYTES;                      // [3] 4 blocks of 64 dims x [64 rows x 128 B], swizzled: K(c), then V(c)
+    unsigned char* Pst = KVst + A3_NBUF * A3_KBYTES;            // hi, lo: [96 rows x 128 B], 128-byte swizzle; then the pad
     __shared__ __align__(8) unsigned long long mbar_s[2], mbar_o;
     __shared__ unsigned tmem_base;
     pdl_wait();   // the rows appended by the kernel before are among the positions read
@@ -418,21 +150,15 @@ __global__ void __launch_bounds__(AU_THREADS) k_attn_umma3(const AuArgs a) {
                          "r"(valid ? 16 : 0));   // invalid rows: zeros
         }
     };
-    const unsigned ks_s = um_s32(Kst), vs_s = um_s32(Vst);
-    auto load_k = [&](int c) { load_rows(a.kc, c_begin + c, ks_s + (c % A3_KST) * A3_KBYTES); };
-    auto load_v = [&](int c) { load_rows(a.vc, c_begin + c, vs_s); };
-    // V has one stage: its copy can start only when the output MMAs of the chunk before are done, so the chunk's lines are
-    // asked into L2 a chunk earlier and the copy itself is short
-    auto prefetch_v = [&](int c) {
-        if (!copier || a.g.pt || (c_begin + c + 1) * A3_CH > ctx_max) return;
-        const uint16_t* src = a.vc + (size_t) (c_begin + c) * A3_CH * row_elems + (size_t) kvl * HD + (lane & 3) * 64;   // 4 lines a row
-#pragma unroll
-        for (int r8 = 0; r8 < A3_CH / 8; ++r8)
-            asm volatile("prefetch.global.L2 [%0];" ::"l"(src + (size_t) (r8 * 8 + (lane >> 2)) * row_elems));
-    };
+    // Three buffers in rotation, chunk c in buffer c % 3: first its K rows, for S(c); once those MMAs are done its V rows
+    // over them, for O += P(c) V(c); once those are done the K rows of chunk c + 3.  V(c) so has more than a chunk's time to
+    // arrive and K(c + 3) most of one, with the memory two stages of each would take less one.
+    const unsigned kv_s = um_s32(KVst);
+    auto load_k = [&](int c) { load_rows(a.kc, c_begin + c, kv_s + (c % A3_NBUF) * A3_KBYTES); };
+    auto load_v = [&](int c) { load_rows(a.vc, c_begin + c, kv_s + (c % A3_NBUF) * A3_KBYTES); };
     load_k(0);
-    load_v(0);
     if (nc > 1) load_k(1);
+    if (nc > 2) load_k(2);
     {   // the queries' image, made by k_attn_qsplit: rows 0..95 of each of its K-blocks of 128 rows
         const unsigned char* img = a.qsplit + (size_t) kvl * 2 * AU_QBYTES;
         for (int i = tid; i < 2 * 4 * A3_QROWS * 8; i += nthreads) {
@@ -460,7 +186,7 @@ __global__ void __launch_bounds__(AU_THREADS) k_attn_umma3(const AuArgs a) {
     const unsigned idesc_o = (1u << 4) | (1u << 16) | ((256u >> 3) << 17) | ((128u >> 4) << 24);   // O: N 256, B MN-major
     auto issue_scores = [&](int c) {
         const unsigned tb = tmem_base + AU2_COL_S + (c & 1) * A3_CH;
-        const unsigned long long dk = um_desc(um_s32(Kst + (size_t) (c % A3_KST) * A3_KBYTES));
+        const unsigned long long dk = um_desc(um_s32(KVst + (size_t) (c % A3_NBUF) * A3_KBYTES));
         const unsigned long long dh = um_desc(um_s32(Qhi)), dl = um_desc(um_s32(Qlo));
 #pragma unroll
         for (int kb = 0; kb < 4; ++kb)
@@ -473,7 +199,7 @@ __global__ void __launch_bounds__(AU_THREADS) k_attn_umma3(const AuArgs a) {
         asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(um_s32(&mbar_s[c & 1])) : "memory");
     };
     auto issue_output = [&](int c) {   // O (+)= (Phi + Plo) V(c)
-        const unsigned long long dv = um_desc_x(um_s32(Vst), A3_KBLK, 1024, 2);
+        const unsigned long long dv = um_desc_x(um_s32(KVst + (size_t) (c % A3_NBUF) * A3_KBYTES), A3_KBLK, 1024, 2);
         const unsigned long long dph = um_desc(um_s32(Pst)), dpl = um_desc(um_s32(Pst + A3_PBYTES));
 #pragma unroll
         for (int ks = 0; ks < A3_CH / 16; ++ks) {
@@ -493,21 +219,30 @@ __global__ void __launch_bounds__(AU_THREADS) k_attn_umma3(const AuArgs a) {
     const bool issuer = tid == 3 * 32;   // warp 3, lane 0
     if (issuer) issue_scores(0);
     bool alive = true;   // false after a wait ran out
+    auto copier_wait = [&](unsigned long long* bar, unsigned parity) {   // the copying warp alone waits for a set of MMAs
+        bool ok = alive && um_wait(bar, parity, a.fault);
+        ok = __all_sync(0xffffffffu, ok);
+        alive = alive && ok;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    };
+    if (copier) {
+        copier_wait(&mbar_s[0], 0u);   // S(0) is complete: V(0) over K(0)
+        load_v(0);
+    }
+    asm volatile("cp.async.commit_group;");
 #pragma unroll 1
     for (int i = 0; i < nc; ++i) {
         const int buf = i & 1;
         if (issuer && i + 1 < nc) issue_scores(i + 1);   // the next chunk's scores while this chunk's are used
-        if (i + 1 < nc) prefetch_v(i + 1);
         float sacc[8][4];
 #pragma unroll
         for (int j = 0; j < 8; ++j) sacc[j][0] = sacc[j][1] = sacc[j][2] = sacc[j][3] = -INFINITY;
-        if (worker || copier) {
-            bool ok = alive && um_wait(&mbar_s[buf], (i >> 1) & 1, a.fault);   // S(i) is complete: K(i)'s stage is free
+        if (worker) {
+            bool ok = alive && um_wait(&mbar_s[buf], (i >> 1) & 1, a.fault);
             ok = __all_sync(0xffffffffu, ok);
             alive = alive && ok;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            if (i + 2 < nc) load_k(i + 2);
-            if (ok && worker) {
+            if (ok) {
 #pragma unroll
                 for (int hf = 0; hf < 2; ++hf) {
                     unsigned r[16];
@@ -551,7 +286,12 @@ __global__ void __launch_bounds__(AU_THREADS) k_attn_umma3(const AuArgs a) {
             alive = alive && ok;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         }
-        if (i > 0) load_v(i);   // the one V stage held chunk i - 1 until those MMAs were done
+        if (i > 0 && i + 2 < nc) load_k(i + 2);   // over V(i - 1), whose MMAs are done
+        asm volatile("cp.async.commit_group;");
+        if (copier && i + 1 < nc) {
+            copier_wait(&mbar_s[buf ^ 1], (unsigned) (((i + 1) >> 1) & 1));   // S(i + 1) is complete: V(i + 1) over K(i + 1)
+            load_v(i + 1);
+        }
         asm volatile("cp.async.commit_group;");
         if (worker) {
             // rows of this warp whose reference went up (and had something accumulated): O row *= f, 32 columns at a time
@@ -607,8 +347,8 @@ __global__ void __launch_bounds__(AU_THREADS) k_attn_umma3(const AuArgs a) {
             z0 = z0 * f0 + ps0;
             z1 = z1 * f1 + ps1;
         }
-        // ---- P is written, V(i) and K(i + 2) have landed (K(i + 1) a chunk ago): the output MMAs of this chunk
-        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        // ---- P is written; V(i), asked for a chunk ago, and K(i + 2) have landed: the output MMAs of this chunk
+        asm volatile("cp.async.wait_group 1;" ::: "memory");   // all but V(i + 1), just asked for
         sync_all();
         if (issuer) issue_output(i);
     }
@@ -649,9 +389,8 @@ __global__ void __launch_bounds__(AU_THREADS) k_attn_umma3(const AuArgs a) {
     if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512));
 }
 
-size_t attn_umma3_smem() { return (size_t) 2 * A3_QBYTES + (A3_KST + 1) * A3_KBYTES + 2 * A3_PBYTES + A3_PAD + 1024; }
+size_t attn_umma_smem() { return (size_t) 2 * A3_QBYTES + A3_NBUF * A3_KBYTES + 2 * A3_PBYTES + A3_PAD + 1024; }
 
-size_t attn_umma2_smem() { return (size_t) 2 * AU_QBYTES + (AU2_KST + AU2_VST) * AU_KBYTES + 2 * AU2_PBYTES + 1024; }
 
 // the scan part of fnx_attn_partial for head dimension 256 and at most 96 query rows a KV head; -1 when it does not apply
 int attn_umma_launch(const float* qg, const uint16_t* kc, const uint16_t* vc, FnxKvPages g, float* scratch, int card, int ncard, int T,
@@ -665,16 +404,9 @@ int attn_umma_launch(const float* qg, const uint16_t* kc, const uint16_t* vc, Fn
     AuArgs a{qg, kc, vc, g, scratch, qsplit, nq, nkv, T, card, ncard, nsplit, pos0, fault};
     launch(0, k_attn_qsplit, (nkv * AU_ROWS * (AU_HD / 2) + 255) / 256, 256, 0, st, a);
     if (launch_ok("attn query split")) return 1;
-    static const bool ch64 = getenv("FNX_ATTN_CH64") != nullptr;   // chunks of 64 positions (k_attn_umma3)
-    if (ch64) {
-        const size_t sm3 = attn_umma3_smem();
-        if (cudaFuncSetAttribute(k_attn_umma3, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) sm3) != cudaSuccess) return -1;
-        launch(6, k_attn_umma3, dim3(nsplit, nkv), AU_THREADS, sm3, st, a);
-        return launch_ok("attn scan (tcgen05, chunks of 64)");
-    }
-    const size_t sm2 = attn_umma2_smem();
-    if (cudaFuncSetAttribute(k_attn_umma2, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) sm2) != cudaSuccess) return -1;
-    launch(6, k_attn_umma2, dim3(nsplit, nkv), AU_THREADS, sm2, st, a);
+    const size_t sm3 = attn_umma_smem();
+    if (cudaFuncSetAttribute(k_attn_umma, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) sm3) != cudaSuccess) return -1;
+    launch(6, k_attn_umma, dim3(nsplit, nkv), AU_THREADS, sm3, st, a);
     return launch_ok("attn scan (tcgen05)");
 }
 
