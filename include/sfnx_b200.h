@@ -13,7 +13,8 @@
  *  - the return value is 0, or non-zero after a refused argument or a failed launch, with the text in
  *    fnx_last_error() (the reference throws std::runtime_error with the same kind of text);
  *  - device-side faults never trap: kernels OR bits into a caller-supplied `unsigned* err` word
- *    (bit 16: a non-finite logit; reference src/kernels.hpp:329-332) and run to completion.
+ *    (bit 1: a peer's addend never came; bit 8: a bounded on-chip wait ran out; bit 16: a non-finite logit; reference
+ *    src/kernels.hpp:329-332) and run to completion.
  */
 #ifndef SFNX_B200_H
 #define SFNX_B200_H
@@ -91,9 +92,10 @@ typedef struct FnxCopyJob {
 const char* fnx_last_error(void);
 /* the compute capability the library was built for (100) and whether the current device matches it */
 int fnx_built_arch(void);
-/* reads and clears the device-side fault word of the staged kernels: 0, or bit 1 when a bounded wait for a bulk copy ran
- * out (the kernel then finished without the data instead of spinning; reference kernels report through err words the
- * same way, src/kernels.hpp:329-332) */
+/* reads and clears the library's own device-side fault word: 0, or bit 8 when a bounded on-chip wait of a tcgen05 kernel
+ * (fnx_attn_partial, fnx_moe_gate_up_mma, fnx_moe_down_mma) ran out: the kernel then finished with what it had instead
+ * of spinning (reference kernels report through err words the same way, src/kernels.hpp:329-332).  Inside
+ * fnx_window_stage the same bit goes into the window's error word (FNX_BUF_ERR) instead. */
 unsigned fnx_device_fault(void);
 
 /* ---- activations */
@@ -253,7 +255,8 @@ typedef struct FnxRing {
 int fnx_ring_sum(float* x, int rows, int row_len, const FnxRing* ring, unsigned* err, void* st);
 
 /* ---- head */
-/* reference src/kernels.hpp:384 argmax (src/kernels.cu:870-908); keys: FNX_MAXT words zeroed once */
+/* reference src/kernels.hpp:384 argmax (src/kernels.cu:870-908): per row the largest logit and its index + v0, the lowest
+ * index on a tie; a non-finite logit sets bit 16 of *err.  keys: 2 * FNX_MAXT 64-bit words, zeroed once (left at zero) */
 int fnx_argmax(const float* logits, int rows, int T, int v0, float* best_v, int* best_i, unsigned long long* keys, unsigned* err,
                void* st);
 /* reference src/kernels.hpp:387 penalize_row (src/kernels.cu:1454-1470) */
@@ -358,7 +361,8 @@ int fnx_window_commit_lanes(const FnxStackCfg* cfg, const FnxLayer* layers, void
 /* per-call timing of windows enqueued outside a graph (the reference's engine keeps per-window timers,
  * src/engine.hpp:182-187): between fnx_trace_begin and fnx_trace_end every C ABI call of fnx_window_stage is bracketed by
  * CUDA events on its stream; fnx_trace_end waits for them and returns each call's name, layer and milliseconds.
- * fnx_window_kernel_count: kernels launched through fnx_window_stage so far (reset != 0 zeroes the count) */
+ * fnx_window_kernel_count: kernel launches this library has made so far, counted at each launch's check, whoever the
+ * caller (reset != 0 reads and zeroes the count) */
 int fnx_trace_begin(void);
 int fnx_trace_end(float* ms, int* layer, const char** names, int cap);
 long fnx_window_kernel_count(int reset);

@@ -1,6 +1,7 @@
-// Position-split attention of the verify window: per-head RMS norm + NEOX rotary + K/V append, the split-K
-// online-softmax scan over the positions this GPU owns, the merge of the splits, and the merge of the GPUs' partials
-// with the output gate.  Replaces reference src/kernels.cu:451-469, 480-691, 1539-1569.
+// Position-split attention of the verify window: per-head RMS norm + NEOX rotary + K/V append, the scan over the
+// positions this GPU owns in the reference's order of sums (bit-reproducible; also the scan of windows of several
+// sequences), the joining of its runs, and the merge of the GPUs' partials with the output gate.  Covers what reference
+// src/kernels.cu:451-469, 480-691, 1539-1569 compute.
 //
 // K/V placement (reference src/kernels.hpp:126-130): blocks of 4 positions are dealt round-robin, block j on GPU
 // j % ncard at local block j / ncard; local row = local block * 4 + p % 4.
@@ -8,6 +9,7 @@
 
 #include "common.cuh"
 #include "exact_math.cuh"
+#include "moe_internal.cuh"
 
 namespace fnxk {
 
@@ -81,111 +83,234 @@ __global__ void k_attn_prep_append(float* qg, float* k, const float* v, const fl
     (is_k ? kc : vc)[kv_row_at(g, r, nkv, hd) + e] = f2h(x);
 }
 
-// ---------------------------------------------------------------- exact split-K scan (the reference's order of sums)
-// block (split s, row t, KV head kvl), hd threads: positions [s len, (s + 1) len) of the row's owned positions in
-// chunks of 32; thread i holds dimension i of the chunk's V rows and of every local head's accumulator; warp w scores
-// head w (lane = position) and takes its online-softmax step.  scratch: acc [T][nq][16][hd], then (m, z) [T][nq][16].
+// ---------------------------------------------------------------- the scan in the reference's order of sums
+// The reference's statement (src/kernels.cu:497-606) fixes, for every (row, head), a split of the row's owned positions
+// into 16 runs of `len` rows, chunks of 32 positions inside a run, a score as one fused chain over the head dimension,
+// an online-softmax step per chunk (warp xor-trees over the chunk's 32 weights) and value rows added in ascending
+// position; this kernel keeps all of that and changes who does it.  One block takes (run s, KV head, group of rows):
+// the rows of a window that read the same K/V (the same sequence) and have the same `len` walk the same chunks, so the
+// block stages each chunk of K and V once, as f32, and applies it to every (row, head) pair of the group - up to 96
+// pairs at a time - instead of once per row.  Rows group themselves on the device: block z = t works only if row t is
+// the first of its group, and then takes every later row of the group with it.
+//   scores : warp w holds pairs w, w + 8, ...; lane = position of the chunk; 12 independent chains a thread, the
+//            pair's query row read as float4 broadcasts
+//   softmax: the pair's 32 weights sit across the lanes of one warp, as the reference's trees want them
+//   values : thread = head dimension, one accumulator per pair in registers, the chunk's 32 V values of that
+//            dimension in registers too
+// scratch: acc [T][nq][16][hd], then (m, z) [T][nq][16].
 struct AttPart {
     float m, z;
 };
+constexpr int AX_THREADS = 256, AX_WARPS = AX_THREADS / 32, AX_PT = 96, AX_PPW = AX_PT / AX_WARPS;
 
 template <int HD>
-__global__ void __launch_bounds__(HD) k_attn_part(const float* __restrict__ qg, const uint16_t* __restrict__ kc,
-                                                  const uint16_t* __restrict__ vc, FnxKvPages g, float* __restrict__ acc_out,
-                                                  AttPart* __restrict__ mz_out, int nq, int nkv, const int* __restrict__ pos0p, int card,
-                                                  int ncard, FnxLaneRows lr) {
-    const int s = blockIdx.x, t = blockIdx.y, kvl = blockIdx.z, i = threadIdx.x, lane = i & 31, warp = i >> 5;
-    const int qpk = nq / nkv, h0 = kvl * qpk;
-    // a row of a lane of its own: the lane's position word and page table (reference src/kernels.hpp:189-193)
-    if (lr.pt) g.pt = lr.pt[t];
-    const int ctx = kv_owned(lr.pos ? *lr.pos[t] : *pos0p + t, card, ncard);
-    const int len = ((ctx + ATT_SPLITS - 1) / ATT_SPLITS + ATT_CH - 1) / ATT_CH * ATT_CH;
-    const int p0 = s * len, p1 = min(ctx, p0 + len);
-    extern __shared__ __align__(16) float att_sm[];
-    float* q = att_sm;                                  // [qpk][HD]
-    float* kk = q + (size_t) qpk * HD;                  // [32][HD + 1]
-    float* e = kk + (size_t) ATT_CH * (HD + 1);         // [qpk][32]
-    float* scale = e + (size_t) qpk * ATT_CH;           // [qpk]
-    for (int k = i; k < qpk * HD; k += HD) q[k] = qg[((size_t) t * nq + h0 + k / HD) * 2 * HD + k % HD];
-    constexpr int NW = HD / 32, HPW = (ATT_MAXQPK + NW - 1) / NW;
-    float m[HPW], z[HPW];
-#pragma unroll
-    for (int k = 0; k < HPW; ++k) m[k] = -INFINITY, z[k] = 0.f;
-    float acc[ATT_MAXQPK];
-#pragma unroll
-    for (int hh = 0; hh < ATT_MAXQPK; ++hh) acc[hh] = 0.f;
-    const float rs = ex_rsqrt((float) HD);
+__global__ void __launch_bounds__(AX_THREADS, 1) k_attn_rows(const float* __restrict__ qg, const uint16_t* __restrict__ kc,
+                                                           const uint16_t* __restrict__ vc, FnxKvPages g, float* __restrict__ acc_out,
+                                                           AttPart* __restrict__ mz_out, int T, int nq, int nkv,
+                                                           const int* __restrict__ pos0p, int card, int ncard, FnxLaneRows lr) {
+    constexpr int G = AX_THREADS / HD, APT = AX_PT / G, KLD = HD + 4;   // thread groups over the pairs; accumulators a thread
+    const int s = blockIdx.x, kvl = blockIdx.y, lead = blockIdx.z, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int qpk = nq / nkv;
+    __shared__ int ctx_s[FNX_MAXT], len_s[FNX_MAXT], rows_s[FNX_MAXT], nr_s;
+    __shared__ const int* pt_s[FNX_MAXT];
+    if (tid < T) {
+        const int c = kv_owned(lr.pos ? *lr.pos[tid] : *pos0p + tid, card, ncard);
+        ctx_s[tid] = c;
+        len_s[tid] = ((c + ATT_SPLITS - 1) / ATT_SPLITS + ATT_CH - 1) / ATT_CH * ATT_CH;
+        pt_s[tid] = lr.pt ? lr.pt[tid] : g.pt;
+    }
     __syncthreads();
+    if (tid == 0) {
+        int nr = 0;
+        bool first = true;
+        for (int t = 0; t < T; ++t) {
+            if (pt_s[t] != pt_s[lead] || len_s[t] != len_s[lead]) continue;
+            if (t < lead) first = false;
+            else rows_s[nr++] = t;
+        }
+        nr_s = first ? nr : 0;
+    }
+    __syncthreads();
+    const int nr = nr_s;
+    if (nr == 0) return;   // an earlier row leads this row's group
+    g.pt = pt_s[lead];
+    const int len = len_s[lead], p0 = s * len;
+    int pend = 0;          // where the group's longest row ends inside this run
+    for (int r = 0; r < nr; ++r) pend = max(pend, min(ctx_s[rows_s[r]], p0 + len));
+    extern __shared__ __align__(16) float ax_sm[];
+    float* q_s = ax_sm;                          // [AX_PT][HD]
+    float* k_s = q_s + (size_t) AX_PT * HD;      // [32][HD + 4]
+    float* v_s = k_s + (size_t) ATT_CH * KLD;    // [32][HD]
+    float* w_s = v_s + (size_t) ATT_CH * HD;     // [AX_PT][32]
+    float* sc_s = w_s + (size_t) AX_PT * ATT_CH; // [AX_PT]
+    int* np_s = reinterpret_cast<int*>(sc_s + AX_PT);   // [AX_PT]: positions of the chunk the pair takes (0: none)
+    const float rs = ex_rsqrt((float) HD);
+    const int grp = tid / HD, d = tid % HD;
+    const int npairs = nr * qpk;
 #pragma unroll 1
-    for (int c0 = p0; c0 < p1; c0 += ATT_CH) {
-        const int np = min(ATT_CH, p1 - c0);
-        float vr[ATT_CH];
-#pragma unroll
-        for (int pp = 0; pp < ATT_CH; ++pp) {
-            const size_t r = kv_row_at(g, pp < np ? c0 + pp : 0, nkv, HD) + (size_t) kvl * HD + i;
-            kk[pp * (HD + 1) + i] = pp < np ? h2f(kc[r]) : 0.f;
-            vr[pp] = pp < np ? h2f(vc[r]) : 0.f;
+    for (int pb = 0; pb < npairs; pb += AX_PT) {
+        const int npt = min(AX_PT, npairs - pb);
+        __syncthreads();
+        for (int e = tid; e < npt * (HD / 4); e += AX_THREADS) {
+            const int pi = e / (HD / 4), c4 = e % (HD / 4), t = rows_s[(pb + pi) / qpk], h = kvl * qpk + (pb + pi) % qpk;
+            reinterpret_cast<float4*>(q_s + (size_t) pi * HD)[c4] = reinterpret_cast<const float4*>(qg + ((size_t) t * nq + h) * 2 * HD)[c4];
         }
-        __syncthreads();
+        float m[AX_PPW], z[AX_PPW];
 #pragma unroll
-        for (int k = 0; k < HPW; ++k) {
-            const int hh = warp + k * NW;
-            if (hh >= qpk) break;
-            float sacc = 0.f;
-#pragma unroll 8
-            for (int d = 0; d < HD; ++d) sacc = ffma(q[hh * HD + d], kk[lane * (HD + 1) + d], sacc);
-            const float sv = lane < np ? fmul(sacc, rs) : -INFINITY;
-            const float mn = fmaxf(m[k], wmax(sv));
-            const float w = sv == -INFINITY ? 0.f : ex_expf(fsub(sv, mn));
-            const float sc = m[k] == -INFINITY ? 0.f : ex_expf(fsub(m[k], mn));
-            z[k] = ffma(z[k], sc, wsum(w));
-            m[k] = mn;
-            e[hh * ATT_CH + lane] = w;
-            if (lane == 0) scale[hh] = sc;
+        for (int i = 0; i < AX_PPW; ++i) m[i] = -INFINITY, z[i] = 0.f;
+        float acc[APT];
+#pragma unroll
+        for (int i = 0; i < APT; ++i) acc[i] = 0.f;
+#pragma unroll 1
+        for (int c0 = p0; c0 < pend; c0 += ATT_CH) {
+            const int npmax = min(ATT_CH, pend - c0);
+            __syncthreads();   // the chunk before has been used up
+            // ---- the chunk's K and V rows as f32: 16-byte pieces of 8 halves
+            for (int e = tid; e < ATT_CH * (HD / 8); e += AX_THREADS) {
+                const int pp = e / (HD / 8), c8 = e % (HD / 8);
+                uint4 kr = make_uint4(0, 0, 0, 0), vr = kr;
+                if (pp < npmax) {
+                    const size_t at = kv_row_at(g, c0 + pp, nkv, HD) + (size_t) kvl * HD + 8 * c8;
+                    kr = *reinterpret_cast<const uint4*>(kc + at);
+                    vr = *reinterpret_cast<const uint4*>(vc + at);
+                }
+                const unsigned kw[4] = {kr.x, kr.y, kr.z, kr.w}, vw[4] = {vr.x, vr.y, vr.z, vr.w};
+                float kf[8], vf[8];
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    kf[2 * k] = h2f((uint16_t) (kw[k] & 0xffff)), kf[2 * k + 1] = h2f((uint16_t) (kw[k] >> 16));
+                    vf[2 * k] = h2f((uint16_t) (vw[k] & 0xffff)), vf[2 * k + 1] = h2f((uint16_t) (vw[k] >> 16));
+                }
+                float4* kd = reinterpret_cast<float4*>(k_s + (size_t) pp * KLD + 8 * c8);
+                float4* vd = reinterpret_cast<float4*>(v_s + (size_t) pp * HD + 8 * c8);
+                kd[0] = make_float4(kf[0], kf[1], kf[2], kf[3]), kd[1] = make_float4(kf[4], kf[5], kf[6], kf[7]);
+                vd[0] = make_float4(vf[0], vf[1], vf[2], vf[3]), vd[1] = make_float4(vf[4], vf[5], vf[6], vf[7]);
+            }
+            __syncthreads();
+            // ---- scores: this lane's position against the warp's pairs, each a fused chain over the head dimension
+            float sa[AX_PPW];
+#pragma unroll
+            for (int i = 0; i < AX_PPW; ++i) sa[i] = 0.f;
+            const float4* k4 = reinterpret_cast<const float4*>(k_s + (size_t) lane * KLD);
+#pragma unroll 2
+            for (int c4 = 0; c4 < HD / 4; ++c4) {
+                const float4 kk = k4[c4];
+#pragma unroll
+                for (int i = 0; i < AX_PPW; ++i) {
+                    const float4 qq = reinterpret_cast<const float4*>(q_s + (size_t) (warp + AX_WARPS * i) * HD)[c4];
+                    sa[i] = ffma(qq.x, kk.x, sa[i]);
+                    sa[i] = ffma(qq.y, kk.y, sa[i]);
+                    sa[i] = ffma(qq.z, kk.z, sa[i]);
+                    sa[i] = ffma(qq.w, kk.w, sa[i]);
+                }
+            }
+            // ---- the online-softmax step of every pair of the warp (all lanes hold the pair's m and z)
+#pragma unroll
+            for (int i = 0; i < AX_PPW; ++i) {
+                const int pi = warp + AX_WARPS * i;
+                if (pi < npt) {
+                    const int t = rows_s[(pb + pi) / qpk];
+                    const int np = min(ATT_CH, min(ctx_s[t], p0 + len) - c0);   // <= 0: this row's run ended before the chunk
+                    if (np > 0) {
+                        const float sv = lane < np ? fmul(sa[i], rs) : -INFINITY;
+                        const float mn = fmaxf(m[i], wmax(sv));
+                        const float w = sv == -INFINITY ? 0.f : ex_expf(fsub(sv, mn));
+                        const float sc = m[i] == -INFINITY ? 0.f : ex_expf(fsub(m[i], mn));
+                        z[i] = ffma(z[i], sc, wsum(w));
+                        m[i] = mn;
+                        w_s[pi * ATT_CH + lane] = w;
+                        if (lane == 0) sc_s[pi] = sc;
+                    }
+                    if (lane == 0) np_s[pi] = max(np, 0);
+                }
+            }
+            __syncthreads();
+            // ---- values: acc = acc sc, then + w v in ascending position, for this thread's dimension
+            float vv[ATT_CH];
+#pragma unroll
+            for (int pp = 0; pp < ATT_CH; ++pp) vv[pp] = v_s[(size_t) pp * HD + d];
+#pragma unroll
+            for (int i = 0; i < APT; ++i) {
+                const int pi = grp * APT + i;
+                if (pi < npt) {
+                    const int np = np_s[pi];
+                    if (np == ATT_CH) {
+                        float a = fmul(acc[i], sc_s[pi]);
+                        const float4* w4 = reinterpret_cast<const float4*>(w_s + (size_t) pi * ATT_CH);
+#pragma unroll
+                        for (int p4 = 0; p4 < ATT_CH / 4; ++p4) {
+                            const float4 ww = w4[p4];
+                            a = ffma(ww.x, vv[4 * p4], a);
+                            a = ffma(ww.y, vv[4 * p4 + 1], a);
+                            a = ffma(ww.z, vv[4 * p4 + 2], a);
+                            a = ffma(ww.w, vv[4 * p4 + 3], a);
+                        }
+                        acc[i] = a;
+                    } else if (np > 0) {   // a row's last, partial chunk
+                        float a = fmul(acc[i], sc_s[pi]);
+                        for (int pp = 0; pp < np; ++pp) a = ffma(w_s[pi * ATT_CH + pp], v_s[(size_t) pp * HD + d], a);
+                        acc[i] = a;
+                    }
+                }
+            }
         }
-        __syncthreads();
+        // ---- this run's partial of every pair of the tile
 #pragma unroll
-        for (int hh = 0; hh < ATT_MAXQPK; ++hh)
-            if (hh < qpk) acc[hh] = fmul(acc[hh], scale[hh]);
+        for (int i = 0; i < APT; ++i) {
+            const int pi = grp * APT + i;
+            if (pi < npt) {
+                const int t = rows_s[(pb + pi) / qpk], h = kvl * qpk + (pb + pi) % qpk;
+                acc_out[(((size_t) t * nq + h) * ATT_SPLITS + s) * HD + d] = acc[i];
+            }
+        }
 #pragma unroll
-        for (int pp = 0; pp < ATT_CH; ++pp)
-#pragma unroll
-            for (int hh = 0; hh < ATT_MAXQPK; ++hh)
-                if (hh < qpk) acc[hh] = ffma(e[hh * ATT_CH + pp], vr[pp], acc[hh]);
-        __syncthreads();
-    }
-#pragma unroll
-    for (int hh = 0; hh < ATT_MAXQPK; ++hh) {
-        if (hh >= qpk) break;
-        acc_out[(((size_t) t * nq + h0 + hh) * ATT_SPLITS + s) * HD + i] = acc[hh];
-    }
-#pragma unroll
-    for (int k = 0; k < HPW; ++k) {
-        const int hh = warp + k * NW;
-        if (hh < qpk && lane == 0) mz_out[((size_t) t * nq + h0 + hh) * ATT_SPLITS + s] = AttPart{m[k], z[k]};
+        for (int i = 0; i < AX_PPW; ++i) {
+            const int pi = warp + AX_WARPS * i;
+            if (pi < npt && lane == 0) {
+                const int t = rows_s[(pb + pi) / qpk], h = kvl * qpk + (pb + pi) % qpk;
+                mz_out[((size_t) t * nq + h) * ATT_SPLITS + s] = AttPart{m[i], z[i]};
+            }
+        }
     }
 }
 
-// the 16 splits of (row t, head h) as one partial: part[(t nq + h) (hd + 2)] = acc[hd], m, z
-__global__ void k_attn_local(const float* __restrict__ acc_in, const AttPart* __restrict__ mz_in, float* __restrict__ part, int nq,
-                             int hd) {
-    const int h = blockIdx.x, t = blockIdx.y, i = threadIdx.x;
-    const size_t base = ((size_t) t * nq + h) * ATT_SPLITS;
-    float mx = -INFINITY;
-#pragma unroll
-    for (int s = 0; s < ATT_SPLITS; ++s) mx = fmaxf(mx, mz_in[base + s].m);
-    float z = 0.f, acc = 0.f;
-#pragma unroll
-    for (int s = 0; s < ATT_SPLITS; ++s) {
-        const AttPart p = mz_in[base + s];
-        if (p.m == -INFINITY) continue;
-        const float w = ex_expf(fsub(p.m, mx));
-        z = ffma(w, p.z, z);
-        acc = ffma(w, acc_in[(base + s) * hd + i], acc);
+// the 16 runs of every (row t, head) as one partial: part[(t nq + h) (hd + 2)] = acc[hd], m, z.  Block = row t; a warp
+// per head first turns the runs' maxima into weights exp(m_s - max) (a run without positions is left out), z added in
+// run order by one lane; then every thread adds its elements' 16 weighted accumulators in run order.
+__global__ void __launch_bounds__(256) k_attn_join_runs(const float* __restrict__ acc_in, const AttPart* __restrict__ mz_in,
+                                                        float* __restrict__ part, int nq, int hd) {
+    extern __shared__ float jw[];   // [nq][16] weights, negative where the run is left out
+    const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    for (int h = warp; h < nq; h += 8) {
+        const size_t base = ((size_t) t * nq + h) * ATT_SPLITS;
+        const AttPart p = lane < ATT_SPLITS ? mz_in[base + lane] : AttPart{-INFINITY, 0.f};
+        const float mx = wmax(p.m);
+        const float w = p.m == -INFINITY ? -1.f : ex_expf(fsub(p.m, mx));
+        if (lane < ATT_SPLITS) jw[h * ATT_SPLITS + lane] = w;
+        float zs = 0.f;
+        for (int r = 0; r < ATT_SPLITS; ++r) {
+            const float wr = __shfl_sync(0xffffffffu, w, r), zr = __shfl_sync(0xffffffffu, p.z, r);
+            if (wr >= 0.f) zs = ffma(wr, zr, zs);
+        }
+        if (lane == 0) {
+            float* o = part + ((size_t) t * nq + h) * (hd + 2);
+            o[hd] = mx, o[hd + 1] = zs;
+        }
     }
-    float* o = part + ((size_t) t * nq + h) * (hd + 2);
-    o[i] = acc;
-    if (i == 0) o[hd] = mx, o[hd + 1] = z;
+    __syncthreads();
+    for (int e = tid; e < nq * hd; e += 256) {
+        const int h = e / hd, i = e % hd;
+        const float* a = acc_in + ((size_t) t * nq + h) * ATT_SPLITS * hd + i;
+        float v[ATT_SPLITS], acc = 0.f;
+#pragma unroll
+        for (int r = 0; r < ATT_SPLITS; ++r) v[r] = a[(size_t) r * hd];
+#pragma unroll
+        for (int r = 0; r < ATT_SPLITS; ++r) {
+            const float w = jw[h * ATT_SPLITS + r];
+            if (w >= 0.f) acc = ffma(w, v[r], acc);
+        }
+        part[((size_t) t * nq + h) * (hd + 2) + i] = acc;
+    }
 }
 
 // the GPUs' partials of head h0 + blockIdx.x merged in ring order starting at partial `first` + 1 and ending with
@@ -244,21 +369,20 @@ static int attn_partial_rows(const float* qg, const uint16_t* kc, const uint16_t
     FNX_REQUIRE(hd == 256 || hd == 128, "attn: head dim %d (128 or 256)", hd);
     FNX_REQUIRE(nkv >= 1 && nq % nkv == 0 && nq / nkv <= ATT_MAXQPK, "attn: %d query heads over %d KV heads", nq, nkv);
     FNX_REQUIRE(ncard >= 1 && card >= 0 && card < ncard, "attn: GPU %d of %d", card, ncard);
-    const int qpk = nq / nkv;
     float* acc = scratch;
     AttPart* mz = (AttPart*) (scratch + (size_t) T * nq * ATT_SPLITS * hd);
-    const size_t sm = ((size_t) qpk * hd + (size_t) ATT_CH * (hd + 1) + (size_t) qpk * ATT_CH + qpk) * sizeof(float);
-    const dim3 grid(ATT_SPLITS, T, nkv);
+    const size_t sm = ((size_t) AX_PT * hd + (size_t) ATT_CH * (hd + 4) + (size_t) ATT_CH * hd + (size_t) AX_PT * ATT_CH + 2 * AX_PT) * sizeof(float);
+    const dim3 grid(ATT_SPLITS, nkv, T);   // block z = t works only when row t leads a group of rows
     if (hd == 256) {
-        if (sm > 48 * 1024) cudaFuncSetAttribute(k_attn_part<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) sm);
-        k_attn_part<256><<<grid, 256, sm, strm(st)>>>(qg, kc, vc, g, acc, mz, nq, nkv, pos0, card, ncard, lr);
+        if (smem_optin(k_attn_rows<256>, sm, "attn partial")) return 1;
+        k_attn_rows<256><<<grid, AX_THREADS, sm, strm(st)>>>(qg, kc, vc, g, acc, mz, T, nq, nkv, pos0, card, ncard, lr);
     } else {
-        if (sm > 48 * 1024) cudaFuncSetAttribute(k_attn_part<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) sm);
-        k_attn_part<128><<<grid, 128, sm, strm(st)>>>(qg, kc, vc, g, acc, mz, nq, nkv, pos0, card, ncard, lr);
+        if (smem_optin(k_attn_rows<128>, sm, "attn partial")) return 1;
+        k_attn_rows<128><<<grid, AX_THREADS, sm, strm(st)>>>(qg, kc, vc, g, acc, mz, T, nq, nkv, pos0, card, ncard, lr);
     }
     if (launch_ok("attn partial")) return 1;
-    k_attn_local<<<dim3(nq, T), hd, 0, strm(st)>>>(acc, mz, part, nq, hd);
-    return launch_ok("attn local");
+    k_attn_join_runs<<<T, 256, (size_t) nq * ATT_SPLITS * sizeof(float), strm(st)>>>(acc, mz, part, nq, hd);
+    return launch_ok("attn join");
 }
 
 int fnx_attn_partial_exact(const float* qg, const uint16_t* kc, const uint16_t* vc, FnxKvPages g, float* part, int card, int ncard, int T,

@@ -15,6 +15,8 @@ char* err_buf();
 int fail(const char* fmt, ...);
 // cudaGetLastError after a launch: 0, or the failure recorded under `what`
 int launch_ok(const char* what);
+// kernels launched by this library so far (every launch is checked by one launch_ok()); reset: read and zero
+long launch_count(bool reset);
 
 inline cudaStream_t strm(void* st) { return (cudaStream_t) st; }
 

@@ -165,161 +165,6 @@ struct QSegs {
     int stride[3], rows[3], blk_end[3];
 };
 
-template <int NT>   // activation rows in tiles of 8: 1 (T <= 8) or 2
-__global__ void __launch_bounds__(QM_THREADS, 2) k_q8s_mma(const QSegs sg, int cols,
-                                                          const uint8_t* __restrict__ yq, const int8_t* __restrict__ pq,
-                                                          const float* __restrict__ pd, int T, unsigned sw_off, unsigned ring_off) {
-    extern __shared__ __align__(16) unsigned char smem[];
-    // this block's segment, by selects (indexing the parameter arrays at run time would put them in local memory)
-    const int seg = (int) blockIdx.x < sg.blk_end[0] ? 0 : (int) blockIdx.x < sg.blk_end[1] ? 1 : 2;
-    const int8_t* __restrict__ wq = seg == 0 ? sg.q[0] : seg == 1 ? sg.q[1] : sg.q[2];
-    const uint16_t* __restrict__ wd = seg == 0 ? sg.d[0] : seg == 1 ? sg.d[1] : sg.d[2];
-    float* __restrict__ out = seg == 0 ? sg.out[0] : seg == 1 ? sg.out[1] : sg.out[2];
-    const int out_stride = seg == 0 ? sg.stride[0] : seg == 1 ? sg.stride[1] : sg.stride[2];
-    const int rows = seg == 0 ? sg.rows[0] : seg == 1 ? sg.rows[1] : sg.rows[2];
-    const int blk0 = seg == 0 ? 0 : seg == 1 ? sg.blk_end[0] : sg.blk_end[1];
-    const int nb = cols / 32, lda = cols + QM_APAD, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, q = lane & 3, r8 = lane >> 2;
-    int8_t* sq = reinterpret_cast<int8_t*>(smem);                          // [8 NT][cols + pad], rows >= T zero
-    float* sd = reinterpret_cast<float*>(smem + (size_t) 8 * NT * lda);    // [8 NT][nb]
-    float* red = reinterpret_cast<float*>(smem);                           // after the main loop: [32 lanes][QM_ROWS][8 NT]
-    float* sw = reinterpret_cast<float*>(smem + sw_off);                   // the block's weight scales [QM_ROWS][nb + 1]
-    const int row0 = ((int) blockIdx.x - blk0) * QM_ROWS;
-    for (int it = tid; it < QM_ROWS * nb; it += QM_THREADS) {
-        const int r = it / nb, b = it % nb;
-        sw[r * (nb + 1) + b] = h2f(__ldg(wd + (size_t) min(row0 + r, rows - 1) * nb + b));
-    }
-    for (int it = tid; it < 8 * NT * nb; it += QM_THREADS) {
-        const int t = it / nb, b = it % nb;
-        uint4 v0 = make_uint4(0, 0, 0, 0), v1 = v0;
-        float d = 0.f;
-        if (t < T) {
-            if (yq) {
-                const unsigned* src = reinterpret_cast<const unsigned*>(yq + (size_t) it * 36);
-                d = h2f((uint16_t) (src[0] & 0xffff));
-                v0 = make_uint4(src[1], src[2], src[3], src[4]);
-                v1 = make_uint4(src[5], src[6], src[7], src[8]);
-            } else {
-                const uint4* src = reinterpret_cast<const uint4*>(pq + (size_t) t * cols + b * 32);
-                v0 = src[0], v1 = src[1];
-                d = pd[it];
-            }
-        }
-        uint4* dst = reinterpret_cast<uint4*>(sq + (size_t) t * lda + b * 32);
-        dst[0] = v0, dst[1] = v1;
-        sd[it] = d;
-    }
-    __syncthreads();
-    f32x2 acc[QM_MT][4][NT][2];   // [..][h]: row 8 h + lane / 4 of the tile, activation rows 2 (lane % 4), + 1
-#pragma unroll
-    for (int mt = 0; mt < QM_MT; ++mt)
-#pragma unroll
-        for (int v = 0; v < 4; ++v)
-#pragma unroll
-            for (int nt = 0; nt < NT; ++nt) acc[mt][v][nt][0] = acc[mt][v][nt][1] = 0ull;
-    const f32x2 unmagic = pack2(-12582912.0f, -12582912.0f);
-    // the warp's weights: its 64 columns of the block's 32 rows per step (2 KB) come through a two-stage ring of its own,
-    // filled with 16-byte cp.async (4 lanes cover a row's 64 contiguous bytes) one step ahead of the MMAs; rows are padded
-    // to 80 bytes so that the fragment reads (row lane / 4, 4 bytes at 4 (lane % 4)) hit 32 different banks
-    unsigned char* ring = smem + ring_off + (size_t) warp * 2 * QM_ROWS * QM_RING_LD;
-    const int8_t* src[4];
-    unsigned dst[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const int j = lane + 32 * i, row = j >> 2, seg = j & 3;
-        src[i] = wq + (size_t) min(row0 + row, rows - 1) * cols + 16 * seg;
-        dst[i] = (unsigned) __cvta_generic_to_shared(ring + row * QM_RING_LD + 16 * seg);
-    }
-    auto issue = [&](int cb, int stage) {
-#pragma unroll
-        for (int i = 0; i < 4; ++i)
-            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst[i] + stage * QM_ROWS * QM_RING_LD), "l"(src[i] + cb));
-        asm volatile("cp.async.commit_group;");
-    };
-    if (64 * warp < cols) issue(64 * warp, 0);
-    int it = 0;
-#pragma unroll 1
-    for (int cb = 64 * warp; cb < cols; cb += 512, ++it) {
-        if (cb + 512 < cols) {
-            issue(cb + 512, (it + 1) & 1);
-            asm volatile("cp.async.wait_group 1;" ::: "memory");
-        } else {
-            asm volatile("cp.async.wait_group 0;" ::: "memory");
-        }
-        __syncwarp();
-        const unsigned char* rs = ring + (size_t) (it & 1) * QM_ROWS * QM_RING_LD + r8 * QM_RING_LD + 4 * q;
-        unsigned a[QM_MT][4][2];
-#pragma unroll
-        for (int mt = 0; mt < QM_MT; ++mt)
-#pragma unroll
-            for (int v = 0; v < 4; ++v) {
-                a[mt][v][0] = *reinterpret_cast<const unsigned*>(rs + (16 * mt) * QM_RING_LD + 16 * v);
-                a[mt][v][1] = *reinterpret_cast<const unsigned*>(rs + (16 * mt + 8) * QM_RING_LD + 16 * v);
-            }
-#pragma unroll
-        for (int bb = 0; bb < 2; ++bb) {   // the two 32-column blocks of the warp's 64 columns
-            const int b = (cb >> 5) + bb;
-            f32x2 w[QM_MT][2][NT];   // fl(dw da) of (row, activation row pair) for this block
-            f32x2 da[NT];
-#pragma unroll
-            for (int nt = 0; nt < NT; ++nt) da[nt] = pack2(sd[(8 * nt + 2 * q) * nb + b], sd[(8 * nt + 2 * q + 1) * nb + b]);
-#pragma unroll
-            for (int mt = 0; mt < QM_MT; ++mt)
-#pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    const float dw = sw[(16 * mt + 8 * h + r8) * (nb + 1) + b];
-                    const f32x2 dw2 = pack2(dw, dw);
-#pragma unroll
-                    for (int nt = 0; nt < NT; ++nt) w[mt][h][nt] = mul2(dw2, da[nt]);
-                }
-#pragma unroll
-            for (int vv = 0; vv < 2; ++vv) {
-                const int v = 2 * bb + vv, c = cb + 16 * v;
-                unsigned bf[NT];
-#pragma unroll
-                for (int nt = 0; nt < NT; ++nt) bf[nt] = *reinterpret_cast<const unsigned*>(sq + (size_t) (8 * nt + r8) * lda + c + 4 * q);
-#pragma unroll
-                for (int mt = 0; mt < QM_MT; ++mt)
-#pragma unroll
-                    for (int nt = 0; nt < NT; ++nt) {
-                        int d[4];
-                        mma_s8_16816(d, a[mt][v][0], a[mt][v][1], bf[nt]);
-                        acc[mt][v][nt][0] = fma2(w[mt][0][nt], add2(pack2i(d[0], d[1]), unmagic), acc[mt][v][nt][0]);
-                        acc[mt][v][nt][1] = fma2(w[mt][1][nt], add2(pack2i(d[2], d[3]), unmagic), acc[mt][v][nt][1]);
-                    }
-            }
-        }
-        __syncwarp();   // every lane has read this stage before the next step's copies land in it
-    }
-    __syncthreads();   // the activations are no longer read: their memory takes the lane sums
-    constexpr int TO = 8 * NT, OUTS = QM_ROWS * TO;
-#pragma unroll
-    for (int mt = 0; mt < QM_MT; ++mt)
-#pragma unroll
-        for (int v = 0; v < 4; ++v)
-#pragma unroll
-            for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-                for (int h = 0; h < 2; ++h)
-                    *reinterpret_cast<f32x2*>(red + (size_t) (4 * warp + v) * OUTS + (16 * mt + 8 * h + r8) * TO + 8 * nt + 2 * q) =
-                        acc[mt][v][nt][h];
-    __syncthreads();
-    for (int o = 2 * tid; o < OUTS; o += 2 * QM_THREADS) {   // two neighbouring activation rows of a weight row a thread
-        f32x2 p[32];
-#pragma unroll
-        for (int l = 0; l < 32; ++l) p[l] = *reinterpret_cast<const f32x2*>(red + (size_t) l * OUTS + o);
-#pragma unroll
-        for (int w2 = 16; w2; w2 >>= 1)
-#pragma unroll
-            for (int l = 0; l < 16; ++l)
-                if (l < w2) p[l] = add2(p[l], p[l + w2]);
-        const int row = row0 + o / TO, t = o % TO;
-        float v0, v1;
-        unpack2(p[0], v0, v1);
-        if (row < rows && t < T) out[(size_t) t * out_stride + row] = v0;
-        if (row < rows && t + 1 < T) out[(size_t) (t + 1) * out_stride + row] = v1;
-    }
-}
-
 // ---------------------------------------------------------------- the same sums, weights streamed by persistent blocks
 // One block of 16 warps per multiprocessor stages the activations once and walks row tiles (16 MT rows) until the
 // matrix is done.  With WPT = 8 the block is two groups of 8 warps on tiles of their own (their only shared state is
@@ -629,7 +474,6 @@ __global__ void __launch_bounds__(256) k_swiglu_rows(const float* __restrict__ g
     if (lane == 0) hd[(size_t) e * nb + b] = h2f(f2h(d));
 }
 
-// the tensor-core kernel over 1..3 matrices; -1 when its shared memory does not fit (the caller falls back)
 static int sm_count() {
     static int n[64] = {};
     int dev = 0;
@@ -694,50 +538,15 @@ int q8s_stream_launch(const FnxQ8S* w, const int* rows, float* const* out, const
     return -1;
 }
 
-int q8s_mma_launch(const FnxQ8S* w, const int* rows, float* const* out, const int* out_stride, int nseg, int cols, const void* yq,
-                   const int8_t* pq, const float* pd, int T, cudaStream_t st, const char* what) {
-    const int NT = T <= 8 ? 1 : 2;
-    const size_t act = (size_t) 8 * NT * (cols + QM_APAD) + (size_t) 8 * NT * (cols / 32) * 4, redb = (size_t) 32 * QM_ROWS * 8 * NT * 4;
-    // activations | weight scales | the warps' rings; the lane sums reuse the whole region after the main loop
-    const size_t sw_off = (act + 15) & ~(size_t) 15;
-    const size_t ring_off = (sw_off + (size_t) QM_ROWS * (cols / 32 + 1) * 4 + 15) & ~(size_t) 15;
-    const size_t used = ring_off + (size_t) (QM_THREADS / 32) * 2 * QM_ROWS * QM_RING_LD;
-    const size_t smm = used > redb ? used : redb;
-    if (smm > 227 * 1024) return -1;
-    for (int s = 0; s < nseg; ++s)
-        if ((uintptr_t) w[s].q % 16) return -1;   // the 16-byte copies need aligned rows
-    QSegs sg{};
-    int g = 0;
-    for (int s = 0; s < 3; ++s) {
-        const int k = s < nseg ? s : nseg - 1;
-        sg.q[s] = w[k].q, sg.d[s] = w[k].d, sg.out[s] = out[k], sg.stride[s] = out_stride[k], sg.rows[s] = rows[k];
-        if (s < nseg) g += (rows[s] + QM_ROWS - 1) / QM_ROWS;
-        sg.blk_end[s] = g;
-    }
-    if (NT == 1) {
-        if (smm > 48 * 1024 && cudaFuncSetAttribute(k_q8s_mma<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smm) != cudaSuccess)
-            return fail("%s: shared memory opt-in failed", what);
-        k_q8s_mma<1><<<g, QM_THREADS, smm, st>>>(sg, cols, (const uint8_t*) yq, pq, pd, T, (unsigned) sw_off, (unsigned) ring_off);
-    } else {
-        if (smm > 48 * 1024 && cudaFuncSetAttribute(k_q8s_mma<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smm) != cudaSuccess)
-            return fail("%s: shared memory opt-in failed", what);
-        k_q8s_mma<2><<<g, QM_THREADS, smm, st>>>(sg, cols, (const uint8_t*) yq, pq, pd, T, (unsigned) sw_off, (unsigned) ring_off);
-    }
-    return launch_ok(what);
-}
-
 int q8s_launch(FnxQ8S w, int rows, int cols, const void* yq, const int8_t* pq, const float* pd, float* out, int out_stride, int T,
                cudaStream_t st, const char* what) {
     if (!(T >= 1 && T <= FNX_MAXT)) return fail("%s: T %d outside 1..%d", what, T, FNX_MAXT);
     if (!(cols > 0 && cols % 32 == 0 && rows > 0)) return fail("%s: %d x %d (columns a multiple of 32)", what, rows, cols);
-    if (cols % 64 == 0) {   // the tensor-core kernel: 32 rows a block
+    if (cols % 64 == 0) {   // the persistent tensor-core kernel
         const FnxQ8S ws[1] = {w};
         const int rs[1] = {rows}, strides[1] = {out_stride};
         float* outs[1] = {out};
-        static const bool tiled = getenv("FNX_DENSE_TILED") != nullptr;   // a tuning knob: the one-tile-a-block kernel instead
-        int rc = tiled ? -1 : q8s_stream_launch(ws, rs, outs, strides, 1, cols, yq, pq, pd, T, st, what);
-        if (rc >= 0) return rc;
-        rc = q8s_mma_launch(ws, rs, outs, strides, 1, cols, yq, pq, pd, T, st, what);
+        const int rc = q8s_stream_launch(ws, rs, outs, strides, 1, cols, yq, pq, pd, T, st, what);
         if (rc >= 0) return rc;
     }
     // enough blocks to fill the GPU twice over, at most 128 rows each so the staged activations are amortised
@@ -776,10 +585,7 @@ int fnx_q8s_gemv_segs(const FnxQ8S* w, const int* rows, float* const* out, const
     FNX_REQUIRE(n >= 1 && n <= 3, "q8s_gemv_segs: %d matrices (1..3)", n);
     FNX_REQUIRE(T >= 1 && T <= FNX_MAXT, "q8s_gemv_segs: T %d outside 1..%d", T, FNX_MAXT);
     if (cols % 64 == 0) {
-        static const bool tiled = getenv("FNX_DENSE_TILED") != nullptr;
-        int rc = tiled ? -1 : q8s_stream_launch(w, rows, out, out_stride, n, cols, y, nullptr, nullptr, T, strm(st), "q8s_gemv_segs");
-        if (rc >= 0) return rc;
-        rc = q8s_mma_launch(w, rows, out, out_stride, n, cols, y, nullptr, nullptr, T, strm(st), "q8s_gemv_segs");
+        const int rc = q8s_stream_launch(w, rows, out, out_stride, n, cols, y, nullptr, nullptr, T, strm(st), "q8s_gemv_segs");
         if (rc >= 0) return rc;
     }
     for (int s = 0; s < n; ++s)

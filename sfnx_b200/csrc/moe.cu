@@ -711,9 +711,6 @@ int fnx_moe_gate_up(const FnxExperts* A, const FnxJob* jobs, const int* njobs, i
         FNX_REQUIRE(n % 512 == 0 && n / 512 >= 1 && n / 512 <= 8, "moe gate|up q4_K: %d columns (multiples of 512 up to 4096)", n);
         // blocks of 128 rows with direct 16-byte loads one step ahead (measured faster than staging the weights through
         // shared memory, by cp.async rings or bulk copies: there every operand crosses the shared-memory pipe)
-        static const bool staged = getenv("FNX_GU_TMA") != nullptr;   // a tuning knob: the TMA-staged persistent kernel instead
-        if (staged && gu_q4k_tma_smem(n) + 1024 <= 227 * 1024 && ((uintptr_t) A->a % 16) == 0 && A->stride % 16 == 0)
-            return gu_q4k_tma_launch((const uint8_t*) A->a, A->stride, nrows, n, jobs, njobs, (const uint8_t*) xq, gu, strm(st));
         const dim3 grid((nrows + GU_RPB - 1) / GU_RPB, njobs_max);
         const size_t sm = (size_t) GU_TC * (n + (n / 64) * 16);
         const uint8_t* a = (const uint8_t*) A->a;

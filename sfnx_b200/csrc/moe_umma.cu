@@ -319,8 +319,10 @@ static int moe_umma(const char* what, const FnxExperts* A, const FnxBigJob* jobs
     FNX_REQUIRE(A && jobs && njobs && njobs_cap >= 1 && x && out, "%s: no experts, jobs, rows or output", what);
     FNX_REQUIRE(A->nrows >= 1 && A->ncols >= 32 && A->ncols % 32 == 0, "%s: %d x %d (columns in units of 32)", what, A->nrows, A->ncols);
     FNX_REQUIRE(((uintptr_t) x % 16) == 0, "%s: activation rows not 16-byte aligned", what);
+    unsigned* fault = device_fault_word();
+    FNX_REQUIRE(fault, "%s: no device fault word (no current device?)", what);
     MuArgs a{A->type, A->nrows, A->ncols, (const unsigned char*) A->a, (const unsigned char*) A->b, (const unsigned char*) A->c,
-             (const unsigned char*) A->d, A->stride, A->stride_b, jobs, njobs, x, out, device_fault_word()};
+             (const unsigned char*) A->d, A->stride, A->stride_b, jobs, njobs, x, out, fault};
     const dim3 grid((A->nrows + MU_BM - 1) / MU_BM, njobs_cap);
 #define MU_LAUNCH(T)                                                            \
     if (smem_optin(k_moe_umma<T>, MU_SMEM, what)) return 1;                     \

@@ -25,7 +25,7 @@ __device__ __forceinline__ void um_mma(unsigned tmem, unsigned long long da, uns
                  : "memory");
 }
 
-// Waits for the phase of `bar` with this parity; gives up after 2^22 polls, sets bit 1 of *fault and returns false (the
+// Waits for the phase of `bar` with this parity; gives up after 2^22 polls, sets bit 8 of *fault and returns false (the
 // caller goes on with what it has: no wait in these kernels is unbounded).
 __device__ __forceinline__ bool um_wait(unsigned long long* bar, unsigned parity, unsigned* fault) {
     unsigned ok = 0;
@@ -34,7 +34,7 @@ __device__ __forceinline__ bool um_wait(unsigned long long* bar, unsigned parity
                      : "=r"(ok)
                      : "r"(um_s32(bar)), "r"(parity)
                      : "memory");
-    if (!ok) atomicOr(fault, 1u);
+    if (!ok) atomicOr(fault, 8u);
     return ok != 0;
 }
 

@@ -1,4 +1,5 @@
 // Error reporting, activation quantisation, RMS norm, batched copies, load-time repacks, synthetic weights.
+#include <atomic>
 #include <cstdlib>
 #include <cstring>
 
@@ -29,9 +30,28 @@ bool pdl_on(int kind) {
     return !off && !g_pdl_hold && (mask >> kind & 1u);
 }
 void pdl_hold(bool hold) { g_pdl_hold = hold; }
+
+// ---- the device-side fault word: bit 8 = a bounded on-chip wait (an mbarrier of the tcgen05 kernels) ran out.  Kernels
+// launched inside a window report into the window's own error word instead (fault_sink), so that the host sees the
+// timeout with the window's other faults.
+static __device__ unsigned g_fault = 0;
+static thread_local unsigned* g_fault_sink = nullptr;
+void fault_sink(unsigned* err) { g_fault_sink = err; }
+unsigned* device_fault_word() {
+    if (g_fault_sink) return g_fault_sink;
+    static unsigned* ptr[64] = {};   // per device; written without a lock: every writer stores the same address
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    if (!ptr[dev] && cudaGetSymbolAddress((void**) &ptr[dev], g_fault) != cudaSuccess) ptr[dev] = nullptr;
+    return ptr[dev];
+}
+// every kernel launch of the library is followed by one launch_ok(): the launches are counted here
+static std::atomic<long> g_launches{0};
+long launch_count(bool reset) { return reset ? g_launches.exchange(0) : g_launches.load(); }
 int launch_ok(const char* what) {
     const cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return fail("%s: %s", what, cudaGetErrorString(e));
+    g_launches.fetch_add(1, std::memory_order_relaxed);
     return 0;
 }
 
@@ -281,6 +301,12 @@ extern "C" {
 
 const char* fnx_last_error(void) { return err_buf(); }
 int fnx_built_arch(void) { return 100; }
+unsigned fnx_device_fault(void) {
+    unsigned v = 0, zero = 0;
+    if (cudaMemcpyFromSymbol(&v, fnxk::g_fault, sizeof v) != cudaSuccess) return ~0u;
+    if (v) cudaMemcpyToSymbol(fnxk::g_fault, &zero, sizeof zero);
+    return v;
+}
 
 int fnx_quantize_q8_1(const float* x, void* q, int n, int rows, void* st) {
     FNX_REQUIRE(n > 0 && n % 32 == 0 && rows >= 0, "quantize_q8_1: n %d must be a positive multiple of 32", n);

@@ -7,14 +7,14 @@
 #include <cstring>
 
 #include "common.cuh"
+#include "moe_internal.cuh"
 
 namespace fnxk {
 
 static inline size_t al(size_t v) { return (v + 255) & ~(size_t) 255; }
 
-// per-call timing of a window enqueued outside a graph: an event before and after every C ABI call of a stage, and the
-// count of kernels the calls launch (the engine's own per-window timers are the reference's counterpart,
-// src/engine.hpp:182-187)
+// per-call timing of a window enqueued outside a graph: an event before and after every C ABI call of a stage (the
+// engine's own per-window timers are the reference's counterpart, src/engine.hpp:182-187)
 constexpr int TRACE_CAP = 4096;
 struct Trace {
     bool on = false;
@@ -23,7 +23,6 @@ struct Trace {
     const char* name[TRACE_CAP];
     int layer[TRACE_CAP];
     bool made = false;
-    long kernels = 0;
 };
 static Trace g_trace;
 
@@ -48,8 +47,7 @@ static int side_join(void* st) {
 struct Traced {
     int slot = -1;
     cudaStream_t st;
-    Traced(const char* name, int layer, int kernels, void* stream) : st((cudaStream_t) stream) {
-        g_trace.kernels += kernels;
+    Traced(const char* name, int layer, void* stream) : st((cudaStream_t) stream) {
         if (!g_trace.on || g_trace.n >= TRACE_CAP) return;
         slot = g_trace.n++;
         g_trace.name[slot] = name;
@@ -105,7 +103,7 @@ static Ws carve(const FnxStackCfg& c) {
     w.shq = take(fnx_moe_h_bytes((int) T, c.ff));
     w.sh = take(T * n * 4);
     w.logits = take(T * (size_t) c.vocab_rows * 4);
-    w.keys = take(T * 8);
+    w.keys = take(2 * T * 8);
     w.best_v = take(T * 4);
     w.best_i = take(T * 4);
     w.err = take(16);
@@ -158,11 +156,11 @@ using namespace fnxk;
     do {                  \
         if (call) return 1; \
     } while (0)
-// a traced call: name, kernels it launches
-#define TRK(name, kernels, call)                      \
-    do {                                              \
-        Traced tr_(name, sg.layer, kernels, st);      \
-        if (call) return 1;                           \
+// a traced call
+#define TRK(name, call)                      \
+    do {                                     \
+        Traced tr_(name, sg.layer, st);      \
+        if (call) return 1;                  \
     } while (0)
 
 extern "C" {
@@ -197,7 +195,7 @@ int fnx_window_init(const FnxStackCfg* cfg, void* ws, void* st) {
     const Ws w = carve(*cfg);
     char* b = (char*) ws;
     auto zero = [&](size_t at, size_t bytes) { return cudaMemsetAsync(b + at, 0, bytes, strm(st)) != cudaSuccess; };
-    if (zero(w.rscratch, fnx_router_scratch_bytes()) || zero(w.keys, FNX_MAXT * 8) || zero(w.err, 16) || zero(w.njobs, 16) ||
+    if (zero(w.rscratch, fnx_router_scratch_bytes()) || zero(w.keys, 2 * FNX_MAXT * 8) || zero(w.err, 16) || zero(w.njobs, 16) ||
         zero(w.gdn_scratch, fnx_gdn_scratch_floats(cfg->nv) * 4))
         return fail("window_init: %s", cudaGetErrorString(cudaGetLastError()));
     return 0;
@@ -230,41 +228,41 @@ static int window_stage(const FnxStackCfg* cfg, const FnxLayer* layers, const Fn
     const float* pending = stage == 0 ? nullptr : bo;
     if (sg.part == 3) {
         FNX_REQUIRE(head, "window: no head");
-        TRK("rms_norm", 1, fnx_rms_norm_rows(x, pending, head->norm, nullptr, xq, T, c.n, c.eps, st));
+        TRK("rms_norm", fnx_rms_norm_rows(x, pending, head->norm, nullptr, xq, T, c.n, c.eps, st));
         float* logits = (float*) (b + w.logits);
-        TRK("head", 1, fnx_q8s_gemv(head->out, c.vocab_rows, c.n, xq, logits, c.vocab_rows, T, st));
-        TRK("argmax", 2, fnx_argmax(logits, c.vocab_rows, T, c.vocab0, (float*) (b + w.best_v), (int*) (b + w.best_i),
+        TRK("head", fnx_q8s_gemv(head->out, c.vocab_rows, c.n, xq, logits, c.vocab_rows, T, st));
+        TRK("argmax", fnx_argmax(logits, c.vocab_rows, T, c.vocab0, (float*) (b + w.best_v), (int*) (b + w.best_i),
                                     (unsigned long long*) (b + w.keys), (unsigned*) (b + w.err), st));
         return 0;
     }
     const FnxLayer& L = layers[sg.layer];
     if (sg.part == 0 && L.kind == 0) {   // Gated DeltaNet mixer
         const int rows = (2 * c.nk + 2 * c.nv) * FNX_HS;
-        TRK("rms_norm", 1, fnx_rms_norm_rows(x, pending, L.norm1, xn, xq, T, c.n, c.eps, st));
+        TRK("rms_norm", fnx_rms_norm_rows(x, pending, L.norm1, xn, xq, T, c.n, c.eps, st));
         const bool forked = side_fork(st);
-        TRK("ab", 1, fnx_gemv_f32(L.ab, xn, (float*) (b + w.ab), 2 * c.nv, c.n, T, forked ? (void*) g_side.st : st));
-        TRK("qkvz", 1, fnx_q8s_gemv(L.qkvz, rows, c.n, xq, (float*) (b + w.qkvz), rows, T, st));
+        TRK("ab", fnx_gemv_f32(L.ab, xn, (float*) (b + w.ab), 2 * c.nv, c.n, T, forked ? (void*) g_side.st : st));
+        TRK("qkvz", fnx_q8s_gemv(L.qkvz, rows, c.n, xq, (float*) (b + w.qkvz), rows, T, st));
         if (forked) TRY(side_join(st));
         if (lanes) {   // every lane's rows chain through that lane's state, all lanes in one launch
             const FnxGdnLanes gl{lanes->S[sg.layer], lanes->hist[sg.layer], lanes->ctl, lanes->row0, L.snap, L.hsnap};
-            TRK("gdn_core", 1, fnx_gdn_core_segs((const float*) (b + w.qkvz), (const float*) (b + w.ab), L.conv, L.dt, L.a, L.ssm_norm, b + w.yq,
+            TRK("gdn_core", fnx_gdn_core_segs((const float*) (b + w.qkvz), (const float*) (b + w.ab), L.conv, L.dt, L.a, L.ssm_norm, b + w.yq,
                                                  (float*) (b + w.gdn_scratch), c.nk, c.nv, L.vmap, &gl, lanes->nseg, lanes->rows, c.eps, st));
         } else
-            TRK("gdn_core", 1, fnx_gdn_core((const float*) (b + w.qkvz), (const float*) (b + w.ab), L.hist, L.conv, L.dt, L.a, L.ssm_norm, L.S,
+            TRK("gdn_core", fnx_gdn_core((const float*) (b + w.qkvz), (const float*) (b + w.ab), L.hist, L.conv, L.dt, L.a, L.ssm_norm, L.S,
                                             b + w.yq, ctl, (float*) (b + w.gdn_scratch), L.snap, L.hsnap, c.nk, c.nv, L.vmap, T, c.eps, st, nullptr));
-        TRK("ssm_out", 1, fnx_q8s_gemv(L.ssm_out, c.n, c.nv * FNX_HS, b + w.yq, bo, c.n, T, st));
+        TRK("ssm_out", fnx_q8s_gemv(L.ssm_out, c.n, c.nv * FNX_HS, b + w.yq, bo, c.n, T, st));
         return 0;
     }
     if (sg.part == 0) {   // attention, up to this GPU's partials
         float* qg = (float*) (b + w.qg);
         float* k = (float*) (b + w.k);
         float* v = (float*) (b + w.v);
-        TRK("rms_norm", 1, fnx_rms_norm_rows(x, pending, L.norm1, nullptr, xq, T, c.n, c.eps, st));
+        TRK("rms_norm", fnx_rms_norm_rows(x, pending, L.norm1, nullptr, xq, T, c.n, c.eps, st));
         {   // q, k and v in one launch
             const FnxQ8S ws[3] = {L.wq, L.wk, L.wv};
             const int rows3[3] = {c.nq * c.hd * 2, c.nkv * c.hd, c.nkv * c.hd};
             float* const outs[3] = {qg, k, v};
-            TRK("wqkv", 1, fnx_q8s_gemv_segs(ws, rows3, outs, rows3, 3, c.n, xq, T, st));
+            TRK("wqkv", fnx_q8s_gemv_segs(ws, rows3, outs, rows3, 3, c.n, xq, T, st));
         }
         const FnxRope rope{c.rope_base, c.nrot};
         float* mine = (float*) (b + w.partials) + (size_t) c.card * T * c.nq * (c.hd + 2);
@@ -275,61 +273,76 @@ static int window_stage(const FnxStackCfg* cfg, const FnxLayer* layers, const Fn
                 const size_t r0 = (size_t) sI * lanes->rows;
                 FnxKvPages pg = L.pages;
                 pg.pt = lanes->pt_host[sI];
-                TRK("attn_prep_append", 1, fnx_attn_prep_append(qg + r0 * c.nq * 2 * c.hd, k + r0 * c.nkv * c.hd, v + r0 * c.nkv * c.hd, L.q_norm, L.k_norm,
+                TRK("attn_prep_append", fnx_attn_prep_append(qg + r0 * c.nq * 2 * c.hd, k + r0 * c.nkv * c.hd, v + r0 * c.nkv * c.hd, L.q_norm, L.k_norm,
                                                                 L.kc, L.vc, pg, c.card, c.ncard, lanes->rows, lanes->ctl_host[sI], c.eps, rope, c.nq,
                                                                 c.nkv, c.hd, st));
             }
-            TRK("attn_partial", 2, fnx_attn_part_lanes(qg, L.kc, L.vc, L.pages, FnxLaneRows{lanes->row_pos, lanes->row_pt}, mine, c.card, c.ncard, T,
+            TRK("attn_partial", fnx_attn_part_lanes(qg, L.kc, L.vc, L.pages, FnxLaneRows{lanes->row_pos, lanes->row_pt}, mine, c.card, c.ncard, T,
                                                        c.nq, c.nkv, c.hd, (float*) (b + w.att_scratch), st));
             return 0;
         }
-        TRK("attn_prep_append", 1, fnx_attn_prep_append(qg, k, v, L.q_norm, L.k_norm, L.kc, L.vc, L.pages, c.card, c.ncard, T, ctl, c.eps,
+        TRK("attn_prep_append", fnx_attn_prep_append(qg, k, v, L.q_norm, L.k_norm, L.kc, L.vc, L.pages, c.card, c.ncard, T, ctl, c.eps,
                                                         rope, c.nq, c.nkv, c.hd, st));
         // FNX_ATTN_EXACT=1: the scan in the reference's order of sums (bit-reproducible against the CPU statement, several
         // times slower); default: the one-pass tensor-core scan
         const char* ex = getenv("FNX_ATTN_EXACT");
         if (ex && ex[0] == '1')
-            TRK("attn_partial", 2, fnx_attn_partial_exact(qg, L.kc, L.vc, L.pages, mine, c.card, c.ncard, T, ctl, c.nq, c.nkv, c.hd,
+            TRK("attn_partial", fnx_attn_partial_exact(qg, L.kc, L.vc, L.pages, mine, c.card, c.ncard, T, ctl, c.nq, c.nkv, c.hd,
                                                           (float*) (b + w.att_scratch), st));
         else
-            TRK("attn_partial", 2, fnx_attn_partial(qg, L.kc, L.vc, L.pages, mine, c.card, c.ncard, T, ctl, c.nq, c.nkv, c.hd,
+            TRK("attn_partial", fnx_attn_partial(qg, L.kc, L.vc, L.pages, mine, c.card, c.ncard, T, ctl, c.nq, c.nkv, c.hd,
                                                     (float*) (b + w.att_scratch), st));
         return 0;
     }
     if (sg.part == 1) {   // attention: merge the GPUs' partials for this GPU's heads, gate, output projection
         const int own = c.nq / c.ncard;
         float* att = (float*) (b + w.att);
-        TRK("attn_finish", 1, fnx_attn_finish((const float*) (b + w.partials), c.ncard, c.card, (const float*) (b + w.qg), att, T, c.nq,
+        TRK("attn_finish", fnx_attn_finish((const float*) (b + w.partials), c.ncard, c.card, (const float*) (b + w.qg), att, T, c.nq,
                                               c.card * own, own, c.hd, st));
-        TRK("quantize", 1, fnx_quantize_q8_1(att, b + w.yq, own * c.hd, T, st));
-        TRK("wo", 1, fnx_q8s_gemv(L.wo, c.n, own * c.hd, b + w.yq, bo, c.n, T, st));
+        TRK("quantize", fnx_quantize_q8_1(att, b + w.yq, own * c.hd, T, st));
+        TRK("wo", fnx_q8s_gemv(L.wo, c.n, own * c.hd, b + w.yq, bo, c.n, T, st));
         return 0;
     }
     // FFN half
     const int P = T * c.topk;
     float* rl = (float*) (b + w.rlogits);
-    TRK("rms_norm", 1, fnx_rms_norm_rows(x, pending, L.norm2, xn, xq, T, c.n, c.eps, st));
+    TRK("rms_norm", fnx_rms_norm_rows(x, pending, L.norm2, xn, xq, T, c.n, c.eps, st));
     const bool forked = side_fork(st);   // the shared expert beside the router and the routed experts
     if (forked)
         TRY(fnx_shared_expert(L.sh_gate_up, L.sh_down, xq, T, c.n, c.ff, (float*) (b + w.sh_gu), b + w.shq, (float*) (b + w.sh), g_side.st));
-    TRK("router_route", 1, fnx_router_route(L.router, xn, rl, T, c.n, c.nexp, c.topk, (int*) (b + w.topi), (float*) (b + w.topw),
+    TRK("router_route", fnx_router_route(L.router, xn, rl, T, c.n, c.nexp, c.topk, (int*) (b + w.topi), (float*) (b + w.topw),
                                             (FnxJob*) (b + w.jobs_gu), (FnxJob*) (b + w.jobs_dn), (int*) (b + w.njobs), b + w.rscratch, st));
-    TRK("moe_gate_up", 1, fnx_moe_gate_up(&L.gate_up, (const FnxJob*) (b + w.jobs_gu), (const int*) (b + w.njobs), P, xq, (float*) (b + w.gu), st));
-    TRK("moe_down", 2, fnx_moe_down(&L.down, (const FnxJob*) (b + w.jobs_dn), (const int*) (b + w.njobs), P, (const float*) (b + w.gu), P,
+    TRK("moe_gate_up", fnx_moe_gate_up(&L.gate_up, (const FnxJob*) (b + w.jobs_gu), (const int*) (b + w.njobs), P, xq, (float*) (b + w.gu), st));
+    TRK("moe_down", fnx_moe_down(&L.down, (const FnxJob*) (b + w.jobs_dn), (const int*) (b + w.njobs), P, (const float*) (b + w.gu), P,
                                     b + w.hq, (float*) (b + w.part), st));
     if (forked) {
-        g_trace.kernels += 3;
         TRY(side_join(st));
     } else {
-        TRK("shared_expert", 3, fnx_shared_expert(L.sh_gate_up, L.sh_down, xq, T, c.n, c.ff, (float*) (b + w.sh_gu), b + w.shq, (float*) (b + w.sh), st));
+        TRK("shared_expert", fnx_shared_expert(L.sh_gate_up, L.sh_down, xq, T, c.n, c.ff, (float*) (b + w.sh_gu), b + w.shq, (float*) (b + w.sh), st));
     }
-    TRK("moe_combine", 1, fnx_moe_combine((const float*) (b + w.part), (const float*) (b + w.topw), (const float*) (b + w.sh), rl, c.nexp, bo,
+    TRK("moe_combine", fnx_moe_combine((const float*) (b + w.part), (const float*) (b + w.topw), (const float*) (b + w.sh), rl, c.nexp, bo,
                                           T, c.n, c.topk, st));
     return 0;
 }
 
+// a stage with the window's error word as the sink of its kernels' bounded waits (bit 8), so that a wait that ran out
+// shows in the word the host reads after the window
+static int window_stage_sunk(const FnxStackCfg* cfg, const FnxLayer* layers, const FnxHead* head, void* ws, int T, int stage,
+                             const FnxWindowLanes* lanes, void* st) {
+    if (check_cfg(cfg) || !ws) return fail("window: no configuration or workspace");
+    const Ws w = carve(*cfg);
+    unsigned* err = (unsigned*) ((char*) ws + w.err);
+    // a window starts with a clean error word: the host reads the word after every window (the reference's engine throws on
+    // it, src/engine_impl.hpp:154-167), so an earlier window's fault has been reported by then
+    if (stage == 0 && cudaMemsetAsync(err, 0, 4, strm(st)) != cudaSuccess) return fail("window: clearing the error word failed");
+    fault_sink(err);
+    const int rc = window_stage(cfg, layers, head, ws, T, stage, lanes, st);
+    fault_sink(nullptr);
+    return rc;
+}
+
 int fnx_window_stage(const FnxStackCfg* cfg, const FnxLayer* layers, const FnxHead* head, void* ws, int T, int stage, void* st) {
-    return window_stage(cfg, layers, head, ws, T, stage, nullptr, st);
+    return window_stage_sunk(cfg, layers, head, ws, T, stage, nullptr, st);
 }
 
 int fnx_window_stage_lanes(const FnxStackCfg* cfg, const FnxLayer* layers, const FnxHead* head, void* ws, const FnxWindowLanes* lanes, int stage,
@@ -338,7 +351,7 @@ int fnx_window_stage_lanes(const FnxStackCfg* cfg, const FnxLayer* layers, const
                 lanes ? lanes->nseg : 0, lanes ? lanes->rows : 0, FNX_MAXT);
     FNX_REQUIRE(lanes->ctl && lanes->row0 && lanes->row_pos && lanes->row_pt && lanes->ctl_host && lanes->pt_host && lanes->S && lanes->hist,
                 "window: lanes without their tables");
-    return window_stage(cfg, layers, head, ws, lanes->nseg * lanes->rows, stage, lanes, st);
+    return window_stage_sunk(cfg, layers, head, ws, lanes->nseg * lanes->rows, stage, lanes, st);
 }
 
 // keeps the first n[s] rows of lane s: its state and history from the checkpoints of window row s rows + n[s] - 1
@@ -428,12 +441,8 @@ int fnx_trace_end(float* ms, int* layer, const char** names, int cap) {
     }
     return n;
 }
-// kernels launched by fnx_window_stage calls since the last reset (reset != 0: read and zero)
-long fnx_window_kernel_count(int reset) {
-    const long k = g_trace.kernels;
-    if (reset) g_trace.kernels = 0;
-    return k;
-}
+// kernels this library has launched since the last reset (reset != 0: read and zero): counted where each launch is checked
+long fnx_window_kernel_count(int reset) { return launch_count(reset != 0); }
 
 // ---- the partition rule (reference src/card_split.hpp:12-26)
 int fnx_ff_lo(int ff, int n, int c) {

@@ -51,10 +51,24 @@ def moe_weights_q8(n, nexp, ffs, seed=0, sigma=0.02):
 
 
 def big_jobs(ntok, nexp, topk, seed=0, cap=64):
-    """The prompt path's jobs (the package's own generator, so that the tests and its microbenchmark route alike)."""
-    from sfnx_b200.moe_mma_bench import big_jobs as make
-
-    return make(ntok, nexp, topk, seed=seed, cap=cap)
+    """The prompt path's jobs: every token picks topk distinct experts, pair p = t topk + k; an expert's pairs in pair
+    order, cut into jobs of at most `cap` rows (reference src/kernels.hpp:25-32).  Returns (jobs, pairs)."""
+    rng = np.random.default_rng(seed)
+    picks = np.argsort(rng.random((ntok, nexp)), axis=1)[:, :topk]
+    order = np.argsort(picks.reshape(-1), kind="stable")   # pairs grouped by expert, in pair order inside an expert
+    experts = picks.reshape(-1)[order]
+    jobs, start = [], 0
+    while start < len(order):
+        e = experts[start]
+        end = start + int(np.searchsorted(experts[start:], e, side="right"))
+        for i in range(start, end, cap):
+            jobs.append((e, order[i:min(i + cap, end)]))
+        start = end
+    out = np.zeros(len(jobs), O.BIGJOB_DTYPE)
+    for j, (e, pairs) in enumerate(jobs):
+        out[j]["w"], out[j]["n"] = e, len(pairs)
+        out[j]["y"][:len(pairs)], out[j]["out"][:len(pairs)] = pairs // topk, pairs
+    return out, ntok * topk
 
 
 def moe_oracle(w, x, topk=10):

@@ -114,7 +114,7 @@ def test_argmax_and_top64(oracle):
         ref_l = logits.copy()
         rv, ri, _ = oracle.top_tokens(ref_l, v0, tok, cnt, pn, par)
         dl = G.dev(logits)
-        keys, err = G.zeros(16, torch.int64), G.zeros(1, torch.int32)
+        keys, err = G.zeros(32, torch.int64), G.zeros(1, torch.int32)
         bv, bi = G.zeros(T), G.zeros(T, torch.int32)
         L.call("fnx_argmax", dl.data_ptr(), n, T, v0, bv.data_ptr(), bi.data_ptr(), keys.data_ptr(), err.data_ptr(), L.stream())
         ov, oi = G.zeros((T, 64)), G.zeros((T, 64), torch.int32)
@@ -130,7 +130,7 @@ def test_argmax_and_top64(oracle):
     bad = np.zeros((2, 4096), np.float32)
     bad[1, 77] = np.nan
     dl, err = G.dev(bad), G.zeros(1, torch.int32)
-    keys, bv, bi = G.zeros(16, torch.int64), G.zeros(2), G.zeros(2, torch.int32)
+    keys, bv, bi = G.zeros(32, torch.int64), G.zeros(2), G.zeros(2, torch.int32)
     L.call("fnx_argmax", dl.data_ptr(), 4096, 2, 0, bv.data_ptr(), bi.data_ptr(), keys.data_ptr(), err.data_ptr(), L.stream())
     G.sync()
     assert int(G.host(err)[0]) == 16
