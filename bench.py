@@ -1,21 +1,34 @@
-"""Verify-window benchmark: accepted tok/s at draft length 16 on N B200s, with the roofline of the dominant kernel and
+"""Verify-window benchmark: accepted tok/s at draft length 16 on N B200s, every kernel's share of the HBM roofline, and
 the CPU oracle timed beside it.
 
-  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--config cfg2|cfg3|cfg4]
   python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P bench.py --gpus N ...
 
-Workload (N = 1): the 8-layer synthetic stack (6 Gated DeltaNet + 2 attention layers, every layer with the 512-expert
-top-10 + shared-expert FFN in Q4_K/Q6_K, Q8_0 dense projections and head), batch 1, 32 768-token fp16 K/V context, one
-window of 16 rows (the last committed token + 15 drafts) per step, greedy prefix acceptance, rollback of the rejected
-rows.  Drafts are uniform over the vocabulary, overwritten with the greedy continuation where a Bernoulli(0.8) draw per
-position is true; they are prepared before the timed region (the draft model is not part of the measured path) and the
-timed region replays the recorded windows from the saved initial state.  N > 1: the same model split across the GPUs
-(experts by FF width, DeltaNet by value heads, K/V by position, vocabulary by ranges) with NCCL all-reduce / all-gather
-between the stages: strong scaling.
+Workloads (the benchmark configurations; a step is one verify round, a window of 16 rows = the last committed token + 15
+drafts per sequence, then acceptance and the rollback of the rejected rows):
+  cfg2 (default)  8-layer synthetic stack (6 Gated DeltaNet + 2 attention layers, each with the 512-expert top-10 + shared
+                  expert FFN in Q4_K / Q6_K, Q8_0 dense projections and head), batch 1, 32 768-token fp16 K/V context,
+                  greedy prefix acceptance; drafts uniform over the vocabulary, overwritten with the greedy continuation
+                  where a Bernoulli(0.8) draw per position is true.  Fits one GPU.
+  cfg3            48 layers (36 + 12), Q4_K experts, 6 concurrent sequences (each its own DeltaNet state and K/V region of
+                  160 000 positions), rejection-sampling acceptance at temperature 1.0 against fixed (one-hot) drafts; a
+                  step is one window per sequence, six windows in all.  2 GPUs or more.
+  cfg4            48 layers, all experts Q8_0, batch 1, 262 144-token context, greedy acceptance.  2 GPUs or more (the
+                  experts alone are 185 GB); --layers L runs a stated subset on one GPU.
+Drafts are prepared before the timed region (the draft model is not part of the measured path); the timed region replays
+the recorded windows from the saved initial state.  N > 1: the same model split across the GPUs (experts by FF width,
+DeltaNet by value heads, K/V by position, vocabulary by ranges), the sums across GPUs by the library's peer-memory kernel
+and the gathers by NCCL, all inside the window's CUDA graph: strong scaling.
+
+Timing: K steps form a segment, timed on the device with CUDA events on the runner's stream; the segment is repeated over
+fresh recorded windows (about 200 windows in all for cfg2) and ms_per_step is the median segment's, so that neither the
+drafts' luck nor a single slow replay moves the value; value = mean accepted tokens per step over all timed steps /
+ms_per_step.
 """
 import argparse
 import ctypes as C
 import json
+import math
 import os
 import subprocess
 import sys
@@ -26,37 +39,64 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
+METRIC = "accepted tok/s @ draft len 16"
+DTYPE = "int8 x int4/int6/int8 dot products, f32 accumulate"
+T = 16
+
 
 def parse():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=40)
+    ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--layers", type=int, default=8, help="stack depth (8 = the benchmark configuration)")
-    ap.add_argument("--ctx", type=int, default=32768)
+    ap.add_argument("--config", default="cfg2", choices=["cfg2", "cfg3", "cfg4"])
+    ap.add_argument("--repeats", type=int, default=0, help="timed segments of --steps steps (0: about 200 windows for cfg2, one segment otherwise)")
+    ap.add_argument("--layers", type=int, default=0, help="stack depth (0: the configuration's own: 8 for cfg2, 48 for cfg3 / cfg4)")
+    ap.add_argument("--ctx", type=int, default=0, help="K/V context (0: the configuration's own)")
     ap.add_argument("--seed", type=int, default=0)
-    ap.add_argument("--experts", type=int, default=512, help="routed experts (512 = the benchmark configuration; fewer for small profiling runs)")
-    ap.add_argument("--vocab", type=int, default=151936, help="vocabulary (151936 = the benchmark configuration)")
-    ap.add_argument("--expert-type", default="q4k", choices=["q4k", "q8_0"],
-                    help="routed experts: q4k (Q4_K gate|up + Q6_K down, the benchmark configuration) or q8_0 (the all-Q8_0 configuration)")
+    ap.add_argument("--experts", type=int, default=512, help="routed experts (512 = the benchmark configurations; fewer for small profiling runs)")
+    ap.add_argument("--vocab", type=int, default=151936, help="vocabulary (151936 = the benchmark configurations)")
+    ap.add_argument("--expert-type", default="", choices=["", "q4k", "q8_0"], help="override the configuration's expert format")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="enqueue every window call by call instead of replaying a CUDA graph")
+    ap.add_argument("--no-parity", action="store_true", help="N > 1: skip the comparison with the unsplit model")
     return ap.parse_args()
 
 
+def workload(args):
+    """The named configuration as (kinds, ctx, sequences, expert format, sampled acceptance)."""
+    base = {"cfg2": (8, 32768, 1, "q4k", False), "cfg3": (48, 160000, 6, "q4k", True), "cfg4": (48, 262144, 1, "q8_0", False)}[args.config]
+    layers = args.layers or base[0]
+    kinds = [1 if (i % 4) == 3 else 0 for i in range(layers)]
+    return {"name": args.config, "kinds": kinds, "ctx": args.ctx or base[1], "nseq": base[2], "experts": args.expert_type or base[3],
+            "sampled": base[4], "full_layers": base[0]}
+
+
+def accepted_from_draws(seed, nwindows):
+    """Greedy acceptance under the benchmark's drafts is decided by the Bernoulli(0.8) draws alone: a draft that was
+    overwritten with the greedy continuation is accepted, a uniform one is not (it equals the greedy token with probability
+    1 / vocabulary), so a window keeps 1 + its leading true draws.  Both arms take their numerator from this stream."""
+    import numpy as np
+
+    rng = np.random.default_rng([seed, 1])
+    draws = rng.random((nwindows, T - 1)) < 0.8
+    n = [1 + int(np.argmin(np.append(d, False))) for d in draws]
+    return draws, n
+
+
 class ClockSampler:
-    """Samples SM clocks and throttle reasons of one GPU with nvidia-smi while the timed region runs."""
+    """Samples SM clocks and throttle reasons of one GPU (by UUID) with nvidia-smi while the timed regions run; read-only."""
     Q = "clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown," \
         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
 
-    def __init__(self, index):
-        self.index, self.proc, self.lines = index, None, []
+    def __init__(self, gpu_id):
+        self.gpu_id, self.proc, self.lines = gpu_id, None, []
 
     def start(self):
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q, "--format=csv,noheader,nounits",
-                                          "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.gpu_id), "--query-gpu=" + self.Q, "--format=csv,noheader,nounits",
+                                          "-lms", "50"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=lambda: self.lines.extend(self.proc.stdout), daemon=True)
             self.thread.start()
         except OSError:
@@ -81,31 +121,45 @@ class ClockSampler:
         return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def algorithmic_bytes(shape, distinct_experts, ctx):
-    """Bytes a window must move once (weights, K/V, state + checkpoints, logits), per kernel family, whole model."""
+def algorithmic_bytes(shape, ctx):
+    """Bytes one call of each kernel family must move once (weights, K/V, state + checkpoints, logits) on the whole
+    model; the expert entries are per distinct expert."""
     n, ff = shape.n, shape.ff
     q8 = lambda r, c: r * c * 34 // 32  # noqa: E731
     gu = 2 * ff * (n // 256) * 144 if shape.experts == "q4k" else q8(2 * ff, n)
     dn = n * (ff // 256) * 210 if shape.experts == "q4k" else q8(n, ff)
     state = shape.nvh * 128 * 128 * 4
-    b = {"moe_gate_up": gu, "moe_down": dn, "router": (shape.nexp + 1) * n * 4, "shared": q8(2 * ff, n) + q8(n, ff),
-         "gdn_core": 17 * state, "qkvz": q8((2 * shape.nkh + 2 * shape.nvh) * 128, n), "ssm_out": q8(n, shape.nvh * 128),
-         "wq": q8(shape.nq * shape.hd * 2, n), "wkv": 2 * q8(shape.nkv * shape.hd, n), "wo": q8(n, shape.nq * shape.hd),
-         "attn_kv": ctx * shape.nkv * shape.hd * 2 * 2, "head": q8(shape.vocab, n) + 16 * shape.vocab * 4}
-    return b
+    return {"moe_gate_up": gu, "moe_down": dn, "router": (shape.nexp + 1) * n * 4, "shared": q8(2 * ff, n) + q8(n, ff),
+            "gdn_core": 17 * state, "qkvz": q8((2 * shape.nkh + 2 * shape.nvh) * 128, n), "ssm_out": q8(n, shape.nvh * 128),
+            "wq": q8(shape.nq * shape.hd * 2, n), "wkv": 2 * q8(shape.nkv * shape.hd, n), "wo": q8(n, shape.nq * shape.hd),
+            "attn_kv": ctx * shape.nkv * shape.hd * 2 * 2, "head": q8(shape.vocab, n) + T * shape.vocab * 4,
+            "ab": 2 * shape.nvh * n * 4, "rows": T * n * 4}
 
 
-def workload_config(shape, kinds, ctx, world):
+def window_bytes(shape, ctx, d_exp, world):
+    """Algorithmic bytes of one window per GPU: what splits divides by the GPUs, what is replicated does not."""
+    b = algorithmic_bytes(shape, ctx)
+    kinds = shape.kinds
+    split = (len(kinds) * (d_exp * (b["moe_gate_up"] + b["moe_down"]) + b["shared"]) + kinds.count(0) * (b["qkvz"] + b["ssm_out"] + b["gdn_core"]) +
+             kinds.count(1) * (b["wo"] + b["attn_kv"]) + b["head"])
+    repl = len(kinds) * b["router"] + kinds.count(0) * b["ab"] + kinds.count(1) * (b["wq"] + b["wkv"])
+    return split / world + repl if world > 1 else split + repl
+
+
+def workload_config(wl, shape, world):
     """The `config` object of the result line: the same for this arm and for the CPU arm."""
-    b = algorithmic_bytes(shape, 0, ctx)
+    kinds, ctx = shape.kinds, wl["ctx"]
+    b = algorithmic_bytes(shape, ctx)
     experts_all = shape.nexp * (b["moe_gate_up"] + b["moe_down"])
     resident = (len(kinds) * (experts_all + b["router"] + b["shared"]) + kinds.count(0) * (b["qkvz"] + b["ssm_out"] + b["gdn_core"]) +
-                kinds.count(1) * (b["wq"] + b["wkv"] + b["wo"] + b["attn_kv"]) + b["head"])
-    d_exp = shape.nexp * (1.0 - (1.0 - shape.topk / shape.nexp) ** 16)   # expected distinct experts of 16 rows
-    window = (len(kinds) * (d_exp * (b["moe_gate_up"] + b["moe_down"]) + b["router"] + b["shared"]) +
-              kinds.count(0) * (b["qkvz"] + b["ssm_out"] + b["gdn_core"]) + kinds.count(1) * (b["wq"] + b["wkv"] + b["wo"] + b["attn_kv"]) + b["head"])
-    return {"workload": "cfg2: %d-layer stack (%d DeltaNet + %d attention), batch 1, ctx %d, T=16 rows (1 committed + 15 drafts), "
-                        "greedy acceptance, Bernoulli(0.8) drafts" % (len(kinds), kinds.count(0), kinds.count(1), ctx),
+                kinds.count(1) * (b["wq"] + b["wkv"] + b["wo"] + wl["nseq"] * b["attn_kv"]) + b["head"])
+    d_exp = shape.nexp * (1.0 - (1.0 - shape.topk / shape.nexp) ** T)   # expected distinct experts of 16 rows
+    window = window_bytes(shape, ctx, d_exp, 1)
+    what = {"cfg2": "greedy acceptance, Bernoulli(0.8) drafts", "cfg3": "rejection sampling at temperature 1.0 against one-hot drafts, a step = one "
+            "window per sequence", "cfg4": "greedy acceptance, Bernoulli(0.8) drafts"}[wl["name"]]
+    sub = "" if len(kinds) == wl["full_layers"] else " [a %d-layer subset of the configuration's %d]" % (len(kinds), wl["full_layers"])
+    return {"workload": "%s: %d-layer stack (%d DeltaNet + %d attention)%s, %d sequence%s, ctx %d, T=16 rows (1 committed + 15 drafts), %s" %
+                        (wl["name"], len(kinds), kinds.count(0), kinds.count(1), sub, wl["nseq"], "s" if wl["nseq"] > 1 else "", ctx, what),
             "hidden": shape.n, "experts": shape.nexp, "expert_type": shape.experts, "topk": shape.topk, "ff": shape.ff, "vocab": shape.vocab,
             "l2": "inputs larger than L2, no flush: %.1f GB of weights, state and K/V resident, about %.1f GB of them read per window "
                   "(126 MB of L2)" % (resident / 1e9, window / 1e9),
@@ -122,10 +176,6 @@ def emit(line):
 
 def main():
     args = parse()
-    import numpy as np
-    import torch
-    import torch.distributed as dist
-
     # stdout carries the one JSON line and nothing else: whatever libraries print there (NCCL's version line) goes to
     # stderr, and the line is written to the saved descriptor at the end
     global _REAL_STDOUT
@@ -135,10 +185,15 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
+    wl = workload(args)
     if args.impl == "reference":
-        import bench_reference
+        import bench_reference   # numpy + the CPU oracle only: no torch, no CUDA library
 
-        return bench_reference.main(args, rank, world, emit, workload_config)
+        return bench_reference.main(args, rank, wl, emit)
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+
     assert world == args.gpus, "launch with torch.distributed.run --nproc-per-node %d for --gpus %d" % (args.gpus, args.gpus)
     torch.cuda.set_device(local)
     group = None
@@ -148,49 +203,69 @@ def main():
     from sfnx_b200 import lib as L
     from sfnx_b200.window import StackShape, SyntheticStack, WindowRunner
 
-    L.load()
-    kinds = [1 if (i % 4) == 3 else 0 for i in range(args.layers)]
-    T = L.MAXT
-    shape = StackShape(kinds=kinds, ctx=args.ctx, kv_slack=(args.warmup + args.steps + 2) * T, nexp=args.experts, vocab=args.vocab,
-                       experts=args.expert_type)
+    lib = L.load()
+    kinds, nseq, sampled = wl["kinds"], wl["nseq"], wl["sampled"]
+    repeats = args.repeats or (max(1, min(10, math.ceil(200 / max(1, args.steps)))) if wl["name"] == "cfg2" else 1)
+    nsteps = args.warmup + args.steps * repeats
+    shape = StackShape(kinds=kinds, ctx=wl["ctx"], kv_slack=(nsteps + 2) * T, nexp=args.experts, vocab=args.vocab, experts=wl["experts"])
     t_build = time.time()
     stack = SyntheticStack(shape, ncard=world, card=rank, seed=args.seed, device="cuda:%d" % local)
-    runner = WindowRunner(stack, T, group=group, graph=not args.no_graph)
+    seqs = [stack] + [stack.sequence_view(i) for i in range(1, nseq)]
+    main_stream = torch.cuda.Stream()   # the sequences share the workspace, so their windows share one stream
+    runners = [WindowRunner(s, T, group=group, graph=not args.no_graph, sampled=sampled, stream=main_stream) for s in seqs]
     t_build = time.time() - t_build
-    lib = L.load()
+    sp = dict(temperature=1.0, top_p=1.0, min_p=0.0, top_k=0)
 
-    # ---- drafting pass (untimed): the rows of every step, recorded
-    rng = np.random.default_rng(args.seed + 1)
-    state0 = stack.save_state()
-    nsteps = args.warmup + args.steps
-    rec, pos, tag, x = [], args.ctx, 1, int(rng.integers(0, shape.vocab))
-    out_c = (C.c_int * T)()
-    rows_c = (C.c_int * T)()
+    def save_all():
+        return [s.save_state() for s in seqs]
+
+    def load_all(saved):
+        for s, st in zip(seqs, saved):
+            s.load_state(st)
+
+    # ---- drafting pass (untimed): the rows of every step and sequence, recorded
+    draws, n_draws = accepted_from_draws(args.seed, nsteps * nseq)
+    rng = np.random.default_rng([args.seed, 2])
+    state0 = save_all()
+    rec = [[None] * nseq for _ in range(nsteps)]
+    pos, tag = [wl["ctx"]] * nseq, [1] * nseq
+    last = [int(v) for v in rng.integers(0, shape.vocab, nseq)]
+    out_c, rows_c = (C.c_int * T)(), (C.c_int * T)()
+    rngs = [lib.fnx_rng_new(args.seed * 7919 + 13 * q + 1) for q in range(nseq)]
+    fix_rounds = T if not sampled else 3   # sampled acceptance at temperature 1.0 rarely gets past the first drafts
     for s in range(nsteps):
-        draws = rng.random(T - 1) < 0.8
-        rows = [x] + [int(v) for v in rng.integers(0, shape.vocab, T - 1)]
-        saved = stack.save_state()
-        for _ in range(T):   # rows[j + 1] = the greedy token after row j wherever the leading draws are true
-            out = runner.window(rows, pos, tag)
-            stack.load_state(saved)
-            changed = False
-            for j in range(T - 1):
-                if not draws[j]:
+        for q in range(nseq):
+            runner, view, dr = runners[q], seqs[q], draws[s * nseq + q]
+            rows = [last[q]] + [int(v) for v in rng.integers(0, shape.vocab, T - 1)]
+            saved = view.save_state()
+            for _ in range(fix_rounds):   # rows[j + 1] = the greedy token after row j wherever the leading draws are true
+                out = runner.window(rows, pos[q], tag[q])
+                view.load_state(saved)
+                changed = False
+                for j in range(T - 1):
+                    if not dr[j]:
+                        break
+                    if rows[j + 1] != out[j]:
+                        rows[j + 1] = out[j]
+                        changed = True
+                        break
+                if not changed:
                     break
-                if rows[j + 1] != out[j]:
-                    rows[j + 1] = out[j]
-                    changed = True
-                    break
-            if not changed:
-                break
-        out = runner.window(rows, pos, tag)
-        rows_c[:], out_c[:] = rows, out
-        n = lib.fnx_accept_greedy(rows_c, out_c, T)
-        runner.commit(n, tag)
-        rec.append((rows, pos, tag, n, out))
-        pos, tag, x = pos + n, tag + 1, out[n - 1]
+            if sampled:
+                toks, n = runner.window_sampled(rows, pos[q], tag[q], rngs[q], **sp)
+                nxt = toks[-1]
+            else:
+                out = runner.window(rows, pos[q], tag[q])
+                rows_c[:], out_c[:] = rows, out
+                n = lib.fnx_accept_greedy(rows_c, out_c, T)
+                nxt = out[n - 1]
+            runner.commit(n, tag[q])
+            rec[s][q] = (rows, pos[q], tag[q], n)
+            pos[q], tag[q], last[q] = pos[q] + n, tag[q] + 1, nxt
     torch.cuda.synchronize()
-    accepted = sum(r[3] for r in rec[args.warmup:])
+    timed = [r for step in rec[args.warmup:] for r in step]
+    accepted_per_step = sum(r[3] for r in timed) / (args.steps * repeats)
+    draws_agree = sampled or [r[3] for step in rec for r in step] == n_draws
 
     def barrier():
         torch.cuda.synchronize()
@@ -198,67 +273,101 @@ def main():
             dist.barrier()
             torch.cuda.synchronize()
 
-    def max_over_ranks(v):
+    def max_over_ranks(vals):
         if world == 1:
-            return v
-        t = torch.tensor([v], dtype=torch.float64, device="cuda")
+            return list(vals)
+        t = torch.tensor(list(vals), dtype=torch.float64, device="cuda")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t[0])
+        return [float(v) for v in t]
 
     # ---- device-timed replay: ids and (position, tag) of every step already in HBM, no host read-back
-    d_ids = torch.tensor([r[0] for r in rec], dtype=torch.int32, device=stack.dev)
-    d_ctl = torch.tensor([[r[1], r[2]] for r in rec], dtype=torch.int32, device=stack.dev)
-    clocks = ClockSampler(local)
+    d_ids = [torch.tensor([rec[s][q][0] for s in range(nsteps)], dtype=torch.int32, device=stack.dev) for q in range(nseq)]
+    d_ctl = [torch.tensor([[rec[s][q][1], rec[s][q][2]] for s in range(nsteps)], dtype=torch.int32, device=stack.dev) for q in range(nseq)]
+    gpu_uuid = str(torch.cuda.get_device_properties(local).uuid)
+    clocks = ClockSampler(gpu_uuid if gpu_uuid.startswith("GPU-") else "GPU-" + gpu_uuid)
 
     def device_step(i):
-        with torch.cuda.stream(runner.stream):
-            runner.ids[:T].copy_(d_ids[i], non_blocking=True)
-            runner.ctl_in.copy_(d_ctl[i], non_blocking=True)
-            runner.launch()
-        runner.commit(rec[i][3], rec[i][2])
+        for q in range(nseq):
+            r = runners[q]
+            with torch.cuda.stream(main_stream):
+                r.ids[:T].copy_(d_ids[q][i], non_blocking=True)
+                r.ctl_in.copy_(d_ctl[q][i], non_blocking=True)
+                if r.graph is not None:
+                    r.graph.replay()
+                else:
+                    r._enqueue()
+            L.call("fnx_window_commit", C.byref(seqs[q].cfg), seqs[q].layers, stack.ws.data_ptr(), T, rec[i][q][3], rec[i][q][2],
+                   r.h_jobs.data_ptr() + (i % 64) * r.job_bytes, main_stream.cuda_stream) if rec[i][q][3] < T else None
 
-    stack.load_state(state0)
+    load_all(state0)
     clocks.start()
     for i in range(args.warmup):
         device_step(i)
     barrier()
-    lib.fnx_window_kernel_count(1)
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record(runner.stream)
-    for i in range(args.warmup, nsteps):
-        device_step(i)
-    e1.record(runner.stream)
+    evs = [torch.cuda.Event(enable_timing=True) for _ in range(repeats + 1)]
+    evs[0].record(main_stream)
+    for r in range(repeats):
+        for i in range(args.warmup + r * args.steps, args.warmup + (r + 1) * args.steps):
+            device_step(i)
+            if i % 64 == 63:
+                main_stream.synchronize()   # the host's job tables are a ring of 64
+        evs[r + 1].record(main_stream)
     barrier()
-    dev_ms = max_over_ranks(e0.elapsed_time(e1))
+    seg_ms = max_over_ranks(evs[r].elapsed_time(evs[r + 1]) for r in range(repeats))
+    dev_ms = sorted(seg_ms)[len(seg_ms) // 2]
+    err_dev = max(int(r.err[0].item()) for r in runners)
 
-    # ---- end-to-end replay through the runner's public call: host token ids in, host argmax tokens out, acceptance on
-    # the host, rollback
-    stack.load_state(state0)
+    # ---- end-to-end replay through the runner's public call: host token ids in, host tokens out, acceptance on the
+    # host, rollback
+    load_all(state0)
+    if sampled:
+        for q in range(nseq):
+            lib.fnx_rng_free(rngs[q])
+            rngs[q] = lib.fnx_rng_new(args.seed * 7919 + 13 * q + 1)
+    e2e_seg, e2e_accepted, diverged = [], 0, None
+
+    def e2e_step(i):
+        got = 0
+        for q in range(nseq):
+            rows, p, tg, n_rec = rec[i][q]
+            if sampled:
+                _, n = runners[q].window_sampled(rows, p, tg, rngs[q], **sp)
+            else:
+                out = runners[q].window(rows, p, tg)
+                rows_c[:], out_c[:] = rows, out
+                n = lib.fnx_accept_greedy(rows_c, out_c, T)
+            runners[q].commit(n, tg)
+            got += n
+            if n != n_rec:
+                return got, (i, q, n, n_rec)
+        return got, None
+
     for i in range(args.warmup):
-        out = runner.window(rec[i][0], rec[i][1], rec[i][2])
-        runner.commit(rec[i][3], rec[i][2])
+        _, bad = e2e_step(i)
+        diverged = diverged or bad
     barrier()
-    t0 = time.perf_counter()
-    e2e_accepted = 0
-    for i in range(args.warmup, nsteps):
-        rows, p, tg, n_rec, out_rec = rec[i]
-        out = runner.window(rows, p, tg)
-        rows_c[:], out_c[:] = rows, out
-        n = lib.fnx_accept_greedy(rows_c, out_c, T)
-        runner.commit(n, tg)
-        e2e_accepted += n
-        assert n == n_rec and out[:n] == out_rec[:n], "replay diverged from the recorded windows at step %d" % i
+    for r in range(repeats):
+        t0 = time.perf_counter()
+        for i in range(args.warmup + r * args.steps, args.warmup + (r + 1) * args.steps):
+            got, bad = e2e_step(i)
+            e2e_accepted += got
+            diverged = diverged or bad
+        torch.cuda.synchronize()
+        e2e_seg.append((time.perf_counter() - t0) * 1e3)
     barrier()
-    e2e_ms = max_over_ranks((time.perf_counter() - t0) * 1e3)
+    e2e_seg = max_over_ranks(e2e_seg)
+    e2e_ms = sorted(e2e_seg)[len(e2e_seg) // 2]
     clk = clocks.stop()
+    assert diverged is None, "the replay diverged from the recorded windows: (step, sequence, accepted, recorded) = %s" % (diverged,)
 
     # ---- per-kernel timing of the same windows enqueued call by call (no graph): CUDA events around every C ABI call
-    stack.load_state(state0)
-    eager = WindowRunner(stack, T, group=group, graph=False)
+    load_all(state0)
+    eager = WindowRunner(stack, T, group=group, graph=False, sampled=sampled)
     per = {}
     ntr = min(8, args.steps)
+    lib.fnx_window_kernel_count(1)
     for i in range(args.warmup, args.warmup + ntr):
-        rows, p, tg, n_rec, _ = rec[i]
+        rows, p, tg, n_rec = rec[i][0]
         eager.h_ids[:T] = torch.as_tensor(rows, dtype=torch.int32)
         eager.h_ctl[0], eager.h_ctl[1] = p, tg
         with torch.cuda.stream(eager.stream):
@@ -272,80 +381,184 @@ def main():
         k = lib.fnx_trace_end(ms, lay, names, 4096)
         for j in range(k):
             per.setdefault(names[j].decode(), []).append(ms[j])
-        # distinct experts of this window's layers: read the job counts back (the last layer's is left in the workspace)
         eager.commit(n_rec, tg)
     torch.cuda.synchronize()
-    kernels_per_window = lib.fnx_window_kernel_count(1) // max(1, ntr)
+    kernels_per_window = lib.fnx_window_kernel_count(1) // max(1, ntr)   # counted where the library checks each launch
+    calls_per_window = {k: len(v) // max(1, ntr) for k, v in per.items()}
 
-    # distinct experts per layer, measured on one window: run stage by stage and read njobs
-    # (E[D] = 512 (1 - (1 - 10/512)^16) = 138.6 for independent uniform picks)
-    algo = algorithmic_bytes(shape, 0, args.ctx)
+    # ---- roofline: every traced call's algorithmic bytes on this GPU over its mean time
+    algo = algorithmic_bytes(shape, wl["ctx"])
     peaks = {}
     try:
         peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
     except (OSError, ValueError):
         pass
     peak_gbs = float(peaks.get("hbm_gbs", 6650.0))
-    D = distinct_experts(stack, runner, rec[args.warmup], T)
-    gu_ms = float(np.mean(per["moe_gate_up"])) if "moe_gate_up" in per else None
-    gu_bytes = D * algo["moe_gate_up"] / world
+    D = distinct_experts(stack, eager, rec[args.warmup][0])
+    kb = {"moe_gate_up": D * algo["moe_gate_up"] / world, "moe_down": D * algo["moe_down"] / world, "router_route": algo["router"],
+          "ffn_route": algo["router"], "shared_expert": algo["shared"] / world, "gdn_core": algo["gdn_core"] / world, "qkvz": algo["qkvz"] / world,
+          "ssm_out": algo["ssm_out"] / world, "wqkv": algo["wq"] + algo["wkv"], "wo": algo["wo"] / world, "attn_partial": algo["attn_kv"] / world,
+          "head": algo["head"] / world, "ab": algo["ab"] / world, "rms_norm": 3 * algo["rows"], "moe_combine": (shape.topk + 2) * algo["rows"],
+          "argmax": T * shape.vocab * 4 / world, "quantize": algo["rows"] * 2, "attn_finish": world * T * shape.nq * (shape.hd + 2) * 4,
+          "attn_prep_append": 2 * T * shape.nq * shape.hd * 2 * 4, "top_tokens": 2 * T * shape.vocab * 4 / world}
+    per_kernel = {}
+    for name, v in sorted(per.items()):
+        us = float(np.mean(v)) * 1e3
+        by = kb.get(name)
+        per_kernel[name] = {"us": round(us, 2), "calls": calls_per_window[name], "bytes": int(by) if by else None,
+                            "gbs": round(by / us / 1e3, 1) if by else None, "frac": round(by / us / 1e3 / peak_gbs, 4) if by else None}
+    gu = per_kernel.get("moe_gate_up")
     roof = None
-    if gu_ms:
-        ach = gu_bytes / (gu_ms * 1e-3) / 1e9
-        roof = {"kernel": "k_moe_gu_q4k" if shape.experts == "q4k" else "k_moe_gu_q8", "bound": "hbm", "achieved": round(ach, 1), "peak": peak_gbs, "unit": "GB/s",
-                # dram read + write bytes of one launch: ncu on a 128-expert case measured 1.00 x the algorithmic bytes
-                # read (each selected expert's rows once) + the output rows written; scaled to this launch by D
-                "frac": round(ach / peak_gbs, 4), "traffic": int(gu_bytes + T * shape.topk * 2 * (shape.ff // world) * 4),
-                "peak_source": "measured" if peaks else "fallback",
-                "bytes_per_launch": int(gu_bytes), "us_per_launch": round(gu_ms * 1e3, 2), "distinct_experts": D}
-    breakdown = {k: round(float(np.mean(v)) * 1e3, 2) for k, v in sorted(per.items())}
-
+    if gu:
+        roof = {"kernel": "k_moe_gu_q4k" if shape.experts == "q4k" else "k_moe_gu_q8", "bound": "hbm", "achieved": gu["gbs"], "peak": peak_gbs,
+                "unit": "GB/s", "frac": gu["frac"],
+                # dram read + write bytes of one launch: ncu on a 128-expert case measured 1.00 x the algorithmic bytes read
+                # (each selected expert's rows once) + the output rows written; scaled to this launch by D
+                "traffic": int(kb["moe_gate_up"] + T * shape.topk * 2 * (shape.ff // world) * 4), "peak_source": "measured" if peaks else "fallback",
+                "bytes_per_launch": int(kb["moe_gate_up"]), "us_per_launch": gu["us"], "distinct_experts": D}
+    wbytes = window_bytes(shape, wl["ctx"], D, world) * nseq
+    ms_step = dev_ms / args.steps
     result = {
-        "metric": "accepted tok/s @ draft len 16", "value": round(accepted / (dev_ms * 1e-3), 2), "unit": "tok/s", "n_gpus": world,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(dev_ms / args.steps, 4), "higher_is_better": True,
-        "scaling": "strong", "vs_baseline": None, "dtype": "int8 x int4/int6/int8 dot products, f32 accumulate", "data": "synthetic",
-        "config": workload_config(shape, kinds, args.ctx, world),
-        "accepted_per_window": round(accepted / args.steps, 3),
-        "e2e": {"value": round(e2e_accepted / (e2e_ms * 1e-3), 2), "unit": "tok/s", "ms_per_step": round(e2e_ms / args.steps, 4),
-                "h2d_bytes_per_step": runner.h2d_bytes + runner.job_bytes, "d2h_bytes_per_step": runner.d2h_bytes},
-        "gpu_launches": int(kernels_per_window * args.steps), "kernels_per_window": int(kernels_per_window),
-        "clocks": clk, "roofline": roof, "kernel_us": breakdown, "build_s": round(t_build, 1),
+        "metric": METRIC, "value": round(accepted_per_step / (ms_step * 1e-3), 2), "unit": "tok/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_step, 4), "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": DTYPE, "data": "synthetic",
+        "config": workload_config(wl, shape, world),
+        "accepted_per_step": round(accepted_per_step, 3),
+        "timing": {"repeats": repeats, "statistic": "median segment of --steps steps, CUDA events on the runner's stream, max over ranks",
+                   "segment_ms": [round(v, 3) for v in seg_ms], "windows_timed": args.steps * repeats * nseq,
+                   "numerator": "accepted tokens per step, mean over all timed steps" + ("" if sampled else " (= 1 + leading true Bernoulli draws: %s)" %
+                                                                                          ("checked" if draws_agree else "NOT reproduced by the windows"))},
+        "e2e": {"value": round(accepted_per_step / (e2e_ms / args.steps * 1e-3), 2), "unit": "tok/s", "ms_per_step": round(e2e_ms / args.steps, 4),
+                "h2d_bytes_per_step": nseq * (runners[0].h2d_bytes + runners[0].job_bytes),
+                "d2h_bytes_per_step": nseq * (runners[0].d2h_bytes + (world * T * 64 * 8 if sampled else 0)),
+                "accepted_per_step": round(e2e_accepted / (args.steps * repeats), 3)},
+        "gpu_launches": int(kernels_per_window * nseq * args.steps), "kernels_per_window": int(kernels_per_window),
+        "clocks": clk, "roofline": roof, "roofline_per_kernel": per_kernel,
+        "window_roofline": {"bytes_per_gpu": int(wbytes), "gbs": round(wbytes / (ms_step * 1e-3) / 1e9, 1), "peak": peak_gbs,
+                            "frac": round(wbytes / (ms_step * 1e-3) / 1e9 / peak_gbs, 4)},
+        "kernel_us": {k: v["us"] for k, v in per_kernel.items()}, "device_err": err_dev, "build_s": round(t_build, 1),
     }
-    if rank == 0 and world == 1 and not args.no_cpu_baseline and shape.experts == "q4k":
+    if world > 1:
+        result["ring_check"] = runners[0].ring_self_check()
+        assert result["ring_check"] is None or (result["ring_check"]["bits_equal"] and result["ring_check"]["err"] == 0), result["ring_check"]
+        if wl["name"] == "cfg2" and not args.no_parity:
+            result["parity"] = parity_vs_unsplit(args, shape, seqs[0], runners[0], state0[0], rec, rank, world, local)
+        else:
+            result["parity"] = None if args.no_parity else {"unavailable": "the unsplit model does not fit one GPU"}
+    assert err_dev == 0, "device error word %d after the timed replay" % err_dev
+    if rank == 0 and world == 1 and not args.no_cpu_baseline and not sampled:
         import bench_reference
 
-        result["cpu_baseline"] = bench_reference.cpu_baseline(stack, runner, rec[args.warmup], shape, accepted / args.steps)
+        result["cpu_baseline"] = bench_reference.cpu_baseline(wl, shape, accepted_per_step)
     if rank == 0:
         emit(json.dumps(result))
     sys.stdout.flush()
+    for q in range(nseq):
+        lib.fnx_rng_free(rngs[q])
     if world > 1:
-        # leave without tearing the communicator down: its destruction can wait for ever on the captured graphs' kernels
-        dist.barrier()
+        # the graphs hold NCCL nodes and the ring holds peer mappings: both go before the process group does
+        barrier()
+        for r in runners + [eager]:
+            r.close()
+        del runners, eager
+        barrier()
+        dist.destroy_process_group()
+
+
+def parity_vs_unsplit(args, shape, stack, runner, state0, rec, rank, world, local):
+    """N > 1: the first recorded windows again on the split model and, on rank 0, on the unsplit model built from the same
+    seeds; compares greedy tokens, accepted counts, top-1 and the logits' KL (the reference's definition over each side's 64
+    best, tools/fnx_run.cpp:244-288; bar 1.25 x 4.85e-4).  The sums across GPUs add in the ring's order, the unsplit
+    model's in its own, so logits agree to rounding, not bit for bit."""
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+
+    from sfnx_b200 import lib as L
+    from sfnx_b200.window import SyntheticStack, WindowRunner
+
+    lib = L.load()
+    nwin = min(4, len(rec))
+    per = (shape.vocab + world - 1) // world
+    stack.load_state(state0)
+    split_logits, split_out = [], []
+    gathered = torch.zeros((world, T, per), dtype=torch.float32, device=stack.dev)
+    mine = torch.zeros((T, per), dtype=torch.float32, device=stack.dev)
+    for i in range(nwin):
+        rows, p, tg, n = rec[i][0]
+        split_out.append(runner.window(rows, p, tg))
+        mine.zero_()
+        mine[:, :stack.vrows] = runner.logits
+        dist.all_gather_into_tensor(gathered.view(-1), mine.view(-1))
+        split_logits.append(gathered.permute(1, 0, 2).reshape(T, world * per)[:, :shape.vocab].cpu().numpy())
+        runner.commit(n, tg)
+    torch.cuda.synchronize()
+    res = None
+    if rank == 0:
+        one = SyntheticStack(shape, ncard=1, card=0, seed=args.seed, device="cuda:%d" % local)
+        r1 = WindowRunner(one, T, group=None, graph=False)
+        # the split runner's warm-up windows changed the K/V rows at positions 0 .. 15 and the states on every GPU alike;
+        # the same two warm-up windows have just run here, and the saved initial states are per slice, so the unsplit
+        # model replays from its own state after the same warm-up
+        kls, top1, toks_eq, acc_eq = [], [], True, True
+        rows_c, out_c = (C.c_int * T)(), (C.c_int * T)()
+        for i in range(nwin):
+            rows, p, tg, n = rec[i][0]
+            out = r1.window(rows, p, tg)
+            ref = r1.logits.cpu().numpy()
+            rows_c[:], out_c[:] = rows, out
+            n1 = lib.fnx_accept_greedy(rows_c, out_c, T)
+            kls.append(float(kl_top64(ref, split_logits[i]).mean()))
+            top1.append(float(np.mean(np.array(out) == np.array(split_out[i]))))
+            toks_eq = toks_eq and out[:n1] == split_out[i][:n1]
+            acc_eq = acc_eq and n1 == n
+            r1.commit(n, tg)
         torch.cuda.synchronize()
-        os._exit(0)
+        res = {"windows": nwin, "tokens_equal": bool(toks_eq), "accepted_equal": bool(acc_eq), "kl_mean": float(np.mean(kls)),
+               "top1_equal": float(np.mean(top1)), "kl_bar": 1.25 * 4.85e-4}
+        del r1, one
+        torch.cuda.empty_cache()
+    dist.barrier()
+    stack.load_state(state0)
+    if res is not None:
+        assert res["kl_mean"] <= res["kl_bar"] and res["accepted_equal"], "the split model left the unsplit model's results: %s" % res
+    return res
 
 
-def distinct_experts(stack, runner, step, T):
-    """Mean number of distinct routed experts per layer in one recorded window (the job counts, read back per layer)."""
+def kl_top64(ref, new):
+    """Per-row KL(ref || new) over the union of both rows' 64 highest logits, a token outside a side's 64 taking that
+    side's 64th logit, probabilities from each side's full-row log-sum-exp (reference tools/fnx_run.cpp:244-288)."""
+    import numpy as np
+
+    out = []
+    for a, b in zip(ref.astype(np.float64), new.astype(np.float64)):
+        ia, ib = np.argsort(-a, kind="stable")[:64], np.argsort(-b, kind="stable")[:64]
+        union = np.union1d(ia, ib)
+        la = a.max() + np.log(np.exp(a - a.max()).sum())
+        lb = b.max() + np.log(np.exp(b - b.max()).sum())
+        va = np.where(np.isin(union, ia), a[union], a[ia[-1]]) - la
+        vb = np.where(np.isin(union, ib), b[union], b[ib[-1]]) - lb
+        out.append(float(np.sum(np.exp(va) * (va - vb))))
+    return np.array(out)
+
+
+def distinct_experts(stack, runner, step):
+    """Mean number of distinct routed experts per layer in one recorded window: the job count read back after every FFN
+    stage of a window enqueued stage by stage."""
     import torch
 
     from sfnx_b200 import lib as L
 
-    rows, pos, tag, n_rec, _ = step
+    rows, pos, tag, _ = step
     saved = stack.save_state()
-    eager = runner
     counts = []
     with torch.cuda.stream(runner.stream):
         runner.ids[:T].copy_(torch.tensor(rows, dtype=torch.int32, device=stack.dev))
         runner.ctl_in.copy_(torch.tensor([pos, tag], dtype=torch.int32, device=stack.dev))
         runner.ctl.copy_(runner.ctl_in)
         st = torch.cuda.current_stream().cuda_stream
+        L.call("fnx_window_side_stream", None, None, None)
         L.call("fnx_embed_rows", stack.embed.data_ptr(), runner.ids.data_ptr(), runner.x.data_ptr(), T, stack.shape.n, st)
-        # the job count lives at a fixed place of the workspace; find it through the layout: run every stage and read it
-        # after each FFN stage (kind 1 of `after` follows both mixer and FFN stages, so read after every stage)
-        import ctypes as C
-
-        nj_prev = None
         for i in range(runner.nstages):
             L.call("fnx_window_stage", C.byref(stack.cfg), stack.layers, C.byref(stack.head), stack.ws.data_ptr(), T, i, st)
             if stack.ncard > 1:
@@ -355,16 +568,11 @@ def distinct_experts(stack, runner, step, T):
                     per = runner.partials.numel() // stack.ncard
                     runner.dist.all_gather_into_tensor(runner.partials, runner.partials[stack.card * per:(stack.card + 1) * per],
                                                        group=runner.group)
-            nj = int(stack.buf(9, torch.int32, 2)[0].item())
-            if nj != nj_prev or True:
-                counts.append(nj)
-            nj_prev = nj
+            counts.append(int(stack.buf(9, torch.int32, 2)[0].item()))   # left by the last FFN stage that ran
     torch.cuda.synchronize()
     stack.load_state(saved)
-    # njobs changes only at FFN stages; keep the value seen right after each FFN stage
-    ffn = []
-    s = 0
-    for l, kind in enumerate(stack.shape.kinds):
+    ffn, s = [], 0
+    for kind in stack.shape.kinds:   # a layer's stages: mixer (two for attention), then its FFN stage
         s += 2 if kind == 1 else 1
         ffn.append(counts[s])
         s += 1

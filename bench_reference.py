@@ -3,88 +3,124 @@
 The reference (johnfink8/sfnx) has no CPU implementation of this path and its CUDA kernels need an un-vendored
 dependency to compile, so what is timed is the CPU oracle (oracle/, a plain-C restatement of the reference's kernel
 arithmetic, OpenMP over experts / heads / vocabulary rows): kind "port".  A step is a bounded sample of one window of the
-benchmark's workload: one FFN half, one DeltaNet mixer, one attention mixer at the configured context and the head,
-each on the synthetic stack's own tensors; the window's time is the sum scaled by the layer counts.
+benchmark's workload: one FFN half, one DeltaNet mixer, one attention mixer at the configured context and the head, each
+on seeded synthetic tensors of the workload's shapes and formats made with numpy (the timed arithmetic does not depend on
+the values: every block is read and every product taken whatever the bits); the window's time is the sum scaled by the
+layer counts.  Nothing here touches a GPU or the CUDA library.
 """
 import json
 import os
 import time
 
-
-def _np(t, dtype=None):
-    a = t.detach().cpu().numpy()
-    return a.view(dtype) if dtype is not None else a
+T = 16
 
 
-def _sample(stack, shape, seed=0):
+def _cores():
+    return len(os.sched_getaffinity(0))
+
+
+def _use_all_cores():
+    """OpenMP reads its thread count when the oracle library is loaded: launchers such as torch.distributed.run export
+    OMP_NUM_THREADS=1 to their children, which would time one core; use the process's affinity mask instead."""
+    os.environ["OMP_NUM_THREADS"] = str(_cores())
+
+
+def synthetic_pieces(shape, ctx, seed=0, nexp_pool=160):
+    """Seeded tensors of one layer of each kind at the workload's shapes.  The routed experts are a pool of `nexp_pool`
+    matrices (a window touches about 120 - 140 distinct experts of the 512; the router's picks are folded into the pool)."""
+    import numpy as np
+
+    from oracle import binding as O
+
+    rng = np.random.default_rng([seed, 3])
+    n, ff, nq, nkv, hd = shape.n, shape.ff, shape.nq, shape.nkv, shape.hd
+    f16 = lambda lo, hi, size: (rng.random(size, dtype=np.float32) * (hi - lo) + lo).astype(np.float16).view(np.uint16)   # noqa: E731
+
+    def q8s(rows, cols):
+        return rng.integers(-127, 128, size=(rows, cols), dtype=np.int8), f16(1e-4, 3e-4, (rows, cols // 32))
+
+    p = {"x": rng.standard_normal((T, n)).astype(np.float32), "router": (rng.standard_normal((shape.nexp + 1, n)) * 0.02).astype(np.float32)}
+    if shape.experts == "q4k":
+        gu = rng.integers(0, 256, size=(nexp_pool, 2 * ff * (n // 256), 144), dtype=np.uint8)
+        gu[:, :, 0:2] = np.frombuffer(np.float16(2e-4).tobytes(), np.uint8)   # d, dmin: finite f16 values
+        gu[:, :, 2:4] = np.frombuffer(np.float16(1e-4).tobytes(), np.uint8)
+        p["gu"] = gu.reshape(nexp_pool, -1)
+        nu = ff // 32
+        p["dn"] = (rng.integers(0, 256, size=(nexp_pool, n, nu, 16), dtype=np.uint8), rng.integers(0, 256, size=(nexp_pool, n, nu, 8), dtype=np.uint8),
+                   rng.integers(-32, 32, size=(nexp_pool, n, nu, 2), dtype=np.int8), f16(1e-5, 3e-5, (nexp_pool, n, nu)))
+    else:
+        q, d = q8s(nexp_pool * 2 * ff, n)
+        p["gu"] = (q.reshape(nexp_pool, 2 * ff, n), d.reshape(nexp_pool, 2 * ff, n // 32))
+        q, d = q8s(nexp_pool * n, ff)
+        p["dn"] = (q.reshape(nexp_pool, n, ff), d.reshape(nexp_pool, n, ff // 32))
+    p["sh_gu"], p["sh_dn"] = q8s(2 * ff, n), q8s(n, ff)
+    nk, nv = shape.nkh, shape.nvh
+    ch = (2 * nk + nv) * 128
+    p["qkvz"], p["ssm_out"] = q8s(ch + nv * 128, n), q8s(n, nv * 128)
+    p["ab"] = (rng.standard_normal((2 * nv, n)) * 0.02).astype(np.float32)
+    p["S"] = (rng.standard_normal((nv, 128, 128)) * 0.1).astype(np.float32)
+    p["hist"] = rng.standard_normal((2, 3, ch)).astype(np.float32)
+    p["conv"] = (rng.standard_normal((ch, 4)) * 0.5).astype(np.float32)
+    vpk = nv // nk
+    p["vmap"] = np.array([(v // vpk) | ((1 if v % vpk == 0 else 0) << 8) for v in range(nv)], np.int32)
+    p["wq"], p["wk"], p["wv"], p["wo"] = q8s(nq * hd * 2, n), q8s(nkv * hd, n), q8s(nkv * hd, n), q8s(n, nq * hd)
+    rows = (ctx + 64 + 3) // 4 * 4
+    p["kc"] = rng.standard_normal((rows, nkv, hd), dtype=np.float32).astype(np.float16).view(np.uint16)
+    p["vc"] = rng.standard_normal((rows, nkv, hd), dtype=np.float32).astype(np.float16).view(np.uint16)
+    p["head"] = q8s(shape.vocab, n)
+    p["pool"] = nexp_pool
+    O.build()
+    return p
+
+
+def sample(p, shape, ctx):
     """Times one layer of each kind on the CPU oracle.  Returns seconds per piece."""
     import numpy as np
 
     from oracle import binding as O
 
-    O.build()
-    rng = np.random.default_rng(seed)
-    T, n, topk = 16, shape.n, shape.topk
-    kinds = shape.kinds
-    lg, la = kinds.index(0), kinds.index(1)
-    x = rng.standard_normal((T, n)).astype(np.float32)
-    t = {}
-    # ---- FFN half of layer lg (its own router, so the picks are the model's; only the picked experts are fetched)
-    router = _np(stack.named[(lg, "router")])
+    n, topk, ff = shape.n, shape.topk, shape.ff
+    x, t = p["x"], {}
     t0 = time.perf_counter()
     xq = O.quantize_q8_1(x)
-    logits, topi, topw, jgu, jdn, nj = O.router_route(router, x, topk)
+    logits, topi, topw, jgu, jdn, nj = O.router_route(p["router"], x, topk)
     t["router"] = time.perf_counter() - t0
-    experts = [int(j["w"]) for j in jgu[:nj]]
-    idx = stack.named[(lg, "gate_up")].new_tensor(experts, dtype=__import__("torch").long)
-    gu_w = _np(stack.named[(lg, "gate_up")][idx])
-    planes = tuple(_np(p[idx]) for p in stack.named[(lg, "down")])
-    planes = (planes[0], planes[1], planes[2].view(np.int8), planes[3].view(np.uint16))
-    for j in range(nj):
-        jgu[j]["w"] = jdn[j]["w"] = j
-    sgu = tuple(_np(a) for a in stack.named[(lg, "sh_gate_up")])
-    sdn = tuple(_np(a) for a in stack.named[(lg, "sh_down")])
+    for j in range(nj):   # the picked experts' matrices come from the pool
+        jgu[j]["w"] = jdn[j]["w"] = j % p["pool"]
     t0 = time.perf_counter()
-    gu = O.moe_gate_up_q4k(gu_w, gu_w.shape[1], jgu, nj, xq, n, 2 * stack.ffs, T * topk)
-    part = O.moe_down_q6p(planes, jdn, nj, gu, n, stack.ffs, T * topk)
-    _, sh = O.shared_expert(sgu[0], sgu[1].view(np.uint16), sdn[0], sdn[1].view(np.uint16), xq, T)
+    if shape.experts == "q4k":
+        gu = O.moe_gate_up_q4k(p["gu"], p["gu"].shape[1], jgu, nj, xq, n, 2 * ff, T * topk)
+        part = O.moe_down_q6p(p["dn"], jdn, nj, gu, n, ff, T * topk)
+    else:
+        gu = O.moe_gate_up_q8(p["gu"][0], p["gu"][1], jgu, nj, xq, T, T * topk)
+        part = O.moe_down_q8(p["dn"][0], p["dn"][1], jdn, nj, gu, T * topk)
+    _, sh = O.shared_expert(p["sh_gu"][0], p["sh_gu"][1], p["sh_dn"][0], p["sh_dn"][1], xq, T)
     O.moe_combine(part, topw, sh, logits, T, n, topk)
     t["experts"] = time.perf_counter() - t0
-    # ---- DeltaNet mixer of layer lg
-    qkvz_w = tuple(_np(a) for a in stack.named[(lg, "qkvz")])
-    out_w = tuple(_np(a) for a in stack.named[(lg, "ssm_out")])
-    ab_w = _np(stack.named[(lg, "ab")])
-    S, hist = _np(stack.named[(lg, "S")]).copy(), _np(stack.named[(lg, "hist")]).copy()
-    conv, vmap = _np(stack.named[(lg, "conv")]), _np(stack.named[(lg, "vmap")])
-    nk, nv = stack.nk, stack.nv
+    nk, nv = shape.nkh, shape.nvh
+    S, hist = p["S"].copy(), p["hist"].copy()
     t0 = time.perf_counter()
-    qkvz = O.q8s_gemv(qkvz_w[0], qkvz_w[1].view(np.uint16), xq, T)
-    ab = O.gemv_f32(ab_w, x, 4)
-    yq, _, _, _ = O.gdn_core(qkvz, ab, hist, conv, np.zeros(nv, np.float32), -np.ones(nv, np.float32), np.ones(128, np.float32), S,
-                             np.array([shape.ctx, 1], np.int32), nk, nv, vmap, shape.eps, want_y32=False)
-    O.q8s_gemv(out_w[0], out_w[1].view(np.uint16), yq, T)
+    qkvz = O.q8s_gemv(p["qkvz"][0], p["qkvz"][1], xq, T)
+    ab = O.gemv_f32(p["ab"], x, 4)
+    yq, _, _, _ = O.gdn_core(qkvz, ab, hist, p["conv"], np.zeros(nv, np.float32), -np.ones(nv, np.float32), np.ones(128, np.float32), S,
+                             np.array([ctx, 1], np.int32), nk, nv, p["vmap"], shape.eps, want_y32=False)
+    O.q8s_gemv(p["ssm_out"][0], p["ssm_out"][1], yq, T)
     t["gdn_layer"] = time.perf_counter() - t0
-    # ---- attention mixer of layer la
-    wq, wk, wv, wo = (tuple(_np(a) for a in stack.named[(la, k)]) for k in ("wq", "wk", "wv", "wo"))
-    kc, vc = _np(stack.named[(la, "kc")], np.uint16).copy(), _np(stack.named[(la, "vc")], np.uint16).copy()
     ones = np.ones(shape.hd, np.float32)
     t0 = time.perf_counter()
-    qg = O.q8s_gemv(wq[0], wq[1].view(np.uint16), xq, T).reshape(T, shape.nq, 2 * shape.hd)
-    k = O.q8s_gemv(wk[0], wk[1].view(np.uint16), xq, T).reshape(T, shape.nkv, shape.hd)
-    v = O.q8s_gemv(wv[0], wv[1].view(np.uint16), xq, T).reshape(T, shape.nkv, shape.hd)
-    O.attn_prep_append(qg, k, v, ones, ones, kc, vc, stack.card, stack.ncard, shape.ctx, shape.eps, shape.rope_base, shape.nq, shape.nkv,
-                       shape.hd, shape.nrot)
-    part = O.attn_partial(qg, kc, vc, stack.card, stack.ncard, shape.ctx, shape.nq, shape.nkv, shape.hd)
+    qg = O.q8s_gemv(p["wq"][0], p["wq"][1], xq, T).reshape(T, shape.nq, 2 * shape.hd)
+    k = O.q8s_gemv(p["wk"][0], p["wk"][1], xq, T).reshape(T, shape.nkv, shape.hd)
+    v = O.q8s_gemv(p["wv"][0], p["wv"][1], xq, T).reshape(T, shape.nkv, shape.hd)
+    O.attn_prep_append(qg, k, v, ones, ones, p["kc"], p["vc"], 0, 1, ctx, shape.eps, shape.rope_base, shape.nq, shape.nkv, shape.hd, shape.nrot)
+    part = O.attn_partial(qg, p["kc"], p["vc"], 0, 1, ctx, shape.nq, shape.nkv, shape.hd)
     att = O.attn_merge([part], qg, shape.nq, shape.hd)
-    aq = O.quantize_q8_1(att.reshape(T, -1))
-    O.q8s_gemv(wo[0], wo[1].view(np.uint16), aq, T)
+    O.q8s_gemv(p["wo"][0], p["wo"][1], O.quantize_q8_1(att.reshape(T, -1)), T)
     t["attn_layer"] = time.perf_counter() - t0
-    # ---- head
-    hw = tuple(_np(a) for a in stack.named[(len(kinds), "output")])
     t0 = time.perf_counter()
-    logits = O.q8s_gemv(hw[0], hw[1].view(np.uint16), xq, T)
-    O.argmax(logits)
+    lg = O.q8s_gemv(p["head"][0], p["head"][1], xq, T)
+    O.argmax(lg)
     t["head"] = time.perf_counter() - t0
+    t["distinct_experts"] = nj
     return t
 
 
@@ -92,48 +128,51 @@ def window_seconds(t, kinds):
     return len(kinds) * (t["router"] + t["experts"]) + kinds.count(0) * t["gdn_layer"] + kinds.count(1) * t["attn_layer"] + t["head"]
 
 
-def cpu_baseline(stack, runner, step, shape, accepted_per_window):
-    cores = len(os.sched_getaffinity(0))
-    t = _sample(stack, shape)
-    w = window_seconds(t, shape.kinds)
-    return {"value": round(accepted_per_window / w, 4), "unit": "tok/s", "cores": cores, "kind": "port",
-            "sample": "CPU oracle (C + OpenMP) on one FFN half, one DeltaNet mixer, one attention mixer (ctx %d) and the head of the same "
-                      "stack, once each; window time = sum scaled by the layer counts (%d FFN, %d DeltaNet, %d attention)" %
-                      (shape.ctx, len(shape.kinds), shape.kinds.count(0), shape.kinds.count(1)),
+SAMPLE = ("CPU oracle (C + OpenMP) on one FFN half, one DeltaNet mixer, one attention mixer at the workload's context and the head, on numpy-made "
+          "tensors of the workload's shapes; window time = sum scaled by the layer counts")
+
+
+def cpu_baseline(wl, shape, accepted_per_step):
+    """The `cpu_baseline` object of this arm's line: one sample on this host's cores, the same numerator as the GPU's."""
+    _use_all_cores()
+    p = synthetic_pieces(shape, wl["ctx"])
+    t = sample(p, shape, wl["ctx"])
+    w = window_seconds(t, shape.kinds) * wl["nseq"]
+    return {"value": round(accepted_per_step / w, 4), "unit": "tok/s", "cores": _cores(), "kind": "port", "sample": SAMPLE + ", once",
             "window_s": round(w, 3), "pieces_s": {k: round(v, 4) for k, v in t.items()}}
 
 
-def main(args, rank, world, emit=print, workload_config=None):
+def main(args, rank, wl, emit=print):
     """`bench.py --impl reference`: rank 0 alone runs (the other ranks exit 0 without work)."""
     if rank != 0:
         return 0
-    import torch
+    _use_all_cores()
+    import bench
+    from sfnx_b200.shapes import StackShape
 
-    from sfnx_b200.window import StackShape, SyntheticStack
-
-    kinds = [1 if (i % 4) == 3 else 0 for i in range(args.layers)]
-    full = StackShape(kinds=kinds, ctx=args.ctx)
-    # a two-layer stack (one DeltaNet, one attention) holds every tensor the sample reads; the inputs are generated on
-    # the device and copied to the host, the timed arithmetic runs on the host cores only
-    small = StackShape(kinds=[0, 1], ctx=args.ctx)
-    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
-    stack = SyntheticStack(small, ncard=1, card=0, seed=args.seed)
-    cores = len(os.sched_getaffinity(0))
-    accepted = 1 + sum(0.8 ** k for k in range(1, 16))   # expected tokens per window under Bernoulli(0.8) drafts
+    shape = StackShape(kinds=wl["kinds"], ctx=wl["ctx"], nexp=args.experts, vocab=args.vocab, experts=wl["experts"])
+    p = synthetic_pieces(shape, wl["ctx"], seed=args.seed)
+    repeats = args.repeats or (max(1, min(10, -(-200 // max(1, args.steps)))) if wl["name"] == "cfg2" else 1)
+    nsteps = args.warmup + args.steps * repeats
+    if wl["sampled"]:
+        accepted, numerator = float(wl["nseq"]), "1 token per window and sequence (what rejection sampling emits at the least)"
+    else:   # the numerator of the GPU arm: decided by the same Bernoulli draws
+        _, n = bench.accepted_from_draws(args.seed, nsteps * wl["nseq"])
+        accepted = sum(n[args.warmup * wl["nseq"]:]) / (args.steps * repeats)
+        numerator = "mean accepted tokens per step of the same %d windows the GPU arm times (1 + leading true Bernoulli draws)" % (args.steps * repeats)
     times = []
     for i in range(args.warmup + args.steps):
-        t = _sample(stack, small, seed=i)
+        t = sample(p, shape, wl["ctx"])
         if i >= args.warmup:
-            times.append(window_seconds(t, full.kinds))
-    w = sum(times) / len(times)
+            times.append(window_seconds(t, shape.kinds) * wl["nseq"])
+    times.sort()
+    w = times[len(times) // 2]
     val = round(accepted / w, 4)
     emit(json.dumps({
-        "impl": "reference", "metric": "accepted tok/s @ draft len 16", "value": val, "unit": "tok/s", "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(w * 1e3, 2), "higher_is_better": True, "scaling": "strong",
-        "vs_baseline": None, "dtype": "int8 x int4/int6/int8 dot products, f32 accumulate", "data": "synthetic",
-        "config": workload_config(full, kinds, args.ctx, max(1, args.gpus)),
-        "cpu_baseline": {"value": val, "unit": "tok/s", "cores": cores, "kind": "port",
-                         "sample": "each step: CPU oracle on one FFN half, one DeltaNet mixer, one attention mixer and the head, scaled "
-                                   "by the layer counts"},
+        "impl": "reference", "metric": bench.METRIC, "value": val, "unit": "tok/s", "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": round(w * 1e3, 2), "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": bench.DTYPE, "data": "synthetic", "config": bench.workload_config(wl, shape, max(1, args.gpus)),
+        "accepted_per_step": round(accepted, 3), "timing": {"statistic": "median step", "numerator": numerator},
+        "cpu_baseline": {"value": val, "unit": "tok/s", "cores": _cores(), "kind": "port", "sample": "each step: " + SAMPLE},
         "e2e": {"value": val, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
     return 0

@@ -332,9 +332,8 @@ static int window_stage_sunk(const FnxStackCfg* cfg, const FnxLayer* layers, con
     if (check_cfg(cfg) || !ws) return fail("window: no configuration or workspace");
     const Ws w = carve(*cfg);
     unsigned* err = (unsigned*) ((char*) ws + w.err);
-    // a window starts with a clean error word: the host reads the word after every window (the reference's engine throws on
-    // it, src/engine_impl.hpp:154-167), so an earlier window's fault has been reported by then
-    if (stage == 0 && cudaMemsetAsync(err, 0, 4, strm(st)) != cudaSuccess) return fail("window: clearing the error word failed");
+    // the word is sticky across windows (a device-timed replay reads it once at the end); the host clears it after it has
+    // reported a fault (the reference's engine throws on it after every window, src/engine_impl.hpp:154-167)
     fault_sink(err);
     const int rc = window_stage(cfg, layers, head, ws, T, stage, lanes, st);
     fault_sink(nullptr);

@@ -9,34 +9,10 @@ the vocabulary in contiguous ranges; the router, the norms and the embeddings ar
 import ctypes as C
 import os
 import sys
-from dataclasses import dataclass, field
-
 import torch
 
 from . import lib as L
-
-
-@dataclass
-class StackShape:
-    """The whole model's shapes (the benchmark configurations' defaults)."""
-    n: int = 3072
-    nexp: int = 512
-    topk: int = 10
-    ff: int = 768
-    nkh: int = 16
-    nvh: int = 48
-    nq: int = 24
-    nkv: int = 4
-    hd: int = 256
-    nrot: int = 64
-    vocab: int = 151936
-    kinds: list = field(default_factory=lambda: [0, 0, 0, 1, 0, 0, 0, 1])   # 0 DeltaNet, 1 attention
-    ctx: int = 32768
-    kv_slack: int = 64   # positions the K/V cache holds past ctx (the tokens a run appends)
-    eps: float = 1e-6
-    rope_base: float = 1e7
-    sigma: float = 0.02
-    experts: str = "q4k"   # routed experts: "q4k" (Q4_K gate|up, Q6_K down) or "q8_0" (both Q8_0)
+from .shapes import StackShape  # noqa: F401  (defined in a module without torch; re-exported here)
 
 
 def _seed(base, layer, name):
@@ -247,6 +223,33 @@ class SyntheticStack:
     def weight_bytes(self):
         return sum(t.numel() * t.element_size() for t in self.keep)
 
+    def sequence_view(self, index):
+        """Another sequence over the same weights: a copy of this stack's description whose DeltaNet states, conv
+        histories and K/V caches are tensors of its own (seeded by `index`); the weights, the checkpoints' scratch and the
+        workspace are shared, so windows of different sequences run one after the other on one stream."""
+        import copy
+
+        v = copy.copy(self)
+        v.layers = type(self.layers).from_buffer_copy(self.layers)
+        v.keep, v.named, v.gdn_state = [], dict(self.named), []
+        s = self.shape
+        for l, kind in enumerate(s.kinds):
+            Lr = v.layers[l]
+            if kind == 0:
+                S0, h0 = self.named[(l, "S")], self.named[(l, "hist")]
+                S = v._t(S0 * (1.0 + 0.05 * index))
+                hist = v._t(h0 * (1.0 - 0.03 * index))
+                Lr.S, Lr.hist = S.data_ptr(), hist.data_ptr()
+                v.gdn_state.append((S, hist))
+                v.named[(l, "S")], v.named[(l, "hist")] = S, hist
+            else:
+                kv = (self.kv_rows, s.nkv, s.hd)
+                kc = v._t(self._normal(l, "kc%d_seq%d" % (self.card, index), kv, 1.0).half().view(torch.int16))
+                vc = v._t(self._normal(l, "vc%d_seq%d" % (self.card, index), kv, 1.0).half().view(torch.int16))
+                Lr.kc, Lr.vc = kc.data_ptr(), vc.data_ptr()
+                v.named[(l, "kc")], v.named[(l, "vc")] = kc, vc
+        return v
+
 
 def merge_best(values, indices):
     """Per row, the token of the GPU whose slice holds the largest logit: strict > scanning GPU 0 upward, so the lower
@@ -339,7 +342,7 @@ class WindowRunner:
     """One window of T rows as a CUDA graph on its own stream: embedding rows from the token ids, every stage, and
     between stages the collectives of the process group (NCCL) when there is more than one GPU."""
 
-    def __init__(self, stack, T, group=None, graph=True, overlap=True, sampled=False, lanes=None):
+    def __init__(self, stack, T, group=None, graph=True, overlap=True, sampled=False, lanes=None, stream=None):
         import torch.distributed as dist
 
         self.stack, self.T, self.group = stack, T, group
@@ -354,7 +357,8 @@ class WindowRunner:
         self.nstages = lib.fnx_window_plan(C.byref(cfg), stack.layers, after, 1024)
         assert 0 < self.nstages <= 1024, lib.fnx_last_error()
         self.after = list(after[: self.nstages])
-        self.stream = torch.cuda.Stream()
+        # runners that share a workspace (several sequences over one stack) must share their stream too
+        self.stream = stream if stream is not None else torch.cuda.Stream()
         # what a window takes from the host, one buffer and one copy: the token ids, then (position, tag); the window's
         # first node copies the pair into the workspace's control words
         self.d_in = torch.zeros(L.MAXT + 2, dtype=torch.int32, device=stack.dev)
@@ -391,7 +395,7 @@ class WindowRunner:
         # the sum across GPUs after each half layer: the library's own peer-memory sum in the reference ring's order
         # (fnx_ring_sum) over torch's symmetric memory, or NCCL's all-reduce (FNX_RING=nccl, or when peer memory cannot
         # be set up)
-        self.ring = None
+        self.ring, self.ring_keep = None, None
         if self.dist is not None and os.environ.get("FNX_RING", "peer") != "nccl":
             self.ring = self._make_ring(T * s.n)
         self.job_bytes = len(s.kinds) * 2 * C.sizeof(L.CopyJob)
@@ -418,6 +422,7 @@ class WindowRunner:
     def _make_ring(self, count):
         """Two slots of `count` floats and 64 flag words that every GPU of the group can address, and this GPU's view of
         them (FnxRing).  Returns None (NCCL is used) when symmetric memory is not available."""
+        ptrs, why = None, ""
         try:
             import torch.distributed._symmetric_memory as symm
 
@@ -427,9 +432,15 @@ class WindowRunner:
             torch.cuda.synchronize()
             hdl = symm.rendezvous(buf, group)
             ptrs = [int(p) for p in hdl.buffer_ptrs]
-            self.dist.barrier(group=self.group)   # every slot and flag is zero before anyone can signal
         except Exception as e:   # noqa: BLE001
-            sys.stderr.write("peer-memory ring not available (%s): sums across GPUs go through NCCL\n" % (e,))
+            why = str(e)
+        # the ranks must take the same path: the peer-memory sum only if every rank has its buffers (a rank that went to
+        # NCCL alone would wait in a collective nobody else joins)
+        ok = torch.tensor([1 if ptrs else 0], dtype=torch.int32, device=self.stack.dev)
+        self.dist.all_reduce(ok, op=self.dist.ReduceOp.MIN, group=self.group)   # also: every slot and flag is zero before anyone signals
+        torch.cuda.synchronize()
+        if int(ok[0]) == 0:
+            sys.stderr.write("peer-memory ring not available on every rank (%s): sums across GPUs go through NCCL\n" % (why or "a peer failed"))
             return None
         ring = L.Ring()
         ring.nrank, ring.rank = self.stack.ncard, self.stack.card
@@ -511,7 +522,11 @@ class WindowRunner:
         self.stream.synchronize()
         err = int(self.h_err[0])
         if err != 0:
-            raise L.FnxError("window error word %d (bit 16: a non-finite logit)" % err)
+            with torch.cuda.stream(self.stream):
+                self.err.zero_()   # reported: the next window starts clean
+            self.stream.synchronize()
+            raise L.FnxError("window error word %d (bit 1: a peer's addend never came; bit 8: a bounded on-chip wait ran out; bit 16: a "
+                             "non-finite logit); the window's results are not to be used, the next window starts clean" % err)
         return self.merge_best()
 
     def window_lanes(self, rows, pos, tags):
@@ -575,6 +590,46 @@ class WindowRunner:
             self.stream.synchronize()
         L.call("fnx_window_commit", C.byref(self.stack.cfg), self.stack.layers, self.stack.ws.data_ptr(), self.T, n, tag,
                self.h_jobs.data_ptr() + slot * self.job_bytes, self.stream.cuda_stream)
+
+    def close(self):
+        """Releases what must go before the process group does: the captured graph (its NCCL nodes hold the communicator)
+        and the peer-mapped buffers of the sum across GPUs."""
+        torch.cuda.synchronize()
+        self.graph = None
+        self.ring = None
+        self.ring_keep = None
+        torch.cuda.synchronize()
+
+    def ring_self_check(self, rounds=8, seed=0):
+        """The sum across GPUs on the real peers: every rank makes all ranks' seeded addends, runs `rounds` sums back to
+        back on its own addend through this runner's ring (slots of both parities, the flags' epochs running on) and
+        compares the bits with the same chunks added in the ring's order by plain elementwise float adds.  Returns
+        {"rounds", "bits_equal", "err"}; None when the sums go through NCCL."""
+        if self.ring is None:
+            return None
+        n, me, T, width = self.stack.ncard, self.stack.card, self.T, self.stack.shape.n
+        NP = width // 2
+        ok, err = True, 0
+        x = torch.empty(T * width, dtype=torch.float32, device=self.stack.dev)
+        errw = torch.zeros(1, dtype=torch.int32, device=self.stack.dev)
+        with torch.cuda.stream(self.stream):
+            for r in range(rounds):
+                g = torch.Generator(device=self.stack.dev)
+                g.manual_seed(seed * 1000 + r)
+                adds = torch.randn((n, T, width), generator=g, device=self.stack.dev) * (10.0 ** (r % 3))
+                want = torch.empty((T, width), dtype=torch.float32, device=self.stack.dev)
+                for c in range(n):   # chunk c: float pairs [c NP / n, (c + 1) NP / n) of every row, started by GPU c
+                    lo, hi = 2 * (c * NP // n), 2 * ((c + 1) * NP // n)
+                    acc = adds[c, :, lo:hi].clone()
+                    for k in range(1, n):
+                        acc = acc + adds[(c + k) % n, :, lo:hi]
+                    want[:, lo:hi] = acc
+                x.copy_(adds[me].reshape(-1))
+                L.call("fnx_ring_sum", x.data_ptr(), T, width, C.byref(self.ring), errw.data_ptr(), self.stream.cuda_stream)
+                ok = ok and bool(torch.equal(x.view(torch.int32), want.reshape(-1).view(torch.int32)))
+            self.stream.synchronize()
+            err = int(errw[0])
+        return {"rounds": rounds, "bits_equal": ok, "err": err}
 
     h2d_bytes = property(lambda self: (L.MAXT + 2) * 4)
     d2h_bytes = property(lambda self: self.stack.ncard * self.T * 8 + 4)
