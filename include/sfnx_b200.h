@@ -254,6 +254,19 @@ typedef struct FnxRing {
 } FnxRing;
 int fnx_ring_sum(float* x, int rows, int row_len, const FnxRing* ring, unsigned* err, void* st);
 
+/* What lies between two halves of a layer, in one launch (the reference folds the same steps into its ring: src/kernels.hpp:
+ * 308-313 RingMoe, src/kernels.cu:797-806 ring_x; the norm is its hc_read's): the ended half's addend - bo[T][n], or the
+ * routed experts' rows weighted and added with the gated shared expert as fnx_moe_combine does (moe), or none (both null:
+ * a window's first half) - summed across the GPUs as fnx_ring_sum does (ring with nrank > 1; same slots, flags and state,
+ * slots of T * n floats), x += sum, then y = RMS norm of the new x with weight w (y may be null) and its q8_1 rows q (may be
+ * null), all as the separate entry points give them, bit for bit. */
+typedef struct FnxMoeRows {
+    const float *part, *topw, *sh, *logits; /* [T topk][n], [T][topk], [T][n], router logits [T][nexp + 1] */
+    int nexp, topk;
+} FnxMoeRows;
+int fnx_boundary_rows(float* x, const float* bo, const FnxMoeRows* moe, const FnxRing* ring, const float* w, float* y, void* q, int T, int n,
+                      float eps, unsigned* err, void* st);
+
 /* ---- head */
 /* reference src/kernels.hpp:384 argmax (src/kernels.cu:870-908): per row the largest logit and its index + v0, the lowest
  * index on a tie; a non-finite logit sets bit 16 of *err.  keys: 2 * FNX_MAXT 64-bit words, zeroed once (left at zero) */
@@ -331,6 +344,11 @@ int fnx_window_commit(const FnxStackCfg* cfg, const FnxLayer* layers, void* ws, 
  * alpha/beta projection beside qkvz; the reference's st2, src/engine.cu:939-946), with the two events (cudaEvent_t) the
  * forks and joins record; set per host thread, null to stay on one stream.  Capture-safe. */
 int fnx_window_side_stream(void* st2, void* ev_fork, void* ev_join);
+/* the peer-memory ring (FnxRing, slots of FNX_MAXT * n floats) of the calling thread's windows, null for none.  With a
+ * ring - and always on one GPU - a stage begins with fnx_boundary_rows, which sums the ended half's addends across the GPUs
+ * itself, and fnx_window_plan asks for no FNX_AFTER_SUM_BO; without one the caller sums FNX_BUF_BO between the stages (any
+ * all-reduce).  Set it before fnx_window_plan and before the stages are enqueued. */
+int fnx_window_ring(const FnxRing* ring);
 
 /* A window of several sequences ("lanes"; reference src/engine.cu:1137-1216 enqueue_rows / src/engine_common.cu:1136-1195
  * commit_rows): nseg lanes x `rows` window rows each, at most FNX_MAXT rows in all; lane s's rows are window rows

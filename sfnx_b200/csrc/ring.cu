@@ -105,6 +105,150 @@ __global__ void __launch_bounds__(RS_THREADS) k_ring_sum(float* __restrict__ x, 
     }
 }
 
+// ---------------------------------------------------------------- a half layer's boundary in one launch
+// What sits between two halves of a layer, in one kernel instead of three: the addend of the half that ended (its
+// output rows, or the routed experts' rows weighted and added with the gated shared expert: reference src/kernels.cu:
+// 797-806, ring_x), the sum of the GPUs' addends in the ring's order (as k_ring_sum, over the same slots, flags and
+// state), the residual update x += sum, and the RMS norm of the new x with its q8_1 copy for the half that begins
+// (k_rms_norm_rows' order of sums).  A block per row, 1024 threads; the row stays in shared memory between the steps.
+struct BoundaryArgs {
+    float* x;
+    const float* bo;
+    FnxMoeRows moe;
+    FnxRing ring;
+    const float* w;
+    float* y;
+    uint8_t* q;
+    int n;
+    float eps;
+    unsigned* err;
+};
+constexpr int BD_THREADS = 1024, BD_MAXN = 4096;
+
+__device__ __forceinline__ void bd_q8_1_store(float xi, uint8_t* blk, int lane) {
+    const float amax = wmax(fabsf(xi)), sum = wsum(xi);
+    const float d = fdiv(amax, 127.0f);
+    reinterpret_cast<int8_t*>(blk + 4)[lane] = amax == 0.0f ? 0 : (int8_t) roundf(fdiv(xi, d));
+    if (lane == 0) {
+        reinterpret_cast<uint16_t*>(blk)[0] = f2h(d);
+        reinterpret_cast<uint16_t*>(blk)[1] = f2h(sum);
+    }
+}
+
+__global__ void __launch_bounds__(BD_THREADS) k_boundary_rows(const BoundaryArgs a) {
+    __shared__ __align__(16) float row[BD_MAXN];
+    __shared__ float sh[32];
+    __shared__ bool last;
+    const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, n = a.n, nr = a.ring.nrank, me = a.ring.rank;
+    float* xr = a.x + (size_t) t * n;
+    pdl_wait();
+    pdl_go();
+    const bool has_add = a.bo || a.moe.part;
+    // ---- this GPU's addend of the row
+    if (a.moe.part) {
+        const int topk = a.moe.topk;
+        const float gate = ex_sigmoid(a.moe.logits[(size_t) t * (a.moe.nexp + 1) + a.moe.nexp]);
+        for (int i = tid; i < n; i += BD_THREADS) {
+            float s = 0.f;
+            for (int k = 0; k < topk; ++k) s = ffma(a.moe.topw[t * topk + k], a.moe.part[((size_t) t * topk + k) * n + i], s);
+            row[i] = ffma(gate, a.moe.sh[(size_t) t * n + i], s);
+        }
+    } else if (a.bo) {
+        for (int i = tid; i < n; i += BD_THREADS) row[i] = a.bo[(size_t) t * n + i];
+    }
+    if (nr > 1 && has_add) {
+        unsigned* state = a.ring.state;
+        const unsigned epoch = *reinterpret_cast<volatile unsigned*>(state) + 1u;
+        const int parity = (int) (epoch & 1u), n4 = n / 4;
+        __syncthreads();
+        float4* mine = reinterpret_cast<float4*>(a.ring.slot[parity][me] + (size_t) t * n);
+        for (int i = tid; i < n4; i += BD_THREADS) mine[i] = reinterpret_cast<const float4*>(row)[i];
+        __threadfence_system();
+        __syncthreads();
+        if (tid == 0) last = atomicAdd(&state[1], 1u) == gridDim.x - 1;
+        __syncthreads();
+        if (last) {   // every row of the addend is in the slot: tell every peer
+            __threadfence_system();
+            if (tid < nr && tid != me) st_release_sys(a.ring.pad[tid] + me, epoch);
+            if (tid == 0) state[1] = 0u;
+        }
+        if (tid < nr && tid != me) {
+            const unsigned* flag = a.ring.pad[me] + tid;
+            unsigned spins = 0;
+            while ((int) (ld_acquire_sys(flag) - epoch) < 0) {
+                if (++spins >= a.ring.spin_limit) {
+                    atomicOr(a.err, 1u);
+                    break;
+                }
+                __nanosleep(64);
+            }
+        }
+        __syncthreads();
+        const int NP = n / 2;
+        auto chunk_of = [&](int p) {
+            int c = (int) ((long long) p * nr / NP);
+            while (c + 1 < nr && (long long) (c + 1) * NP / nr <= p) ++c;
+            while (c > 0 && (long long) c * NP / nr > p) --c;
+            return c;
+        };
+        for (int i = tid; i < n4; i += BD_THREADS) {
+            const int p0 = 2 * i, ca = chunk_of(p0), cb = chunk_of(p0 + 1);
+            float4 v[FNX_RING_MAX];
+#pragma unroll
+            for (int r = 0; r < FNX_RING_MAX; ++r)
+                if (r < nr) v[r] = r == me ? reinterpret_cast<const float4*>(row)[i] : ld_peer(a.ring.slot[parity][r] + (size_t) t * n + 4 * (size_t) i);
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int k = 0; k < FNX_RING_MAX; ++k)
+                if (k < nr) {
+                    const int ra = ca + k < nr ? ca + k : ca + k - nr, rb = cb + k < nr ? cb + k : cb + k - nr;
+                    float ax = 0.f, ay = 0.f, bz = 0.f, bw = 0.f;
+#pragma unroll
+                    for (int r = 0; r < FNX_RING_MAX; ++r) {
+                        if (r == ra) ax = v[r].x, ay = v[r].y;
+                        if (r == rb) bz = v[r].z, bw = v[r].w;
+                    }
+                    if (k == 0) acc = make_float4(ax, ay, bz, bw);
+                    else acc.x = fadd(acc.x, ax), acc.y = fadd(acc.y, ay), acc.z = fadd(acc.z, bz), acc.w = fadd(acc.w, bw);
+                }
+            __syncwarp();
+            reinterpret_cast<float4*>(row)[i] = acc;   // a thread reads only its own float4 of the row above
+        }
+        __syncthreads();
+        if (tid == 0 && atomicAdd(&state[2], 1u) == gridDim.x - 1) {
+            state[2] = 0u;
+            __threadfence();
+            *reinterpret_cast<volatile unsigned*>(state) = epoch;
+        }
+    }
+    __syncthreads();
+    // ---- x += sum; RMS norm: thread i the squares of columns i, i + 1024, ... in order, warp trees, the warps in order
+    float s = 0.f;
+    for (int i = tid; i < n; i += BD_THREADS) {
+        float v = xr[i];
+        if (has_add) {
+            v = fadd(v, row[i]);
+            xr[i] = v;
+        }
+        row[i] = v;
+        s = ffma(v, v, s);
+    }
+    s = wsum(s);
+    if (lane == 0) sh[warp] = s;
+    __syncthreads();
+    float tot = 0.f;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) tot = fadd(tot, sh[i]);
+    const float r = ex_rsqrt(fadd(fdiv(tot, (float) n), a.eps));
+    for (int i0 = 0; i0 < n; i0 += BD_THREADS) {
+        const int i = i0 + tid;
+        const bool live = i < n;
+        const float v = live ? fmul(fmul(row[i], r), a.w[i]) : 0.f;
+        if (live && a.y) a.y[(size_t) t * n + i] = v;
+        if (a.q && (i0 + warp * 32) < n) bd_q8_1_store(v, a.q + ((size_t) t * (n / 32) + (i >> 5)) * 36, lane);
+    }
+}
+
 }  // namespace fnxk
 
 using namespace fnxk;
@@ -124,5 +268,28 @@ int fnx_ring_sum(float* x, int rows, int row_len, const FnxRing* ring, unsigned*
     const int blocks = std::min(64, (count / 4 + RS_THREADS - 1) / RS_THREADS);
     k_ring_sum<<<blocks, RS_THREADS, 0, strm(st)>>>(x, count, row_len, *ring, err);
     return launch_ok("ring_sum");
+}
+
+int fnx_boundary_rows(float* x, const float* bo, const FnxMoeRows* moe, const FnxRing* ring, const float* w, float* y, void* q, int T, int n,
+                      float eps, unsigned* err, void* st) {
+    FNX_REQUIRE(x && w && T >= 1 && T <= FNX_MAXT, "boundary_rows: %d rows (1..%d)", T, FNX_MAXT);
+    FNX_REQUIRE(n > 0 && n % 32 == 0 && n <= BD_MAXN, "boundary_rows: %d columns (a multiple of 32 up to %d)", n, BD_MAXN);
+    FNX_REQUIRE(!(bo && moe), "boundary_rows: the ended half's rows or the experts' rows, not both");
+    BoundaryArgs a{};
+    a.x = x, a.bo = bo, a.w = w, a.y = y, a.q = (uint8_t*) q, a.n = n, a.eps = eps, a.err = err;
+    if (moe) {
+        FNX_REQUIRE(moe->part && moe->topw && moe->sh && moe->logits && moe->topk >= 1 && moe->nexp >= 1, "boundary_rows: the experts' rows are incomplete");
+        a.moe = *moe;
+    }
+    a.ring.nrank = 1;
+    if (ring && ring->nrank > 1 && (bo || moe)) {
+        FNX_REQUIRE(ring->nrank <= FNX_RING_MAX && ring->rank >= 0 && ring->rank < ring->nrank, "boundary_rows: GPU %d of %d", ring->rank, ring->nrank);
+        FNX_REQUIRE(ring->state && ring->spin_limit > 0 && err && n % 4 == 0, "boundary_rows: no state words, spin limit or error word");
+        for (int r = 0; r < ring->nrank; ++r)
+            FNX_REQUIRE(ring->slot[0][r] && ring->slot[1][r] && ring->pad[r], "boundary_rows: GPU %d's slots or flags are missing", r);
+        a.ring = *ring;
+    }
+    launch(0, k_boundary_rows, T, BD_THREADS, 0, strm(st), a);
+    return launch_ok("boundary_rows");
 }
 }

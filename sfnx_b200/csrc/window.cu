@@ -44,6 +44,12 @@ static int side_join(void* st) {
     return 0;
 }
 
+// the peer-memory ring of the sum across GPUs, given by the caller (fnx_window_ring): with it a stage begins with the fused
+// boundary kernel, which sums the ended half's addends itself, and the plan asks the caller for no sum between stages
+static thread_local FnxRing g_ring;
+static thread_local bool g_ring_set = false;
+static bool fused_boundaries(const FnxStackCfg& c) { return c.ncard == 1 || g_ring_set; }
+
 struct Traced {
     int slot = -1;
     cudaStream_t st;
@@ -135,14 +141,15 @@ static int plan(const FnxStackCfg& c, const FnxLayer* L, Stage* out, int* after,
         }
         ++s;
     };
+    const int sum = fused_boundaries(c) ? FNX_AFTER_NONE : FNX_AFTER_SUM_BO;   // fused: the next stage's first kernel sums
     for (int l = 0; l < c.nlayers; ++l) {
         if (L[l].kind == 1) {
             put(l, 0, FNX_AFTER_GATHER_PARTIALS);
-            put(l, 1, FNX_AFTER_SUM_BO);
+            put(l, 1, sum);
         } else {
-            put(l, 0, FNX_AFTER_SUM_BO);
+            put(l, 0, sum);
         }
-        put(l, 2, FNX_AFTER_SUM_BO);
+        put(l, 2, sum);
     }
     put(c.nlayers, 3, FNX_AFTER_GATHER_BEST);
     return s;
@@ -223,12 +230,23 @@ static int window_stage(const FnxStackCfg* cfg, const FnxLayer* layers, const Fn
     float* xn = (float*) (b + w.xn);
     void* xq = b + w.xq;
     const int* ctl = (const int*) (b + w.ctl);
-    // the previous half's output is still pending: every stage that reads x first folds bo into it (not stage 0, and
-    // not the attention's second part, which continues its own layer's mixer)
+    // the previous half's output is still pending: every stage that reads x first folds it into x (not stage 0, and not
+    // the attention's second part, which continues its own layer's mixer).  Fused: one kernel takes the ended half's rows
+    // (a mixer's bo, or the experts' rows with their weights), sums them across the GPUs, updates x and norms it; else the
+    // ended FFN half has combined its rows into bo, the caller has summed bo, and the norm kernel adds it.
     const float* pending = stage == 0 ? nullptr : bo;
+    const bool fused = fused_boundaries(c);
+    const bool after_ffn = stage > 0 && stages[stage - 1].part == 2;
+    const FnxMoeRows moe_rows{(const float*) (b + w.part), (const float*) (b + w.topw), (const float*) (b + w.sh), (const float*) (b + w.rlogits), c.nexp, c.topk};
+    auto begin_half = [&](const float* norm_w, float* y) -> int {
+        if (!fused) return fnx_rms_norm_rows(x, pending, norm_w, y, xq, T, c.n, c.eps, st);
+        return fnx_boundary_rows(x, after_ffn ? nullptr : pending, after_ffn ? &moe_rows : nullptr, c.ncard > 1 ? &g_ring : nullptr, norm_w, y, xq, T, c.n,
+                                 c.eps, (unsigned*) (b + w.err), st);
+    };
+    const char* begin_name = fused ? "boundary" : "rms_norm";
     if (sg.part == 3) {
         FNX_REQUIRE(head, "window: no head");
-        TRK("rms_norm", fnx_rms_norm_rows(x, pending, head->norm, nullptr, xq, T, c.n, c.eps, st));
+        TRK(begin_name, begin_half(head->norm, nullptr));
         float* logits = (float*) (b + w.logits);
         TRK("head", fnx_q8s_gemv(head->out, c.vocab_rows, c.n, xq, logits, c.vocab_rows, T, st));
         TRK("argmax", fnx_argmax(logits, c.vocab_rows, T, c.vocab0, (float*) (b + w.best_v), (int*) (b + w.best_i),
@@ -238,7 +256,7 @@ static int window_stage(const FnxStackCfg* cfg, const FnxLayer* layers, const Fn
     const FnxLayer& L = layers[sg.layer];
     if (sg.part == 0 && L.kind == 0) {   // Gated DeltaNet mixer
         const int rows = (2 * c.nk + 2 * c.nv) * FNX_HS;
-        TRK("rms_norm", fnx_rms_norm_rows(x, pending, L.norm1, xn, xq, T, c.n, c.eps, st));
+        TRK(begin_name, begin_half(L.norm1, xn));
         const bool forked = side_fork(st);
         TRK("ab", fnx_gemv_f32(L.ab, xn, (float*) (b + w.ab), 2 * c.nv, c.n, T, forked ? (void*) g_side.st : st));
         TRK("qkvz", fnx_q8s_gemv(L.qkvz, rows, c.n, xq, (float*) (b + w.qkvz), rows, T, st));
@@ -257,7 +275,7 @@ static int window_stage(const FnxStackCfg* cfg, const FnxLayer* layers, const Fn
         float* qg = (float*) (b + w.qg);
         float* k = (float*) (b + w.k);
         float* v = (float*) (b + w.v);
-        TRK("rms_norm", fnx_rms_norm_rows(x, pending, L.norm1, nullptr, xq, T, c.n, c.eps, st));
+        TRK(begin_name, begin_half(L.norm1, nullptr));
         {   // q, k and v in one launch
             const FnxQ8S ws[3] = {L.wq, L.wk, L.wv};
             const int rows3[3] = {c.nq * c.hd * 2, c.nkv * c.hd, c.nkv * c.hd};
@@ -306,7 +324,7 @@ static int window_stage(const FnxStackCfg* cfg, const FnxLayer* layers, const Fn
     // FFN half
     const int P = T * c.topk;
     float* rl = (float*) (b + w.rlogits);
-    TRK("rms_norm", fnx_rms_norm_rows(x, pending, L.norm2, xn, xq, T, c.n, c.eps, st));
+    TRK(begin_name, begin_half(L.norm2, xn));
     const bool forked = side_fork(st);   // the shared expert beside the router and the routed experts
     if (forked)
         TRY(fnx_shared_expert(L.sh_gate_up, L.sh_down, xq, T, c.n, c.ff, (float*) (b + w.sh_gu), b + w.shq, (float*) (b + w.sh), g_side.st));
@@ -320,8 +338,9 @@ static int window_stage(const FnxStackCfg* cfg, const FnxLayer* layers, const Fn
     } else {
         TRK("shared_expert", fnx_shared_expert(L.sh_gate_up, L.sh_down, xq, T, c.n, c.ff, (float*) (b + w.sh_gu), b + w.shq, (float*) (b + w.sh), st));
     }
-    TRK("moe_combine", fnx_moe_combine((const float*) (b + w.part), (const float*) (b + w.topw), (const float*) (b + w.sh), rl, c.nexp, bo,
-                                          T, c.n, c.topk, st));
+    if (!fused)   // fused: the next stage's boundary kernel weighs and adds the experts' rows itself
+        TRK("moe_combine", fnx_moe_combine((const float*) (b + w.part), (const float*) (b + w.topw), (const float*) (b + w.sh), rl, c.nexp, bo,
+                                              T, c.n, c.topk, st));
     return 0;
 }
 
@@ -411,6 +430,13 @@ int fnx_window_side_stream(void* st2, void* ev_fork, void* ev_join) {
     g_side.st = (cudaStream_t) st2;
     g_side.fork = (cudaEvent_t) ev_fork;
     g_side.join = (cudaEvent_t) ev_join;
+    return 0;
+}
+
+// the ring of the sum across GPUs for the calling thread's windows (null: none; the plan then asks the caller to sum)
+int fnx_window_ring(const FnxRing* ring) {
+    g_ring_set = ring != nullptr && ring->nrank > 1;
+    if (g_ring_set) g_ring = *ring;
     return 0;
 }
 

@@ -86,6 +86,10 @@ class Ring(C.Structure):
                 ("state", C.c_void_p), ("spin_limit", C.c_uint)]
 
 
+class MoeRows(C.Structure):
+    _fields_ = [("part", C.c_void_p), ("topw", C.c_void_p), ("sh", C.c_void_p), ("logits", C.c_void_p), ("nexp", C.c_int), ("topk", C.c_int)]
+
+
 class CopyJob(C.Structure):
     _fields_ = [("dst", C.c_void_p), ("src", C.c_void_p), ("bytes", C.c_size_t)]
 
@@ -130,12 +134,14 @@ _SIGS = {
     "fnx_embed_rows": [_p, _p, _p, _i, _i, _p],
     "fnx_window_init": [_p, _p, _p],
     "fnx_window_side_stream": [_p, _p, _p],
+    "fnx_window_ring": [_p],
     "fnx_window_stage": [_p, _p, _p, _p, _i, _i, _p],
     "fnx_window_commit": [_p, _p, _p, _i, _i, _i, _p, _p],
     "fnx_window_stage_lanes": [_p, _p, _p, _p, C.POINTER(WindowLanes), _i, _p],
     "fnx_window_commit_lanes": [_p, _p, _p, C.POINTER(WindowLanes), _p, _p, _p, _p],
     "fnx_top_merge": [_p, _p, _i, _i, _p, _p],
     "fnx_ring_sum": [_p, _i, _i, C.POINTER(Ring), _p, _p],
+    "fnx_boundary_rows": [_p, _p, _p, _p, _p, _p, _p, _i, _i, _f, _p, _p],
 }
 _OTHER = {
     "fnx_last_error": (C.c_char_p, []),

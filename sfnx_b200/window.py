@@ -93,6 +93,16 @@ class SyntheticStack:
         self.named[(layer, name)] = (q, d)
         return L.Q8S(q.data_ptr(), d.data_ptr())
 
+    def _kv_slice(self, layer, name):
+        """This GPU's rows of a K or V cache N(0, 1) over every position: the whole cache is generated (the same on every
+        GPU) and local row r = the row of position ((r / 4) ncard + card) 4 + r % 4."""
+        s = self.shape
+        full = self._normal(layer, name, (self.kv_rows * self.ncard, s.nkv, s.hd), 1.0).half()
+        if self.ncard == 1:
+            return self._t(full.view(torch.int16))
+        r = torch.arange(self.kv_rows, device=self.dev)
+        return self._t(full[((r // 4) * self.ncard + self.card) * 4 + r % 4].view(torch.int16))
+
     def _idx(self, lst):
         return torch.tensor(lst, dtype=torch.long, device=self.dev)
 
@@ -143,9 +153,7 @@ class SyntheticStack:
             Lr.wo = self._q8s(l, "wo", s.n, s.nq * s.hd, cols_idx=self._idx(list(range(self.card * own * nb, (self.card + 1) * own * nb))))
             Lr.q_norm = self._t(torch.ones(s.hd, device=self.dev)).data_ptr()
             Lr.k_norm = self._t(torch.ones(s.hd, device=self.dev)).data_ptr()
-            kv = (self.kv_rows, s.nkv, s.hd)
-            kc = self._t(self._normal(l, "kc%d" % self.card, kv, 1.0).half().view(torch.int16))
-            vc = self._t(self._normal(l, "vc%d" % self.card, kv, 1.0).half().view(torch.int16))
+            kc, vc = self._kv_slice(l, "kc"), self._kv_slice(l, "vc")
             Lr.kc, Lr.vc = kc.data_ptr(), vc.data_ptr()
             self.named[(l, "kc")], self.named[(l, "vc")] = kc, vc
             Lr.pages = L.KvPages(None, 0, 0, self.kv_rows)
@@ -243,9 +251,7 @@ class SyntheticStack:
                 v.gdn_state.append((S, hist))
                 v.named[(l, "S")], v.named[(l, "hist")] = S, hist
             else:
-                kv = (self.kv_rows, s.nkv, s.hd)
-                kc = v._t(self._normal(l, "kc%d_seq%d" % (self.card, index), kv, 1.0).half().view(torch.int16))
-                vc = v._t(self._normal(l, "vc%d_seq%d" % (self.card, index), kv, 1.0).half().view(torch.int16))
+                kc, vc = v._t(self._kv_slice(l, "kc_seq%d" % index)), v._t(self._kv_slice(l, "vc_seq%d" % index))
                 Lr.kc, Lr.vc = kc.data_ptr(), vc.data_ptr()
                 v.named[(l, "kc")], v.named[(l, "vc")] = kc, vc
         return v
@@ -353,10 +359,6 @@ class WindowRunner:
         self.dist = dist if stack.ncard > 1 else None
         cfg, s = stack.cfg, stack.shape
         lib = L.load()
-        after = (C.c_int * 1024)()
-        self.nstages = lib.fnx_window_plan(C.byref(cfg), stack.layers, after, 1024)
-        assert 0 < self.nstages <= 1024, lib.fnx_last_error()
-        self.after = list(after[: self.nstages])
         # runners that share a workspace (several sequences over one stack) must share their stream too
         self.stream = stream if stream is not None else torch.cuda.Stream()
         # what a window takes from the host, one buffer and one copy: the token ids, then (position, tag); the window's
@@ -397,7 +399,13 @@ class WindowRunner:
         # be set up)
         self.ring, self.ring_keep = None, None
         if self.dist is not None and os.environ.get("FNX_RING", "peer") != "nccl":
-            self.ring = self._make_ring(T * s.n)
+            self.ring = self._make_ring(L.MAXT * s.n)
+        # the plan depends on who sums across the GPUs: the library's boundary kernel over the ring, or the caller
+        L.call("fnx_window_ring", C.byref(self.ring) if self.ring is not None else None)
+        after = (C.c_int * 1024)()
+        self.nstages = lib.fnx_window_plan(C.byref(cfg), stack.layers, after, 1024)
+        assert 0 < self.nstages <= 1024, lib.fnx_last_error()
+        self.after = list(after[: self.nstages])
         self.job_bytes = len(s.kinds) * 2 * C.sizeof(L.CopyJob)
         self.h_jobs = torch.zeros(64 * self.job_bytes, dtype=torch.uint8).pin_memory()   # a ring of job tables
         self.commits = 0
@@ -459,6 +467,7 @@ class WindowRunner:
             L.call("fnx_window_side_stream", self.side.cuda_stream, self.ev_fork.cuda_event, self.ev_join.cuda_event)
         else:
             L.call("fnx_window_side_stream", None, None, None)
+        L.call("fnx_window_ring", C.byref(self.ring) if self.ring is not None else None)
         self.ctl.copy_(self.ctl_in)
         L.call("fnx_embed_rows", stack.embed.data_ptr(), self.ids.data_ptr(), self.x.data_ptr(), T, stack.shape.n, st)
         for i in range(self.nstages):

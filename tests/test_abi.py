@@ -18,7 +18,7 @@ def test_sizes_and_host_helpers(fnx):
     lib = fnx.load()
     assert lib.fnx_kv_rows_per_card(32768, 1) == 32768 and lib.fnx_kv_rows_per_card(32768, 8) == 4096
     assert lib.fnx_kv_rows_per_card(10, 4) == 4
-    assert lib.fnx_gdn_scratch_floats(48) == 16 * 48 * 128 + 48 * 16 * 4 + 48
+    assert lib.fnx_gdn_scratch_floats(48) == 16 * 3 * 48 * 128 + 16 * 48 * 2
     assert lib.fnx_moe_h_bytes(160, 768) == 160 * 768 + 160 * 24 * 4
 
 

@@ -65,3 +65,71 @@ def test_ring_sum_gives_up_when_a_peer_never_signals():
     y.fill_(3.0)
     G.sync()
     assert float(G.host(y)[0]) == 3.0
+
+
+@pytest.mark.parametrize("n,T,width,moe", [(1, 16, 3072, True), (1, 5, 512, False), (2, 16, 3072, True), (8, 16, 3072, False), (4, 3, 1024, True)])
+def test_boundary_rows_equals_the_separate_steps(n, T, width, moe):
+    """The fused boundary (experts' rows weighted and added | the half's rows, summed across the GPUs, x += sum, RMS norm,
+    q8_1) against fnx_moe_combine -> fnx_ring_sum -> fnx_rms_norm_rows on the same buffers, bit for bit; the peers of one
+    GPU are emulated as in the ring test above (their addends and flags in place before the launch)."""
+    import torch
+
+    from sfnx_b200 import lib as L
+    from tests import gpu_util as G
+
+    rng = np.random.default_rng(7 * n + T)
+    topk, nexp = 10, 32
+    x0 = rng.standard_normal((T, width)).astype(np.float32)
+    wn = (1 + 0.1 * rng.standard_normal(width)).astype(np.float32)
+    peers = [(rng.standard_normal((T, width)) * 10 ** rng.uniform(-2, 2, (T, width))).astype(np.float32) for _ in range(n)]
+    part = rng.standard_normal((T * topk, width)).astype(np.float32)
+    topw = rng.random((T, topk)).astype(np.float32)
+    sh = rng.standard_normal((T, width)).astype(np.float32)
+    logits = rng.standard_normal((T, nexp + 1)).astype(np.float32)
+    st = L.stream()
+    for rank in range(n):
+        dpart, dtopw, dsh, dlog, dw = G.dev(part), G.dev(topw), G.dev(sh), G.dev(logits), G.dev(wn)
+        # ---- the separate steps
+        bo = G.zeros((T, width))
+        if moe:
+            L.call("fnx_moe_combine", dpart.data_ptr(), dtopw.data_ptr(), dsh.data_ptr(), dlog.data_ptr(), nexp, bo.data_ptr(), T, width, topk, st)
+        else:
+            bo.copy_(G.dev(peers[rank]))
+        G.sync()
+        mine = G.host(bo).copy()   # this GPU's addend; the emulated peers hold theirs
+        adds = [mine if k == rank else peers[k] for k in range(n)]
+
+        def ring_for(epoch):
+            slots = [[G.dev(adds[k]) if p == epoch % 2 else G.zeros((T, width)) for p in range(2)] for k in range(n)]
+            pads = [torch.full((16,), epoch, dtype=torch.int32, device=G.DEV) for _ in range(n)]
+            state = torch.tensor([epoch - 1, 0, 0, 0], dtype=torch.int32, device=G.DEV)
+            return _ring(L, G, torch, n, rank, slots, pads, state, 1 << 20), (slots, pads, state)
+
+        err = G.zeros(1, torch.int32)
+        ring, keep = ring_for(1)
+        L.call("fnx_ring_sum", bo.data_ptr(), T, width, C.byref(ring), err.data_ptr(), st)
+        x1, y1, q1 = G.dev(x0), G.zeros((T, width)), G.zeros(T * (width // 32) * 36, torch.uint8)
+        L.call("fnx_rms_norm_rows", x1.data_ptr(), bo.data_ptr(), dw.data_ptr(), y1.data_ptr(), q1.data_ptr(), T, width, 1e-6, st)
+        # ---- the one launch
+        ring2, keep2 = ring_for(1)
+        x2, y2, q2 = G.dev(x0), G.zeros((T, width)), G.zeros(T * (width // 32) * 36, torch.uint8)
+        rows = L.MoeRows(dpart.data_ptr(), dtopw.data_ptr(), dsh.data_ptr(), dlog.data_ptr(), nexp, topk)
+        bo2 = G.dev(peers[rank])
+        L.call("fnx_boundary_rows", x2.data_ptr(), None if moe else bo2.data_ptr(), C.byref(rows) if moe else None, C.byref(ring2) if n > 1 else None,
+               dw.data_ptr(), y2.data_ptr(), q2.data_ptr(), T, width, 1e-6, err.data_ptr(), st)
+        G.sync()
+        assert int(G.host(err)[0]) == 0
+        assert np.array_equal(G.host(x2).view(np.uint32), G.host(x1).view(np.uint32)), (n, rank, "x")
+        assert np.array_equal(G.host(y2).view(np.uint32), G.host(y1).view(np.uint32)), (n, rank, "y")
+        assert np.array_equal(G.host(q2), G.host(q1)), (n, rank, "q8_1")
+        if n > 1:
+            assert G.host(keep2[2]).tolist()[:3] == [1, 0, 0]
+    # a window's first half: no addend, the norm alone
+    x3, y3, q3 = G.dev(x0), G.zeros((T, width)), G.zeros(T * (width // 32) * 36, torch.uint8)
+    x4, y4, q4 = G.dev(x0), G.zeros((T, width)), G.zeros(T * (width // 32) * 36, torch.uint8)
+    dw = G.dev(wn)
+    L.call("fnx_rms_norm_rows", x3.data_ptr(), None, dw.data_ptr(), y3.data_ptr(), q3.data_ptr(), T, width, 1e-6, st)
+    L.call("fnx_boundary_rows", x4.data_ptr(), None, None, None, dw.data_ptr(), y4.data_ptr(), q4.data_ptr(), T, width, 1e-6, None, st)
+    G.sync()
+    assert np.array_equal(G.host(y4).view(np.uint32), G.host(y3).view(np.uint32)) and np.array_equal(G.host(q4), G.host(q3))
+    assert np.array_equal(G.host(x4), x0)
