@@ -297,7 +297,7 @@ def main():
                 else:
                     r._enqueue()
             L.call("fnx_window_commit", C.byref(seqs[q].cfg), seqs[q].layers, stack.ws.data_ptr(), T, rec[i][q][3], rec[i][q][2],
-                   r.h_jobs.data_ptr() + (i % 64) * r.job_bytes, main_stream.cuda_stream) if rec[i][q][3] < T else None
+                   r.h_jobs.data_ptr() + (i % 64) * r.job_bytes, main_stream.cuda_stream)
 
     load_all(state0)
     clocks.start()

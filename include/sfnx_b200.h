@@ -182,6 +182,25 @@ size_t fnx_gdn_scratch_floats(int nv);
 int fnx_gdn_core(const float* qkvz, const float* ab, float* hist, const float* convw, const float* dt, const float* a,
                  const float* nw, float* S, void* yq, const int* ctl, float* scratch, float* snap, float* hsnap, int nk, int nv,
                  const int* vmap, int T, float eps, void* st, float* y32);
+/* The same window without checkpoints (no counterpart in the reference, whose rollback copies a checkpoint back,
+ * src/engine_common.cu:525-568): S is read and left as it is; each row's decay, key and delta go into `log`
+ * (fnx_gdn_log_floats(nk, nv) floats, this layer's and sequence's own), and fnx_gdn_replay then sets S to the state after the
+ * first n rows - S <- g_t S + k_t (x) delta_t for t < n, the window's own operations, so the bits are those the
+ * checkpoints would hold - for n = T as well: a logged window's state advances only through the replay.  yq, hist and hsnap
+ * as fnx_gdn_core's.  A window moves 3 state-sized transfers instead of 17. */
+size_t fnx_gdn_log_floats(int nk, int nv);
+int fnx_gdn_core_log(const float* qkvz, const float* ab, float* hist, const float* convw, const float* dt, const float* a, const float* nw,
+                     const float* S, void* yq, const int* ctl, float* scratch, float* log, float* hsnap, int nk, int nv, const int* vmap, int T, float eps,
+                     void* st);
+typedef struct FnxGdnReplay {
+    float* S;        /* [nv][128][128], advanced in place */
+    const float* log;
+    const int* vmap; /* as fnx_gdn_core's */
+    int nk, nv;
+    int row0, n;     /* the log's rows row0 .. row0 + n - 1 */
+} FnxGdnReplay;
+/* jobs: device array; a block per (value head < nv_max, job) */
+int fnx_gdn_replay(const FnxGdnReplay* jobs, int njobs, int nv_max, void* st);
 /* reference src/kernels.hpp:94-111 GdnLanes, gdn_core_lanes, gdn_core_segs: several sequences ("lanes") in one launch.
  * Device arrays give segment s's state, conv history (this layer's) and ctl; its rows are window rows row0[s] ..
  * row0[s] + T - 1 of qkvz, ab and yq, and its snapshots (snap, hsnap as fnx_gdn_core's) are written from window row
@@ -313,6 +332,10 @@ typedef struct FnxLayer {
     const float* router;
     FnxExperts gate_up, down;
     FnxQ8S sh_gate_up, sh_down;
+    /* DeltaNet: this sequence's replay log (fnx_gdn_log_floats), or null.  With a log the window runs fnx_gdn_core_log (snap
+     * is not used) and fnx_window_commit replays the kept rows into S, also when every row is kept; without one it runs
+     * fnx_gdn_core and the commit copies a checkpoint back. */
+    float* gdn_log;
 } FnxLayer;
 
 typedef struct FnxHead {
@@ -337,7 +360,7 @@ int fnx_window_stage(const FnxStackCfg* cfg, const FnxLayer* layers, const FnxHe
 void* fnx_window_buf(const FnxStackCfg* cfg, void* ws, int which);
 /* keep the first n of the last window's T rows (reference Engine::commit, src/engine_common.cu:525-568): per DeltaNet
  * layer S <- snap[n-1] and the written history half <- hsnap[n-1]; tag is the window's tag (its parity names the
- * half).  host_jobs: pinned host memory for nlayers * 2 FnxCopyJob, copied to FNX_BUF_COPY_JOBS */
+ * half).  host_jobs: pinned host memory for nlayers * (2 FnxCopyJob + 1 FnxGdnReplay), copied into the workspace */
 int fnx_window_commit(const FnxStackCfg* cfg, const FnxLayer* layers, void* ws, int T, int n, int tag, void* host_jobs, void* st);
 
 /* a second stream for work that does not depend on its neighbours (the shared expert beside the routed experts, the

@@ -17,6 +17,12 @@
 //               through distributed shared memory and each norms, gates and quantises its own columns.
 //
 // The state's loads are issued before the kernel ahead in the stream has finished (they depend on nothing in the window).
+//
+// Checkpoints or a log.  fnx_gdn_core keeps the reference's contract: the state after every row but the last is written
+// out (15 state-sized writes a window) and the rollback copies one back.  fnx_gdn_core_log writes no state at all: it
+// leaves the state as it was and logs each row's decay, key and delta (a few hundred KB), from which k_gdn_replay rebuilds
+// the state after the accepted rows with the window's own operations, bit for bit: 3 state-sized transfers a window
+// instead of 17 (+2 for a rollback).
 #include <cooperative_groups.h>
 
 #include "common.cuh"
@@ -46,7 +52,24 @@ struct GdnArgs {
     float* const* lhist;
     const int* const* lctl;
     const int* row0;
+    // the replay log (fnx_gdn_core_log): with it the rows kernel writes neither checkpoints nor the new state, only each
+    // row's delta; the keys and gates go into the log instead of the scratch, and fnx_gdn_replay rebuilds the state after
+    // the first n rows from the untouched state
+    float* log;
 };
+
+// the replay log of one layer and sequence: k [MAXT][nk][128] (permuted as the scratch's), gates [MAXT][nv][2], delta
+// [MAXT][nv][128]: what S_t = g_t S_(t-1) + k_t (x) delta_t needs, row by row
+struct GdnLog {
+    float *k, *g, *delta;
+};
+__host__ __device__ inline GdnLog gdn_log(float* p, int nk, int nv) {
+    GdnLog r;
+    r.k = p;
+    r.g = r.k + (size_t) FNX_MAXT * nk * HS;
+    r.delta = r.g + (size_t) FNX_MAXT * nv * 2;
+    return r;
+}
 
 // scratch (by window row): q [MAXT][nk][128] and k likewise, each head's 128 values permuted so that the 8 rows a thread of
 // k_gdn_rows needs are neighbours (element r = 32 part + 4 i + j at part * 32 + j * 8 + i); v [MAXT][nv][128]; gates
@@ -95,7 +118,11 @@ __global__ void __launch_bounds__(HS) k_gdn_prep(const GdnArgs g) {
         float* h = t + 1 < T ? g.hsnap + (size_t) (r0 + t) * 3 * ch : hist + (size_t) (parity ^ 1u) * 3 * ch;
         h[c] = in[1], h[(size_t) ch + c] = in[2], h[(size_t) 2 * ch + c] = in[3];
     }
-    const GdnScratch sc = gdn_scratch(g.scratch, nk, nv);
+    GdnScratch sc = gdn_scratch(g.scratch, nk, nv);
+    if (g.log) {
+        const GdnLog lg = gdn_log(g.log, nk, nv);
+        sc.k = lg.k, sc.g = lg.g;
+    }
     if (slot < 2 * nk) {   // L2 norm over the head: 32-element groups by warp trees, the four groups added in order
         __shared__ float gs[4];
         const float w = wsum(fmul(y, y));
@@ -146,7 +173,13 @@ __global__ void __cluster_dims__(GR_CL, 1, 1) __launch_bounds__(GR_THREADS, 1) k
     __shared__ float sqs[FNX_MAXT][2];   // per row: the square sums of this block's two 32-column quarters
     pdl_wait();
     pdl_go();
-    const GdnScratch sc = gdn_scratch(g.scratch, nk, nv);
+    GdnScratch sc = gdn_scratch(g.scratch, nk, nv);
+    float* dlog = nullptr;
+    if (g.log) {
+        const GdnLog lg = gdn_log(g.log, nk, nv);
+        sc.k = lg.k, sc.g = lg.g;
+        dlog = lg.delta + ((size_t) r0 * nv + lv) * HS + col;
+    }
     for (int e = tid; e < T * (HS / 4); e += GR_THREADS) {
         const int t = e / (HS / 4), c4 = e % (HS / 4);
         const size_t at = ((size_t) (r0 + t) * nk + kh) * HS + 4 * c4;
@@ -198,15 +231,20 @@ __global__ void __cluster_dims__(GR_CL, 1, 1) __launch_bounds__(GR_THREADS, 1) k
             }
             o[c] = fmul(tree(aj), scale);
         }
-        if ((lane & 15) == 0) *reinterpret_cast<float4*>(&osm[t][4 * cq]) = make_float4(o[0], o[1], o[2], o[3]);
-        if (t < T - 1) {
+        if ((lane & 15) == 0) {
+            *reinterpret_cast<float4*>(&osm[t][4 * cq]) = make_float4(o[0], o[1], o[2], o[3]);
+            if (dlog) *reinterpret_cast<float4*>(dlog + (size_t) t * nv * HS) = make_float4(delta[0], delta[1], delta[2], delta[3]);
+        }
+        if (!dlog && t < T - 1) {
             float* sp = snap + (size_t) t * nv * HS * HS;
 #pragma unroll
             for (int i = 0; i < 8; ++i) stcs4(sp + (size_t) 4 * i * HS, s[i][0], s[i][1], s[i][2], s[i][3]);
         }
     }
+    if (!dlog) {
 #pragma unroll
-    for (int i = 0; i < 8; ++i) *reinterpret_cast<float4*>(st + (size_t) 4 * i * HS) = make_float4(s[i][0], s[i][1], s[i][2], s[i][3]);
+        for (int i = 0; i < 8; ++i) *reinterpret_cast<float4*>(st + (size_t) 4 * i * HS) = make_float4(s[i][0], s[i][1], s[i][2], s[i][3]);
+    }
     __syncthreads();
     if (tid < 2 * T) {   // a 32-column quarter's square sum: eight columns by a tree (a warp's butterfly over them), the four eights in order
         const int t = tid >> 1, qq = tid & 1;
@@ -247,10 +285,47 @@ __global__ void __cluster_dims__(GR_CL, 1, 1) __launch_bounds__(GR_THREADS, 1) k
     cluster.sync();   // no block leaves while its square sums may still be read
 }
 
+// ---- the state after the first n rows of a logged window: S <- g_t S + k_t (x) delta_t for t < n, every element with the
+// very operations the rows kernel applied to it (fmul then ffma), so the bits are those of the window's own states.  Block
+// (value head, job): 256 threads, thread = a quad of columns and 16 rows of it.
+__global__ void __launch_bounds__(256) k_gdn_replay(const FnxGdnReplay* __restrict__ jobs) {
+    const FnxGdnReplay jb = jobs[blockIdx.y];
+    const int lv = blockIdx.x, tid = threadIdx.x, cq = tid & 31, rb = tid >> 5;
+    if (lv >= jb.nv || jb.n <= 0) return;
+    const int kh = jb.vmap[lv] & 255;
+    const GdnLog lg = gdn_log(const_cast<float*>(jb.log), jb.nk, jb.nv);
+    float* Sh = jb.S + (size_t) lv * HS * HS + 4 * cq;
+    float s[16][4];
+    int kidx[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        const int r = rb + 8 * i;
+        const float4 v = *reinterpret_cast<const float4*>(Sh + (size_t) r * HS);
+        s[i][0] = v.x, s[i][1] = v.y, s[i][2] = v.z, s[i][3] = v.w;
+        kidx[i] = (r >> 5) * 32 + (r & 3) * 8 + ((r >> 2) & 7);   // where the log keeps key row r
+    }
+    for (int t = 0; t < jb.n; ++t) {
+        const size_t row = (size_t) jb.row0 + t;
+        const float gv = lg.g[(row * jb.nv + lv) * 2];
+        const float4 d = *reinterpret_cast<const float4*>(lg.delta + (row * jb.nv + lv) * HS + 4 * cq);
+        const float* k = lg.k + (row * jb.nk + kh) * HS;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const float kx = k[kidx[i]];
+            s[i][0] = ffma(kx, d.x, fmul(gv, s[i][0]));
+            s[i][1] = ffma(kx, d.y, fmul(gv, s[i][1]));
+            s[i][2] = ffma(kx, d.z, fmul(gv, s[i][2]));
+            s[i][3] = ffma(kx, d.w, fmul(gv, s[i][3]));
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 16; ++i) *reinterpret_cast<float4*>(Sh + (size_t) (rb + 8 * i) * HS) = make_float4(s[i][0], s[i][1], s[i][2], s[i][3]);
+}
+
 static int gdn_launch(const GdnArgs& g, int nseg, cudaStream_t st, const char* what) {
     launch(5, k_gdn_prep, dim3(2 * g.nk + g.nv, g.T, nseg), HS, 0, st, g);
     if (launch_ok(what)) return 1;
-    launch(5, k_gdn_rows, dim3(g.nv * GR_CL, nseg), GR_THREADS, 0, st, g);
+    launch(8, k_gdn_rows, dim3(g.nv * GR_CL, nseg), GR_THREADS, 0, st, g);
     return launch_ok(what);
 }
 
@@ -271,8 +346,30 @@ int fnx_gdn_core(const float* qkvz, const float* ab, float* hist, const float* c
     FNX_REQUIRE(T == 1 || (snap && hsnap), "gdn_core: a window of %d rows needs snap and hsnap", T);
     FNX_REQUIRE(scratch && ((uintptr_t) scratch % 16) == 0 && ((uintptr_t) S % 16) == 0 && (!snap || ((uintptr_t) snap % 16) == 0),
                 "gdn_core: scratch, state and checkpoints must be 16-byte aligned");
-    GdnArgs g{qkvz, ab, hist, convw, dt, a, nw, S, (uint8_t*) yq, ctl, scratch, snap, hsnap, nk, nv, vmap, T, eps, y32, nullptr, nullptr, nullptr, nullptr};
+    GdnArgs g{qkvz, ab, hist, convw, dt, a, nw, S, (uint8_t*) yq, ctl, scratch, snap, hsnap, nk, nv, vmap, T, eps, y32, nullptr, nullptr, nullptr, nullptr, nullptr};
     return gdn_launch(g, 1, strm(st), "gdn_core");
+}
+
+size_t fnx_gdn_log_floats(int nk, int nv) { return (size_t) FNX_MAXT * ((size_t) nk * HS + (size_t) nv * 2 + (size_t) nv * HS); }
+
+int fnx_gdn_core_log(const float* qkvz, const float* ab, float* hist, const float* convw, const float* dt, const float* a, const float* nw,
+                     const float* S, void* yq, const int* ctl, float* scratch, float* log, float* hsnap, int nk, int nv, const int* vmap, int T, float eps,
+                     void* st) {
+    FNX_REQUIRE(T >= 1 && T <= FNX_MAXT, "gdn_core_log: T %d outside 1..%d", T, FNX_MAXT);
+    FNX_REQUIRE(nk >= 1 && nk <= 255 && nv >= 1 && nk <= nv, "gdn_core_log: %d key heads, %d value heads", nk, nv);
+    FNX_REQUIRE(T == 1 || hsnap, "gdn_core_log: a window of %d rows needs hsnap", T);
+    FNX_REQUIRE(scratch && log && ((uintptr_t) scratch % 16) == 0 && ((uintptr_t) log % 16) == 0 && ((uintptr_t) S % 16) == 0,
+                "gdn_core_log: scratch, log and state must be 16-byte aligned");
+    GdnArgs g{qkvz, ab, hist, convw, dt, a, nw, const_cast<float*>(S), (uint8_t*) yq, ctl, scratch, nullptr, hsnap, nk, nv, vmap, T, eps, nullptr,
+              nullptr, nullptr, nullptr, nullptr, log};
+    return gdn_launch(g, 1, strm(st), "gdn_core_log");
+}
+
+int fnx_gdn_replay(const FnxGdnReplay* jobs, int njobs, int nv_max, void* st) {
+    if (njobs <= 0) return 0;
+    FNX_REQUIRE(jobs && nv_max >= 1, "gdn_replay: no jobs");
+    launch(0, k_gdn_replay, dim3(nv_max, njobs), 256, 0, strm(st), jobs);
+    return launch_ok("gdn_replay");
 }
 
 int fnx_gdn_core_segs(const float* qkvz, const float* ab, const float* convw, const float* dt, const float* a, const float* nw, void* yq,
@@ -283,7 +380,7 @@ int fnx_gdn_core_segs(const float* qkvz, const float* ab, const float* convw, co
     FNX_REQUIRE(T == 1 || (gl->snap && gl->hsnap && gl->row0), "gdn_core_segs: segments of %d rows need row0, snap and hsnap", T);
     FNX_REQUIRE(scratch && ((uintptr_t) scratch % 16) == 0, "gdn_core_segs: scratch must be 16-byte aligned");
     GdnArgs g{qkvz, ab, nullptr, convw, dt, a, nw, nullptr, (uint8_t*) yq, nullptr, scratch, gl->snap, gl->hsnap, nk, nv, vmap, T, eps, nullptr,
-              gl->S, gl->hist, gl->ctl, gl->row0};
+              gl->S, gl->hist, gl->ctl, gl->row0, nullptr};
     return gdn_launch(g, nseg, strm(st), "gdn_core_segs");
 }
 

@@ -7,6 +7,8 @@
 // index" and no two elements compare equal.
 #include <cooperative_groups.h>
 
+#include <algorithm>
+
 #include "common.cuh"
 #include "exact_math.cuh"
 
@@ -21,7 +23,7 @@ __device__ __forceinline__ unsigned comp_index(unsigned long long c) { return 0x
 // One launch: grid (AM_SPLIT, T).  A block scans its stripe of row t with every thread keeping the largest composite it
 // has seen, the block's largest goes into keys[t] by one 64-bit atomic, and the block that arrives last at the row's
 // counter (keys[FNX_MAXT + t]) decodes the row's result and puts both words back to zero for the next call.
-constexpr int AM_THREADS = 512, AM_SPLIT = 8;
+constexpr int AM_THREADS = 512, AM_SPLIT = 64;
 
 __global__ void __launch_bounds__(AM_THREADS) k_argmax_rows(const float* __restrict__ logits, int rows, int v0, float* __restrict__ bv,
                                                            int* __restrict__ bi, unsigned long long* keys, unsigned* err) {
@@ -295,7 +297,8 @@ int fnx_argmax(const float* logits, int rows, int T, int v0, float* best_v, int*
                void* st) {
     FNX_REQUIRE(T >= 1 && T <= FNX_MAXT && rows >= 1, "argmax: T %d, %d logits a row", T, rows);
     FNX_REQUIRE(logits && best_v && best_i && keys && err, "argmax: a null buffer");
-    const int split = rows >= 4 * AM_THREADS * AM_SPLIT ? AM_SPLIT : 1;
+    // stripes of about 2048 logits (one round of four loads a thread), at most AM_SPLIT a row
+    const int split = std::max(1, std::min(AM_SPLIT, rows / (4 * AM_THREADS)));
     launch(0, k_argmax_rows, dim3(split, T), AM_THREADS, 0, strm(st), logits, rows, v0, best_v, best_i, keys, err);
     return launch_ok("argmax");
 }

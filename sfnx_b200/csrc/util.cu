@@ -26,7 +26,7 @@ bool pdl_on(int kind) {
     // scan, 7 f32 GEMV.  Measured on the 8-layer benchmark window (ms per window; none 2.52): dense alone 2.39, router
     // alone 2.43, gate|up alone 2.74 (its blocks take the registers of every multiprocessor while the router still runs
     // and push the shared expert off its overlap), classes 0, 1, 2, 4, 5 together 2.32.
-    static const unsigned mask = getenv("FNX_PDL_MASK") ? (unsigned) strtoul(getenv("FNX_PDL_MASK"), nullptr, 0) : 0x37u;
+    static const unsigned mask = getenv("FNX_PDL_MASK") ? (unsigned) strtoul(getenv("FNX_PDL_MASK"), nullptr, 0) : 0x17u;
     return !off && !g_pdl_hold && (mask >> kind & 1u);
 }
 void pdl_hold(bool hold) { g_pdl_hold = hold; }

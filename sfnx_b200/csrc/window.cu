@@ -68,7 +68,7 @@ struct Traced {
 // the workspace's buffers, as offsets from its base
 struct Ws {
     size_t x, bo, xn, xq, qkvz, ab, yq, qg, k, v, att, partials, att_scratch, rlogits, topi, topw, jobs_gu, jobs_dn, njobs, rscratch, gu,
-        hq, part, sh_gu, shq, sh, logits, keys, best_v, best_i, err, ctl, gdn_scratch, copy_jobs, total;
+        hq, part, sh_gu, shq, sh, logits, keys, best_v, best_i, err, ctl, gdn_scratch, copy_jobs, replay_jobs, total;
 };
 
 static Ws carve(const FnxStackCfg& c) {
@@ -116,6 +116,7 @@ static Ws carve(const FnxStackCfg& c) {
     w.ctl = take(16);
     w.gdn_scratch = take(fnx_gdn_scratch_floats(c.nv) * 4);
     w.copy_jobs = take((size_t) c.nlayers * 2 * FNX_MAXT * sizeof(FnxCopyJob));   // up to a lane a row
+    w.replay_jobs = take((size_t) c.nlayers * sizeof(FnxGdnReplay));
     w.total = o;
     return w;
 }
@@ -265,6 +266,9 @@ static int window_stage(const FnxStackCfg* cfg, const FnxLayer* layers, const Fn
             const FnxGdnLanes gl{lanes->S[sg.layer], lanes->hist[sg.layer], lanes->ctl, lanes->row0, L.snap, L.hsnap};
             TRK("gdn_core", fnx_gdn_core_segs((const float*) (b + w.qkvz), (const float*) (b + w.ab), L.conv, L.dt, L.a, L.ssm_norm, b + w.yq,
                                                  (float*) (b + w.gdn_scratch), c.nk, c.nv, L.vmap, &gl, lanes->nseg, lanes->rows, c.eps, st));
+        } else if (L.gdn_log) {   // no checkpoints: the commit replays the kept rows from the log
+            TRK("gdn_core", fnx_gdn_core_log((const float*) (b + w.qkvz), (const float*) (b + w.ab), L.hist, L.conv, L.dt, L.a, L.ssm_norm, L.S,
+                                                b + w.yq, ctl, (float*) (b + w.gdn_scratch), L.gdn_log, L.hsnap, c.nk, c.nv, L.vmap, T, c.eps, st));
         } else
             TRK("gdn_core", fnx_gdn_core((const float*) (b + w.qkvz), (const float*) (b + w.ab), L.hist, L.conv, L.dt, L.a, L.ssm_norm, L.S,
                                             b + w.yq, ctl, (float*) (b + w.gdn_scratch), L.snap, L.hsnap, c.nk, c.nv, L.vmap, T, c.eps, st, nullptr));
@@ -404,24 +408,34 @@ int fnx_window_commit_lanes(const FnxStackCfg* cfg, const FnxLayer* layers, void
 int fnx_window_commit(const FnxStackCfg* cfg, const FnxLayer* layers, void* ws, int T, int n, int tag, void* host_jobs, void* st) {
     TRY(check_cfg(cfg));
     FNX_REQUIRE(T >= 1 && T <= FNX_MAXT && n >= 1 && n <= T, "commit: %d of %d rows", n, T);
-    if (n == T) return 0;
     const FnxStackCfg& c = *cfg;
     const Ws w = carve(c);
+    FNX_REQUIRE(host_jobs, "commit: no host job table");
+    // the host table: nlayers * 2 copy jobs, then nlayers replay jobs
     FnxCopyJob* hj = (FnxCopyJob*) host_jobs;
-    FNX_REQUIRE(hj, "commit: no host job table");
+    FnxGdnReplay* hr = (FnxGdnReplay*) ((char*) host_jobs + (size_t) c.nlayers * 2 * sizeof(FnxCopyJob));
     const size_t ch = (size_t) (2 * c.nk + c.nv) * FNX_HS, state = (size_t) c.nv * FNX_HS * FNX_HS;
     const unsigned written = ((unsigned) tag & 1u) ^ 1u;   // the window read half (tag & 1) and wrote the other
-    int nj = 0;
+    int nj = 0, nr = 0;
     for (int l = 0; l < c.nlayers; ++l) {
         if (layers[l].kind != 0) continue;
-        hj[nj++] = FnxCopyJob{layers[l].S, layers[l].snap + (size_t) (n - 1) * state, state * 4};
-        hj[nj++] = FnxCopyJob{layers[l].hist + (size_t) written * 3 * ch, layers[l].hsnap + (size_t) (n - 1) * 3 * ch, 3 * ch * 4};
+        if (layers[l].gdn_log) hr[nr++] = FnxGdnReplay{layers[l].S, layers[l].gdn_log, layers[l].vmap, c.nk, c.nv, 0, n};   // also when every row is kept
+        else if (n < T) hj[nj++] = FnxCopyJob{layers[l].S, layers[l].snap + (size_t) (n - 1) * state, state * 4};
+        if (n < T) hj[nj++] = FnxCopyJob{layers[l].hist + (size_t) written * 3 * ch, layers[l].hsnap + (size_t) (n - 1) * 3 * ch, 3 * ch * 4};
     }
-    if (!nj) return 0;
-    FnxCopyJob* dj = (FnxCopyJob*) ((char*) ws + w.copy_jobs);
-    if (cudaMemcpyAsync(dj, hj, (size_t) nj * sizeof(FnxCopyJob), cudaMemcpyHostToDevice, strm(st)) != cudaSuccess)
-        return fail("commit: job table upload: %s", cudaGetErrorString(cudaGetLastError()));
-    return fnx_copy_many(dj, nj, st);
+    if (nj) {
+        FnxCopyJob* dj = (FnxCopyJob*) ((char*) ws + w.copy_jobs);
+        if (cudaMemcpyAsync(dj, hj, (size_t) nj * sizeof(FnxCopyJob), cudaMemcpyHostToDevice, strm(st)) != cudaSuccess)
+            return fail("commit: job table upload: %s", cudaGetErrorString(cudaGetLastError()));
+        TRY(fnx_copy_many(dj, nj, st));
+    }
+    if (nr) {
+        FnxGdnReplay* dr = (FnxGdnReplay*) ((char*) ws + w.replay_jobs);
+        if (cudaMemcpyAsync(dr, hr, (size_t) nr * sizeof(FnxGdnReplay), cudaMemcpyHostToDevice, strm(st)) != cudaSuccess)
+            return fail("commit: replay table upload: %s", cudaGetErrorString(cudaGetLastError()));
+        TRY(fnx_gdn_replay(dr, nr, c.nv, st));
+    }
+    return 0;
 }
 
 // the side stream and the two events the forks use (null stream: everything on the window's stream)

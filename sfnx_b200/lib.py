@@ -61,7 +61,7 @@ class Layer(C.Structure):
                 ("S", C.c_void_p), ("hist", C.c_void_p), ("snap", C.c_void_p), ("hsnap", C.c_void_p),
                 ("wq", Q8S), ("wk", Q8S), ("wv", Q8S), ("wo", Q8S), ("q_norm", C.c_void_p), ("k_norm", C.c_void_p),
                 ("kc", C.c_void_p), ("vc", C.c_void_p), ("pages", KvPages),
-                ("router", C.c_void_p), ("gate_up", Experts), ("down", Experts), ("sh_gate_up", Q8S), ("sh_down", Q8S)]
+                ("router", C.c_void_p), ("gate_up", Experts), ("down", Experts), ("sh_gate_up", Q8S), ("sh_down", Q8S), ("gdn_log", C.c_void_p)]
 
 
 class WindowLanes(C.Structure):
@@ -88,6 +88,10 @@ class Ring(C.Structure):
 
 class MoeRows(C.Structure):
     _fields_ = [("part", C.c_void_p), ("topw", C.c_void_p), ("sh", C.c_void_p), ("logits", C.c_void_p), ("nexp", C.c_int), ("topk", C.c_int)]
+
+
+class GdnReplay(C.Structure):
+    _fields_ = [("S", C.c_void_p), ("log", C.c_void_p), ("vmap", C.c_void_p), ("nk", C.c_int), ("nv", C.c_int), ("row0", C.c_int), ("n", C.c_int)]
 
 
 class CopyJob(C.Structure):
@@ -118,6 +122,8 @@ _SIGS = {
     "fnx_gdn_core_segs": [_p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _p, C.POINTER(GdnLanes), _i, _i, _f, _p],
     "fnx_gdn_core_lanes": [_p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _p, C.POINTER(GdnLanes), _i, _f, _p],
     "fnx_copy_many": [_p, _i, _p],
+    "fnx_gdn_core_log": [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _p, _i, _f, _p],
+    "fnx_gdn_replay": [_p, _i, _i, _p],
     "fnx_attn_prep_append": [_p, _p, _p, _p, _p, _p, _p, KvPages, _i, _i, _i, _p, _f, Rope, _i, _i, _i, _p],
     "fnx_attn_partial": [_p, _p, _p, KvPages, _p, _i, _i, _i, _p, _i, _i, _i, _p, _p],
     "fnx_attn_partial_exact": [_p, _p, _p, KvPages, _p, _i, _i, _i, _p, _i, _i, _i, _p, _p],
@@ -150,6 +156,7 @@ _OTHER = {
     "fnx_router_scratch_bytes": (_z, []),
     "fnx_moe_h_bytes": (_z, [_i, _i]),
     "fnx_gdn_scratch_floats": (_z, [_i]),
+    "fnx_gdn_log_floats": (_z, [_i, _i]),
     "fnx_attn_scratch_floats": (_z, [_i, _i, _i]),
     "fnx_kv_rows_per_card": (_i, [_i, _i]),
     "fnx_attn_splits": (_i, [_i]),

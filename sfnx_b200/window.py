@@ -26,8 +26,10 @@ class SyntheticStack:
     """Random-init weights and states of one GPU's slice, generated on the device from seeds: every GPU generates the
     same full tensor and keeps its slice, so the slices of N GPUs are one model."""
 
-    def __init__(self, shape, ncard=1, card=0, seed=0, device="cuda"):
-        self.shape, self.ncard, self.card, self.seed = shape, ncard, card, seed
+    def __init__(self, shape, ncard=1, card=0, seed=0, device="cuda", gdn_log=True):
+        """gdn_log: the DeltaNet layers keep a replay log instead of per-row checkpoints of the state (fnx_gdn_core_log);
+        False: checkpoints, which windows of several sequences (LaneSet) need."""
+        self.shape, self.ncard, self.card, self.seed, self.gdn_log = shape, ncard, card, seed, gdn_log
         self.dev = torch.device(device)
         self.keep = []
         self.named = {}   # (layer, name) -> tensors, for callers that need the values (tests, CPU baselines)
@@ -139,9 +141,14 @@ class SyntheticStack:
             Lr.vmap = self.named[(l, "vmap")].data_ptr()
             S = self._t(self._normal(l, "S", (s.nvh, HS, HS), 0.1)[self._idx(self.vheads)])
             hist = self._t(self._normal(l, "hist", (2, 3, ch_full), 1.0)[:, :, self._idx(rows[: (2 * self.nk + self.nv) * HS])])
-            snap = self._t(torch.zeros((L.MAXT - 1, self.nv, HS, HS), device=self.dev))
             hsnap = self._t(torch.zeros((L.MAXT, 3, (2 * self.nk + self.nv) * HS), device=self.dev))
-            Lr.S, Lr.hist, Lr.snap, Lr.hsnap = S.data_ptr(), hist.data_ptr(), snap.data_ptr(), hsnap.data_ptr()
+            Lr.S, Lr.hist, Lr.hsnap = S.data_ptr(), hist.data_ptr(), hsnap.data_ptr()
+            if self.gdn_log:
+                Lr.snap = None
+                Lr.gdn_log = self._t(torch.zeros(L.load().fnx_gdn_log_floats(self.nk, self.nv), device=self.dev)).data_ptr()
+            else:
+                Lr.snap = self._t(torch.zeros((L.MAXT - 1, self.nv, HS, HS), device=self.dev)).data_ptr()
+                Lr.gdn_log = None
             self.gdn_state.append((S, hist))
             self.named[(l, "S")], self.named[(l, "hist")] = S, hist
         else:
@@ -248,6 +255,8 @@ class SyntheticStack:
                 S = v._t(S0 * (1.0 + 0.05 * index))
                 hist = v._t(h0 * (1.0 - 0.03 * index))
                 Lr.S, Lr.hist = S.data_ptr(), hist.data_ptr()
+                if self.gdn_log:
+                    Lr.gdn_log = v._t(torch.zeros(L.load().fnx_gdn_log_floats(self.nk, self.nv), device=self.dev)).data_ptr()
                 v.gdn_state.append((S, hist))
                 v.named[(l, "S")], v.named[(l, "hist")] = S, hist
             else:
@@ -285,6 +294,7 @@ class LaneSet:
 
     def __init__(self, stack, nseg, rows, rpp=64):
         assert nseg * rows <= L.MAXT
+        assert not stack.gdn_log, "windows of several sequences keep checkpoints: build the stack with gdn_log=False"
         self.stack, self.nseg, self.rows, self.rpp = stack, nseg, rows, rpp
         dev, s, T = stack.dev, stack.shape, nseg * rows
         nl = len(s.kinds)
@@ -406,7 +416,7 @@ class WindowRunner:
         self.nstages = lib.fnx_window_plan(C.byref(cfg), stack.layers, after, 1024)
         assert 0 < self.nstages <= 1024, lib.fnx_last_error()
         self.after = list(after[: self.nstages])
-        self.job_bytes = len(s.kinds) * 2 * C.sizeof(L.CopyJob)
+        self.job_bytes = len(s.kinds) * (2 * C.sizeof(L.CopyJob) + C.sizeof(L.GdnReplay))
         self.h_jobs = torch.zeros(64 * self.job_bytes, dtype=torch.uint8).pin_memory()   # a ring of job tables
         self.commits = 0
         self.launches = 0
@@ -590,8 +600,9 @@ class WindowRunner:
         return list(out[:n]), n
 
     def commit(self, n, tag):
-        """Keep the first n rows of the last window: the DeltaNet layers' states and histories back to row n - 1."""
-        if n >= self.T:
+        """Keep the first n rows of the last window: the DeltaNet layers' states and histories as after row n - 1 (with a
+        replay log the states advance only here, also when every row is kept)."""
+        if n >= self.T and not self.stack.gdn_log:
             return
         slot = self.commits % 64   # the table is read by an asynchronous copy: a slot is reused only 64 commits later
         self.commits += 1

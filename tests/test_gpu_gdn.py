@@ -127,3 +127,37 @@ def test_gdn_one_row_per_lane():
         assert np.array_equal(got["yq"][s:s + 1], ref["yq"]), s
         assert np.array_equal(got["S"][s].view(np.uint32), ref["S"].view(np.uint32)), s
         assert np.array_equal(got["hist"][s], ref["hist"]), s
+
+
+def test_gdn_log_and_replay_equal_the_checkpoints():
+    """The window without checkpoints: fnx_gdn_core_log leaves the state as it was and gives the same output rows and conv
+    history as fnx_gdn_core; fnx_gdn_replay of the first n rows gives, bit for bit, the checkpoint after row n - 1 (n < T) and
+    the final state (n = T).  At the benchmark's head counts and at a small ragged shape."""
+    import torch
+
+    from sfnx_b200 import lib as L
+    from tests import gpu_util as G
+
+    for nk, nv, T, seed in ((16, 48, 16, 37), (2, 6, 5, 38)):
+        c = cases.gdn_case(T=T, nk=nk, nv=nv, seed=seed)
+        ref = cases.gdn_oracle(c)
+        t = {k: G.dev(c[k]) for k in ("qkvz", "ab", "hist", "convw", "dt", "a", "nw", "S", "vmap", "ctl")}
+        yq = G.zeros(T * (nv * 128 // 32) * 36, torch.uint8)
+        scratch = G.zeros(L.load().fnx_gdn_scratch_floats(nv))
+        log = G.zeros(L.load().fnx_gdn_log_floats(nk, nv))
+        hsnap = G.zeros((16, 3, c["ch"]))
+        L.call("fnx_gdn_core_log", t["qkvz"].data_ptr(), t["ab"].data_ptr(), t["hist"].data_ptr(), t["convw"].data_ptr(), t["dt"].data_ptr(),
+               t["a"].data_ptr(), t["nw"].data_ptr(), t["S"].data_ptr(), yq.data_ptr(), t["ctl"].data_ptr(), scratch.data_ptr(), log.data_ptr(),
+               hsnap.data_ptr(), nk, nv, t["vmap"].data_ptr(), T, c["eps"], L.stream())
+        G.sync()
+        assert np.array_equal(G.host(yq).reshape(T, -1), ref["yq"]), "q8_1 output"
+        assert np.array_equal(G.host(t["S"]), c["S"]), "the state is left as it was"
+        assert np.array_equal(G.host(t["hist"]), ref["hist"]) and np.array_equal(G.host(hsnap)[: T - 1], ref["hsnap"][: T - 1])
+        for n in range(1, T + 1):
+            dS = G.dev(c["S"])
+            job = L.GdnReplay(dS.data_ptr(), log.data_ptr(), t["vmap"].data_ptr(), nk, nv, 0, n)
+            dj = torch.frombuffer(bytearray(bytes(job)), dtype=torch.uint8).to(G.DEV)
+            L.call("fnx_gdn_replay", dj.data_ptr(), 1, nv, L.stream())
+            G.sync()
+            want = ref["S"] if n == T else ref["snap"][n - 1]
+            assert np.array_equal(G.host(dS).view(np.uint32), want.view(np.uint32)), (nk, nv, n)

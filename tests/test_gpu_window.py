@@ -239,7 +239,7 @@ def test_window_of_several_sequences_equals_each_alone(monkeypatch):
     monkeypatch.setenv("FNX_ATTN_EXACT", "1")   # the one-sequence windows in the order of sums the lanes' scan uses
     shape = StackShape(n=512, nexp=32, topk=4, ff=256, nkh=2, nvh=4, nq=4, nkv=2, hd=128, nrot=64, vocab=2048, kinds=(0, 1, 0, 1), ctx=300,
                        kv_slack=256)
-    stack = SyntheticStack(shape, seed=11, device="cuda:0")
+    stack = SyntheticStack(shape, seed=11, device="cuda:0", gdn_log=False)   # lanes keep checkpoints
     nseg, rows = 3, 4
     lanes = LaneSet(stack, nseg, rows)
     alone = WindowRunner(stack, rows, graph=False)
