@@ -420,6 +420,11 @@ int fnx_accept_greedy(const int* rows, const int* out, int T);
 void* fnx_rng_new(unsigned long long seed);
 void fnx_rng_free(void* rng);
 int fnx_accept_sampled(const int* rows, int T, const float* cand_v, const int* cand_i, const FnxSampling* s, void* rng, int* o);
+/* n-gram lookup drafts (reference src/session.hpp:48-51, src/session.cpp:377-394 lookup_drafts): ctx = the n tokens so far
+ * (host), lk = the most drafts wanted, d1 = the token the first draft must be (the draft layer's, or -1 for any),
+ * image_tok = the first image-cell id (the reference's Engine::IMAGE_TOK, 1 << 30).  Writes the drafts to out (room for lk)
+ * and returns their number (0: none); negative on bad arguments */
+int fnx_lookup_drafts(const int* ctx, int n, int lk, int d1, int image_tok, int* out);
 /* merges nslice per-GPU candidate lists [nslice][T][64] into the rows' 64 best (reference src/engine_common.cu:640-653) */
 int fnx_top_merge(const float* vs, const int* is, int nslice, int T, float* out_v, int* out_i);
 /* the partition rule (reference src/card_split.hpp:12-26): FF slice, value-head owner, key heads of a GPU */

@@ -372,6 +372,13 @@ def mt_unif(g):
     return lib().orc_mt_unif(C.byref(g))
 
 
+def lookup_drafts(ctx, lk, d1=-1, image_tok=1 << 30):
+    ctx = np.ascontiguousarray(ctx, np.int32)
+    out = np.zeros(max(lk, 1), np.int32)
+    n = lib().orc_lookup_drafts(P(ctx), len(ctx), lk, d1, image_tok, P(out))
+    return out[:n].copy()
+
+
 def accept_greedy(rows, out):
     rows = np.ascontiguousarray(rows, np.int32)
     out = np.ascontiguousarray(out, np.int32)

@@ -191,6 +191,32 @@ double orc_mt_unif(OrcMt* g) {
 
 /* greedy: rows[0] is the last committed token, rows[1..] the drafts, out[t] row t's argmax; n = 1 + the longest
  * prefix with rows[n] == out[n - 1] */
+/* n-gram lookup drafts (reference src/session.cpp:377-394).  Written as the definition reads: among the starts s < n - 3 of a
+ * trigram equal to the last one take the largest; it yields drafts only if position s + 3 exists before the end and holds d1
+ * (when d1 >= 0); the count is min(lk, max(3, m)) where m - 3 is how many tokens before both trigrams agree (capped so that
+ * m <= lk and the earlier run does not leave the context); image cells end the list. */
+int orc_lookup_drafts(const int* ctx, int n, int lk, int d1, int image_tok, int* out) {
+    if (lk == 0 || n <= 3) return 0;
+    const int n0 = n - 3;
+    int s = -1;
+    for (int c = 0; c < n0; ++c)
+        if (ctx[c] == ctx[n0] && ctx[c + 1] == ctx[n0 + 1] && ctx[c + 2] == ctx[n0 + 2]) s = c; /* the last one found is the latest */
+    if (s < 0) return 0;
+    if (!(s + 3 < n)) return 0;
+    if (d1 >= 0 && ctx[s + 3] != d1) return 0;
+    int back = 0;
+    while (3 + back < lk && back < s && ctx[s - 1 - back] == ctx[n0 - 1 - back]) ++back;
+    int k = 3 + back;
+    if (k < 3) k = 3;
+    if (k > lk) k = lk;
+    int cnt = 0;
+    for (int i = s + 3; i < n && i < s + 3 + k; ++i) {
+        if (ctx[i] >= image_tok) break;
+        out[cnt++] = ctx[i];
+    }
+    return cnt;
+}
+
 int orc_accept_greedy(const int* rows, const int* out, int T) {
     int n = 1;
     while (n < T && rows[n] == out[n - 1]) ++n;

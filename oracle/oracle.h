@@ -118,6 +118,7 @@ void orc_mt_seed(OrcMt* g, uint64_t seed);
 uint64_t orc_mt_next(OrcMt* g);
 double orc_mt_unif(OrcMt* g);
 int orc_accept_greedy(const int* rows, const int* out, int T);
+int orc_lookup_drafts(const int* ctx, int n, int lk, int d1, int image_tok, int* out);
 int orc_accept_sampled(const int* rows, int T, const float* cand_v, const int* cand_i, const OrcSampling* s, OrcMt* rng, int* o);
 void orc_ring_sum(const float* const* x, float* out, int nrank, int T, int row_len);
 

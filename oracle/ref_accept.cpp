@@ -92,6 +92,13 @@ int ref_accept_sampled(const int* rows, int T, const float* cand_v, const int* c
     return n;
 }
 
+// the reference's own lookup_drafts (src/session.cpp:377-394): returns the number of drafts written to out
+int ref_lookup_drafts(const int* ctx, int n, int lk, int d1, int* out) {
+    const std::vector<int> r = fnx::lookup_drafts(std::vector<int>(ctx, ctx + n), lk, d1);
+    for (size_t i = 0; i < r.size(); ++i) out[i] = r[i];
+    return (int) r.size();
+}
+
 // the unit uniforms std::mt19937_64(seed) gives through uniform_real_distribution<double>(0, 1)
 void ref_uniforms(unsigned long long seed, int n, double* u) {
     std::mt19937_64 rng(seed);

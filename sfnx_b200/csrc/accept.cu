@@ -123,6 +123,28 @@ int fnx_accept_sampled(const int* rows, int T, const float* cand_v, const int* c
     return n;
 }
 
+// n-gram lookup drafts (reference src/session.cpp:377-394, lookup_drafts; LOOKUP_N = LOOKUP_MIN = 3): the tokens that followed
+// the latest earlier occurrence of the context's last three tokens.  Only that latest occurrence is looked at; it offers
+// drafts if a token follows it and (d1 >= 0) that token is d1.  How many: the match is grown backwards from the trigram, up
+// to lk tokens, and k = min(lk, max(3, match length)) tokens are taken (fewer at the context's end); tokens from the first
+// image cell (>= image_tok) on are dropped.  Returns the number of drafts written to out (room for lk).
+int fnx_lookup_drafts(const int* ctx, int n, int lk, int d1, int image_tok, int* out) {
+    constexpr int NG = 3, KMIN = 3;
+    if (!ctx || !out || n < 0 || lk < 0) return -fnxk::fail("lookup_drafts: bad arguments (%d tokens, %d drafts)", n, lk);
+    if (lk == 0 || n <= NG) return 0;
+    const int tail = n - NG;   // where the context's last trigram starts
+    int found = -1;
+    for (int s = tail - 1; s >= 0 && found < 0; --s)
+        if (ctx[s] == ctx[tail] && ctx[s + 1] == ctx[tail + 1] && ctx[s + 2] == ctx[tail + 2]) found = s;
+    if (found < 0 || found + NG >= n || (d1 >= 0 && ctx[found + NG] != d1)) return 0;
+    int m = NG;   // tokens before the two trigrams that agree as well
+    while (m < lk && m - NG < found && ctx[found - 1 - (m - NG)] == ctx[tail - 1 - (m - NG)]) ++m;
+    const int k = std::min(lk, std::max(KMIN, m)), end = std::min(n, found + NG + k);
+    int cnt = 0;
+    for (int i = found + NG; i < end && ctx[i] < image_tok; ++i) out[cnt++] = ctx[i];
+    return cnt;
+}
+
 int fnx_top_merge(const float* vs, const int* is, int nslice, int T, float* out_v, int* out_i) {
     if (nslice < 1 || T < 1) return fnxk::fail("top_merge: %d slices, %d rows", nslice, T);
     std::vector<std::pair<float, int>> c((size_t) nslice * FNX_TOPK_N);

@@ -164,6 +164,7 @@ _OTHER = {
     "fnx_window_plan": (_i, [_p, _p, _p, _i]),
     "fnx_window_buf": (_p, [_p, _p, _i]),
     "fnx_accept_greedy": (_i, [_p, _p, _i]),
+    "fnx_lookup_drafts": (_i, [_p, _i, _i, _i, _i, _p]),
     "fnx_trace_begin": (_i, []),
     "fnx_trace_end": (_i, [_p, _p, _p, _i]),
     "fnx_window_kernel_count": (C.c_long, [_i]),

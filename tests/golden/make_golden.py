@@ -6,6 +6,8 @@ package are present; the fixtures then travel with the repository).
   accept.npz    candidate lists, sampling settings and seeds with the outputs of the reference's own make_dist / draw
                 (johnfink8/sfnx src/session.cpp, compiled unmodified into oracle/_ref/libref_accept.so) and of the
                 acceptance loop around them, plus the unit uniforms of std::mt19937_64
+  lookup.npz    token histories with draft budgets and required first drafts, and the n-gram lookup drafts the reference's
+                own lookup_drafts (src/session.cpp:377-394, the same object code) returns for them
 
 Usage: make -C oracle ref && python tests/golden/make_golden.py
 """
@@ -86,7 +88,37 @@ def accept_fixture():
                         toks=toks, dist_n=dist_n, dist_ids=dist_ids, dist_p=dist_p, unif_seed=np.uint64(424242), unif=u)
 
 
+def lookup_fixture():
+    """Contexts over small alphabets (so that trigrams repeat), with copied runs, image cells and contexts that end in the
+    middle of a repeat; for each a draft budget lk and a required first draft d1: the reference's own lookup_drafts."""
+    ref = C.CDLL(os.path.join(ROOT, "oracle", "_ref", "libref_accept.so"))
+    rng = np.random.default_rng(4242)
+    ncase, maxn = 400, 96
+    ctx = np.zeros((ncase, maxn), np.int32)
+    n = np.zeros(ncase, np.int32)
+    lk = np.zeros(ncase, np.int32)
+    d1 = np.zeros(ncase, np.int32)
+    cnt = np.zeros(ncase, np.int32)
+    out = np.zeros((ncase, 16), np.int32)
+    for c in range(ncase):
+        n[c] = rng.integers(0, maxn + 1)
+        seq = rng.integers(0, int(rng.choice([2, 3, 5, 50])), maxn).astype(np.int32)
+        if n[c] > 24 and rng.random() < 0.6:   # a copied run: the tail repeats an earlier stretch
+            L = int(rng.integers(4, 12))
+            src = int(rng.integers(0, n[c] - 2 * L))
+            seq[n[c] - L:n[c]] = seq[src:src + L]
+        if rng.random() < 0.2 and n[c] > 8:
+            seq[rng.integers(0, n[c])] = (1 << 30) + 5   # an image cell somewhere
+        ctx[c] = seq
+        lk[c] = rng.integers(0, 16)
+        d1[c] = -1 if rng.random() < 0.5 else rng.integers(0, 5)
+        cnt[c] = ref.ref_lookup_drafts(O.P(ctx[c]), int(n[c]), int(lk[c]), int(d1[c]), O.P(out[c]))
+    assert (cnt > 0).sum() > 60, "too few cases with drafts"
+    np.savez_compressed(os.path.join(OUT, "lookup.npz"), ctx=ctx, n=n, lk=lk, d1=d1, cnt=cnt, out=out)
+
+
 if __name__ == "__main__":
     dequant_fixture()
     accept_fixture()
+    lookup_fixture()
     print("wrote", sorted(f for f in os.listdir(OUT) if f.endswith(".npz")))
