@@ -113,6 +113,13 @@ int fnx_embed_rows(const uint16_t* table, const int* ids, float* x, int T, int n
 /* ---- dense projections */
 /* reference src/kernels.hpp:47 q8s_gemv (src/dense.cuh:24-160): out[t][r] = W[r] . y[t], T <= FNX_MAXT */
 int fnx_q8s_gemv(FnxQ8S w, int rows, int cols, const void* y, float* out, int out_stride, int T, void* st);
+/* The same product on the tcgen05 tensor cores (no counterpart in the reference): a 32-column block's integer dot of 128 weight
+ * rows against the window's rows is one tcgen05.mma kind::i8 into tensor memory, the blocks' terms fl(dw da) (float) isum are
+ * added in ascending block order - not the reference's order (16-column pieces on 32 interleaved lanes and a tree), so the
+ * result equals fnx_q8s_gemv's to fp32 rounding of the sum, not bit for bit.  Shapes: cols a multiple of 256 up to 3072, at
+ * least 64 tiles of 128 rows, planes 16-byte aligned; refused otherwise.  Capture-safe (the tensor maps are built on the host
+ * at enqueue time and passed by value).  The window uses it for the head, qkvz and wq|wk|wv unless FNX_EXACT=1. */
+int fnx_q8s_gemv_blocks(FnxQ8S w, int rows, int cols, const void* y, float* out, int out_stride, int T, void* st);
 /* reference src/kernels.hpp:365-368 q8s_gemv_segs: n (1..3) Q8_0 matrices of `cols` columns over the same q8_1 rows in one
  * launch; each output as fnx_q8s_gemv of that matrix alone gives it */
 int fnx_q8s_gemv_segs(const FnxQ8S* w, const int* rows, float* const* out, const int* out_stride, int n, int cols, const void* y, int T,

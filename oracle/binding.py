@@ -182,6 +182,14 @@ def q8s_gemv(wq, wd, yq, T):
     return out
 
 
+def q8s_gemv_blocks(wq, wd, yq, T):
+    """The dense product with its sums in block order (this library's tensor-core kernel's order, not the reference's)."""
+    rows, cols = wq.shape
+    out = np.zeros((T, rows), np.float32)
+    lib().orc_q8s_gemv_blocks(P(wq), P(wd), rows, cols, P(yq), P(out), rows, T)
+    return out
+
+
 def moe_gate_up_q8(wq, wd, jobs, njobs, xq, T, nout):
     nexp, nrows, n = wq.shape
     gu = np.zeros((nout, nrows), np.float32)

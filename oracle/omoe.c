@@ -212,6 +212,31 @@ void orc_q8s_gemv(const int8_t* wq, const o_half* wd, int rows, int cols, const 
     free(da);
 }
 
+/* The same product with its sums in block order: acc = fma(fl(dw_b da_b), (float) isum_b, acc) for the 32-column blocks b in
+ * ascending order, isum_b the block's exact integer dot.  This is NOT the reference's order of sums (its kernel adds
+ * half-block terms on 32 interleaved lanes and a tree, orc_q8s_row_dot above); it is the order of this library's tensor-core
+ * dense kernel (fnx_q8s_gemv_blocks), stated here so that the kernel can be checked bit for bit; against the reference's
+ * order the two agree to fp32 rounding of the sum. */
+void orc_q8s_gemv_blocks(const int8_t* wq, const o_half* wd, int rows, int cols, const uint8_t* yq, float* out, int out_stride, int T) {
+    int8_t* a = (int8_t*) malloc((size_t) T * cols);
+    float* da = (float*) malloc((size_t) T * (cols / 32) * 4);
+    orc_q8_1_unpack(yq, cols, T, a, da);
+    const int nb = cols / 32;
+#pragma omp parallel for
+    for (int r = 0; r < rows; ++r)
+        for (int t = 0; t < T; ++t) {
+            float acc = 0.f;
+            for (int b = 0; b < nb; ++b) {
+                int isum = 0;
+                for (int l = 0; l < 32; ++l) isum += (int) wq[(size_t) r * cols + b * 32 + l] * (int) a[(size_t) t * cols + b * 32 + l];
+                acc = fmaf(o_h2f(wd[(size_t) r * nb + b]) * da[(size_t) t * nb + b], (float) isum, acc);
+            }
+            out[(size_t) t * out_stride + r] = acc;
+        }
+    free(a);
+    free(da);
+}
+
 /* gate|up over split-Q8_0 experts (expert e: planes at wq + e sq, wd + e sd): the dense row dot per (job row, pair) */
 void orc_moe_gate_up_q8(const int8_t* wq, size_t sq, const o_half* wd, size_t sd, const OrcJob* jobs, int njobs,
                         const uint8_t* xq, int T, float* gu, int n, int nrows) {

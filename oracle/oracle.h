@@ -71,6 +71,7 @@ void orc_moe_gate_up_q4k(const uint8_t* A, size_t sa, const OrcJob* jobs, int nj
 float orc_q8s_row_dot(const int8_t* wq, const o_half* wd, const int8_t* a, const float* da, int cols);
 void orc_q8_1_unpack(const uint8_t* yq, int cols, int rows, int8_t* a, float* da);
 void orc_q8s_gemv(const int8_t* wq, const o_half* wd, int rows, int cols, const uint8_t* yq, float* out, int out_stride, int T);
+void orc_q8s_gemv_blocks(const int8_t* wq, const o_half* wd, int rows, int cols, const uint8_t* yq, float* out, int out_stride, int T);
 void orc_moe_gate_up_q8(const int8_t* wq, size_t sq, const o_half* wd, size_t sd, const OrcJob* jobs, int njobs,
                         const uint8_t* xq, int T, float* gu, int n, int nrows);
 void orc_swiglu_q8(const float* gu_row, int ffs, int8_t* hq, float* hd);

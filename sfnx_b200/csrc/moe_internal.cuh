@@ -12,6 +12,10 @@ namespace fnxk {
 int attn_umma_launch(const float* qg, const uint16_t* kc, const uint16_t* vc, FnxKvPages g, float* scratch, int card, int ncard, int T,
                      const int* pos0, int nq, int nkv, int nsplit, cudaStream_t st);
 
+// dense_umma.cu: the tcgen05 dense kernel (sums in block order) over 1..3 split-Q8_0 matrices; -1 when the shape is not its
+int q8s_umma_launch(const FnxQ8S* w, const int* rows, float* const* out, const int* out_stride, int nseg, int cols, const void* yq, int T, cudaStream_t st,
+                    const char* what);
+
 // where a kernel with bounded on-chip waits reports a wait that ran out (bit 8): the window's error word while a window
 // stage is being enqueued (fault_sink), else the library's own word, which fnx_device_fault() reads and clears
 unsigned* device_fault_word();

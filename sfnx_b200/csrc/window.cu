@@ -50,6 +50,22 @@ static thread_local FnxRing g_ring;
 static thread_local bool g_ring_set = false;
 static bool fused_boundaries(const FnxStackCfg& c) { return c.ncard == 1 || g_ring_set; }
 
+// FNX_EXACT=1: every kernel in the reference's order of sums (the window then equals the CPU statement of the reference bit
+// for bit); default: the attention scan and the large dense projections run on the tcgen05 tensor cores in orders of their
+// own (equal to fp32 rounding of the sums; the window is then held to the reference's KL bar).  FNX_ATTN_EXACT=1: the scan alone.
+static bool env_on(const char* name) {
+    const char* v = getenv(name);
+    return v && v[0] == '1';
+}
+// a dense projection of the window: the tensor-core kernel where the shape is its and exactness is not asked for
+static int dense(const FnxQ8S* ws, const int* rows, float* const* outs, int nseg, int cols, const void* xq, int T, void* st) {
+    if (!env_on("FNX_EXACT")) {
+        const int rc = q8s_umma_launch(ws, rows, outs, rows, nseg, cols, xq, T, strm(st), "window dense");
+        if (rc >= 0) return rc;
+    }
+    return fnx_q8s_gemv_segs(ws, rows, outs, rows, nseg, cols, xq, T, st);
+}
+
 struct Traced {
     int slot = -1;
     cudaStream_t st;
@@ -249,7 +265,12 @@ static int window_stage(const FnxStackCfg* cfg, const FnxLayer* layers, const Fn
         FNX_REQUIRE(head, "window: no head");
         TRK(begin_name, begin_half(head->norm, nullptr));
         float* logits = (float*) (b + w.logits);
-        TRK("head", fnx_q8s_gemv(head->out, c.vocab_rows, c.n, xq, logits, c.vocab_rows, T, st));
+        {
+            const FnxQ8S ws1[1] = {head->out};
+            const int rows1[1] = {c.vocab_rows};
+            float* const outs1[1] = {logits};
+            TRK("head", dense(ws1, rows1, outs1, 1, c.n, xq, T, st));
+        }
         TRK("argmax", fnx_argmax(logits, c.vocab_rows, T, c.vocab0, (float*) (b + w.best_v), (int*) (b + w.best_i),
                                     (unsigned long long*) (b + w.keys), (unsigned*) (b + w.err), st));
         return 0;
@@ -260,7 +281,12 @@ static int window_stage(const FnxStackCfg* cfg, const FnxLayer* layers, const Fn
         TRK(begin_name, begin_half(L.norm1, xn));
         const bool forked = side_fork(st);
         TRK("ab", fnx_gemv_f32(L.ab, xn, (float*) (b + w.ab), 2 * c.nv, c.n, T, forked ? (void*) g_side.st : st));
-        TRK("qkvz", fnx_q8s_gemv(L.qkvz, rows, c.n, xq, (float*) (b + w.qkvz), rows, T, st));
+        {
+            const FnxQ8S ws1[1] = {L.qkvz};
+            const int rows1[1] = {rows};
+            float* const outs1[1] = {(float*) (b + w.qkvz)};
+            TRK("qkvz", dense(ws1, rows1, outs1, 1, c.n, xq, T, st));
+        }
         if (forked) TRY(side_join(st));
         if (lanes) {   // every lane's rows chain through that lane's state, all lanes in one launch
             const FnxGdnLanes gl{lanes->S[sg.layer], lanes->hist[sg.layer], lanes->ctl, lanes->row0, L.snap, L.hsnap};
@@ -284,7 +310,7 @@ static int window_stage(const FnxStackCfg* cfg, const FnxLayer* layers, const Fn
             const FnxQ8S ws[3] = {L.wq, L.wk, L.wv};
             const int rows3[3] = {c.nq * c.hd * 2, c.nkv * c.hd, c.nkv * c.hd};
             float* const outs[3] = {qg, k, v};
-            TRK("wqkv", fnx_q8s_gemv_segs(ws, rows3, outs, rows3, 3, c.n, xq, T, st));
+            TRK("wqkv", dense(ws, rows3, outs, 3, c.n, xq, T, st));
         }
         const FnxRope rope{c.rope_base, c.nrot};
         float* mine = (float*) (b + w.partials) + (size_t) c.card * T * c.nq * (c.hd + 2);
@@ -307,8 +333,7 @@ static int window_stage(const FnxStackCfg* cfg, const FnxLayer* layers, const Fn
                                                         rope, c.nq, c.nkv, c.hd, st));
         // FNX_ATTN_EXACT=1: the scan in the reference's order of sums (bit-reproducible against the CPU statement, several
         // times slower); default: the one-pass tensor-core scan
-        const char* ex = getenv("FNX_ATTN_EXACT");
-        if (ex && ex[0] == '1')
+        if (env_on("FNX_EXACT") || env_on("FNX_ATTN_EXACT"))
             TRK("attn_partial", fnx_attn_partial_exact(qg, L.kc, L.vc, L.pages, mine, c.card, c.ncard, T, ctl, c.nq, c.nkv, c.hd,
                                                           (float*) (b + w.att_scratch), st));
         else

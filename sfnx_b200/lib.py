@@ -106,6 +106,7 @@ _SIGS = {
     "fnx_rms_norm_rows": [_p, _p, _p, _p, _p, _i, _i, _f, _p],
     "fnx_q8s_gemv": [Q8S, _i, _i, _p, _p, _i, _i, _p],
     "fnx_q8s_gemv_segs": [_p, _p, _p, _p, _i, _i, _p, _i, _p],
+    "fnx_q8s_gemv_blocks": [Q8S, _i, _i, _p, _p, _i, _i, _p],
     "fnx_gemv_f32": [_p, _p, _p, _i, _i, _i, _p],
     "fnx_router_route": [_p, _p, _p, _i, _i, _i, _i, _p, _p, _p, _p, _p, _p, _p],
     "fnx_moe_gate_up": [C.POINTER(Experts), _p, _p, _i, _p, _p, _p],

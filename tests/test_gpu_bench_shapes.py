@@ -156,19 +156,21 @@ def _windows(shape, stack, runner, orc, nwin, seed, exact):
 
 
 def test_window_benchmark_shapes_exact_attention_bit_exact(monkeypatch):
-    """Two layers of the benchmark's shapes with the attention scan in the reference's order of sums: logits of all
-    151 936 tokens, greedy tokens, accepted counts and rolled-back states equal the oracle's bit for bit."""
-    monkeypatch.setenv("FNX_ATTN_EXACT", "1")
+    """Two layers of the benchmark's shapes with every kernel in the reference's order of sums (FNX_EXACT=1: the exact
+    attention scan and the exact dense kernel): logits of all 151 936 tokens, greedy tokens, accepted counts and rolled-back
+    states equal the oracle's bit for bit."""
+    monkeypatch.setenv("FNX_EXACT", "1")
     shape, stack, runner, orc = _make(seed=21)
     _, _, total = _windows(shape, stack, runner, orc, nwin=3, seed=5, exact=True)
     assert 3 <= total <= 48
 
 
 def test_window_benchmark_shapes_tcgen05_attention_within_bar(monkeypatch):
-    """The same stack on the default path (head dimension 256: the tcgen05 scan, as in the benchmark): mean KL of the
-    logits against the oracle's within the reference's bar and the same top-1 on every row (a flip only where the
-    oracle's own two logits are within 2e-3)."""
+    """The same stack on the default path, as the benchmark runs it (the tcgen05 attention scan and the tcgen05 dense kernel
+    for the head, qkvz and wq|wk|wv): mean KL of the logits against the oracle's within the reference's bar and the same top-1
+    on every row (a flip only where the oracle's own two logits are within 2e-3)."""
     monkeypatch.delenv("FNX_ATTN_EXACT", raising=False)
+    monkeypatch.delenv("FNX_EXACT", raising=False)
     shape, stack, runner, orc = _make(seed=21)
     kls, flips, _ = _windows(shape, stack, runner, orc, nwin=3, seed=5, exact=False)
     assert np.mean(kls) <= KL_BAR, kls

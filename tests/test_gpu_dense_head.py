@@ -55,6 +55,32 @@ def test_q8s_gemv(rows, cols, T):
     assert np.array_equal(G.host(out).view(np.uint32), ref.view(np.uint32))
 
 
+@pytest.mark.parametrize("rows,cols,T", [(16384, 3072, 16), (8200, 1024, 5), (40000, 2560, 1), (9000, 256, 16)])
+def test_q8s_gemv_blocks_tensor_cores(rows, cols, T):
+    """The tcgen05 dense kernel: bit-equal to the oracle's statement of its order of sums (blocks in ascending order), equal
+    to the reference-order product to fp32 rounding of the sum, over ragged row counts (a last tile past the matrix), one
+    to sixteen window rows and several widths; no bounded wait ran out."""
+    from sfnx_b200 import lib as L
+    from tests import gpu_util as G
+
+    rng = np.random.default_rng(rows + T)
+    wq = rng.integers(-127, 128, size=(rows, cols), dtype=np.int8)
+    wd = (rng.random((rows, cols // 32), dtype=np.float32) * 2e-4 + 1e-4).astype(np.float16).view(np.uint16)
+    yq = cases.O.quantize_q8_1(rng.standard_normal((T, cols)).astype(np.float32))
+    want = cases.O.q8s_gemv_blocks(wq, wd, yq, T)
+    w, keep = G.q8s((wq, wd))
+    dy, out = G.dev(yq), G.zeros((T, rows))
+    for _ in range(2):   # twice: the barriers' phases start afresh with every launch
+        out.zero_()
+        L.call("fnx_q8s_gemv_blocks", w, rows, cols, dy.data_ptr(), out.data_ptr(), rows, T, L.stream())
+        G.sync()
+        assert L.load().fnx_device_fault() == 0
+        assert np.array_equal(G.host(out).view(np.uint32), want.view(np.uint32))
+    ref = cases.O.q8s_gemv(wq, wd, yq, T)
+    assert np.allclose(want, ref, rtol=0, atol=4e-6 * np.abs(ref).max())
+    assert L.load().fnx_q8s_gemv_blocks(w, 100, cols, dy.data_ptr(), out.data_ptr(), rows, T, L.stream()) != 0   # too few rows: refused
+
+
 def test_q8s_gemv_f32_pair(oracle):
     """The quantised projection and the small f32 one behind one call (the DeltaNet layer's qkvz and alpha|beta): each
     output as its own entry point gives it."""
