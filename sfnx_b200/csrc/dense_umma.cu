@@ -64,6 +64,34 @@ __device__ __forceinline__ void du_commit(unsigned long long* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(um_s32(bar)) : "memory");
 }
 
+// two f32 in a 64-bit register, each half rounded as its scalar operation would be (Blackwell's packed f32 pipe)
+typedef unsigned long long du_f32x2;
+__device__ __forceinline__ du_f32x2 du_pack(float lo, float hi) {
+    du_f32x2 r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ du_f32x2 du_packi(int lo, int hi) {
+    du_f32x2 r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi));
+    return r;
+}
+__device__ __forceinline__ du_f32x2 du_fma2(du_f32x2 a, du_f32x2 b, du_f32x2 c) {
+    du_f32x2 d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ du_f32x2 du_add2(du_f32x2 a, du_f32x2 b) {
+    du_f32x2 d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ du_f32x2 du_mul2(du_f32x2 a, du_f32x2 b) {
+    du_f32x2 d;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+
 struct DuTile {
     int seg, row0;
 };
@@ -156,7 +184,6 @@ __global__ void __launch_bounds__(DU_THREADS, 1) k_q8s_umma(const __grid_constan
                     const int s = c % DU_STAGES, slot = c % DU_SLOTS;
                     if (alive) alive = um_wait(&full_a[s], (unsigned) ((c / DU_STAGES) & 1), a.fault);
                     if (c >= DU_SLOTS && alive) alive = um_wait(&tm_empty[slot], (unsigned) ((c / DU_SLOTS - 1) & 1), a.fault);
-                    alive = __all_sync(0xffffffffu, alive);
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     if (lane == 0) {
                         const unsigned long long da = um_desc(a_s32 + s * DU_ABYTES), db = um_desc(b_s32 + kc * DU_BCHUNK);
@@ -176,13 +203,14 @@ __global__ void __launch_bounds__(DU_THREADS, 1) k_q8s_umma(const __grid_constan
                 if (alive) alive = um_wait(&dw_full[tp], (unsigned) ((nt / 2) & 1), a.fault);
                 alive = __all_sync(0xffffffffu, alive);
                 const uint16_t* dwr = dw_s + ((size_t) tp * DU_M + r_in) * nb;
-                float acc[4] = {0.f, 0.f, 0.f, 0.f};
-                uint4 dw8 = make_uint4(0, 0, 0, 0);
+                du_f32x2 acc01 = 0ull, acc23 = 0ull;   // window rows 4 g, + 1 and + 2, + 3 of this thread's weight row
+                const du_f32x2 unmagic = du_pack(-12582912.0f, -12582912.0f);
+                const float* dap = da_s + 4 * g;
+#pragma unroll 2
                 for (int kc = 0; kc < nkc; ++kc, ++c) {
                     const int slot = c % DU_SLOTS;
-                    if ((kc & 1) == 0) dw8 = *reinterpret_cast<const uint4*>(dwr + 4 * kc);   // the scales of this stage's and the next one's blocks
+                    const uint2 dwh = *reinterpret_cast<const uint2*>(dwr + 4 * kc);   // this stage's four block scales
                     if (alive) alive = um_wait(&tm_full[slot], (unsigned) ((c / DU_SLOTS) & 1), a.fault);
-                    alive = __all_sync(0xffffffffu, alive);
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     unsigned v[16];
                     const unsigned ta = tmem_base + ((unsigned) (32 * q) << 16) + (unsigned) (slot * 64 + 4 * g);
@@ -195,19 +223,22 @@ __global__ void __launch_bounds__(DU_THREADS, 1) k_q8s_umma(const __grid_constan
                     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                     __syncwarp();
                     if (lane == 0) du_arrive(&tm_empty[slot]);   // the group may be overwritten: its values are in registers
-                    const unsigned dww[2] = {(kc & 1) ? dw8.z : dw8.x, (kc & 1) ? dw8.w : dw8.y};
+                    const unsigned dww[2] = {dwh.x, dwh.y};
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
                         const float dw = h2f((uint16_t) (j & 1 ? dww[j >> 1] >> 16 : dww[j >> 1] & 0xffff));
-                        const float4 da4 = *reinterpret_cast<const float4*>(da_s + (size_t) (4 * kc + j) * 16 + 4 * g);
-                        const float dav[4] = {da4.x, da4.y, da4.z, da4.w};
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            const float f = fsub(__int_as_float((int) v[4 * j + i] + DU_MAGIC), 12582912.0f);   // (float) isum, exactly
-                            acc[i] = ffma(fmul(dw, dav[i]), f, acc[i]);
-                        }
+                        const du_f32x2 dw2 = du_pack(dw, dw);
+                        const ulonglong2 da4 = *reinterpret_cast<const ulonglong2*>(dap + (size_t) (4 * kc + j) * 16);
+                        // (float) isum exactly: the bits of 1.5 * 2^23 + isum, less 1.5 * 2^23; then acc = fma(fl(dw da), ., acc)
+                        const du_f32x2 f01 = du_add2(du_packi((int) v[4 * j] + DU_MAGIC, (int) v[4 * j + 1] + DU_MAGIC), unmagic);
+                        const du_f32x2 f23 = du_add2(du_packi((int) v[4 * j + 2] + DU_MAGIC, (int) v[4 * j + 3] + DU_MAGIC), unmagic);
+                        acc01 = du_fma2(du_mul2(dw2, da4.x), f01, acc01);
+                        acc23 = du_fma2(du_mul2(dw2, da4.y), f23, acc23);
                     }
                 }
+                float acc[4];
+                asm("mov.b64 {%0, %1}, %2;" : "=f"(acc[0]), "=f"(acc[1]) : "l"(acc01));
+                asm("mov.b64 {%0, %1}, %2;" : "=f"(acc[2]), "=f"(acc[3]) : "l"(acc23));
                 __syncwarp();
                 if (lane == 0) du_arrive(&dw_empty[tp]);
                 const int seg = t.seg, row = t.row0 + r_in;
