@@ -191,6 +191,17 @@ __global__ void __cluster_dims__(GR_CL, 1, 1) __launch_bounds__(GR_THREADS, 1) k
         *reinterpret_cast<float4*>(&vs[t][4 * c4]) = *reinterpret_cast<const float4*>(sc.v + ((size_t) (r0 + t) * nv + lv) * HS + half * GR_COLS + 4 * c4);
     }
     if (tid < 2 * T) gates[tid >> 1][tid & 1] = sc.g[((size_t) (r0 + (tid >> 1)) * nv + lv) * 2 + (tid & 1)];
+    // what the epilogue's (row, 32-column block) tasks of this warp need from global memory, asked for now: the gate
+    // inputs z and the norm weights would otherwise be a dependent load at the head of every task
+    const float* qkvz = g.qkvz + (size_t) r0 * row_stride;
+    constexpr int NTASK = 2 * FNX_MAXT / GR_WARPS;
+    float zpre[NTASK], nwpre[2];
+#pragma unroll
+    for (int k = 0; k < NTASK; ++k) {
+        const int task = warp + k * GR_WARPS, t = task >> 1, b = task & 1;
+        zpre[k] = t < T ? qkvz[(size_t) t * row_stride + ch + lv * HS + half * GR_COLS + 32 * b + lane] : 0.f;
+    }
+    nwpre[0] = g.nw[half * GR_COLS + lane], nwpre[1] = g.nw[half * GR_COLS + 32 + lane];
     __syncthreads();
     const float scale = ex_rsqrt((float) HS);
     float* snap = g.snap ? g.snap + ((size_t) r0 * nv + lv) * HS * HS + (st - (S + (size_t) lv * HS * HS)) : nullptr;
@@ -264,14 +275,15 @@ __global__ void __cluster_dims__(GR_CL, 1, 1) __launch_bounds__(GR_THREADS, 1) k
     cluster.sync();
     const float* sq0 = &cluster.map_shared_rank(&sqs[0][0], 0)[0];
     const float* sq1 = &cluster.map_shared_rank(&sqs[0][0], 1)[0];
-    const float* qkvz = g.qkvz + (size_t) r0 * row_stride;
-    for (int task = warp; task < 2 * T; task += GR_WARPS) {
-        const int t = task >> 1, b = task & 1;   // row, which of this block's two 32-column blocks
+#pragma unroll
+    for (int k = 0; k < NTASK; ++k) {
+        const int task = warp + k * GR_WARPS, t = task >> 1, b = task & 1;   // row, which of this block's two 32-column blocks
+        if (t >= T) break;
         const float ms = fdiv(fadd(fadd(fadd(sq0[2 * t], sq0[2 * t + 1]), sq1[2 * t]), sq1[2 * t + 1]), (float) HS);
         const int c = half * GR_COLS + 32 * b + lane;
         const float v = osm[t][32 * b + lane];
-        const float z = qkvz[(size_t) t * row_stride + ch + lv * HS + c];
-        const float xi = fdiv(fmul(fmul(v, ex_rsqrt(fadd(ms, g.eps))), g.nw[c]), fadd(1.0f, ex_expf(-z)));
+        const float z = zpre[k];
+        const float xi = fdiv(fmul(fmul(v, ex_rsqrt(fadd(ms, g.eps))), b ? nwpre[1] : nwpre[0]), fadd(1.0f, ex_expf(-z)));
         if (g.y32) g.y32[(size_t) (r0 + t) * nv * HS + lv * HS + c] = xi;
         const float amax = wmax(fabsf(xi)), sm = wsum(xi);
         const float d = fdiv(amax, 127.0f);
