@@ -110,6 +110,11 @@ int fnx_rms_norm_rows(float* x, const float* add, const float* w, float* y, void
  * on the host and uploads the rows, src/engine.cu:783-789; a B200 holds the table) */
 int fnx_embed_rows(const uint16_t* table, const int* ids, float* x, int T, int n, void* st);
 
+/* reference src/kernels.hpp:364 l2_prefetch (src/kernels.cu:2173-2193): asks for [p, p + bytes) to be brought into L2; returns
+ * at once (nothing waits for the data), capture-safe.  The window uses it on its side stream to bring a projection's weights
+ * in while a latency-bound kernel leaves HBM idle. */
+int fnx_l2_prefetch(const void* p, size_t bytes, void* st);
+
 /* ---- dense projections */
 /* reference src/kernels.hpp:47 q8s_gemv (src/dense.cuh:24-160): out[t][r] = W[r] . y[t], T <= FNX_MAXT */
 int fnx_q8s_gemv(FnxQ8S w, int rows, int cols, const void* y, float* out, int out_stride, int T, void* st);

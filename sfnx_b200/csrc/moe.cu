@@ -789,7 +789,9 @@ int fnx_moe_down(const FnxExperts* A, const FnxJob* jobs, const int* njobs, int 
 static __device__ __align__(256) unsigned char g_down_scratch[FNX_DOWN_NOALLOC_BYTES];
 
 // In host code the array's name is only a handle for the runtime, not a device address; the address comes from
-// cudaGetSymbolAddress, asked once per device with that device current.
+// cudaGetSymbolAddress, asked once per device with that device current.  The per-device cache below is read and written
+// without synchronisation: two host threads that meet here for the same device both ask the runtime and both store the
+// same address (the write is idempotent and pointer-sized), so the race is benign and costs at most one extra lookup.
 static void* down_scratch_ptr(void) {
     static void* ptr[64] = {};
     int dev = -1;

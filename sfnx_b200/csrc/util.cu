@@ -123,6 +123,18 @@ __global__ void __launch_bounds__(256) k_copy_many(const FnxCopyJob* __restrict_
     for (size_t i = (size_t) blockIdx.x * blockDim.x + threadIdx.x; i < n; i += step) d[i] = s[i];
 }
 
+// ---------------------------------------------------------------- L2 prefetch (reference src/kernels.cu:2173-2193)
+// The reference touches every 32-byte sector with a load; here the TMA unit's bulk prefetch brings 32 KB a thread into L2
+// (cp.async.bulk.prefetch.L2: no registers, no shared memory, nothing to wait for), so a launch of a few hundred threads
+// covers tens of MB and leaves the multiprocessors to the kernels it runs beside.
+constexpr unsigned PF_CHUNK = 32 * 1024;
+__global__ void k_l2_prefetch(const char* p, size_t bytes) {
+    const size_t at = ((size_t) blockIdx.x * blockDim.x + threadIdx.x) * PF_CHUNK;
+    if (at >= bytes) return;
+    const unsigned n = (unsigned) (bytes - at < PF_CHUNK ? bytes - at : PF_CHUNK) & ~15u;
+    if (n) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p + at), "r"(n) : "memory");
+}
+
 // ---------------------------------------------------------------- repacks
 __global__ void k_repack_q8_0(const uint8_t* __restrict__ blocks, int8_t* __restrict__ q, uint16_t* __restrict__ d, size_t nblocks) {
     const size_t b = (size_t) blockIdx.x * blockDim.x + threadIdx.x;
@@ -320,6 +332,16 @@ int fnx_rms_norm_rows(float* x, const float* add, const float* w, float* y, void
     if (rows <= 0) return 0;
     launch(0, k_rms_norm_rows, rows, 1024, 0, strm(st), x, add, w, y, (uint8_t*) q, n, eps);
     return launch_ok("rms_norm_rows");
+}
+
+int fnx_l2_prefetch(const void* p, size_t bytes, void* st) {
+    if (!p || !bytes) return 0;
+    const char* a = (const char*) (((uintptr_t) p + 15) & ~(uintptr_t) 15);   // the bulk prefetch wants 16-byte alignment
+    const size_t skip = (size_t) (a - (const char*) p);
+    if (bytes <= skip + 16) return 0;
+    const size_t n = bytes - skip, chunks = (n + PF_CHUNK - 1) / PF_CHUNK;
+    k_l2_prefetch<<<(unsigned) ((chunks + 63) / 64), 64, 0, strm(st)>>>(a, n);
+    return launch_ok("l2_prefetch");
 }
 
 int fnx_copy_many(const FnxCopyJob* jobs, int n, void* st) {

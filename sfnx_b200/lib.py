@@ -123,6 +123,7 @@ _SIGS = {
     "fnx_gdn_core_segs": [_p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _p, C.POINTER(GdnLanes), _i, _i, _f, _p],
     "fnx_gdn_core_lanes": [_p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _p, C.POINTER(GdnLanes), _i, _f, _p],
     "fnx_copy_many": [_p, _i, _p],
+    "fnx_l2_prefetch": [_p, _z, _p],
     "fnx_gdn_core_log": [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _p, _i, _f, _p],
     "fnx_gdn_replay": [_p, _i, _i, _p],
     "fnx_attn_prep_append": [_p, _p, _p, _p, _p, _p, _p, KvPages, _i, _i, _i, _p, _f, Rope, _i, _i, _i, _p],

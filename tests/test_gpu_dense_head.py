@@ -160,3 +160,18 @@ def test_argmax_and_top64(oracle):
     L.call("fnx_argmax", dl.data_ptr(), 4096, 2, 0, bv.data_ptr(), bi.data_ptr(), keys.data_ptr(), err.data_ptr(), L.stream())
     G.sync()
     assert int(G.host(err)[0]) == 16
+
+
+@pytest.mark.gpu
+def test_l2_prefetch_changes_nothing():
+    """fnx_l2_prefetch (reference src/kernels.hpp:364 l2_prefetch) is a hint: any range, aligned or not, leaves the bytes as
+    they were and raises no error; an empty range is accepted."""
+    import torch
+    from sfnx_b200 import lib
+    x = torch.randint(0, 255, (5 * 1024 * 1024 + 77,), dtype=torch.uint8, device="cuda")
+    ref = x.clone()
+    st = torch.cuda.current_stream().cuda_stream
+    for off, n in [(0, x.numel()), (3, 100), (16, 32768), (5, 1 << 20), (0, 0)]:
+        lib.call("fnx_l2_prefetch", x.data_ptr() + off, n, st)
+    torch.cuda.synchronize()
+    assert torch.equal(x, ref)
