@@ -6,14 +6,22 @@
 #include "common.cuh"
 #include "exact_math.cuh"
 #include "moe_internal.cuh"
+#include "umma.cuh"
 
 namespace fnxk {
 
 // ================================================================ router (reference src/moe.cuh:73-202)
-// logits: two warps per row (column halves); lane l accumulates the float4 chunks i * 32 + l in ascending i, each chunk
-// ((wx bx + wy by) + wz bz) + ww bw with fused steps; xor-tree; half0 + half1.  The grid's last block then picks the
+// logits: a row's columns in two halves, a warp each; lane l accumulates the float4 chunks i * 32 + l in ascending i, each
+// chunk ((wx bx + wy by) + wz bz) + ww bw with fused steps; xor-tree; half0 + half1.  The grid's last block then picks the
 // top-k per row and builds the jobs.
-constexpr int RR_THREADS = 256, RR_ROWS = RR_THREADS / 64, RR_TG = 4;   // rows a block; rows of x taken together
+//
+// A block takes four rows of W.  A warp holds one column half of two of them in registers and walks rows of x in shared
+// memory once for both; the block's two sets of four warps share the window's rows between them in groups of four
+// (a logit's sum is over one row of x: which warp takes which group changes no value).  x arrives by bulk copies (the
+// TMA unit's untiled copy: one instruction per group, any number of bytes in flight), a group an mbarrier, so the sums
+// over the first group run while the later ones are in flight; every block asks for the groups in an order of its own
+// (starting with group blockIdx mod groups) so that the blocks do not all pull on the same lines of the L2 at once.
+constexpr int RR_THREADS = 256, RR_ROWS = 4, RR_TG = 4;   // rows of W a block; rows of x taken together
 
 struct RouterArgs {
     const float* W;
@@ -25,6 +33,7 @@ struct RouterArgs {
     FnxJob *gu, *dn;
     int* njobs;
     unsigned* counter;
+    unsigned* fault;
 };
 
 __device__ __forceinline__ float dot4(const float4& w, const float4& b) {
@@ -36,77 +45,85 @@ __device__ __forceinline__ float dot4(const float4& w, const float4& b) {
 
 __device__ void route_tail(const RouterArgs& a);
 
-__global__ void __launch_bounds__(RR_THREADS) k_router_route(const RouterArgs a, int x_in_smem) {
-    const int e = threadIdx.x, warp = e >> 5, lane = e & 31, rw = warp >> 1, half = warp & 1;
+template <bool SMEM>
+__global__ void __launch_bounds__(RR_THREADS) k_router_route(const RouterArgs a) {
+    const int e = threadIdx.x, warp = e >> 5, lane = e & 31, set = warp >> 2, pair = (warp >> 1) & 1, half = warp & 1;
     const int L = a.nexp + 1, nc = a.n / 256;   // float4 chunks per lane
-    extern __shared__ __align__(16) float xs_sm[];   // the window's rows of x, read once per block (when they fit)
-    __shared__ float rsum[FNX_MAXT][RR_THREADS / 32];
+    extern __shared__ __align__(128) float xs_sm[];   // the window's rows of x, read once per block (when they fit)
+    __shared__ float rsum[FNX_MAXT][RR_ROWS][2];
+    __shared__ __align__(8) unsigned long long xbar[(FNX_MAXT + RR_TG - 1) / RR_TG];
+    const int ngroups = (a.T + RR_TG - 1) / RR_TG, g_first = blockIdx.x % ngroups;
+    if (SMEM && e == 0) {
+        for (int g = 0; g < ngroups; ++g) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(um_s32(&xbar[g])));
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
     // the first rows' weights are asked for before the kernel ahead in the stream has finished (they do not depend on it)
     const int first0 = blockIdx.x * RR_ROWS;
-    float4 wv[16];   // a row half's weights held in registers (up to 16 float4 a lane: n <= 4096)
-    if (first0 + rw < L) {
-        const float4* w4 = reinterpret_cast<const float4*>(a.W + (size_t) (first0 + rw) * a.n) + half * nc * 32;
+    float4 wv[2][16];   // the column half of two rows held in registers (up to 16 float4 a lane and row: n <= 4096)
+    auto fetch = [&](int row0) {
 #pragma unroll
-        for (int i = 0; i < 16; ++i)
-            if (i < nc) wv[i] = __ldg(w4 + i * 32 + lane);
-    }
-    pdl_wait();
-    pdl_go();
-    const float* xs = a.x;
-    if (x_in_smem) {   // asynchronous 16-byte copies: all of a thread's pieces in flight at once, beside the first weights
-        const int n4 = a.T * a.n / 4;
-        for (int i = e; i < n4; i += RR_THREADS)
-            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((unsigned) __cvta_generic_to_shared(xs_sm + 4 * (size_t) i)),
-                         "l"(a.x + 4 * (size_t) i));
-        asm volatile("cp.async.commit_group;");
-        xs = xs_sm;
-    }
-    bool staged = !x_in_smem;
-    // a block takes rows b, b + grid, ... four at a time, two warps a row (column halves)
-    for (int row0 = blockIdx.x * RR_ROWS; row0 < L; row0 += gridDim.x * RR_ROWS) {
-        const int row = row0 + rw;
-        // the rows of x four at a time so that their loads and sums overlap; each logit's summation order is unchanged
-        if (row < L && row0 != first0) {
+        for (int r = 0; r < 2; ++r) {
+            const int row = min(row0 + 2 * pair + r, L - 1);   // past the last row: the last row again, never written
             const float4* w4 = reinterpret_cast<const float4*>(a.W + (size_t) row * a.n) + half * nc * 32;
 #pragma unroll
             for (int i = 0; i < 16; ++i)
-                if (i < nc) wv[i] = __ldg(w4 + i * 32 + lane);
+                if (i < nc) wv[r][i] = __ldg(w4 + i * 32 + lane);
         }
-        if (!staged) {   // block-uniform: the rows of x have landed
-            asm volatile("cp.async.wait_group 0;" ::: "memory");
-            __syncthreads();
-            staged = true;
+    };
+    if (first0 < L) fetch(first0);
+    if (SMEM) __syncthreads();   // the mbarriers are set up
+    pdl_wait();
+    pdl_go();
+    if (SMEM && e == 0 && first0 < L) {
+        for (int gg = 0; gg < ngroups; ++gg) {
+            const int g = (gg + g_first) % ngroups, t0 = g * RR_TG;
+            const unsigned bytes = (unsigned) (min(a.T, t0 + RR_TG) - t0) * a.n * 4u;
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(um_s32(&xbar[g])), "r"(bytes) : "memory");
+            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                             um_s32(xs_sm + (size_t) t0 * a.n)),
+                         "l"(a.x + (size_t) t0 * a.n), "r"(bytes), "r"(um_s32(&xbar[g]))
+                         : "memory");
         }
-        if (row < L) {
-            for (int t = 0; t < a.T; t += RR_TG) {
-                float s[RR_TG];
-                const float4* x4[RR_TG];
+    }
+    for (int row0 = first0; row0 < L; row0 += gridDim.x * RR_ROWS) {
+        if (row0 != first0) fetch(row0);
+        for (int gg = set; gg < ngroups; gg += 2) {
+            const int t = ((gg + g_first) % ngroups) * RR_TG;
+            if (SMEM) um_wait(&xbar[t / RR_TG], 0, a.fault);   // this group's rows of x have landed (bounded)
+            float s[2][RR_TG];
+            const float4* x4[RR_TG];
 #pragma unroll
-                for (int k = 0; k < RR_TG; ++k) {
-                    s[k] = 0.f;
-                    x4[k] = reinterpret_cast<const float4*>(xs + (size_t) min(t + k, a.T - 1) * a.n) + half * nc * 32;
-                }
-#pragma unroll
-                for (int i = 0; i < 16; ++i)
-                    if (i < nc) {
-#pragma unroll
-                        for (int k = 0; k < RR_TG; ++k) s[k] = fadd(s[k], dot4(wv[i], x4[k][i * 32 + lane]));
-                    }
-#pragma unroll
-                for (int k = 0; k < RR_TG; ++k) {
-                    const float v = wsum(s[k]);
-                    if (lane == 0 && t + k < a.T) rsum[t + k][warp] = v;
-                }
+            for (int k = 0; k < RR_TG; ++k) {
+                s[0][k] = s[1][k] = 0.f;
+                const size_t at = (size_t) min(t + k, a.T - 1) * a.n;
+                x4[k] = reinterpret_cast<const float4*>(SMEM ? xs_sm + at : a.x + at) + half * nc * 32;
             }
+#pragma unroll
+            for (int i = 0; i < 16; ++i)
+                if (i < nc) {
+#pragma unroll
+                    for (int k = 0; k < RR_TG; ++k) {
+                        const float4 xv = x4[k][i * 32 + lane];
+                        s[0][k] = fadd(s[0][k], dot4(wv[0][i], xv));
+                        s[1][k] = fadd(s[1][k], dot4(wv[1][i], xv));
+                    }
+                }
+#pragma unroll
+            for (int r = 0; r < 2; ++r)
+#pragma unroll
+                for (int k = 0; k < RR_TG; ++k) {
+                    const float v = wsum(s[r][k]);
+                    if (lane == 0 && t + k < a.T) rsum[t + k][2 * pair + r][half] = v;
+                }
         }
         __syncthreads();
         for (int q = e; q < a.T * RR_ROWS; q += RR_THREADS) {
             const int t = q / RR_ROWS, r = q % RR_ROWS, lrow = row0 + r;
-            if (lrow < L) a.logits[(size_t) t * L + lrow] = fadd(rsum[t][2 * r], rsum[t][2 * r + 1]);
+            if (lrow < L) a.logits[(size_t) t * L + lrow] = fadd(rsum[t][r][0], rsum[t][r][1]);
         }
         __syncthreads();
     }
-    if (!staged) asm volatile("cp.async.wait_group 0;" ::: "memory");   // a block without rows: nothing left in flight at exit
+    // every group was waited for by one of the warp sets before the barrier above: no copy is in flight at exit
     __shared__ bool last;
     __threadfence();
     __syncthreads();
@@ -138,40 +155,146 @@ __device__ void route_tail(const RouterArgs& a) {
     __shared__ unsigned rowmask[MAXE];
     __shared__ int firstpair[MAXE];
     __shared__ unsigned firstmask[PW];
+    __shared__ unsigned candk[NW][2][32];   // a warp's candidates for its two rows: keys, experts; then its picks in order
+    __shared__ int candi[NW][2][32];
+    __shared__ unsigned selk[NW][2][16];
+    __shared__ int seli[NW][2][16];
     if (e < PW) firstmask[e] = 0u;
     for (int i = e; i < a.nexp; i += RR_THREADS) rowmask[i] = 0u, firstpair[i] = P;
-    for (int t = warp; t < a.T; t += NW) {
-        unsigned key[16];
+    // a warp takes its rows two at a time (rows t and t + NW), the two picks' instructions interleaved: each is a chain
+    // of dependent warp-wide steps, and two warps a scheduler do not hide their latency
+    for (int tb = warp; tb < a.T; tb += 2 * NW) {
+        const int nu = tb + NW < a.T ? 2 : 1;
+        unsigned key[2][16];
 #pragma unroll
-        for (int i = 0; i < 16; ++i) key[i] = i < per ? logit_key(__ldcg(a.logits + (size_t) t * L + lane + 32 * i)) : 0u;
-        float mine = 0.f, top0 = 0.f;   // lane k keeps pick k's logit
-        for (int k = 0; k < a.topk; ++k) {
-            unsigned m = key[0];
+        for (int u = 0; u < 2; ++u)
 #pragma unroll
-            for (int i = 1; i < 16; ++i) m = max(m, key[i]);
-            const unsigned M = __reduce_max_sync(0xffffffffu, m);
-            unsigned hit = 0u;
+            for (int i = 0; i < 16; ++i)
+                key[u][i] = (i < per && u < nu) ? logit_key(__ldcg(a.logits + (size_t) (tb + u * NW) * L + lane + 32 * i)) : 0u;
+        float mine[2] = {0.f, 0.f}, top0[2] = {0.f, 0.f};   // lane k keeps pick k's logit
+        // The k-th largest of the 32 lanes' maxima is a lower bound of the k-th largest key (k keys reach it), so the
+        // picks are among the keys that reach it: a handful, ranked by counting (a greater key, or an equal key of a
+        // lower expert, comes first).  Many equal keys can make the candidates more than a warp holds: then pick by pick.
+        unsigned lm[2], hitm[2] = {0u, 0u};
+        int rk[2] = {0, 0}, cnt[2], pre[2], total[2];
 #pragma unroll
-            for (int i = 0; i < 16; ++i) hit |= (unsigned) (key[i] == M) << i;
-            const unsigned cand = hit ? (unsigned) (lane + 32 * (__ffs(hit) - 1)) : 0xffffffffu;
-            const int bi = (int) __reduce_min_sync(0xffffffffu, cand);
-            if ((bi & 31) == lane) {
+        for (int u = 0; u < 2; ++u) {
+            lm[u] = key[u][0];
+#pragma unroll
+            for (int i = 1; i < 16; ++i) lm[u] = max(lm[u], key[u][i]);
+        }
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+                const unsigned o = __shfl_sync(0xffffffffu, lm[u], j);
+                rk[u] += (o > lm[u]) | ((o == lm[u]) & (j < lane));
+            }
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            const unsigned bound = __reduce_max_sync(0xffffffffu, rk[u] == a.topk - 1 ? lm[u] : 0u);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) hitm[u] |= (unsigned) (i < per && u < nu && key[u][i] >= bound) << i;
+            cnt[u] = pre[u] = __popc(hitm[u]);   // pre: inclusive scan over the lanes
+        }
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1)
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+                const int o = __shfl_up_sync(0xffffffffu, pre[u], d);
+                if (lane >= d) pre[u] += o;
+            }
+#pragma unroll
+        for (int u = 0; u < 2; ++u) total[u] = __shfl_sync(0xffffffffu, pre[u], 31);
+        const bool fast = a.topk <= 32 && total[0] <= 32 && total[1] <= 32;   // warp-uniform
+        if (fast) {
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+                int o = pre[u] - cnt[u];
 #pragma unroll
                 for (int i = 0; i < 16; ++i)
-                    if (i == (bi >> 5)) key[i] = 0u;
+                    if ((hitm[u] >> i) & 1u) {
+                        candk[warp][u][o] = key[u][i];
+                        candi[warp][u][o] = lane + 32 * i;
+                        ++o;
+                    }
             }
-            const float bv = key_logit(M);
-            if (k == 0) top0 = bv;
-            if (lane == k) {
-                mine = bv;
-                a.topi[t * a.topk + k] = bi;
-                ex[t * a.topk + k] = bi;
+            __syncwarp();
+            unsigned myk[2];
+            int myi[2], r[2] = {0, 0};
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+                myk[u] = lane < total[u] ? candk[warp][u][lane] : 0u;
+                myi[u] = lane < total[u] ? candi[warp][u][lane] : 0x7fffffff;
+            }
+            const int tmax = max(total[0], total[1]);
+            for (int j = 0; j < tmax; ++j)
+#pragma unroll
+                for (int u = 0; u < 2; ++u) {
+                    const unsigned ok = j < total[u] ? candk[warp][u][j] : 0u;
+                    const int oi = j < total[u] ? candi[warp][u][j] : 0x7fffffff;
+                    r[u] += (ok > myk[u]) | ((ok == myk[u]) & (oi < myi[u]));
+                }
+#pragma unroll
+            for (int u = 0; u < 2; ++u)
+                if (lane < total[u] && r[u] < a.topk) selk[warp][u][r[u]] = myk[u], seli[warp][u][r[u]] = myi[u];
+            __syncwarp();
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+                if (u >= nu) break;
+                const int t = tb + u * NW;
+                top0[u] = key_logit(selk[warp][u][0]);
+                if (lane < a.topk) {
+                    const int bi = seli[warp][u][lane];
+                    mine[u] = key_logit(selk[warp][u][lane]);
+                    a.topi[t * a.topk + lane] = bi;
+                    ex[t * a.topk + lane] = bi;
+                }
+            }
+            __syncwarp();
+        } else {
+            for (int u = 0; u < nu; ++u) {
+                const int t = tb + u * NW;
+                unsigned kk[16];
+#pragma unroll
+                for (int i = 0; i < 16; ++i) kk[i] = u ? key[1][i] : key[0][i];
+                float mn = 0.f, tp = 0.f;
+                for (int k = 0; k < a.topk; ++k) {
+                    unsigned m = kk[0];
+#pragma unroll
+                    for (int i = 1; i < 16; ++i) m = max(m, kk[i]);
+                    const unsigned M = __reduce_max_sync(0xffffffffu, m);
+                    unsigned hit = 0u;
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) hit |= (unsigned) (kk[i] == M) << i;
+                    const unsigned cand = hit ? (unsigned) (lane + 32 * (__ffs(hit) - 1)) : 0xffffffffu;
+                    const int bi = (int) __reduce_min_sync(0xffffffffu, cand);
+                    if ((bi & 31) == lane) {
+#pragma unroll
+                        for (int i = 0; i < 16; ++i)
+                            if (i == (bi >> 5)) kk[i] = 0u;
+                    }
+                    const float bv = key_logit(M);
+                    if (k == 0) tp = bv;
+                    if (lane == k) {
+                        mn = bv;
+                        a.topi[t * a.topk + k] = bi;
+                        ex[t * a.topk + k] = bi;
+                    }
+                }
+                if (u) mine[1] = mn, top0[1] = tp;
+                else mine[0] = mn, top0[0] = tp;
             }
         }
-        const float ek = ex_expf(fsub(mine, top0));
-        float z = 0.f;
-        for (int k = 0; k < a.topk; ++k) z = fadd(z, __shfl_sync(0xffffffffu, ek, k));
-        if (lane < a.topk) a.topw[t * a.topk + lane] = fdiv(ek, z);
+        float ek[2], z[2] = {0.f, 0.f};
+#pragma unroll
+        for (int u = 0; u < 2; ++u) ek[u] = ex_expf(fsub(mine[u], top0[u]));
+        for (int k = 0; k < a.topk; ++k)
+#pragma unroll
+            for (int u = 0; u < 2; ++u) z[u] = fadd(z[u], __shfl_sync(0xffffffffu, ek[u], k));
+#pragma unroll
+        for (int u = 0; u < 2; ++u)
+            if (u < nu && lane < a.topk) a.topw[(tb + u * NW) * a.topk + lane] = fdiv(ek[u], z[u]);
     }
     __syncthreads();
     for (int p = e; p < P; p += RR_THREADS) {
@@ -691,14 +814,21 @@ int fnx_router_route(const float* W, const float* x, float* logits, int T, int n
     FNX_REQUIRE(n > 0 && n % 256 == 0 && n <= 4096, "router_route: n %d must be a multiple of 256 up to 4096", n);
     FNX_REQUIRE(nexp % 32 == 0 && nexp >= 32 && nexp <= 512, "router_route: %d experts (a multiple of 32 up to 512)", nexp);
     FNX_REQUIRE(topk >= 1 && topk <= 16 && topk <= nexp, "router_route: top-%d", topk);
-    RouterArgs a{W, x, logits, T, n, nexp, topk, topi, topw, jobs_gu, jobs_dn, njobs, (unsigned*) scratch};
-    // one block per SM when the rows of x fit its shared memory (each block then reads x once instead of once per row)
+    unsigned* fault = device_fault_word();
+    FNX_REQUIRE(fault, "router_route: no device fault word (no current device?)");
+    RouterArgs a{W, x, logits, T, n, nexp, topk, topi, topw, jobs_gu, jobs_dn, njobs, (unsigned*) scratch, fault};
+    // a block per four rows of W, every block with all of x in its shared memory when it fits (bulk copies: 16-byte
+    // aligned rows); else straight from the L2
     const size_t xbytes = (size_t) T * n * 4;
-    const int fits = xbytes <= 200 * 1024;
+    const bool fits = xbytes <= 200 * 1024 && ((uintptr_t) x % 16) == 0;
     int grid = (nexp + 1 + RR_ROWS - 1) / RR_ROWS;
-    if (fits && grid > 148) grid = 148;
-    if (fits && smem_optin(k_router_route, xbytes, "router_route")) return 1;
-    launch(2, k_router_route, grid, RR_THREADS, fits ? xbytes : 0, strm(st), a, (int) fits);
+    if (grid > 148) grid = 148;
+    if (fits) {
+        if (smem_optin(k_router_route<true>, xbytes, "router_route")) return 1;
+        launch(2, k_router_route<true>, grid, RR_THREADS, xbytes, strm(st), a);
+    } else {
+        launch(2, k_router_route<false>, grid, RR_THREADS, 0, strm(st), a);
+    }
     return launch_ok("router_route");
 }
 
