@@ -12,7 +12,10 @@
 // The mma.sync scan measured 2.2 us of 4.1 us per 32 positions in S = Q K^T alone; here a chunk of 64 takes about 2.4 us
 // in all, most of it the row warps' softmax step (six warps cannot hide their own latencies).
 // Every wait on an mbarrier is bounded; on a timeout the fault word is set and the CTA finishes with what it has.
+#include <cuda.h>
+
 #include <cstdlib>
+#include <cstring>
 
 #include "common.cuh"
 #include "exact_math.cuh"
@@ -46,6 +49,11 @@ __device__ __forceinline__ void au_split2(float x, float y, unsigned& hi, unsign
     hi = (unsigned) __half_as_ushort(hx) | ((unsigned) __half_as_ushort(hy) << 16);
     lo = (unsigned) __half_as_ushort(lx) | ((unsigned) __half_as_ushort(ly) << 16);
 }
+
+// K and V of this GPU's own cache as 2-D tensors [local row][KV heads x 256] for the TMA unit (plain loads, no multicast)
+struct AuMaps {
+    CUtensorMap k, v;
+};
 
 struct AuArgs {
     const float* qg;
@@ -101,7 +109,12 @@ constexpr unsigned AU2_COL_S = 256;   // tensor memory: O in columns 0..255, the
 constexpr int A3_CH = 64, A3_QROWS = 96, A3_QBLK = A3_QROWS * 128, A3_QBYTES = 4 * A3_QBLK, A3_KBLK = A3_CH * 128, A3_KBYTES = 4 * A3_KBLK;
 constexpr int A3_NBUF = 3, A3_PBYTES = A3_QROWS * 128, A3_PAD = 4096;   // the pad: what an MMA reads past the last P row
 
-__global__ void __launch_bounds__(AU_THREADS) k_attn_umma(const AuArgs a) {
+// TMA: the cache is one contiguous run of rows whose count the caller gave (no page table), so K and V chunks come as
+// tensor loads (four boxes of 64 rows x 64 dims, the 128-byte swizzle applied by the copy unit, completion on an
+// mbarrier a buffer) and the queries' image as bulk copies; one lane asks, nobody moves bytes.  Otherwise (pages, or
+// an unknown row count) a warp copies with cp.async as described above.
+template <bool TMA>
+__global__ void __launch_bounds__(AU_THREADS) k_attn_umma(const __grid_constant__ AuMaps maps, const AuArgs a) {
     constexpr int HD = AU_HD;
     const int split = blockIdx.x, kvl = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, nthreads = blockDim.x;
     const int qpk = a.nq / a.nkv, M = a.T * qpk;
@@ -110,8 +123,17 @@ __global__ void __launch_bounds__(AU_THREADS) k_attn_umma(const AuArgs a) {
     unsigned char* Qlo = Qhi + A3_QBYTES;                       // each: 4 K-blocks x [96 rows x 128 B], swizzled
     unsigned char* KVst = Qlo + A3_QBYTES;                      // [3] 4 blocks of 64 dims x [64 rows x 128 B], swizzled: K(c), then V(c)
     unsigned char* Pst = KVst + A3_NBUF * A3_KBYTES;            // hi, lo: [96 rows x 128 B], 128-byte swizzle; then the pad
-    __shared__ __align__(8) unsigned long long mbar_s[2], mbar_o;
+    __shared__ __align__(8) unsigned long long mbar_s[2], mbar_o, kvbar[A3_NBUF], qbar;
     __shared__ unsigned tmem_base;
+    if (tid == 0) {
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(um_s32(&mbar_s[0])));
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(um_s32(&mbar_s[1])));
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(um_s32(&mbar_o)));
+        for (int b = 0; b < A3_NBUF; ++b) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(um_s32(&kvbar[b])));
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(um_s32(&qbar)));
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
     pdl_wait();   // the rows appended by the kernel before are among the positions read
     pdl_go();
     const int pos0 = *a.pos0;
@@ -131,6 +153,14 @@ __global__ void __launch_bounds__(AU_THREADS) k_attn_umma(const AuArgs a) {
     const bool copier = warp == 7;
     const int seg = lane;
     const size_t row_elems = (size_t) a.nkv * HD;
+    // a buffer's mbarrier completes a phase per load: K(c) the even ones, V(c) the odd ones (waited for with parity 0, 1)
+    auto tma_rows = [&](const CUtensorMap* map, int c, int b) {
+        if (!copier || lane) return;
+        um_expect_tx(&kvbar[b], A3_KBYTES);
+#pragma unroll
+        for (int blk = 0; blk < 4; ++blk)
+            um_tma2d(um_s32(KVst) + b * A3_KBYTES + blk * A3_KBLK, map, kvl * HD + blk * 64, c * A3_CH, &kvbar[b]);
+    };
     auto load_rows = [&](const uint16_t* cache, int c, unsigned dst_base) {
         if (!copier) return;
         const unsigned dcol = dst_base + (seg >> 3) * A3_KBLK;
@@ -154,12 +184,25 @@ __global__ void __launch_bounds__(AU_THREADS) k_attn_umma(const AuArgs a) {
     // over them, for O += P(c) V(c); once those are done the K rows of chunk c + 3.  V(c) so has more than a chunk's time to
     // arrive and K(c + 3) most of one, with the memory two stages of each would take less one.
     const unsigned kv_s = um_s32(KVst);
-    auto load_k = [&](int c) { load_rows(a.kc, c_begin + c, kv_s + (c % A3_NBUF) * A3_KBYTES); };
-    auto load_v = [&](int c) { load_rows(a.vc, c_begin + c, kv_s + (c % A3_NBUF) * A3_KBYTES); };
+    auto load_k = [&](int c) {
+        if (TMA) tma_rows(&maps.k, c_begin + c, c % A3_NBUF);
+        else load_rows(a.kc, c_begin + c, kv_s + (c % A3_NBUF) * A3_KBYTES);
+    };
+    auto load_v = [&](int c) {
+        if (TMA) tma_rows(&maps.v, c_begin + c, c % A3_NBUF);
+        else load_rows(a.vc, c_begin + c, kv_s + (c % A3_NBUF) * A3_KBYTES);
+    };
     load_k(0);
     if (nc > 1) load_k(1);
     if (nc > 2) load_k(2);
-    {   // the queries' image, made by k_attn_qsplit: rows 0..95 of each of its K-blocks of 128 rows
+    if (TMA) {   // the queries' image, made by k_attn_qsplit: rows 0..95 of each of its K-blocks of 128 rows, a bulk copy each
+        if (copier && lane == 0) {
+            const unsigned char* img = a.qsplit + (size_t) kvl * 2 * AU_QBYTES;
+            um_expect_tx(&qbar, 2 * A3_QBYTES);
+            for (int blk = 0; blk < 8; ++blk)   // 0..3 hi, 4..7 lo
+                um_bulk(um_s32(Qhi + (size_t) blk * A3_QBLK), img + (size_t) blk * (AU_ROWS * 128), A3_QBLK, &qbar);
+        }
+    } else {
         const unsigned char* img = a.qsplit + (size_t) kvl * 2 * AU_QBYTES;
         for (int i = tid; i < 2 * 4 * A3_QROWS * 8; i += nthreads) {
             const int piece = i & 7, row = (i >> 3) % A3_QROWS, blk = (i >> 3) / A3_QROWS;   // blk: 0..3 hi, 4..7 lo
@@ -168,12 +211,6 @@ __global__ void __launch_bounds__(AU_THREADS) k_attn_umma(const AuArgs a) {
         }
     }
     asm volatile("cp.async.commit_group;");
-    if (tid == 0) {
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(um_s32(&mbar_s[0])));
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(um_s32(&mbar_s[1])));
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(um_s32(&mbar_o)));
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
     if (warp == 0) {   // all 512 columns: O (256), two score tiles (128)
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(um_s32(&tmem_base)), "r"(512));
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
@@ -217,7 +254,10 @@ __global__ void __launch_bounds__(AU_THREADS) k_attn_umma(const AuArgs a) {
     asm volatile("cp.async.wait_group 0;" ::: "memory");
     sync_all();
     const bool issuer = tid == 3 * 32;   // warp 3, lane 0
-    if (issuer) issue_scores(0);
+    if (issuer) {
+        if (TMA) um_wait(&qbar, 0u, a.fault), um_wait(&kvbar[0], 0u, a.fault);   // the queries and K(0) have landed
+        issue_scores(0);
+    }
     bool alive = true;   // false after a wait ran out
     auto copier_wait = [&](unsigned long long* bar, unsigned parity) {   // the copying warp alone waits for a set of MMAs
         bool ok = alive && um_wait(bar, parity, a.fault);
@@ -233,7 +273,10 @@ __global__ void __launch_bounds__(AU_THREADS) k_attn_umma(const AuArgs a) {
 #pragma unroll 1
     for (int i = 0; i < nc; ++i) {
         const int buf = i & 1;
-        if (issuer && i + 1 < nc) issue_scores(i + 1);   // the next chunk's scores while this chunk's are used
+        if (issuer && i + 1 < nc) {   // the next chunk's scores while this chunk's are used
+            if (TMA) um_wait(&kvbar[(i + 1) % A3_NBUF], 0u, a.fault);   // K(i + 1) has landed
+            issue_scores(i + 1);
+        }
         float sacc[8][4];
 #pragma unroll
         for (int j = 0; j < 8; ++j) sacc[j][0] = sacc[j][1] = sacc[j][2] = sacc[j][3] = -INFINITY;
@@ -349,6 +392,14 @@ __global__ void __launch_bounds__(AU_THREADS) k_attn_umma(const AuArgs a) {
         }
         // ---- P is written; V(i), asked for a chunk ago, and K(i + 2) have landed: the output MMAs of this chunk
         asm volatile("cp.async.wait_group 1;" ::: "memory");   // all but V(i + 1), just asked for
+        if (TMA && copier) {
+            // V(i) has landed.  Rows of the range's last chunk past the newest position hold whatever the cache holds
+            // there: their weights are zero, but zero times a stray NaN is not, so they are cleared
+            copier_wait(&kvbar[i % A3_NBUF], 1u);
+            const int have = ctx_max - (c_begin + i) * A3_CH;
+            for (int row = max(have, 0); row < A3_CH; ++row)
+                *reinterpret_cast<uint4*>(KVst + (size_t) (i % A3_NBUF) * A3_KBYTES + (lane >> 3) * A3_KBLK + row * 128 + (lane & 7) * 16) = make_uint4(0u, 0u, 0u, 0u);
+        }
         sync_all();
         if (issuer) issue_output(i);
     }
@@ -405,8 +456,27 @@ int attn_umma_launch(const float* qg, const uint16_t* kc, const uint16_t* vc, Fn
     launch(0, k_attn_qsplit, (nkv * AU_ROWS * (AU_HD / 2) + 255) / 256, 256, 0, st, a);
     if (launch_ok("attn query split")) return 1;
     const size_t sm3 = attn_umma_smem();
-    if (cudaFuncSetAttribute(k_attn_umma, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) sm3) != cudaSuccess) return -1;
-    launch(6, k_attn_umma, dim3(nsplit, nkv), AU_THREADS, sm3, st, a);
+    AuMaps maps;
+    memset(&maps, 0, sizeof(maps));
+    // tensor loads when the cache is a contiguous run of a known number of rows; its rows past the newest position are
+    // inside the maps (read and cleared in shared memory), rows past the cache read as zeros
+    UmEncode enc = um_encoder();
+    bool tma = enc && !g.pt && g.cap >= 1 && (uintptr_t) kc % 16 == 0 && (uintptr_t) vc % 16 == 0 && !getenv("FNX_ATTN_NO_TMA");
+    if (tma) {
+        const cuuint64_t gd[2] = {(cuuint64_t) nkv * AU_HD, (cuuint64_t) g.cap}, gs[1] = {(cuuint64_t) nkv * AU_HD * 2};
+        const cuuint32_t bx[2] = {64, A3_CH}, es[2] = {1, 1};
+        tma = enc(&maps.k, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, (void*) kc, gd, gs, bx, es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS &&
+              enc(&maps.v, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, (void*) vc, gd, gs, bx, es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    }
+    if (tma) {
+        if (cudaFuncSetAttribute(k_attn_umma<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) sm3) != cudaSuccess) return -1;
+        launch(6, k_attn_umma<true>, dim3(nsplit, nkv), AU_THREADS, sm3, st, maps, a);
+    } else {
+        if (cudaFuncSetAttribute(k_attn_umma<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) sm3) != cudaSuccess) return -1;
+        launch(6, k_attn_umma<false>, dim3(nsplit, nkv), AU_THREADS, sm3, st, maps, a);
+    }
     return launch_ok("attn scan (tcgen05)");
 }
 

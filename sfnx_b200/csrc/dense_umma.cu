@@ -43,16 +43,8 @@ struct DuArgs {
     unsigned* fault;
 };
 
-__device__ __forceinline__ void du_expect(unsigned long long* bar, unsigned bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(um_s32(bar)), "r"(bytes) : "memory");
-}
 __device__ __forceinline__ void du_arrive(unsigned long long* bar) {
     asm volatile("{\n\t.reg .b64 t;\n\tmbarrier.arrive.shared::cta.b64 t, [%0];\n\t}" ::"r"(um_s32(bar)) : "memory");
-}
-__device__ __forceinline__ void du_tma2d(unsigned dst, const CUtensorMap* map, int x, int y, unsigned long long* bar) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst), "l"(map),
-                 "r"(x), "r"(y), "r"(um_s32(bar))
-                 : "memory");
 }
 // D[tmem] = A B, 128 x 16 x 32, int8 operands through descriptors, int32 result; issued by one thread
 __device__ __forceinline__ void du_mma_i8(unsigned tmem, unsigned long long da, unsigned long long db, unsigned idesc) {
@@ -143,13 +135,13 @@ __global__ void __launch_bounds__(DU_THREADS, 1) k_q8s_umma(const __grid_constan
                 const CUtensorMap* mw = &maps.w[t.seg];
                 const CUtensorMap* md = &maps.d[t.seg];
                 if (nt >= 2 && alive) alive = um_wait(&dw_empty[tp], (unsigned) ((nt / 2 - 1) & 1), a.fault);
-                du_expect(&dw_full[tp], (unsigned) (DU_M * nb * 2));
-                du_tma2d(um_s32(dw_s + (size_t) tp * DU_M * nb), md, 0, t.row0, &dw_full[tp]);
+                um_expect_tx(&dw_full[tp], (unsigned) (DU_M * nb * 2));
+                um_tma2d(um_s32(dw_s + (size_t) tp * DU_M * nb), md, 0, t.row0, &dw_full[tp]);
                 for (int kc = 0; kc < nkc; ++kc, ++c) {
                     const int s = c % DU_STAGES;
                     if (c >= DU_STAGES && alive) alive = um_wait(&empty_a[s], (unsigned) ((c / DU_STAGES - 1) & 1), a.fault);
-                    du_expect(&full_a[s], DU_ABYTES);
-                    du_tma2d(a_s32 + s * DU_ABYTES, mw, kc * DU_KC, t.row0, &full_a[s]);
+                    um_expect_tx(&full_a[s], DU_ABYTES);
+                    um_tma2d(a_s32 + s * DU_ABYTES, mw, kc * DU_KC, t.row0, &full_a[s]);
                 }
             }
         }
@@ -259,18 +251,6 @@ __global__ void __launch_bounds__(DU_THREADS, 1) k_q8s_umma(const __grid_constan
 }
 
 // ---- host side: tensor maps over this GPU's own memory (plain loads, no multicast)
-typedef CUresult (*DuEncode)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
-                             CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-static DuEncode du_encoder() {
-    static DuEncode fn = nullptr;
-    if (!fn) {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult qr;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qr) == cudaSuccess && qr == cudaDriverEntryPointSuccess) fn = (DuEncode) p;
-    }
-    return fn;
-}
-
 size_t q8s_umma_smem(int cols) {
     const int nb = cols / 32, nkc = cols / DU_KC;
     return (size_t) DU_STAGES * DU_ABYTES + (size_t) nkc * DU_BCHUNK + (size_t) 2 * DU_M * nb * 2 + (size_t) nb * 16 * 4 + 1024;
@@ -287,7 +267,7 @@ int q8s_umma_launch(const FnxQ8S* w, const int* rows, float* const* out, const i
         tiles += (rows[s] + DU_M - 1) / DU_M;
     }
     if (tiles < 64) return -1;   // too few 128-row tiles to fill the GPU: the streaming kernel does better
-    DuEncode enc = du_encoder();
+    UmEncode enc = um_encoder();
     unsigned* fault = device_fault_word();
     if (!enc || !fault) return fail("%s: no tensor-map encoder or fault word", what);
     DuMaps maps;

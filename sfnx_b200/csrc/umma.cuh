@@ -3,6 +3,7 @@
 // mbarrier wait.
 #pragma once
 
+#include <cuda.h>
 #include <cuda_runtime.h>
 
 namespace fnxk {
@@ -36,6 +37,36 @@ __device__ __forceinline__ bool um_wait(unsigned long long* bar, unsigned parity
                      : "memory");
     if (!ok) atomicOr(fault, 8u);
     return ok != 0;
+}
+
+// ---- the TMA unit: plain loads of this GPU's own memory (no multicast), completion as bytes on an mbarrier
+__device__ __forceinline__ void um_expect_tx(unsigned long long* bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(um_s32(bar)), "r"(bytes) : "memory");
+}
+// a box of a 2-D tensor map at element x (x times the element size a multiple of 16 bytes), row y
+__device__ __forceinline__ void um_tma2d(unsigned dst, const CUtensorMap* map, int x, int y, unsigned long long* bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst), "l"(map),
+                 "r"(x), "r"(y), "r"(um_s32(bar))
+                 : "memory");
+}
+// a contiguous run of bytes (both addresses and the size multiples of 16)
+__device__ __forceinline__ void um_bulk(unsigned dst, const void* src, unsigned bytes, unsigned long long* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src), "r"(bytes),
+                 "r"(um_s32(bar))
+                 : "memory");
+}
+
+// the driver's tensor-map encoder, looked up once (no link against the driver library); null when it is not there
+typedef CUresult (*UmEncode)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                             CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+inline UmEncode um_encoder() {
+    static UmEncode fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult qr;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qr) == cudaSuccess && qr == cudaDriverEntryPointSuccess) fn = (UmEncode) p;
+    }
+    return fn;
 }
 
 }  // namespace fnxk

@@ -8,7 +8,9 @@ from tests import cases
 pytestmark = pytest.mark.gpu
 
 
-def _run(c, entry="fnx_attn_partial_exact"):
+def _run(c, entry="fnx_attn_partial_exact", known_rows=False):
+    """known_rows: the cache is handed over with its row count (FnxKvPages.cap), which lets the tensor-core scan fetch K/V
+    by tensor loads; 70 rows of NaNs are put after the case's rows, inside the count, to stand for stale memory."""
     import torch
 
     from sfnx_b200 import lib as L
@@ -22,15 +24,19 @@ def _run(c, entry="fnx_attn_partial_exact"):
     for card in range(ncard):
         qg, k, v = G.dev(c["qg"]), G.dev(c["k"]), G.dev(c["v"])
         qn, kn = G.dev(c["qn"]), G.dev(c["kn"])
-        kc, vc = G.dev(c["kc"][card]), G.dev(c["vc"][card])
-        g = L.KvPages(None, 0, 0, 0)
+        hk, hv = c["kc"][card], c["vc"][card]
+        if known_rows:
+            stale = np.full((70,) + hk.shape[1:], 0x7E00, np.uint16)
+            hk, hv = np.concatenate([hk, stale]), np.concatenate([hv, stale])
+        kc, vc = G.dev(hk), G.dev(hv)
+        g = L.KvPages(None, 0, 0, hk.shape[0] if known_rows else 0)
         L.call("fnx_attn_prep_append", qg.data_ptr(), k.data_ptr(), v.data_ptr(), qn.data_ptr(), kn.data_ptr(), kc.data_ptr(),
                vc.data_ptr(), g, card, ncard, T, pos0.data_ptr(), c["eps"], L.Rope(c["rope_base"], 64), nq, nkv, hd, st)
         scratch = G.zeros(L.load().fnx_attn_scratch_floats(nq, hd, T))
         L.call(entry, qg.data_ptr(), kc.data_ptr(), vc.data_ptr(), g, parts[card].data_ptr(), card, ncard, T,
                pos0.data_ptr(), nq, nkv, hd, scratch.data_ptr(), st)
-        res["kc"].append(G.host(kc, np.uint16))
-        res["vc"].append(G.host(vc, np.uint16))
+        res["kc"].append(G.host(kc, np.uint16)[:c["kc"][card].shape[0]])
+        res["vc"].append(G.host(vc, np.uint16)[:c["vc"][card].shape[0]])
         res["qg"], res["k"] = qg, k
     own = nq // ncard
     outs = [G.zeros((T, own, hd)) for _ in range(ncard)]
@@ -58,12 +64,15 @@ def test_attention_exact(T, ctx, ncard, hd):
 
 @pytest.mark.parametrize("T,ctx,ncard,hd", [(16, 3000, 1, 256), (16, 70, 1, 256), (7, 1500, 2, 256), (5, 515, 4, 128), (1, 0, 1, 256),
                                             (16, 40000, 1, 256), (2, 262144, 1, 256), (3, 70000, 8, 256)])
-def test_attention_fast_scan(T, ctx, ncard, hd):
+@pytest.mark.parametrize("known_rows", [False, True])
+def test_attention_fast_scan(T, ctx, ncard, hd, known_rows):
     """The one-pass tensor-core scan against the oracle: the same partial format and merge, values equal to f32 rounding
-    (its sums run in another order; queries and weights enter the f16 MMAs as high + low halves)."""
+    (its sums run in another order; queries and weights enter the f16 MMAs as high + low halves).  Both ways of fetching
+    K/V: a warp's asynchronous copies (row count unknown) and tensor loads (row count given, stale NaN rows after the
+    newest position)."""
     c = cases.attn_case(T=T, ctx=ctx, nq=8 if hd == 128 else 24, nkv=2 if hd == 128 else 4, hd=hd, ncard=ncard, seed=60 + T)
     ref = cases.attn_oracle(c)
-    got = _run(c, "fnx_attn_partial")
+    got = _run(c, "fnx_attn_partial", known_rows)
     assert np.isfinite(got["out"]).all()
     err = np.abs(got["out"] - ref["out"])
     assert np.allclose(got["out"], ref["out"], rtol=3e-5, atol=2e-6), (err.max(), np.abs(ref["out"]).max())
@@ -74,12 +83,13 @@ def test_attention_fast_scan(T, ctx, ncard, hd):
 
 
 @pytest.mark.parametrize("T,ctx,ramp", [(16, 3000, 8.0), (16, 700, 20.0), (3, 5000, 12.0)])
-def test_attention_fast_scan_rising_scores(T, ctx, ramp):
+@pytest.mark.parametrize("known_rows", [False, True])
+def test_attention_fast_scan_rising_scores(T, ctx, ramp, known_rows):
     """Keys that grow along the cache: every row's largest score rises by far more than the scan's rescaling threshold
     between the first and the last chunk, so the accumulated output is rescaled several times on the way."""
     c = cases.attn_case(T=T, ctx=ctx, seed=90 + T, ramp=ramp)
     ref = cases.attn_oracle(c)
-    got = _run(c, "fnx_attn_partial")
+    got = _run(c, "fnx_attn_partial", known_rows)
     assert np.isfinite(got["out"]).all()
     assert (ref["part"][0][..., 256] > 16).all(), "the case does not reach the rescaling path"
     # scores reach 30 to 70 here, where one f32 rounding of a score moves its weight by 4e-6 relative: the bound is
