@@ -68,12 +68,20 @@ typedef struct FnxExperts {
 } FnxExperts;
 
 /* the paged K/V pool of one layer on this GPU: reference src/kernels.hpp:160-165 (KvPages); pt null: local rows
- * are contiguous */
+ * are contiguous.
+ * q8 (reference kv_q8, src/kernels.hpp:149-181): the rows are int8 in groups of 32 with an f16 scale a group
+ * (d = max |x| / 127, q = round(x / d): src/kernels.cu:1561-1566).  kc / vc then point at bytes: local row r's int8
+ * values start at byte pt[r / rows] * page * 2 + (r % rows) * nkv * hd and its scales at half pt[r / rows] * page +
+ * rows * nkv * hd / 2 + (r % rows) * nkv * hd / 32 (a page's scales follow its rows: kvq_row, kvq_scale); without a
+ * page table the cache is one such page of `cap` rows (cap must be given).  The scan in the reference's order of sums
+ * and the append read and write them; the tensor-core scans take f16 rows only (fnx_attn_partial then runs the
+ * exact-order scan). */
 typedef struct FnxKvPages {
     const int* pt; /* device: logical page -> physical page */
     size_t page;   /* halves per page */
     int rows;      /* local rows per page */
     int cap;       /* local rows the cache holds when pt is null (0: unchecked); a row past it is not appended */
+    int q8;        /* the rows are int8 with f16 group scales */
 } FnxKvPages;
 
 /* unscaled rotary: reference src/rope.hpp:22-27 (Rope, base only) */
@@ -246,6 +254,8 @@ int fnx_attn_prep_append(float* qg, float* k, const float* v, const float* q_nor
  * caller, parts[p] at parts + p * T * nq * (hd + 2)) in ring order for heads [h0, h0 + nh) and applies the gate:
  * out [T][nh][hd] */
 size_t fnx_attn_scratch_floats(int nq, int hd, int T);
+/* halves of one layer's K (or V) rows when they are int8: reference src/kernels.hpp:152-155 kvp_rows_halves */
+size_t fnx_kvq_halves(int rows, int nkv, int hd);
 /* the fast scan (all rows of the window in one pass over the K/V rows, tensor cores, sums in its own order: equal to
  * the exact-order scan to f32 rounding) and the scan in the reference's order of sums (bit-reproducible, slower) */
 int fnx_attn_partial(const float* qg, const uint16_t* kc, const uint16_t* vc, FnxKvPages g, float* part, int card, int ncard, int T,

@@ -28,7 +28,7 @@ BIGJOB_DTYPE = np.dtype([("w", "<i4"), ("n", "<i4"), ("y", "<i4", (PF_JOB,)), ("
 
 
 class KvPages(C.Structure):
-    _fields_ = [("pt", C.c_void_p), ("page", C.c_size_t), ("rows", C.c_int)]
+    _fields_ = [("pt", C.c_void_p), ("page", C.c_size_t), ("rows", C.c_int), ("cap", C.c_int), ("q8", C.c_int)]
 
 
 class Sampling(C.Structure):
@@ -303,17 +303,22 @@ def rope_freqs(base, nrot):
     return f
 
 
-def attn_prep_append(qg, k, v, qn, kn, kc, vc, card, ncard, pos0, eps, base, nq, nkv, hd=256, nrot=64):
+def attn_prep_append(qg, k, v, qn, kn, kc, vc, card, ncard, pos0, eps, base, nq, nkv, hd=256, nrot=64, q8_rows=0):
+    """q8_rows > 0: kc / vc are int8 caches of that many rows (uint16 arrays of kvq_halves(rows) halves)."""
     T = qg.shape[0]
-    g = KvPages(None, 0, 0)
+    g = KvPages(None, 0, 0, q8_rows, 1 if q8_rows else 0)
     lib().orc_attn_prep_append(P(qg), P(k), P(v), P(qn), P(kn), P(kc), P(vc), C.byref(g), card, ncard, T, pos0, C.c_float(eps),
                                C.c_float(base), nq, nkv, hd, nrot)
 
 
-def attn_partial(qg, kc, vc, card, ncard, pos0, nq, nkv, hd=256):
+def kvq_halves(rows, nkv, hd):
+    return rows * nkv * hd // 2 + rows * nkv * hd // 32
+
+
+def attn_partial(qg, kc, vc, card, ncard, pos0, nq, nkv, hd=256, q8_rows=0):
     T = qg.shape[0]
     part = np.zeros((T, nq, hd + 2), np.float32)
-    g = KvPages(None, 0, 0)
+    g = KvPages(None, 0, 0, q8_rows, 1 if q8_rows else 0)
     lib().orc_attn_partial(P(qg), P(kc), P(vc), C.byref(g), P(part), card, ncard, T, pos0, nq, nkv, hd)
     return part
 

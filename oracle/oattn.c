@@ -6,6 +6,9 @@
  *   split-K online softmax over owned positions      src/kernels.cu:497-582
  *   merge of the 16 splits                           src/kernels.cu:585-606
  *   merge of the cards' partials in ring order, gate src/kernels.cu:609-672
+ *   int8 K/V rows (groups of 32, f16 scale)          src/kernels.hpp:149-181; append src/kernels.cu:1561-1566; scan :531-537
+ *     stated with IEEE division where the reference's fast-math build divides: d = amax / 127, id = 1 / d,
+ *     q = roundf(x id), value read back as (float) q * f16(d)
  */
 #include "oracle.h"
 
@@ -21,6 +24,38 @@ int orc_kv_owned(int p, int card, int ncard) { /* positions <= p that `card` own
 static size_t kv_row_at(const OrcKvPages* g, int r, int nkv, int hd) {
     if (!g->pt) return (size_t) r * nkv * hd;
     return (size_t) g->pt[r / g->rows] * g->page + (size_t) (r % g->rows) * nkv * hd;
+}
+
+/* int8 rows: row r's first byte and its first scale (in halves), both from the layer's pointer; a page's scales follow
+ * its rows (kvq_row, kvq_scale); without a page table the cache is one page of g->cap rows */
+static size_t kvq_row_at(const OrcKvPages* g, int r, int nkv, int hd) {
+    if (!g->pt) return (size_t) r * nkv * hd;
+    return (size_t) g->pt[r / g->rows] * g->page * 2 + (size_t) (r % g->rows) * nkv * hd;
+}
+static size_t kvq_scale_at(const OrcKvPages* g, int r, int nkv, int hd) {
+    if (!g->pt) return (size_t) g->cap * nkv * hd / 2 + (size_t) r * nkv * hd / 32;
+    return (size_t) g->pt[r / g->rows] * g->page + (size_t) g->rows * nkv * hd / 2 + (size_t) (r % g->rows) * nkv * hd / 32;
+}
+/* element e of head kvh of local row r as the scan reads it */
+static float kv_value(const o_half* cache, const OrcKvPages* g, int r, int nkv, int hd, int kvh, int d) {
+    if (!g->q8) return o_h2f(cache[kv_row_at(g, r, nkv, hd) + (size_t) kvh * hd + d]);
+    const int e = kvh * hd + d;
+    const int8_t q = ((const int8_t*) cache)[kvq_row_at(g, r, nkv, hd) + e];
+    return (float) q * o_h2f(cache[kvq_scale_at(g, r, nkv, hd) + e / 32]);
+}
+static void kv_append_row(o_half* cache, const OrcKvPages* g, int r, int nkv, int hd, const float* x) {
+    if (!g->q8) {
+        const size_t at = kv_row_at(g, r, nkv, hd);
+        for (int e = 0; e < nkv * hd; ++e) cache[at + e] = o_f2h(x[e]);
+        return;
+    }
+    for (int b = 0; b < nkv * hd / 32; ++b) {
+        float amax = 0.f;
+        for (int l = 0; l < 32; ++l) amax = fmaxf(amax, fabsf(x[b * 32 + l]));
+        const float d = amax / 127.f, id = d != 0.f ? 1.f / d : 0.f;
+        for (int l = 0; l < 32; ++l) ((int8_t*) cache)[kvq_row_at(g, r, nkv, hd) + b * 32 + l] = (int8_t) roundf(x[b * 32 + l] * id);
+        cache[kvq_scale_at(g, r, nkv, hd) + b] = o_f2h(d);
+    }
 }
 
 /* RMS norm with weight, then rotation of the pairs (i, i + nrot/2), i < nrot/2, at position pos */
@@ -63,11 +98,8 @@ void orc_attn_prep_append(float* qg, float* k, const float* v, const float* q_no
         for (int h = 0; h < nkv; ++h) norm_rope(k + ((size_t) t * nkv + h) * hd, k_norm, p, eps, freq, 1.0f, hd, nrot);
         if (j % ncard != card) continue;
         const int r = (j / ncard) * 4 + p % 4;
-        const size_t at = kv_row_at(g, r, nkv, hd);
-        for (int e = 0; e < nkv * hd; ++e) {
-            kc[at + e] = o_f2h(k[(size_t) t * nkv * hd + e]);
-            vc[at + e] = o_f2h(v[(size_t) t * nkv * hd + e]);
-        }
+        kv_append_row(kc, g, r, nkv, hd, k + (size_t) t * nkv * hd);
+        kv_append_row(vc, g, r, nkv, hd, v + (size_t) t * nkv * hd);
     }
 }
 
@@ -98,9 +130,8 @@ void orc_attn_partial(const float* qg, const o_half* kc, const o_half* vc, const
                             sv[pp] = -INFINITY;
                             continue;
                         }
-                        const o_half* kr = kc + kv_row_at(g, c0 + pp, nkv, hd) + (size_t) kvh * hd;
                         float a = 0.f;
-                        for (int d = 0; d < hd; ++d) a = fmaf(q[d], o_h2f(kr[d]), a);
+                        for (int d = 0; d < hd; ++d) a = fmaf(q[d], kv_value(kc, g, c0 + pp, nkv, hd, kvh, d), a);
                         sv[pp] = a * rs;
                         cmax = fmaxf(cmax, sv[pp]);
                     }
@@ -111,8 +142,7 @@ void orc_attn_partial(const float* qg, const o_half* kc, const o_half* vc, const
                     m = mn;
                     for (int d = 0; d < hd; ++d) acc[d] = acc[d] * sc;
                     for (int pp = 0; pp < np; ++pp) {
-                        const o_half* vr = vc + kv_row_at(g, c0 + pp, nkv, hd) + (size_t) kvh * hd;
-                        for (int d = 0; d < hd; ++d) acc[d] = fmaf(w[pp], o_h2f(vr[d]), acc[d]);
+                        for (int d = 0; d < hd; ++d) acc[d] = fmaf(w[pp], kv_value(vc, g, c0 + pp, nkv, hd, kvh, d), acc[d]);
                     }
                 }
                 sm[s] = m;

@@ -35,6 +35,8 @@ typedef struct { /* reference src/kernels.hpp:160-165; pt null: one contiguous r
     const int* pt;
     size_t page; /* halves per page */
     int rows;    /* local rows per page */
+    int cap;     /* rows of a cache without a page table (needed when q8) */
+    int q8;      /* int8 rows with an f16 scale per group of 32: reference src/kernels.hpp:149-181 */
 } OrcKvPages;
 
 typedef struct { /* reference src/session.hpp:18-25 (the fields the distribution uses) */

@@ -25,6 +25,18 @@ __device__ __forceinline__ size_t kv_row_at(const FnxKvPages& g, int r, int nkv,
     return (size_t) g.pt[r / g.rows] * g.page + (size_t) (r % g.rows) * nkv * hd;
 }
 
+// int8 rows (reference src/kernels.hpp:172-177 kvq_row, kvq_scale): row r's first byte, and its first scale in halves,
+// both from the layer's K (or V) pointer; a page's scales follow its rows, and a cache without a page table is one page
+// of g.cap rows
+__device__ __forceinline__ size_t kvq_row_at(const FnxKvPages& g, int r, int nkv, int hd) {
+    if (!g.pt) return (size_t) r * nkv * hd;
+    return (size_t) g.pt[r / g.rows] * g.page * 2 + (size_t) (r % g.rows) * nkv * hd;
+}
+__device__ __forceinline__ size_t kvq_scale_at(const FnxKvPages& g, int r, int nkv, int hd) {
+    if (!g.pt) return (size_t) g.cap * nkv * hd / 2 + (size_t) r * nkv * hd / 32;
+    return (size_t) g.pt[r / g.rows] * g.page + (size_t) g.rows * nkv * hd / 2 + (size_t) (r % g.rows) * nkv * hd / 32;
+}
+
 struct RopeFreqs {
     float f[64];   // unit frequency of pair i, base^(-2 i / nrot), computed by the host's powf
     int nrot;
@@ -80,7 +92,14 @@ __global__ void k_attn_prep_append(float* qg, float* k, const float* v, const fl
     if (j % ncard != card) return;
     const int r = (j / ncard) * 4 + p % 4;
     if (!g.pt && g.cap > 0 && r >= g.cap) return;   // past the cache: the caller refuses such windows; never write outside
-    (is_k ? kc : vc)[kv_row_at(g, r, nkv, hd) + e] = f2h(x);
+    uint16_t* cache = is_k ? kc : vc;
+    if (g.q8) {   // a warp's 32 elements are one group (reference src/kernels.cu:1561-1566)
+        const float d = fdiv(wmax(fabsf(x)), 127.f), id = d != 0.f ? fdiv(1.f, d) : 0.f;
+        reinterpret_cast<int8_t*>(cache)[kvq_row_at(g, r, nkv, hd) + e] = (int8_t) roundf(fmul(x, id));
+        if ((e & 31) == 0) cache[kvq_scale_at(g, r, nkv, hd) + e / 32] = f2h(d);
+        return;
+    }
+    cache[kv_row_at(g, r, nkv, hd) + e] = f2h(x);
 }
 
 // ---------------------------------------------------------------- the scan in the reference's order of sums
@@ -168,18 +187,36 @@ __global__ void __launch_bounds__(AX_THREADS, 1) k_attn_rows(const float* __rest
             // ---- the chunk's K and V rows as f32: 16-byte pieces of 8 halves
             for (int e = tid; e < ATT_CH * (HD / 8); e += AX_THREADS) {
                 const int pp = e / (HD / 8), c8 = e % (HD / 8);
-                uint4 kr = make_uint4(0, 0, 0, 0), vr = kr;
-                if (pp < npmax) {
-                    const size_t at = kv_row_at(g, c0 + pp, nkv, HD) + (size_t) kvl * HD + 8 * c8;
-                    kr = *reinterpret_cast<const uint4*>(kc + at);
-                    vr = *reinterpret_cast<const uint4*>(vc + at);
-                }
-                const unsigned kw[4] = {kr.x, kr.y, kr.z, kr.w}, vw[4] = {vr.x, vr.y, vr.z, vr.w};
                 float kf[8], vf[8];
+                if (g.q8) {   // int8 values times their group's scale (reference src/kernels.cu:531-537): 8 values of one group
+                    uint2 kr = make_uint2(0, 0), vr = kr;
+                    float kd8 = 0.f, vd8 = 0.f;
+                    if (pp < npmax) {
+                        const size_t at = kvq_row_at(g, c0 + pp, nkv, HD) + (size_t) kvl * HD + 8 * c8;
+                        const size_t sc = kvq_scale_at(g, c0 + pp, nkv, HD) + ((size_t) kvl * HD + 8 * c8) / 32;
+                        kr = *reinterpret_cast<const uint2*>(reinterpret_cast<const int8_t*>(kc) + at);
+                        vr = *reinterpret_cast<const uint2*>(reinterpret_cast<const int8_t*>(vc) + at);
+                        kd8 = h2f(kc[sc]), vd8 = h2f(vc[sc]);
+                    }
+                    const unsigned kw[2] = {kr.x, kr.y}, vw[2] = {vr.x, vr.y};
 #pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    kf[2 * k] = h2f((uint16_t) (kw[k] & 0xffff)), kf[2 * k + 1] = h2f((uint16_t) (kw[k] >> 16));
-                    vf[2 * k] = h2f((uint16_t) (vw[k] & 0xffff)), vf[2 * k + 1] = h2f((uint16_t) (vw[k] >> 16));
+                    for (int k = 0; k < 8; ++k) {
+                        kf[k] = fmul((float) (int8_t) (kw[k >> 2] >> (8 * (k & 3))), kd8);
+                        vf[k] = fmul((float) (int8_t) (vw[k >> 2] >> (8 * (k & 3))), vd8);
+                    }
+                } else {
+                    uint4 kr = make_uint4(0, 0, 0, 0), vr = kr;
+                    if (pp < npmax) {
+                        const size_t at = kv_row_at(g, c0 + pp, nkv, HD) + (size_t) kvl * HD + 8 * c8;
+                        kr = *reinterpret_cast<const uint4*>(kc + at);
+                        vr = *reinterpret_cast<const uint4*>(vc + at);
+                    }
+                    const unsigned kw[4] = {kr.x, kr.y, kr.z, kr.w}, vw[4] = {vr.x, vr.y, vr.z, vr.w};
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        kf[2 * k] = h2f((uint16_t) (kw[k] & 0xffff)), kf[2 * k + 1] = h2f((uint16_t) (kw[k] >> 16));
+                        vf[2 * k] = h2f((uint16_t) (vw[k] & 0xffff)), vf[2 * k + 1] = h2f((uint16_t) (vw[k] >> 16));
+                    }
                 }
                 float4* kd = reinterpret_cast<float4*>(k_s + (size_t) pp * KLD + 8 * c8);
                 float4* vd = reinterpret_cast<float4*>(v_s + (size_t) pp * HD + 8 * c8);
@@ -350,6 +387,7 @@ int fnx_attn_prep_append(float* qg, float* k, const float* v, const float* q_nor
     FNX_REQUIRE(hd % 32 == 0 && hd >= 32 && hd <= 1024, "attn_prep_append: head dim %d", hd);
     FNX_REQUIRE(rope.nrot % 2 == 0 && rope.nrot >= 2 && rope.nrot <= 128 && rope.nrot <= hd, "attn_prep_append: rotary width %d", rope.nrot);
     FNX_REQUIRE(ncard >= 1 && card >= 0 && card < ncard, "attn_prep_append: GPU %d of %d", card, ncard);
+    FNX_REQUIRE(!g.q8 || g.pt || g.cap > 0, "attn_prep_append: an int8 cache without a page table needs its row count (cap)");
     RopeFreqs rf;
     rf.nrot = rope.nrot;
     for (int i = 0; i < rope.nrot / 2; ++i) rf.f[i] = powf(rope.base, -2.0f * (float) i / (float) rope.nrot);
@@ -357,6 +395,8 @@ int fnx_attn_prep_append(float* qg, float* k, const float* v, const float* q_nor
            nq, nkv, hd);
     return launch_ok("attn_prep_append");
 }
+
+size_t fnx_kvq_halves(int rows, int nkv, int hd) { return (size_t) rows * nkv * hd / 2 + (size_t) rows * nkv * hd / 32; }
 
 size_t fnx_attn_scratch_floats(int nq, int hd, int T) {   // the larger of the exact scan's 16 splits and the fast scan's (at most 148)
     const size_t exact = (size_t) T * nq * ATT_SPLITS * (hd + 2), fast = (size_t) T * nq * 148 * (hd + 2) + (size_t) 8 * 32768;
@@ -369,6 +409,7 @@ static int attn_partial_rows(const float* qg, const uint16_t* kc, const uint16_t
     FNX_REQUIRE(hd == 256 || hd == 128, "attn: head dim %d (128 or 256)", hd);
     FNX_REQUIRE(nkv >= 1 && nq % nkv == 0 && nq / nkv <= ATT_MAXQPK, "attn: %d query heads over %d KV heads", nq, nkv);
     FNX_REQUIRE(ncard >= 1 && card >= 0 && card < ncard, "attn: GPU %d of %d", card, ncard);
+    FNX_REQUIRE(!g.q8 || lr.pt || g.pt || g.cap > 0, "attn: an int8 cache without a page table needs its row count (cap)");
     float* acc = scratch;
     AttPart* mz = (AttPart*) (scratch + (size_t) T * nq * ATT_SPLITS * hd);
     const size_t sm = ((size_t) AX_PT * hd + (size_t) ATT_CH * (hd + 4) + (size_t) ATT_CH * hd + (size_t) AX_PT * ATT_CH + 2 * AX_PT) * sizeof(float);

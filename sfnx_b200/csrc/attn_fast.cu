@@ -275,6 +275,8 @@ int fnx_attn_partial(const float* qg, const uint16_t* kc, const uint16_t* vc, Fn
     FNX_REQUIRE(hd == 256 || hd == 128, "attn: head dim %d (128 or 256)", hd);
     FNX_REQUIRE(nkv >= 1 && nq % nkv == 0 && T * (nq / nkv) <= 128, "attn: %d query heads over %d KV heads, %d rows", nq, nkv, T);
     FNX_REQUIRE(ncard >= 1 && card >= 0 && card < ncard, "attn: GPU %d of %d", card, ncard);
+    // int8 rows are read by the exact-order scan only (it turns them into f32 as it stages them)
+    if (g.q8) return fnx_attn_partial_exact(qg, kc, vc, g, part, card, ncard, T, pos0, nq, nkv, hd, scratch, st);
     const int M = T * (nq / nkv), Mpad = (M + 15) / 16 * 16, nsplit = fnx_attn_splits(nkv);
     // head dimension 256: S = Q K^T on tcgen05 with the scores in tensor memory (attn_umma.cu); FNX_ATTN_MMA=1 keeps the
     // mma.sync scan below, which also serves the other shapes

@@ -42,7 +42,7 @@ class LaneRows(C.Structure):
 
 
 class KvPages(C.Structure):
-    _fields_ = [("pt", C.c_void_p), ("page", C.c_size_t), ("rows", C.c_int), ("cap", C.c_int)]
+    _fields_ = [("pt", C.c_void_p), ("page", C.c_size_t), ("rows", C.c_int), ("cap", C.c_int), ("q8", C.c_int)]
 
 
 class Rope(C.Structure):
@@ -160,6 +160,7 @@ _OTHER = {
     "fnx_gdn_scratch_floats": (_z, [_i]),
     "fnx_gdn_log_floats": (_z, [_i, _i]),
     "fnx_attn_scratch_floats": (_z, [_i, _i, _i]),
+    "fnx_kvq_halves": (_z, [_i, _i, _i]),
     "fnx_kv_rows_per_card": (_i, [_i, _i]),
     "fnx_attn_splits": (_i, [_i]),
     "fnx_window_workspace_bytes": (_z, [_p]),

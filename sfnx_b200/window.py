@@ -97,13 +97,22 @@ class SyntheticStack:
 
     def _kv_slice(self, layer, name):
         """This GPU's rows of a K or V cache N(0, 1) over every position: the whole cache is generated (the same on every
-        GPU) and local row r = the row of position ((r / 4) ncard + card) 4 + r % 4."""
+        GPU) and local row r = the row of position ((r / 4) ncard + card) 4 + r % 4.  With shape.kv_q8 the rows are int8
+        in groups of 32 (d = max |x| / 127, f16 d), the rows' bytes first and their scales after them (one page)."""
         s = self.shape
         full = self._normal(layer, name, (self.kv_rows * self.ncard, s.nkv, s.hd), 1.0).half()
-        if self.ncard == 1:
-            return self._t(full.view(torch.int16))
-        r = torch.arange(self.kv_rows, device=self.dev)
-        return self._t(full[((r // 4) * self.ncard + self.card) * 4 + r % 4].view(torch.int16))
+        if self.ncard > 1:
+            r = torch.arange(self.kv_rows, device=self.dev)
+            full = full[((r // 4) * self.ncard + self.card) * 4 + r % 4]
+        if not s.kv_q8:
+            return self._t(full.contiguous().view(torch.int16))
+        g = full.float().reshape(self.kv_rows, -1, 32)
+        d = g.abs().amax(-1) / 127.0
+        y = g * torch.where(d != 0, 1.0 / d, torch.zeros_like(d)).unsqueeze(-1)
+        q = (torch.sign(y) * torch.floor(y.abs() + 0.5)).to(torch.int8)
+        words = torch.cat([q.reshape(-1).view(torch.int16), d.half().reshape(-1).view(torch.int16)])
+        assert words.numel() == L.load().fnx_kvq_halves(self.kv_rows, s.nkv, s.hd)
+        return self._t(words)
 
     def _idx(self, lst):
         return torch.tensor(lst, dtype=torch.long, device=self.dev)
@@ -163,7 +172,7 @@ class SyntheticStack:
             kc, vc = self._kv_slice(l, "kc"), self._kv_slice(l, "vc")
             Lr.kc, Lr.vc = kc.data_ptr(), vc.data_ptr()
             self.named[(l, "kc")], self.named[(l, "vc")] = kc, vc
-            Lr.pages = L.KvPages(None, 0, 0, self.kv_rows)
+            Lr.pages = L.KvPages(None, 0, 0, self.kv_rows, 1 if s.kv_q8 else 0)
         # FFN
         self.named[(l, "router")] = self._t(self._normal(l, "router", (s.nexp + 1, s.n), s.sigma))
         Lr.router = self.named[(l, "router")].data_ptr()

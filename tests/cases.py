@@ -155,18 +155,50 @@ def attn_case(T, ctx, nq=24, nkv=4, hd=256, ncard=1, seed=0, ramp=None):
     return c
 
 
+def kv_q8_rows(x):
+    """Rows [rows][nkv][hd] (any float type) as an int8 cache: groups of 32 with d = max |x| / 127, q = round-half-away(x / d),
+    f16 d (reference src/kernels.cu:1561-1566), laid out as one page: the int8 rows, then the rows' scales; returned as
+    the uint16 words the entry points take."""
+    rows = x.shape[0]
+    g = x.astype(np.float32).reshape(rows, -1, 32)
+    d = (np.abs(g).max(-1) / np.float32(127)).astype(np.float32)
+    inv = np.where(d != 0, np.float32(1) / np.where(d != 0, d, np.float32(1)), np.float32(0)).astype(np.float32)
+    y = g * inv[..., None]
+    q = (np.sign(y) * np.floor(np.abs(y) + np.float32(0.5))).astype(np.int8)
+    return np.concatenate([q.reshape(-1).view(np.uint16), d.astype(np.float16).reshape(-1).view(np.uint16)])
+
+
+def kv_q8_values(words, rows, nkv, hd):
+    """The f32 values an int8 cache holds: [rows][nkv][hd]."""
+    n = rows * nkv * hd
+    q = words[:n // 2].view(np.int8).astype(np.float32).reshape(rows, -1, 32)
+    d = words[n // 2:n // 2 + n // 32].view(np.float16).astype(np.float32).reshape(rows, -1)
+    return (q * d[..., None]).reshape(rows, nkv, hd)
+
+
+def attn_case_q8(c):
+    """The same case with int8 K/V caches (the cached rows quantised as the append would have)."""
+    c = dict(c)
+    c["q8_rows"] = c["kc"][0].shape[0]
+    c["kc"] = [kv_q8_rows(k.view(np.float16)) for k in c["kc"]]
+    c["vc"] = [kv_q8_rows(v.view(np.float16)) for v in c["vc"]]
+    return c
+
+
 def attn_oracle(c):
     """Runs prep + append + partials + merge per GPU on copies; returns qg/k after prep, the caches, partials, out."""
     T, nq, nkv, hd, ncard = c["T"], c["nq"], c["nkv"], c["hd"], c["ncard"]
     r = {"kc": [], "vc": [], "part": []}
+    q8 = c.get("q8_rows", 0)
     for card in range(ncard):
         qg, k = c["qg"].copy(), c["k"].copy()
         kc, vc = c["kc"][card].copy(), c["vc"][card].copy()
-        O.attn_prep_append(qg, k, c["v"], c["qn"], c["kn"], kc, vc, card, ncard, c["pos0"], c["eps"], c["rope_base"], nq, nkv, hd)
+        O.attn_prep_append(qg, k, c["v"], c["qn"], c["kn"], kc, vc, card, ncard, c["pos0"], c["eps"], c["rope_base"], nq, nkv, hd,
+                           q8_rows=q8)
         r["qg"], r["k"] = qg, k
         r["kc"].append(kc)
         r["vc"].append(vc)
-        r["part"].append(O.attn_partial(qg, kc, vc, card, ncard, c["pos0"], nq, nkv, hd))
+        r["part"].append(O.attn_partial(qg, kc, vc, card, ncard, c["pos0"], nq, nkv, hd, q8_rows=q8))
     r["out"] = O.attn_merge(r["part"], r["qg"], nq, hd)
     return r
 

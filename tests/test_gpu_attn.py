@@ -29,7 +29,9 @@ def _run(c, entry="fnx_attn_partial_exact", known_rows=False):
             stale = np.full((70,) + hk.shape[1:], 0x7E00, np.uint16)
             hk, hv = np.concatenate([hk, stale]), np.concatenate([hv, stale])
         kc, vc = G.dev(hk), G.dev(hv)
-        g = L.KvPages(None, 0, 0, hk.shape[0] if known_rows else 0)
+        g = L.KvPages(None, 0, 0, hk.shape[0] if known_rows else 0, 0)
+        if c.get("q8_rows"):
+            g = L.KvPages(None, 0, 0, c["q8_rows"], 1)
         L.call("fnx_attn_prep_append", qg.data_ptr(), k.data_ptr(), v.data_ptr(), qn.data_ptr(), kn.data_ptr(), kc.data_ptr(),
                vc.data_ptr(), g, card, ncard, T, pos0.data_ptr(), c["eps"], L.Rope(c["rope_base"], 64), nq, nkv, hd, st)
         scratch = G.zeros(L.load().fnx_attn_scratch_floats(nq, hd, T))
@@ -60,6 +62,21 @@ def test_attention_exact(T, ctx, ncard, hd):
         assert np.array_equal(got["kc"][card], ref["kc"][card]) and np.array_equal(got["vc"][card], ref["vc"][card]), "append"
         assert np.array_equal(got["part"][card].view(np.uint32), ref["part"][card].view(np.uint32)), "partials"
     assert np.array_equal(got["out"].view(np.uint32), ref["out"].view(np.uint32)), "merged, gated output"
+
+
+@pytest.mark.parametrize("T,ctx,ncard,hd", [(16, 1000, 1, 256), (3, 5, 1, 256), (16, 2077, 2, 256), (5, 515, 4, 128), (1, 0, 1, 256)])
+def test_attention_int8_kv(T, ctx, ncard, hd):
+    """int8 K/V rows (reference kv_q8: groups of 32 with an f16 scale): the appended rows' bytes and scales, the partials of
+    the exact-order scan over them and the merged output, bit for bit against the oracle; fnx_attn_partial hands an int8
+    cache to the same scan."""
+    c = cases.attn_case_q8(cases.attn_case(T=T, ctx=ctx, nq=8 if hd == 128 else 24, nkv=2 if hd == 128 else 4, hd=hd, ncard=ncard, seed=50 + T))
+    ref = cases.attn_oracle(c)
+    for entry in ("fnx_attn_partial_exact", "fnx_attn_partial"):
+        got = _run(c, entry)
+        for card in range(ncard):
+            assert np.array_equal(got["kc"][card], ref["kc"][card]) and np.array_equal(got["vc"][card], ref["vc"][card]), "append"
+            assert np.array_equal(got["part"][card].view(np.uint32), ref["part"][card].view(np.uint32)), "partials"
+        assert np.array_equal(got["out"].view(np.uint32), ref["out"].view(np.uint32)), "merged, gated output"
 
 
 @pytest.mark.parametrize("T,ctx,ncard,hd", [(16, 3000, 1, 256), (16, 70, 1, 256), (7, 1500, 2, 256), (5, 515, 4, 128), (1, 0, 1, 256),

@@ -40,7 +40,7 @@ class OracleStack:
 
     def __init__(self, stack):
         self.s, self.h = stack.shape, _host(stack)
-        self.nk, self.nv, self.ffs = stack.nk, stack.nv, stack.ffs
+        self.nk, self.nv, self.ffs, self.kv_rows = stack.nk, stack.nv, stack.ffs, stack.kv_rows
         self.state = {k: v.copy() for k, v in self.h.items() if k[1] in ("S", "hist", "kc", "vc")}
         self.last = None
 
@@ -71,8 +71,9 @@ class OracleStack:
                 v = O.q8s_gemv(*_q8s(h, (l, "wv")), xq, T).reshape(T, s.nkv, s.hd)
                 kc, vc = self.state[(l, "kc")].view(np.uint16), self.state[(l, "vc")].view(np.uint16)
                 hd1 = np.ones(s.hd, np.float32)
-                O.attn_prep_append(qg, k, v, hd1, hd1, kc, vc, 0, 1, pos0, s.eps, s.rope_base, s.nq, s.nkv, s.hd, s.nrot)
-                part = O.attn_partial(qg, kc, vc, 0, 1, pos0, s.nq, s.nkv, s.hd)
+                q8_rows = self.kv_rows if s.kv_q8 else 0
+                O.attn_prep_append(qg, k, v, hd1, hd1, kc, vc, 0, 1, pos0, s.eps, s.rope_base, s.nq, s.nkv, s.hd, s.nrot, q8_rows=q8_rows)
+                part = O.attn_partial(qg, kc, vc, 0, 1, pos0, s.nq, s.nkv, s.hd, q8_rows=q8_rows)
                 att = O.attn_merge([part], qg, s.nq, s.hd)
                 bo = O.q8s_gemv(*_q8s(h, (l, "wo")), O.quantize_q8_1(att.reshape(T, -1)), T)
             x = x + bo
@@ -99,11 +100,11 @@ class OracleStack:
             O.gdn_rollback(self.state[(l, "S")], self.state[(l, "hist")], snap, hsnap, np.array([0, tag], np.int32), self.nk, self.nv, T, n)
 
 
-def _make(kinds, seed, experts="q4k"):
+def _make(kinds, seed, experts="q4k", kv_q8=False):
     from sfnx_b200.window import StackShape, SyntheticStack, WindowRunner
 
     shape = StackShape(n=512, nexp=32, topk=4, ff=256, nkh=2, nvh=4, nq=4, nkv=2, hd=128, nrot=64, vocab=2048, kinds=kinds, ctx=300,
-                       kv_slack=256, experts=experts)
+                       kv_slack=256, experts=experts, kv_q8=kv_q8)
     stack = SyntheticStack(shape, seed=seed, device="cuda:0")
     return shape, stack, WindowRunner(stack, 16, graph=True), OracleStack(stack)
 
@@ -166,6 +167,14 @@ def test_window_q8_0_experts_bit_exact(monkeypatch):
     monkeypatch.setenv("FNX_ATTN_EXACT", "1")
     shape, stack, runner, orc = _make([0, 1], seed=8, experts="q8_0")
     _, total = _run_windows(shape, stack, runner, orc, nwin=3, seed=3, exact=True)
+    assert 3 <= total <= 48
+
+
+def test_window_int8_kv_bit_exact():
+    """Whole windows over int8 K/V caches (the reference's kv_q8): the append, the scan and everything after it, bit for
+    bit; an int8 cache always takes the exact-order scan, so no switch is needed."""
+    shape, stack, runner, orc = _make([0, 1, 0, 1], seed=9, kv_q8=True)
+    _, total = _run_windows(shape, stack, runner, orc, nwin=3, seed=4, exact=True)
     assert 3 <= total <= 48
 
 

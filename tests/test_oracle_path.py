@@ -240,6 +240,44 @@ def test_attention_position_split_matches_single(oracle):
             assert np.allclose(one["out"][t, h], o, rtol=2e-4, atol=2e-5)
 
 
+def test_attention_int8_kv(oracle):
+    """int8 K/V rows (reference kv_q8): the oracle's append writes the bytes numpy's statement of the quantiser gives, the
+    scan over them equals a float64 softmax attention over the values the cache holds, and its result stays within the
+    quantisation error of the f16 cache's."""
+    T, ctx, nq, nkv, hd = 3, 203, 4, 2, 128
+    for ncard in (1, 2):
+        c16 = cases.attn_case(T=T, ctx=ctx, nq=nq, nkv=nkv, hd=hd, ncard=ncard, seed=13)
+        c8 = cases.attn_case_q8(c16)
+        r16, r8 = cases.attn_oracle(c16), cases.attn_oracle(c8)
+        rows = c8["q8_rows"]
+        for card in range(ncard):
+            # the appended rows: quantised from the normed, rotated k and from v as numpy quantises them
+            want_k, want_v = c8["kc"][card].copy(), c8["vc"][card].copy()
+            for t in range(T):
+                p = ctx + t
+                if (p // 4) % ncard != card:
+                    continue
+                row = (p // 4 // ncard) * 4 + p % 4
+                for want, src in ((want_k, r8["k"][t]), (want_v, c8["v"][t])):
+                    one = cases.kv_q8_rows(src[None])
+                    n = nkv * hd
+                    want[row * n // 2:(row + 1) * n // 2] = one[:n // 2]
+                    want[rows * n // 2 + row * n // 32:rows * n // 2 + (row + 1) * n // 32] = one[n // 2:]
+            assert np.array_equal(r8["kc"][card], want_k) and np.array_equal(r8["vc"][card], want_v)
+        assert np.abs(r8["out"] - r16["out"]).max() < 0.05 and not np.array_equal(r8["out"], r16["out"])
+        if ncard == 1:
+            kc = cases.kv_q8_values(r8["kc"][0], rows, nkv, hd).astype(np.float64)
+            vc = cases.kv_q8_values(r8["vc"][0], rows, nkv, hd).astype(np.float64)
+            qg = r8["qg"].astype(np.float64)
+            for t in range(T):
+                for h in range(nq):
+                    L = ctx + t + 1
+                    s = kc[:L, h // 2] @ qg[t, h, :hd] / np.sqrt(hd)
+                    w = np.exp(s - s.max())
+                    o = (w[:, None] * vc[:L, h // 2]).sum(0) / w.sum() / (1 + np.exp(-qg[t, h, hd:]))
+                    assert np.allclose(r8["out"][t, h], o, rtol=2e-4, atol=2e-5)
+
+
 def test_moe_layer_against_dequantised_float64(oracle):
     """The quantised FFN half equals, to quantisation error of the activations, the float64 product of the dequantised
     weights (the kind of check the reference's moe_mma_bench makes, tools/moe_mma_bench.cu:198-224)."""
