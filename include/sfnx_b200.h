@@ -276,6 +276,21 @@ int fnx_attn_splits(int nkv);
 int fnx_attn_finish(const float* parts, int nparts, int first_part, const float* qg, float* out, int T, int nq, int h0, int nh,
                     int hd, void* st);
 
+/* ---- hyper-connections of the residual streams (R: [T][hc][n], hc streams of width n)
+ * reference src/kernels.hpp:356 hc_write (src/kernels.cu:1493-1503): R[t][c] += bo[t] * 2 sigmoid(inj[t][c] / hc) */
+int fnx_hc_write(float* R, const float* bo, const float* inj, int T, int n, int hc, void* st);
+/* reference src/kernels.hpp:51-66 hc_read / hc_scratch_floats (src/hc.cuh k_hc): the read with the previous half's write
+ * folded in when bo_prev is not null (R' = R + bo_prev * 2 sigmoid(inj_prev / hc), R <- R'):
+ *   mixed[t] = mean over the streams of xn_c * sigmoid(w_up_c . lo),  lo = silu(w_down . xn / hc) as int8 per 32,
+ *   xn = R' w_norm rs (rs the stream's RMS factor), inject[t][c] = w_inj[c] . xn when w_inj (bf16 [hc][hc n]) is given;
+ *   mixed also as q8_1 rows into q8 when not null.  w_down: split Q8_0 [lr][hc n]; w_up: split Q8_0 [hc n][lr].
+ * The reference's single launch holds two grid-wide spin barriers (every block resident, nothing else on the GPU,
+ * err bit 4 on a timeout); here the read is three launches in stream order, so it has no barrier, takes no err word
+ * and may run beside other streams' work.  scratch: fnx_hc_scratch_floats floats, never read before written. */
+size_t fnx_hc_scratch_floats(int T, int n, int hc, int lr);
+int fnx_hc_read(float* R, const float* bo_prev, const float* inj_prev, const float* w_norm, FnxQ8S w_down, FnxQ8S w_up, const uint16_t* w_inj,
+                float eps, float* mixed, float* inject, float* scratch, void* q8, int T, int n, int hc, int lr, void* st);
+
 /* ---- sum across GPUs */
 /* all-reduce(sum) of x[rows][row_len] in the reference ring's order, chunk c = float pairs [c NP / n, (c + 1) NP / n) of
  * every row (NP = row_len / 2) summed as ((x_c + x_{c+1}) + ...) + x_{c+n-1} (reference src/kernels.hpp:321-353 ring_sum / Ring, src/kernels.cu:755-868

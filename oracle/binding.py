@@ -331,6 +331,27 @@ def attn_merge(parts, qg, nq, hd=256):
     return out
 
 
+# ---------------------------------------------------------------- hyper-connections
+def hc_write(R, bo, inj):
+    """R [T][hc][n] += bo [T][n] * 2 sigmoid(inj [T][hc] / hc), in place."""
+    T, hc, n = R.shape
+    lib().orc_hc_write(P(R), P(_f32(bo)), P(_f32(inj)), T, n, hc)
+
+
+def hc_read(R, w_norm, down, up, eps, bo_prev=None, inj_prev=None, w_inj=None, want_q8=False):
+    """The read (R updated in place when bo_prev is given).  down = (int8 [lr][hc n], f16 bits [lr][hc n / 32]),
+    up = (int8 [hc n][lr], f16 bits [hc n][lr / 32]), w_inj bf16 bits [hc][hc n] or None.  Returns mixed [T][n],
+    inject [T][hc] (None without w_inj), q8_1 rows of mixed (None unless asked)."""
+    T, hc, n = R.shape
+    lr = down[0].shape[0]
+    mixed = np.zeros((T, n), np.float32)
+    inject = np.zeros((T, hc), np.float32) if w_inj is not None else None
+    q8 = np.zeros((T, n // 32 * Q81_B), np.uint8) if want_q8 else None
+    lib().orc_hc_read(P(R), P(bo_prev), P(inj_prev), P(w_norm), P(down[0]), P(down[1]), P(up[0]), P(up[1]), P(w_inj), C.c_float(eps), P(mixed),
+                      P(inject), P(q8), T, n, hc, lr)
+    return mixed, inject, q8
+
+
 # ---------------------------------------------------------------- head and acceptance
 def argmax(logits, v0=0):
     logits = _f32(logits)

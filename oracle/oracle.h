@@ -110,6 +110,12 @@ void orc_attn_partial(const float* qg, const o_half* kc, const o_half* vc, const
                       int T, int pos0, int nq, int nkv, int hd);
 void orc_attn_merge(const float* const* parts, const float* qg, float* out, int ncard, int T, int nq, int hd);
 
+/* hyper-connections (ohc.c) */
+void orc_hc_write(float* R, const float* bo, const float* inj, int T, int n, int hc);
+void orc_hc_read(float* R, const float* bo_prev, const float* inj_prev, const float* w_norm, const int8_t* down_q, const o_half* down_d,
+                 const int8_t* up_q, const o_half* up_d, const uint16_t* w_inj, float eps, float* mixed, float* inject, uint8_t* q8, int T,
+                 int n, int hc, int lr);
+
 /* head, acceptance, ring order */
 unsigned orc_argmax(const float* logits, int rows, int T, int v0, float* best_v, int* best_i);
 void orc_argmax_merge(const float* best_v, const int* best_i, int nslice, int T, int* out);

@@ -126,6 +126,8 @@ _SIGS = {
     "fnx_l2_prefetch": [_p, _z, _p],
     "fnx_gdn_core_log": [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _p, _i, _f, _p],
     "fnx_gdn_replay": [_p, _i, _i, _p],
+    "fnx_hc_write": [_p, _p, _p, _i, _i, _i, _p],
+    "fnx_hc_read": [_p, _p, _p, _p, Q8S, Q8S, _p, _f, _p, _p, _p, _p, _i, _i, _i, _i, _p],
     "fnx_attn_prep_append": [_p, _p, _p, _p, _p, _p, _p, KvPages, _i, _i, _i, _p, _f, Rope, _i, _i, _i, _p],
     "fnx_attn_partial": [_p, _p, _p, KvPages, _p, _i, _i, _i, _p, _i, _i, _i, _p, _p],
     "fnx_attn_partial_exact": [_p, _p, _p, KvPages, _p, _i, _i, _i, _p, _i, _i, _i, _p, _p],
@@ -161,6 +163,7 @@ _OTHER = {
     "fnx_gdn_log_floats": (_z, [_i, _i]),
     "fnx_attn_scratch_floats": (_z, [_i, _i, _i]),
     "fnx_kvq_halves": (_z, [_i, _i, _i]),
+    "fnx_hc_scratch_floats": (_z, [_i, _i, _i, _i]),
     "fnx_kv_rows_per_card": (_i, [_i, _i]),
     "fnx_attn_splits": (_i, [_i]),
     "fnx_window_workspace_bytes": (_z, [_p]),

@@ -217,3 +217,20 @@ def kl_top64(ref, new):
         vb = np.where(np.isin(union, ib), b[union], b[ib[-1]]) - lb
         out.append(float(np.sum(np.exp(va) * (va - vb))))
     return np.array(out)
+
+
+# ---------------------------------------------------------------- hyper-connections
+def hc_case(T, n, hc, lr, seed, fold=True, inject=True):
+    """Residual streams R [T][hc][n], the norm weights, split Q8_0 down [lr][hc n] and up [hc n][lr] (random int8 codes
+    and f16 scales), bf16 inject rows, and the previous half's output and inject values when its write is folded in."""
+    rng = np.random.default_rng(seed)
+    D = n * hc
+    c = {"T": T, "n": n, "hc": hc, "lr": lr, "eps": 1e-6}
+    c["R"] = rng.standard_normal((T, hc, n)).astype(np.float32)
+    c["w_norm"] = (1 + 0.1 * rng.standard_normal(D)).astype(np.float32)
+    c["down"] = (rng.integers(-127, 128, (lr, D), dtype=np.int8), (0.02 * rng.random((lr, D // 32)) / 127).astype(np.float16).view(np.uint16))
+    c["up"] = (rng.integers(-127, 128, (D, lr), dtype=np.int8), (0.3 * rng.random((D, lr // 32)) / 127).astype(np.float16).view(np.uint16))
+    c["w_inj"] = (rng.standard_normal((hc, D)).astype(np.float32).view(np.uint32) >> 16).astype(np.uint16) if inject else None
+    c["bo"] = rng.standard_normal((T, n)).astype(np.float32) if fold else None
+    c["inj_prev"] = rng.standard_normal((T, hc)).astype(np.float32) if fold else None
+    return c

@@ -300,3 +300,43 @@ def test_moe_layer_against_dequantised_float64(oracle):
             acc += r["topw"][t, k] * r["part"][t * 4 + k]
         acc += r["sh"][t] / (1 + np.exp(-r["logits"][t, nexp]))
         assert np.allclose(r["out"][t], acc, rtol=1e-4, atol=1e-5)
+
+
+def test_hyper_connections_against_float64(oracle):
+    """The hyper-connection write and read: the oracle against a float64 statement of the same mixing with the same int8
+    roundings of xs and lo (taken from a first float64 pass), to f32 rounding."""
+    c = cases.hc_case(T=3, n=1024, hc=4, lr=64, seed=21)
+    T, n, hc, lr = c["T"], c["n"], c["hc"], c["lr"]
+    R = c["R"].copy()
+    oracle.hc_write(R, c["bo"], c["inj_prev"])
+    g = 2.0 / (1.0 + np.exp(-c["inj_prev"].astype(np.float64) / hc))
+    want = c["R"].astype(np.float64) + c["bo"].astype(np.float64)[:, None, :] * g[:, :, None]
+    assert np.allclose(R, want, rtol=1e-6, atol=1e-6)
+    R2 = c["R"].copy()
+    mixed, inject, q8 = oracle.hc_read(R2, c["w_norm"], c["down"], c["up"], c["eps"], c["bo"], c["inj_prev"], c["w_inj"], want_q8=True)
+    assert np.allclose(R2, want, rtol=1e-6, atol=1e-6), "the folded write"
+    assert np.array_equal(q8, oracle.quantize_q8_1(mixed))
+    # float64 restatement
+    Rp = R2.astype(np.float64).reshape(T, hc * n)
+    xs = Rp * c["w_norm"]
+    rs = 1.0 / np.sqrt((R2.astype(np.float64) ** 2).mean(-1) + c["eps"])                # [T][hc]
+    xb = xs.reshape(T, -1, 32)
+    xd = np.abs(xb).max(-1) / 127
+    xq = np.round(xb / np.where(xd == 0, 1, xd)[..., None])
+    dw = c["down"][0].astype(np.float64).reshape(lr, -1, 32) * c["down"][1].view(np.float16).astype(np.float64)[..., None]
+    xdq = (xq * xd[..., None]).reshape(T, hc, n)
+    lo_pre = np.einsum("rcn,tcn,tc->tr", dw.reshape(lr, hc, n), xdq, rs) / hc
+    lo = lo_pre / (1 + np.exp(-lo_pre))
+    lb = lo.reshape(T, -1, 32)
+    ld = np.abs(lb).max(-1) / 127
+    lq = np.round(lb / ld[..., None]) * ld[..., None]
+    uw = c["up"][0].astype(np.float64).reshape(hc * n, -1, 32) * c["up"][1].view(np.float16).astype(np.float64)[..., None]
+    gate = 1 / (1 + np.exp(-(uw.reshape(hc * n, lr) @ lq.reshape(T, lr).T).T))          # [T][hc n]
+    xn = (xs.reshape(T, hc, n) * rs[..., None]).reshape(T, hc * n)
+    ref = (gate * xn).reshape(T, hc, n).mean(1)
+    # a rounding of xs or lo that falls the other way in float64 moves one code by one step: compare in the bulk
+    err = np.abs(mixed - ref)
+    assert np.median(err) < 2e-5 and np.quantile(err, 0.99) < 5e-3, (np.median(err), err.max())
+    wi = (c["w_inj"].astype(np.uint32) << 16).view(np.float32).astype(np.float64)
+    inj = np.einsum("jcn,tcn,tc->tj", wi.reshape(hc, hc, n), xs.reshape(T, hc, n), rs)
+    assert np.allclose(inject, inj, rtol=1e-4, atol=1e-4)
