@@ -86,14 +86,19 @@ def accepted_from_draws(seed, nwindows):
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons of one GPU (by UUID) with nvidia-smi while the timed regions run; read-only."""
-    Q = "clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown," \
+    """Samples SM clocks and throttle reasons of one GPU (by UUID) with nvidia-smi; read-only.  One process on rank 0 only
+    (several pollers on one box contend for the driver and disturb the ranks they are meant to watch), started early
+    because nvidia-smi takes a second to come up on a box of eight GPUs; only the samples whose timestamps fall inside
+    the timed regions (mark_begin .. mark_end) are used."""
+    Q = "timestamp,clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown," \
         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
 
-    def __init__(self, gpu_id):
-        self.gpu_id, self.proc, self.lines = gpu_id, None, []
+    def __init__(self, gpu_id, enabled=True):
+        self.gpu_id, self.proc, self.lines, self.enabled, self.t0, self.t1 = gpu_id, None, [], enabled, None, None
 
     def start(self):
+        if not self.enabled:
+            return
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.gpu_id), "--query-gpu=" + self.Q, "--format=csv,noheader,nounits",
                                           "-lms", "50"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
@@ -102,7 +107,18 @@ class ClockSampler:
         except OSError:
             self.proc = None
 
+    def mark_begin(self):
+        import datetime
+        self.t0 = datetime.datetime.now()
+
+    def mark_end(self):
+        import datetime
+        self.t1 = datetime.datetime.now()
+
     def stop(self):
+        import datetime
+        if not self.enabled:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "note": "sampled on rank 0 only"}
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
@@ -110,11 +126,17 @@ class ClockSampler:
         sm, mx, reasons = [], None, set()
         for ln in self.lines:
             f = [v.strip() for v in ln.split(",")]
-            if len(f) < 6 or not f[0].isdigit():
+            if len(f) < 7 or not f[1].isdigit():
                 continue
-            sm.append(int(f[0]))
-            mx = int(f[1])
-            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[2:6]):
+            try:
+                ts = datetime.datetime.strptime(f[0], "%Y/%m/%d %H:%M:%S.%f")
+            except ValueError:
+                continue
+            if (self.t0 and ts < self.t0) or (self.t1 and ts > self.t1):
+                continue
+            sm.append(int(f[1]))
+            mx = int(f[2])
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[3:7]):
                 if v.lower().startswith("active"):
                     reasons.add(name)
         sm.sort()
@@ -284,7 +306,8 @@ def main():
     d_ids = [torch.tensor([rec[s][q][0] for s in range(nsteps)], dtype=torch.int32, device=stack.dev) for q in range(nseq)]
     d_ctl = [torch.tensor([[rec[s][q][1], rec[s][q][2]] for s in range(nsteps)], dtype=torch.int32, device=stack.dev) for q in range(nseq)]
     gpu_uuid = str(torch.cuda.get_device_properties(local).uuid)
-    clocks = ClockSampler(gpu_uuid if gpu_uuid.startswith("GPU-") else "GPU-" + gpu_uuid)
+    clocks = ClockSampler(gpu_uuid if gpu_uuid.startswith("GPU-") else "GPU-" + gpu_uuid, enabled=rank == 0)
+    clocks.start()
 
     def device_step(i):
         for q in range(nseq):
@@ -300,7 +323,7 @@ def main():
                    r.h_jobs.data_ptr() + (i % 64) * r.job_bytes, main_stream.cuda_stream)
 
     load_all(state0)
-    clocks.start()
+    clocks.mark_begin()
     for i in range(args.warmup):
         device_step(i)
     barrier()
@@ -357,6 +380,7 @@ def main():
     barrier()
     e2e_seg = max_over_ranks(e2e_seg)
     e2e_ms = sorted(e2e_seg)[len(e2e_seg) // 2]
+    clocks.mark_end()
     clk = clocks.stop()
     assert diverged is None, "the replay diverged from the recorded windows: (step, sequence, accepted, recorded) = %s" % (diverged,)
 

@@ -309,6 +309,16 @@ typedef struct FnxRing {
     unsigned spin_limit;
 } FnxRing;
 int fnx_ring_sum(float* x, int rows, int row_len, const FnxRing* ring, unsigned* err, void* st);
+/* The attention layer's merge across GPUs, the gate and the q8_1 rows for the output projection in one launch (reference
+ * src/kernels.cu:609-672 k_att_merge over its ring, :621-672 the gate; src/kernels.hpp:230-236 attn): this GPU's partials
+ * part [T][nq][hd + 2] are published in its slot of the ring (which must hold T * nq * (hd + 2) floats), the peers' are
+ * read from theirs once their flags have come (bounded wait: bit 1 of *err), and the heads this GPU owns
+ * ([rank * nq / nrank, + nq / nrank)) are merged in ring order ending with this GPU.  out [T][nq / nrank][hd] and / or q8
+ * (q8_1 rows of nq / nrank * hd values) may be null.  ring null: one GPU.  Uses the ring's slots, flags and state as
+ * fnx_ring_sum does, as one more exchange in the GPUs' common order. */
+int fnx_attn_finish_ring(const float* part, const FnxRing* ring, const float* qg, float* out, void* q8, int T, int nq, int hd, unsigned* err,
+                         void* st);
+
 
 /* What lies between two halves of a layer, in one launch (the reference folds the same steps into its ring: src/kernels.hpp:
  * 308-313 RingMoe, src/kernels.cu:797-806 ring_x; the norm is its hc_read's): the ended half's addend - bo[T][n], or the

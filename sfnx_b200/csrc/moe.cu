@@ -396,13 +396,15 @@ __device__ __forceinline__ uint4 ldg_stream(const void* p) {
 // writes and reads saturated the shared-memory pipe).  A lane reads the activations of its column group from shared
 // memory once per step and applies them to both rows; the rows of a job are taken GU_TC at a time (three jobs in four
 // have one row, one in a hundred more than three) and the pipeline runs on across those passes.
-constexpr int GU_TC = 2, GU_R = 4, GU_RS = 2, GU_MAGIC = 0x4B400000, GU_RPB = GU_THREADS / 8 * GU_R;
+// GU_R rows a lane group: four where an expert has many rows (a block then covers 128), two where the FF slice of a GPU
+// leaves it a few hundred (twice the blocks, each half as long: the launch is over sooner)
+constexpr int GU_TC = 2, GU_RS = 2, GU_MAGIC = 0x4B400000;
 
 struct GuStep {   // one step's weights of a lane: two rows' header and 32 bytes of nibbles
     uint4 hdr[GU_RS], q0[GU_RS], q1[GU_RS];
 };
 
-template <int GPL>
+template <int GPL, int GU_R>
 __global__ void __launch_bounds__(GU_THREADS, 2) k_moe_gu_q4k(const uint8_t* __restrict__ A, size_t sa, int nrows, int n,
                                                           const FnxJob* __restrict__ jobs, const int* __restrict__ njobs,
                                                           const uint8_t* __restrict__ xq, float* __restrict__ out) {
@@ -419,9 +421,10 @@ __global__ void __launch_bounds__(GU_THREADS, 2) k_moe_gu_q4k(const uint8_t* __r
     int8_t* aq = reinterpret_cast<int8_t*>(smem);                              // [GU_TC][n]
     float4* ag = reinterpret_cast<float4*>(smem + (size_t) GU_TC * n);         // [GU_TC][n / 64]: d8 low, d8 high, sum low, sum high
     const size_t row_b = (size_t) n / 256 * 144;
+    constexpr int GU_RPB = GU_THREADS / 8 * GU_R;
     const int row0 = blockIdx.x * GU_RPB + (threadIdx.x >> 3) * GU_R;          // this lane group's GU_R consecutive rows
     const uint8_t* wrow = A + (size_t) jb.w * sa + (size_t) min(row0, nrows - 1) * row_b;
-    unsigned roff[GU_R];
+    unsigned roff[4] = {0u, 0u, 0u, 0u};
 #pragma unroll
     for (int rr = 0; rr < GU_R; ++rr) roff[rr] = (unsigned) ((min(row0 + rr, nrows - 1) - min(row0, nrows - 1)) * row_b);
     // step s of a pass: rows 2 (s / GPL), +1 of the lane group, column group lane8 + 8 (s % GPL)
@@ -841,18 +844,25 @@ int fnx_moe_gate_up(const FnxExperts* A, const FnxJob* jobs, const int* njobs, i
         FNX_REQUIRE(n % 512 == 0 && n / 512 >= 1 && n / 512 <= 8, "moe gate|up q4_K: %d columns (multiples of 512 up to 4096)", n);
         // blocks of 128 rows with direct 16-byte loads one step ahead (measured faster than staging the weights through
         // shared memory, by cp.async rings or bulk copies: there every operand crosses the shared-memory pipe)
-        const dim3 grid((nrows + GU_RPB - 1) / GU_RPB, njobs_max);
+        const int R = nrows <= 512 && (n / 512) % 2 == 0 ? 2 : 4, rpb = GU_THREADS / 8 * R;   // the step count must stay even
+        const dim3 grid((nrows + rpb - 1) / rpb, njobs_max);
         const size_t sm = (size_t) GU_TC * (n + (n / 64) * 16);
         const uint8_t* a = (const uint8_t*) A->a;
-#define GU_CASE(G)                                                                                                          \
-    case G:                                                                                                                 \
-        if (smem_optin(k_moe_gu_q4k<G>, sm, "moe gate|up q4_K")) return 1;                                                  \
-        launch(3, k_moe_gu_q4k<G>, grid, GU_THREADS, sm, strm(st), a, A->stride, nrows, n, jobs, njobs, (const uint8_t*) xq, gu); \
+#define GU_LAUNCH(G, RR)                                                                                                          \
+    {                                                                                                                             \
+        if (smem_optin(k_moe_gu_q4k<G, RR>, sm, "moe gate|up q4_K")) return 1;                                                    \
+        launch(3, k_moe_gu_q4k<G, RR>, grid, GU_THREADS, sm, strm(st), a, A->stride, nrows, n, jobs, njobs, (const uint8_t*) xq, gu); \
+    }
+#define GU_CASE(G)                      \
+    case G:                             \
+        if (R == 2) GU_LAUNCH(G, 2)     \
+        else GU_LAUNCH(G, 4)            \
         break;
         switch (n / 512) {
             GU_CASE(1) GU_CASE(2) GU_CASE(3) GU_CASE(4) GU_CASE(5) GU_CASE(6) GU_CASE(7) GU_CASE(8)
         }
 #undef GU_CASE
+#undef GU_LAUNCH
         return launch_ok("moe gate|up q4_K");
     }
     if (A->type == FNX_Q8_0) {

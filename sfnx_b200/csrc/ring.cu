@@ -249,6 +249,93 @@ __global__ void __launch_bounds__(BD_THREADS) k_boundary_rows(const BoundaryArgs
     }
 }
 
+
+// ---------------------------------------------------------------- the attention layer's merge across GPUs in one launch
+// Every GPU has scanned the positions it owns for every head; a head's output is the merge of the GPUs' partials in
+// ring order ending with the head's owner (reference src/kernels.cu:609-672, k_att_merge over the ring).  Here the
+// exchange is the same as the sums': a GPU publishes its partials of all heads in its slot, flags its peers, waits for
+// theirs (bounded), and reads the partials of the heads it owns straight from the peers' slots; the gate and the q8_1
+// rows for the output projection follow in the same kernel.  ring null: one GPU, the partial is the result.
+// Block (owned head, row), hd threads; part: this GPU's partials [T][nq][hd + 2] (acc, m, z).
+struct FinishArgs {
+    const float* part;
+    FnxRing ring;
+    const float* qg;
+    float* out;
+    uint8_t* q8;
+    int nq, hd, nrank;
+    unsigned* err;
+};
+
+__device__ __forceinline__ float ld_cg(const float* p) {
+    float v;
+    asm volatile("ld.global.cg.f32 %0, [%1];" : "=f"(v) : "l"(p));
+    return v;
+}
+
+__global__ void k_attn_finish_ring(const FinishArgs a) {
+    pdl_wait();
+    pdl_go();
+    const int n = a.nrank, me = n > 1 ? a.ring.rank : 0, hd = a.hd, nq = a.nq, own = gridDim.x, T = gridDim.y;
+    const int hx = blockIdx.x, t = blockIdx.y, i = threadIdx.x, h = me * own + hx;
+    const size_t psz = (size_t) T * nq * (hd + 2), at = ((size_t) t * nq + h) * (hd + 2);
+    unsigned epoch = 0;
+    int parity = 0;
+    if (n > 1) {
+        unsigned* state = a.ring.state;
+        epoch = *reinterpret_cast<volatile unsigned*>(state) + 1u;
+        parity = (int) (epoch & 1u);
+        float* mine = a.ring.slot[parity][me];
+        const int nblocks = gridDim.x * gridDim.y, b = blockIdx.y * gridDim.x + blockIdx.x;
+        for (size_t e = (size_t) b * blockDim.x + i; e < psz; e += (size_t) nblocks * blockDim.x) mine[e] = a.part[e];
+        __threadfence_system();
+        __syncthreads();
+        __shared__ bool last;
+        if (i == 0) last = atomicAdd(&state[1], 1u) == (unsigned) nblocks - 1;
+        __syncthreads();
+        if (last) {
+            __threadfence_system();
+            if (i < n && i != me) st_release_sys(a.ring.pad[i] + me, epoch);
+            if (i == 0) state[1] = 0u;
+        }
+        if (i < n && i != me) {
+            const unsigned* flag = a.ring.pad[me] + i;
+            unsigned spins = 0;
+            while ((int) (ld_acquire_sys(flag) - epoch) < 0) {
+                if (++spins >= a.ring.spin_limit) {
+                    atomicOr(a.err, 1u);
+                    break;
+                }
+                __nanosleep(64);
+            }
+        }
+        __syncthreads();
+    }
+    auto src = [&](int r) { return r == me || n == 1 ? a.part + at : a.ring.slot[parity][r] + at; };
+    const float* p1 = src((me + 1) % n);
+    float m = ld_cg(p1 + hd), z = ld_cg(p1 + hd + 1), acc = ld_cg(p1 + i);
+    for (int s = 2; s <= n; ++s) {
+        const float* p2 = src((me + s) % n);
+        const float m2 = ld_cg(p2 + hd), z2 = ld_cg(p2 + hd + 1);
+        const float mn = fmaxf(m, m2);
+        const float w1 = m == -INFINITY ? 0.f : ex_expf(fsub(m, mn)), w2 = m2 == -INFINITY ? 0.f : ex_expf(fsub(m2, mn));
+        z = ffma(w2, z2, fmul(w1, z));
+        acc = ffma(w2, ld_cg(p2 + i), fmul(w1, acc));
+        m = mn;
+    }
+    const float v = fmul(fdiv(acc, z), ex_sigmoid(a.qg[((size_t) t * nq + h) * 2 * hd + hd + i]));
+    if (a.out) a.out[((size_t) t * own + hx) * hd + i] = v;
+    if (a.q8) bd_q8_1_store(v, a.q8 + (((size_t) t * own + hx) * (hd / 32) + (i >> 5)) * 36, i & 31);
+    if (n > 1) {   // the last block out counts the exchange
+        __syncthreads();
+        if (i == 0 && atomicAdd(&a.ring.state[2], 1u) == gridDim.x * gridDim.y - 1) {
+            a.ring.state[2] = 0u;
+            __threadfence();
+            *reinterpret_cast<volatile unsigned*>(a.ring.state) = epoch;
+        }
+    }
+}
+
 }  // namespace fnxk
 
 using namespace fnxk;
@@ -291,5 +378,16 @@ int fnx_boundary_rows(float* x, const float* bo, const FnxMoeRows* moe, const Fn
     }
     launch(0, k_boundary_rows, T, BD_THREADS, 0, strm(st), a);
     return launch_ok("boundary_rows");
+}
+
+int fnx_attn_finish_ring(const float* part, const FnxRing* ring, const float* qg, float* out, void* q8, int T, int nq, int hd, unsigned* err,
+                         void* st) {
+    const int n = ring ? ring->nrank : 1;
+    FNX_REQUIRE(T >= 1 && T <= FNX_MAXT && hd % 32 == 0 && hd >= 32 && hd <= 1024, "attn_finish_ring: %d rows, head dim %d", T, hd);
+    FNX_REQUIRE(n >= 1 && n <= FNX_RING_MAX && nq % n == 0, "attn_finish_ring: %d query heads over %d GPUs", nq, n);
+    FNX_REQUIRE(!ring || (ring->rank >= 0 && ring->rank < n && ring->state && err), "attn_finish_ring: rank, state or error word missing");
+    FinishArgs a{part, ring ? *ring : FnxRing{}, qg, out, (uint8_t*) q8, nq, hd, n, err};
+    launch(0, k_attn_finish_ring, dim3(nq / n, T), hd, 0, strm(st), a);
+    return launch_ok("attn_finish_ring");
 }
 }

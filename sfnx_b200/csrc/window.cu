@@ -161,7 +161,7 @@ static int plan(const FnxStackCfg& c, const FnxLayer* L, Stage* out, int* after,
     const int sum = fused_boundaries(c) ? FNX_AFTER_NONE : FNX_AFTER_SUM_BO;   // fused: the next stage's first kernel sums
     for (int l = 0; l < c.nlayers; ++l) {
         if (L[l].kind == 1) {
-            put(l, 0, FNX_AFTER_GATHER_PARTIALS);
+            put(l, 0, fused_boundaries(c) ? FNX_AFTER_NONE : FNX_AFTER_GATHER_PARTIALS);   // fused: the finish kernel reads the peers' partials itself
             put(l, 1, sum);
         } else {
             put(l, 0, sum);
@@ -344,9 +344,15 @@ static int window_stage(const FnxStackCfg* cfg, const FnxLayer* layers, const Fn
     if (sg.part == 1) {   // attention: merge the GPUs' partials for this GPU's heads, gate, output projection
         const int own = c.nq / c.ncard;
         float* att = (float*) (b + w.att);
-        TRK("attn_finish", fnx_attn_finish((const float*) (b + w.partials), c.ncard, c.card, (const float*) (b + w.qg), att, T, c.nq,
-                                              c.card * own, own, c.hd, st));
-        TRK("quantize", fnx_quantize_q8_1(att, b + w.yq, own * c.hd, T, st));
+        if (fused) {   // one launch: exchange of the partials over peer memory (more than one GPU), merge, gate, q8_1 rows
+            const float* mine = (const float*) (b + w.partials) + (size_t) c.card * T * c.nq * (c.hd + 2);
+            TRK("attn_finish", fnx_attn_finish_ring(mine, c.ncard > 1 ? &g_ring : nullptr, (const float*) (b + w.qg), att, b + w.yq, T, c.nq, c.hd,
+                                                       (unsigned*) (b + w.err), st));
+        } else {
+            TRK("attn_finish", fnx_attn_finish((const float*) (b + w.partials), c.ncard, c.card, (const float*) (b + w.qg), att, T, c.nq,
+                                                  c.card * own, own, c.hd, st));
+            TRK("quantize", fnx_quantize_q8_1(att, b + w.yq, own * c.hd, T, st));
+        }
         TRK("wo", fnx_q8s_gemv(L.wo, c.n, own * c.hd, b + w.yq, bo, c.n, T, st));
         return 0;
     }

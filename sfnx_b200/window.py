@@ -418,7 +418,7 @@ class WindowRunner:
         # be set up)
         self.ring, self.ring_keep = None, None
         if self.dist is not None and os.environ.get("FNX_RING", "peer") != "nccl":
-            self.ring = self._make_ring(L.MAXT * s.n)
+            self.ring = self._make_ring(max(L.MAXT * s.n, L.MAXT * s.nq * (s.hd + 2)))   # a slot holds a sum's rows or a GPU's attention partials
         # the plan depends on who sums across the GPUs: the library's boundary kernel over the ring, or the caller
         L.call("fnx_window_ring", C.byref(self.ring) if self.ring is not None else None)
         after = (C.c_int * 1024)()

@@ -73,6 +73,17 @@ def test_moe_benchmark_shape_hidden_3072():
     _check(w, rng.standard_normal((16, 3072)).astype(np.float32), topk=10)
 
 
+def test_moe_benchmark_shape_slices_of_four_and_eight_gpus():
+    """The benchmark's hidden width with the FF slices a GPU of 4 or 8 holds (192 and 96 of 768): gate|up then takes two rows
+    a lane group instead of four."""
+    rng = np.random.default_rng(25)
+    for ffs in (192, 96):
+        w = cases.moe_weights(n=3072, nexp=32, ffs=ffs, seed=40 + ffs)
+        x = rng.standard_normal((16, 3072)).astype(np.float32)
+        x[5] = x[2]
+        _check(w, x, topk=10)
+
+
 def test_moe_q8_0_experts():
     """The all-Q8_0 configuration's routed experts: gate|up in the dense row-dot order, down in 32-column units; small and
     ragged shapes (FF slice 96), one row, tied routing, rows routed alike, and a job of 16 rows."""

@@ -133,3 +133,47 @@ def test_boundary_rows_equals_the_separate_steps(n, T, width, moe):
     G.sync()
     assert np.array_equal(G.host(y4).view(np.uint32), G.host(y3).view(np.uint32)) and np.array_equal(G.host(q4), G.host(q3))
     assert np.array_equal(G.host(x4), x0)
+
+
+@pytest.mark.parametrize("n,T,nq,hd", [(1, 16, 24, 256), (2, 16, 24, 256), (4, 5, 8, 128), (8, 16, 24, 256)])
+def test_attn_finish_ring_equals_the_separate_steps(n, T, nq, hd):
+    """The attention layer's exchange + merge + gate + q8_1 in one launch against fnx_attn_finish over gathered partials
+    followed by fnx_quantize_q8_1, bit for bit; the peers of one GPU are emulated (their partials and flags in place
+    before the launch).  One GPU's partial has no positions for some heads (m = -inf, z = 0)."""
+    import torch
+
+    from sfnx_b200 import lib as L
+    from tests import gpu_util as G
+
+    rng = np.random.default_rng(11 * n + T)
+    parts = rng.standard_normal((n, T, nq, hd + 2)).astype(np.float32)
+    parts[..., hd] = rng.standard_normal((n, T, nq)) * 5          # m
+    parts[..., hd + 1] = rng.random((n, T, nq)) * 100 + 0.5       # z
+    if n > 1:
+        parts[n - 1, :, ::3, :hd] = 0
+        parts[n - 1, :, ::3, hd] = -np.inf
+        parts[n - 1, :, ::3, hd + 1] = 0
+    qg = rng.standard_normal((T, nq, 2 * hd)).astype(np.float32)
+    own, st = nq // n, L.stream()
+    dparts, dqg = G.dev(parts), G.dev(qg)
+    for rank in range(n):
+        out1, q1 = G.zeros((T, own, hd)), G.zeros(T * (own * hd // 32) * 36, torch.uint8)
+        L.call("fnx_attn_finish", dparts.data_ptr(), n, rank, dqg.data_ptr(), out1.data_ptr(), T, nq, rank * own, own, hd, st)
+        L.call("fnx_quantize_q8_1", out1.data_ptr(), q1.data_ptr(), own * hd, T, st)
+        for epoch in (1, 2):
+            slots = [[G.dev(parts[k]) if (p == epoch % 2 and k != rank) else G.zeros((T, nq, hd + 2)) for p in range(2)] for k in range(n)]
+            pads = [torch.full((16,), epoch, dtype=torch.int32, device=G.DEV) for _ in range(n)]
+            state = torch.tensor([epoch - 1, 0, 0, 0], dtype=torch.int32, device=G.DEV)
+            err = G.zeros(1, torch.int32)
+            ring = _ring(L, G, torch, n, rank, slots, pads, state, 1 << 20)
+            out2, q2 = G.zeros((T, own, hd)), G.zeros(T * (own * hd // 32) * 36, torch.uint8)
+            mine = G.dev(parts[rank])
+            L.call("fnx_attn_finish_ring", mine.data_ptr(), C.byref(ring) if n > 1 else None, dqg.data_ptr(), out2.data_ptr(), q2.data_ptr(), T, nq, hd,
+                   err.data_ptr(), st)
+            G.sync()
+            assert int(G.host(err)[0]) == 0
+            assert np.array_equal(G.host(out2).view(np.uint32), G.host(out1).view(np.uint32)), (n, rank, epoch)
+            assert np.array_equal(G.host(q2), G.host(q1)), (n, rank, epoch, "q8_1")
+            if n > 1:
+                assert G.host(state).tolist()[:3] == [epoch, 0, 0]
+                assert np.array_equal(G.host(slots[rank][epoch % 2]).view(np.uint32), parts[rank].view(np.uint32)), "published partials"
