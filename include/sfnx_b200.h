@@ -309,6 +309,11 @@ typedef struct FnxRing {
     unsigned spin_limit;
 } FnxRing;
 int fnx_ring_sum(float* x, int rows, int row_len, const FnxRing* ring, unsigned* err, void* st);
+/* A small all-gather over the ring's slots, flags and state (one more exchange in the GPUs' common order): every GPU's
+ * na + nb 4-byte words (na + nb must fit a slot) to all_a [nrank][na] and all_b [nrank][nb] on every GPU.  The window's
+ * caller uses it where the plan says FNX_AFTER_GATHER_BEST: the per-GPU argmax (value, index), the 64 candidates a row.
+ * No counterpart in the reference, whose host reads every card's values itself (src/engine_common.cu:781-787). */
+int fnx_ring_gather(const void* a, int na, const void* b, int nb, const FnxRing* ring, void* all_a, void* all_b, unsigned* err, void* st);
 /* The attention layer's merge across GPUs, the gate and the q8_1 rows for the output projection in one launch (reference
  * src/kernels.cu:609-672 k_att_merge over its ring, :621-672 the gate; src/kernels.hpp:230-236 attn): this GPU's partials
  * part [T][nq][hd + 2] are published in its slot of the ring (which must hold T * nq * (hd + 2) floats), the peers' are

@@ -336,6 +336,51 @@ __global__ void k_attn_finish_ring(const FinishArgs a) {
     }
 }
 
+
+// ---------------------------------------------------------------- a small all-gather over the ring's slots
+// Every GPU's few words (the argmax (value, index) of its vocabulary range, its 64 candidates a row) to every GPU: the
+// same exchange once more - publish in the own slot, flag, bounded wait, read the peers' slots - as one block.  Two
+// arrays of 4-byte words a call; all_a [nrank][na], all_b [nrank][nb].
+__global__ void __launch_bounds__(1024) k_ring_gather(const unsigned* __restrict__ a, int na, const unsigned* __restrict__ b, int nb, const FnxRing ring,
+                                                      unsigned* __restrict__ all_a, unsigned* __restrict__ all_b, unsigned* err) {
+    pdl_wait();
+    pdl_go();
+    const int n = ring.nrank, me = ring.rank, tid = threadIdx.x;
+    unsigned* state = ring.state;
+    const unsigned epoch = *reinterpret_cast<volatile unsigned*>(state) + 1u;
+    const int parity = (int) (epoch & 1u);
+    unsigned* mine = reinterpret_cast<unsigned*>(ring.slot[parity][me]);
+    for (int i = tid; i < na + nb; i += blockDim.x) mine[i] = i < na ? a[i] : b[i - na];
+    __threadfence_system();
+    __syncthreads();
+    if (tid < n && tid != me) {
+        st_release_sys(ring.pad[tid] + me, epoch);
+        const unsigned* flag = ring.pad[me] + tid;
+        unsigned spins = 0;
+        while ((int) (ld_acquire_sys(flag) - epoch) < 0) {
+            if (++spins >= ring.spin_limit) {
+                atomicOr(err, 1u);
+                break;
+            }
+            __nanosleep(64);
+        }
+    }
+    __syncthreads();
+    for (int i = tid; i < n * (na + nb); i += blockDim.x) {
+        const int r = i / (na + nb), k = i % (na + nb);
+        unsigned v;
+        if (r == me) v = k < na ? a[k] : b[k - na];
+        else asm volatile("ld.global.cg.u32 %0, [%1];" : "=r"(v) : "l"(reinterpret_cast<const unsigned*>(ring.slot[parity][r]) + k));
+        if (k < na) all_a[(size_t) r * na + k] = v;
+        else all_b[(size_t) r * nb + (k - na)] = v;
+    }
+    __syncthreads();
+    if (tid == 0) {
+        __threadfence();
+        *reinterpret_cast<volatile unsigned*>(state) = epoch;
+    }
+}
+
 }  // namespace fnxk
 
 using namespace fnxk;
@@ -389,5 +434,13 @@ int fnx_attn_finish_ring(const float* part, const FnxRing* ring, const float* qg
     FinishArgs a{part, ring ? *ring : FnxRing{}, qg, out, (uint8_t*) q8, nq, hd, n, err};
     launch(0, k_attn_finish_ring, dim3(nq / n, T), hd, 0, strm(st), a);
     return launch_ok("attn_finish_ring");
+}
+
+int fnx_ring_gather(const void* a, int na, const void* b, int nb, const FnxRing* ring, void* all_a, void* all_b, unsigned* err, void* st) {
+    FNX_REQUIRE(ring && ring->nrank >= 2 && ring->nrank <= FNX_RING_MAX && ring->rank >= 0 && ring->rank < ring->nrank && ring->state && err,
+                "ring_gather: no ring of at least two GPUs, state or error word");
+    FNX_REQUIRE(a && all_a && na >= 1 && nb >= 0 && (nb == 0 || (b && all_b)), "ring_gather: %d + %d words without their arrays", na, nb);
+    launch(0, k_ring_gather, 1, 1024, 0, strm(st), (const unsigned*) a, na, (const unsigned*) b, nb, *ring, (unsigned*) all_a, (unsigned*) all_b, err);
+    return launch_ok("ring_gather");
 }
 }

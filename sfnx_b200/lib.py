@@ -126,6 +126,7 @@ _SIGS = {
     "fnx_l2_prefetch": [_p, _z, _p],
     "fnx_gdn_core_log": [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _p, _i, _f, _p],
     "fnx_gdn_replay": [_p, _i, _i, _p],
+    "fnx_ring_gather": [_p, _i, _p, _i, _p, _p, _p, _p, _p],
     "fnx_attn_finish_ring": [_p, _p, _p, _p, _p, _i, _i, _i, _p, _p],
     "fnx_hc_write": [_p, _p, _p, _i, _i, _i, _p],
     "fnx_hc_read": [_p, _p, _p, _p, Q8S, Q8S, _p, _f, _p, _p, _p, _p, _i, _i, _i, _i, _p],

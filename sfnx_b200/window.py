@@ -514,6 +514,13 @@ class WindowRunner:
             if self.sampled:
                 self.all_cv[0].copy_(self.cand_v)
                 self.all_ci[0].copy_(self.cand_i)
+        elif self.ring is not None:   # the library's own small all-gather over the ring's slots: no NCCL call in a window
+            L.call("fnx_ring_gather", self.best_v.data_ptr(), T, self.best_i.data_ptr(), T, C.byref(self.ring), self.all_v.data_ptr(),
+                   self.all_i.data_ptr(), self.err.data_ptr(), st)
+            if self.sampled:
+                nc = T * L.TOPK_N
+                L.call("fnx_ring_gather", self.cand_v.data_ptr(), nc, self.cand_i.data_ptr(), nc, C.byref(self.ring), self.all_cv.data_ptr(),
+                       self.all_ci.data_ptr(), self.err.data_ptr(), st)
         else:
             self.dist.all_gather_into_tensor(self.all_v.view(-1), self.best_v, group=self.group)
             self.dist.all_gather_into_tensor(self.all_i.view(-1), self.best_i, group=self.group)

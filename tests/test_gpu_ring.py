@@ -177,3 +177,41 @@ def test_attn_finish_ring_equals_the_separate_steps(n, T, nq, hd):
             if n > 1:
                 assert G.host(state).tolist()[:3] == [epoch, 0, 0]
                 assert np.array_equal(G.host(slots[rank][epoch % 2]).view(np.uint32), parts[rank].view(np.uint32)), "published partials"
+
+
+@pytest.mark.parametrize("n,na,nb", [(2, 16, 16), (8, 16, 16), (4, 1024, 1024), (3, 5, 0)])
+def test_ring_gather(n, na, nb):
+    """The small all-gather over the ring's slots (the per-GPU argmax pairs, the candidates): every rank's view, with the
+    peers emulated (their words and flags in place before the launch)."""
+    import torch
+
+    from sfnx_b200 import lib as L
+    from tests import gpu_util as G
+
+    rng = np.random.default_rng(5 * n + na)
+    A = rng.standard_normal((n, na)).astype(np.float32)
+    B = rng.integers(0, 1 << 30, (n, max(nb, 1)), dtype=np.int32)[:, :nb]
+    st = L.stream()
+    for rank in range(n):
+        for epoch in (1, 2):
+            def slot(k, p):
+                t = G.zeros(4096)
+                if p == epoch % 2 and k != rank:
+                    t[:na] = G.dev(A[k])
+                    if nb:
+                        t[na:na + nb] = G.dev(B[k]).view(torch.float32)
+                return t
+            slots = [[slot(k, p) for p in range(2)] for k in range(n)]
+            pads = [torch.full((16,), epoch, dtype=torch.int32, device=G.DEV) for _ in range(n)]
+            state = torch.tensor([epoch - 1, 0, 0, 0], dtype=torch.int32, device=G.DEV)
+            err = G.zeros(1, torch.int32)
+            ring = _ring(L, G, torch, n, rank, slots, pads, state, 1 << 20)
+            a, b = G.dev(A[rank]), G.dev(np.ascontiguousarray(B[rank])) if nb else None
+            all_a, all_b = G.zeros((n, na)), G.zeros((n, max(nb, 1)), torch.int32)
+            L.call("fnx_ring_gather", a.data_ptr(), na, b.data_ptr() if nb else None, nb, C.byref(ring), all_a.data_ptr(),
+                   all_b.data_ptr() if nb else None, err.data_ptr(), st)
+            G.sync()
+            assert int(G.host(err)[0]) == 0 and G.host(state).tolist()[0] == epoch
+            assert np.array_equal(G.host(all_a).view(np.uint32), A.view(np.uint32)), (n, rank, epoch)
+            if nb:
+                assert np.array_equal(G.host(all_b)[:, :nb], B), (n, rank, epoch)
