@@ -11,10 +11,14 @@
 // peer has signalled the sum in between, which a peer does after it has finished reading the older slot.
 // Every wait is bounded: when a peer's flag does not arrive within `spin_limit` polls the kernel sets bit 1 of the
 // error word (the reference's "peer value never came", src/kernels.hpp:335) and goes on; the context stays usable.
+#include <cooperative_groups.h>
+
 #include <algorithm>
 
 #include "common.cuh"
 #include "exact_math.cuh"
+
+namespace cg = cooperative_groups;
 
 namespace fnxk {
 
@@ -26,6 +30,11 @@ __device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
     return v;
 }
 __device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) { asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory"); }
+__device__ __forceinline__ float ld_cg(const float* p) {   // peer memory: not through L1
+    float v;
+    asm volatile("ld.global.cg.f32 %0, [%1];" : "=f"(v) : "l"(p));
+    return v;
+}
 __device__ __forceinline__ float4 ld_peer(const float* p) {   // peer memory: not through L1
     float4 v;
     asm volatile("ld.global.cg.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p));
@@ -110,7 +119,7 @@ __global__ void __launch_bounds__(RS_THREADS) k_ring_sum(float* __restrict__ x, 
 // output rows, or the routed experts' rows weighted and added with the gated shared expert: reference src/kernels.cu:
 // 797-806, ring_x), the sum of the GPUs' addends in the ring's order (as k_ring_sum, over the same slots, flags and
 // state), the residual update x += sum, and the RMS norm of the new x with its q8_1 copy for the half that begins
-// (k_rms_norm_rows' order of sums).  A block per row, 1024 threads; the row stays in shared memory between the steps.
+// (k_rms_norm_rows' order of sums).  A cluster of eight blocks per row (see the kernel).
 struct BoundaryArgs {
     float* x;
     const float* bo;
@@ -123,7 +132,7 @@ struct BoundaryArgs {
     float eps;
     unsigned* err;
 };
-constexpr int BD_THREADS = 1024, BD_MAXN = 4096;
+constexpr int BD_THREADS = 1024, BD_MAXN = 4096, BD_CL = 8, BD_CT = BD_THREADS / BD_CL, BD_MAXC = BD_MAXN / BD_THREADS;
 
 __device__ __forceinline__ void bd_q8_1_store(float xi, uint8_t* blk, int lane) {
     const float amax = wmax(fabsf(xi)), sum = wsum(xi);
@@ -135,34 +144,53 @@ __device__ __forceinline__ void bd_q8_1_store(float xi, uint8_t* blk, int lane) 
     }
 }
 
-__global__ void __launch_bounds__(BD_THREADS) k_boundary_rows(const BoundaryArgs a) {
-    __shared__ __align__(16) float row[BD_MAXN];
-    __shared__ float sh[32];
+// A row is the work of 1024 "virtual" threads - thread i owns columns i, i + 1024, ... and the 32 warps' square sums are
+// added in warp order, which is k_rms_norm_rows' order of sums - spread over a cluster of eight blocks of 128 threads:
+// a row's loads (ten expert rows a column) come from eight SMs instead of one, and the norm's 32 partial sums meet
+// through distributed shared memory.  The values stay in registers between the steps.
+__global__ void __cluster_dims__(BD_CL, 1, 1) __launch_bounds__(BD_CT) k_boundary_rows(const BoundaryArgs a) {
+    cg::cluster_group cluster = cg::this_cluster();
+    __shared__ float sh[32];   // every block of the cluster gets all 32 warp sums
     __shared__ bool last;
-    const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, n = a.n, nr = a.ring.nrank, me = a.ring.rank;
+    const int t = blockIdx.x / BD_CL, cr = blockIdx.x % BD_CL, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int vt = cr * BD_CT + tid, n = a.n, nr = a.ring.nrank, me = a.ring.rank;
     float* xr = a.x + (size_t) t * n;
     pdl_wait();
     pdl_go();
     const bool has_add = a.bo || a.moe.part;
-    // ---- this GPU's addend of the row
+    // ---- this GPU's addend of the row, this thread's columns
+    float add[BD_MAXC];
+#pragma unroll
+    for (int k = 0; k < BD_MAXC; ++k) add[k] = 0.f;
     if (a.moe.part) {
         const int topk = a.moe.topk;
         const float gate = ex_sigmoid(a.moe.logits[(size_t) t * (a.moe.nexp + 1) + a.moe.nexp]);
-        for (int i = tid; i < n; i += BD_THREADS) {
-            float s = 0.f;
-            for (int k = 0; k < topk; ++k) s = ffma(a.moe.topw[t * topk + k], a.moe.part[((size_t) t * topk + k) * n + i], s);
-            row[i] = ffma(gate, a.moe.sh[(size_t) t * n + i], s);
+#pragma unroll
+        for (int k = 0; k < BD_MAXC; ++k) {
+            const int i = vt + BD_THREADS * k;
+            if (i < n) {
+                float s = 0.f;
+                for (int kk = 0; kk < topk; ++kk) s = ffma(a.moe.topw[t * topk + kk], a.moe.part[((size_t) t * topk + kk) * n + i], s);
+                add[k] = ffma(gate, a.moe.sh[(size_t) t * n + i], s);
+            }
         }
     } else if (a.bo) {
-        for (int i = tid; i < n; i += BD_THREADS) row[i] = a.bo[(size_t) t * n + i];
+#pragma unroll
+        for (int k = 0; k < BD_MAXC; ++k) {
+            const int i = vt + BD_THREADS * k;
+            if (i < n) add[k] = a.bo[(size_t) t * n + i];
+        }
     }
     if (nr > 1 && has_add) {
         unsigned* state = a.ring.state;
         const unsigned epoch = *reinterpret_cast<volatile unsigned*>(state) + 1u;
-        const int parity = (int) (epoch & 1u), n4 = n / 4;
-        __syncthreads();
-        float4* mine = reinterpret_cast<float4*>(a.ring.slot[parity][me] + (size_t) t * n);
-        for (int i = tid; i < n4; i += BD_THREADS) mine[i] = reinterpret_cast<const float4*>(row)[i];
+        const int parity = (int) (epoch & 1u);
+        float* mine = a.ring.slot[parity][me] + (size_t) t * n;
+#pragma unroll
+        for (int k = 0; k < BD_MAXC; ++k) {
+            const int i = vt + BD_THREADS * k;
+            if (i < n) mine[i] = add[k];
+        }
         __threadfence_system();
         __syncthreads();
         if (tid == 0) last = atomicAdd(&state[1], 1u) == gridDim.x - 1;
@@ -185,34 +213,22 @@ __global__ void __launch_bounds__(BD_THREADS) k_boundary_rows(const BoundaryArgs
         }
         __syncthreads();
         const int NP = n / 2;
-        auto chunk_of = [&](int p) {
-            int c = (int) ((long long) p * nr / NP);
-            while (c + 1 < nr && (long long) (c + 1) * NP / nr <= p) ++c;
-            while (c > 0 && (long long) c * NP / nr > p) --c;
-            return c;
-        };
-        for (int i = tid; i < n4; i += BD_THREADS) {
-            const int p0 = 2 * i, ca = chunk_of(p0), cb = chunk_of(p0 + 1);
-            float4 v[FNX_RING_MAX];
 #pragma unroll
-            for (int r = 0; r < FNX_RING_MAX; ++r)
-                if (r < nr) v[r] = r == me ? reinterpret_cast<const float4*>(row)[i] : ld_peer(a.ring.slot[parity][r] + (size_t) t * n + 4 * (size_t) i);
-            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-            for (int k = 0; k < FNX_RING_MAX; ++k)
-                if (k < nr) {
-                    const int ra = ca + k < nr ? ca + k : ca + k - nr, rb = cb + k < nr ? cb + k : cb + k - nr;
-                    float ax = 0.f, ay = 0.f, bz = 0.f, bw = 0.f;
-#pragma unroll
-                    for (int r = 0; r < FNX_RING_MAX; ++r) {
-                        if (r == ra) ax = v[r].x, ay = v[r].y;
-                        if (r == rb) bz = v[r].z, bw = v[r].w;
-                    }
-                    if (k == 0) acc = make_float4(ax, ay, bz, bw);
-                    else acc.x = fadd(acc.x, ax), acc.y = fadd(acc.y, ay), acc.z = fadd(acc.z, bz), acc.w = fadd(acc.w, bw);
+        for (int k = 0; k < BD_MAXC; ++k) {
+            const int i = vt + BD_THREADS * k;
+            if (i < n) {   // the chunk that holds the column's pair starts the ring's order
+                const int p = i / 2;
+                int c = (int) ((long long) p * nr / NP);
+                while (c + 1 < nr && (long long) (c + 1) * NP / nr <= p) ++c;
+                while (c > 0 && (long long) c * NP / nr > p) --c;
+                float acc = 0.f;
+                for (int kk = 0; kk < nr; ++kk) {
+                    const int r = c + kk < nr ? c + kk : c + kk - nr;
+                    const float v = r == me ? add[k] : ld_cg(a.ring.slot[parity][r] + (size_t) t * n + i);
+                    acc = kk ? fadd(acc, v) : v;
                 }
-            __syncwarp();
-            reinterpret_cast<float4*>(row)[i] = acc;   // a thread reads only its own float4 of the row above
+                add[k] = acc;
+            }
         }
         __syncthreads();
         if (tid == 0 && atomicAdd(&state[2], 1u) == gridDim.x - 1) {
@@ -221,31 +237,40 @@ __global__ void __launch_bounds__(BD_THREADS) k_boundary_rows(const BoundaryArgs
             *reinterpret_cast<volatile unsigned*>(state) = epoch;
         }
     }
-    __syncthreads();
     // ---- x += sum; RMS norm: thread i the squares of columns i, i + 1024, ... in order, warp trees, the warps in order
-    float s = 0.f;
-    for (int i = tid; i < n; i += BD_THREADS) {
-        float v = xr[i];
-        if (has_add) {
-            v = fadd(v, row[i]);
-            xr[i] = v;
+    float v[BD_MAXC], s = 0.f;
+#pragma unroll
+    for (int k = 0; k < BD_MAXC; ++k) {
+        const int i = vt + BD_THREADS * k;
+        v[k] = 0.f;
+        if (i < n) {
+            float val = xr[i];
+            if (has_add) {
+                val = fadd(val, add[k]);
+                xr[i] = val;
+            }
+            v[k] = val;
+            s = ffma(val, val, s);
         }
-        row[i] = v;
-        s = ffma(v, v, s);
     }
     s = wsum(s);
-    if (lane == 0) sh[warp] = s;
-    __syncthreads();
+    if (lane == 0) {
+#pragma unroll
+        for (int r = 0; r < BD_CL; ++r) cluster.map_shared_rank(sh, r)[cr * (BD_CT / 32) + warp] = s;
+    }
+    cluster.sync();
     float tot = 0.f;
 #pragma unroll
     for (int i = 0; i < 32; ++i) tot = fadd(tot, sh[i]);
     const float r = ex_rsqrt(fadd(fdiv(tot, (float) n), a.eps));
-    for (int i0 = 0; i0 < n; i0 += BD_THREADS) {
-        const int i = i0 + tid;
-        const bool live = i < n;
-        const float v = live ? fmul(fmul(row[i], r), a.w[i]) : 0.f;
-        if (live && a.y) a.y[(size_t) t * n + i] = v;
-        if (a.q && (i0 + warp * 32) < n) bd_q8_1_store(v, a.q + ((size_t) t * (n / 32) + (i >> 5)) * 36, lane);
+#pragma unroll
+    for (int k = 0; k < BD_MAXC; ++k) {
+        const int i = vt + BD_THREADS * k;
+        if (i - lane < n) {   // warp-uniform: a warp's 32 columns are one q8_1 block (n is a multiple of 32)
+            const float val = fmul(fmul(v[k], r), a.w[i]);
+            if (a.y) a.y[(size_t) t * n + i] = val;
+            if (a.q) bd_q8_1_store(val, a.q + ((size_t) t * (n / 32) + (i >> 5)) * 36, lane);
+        }
     }
 }
 
@@ -266,12 +291,6 @@ struct FinishArgs {
     int nq, hd, nrank;
     unsigned* err;
 };
-
-__device__ __forceinline__ float ld_cg(const float* p) {
-    float v;
-    asm volatile("ld.global.cg.f32 %0, [%1];" : "=f"(v) : "l"(p));
-    return v;
-}
 
 __global__ void k_attn_finish_ring(const FinishArgs a) {
     pdl_wait();
@@ -421,7 +440,7 @@ int fnx_boundary_rows(float* x, const float* bo, const FnxMoeRows* moe, const Fn
             FNX_REQUIRE(ring->slot[0][r] && ring->slot[1][r] && ring->pad[r], "boundary_rows: GPU %d's slots or flags are missing", r);
         a.ring = *ring;
     }
-    launch(0, k_boundary_rows, T, BD_THREADS, 0, strm(st), a);
+    launch(0, k_boundary_rows, T * BD_CL, BD_CT, 0, strm(st), a);
     return launch_ok("boundary_rows");
 }
 
