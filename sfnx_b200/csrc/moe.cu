@@ -535,8 +535,11 @@ __global__ void __launch_bounds__(GU_THREADS, 2) k_moe_gu_q4k(const uint8_t* __r
 // loads of one step in flight together, the next step's behind them) against the job's rows, GU_TC at a time, staged in
 // shared memory as an int8 plane and float scales.  With 1-2 rows per job the integer dots are a few dp4a: no tensor
 // cores here.
-constexpr int G8_R = 4, G8_RPB = GU_THREADS / 32 * 16;
+// G8_WR rows a warp (G8_R at a time): sixteen where an expert has many rows, four where a GPU's FF slice leaves it a few
+// hundred (four times the blocks, each a single pass: the launch is over sooner)
+constexpr int G8_R = 4;
 
+template <int G8_WR>
 __global__ void __launch_bounds__(GU_THREADS, 3) k_moe_gu_q8(const int8_t* __restrict__ WQ, size_t sq, const uint16_t* __restrict__ WD,
                                                             size_t sd, int nrows, int n, const FnxJob* __restrict__ jobs,
                                                             const int* __restrict__ njobs, const uint8_t* __restrict__ xq,
@@ -569,7 +572,8 @@ __global__ void __launch_bounds__(GU_THREADS, 3) k_moe_gu_q8(const int8_t* __res
         }
         __syncthreads();
 #pragma unroll 1
-        for (int r0 = blockIdx.x * G8_RPB + warp * 16; r0 < blockIdx.x * G8_RPB + warp * 16 + 16; r0 += G8_R) {
+        constexpr int G8_RPB = GU_THREADS / 32 * G8_WR;
+        for (int r0 = blockIdx.x * G8_RPB + warp * G8_WR; r0 < blockIdx.x * G8_RPB + warp * G8_WR + G8_WR; r0 += G8_R) {
             if (r0 >= nrows) break;
             float acc[G8_R][GU_TC];
 #pragma unroll
@@ -639,13 +643,16 @@ __global__ void __launch_bounds__(256) k_swiglu_q8(const float* __restrict__ gu,
 // added in ascending order (reference src/moe.cuh:330-344).
 constexpr int DN_THREADS = 256;
 
-constexpr int DN_TC = 2, DN_UPT = 3, DN_K = 4;   // activation rows a pass; weight rows a thread; row groups a block
+constexpr int DN_TC = 2, DN_UPT = 3;   // activation rows a pass; weight rows a thread
+// row groups a block (dnk): four when rows are wide, fewer for a GPU's narrow FF slice (a pass then covers many rows and
+// the blocks would be few and long)
+static int dn_groups(int nu) { return nu <= 6 ? 1 : nu <= 12 ? 2 : 4; }
 
 // Thread (u, r) takes 32-column unit u of rows r, r + RP, r + 2 RP of a row group (RP = 256 / units-per-row rows a pass),
 // so the activations of its unit are read from shared memory once per activation row and used for three weight rows:
 // the kernel is bound by the shared-memory data pipe otherwise.  Lanes run over consecutive units of consecutive rows,
 // so every plane is read in contiguous 16-, 8- and 2-byte pieces.  A block stages the job's activation rows once and
-// walks DN_K row groups, the next group's weights on their way while this group's are summed: a block's life is a
+// walks dnk row groups, the next group's weights on their way while this group's are summed: a block's life is a
 // chain of dependent global reads (job, weights, activations) and short sums, so the reads are issued as early as
 // their addresses are known.
 struct DnRaw {
@@ -661,7 +668,7 @@ __global__ void __launch_bounds__(DN_THREADS, 3) k_moe_down_q6p(const uint4* __r
                                                                const uint16_t* __restrict__ SC, const uint16_t* __restrict__ D,
                                                                size_t expert_units, int nrows, int ffs, const FnxJob* __restrict__ jobs,
                                                                const int* __restrict__ njobs, const int8_t* __restrict__ hq,
-                                                               const float* __restrict__ hd, float* __restrict__ out) {
+                                                               const float* __restrict__ hd, float* __restrict__ out, int dnk) {
     const int ji = blockIdx.y;
     extern __shared__ __align__(16) unsigned char smem[];
     __shared__ FnxJob jb;
@@ -677,7 +684,7 @@ __global__ void __launch_bounds__(DN_THREADS, 3) k_moe_down_q6p(const uint4* __r
     float* sd = reinterpret_cast<float*>(sq + (size_t) FNX_MAXT * 2 * nu);        // [jn][nu]
     int2* ss = reinterpret_cast<int2*>(sd + (size_t) FNX_MAXT * nu);              // [jn][nu]: 32 x the sums of each half
     float* part = reinterpret_cast<float*>(ss + (size_t) FNX_MAXT * nu);          // [2][DN_TC][rpb][pu]
-    const int rowB = blockIdx.x * rpb * DN_K, u = threadIdx.x % nu, r = threadIdx.x / nu;
+    const int rowB = blockIdx.x * rpb * dnk, u = threadIdx.x % nu, r = threadIdx.x / nu;
     const bool active = r < RP;
     auto load = [&](DnRaw& w, int row0) {
 #pragma unroll
@@ -715,7 +722,7 @@ __global__ void __launch_bounds__(DN_THREADS, 3) k_moe_down_q6p(const uint4* __r
     __syncthreads();
     int buf = 0;
 #pragma unroll 1
-    for (int kk = 0; kk < DN_K; ++kk) {
+    for (int kk = 0; kk < dnk; ++kk) {
         const int row0 = rowB + kk * rpb;
         if (row0 >= nrows) break;
         // this group's weights: codes 0..63 (the -32 goes through ss), kept for every pass over the job's rows
@@ -740,7 +747,7 @@ __global__ void __launch_bounds__(DN_THREADS, 3) k_moe_down_q6p(const uint4* __r
                 }
             }
         }
-        if (kk + 1 < DN_K && row0 + rpb < nrows) load(raw, row0 + rpb);
+        if (kk + 1 < dnk && row0 + rpb < nrows) load(raw, row0 + rpb);
         const int live_rows = min(rpb, nrows - row0);
 #pragma unroll 1
         for (int c0 = 0; c0 < jn; c0 += DN_TC) {
@@ -868,11 +875,18 @@ int fnx_moe_gate_up(const FnxExperts* A, const FnxJob* jobs, const int* njobs, i
     if (A->type == FNX_Q8_0) {
         FNX_REQUIRE(n % 32 == 0 && ((uintptr_t) A->a % 16) == 0 && A->stride % 16 == 0 && n % 16 == 0,
                     "moe gate|up q8_0: %d columns, planes 16-byte aligned", n);
-        const dim3 grid((nrows + G8_RPB - 1) / G8_RPB, njobs_max);
+        const int wr = nrows <= 512 ? 4 : 16, rpb = GU_THREADS / 32 * wr;
+        const dim3 grid((nrows + rpb - 1) / rpb, njobs_max);
         const size_t sm = (size_t) GU_TC * (n + (n / 32) * 4);
-        if (smem_optin(k_moe_gu_q8, sm, "moe gate|up q8_0")) return 1;
-        launch(3, k_moe_gu_q8, grid, GU_THREADS, sm, strm(st), (const int8_t*) A->a, A->stride, (const uint16_t*) A->b, A->stride_b / 2, nrows, n,
-               jobs, njobs, (const uint8_t*) xq, gu);
+        if (wr == 4) {
+            if (smem_optin(k_moe_gu_q8<4>, sm, "moe gate|up q8_0")) return 1;
+            launch(3, k_moe_gu_q8<4>, grid, GU_THREADS, sm, strm(st), (const int8_t*) A->a, A->stride, (const uint16_t*) A->b, A->stride_b / 2, nrows, n,
+                   jobs, njobs, (const uint8_t*) xq, gu);
+        } else {
+            if (smem_optin(k_moe_gu_q8<16>, sm, "moe gate|up q8_0")) return 1;
+            launch(3, k_moe_gu_q8<16>, grid, GU_THREADS, sm, strm(st), (const int8_t*) A->a, A->stride, (const uint16_t*) A->b, A->stride_b / 2, nrows, n,
+                   jobs, njobs, (const uint8_t*) xq, gu);
+        }
         return launch_ok("moe gate|up q8_0");
     }
     return fail("moe_gate_up: expert type %d not supported (Q4_K, Q8_0)", A->type);
@@ -900,9 +914,10 @@ int fnx_moe_down(const FnxExperts* A, const FnxJob* jobs, const int* njobs, int 
         const int rpb = DN_THREADS / nu * DN_UPT;
         const size_t sm = (size_t) FNX_MAXT * nu * (32 + 4 + 8) + (size_t) 2 * DN_TC * rpb * (nu + 1) * 4;
         if (smem_optin(k_moe_down_q6p<false>, sm, "moe_down q6_K")) return 1;
-        const dim3 grid((nrows + rpb * DN_K - 1) / (rpb * DN_K), njobs_max);
+        const int dnk = dn_groups(nu);
+        const dim3 grid((nrows + rpb * dnk - 1) / (rpb * dnk), njobs_max);
         launch(4, k_moe_down_q6p<false>, grid, DN_THREADS, sm, strm(st), (const uint4*) A->a, (const uint2*) A->b, (const uint16_t*) A->c,
-               (const uint16_t*) A->d, A->stride, nrows, ffs, jobs, njobs, (const int8_t*) h8, (const float*) hd, part);
+               (const uint16_t*) A->d, A->stride, nrows, ffs, jobs, njobs, (const int8_t*) h8, (const float*) hd, part, dnk);
         return launch_ok("moe_down q6_K");
     }
     if (A->type == FNX_Q8_0) {   // expert e: values at a + e stride (nrows x ffs int8), scales at b + e stride_b
@@ -913,9 +928,10 @@ int fnx_moe_down(const FnxExperts* A, const FnxJob* jobs, const int* njobs, int 
         const int rpb = DN_THREADS / nu * DN_UPT;
         const size_t sm = (size_t) FNX_MAXT * nu * (32 + 4 + 8) + (size_t) 2 * DN_TC * rpb * (nu + 1) * 4;
         if (smem_optin(k_moe_down_q6p<true>, sm, "moe_down q8_0")) return 1;
-        const dim3 grid((nrows + rpb * DN_K - 1) / (rpb * DN_K), njobs_max);
+        const int dnk = dn_groups(nu);
+        const dim3 grid((nrows + rpb * dnk - 1) / (rpb * dnk), njobs_max);
         launch(4, k_moe_down_q6p<true>, grid, DN_THREADS, sm, strm(st), (const uint4*) A->a, (const uint2*) nullptr, (const uint16_t*) nullptr,
-               (const uint16_t*) A->b, (size_t) nrows * nu, nrows, ffs, jobs, njobs, (const int8_t*) h8, (const float*) hd, part);
+               (const uint16_t*) A->b, (size_t) nrows * nu, nrows, ffs, jobs, njobs, (const int8_t*) h8, (const float*) hd, part, dnk);
         return launch_ok("moe_down q8_0");
     }
     return fail("moe_down: expert type %d not supported (Q6_K units, Q8_0)", A->type);

@@ -191,7 +191,7 @@ __global__ void __cluster_dims__(BD_CL, 1, 1) __launch_bounds__(BD_CT) k_boundar
             const int i = vt + BD_THREADS * k;
             if (i < n) mine[i] = add[k];
         }
-        __threadfence_system();
+        __threadfence();   // device scope here; the last block's system-scope fence and release below carry it to the peers
         __syncthreads();
         if (tid == 0) last = atomicAdd(&state[1], 1u) == gridDim.x - 1;
         __syncthreads();
@@ -213,20 +213,36 @@ __global__ void __cluster_dims__(BD_CL, 1, 1) __launch_bounds__(BD_CT) k_boundar
         }
         __syncthreads();
         const int NP = n / 2;
+        // every peer's value of every column of this thread first (independent loads, all in flight), then the sums
+        float pv[BD_MAXC][FNX_RING_MAX];
 #pragma unroll
         for (int k = 0; k < BD_MAXC; ++k) {
             const int i = vt + BD_THREADS * k;
-            if (i < n) {   // the chunk that holds the column's pair starts the ring's order
+#pragma unroll
+            for (int r = 0; r < FNX_RING_MAX; ++r) {
+                pv[k][r] = 0.f;
+                if (i < n && r < nr) pv[k][r] = r == me ? add[k] : ld_cg(a.ring.slot[parity][r] + (size_t) t * n + i);
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < BD_MAXC; ++k) {
+            const int i = vt + BD_THREADS * k;
+            if (i < n) {   // the chunk that holds the column's pair starts the ring's order (NP * nr fits 32 bits)
                 const int p = i / 2;
-                int c = (int) ((long long) p * nr / NP);
-                while (c + 1 < nr && (long long) (c + 1) * NP / nr <= p) ++c;
-                while (c > 0 && (long long) c * NP / nr > p) --c;
+                int c = p * nr / NP;
+                while (c + 1 < nr && (c + 1) * NP / nr <= p) ++c;
+                while (c > 0 && c * NP / nr > p) --c;
                 float acc = 0.f;
-                for (int kk = 0; kk < nr; ++kk) {
-                    const int r = c + kk < nr ? c + kk : c + kk - nr;
-                    const float v = r == me ? add[k] : ld_cg(a.ring.slot[parity][r] + (size_t) t * n + i);
-                    acc = kk ? fadd(acc, v) : v;
-                }
+#pragma unroll
+                for (int kk = 0; kk < FNX_RING_MAX; ++kk)
+                    if (kk < nr) {
+                        const int r = c + kk < nr ? c + kk : c + kk - nr;
+                        float v = 0.f;
+#pragma unroll
+                        for (int q = 0; q < FNX_RING_MAX; ++q)   // selects, not indexing: the values stay in registers
+                            if (q == r) v = pv[k][q];
+                        acc = kk ? fadd(acc, v) : v;
+                    }
                 add[k] = acc;
             }
         }
@@ -307,7 +323,7 @@ __global__ void k_attn_finish_ring(const FinishArgs a) {
         float* mine = a.ring.slot[parity][me];
         const int nblocks = gridDim.x * gridDim.y, b = blockIdx.y * gridDim.x + blockIdx.x;
         for (size_t e = (size_t) b * blockDim.x + i; e < psz; e += (size_t) nblocks * blockDim.x) mine[e] = a.part[e];
-        __threadfence_system();
+        __threadfence();   // device scope here; the last block's system-scope fence and release below carry it to the peers
         __syncthreads();
         __shared__ bool last;
         if (i == 0) last = atomicAdd(&state[1], 1u) == (unsigned) nblocks - 1;
@@ -370,7 +386,7 @@ __global__ void __launch_bounds__(1024) k_ring_gather(const unsigned* __restrict
     const int parity = (int) (epoch & 1u);
     unsigned* mine = reinterpret_cast<unsigned*>(ring.slot[parity][me]);
     for (int i = tid; i < na + nb; i += blockDim.x) mine[i] = i < na ? a[i] : b[i - na];
-    __threadfence_system();
+    __threadfence();   // the release stores below (system scope, after the barrier) carry the block's writes to the peers
     __syncthreads();
     if (tid < n && tid != me) {
         st_release_sys(ring.pad[tid] + me, epoch);
