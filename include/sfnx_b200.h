@@ -299,6 +299,11 @@ int fnx_hc_read(float* R, const float* bo_prev, const float* inj_prev, const flo
  *   pad[r]      GPU r's flag words (nrank of them, zeroed once), as addressed from this GPU
  *   state       three words of this GPU's own memory, zeroed once
  *   spin_limit  polls a wait may take before it gives up and sets bit 1 of *err
+ *   ll[p][r]    GPU r's receive area of parity p, as addressed from this GPU: nrank runs of ll_count 8-byte words, run s
+ *               written by GPU s (zeroed once).  The window's own exchanges (fnx_boundary_rows, fnx_attn_finish_ring,
+ *               fnx_ring_gather) push every value to the peers as one 8-byte store {value bits, exchange number}, as the
+ *               reference's ring stores its LL words (src/kernels.cu:755-868): a reader polls its own memory until the
+ *               number is the current one, so an exchange costs one one-way trip and needs no flags or fences.
  * x is summed in place; every GPU gets the same bits.  Capture-safe; nrank == 1 does nothing. */
 enum { FNX_RING_MAX = 8 };
 typedef struct FnxRing {
@@ -307,20 +312,22 @@ typedef struct FnxRing {
     unsigned* pad[FNX_RING_MAX];
     unsigned* state;
     unsigned spin_limit;
+    unsigned long long* ll[2][FNX_RING_MAX];
+    size_t ll_count;
 } FnxRing;
 int fnx_ring_sum(float* x, int rows, int row_len, const FnxRing* ring, unsigned* err, void* st);
-/* A small all-gather over the ring's slots, flags and state (one more exchange in the GPUs' common order): every GPU's
- * na + nb 4-byte words (na + nb must fit a slot) to all_a [nrank][na] and all_b [nrank][nb] on every GPU.  The window's
+/* A small all-gather over the ring's receive areas (one more exchange in the GPUs' common order): every GPU's
+ * na + nb 4-byte words (na + nb <= ll_count) to all_a [nrank][na] and all_b [nrank][nb] on every GPU.  The window's
  * caller uses it where the plan says FNX_AFTER_GATHER_BEST: the per-GPU argmax (value, index), the 64 candidates a row.
  * No counterpart in the reference, whose host reads every card's values itself (src/engine_common.cu:781-787). */
 int fnx_ring_gather(const void* a, int na, const void* b, int nb, const FnxRing* ring, void* all_a, void* all_b, unsigned* err, void* st);
 /* The attention layer's merge across GPUs, the gate and the q8_1 rows for the output projection in one launch (reference
  * src/kernels.cu:609-672 k_att_merge over its ring, :621-672 the gate; src/kernels.hpp:230-236 attn): this GPU's partials
- * part [T][nq][hd + 2] are published in its slot of the ring (which must hold T * nq * (hd + 2) floats), the peers' are
- * read from theirs once their flags have come (bounded wait: bit 1 of *err), and the heads this GPU owns
+ * part [T][nq][hd + 2] go to the peers' receive areas, each peer the heads it owns (ll_count >= T * nq / nrank * (hd + 2)),
+ * the peers' arrive in this GPU's (bounded wait: bit 1 of *err), and the heads this GPU owns
  * ([rank * nq / nrank, + nq / nrank)) are merged in ring order ending with this GPU.  out [T][nq / nrank][hd] and / or q8
- * (q8_1 rows of nq / nrank * hd values) may be null.  ring null: one GPU.  Uses the ring's slots, flags and state as
- * fnx_ring_sum does, as one more exchange in the GPUs' common order. */
+ * (q8_1 rows of nq / nrank * hd values) may be null.  ring null: one GPU.  One more exchange in the GPUs' common order
+ * (the ring's state counts them). */
 int fnx_attn_finish_ring(const float* part, const FnxRing* ring, const float* qg, float* out, void* q8, int T, int nq, int hd, unsigned* err,
                          void* st);
 
@@ -328,8 +335,8 @@ int fnx_attn_finish_ring(const float* part, const FnxRing* ring, const float* qg
 /* What lies between two halves of a layer, in one launch (the reference folds the same steps into its ring: src/kernels.hpp:
  * 308-313 RingMoe, src/kernels.cu:797-806 ring_x; the norm is its hc_read's): the ended half's addend - bo[T][n], or the
  * routed experts' rows weighted and added with the gated shared expert as fnx_moe_combine does (moe), or none (both null:
- * a window's first half) - summed across the GPUs as fnx_ring_sum does (ring with nrank > 1; same slots, flags and state,
- * slots of T * n floats), x += sum, then y = RMS norm of the new x with weight w (y may be null) and its q8_1 rows q (may be
+ * a window's first half) - summed across the GPUs in fnx_ring_sum's order (ring with nrank > 1, over its receive areas:
+ * ll_count >= T * n), x += sum, then y = RMS norm of the new x with weight w (y may be null) and its q8_1 rows q (may be
  * null), all as the separate entry points give them, bit for bit. */
 typedef struct FnxMoeRows {
     const float *part, *topw, *sh, *logits; /* [T topk][n], [T][topk], [T][n], router logits [T][nexp + 1] */

@@ -41,6 +41,27 @@ __device__ __forceinline__ float4 ld_peer(const float* p) {   // peer memory: no
     return v;
 }
 
+// ---- the window's own exchanges: a value and the exchange's number in one 8-byte store into the reader's memory
+// ("LL" words, as the reference's ring stores them, src/kernels.cu:755-868).  The store is one transaction, so a reader
+// that sees the number sees the value: no flag, no fence, one one-way trip.  An area is rewritten two exchanges later,
+// which a GPU can reach only after every peer has sent the exchange in between, i.e. after it has read this one.
+__device__ __forceinline__ void ll_store(unsigned long long* p, unsigned bits, unsigned epoch) {
+    asm volatile("st.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(bits), "r"(epoch) : "memory");
+}
+// polls this GPU's own memory (not through L1) until the word carries `epoch`; gives up after `limit` polls (bit 1 of *err)
+__device__ __forceinline__ unsigned ll_load(const unsigned long long* p, unsigned epoch, unsigned limit, unsigned* err) {
+    unsigned x, y, spins = 0;
+    for (;;) {
+        asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(x), "=r"(y) : "l"(p) : "memory");
+        if (y == epoch) return x;
+        if (++spins >= limit) {
+            atomicOr(err, 1u);
+            return 0u;
+        }
+        if (spins > 8) __nanosleep(32);
+    }
+}
+
 __global__ void __launch_bounds__(RS_THREADS) k_ring_sum(float* __restrict__ x, int count, int row_len, const FnxRing ring, unsigned* err) {
     const int n = ring.nrank, me = ring.rank, tid = threadIdx.x;
     unsigned* state = ring.state;              // [0] sums done so far, [1] blocks that have published, [2] blocks that are done
@@ -117,8 +138,8 @@ __global__ void __launch_bounds__(RS_THREADS) k_ring_sum(float* __restrict__ x, 
 // ---------------------------------------------------------------- a half layer's boundary in one launch
 // What sits between two halves of a layer, in one kernel instead of three: the addend of the half that ended (its
 // output rows, or the routed experts' rows weighted and added with the gated shared expert: reference src/kernels.cu:
-// 797-806, ring_x), the sum of the GPUs' addends in the ring's order (as k_ring_sum, over the same slots, flags and
-// state), the residual update x += sum, and the RMS norm of the new x with its q8_1 copy for the half that begins
+// 797-806, ring_x), the sum of the GPUs' addends in the ring's order (k_ring_sum's, over the ring's receive areas: every
+// value goes to every peer as a value + exchange number word), the residual update x += sum, and the RMS norm of the new x with its q8_1 copy for the half that begins
 // (k_rms_norm_rows' order of sums).  A cluster of eight blocks per row (see the kernel).
 struct BoundaryArgs {
     float* x;
@@ -151,7 +172,6 @@ __device__ __forceinline__ void bd_q8_1_store(float xi, uint8_t* blk, int lane) 
 __global__ void __cluster_dims__(BD_CL, 1, 1) __launch_bounds__(BD_CT) k_boundary_rows(const BoundaryArgs a) {
     cg::cluster_group cluster = cg::this_cluster();
     __shared__ float sh[32];   // every block of the cluster gets all 32 warp sums
-    __shared__ bool last;
     const int t = blockIdx.x / BD_CL, cr = blockIdx.x % BD_CL, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int vt = cr * BD_CT + tid, n = a.n, nr = a.ring.nrank, me = a.ring.rank;
     float* xr = a.x + (size_t) t * n;
@@ -185,35 +205,17 @@ __global__ void __cluster_dims__(BD_CL, 1, 1) __launch_bounds__(BD_CT) k_boundar
         unsigned* state = a.ring.state;
         const unsigned epoch = *reinterpret_cast<volatile unsigned*>(state) + 1u;
         const int parity = (int) (epoch & 1u);
-        float* mine = a.ring.slot[parity][me] + (size_t) t * n;
+        const size_t cnt = a.ring.ll_count;
+        // ---- this thread's values to every peer's receive area, then the peers' values out of this GPU's own
 #pragma unroll
         for (int k = 0; k < BD_MAXC; ++k) {
             const int i = vt + BD_THREADS * k;
-            if (i < n) mine[i] = add[k];
-        }
-        __threadfence();   // device scope here; the last block's system-scope fence and release below carry it to the peers
-        __syncthreads();
-        if (tid == 0) last = atomicAdd(&state[1], 1u) == gridDim.x - 1;
-        __syncthreads();
-        if (last) {   // every row of the addend is in the slot: tell every peer
-            __threadfence_system();
-            if (tid < nr && tid != me) st_release_sys(a.ring.pad[tid] + me, epoch);
-            if (tid == 0) state[1] = 0u;
-        }
-        if (tid < nr && tid != me) {
-            const unsigned* flag = a.ring.pad[me] + tid;
-            unsigned spins = 0;
-            while ((int) (ld_acquire_sys(flag) - epoch) < 0) {
-                if (++spins >= a.ring.spin_limit) {
-                    atomicOr(a.err, 1u);
-                    break;
-                }
-                __nanosleep(64);
+            if (i < n) {
+#pragma unroll
+                for (int r = 0; r < FNX_RING_MAX; ++r)
+                    if (r < nr && r != me) ll_store(a.ring.ll[parity][r] + (size_t) me * cnt + (size_t) t * n + i, __float_as_uint(add[k]), epoch);
             }
         }
-        __syncthreads();
-        const int NP = n / 2;
-        // every peer's value of every column of this thread first (independent loads, all in flight), then the sums
         float pv[BD_MAXC][FNX_RING_MAX];
 #pragma unroll
         for (int k = 0; k < BD_MAXC; ++k) {
@@ -221,9 +223,12 @@ __global__ void __cluster_dims__(BD_CL, 1, 1) __launch_bounds__(BD_CT) k_boundar
 #pragma unroll
             for (int r = 0; r < FNX_RING_MAX; ++r) {
                 pv[k][r] = 0.f;
-                if (i < n && r < nr) pv[k][r] = r == me ? add[k] : ld_cg(a.ring.slot[parity][r] + (size_t) t * n + i);
+                if (i < n && r < nr)
+                    pv[k][r] = r == me ? add[k]
+                                       : __uint_as_float(ll_load(a.ring.ll[parity][me] + (size_t) r * cnt + (size_t) t * n + i, epoch, a.ring.spin_limit, a.err));
             }
         }
+        const int NP = n / 2;
 #pragma unroll
         for (int k = 0; k < BD_MAXC; ++k) {
             const int i = vt + BD_THREADS * k;
@@ -246,7 +251,7 @@ __global__ void __cluster_dims__(BD_CL, 1, 1) __launch_bounds__(BD_CT) k_boundar
                 add[k] = acc;
             }
         }
-        __syncthreads();
+        __syncthreads();   // the last block out counts the exchange
         if (tid == 0 && atomicAdd(&state[2], 1u) == gridDim.x - 1) {
             state[2] = 0u;
             __threadfence();
@@ -293,10 +298,10 @@ __global__ void __cluster_dims__(BD_CL, 1, 1) __launch_bounds__(BD_CT) k_boundar
 
 // ---------------------------------------------------------------- the attention layer's merge across GPUs in one launch
 // Every GPU has scanned the positions it owns for every head; a head's output is the merge of the GPUs' partials in
-// ring order ending with the head's owner (reference src/kernels.cu:609-672, k_att_merge over the ring).  Here the
-// exchange is the same as the sums': a GPU publishes its partials of all heads in its slot, flags its peers, waits for
-// theirs (bounded), and reads the partials of the heads it owns straight from the peers' slots; the gate and the q8_1
-// rows for the output projection follow in the same kernel.  ring null: one GPU, the partial is the result.
+// ring order ending with the head's owner (reference src/kernels.cu:609-672, k_att_merge over the ring).  Here a GPU
+// stores, into every peer's receive area, its partials of the heads that peer owns (value + exchange number words), and
+// takes the partials of its own heads out of its own area as they arrive (bounded polls); the gate and the q8_1 rows for
+// the output projection follow in the same kernel.  ring null: one GPU, the partial is the result.
 // Block (owned head, row), hd threads; part: this GPU's partials [T][nq][hd + 2] (acc, m, z).
 struct FinishArgs {
     const float* part;
@@ -313,49 +318,36 @@ __global__ void k_attn_finish_ring(const FinishArgs a) {
     pdl_go();
     const int n = a.nrank, me = n > 1 ? a.ring.rank : 0, hd = a.hd, nq = a.nq, own = gridDim.x, T = gridDim.y;
     const int hx = blockIdx.x, t = blockIdx.y, i = threadIdx.x, h = me * own + hx;
-    const size_t psz = (size_t) T * nq * (hd + 2), at = ((size_t) t * nq + h) * (hd + 2);
+    const size_t at = ((size_t) t * nq + h) * (hd + 2);
     unsigned epoch = 0;
     int parity = 0;
+    const size_t cnt = a.ring.ll_count;
     if (n > 1) {
-        unsigned* state = a.ring.state;
-        epoch = *reinterpret_cast<volatile unsigned*>(state) + 1u;
+        epoch = *reinterpret_cast<volatile unsigned*>(a.ring.state) + 1u;
         parity = (int) (epoch & 1u);
-        float* mine = a.ring.slot[parity][me];
-        const int nblocks = gridDim.x * gridDim.y, b = blockIdx.y * gridDim.x + blockIdx.x;
-        for (size_t e = (size_t) b * blockDim.x + i; e < psz; e += (size_t) nblocks * blockDim.x) mine[e] = a.part[e];
-        __threadfence();   // device scope here; the last block's system-scope fence and release below carry it to the peers
-        __syncthreads();
-        __shared__ bool last;
-        if (i == 0) last = atomicAdd(&state[1], 1u) == (unsigned) nblocks - 1;
-        __syncthreads();
-        if (last) {
-            __threadfence_system();
-            if (i < n && i != me) st_release_sys(a.ring.pad[i] + me, epoch);
-            if (i == 0) state[1] = 0u;
+        // ---- every peer gets this GPU's partials of the heads it owns: run `me` of its receive area, [T][own][hd + 2];
+        // block (hx, t) sends head hx of each peer's heads, row t
+        for (int r = 0; r < n; ++r) {
+            if (r == me) continue;
+            const float* srcp = a.part + ((size_t) t * nq + r * own + hx) * (hd + 2);
+            unsigned long long* dst = a.ring.ll[parity][r] + (size_t) me * cnt + ((size_t) t * own + hx) * (hd + 2);
+            for (int e = i; e < hd + 2; e += blockDim.x) ll_store(dst + e, __float_as_uint(srcp[e]), epoch);
         }
-        if (i < n && i != me) {
-            const unsigned* flag = a.ring.pad[me] + i;
-            unsigned spins = 0;
-            while ((int) (ld_acquire_sys(flag) - epoch) < 0) {
-                if (++spins >= a.ring.spin_limit) {
-                    atomicOr(a.err, 1u);
-                    break;
-                }
-                __nanosleep(64);
-            }
-        }
-        __syncthreads();
     }
-    auto src = [&](int r) { return r == me || n == 1 ? a.part + at : a.ring.slot[parity][r] + at; };
-    const float* p1 = src((me + 1) % n);
-    float m = ld_cg(p1 + hd), z = ld_cg(p1 + hd + 1), acc = ld_cg(p1 + i);
+    // a peer's partial of (row t, owned head hx): element e, out of this GPU's receive area
+    auto peer = [&](int r, int e) {
+        return __uint_as_float(ll_load(a.ring.ll[parity][me] + (size_t) r * cnt + ((size_t) t * own + hx) * (hd + 2) + e, epoch, a.ring.spin_limit, a.err));
+    };
+    auto val = [&](int r, int e) { return r == me || n == 1 ? a.part[at + e] : peer(r, e); };
+    const int r1 = (me + 1) % n;
+    float m = val(r1, hd), z = val(r1, hd + 1), acc = val(r1, i);
     for (int s = 2; s <= n; ++s) {
-        const float* p2 = src((me + s) % n);
-        const float m2 = ld_cg(p2 + hd), z2 = ld_cg(p2 + hd + 1);
+        const int r2 = (me + s) % n;
+        const float m2 = val(r2, hd), z2 = val(r2, hd + 1);
         const float mn = fmaxf(m, m2);
         const float w1 = m == -INFINITY ? 0.f : ex_expf(fsub(m, mn)), w2 = m2 == -INFINITY ? 0.f : ex_expf(fsub(m2, mn));
         z = ffma(w2, z2, fmul(w1, z));
-        acc = ffma(w2, ld_cg(p2 + i), fmul(w1, acc));
+        acc = ffma(w2, val(r2, i), fmul(w1, acc));
         m = mn;
     }
     const float v = fmul(fdiv(acc, z), ex_sigmoid(a.qg[((size_t) t * nq + h) * 2 * hd + hd + i]));
@@ -372,10 +364,10 @@ __global__ void k_attn_finish_ring(const FinishArgs a) {
 }
 
 
-// ---------------------------------------------------------------- a small all-gather over the ring's slots
+// ---------------------------------------------------------------- a small all-gather over the ring's receive areas
 // Every GPU's few words (the argmax (value, index) of its vocabulary range, its 64 candidates a row) to every GPU: the
-// same exchange once more - publish in the own slot, flag, bounded wait, read the peers' slots - as one block.  Two
-// arrays of 4-byte words a call; all_a [nrank][na], all_b [nrank][nb].
+// same exchange once more - the words stored into every peer's area, the peers' polled out of the own - as one block.
+// Two arrays of 4-byte words a call; all_a [nrank][na], all_b [nrank][nb].
 __global__ void __launch_bounds__(1024) k_ring_gather(const unsigned* __restrict__ a, int na, const unsigned* __restrict__ b, int nb, const FnxRing ring,
                                                       unsigned* __restrict__ all_a, unsigned* __restrict__ all_b, unsigned* err) {
     pdl_wait();
@@ -384,28 +376,14 @@ __global__ void __launch_bounds__(1024) k_ring_gather(const unsigned* __restrict
     unsigned* state = ring.state;
     const unsigned epoch = *reinterpret_cast<volatile unsigned*>(state) + 1u;
     const int parity = (int) (epoch & 1u);
-    unsigned* mine = reinterpret_cast<unsigned*>(ring.slot[parity][me]);
-    for (int i = tid; i < na + nb; i += blockDim.x) mine[i] = i < na ? a[i] : b[i - na];
-    __threadfence();   // the release stores below (system scope, after the barrier) carry the block's writes to the peers
-    __syncthreads();
-    if (tid < n && tid != me) {
-        st_release_sys(ring.pad[tid] + me, epoch);
-        const unsigned* flag = ring.pad[me] + tid;
-        unsigned spins = 0;
-        while ((int) (ld_acquire_sys(flag) - epoch) < 0) {
-            if (++spins >= ring.spin_limit) {
-                atomicOr(err, 1u);
-                break;
-            }
-            __nanosleep(64);
-        }
+    const size_t cnt = ring.ll_count;
+    for (int i = tid; i < (n - 1) * (na + nb); i += blockDim.x) {   // this GPU's words to every peer's receive area
+        const int q = i / (na + nb), k = i % (na + nb), r = q < me ? q : q + 1;
+        ll_store(ring.ll[parity][r] + (size_t) me * cnt + k, k < na ? a[k] : b[k - na], epoch);
     }
-    __syncthreads();
     for (int i = tid; i < n * (na + nb); i += blockDim.x) {
         const int r = i / (na + nb), k = i % (na + nb);
-        unsigned v;
-        if (r == me) v = k < na ? a[k] : b[k - na];
-        else asm volatile("ld.global.cg.u32 %0, [%1];" : "=r"(v) : "l"(reinterpret_cast<const unsigned*>(ring.slot[parity][r]) + k));
+        const unsigned v = r == me ? (k < na ? a[k] : b[k - na]) : ll_load(ring.ll[parity][me] + (size_t) r * cnt + k, epoch, ring.spin_limit, err);
         if (k < na) all_a[(size_t) r * na + k] = v;
         else all_b[(size_t) r * nb + (k - na)] = v;
     }
@@ -452,8 +430,9 @@ int fnx_boundary_rows(float* x, const float* bo, const FnxMoeRows* moe, const Fn
     if (ring && ring->nrank > 1 && (bo || moe)) {
         FNX_REQUIRE(ring->nrank <= FNX_RING_MAX && ring->rank >= 0 && ring->rank < ring->nrank, "boundary_rows: GPU %d of %d", ring->rank, ring->nrank);
         FNX_REQUIRE(ring->state && ring->spin_limit > 0 && err && n % 4 == 0, "boundary_rows: no state words, spin limit or error word");
+        FNX_REQUIRE(ring->ll_count >= (size_t) T * n, "boundary_rows: receive areas of %zu words for %d x %d values", ring->ll_count, T, n);
         for (int r = 0; r < ring->nrank; ++r)
-            FNX_REQUIRE(ring->slot[0][r] && ring->slot[1][r] && ring->pad[r], "boundary_rows: GPU %d's slots or flags are missing", r);
+            FNX_REQUIRE(ring->ll[0][r] && ring->ll[1][r], "boundary_rows: GPU %d's receive areas are missing", r);
         a.ring = *ring;
     }
     launch(0, k_boundary_rows, T * BD_CL, BD_CT, 0, strm(st), a);
@@ -465,7 +444,12 @@ int fnx_attn_finish_ring(const float* part, const FnxRing* ring, const float* qg
     const int n = ring ? ring->nrank : 1;
     FNX_REQUIRE(T >= 1 && T <= FNX_MAXT && hd % 32 == 0 && hd >= 32 && hd <= 1024, "attn_finish_ring: %d rows, head dim %d", T, hd);
     FNX_REQUIRE(n >= 1 && n <= FNX_RING_MAX && nq % n == 0, "attn_finish_ring: %d query heads over %d GPUs", nq, n);
-    FNX_REQUIRE(!ring || (ring->rank >= 0 && ring->rank < n && ring->state && err), "attn_finish_ring: rank, state or error word missing");
+    FNX_REQUIRE(!ring || (ring->rank >= 0 && ring->rank < n && ring->state && err && ring->spin_limit > 0), "attn_finish_ring: rank, state or error word missing");
+    if (n > 1) {
+        FNX_REQUIRE(ring->ll_count >= (size_t) T * (nq / n) * (hd + 2), "attn_finish_ring: receive areas of %zu words for %d x %d x %d", ring->ll_count, T,
+                    nq / n, hd + 2);
+        for (int r = 0; r < n; ++r) FNX_REQUIRE(ring->ll[0][r] && ring->ll[1][r], "attn_finish_ring: GPU %d's receive areas are missing", r);
+    }
     FinishArgs a{part, ring ? *ring : FnxRing{}, qg, out, (uint8_t*) q8, nq, hd, n, err};
     launch(0, k_attn_finish_ring, dim3(nq / n, T), hd, 0, strm(st), a);
     return launch_ok("attn_finish_ring");
@@ -475,6 +459,8 @@ int fnx_ring_gather(const void* a, int na, const void* b, int nb, const FnxRing*
     FNX_REQUIRE(ring && ring->nrank >= 2 && ring->nrank <= FNX_RING_MAX && ring->rank >= 0 && ring->rank < ring->nrank && ring->state && err,
                 "ring_gather: no ring of at least two GPUs, state or error word");
     FNX_REQUIRE(a && all_a && na >= 1 && nb >= 0 && (nb == 0 || (b && all_b)), "ring_gather: %d + %d words without their arrays", na, nb);
+    FNX_REQUIRE(ring->ll_count >= (size_t) (na + nb) && ring->spin_limit > 0, "ring_gather: receive areas of %zu words for %d", ring->ll_count, na + nb);
+    for (int r = 0; r < ring->nrank; ++r) FNX_REQUIRE(ring->ll[0][r] && ring->ll[1][r], "ring_gather: GPU %d's receive areas are missing", r);
     launch(0, k_ring_gather, 1, 1024, 0, strm(st), (const unsigned*) a, na, (const unsigned*) b, nb, *ring, (unsigned*) all_a, (unsigned*) all_b, err);
     return launch_ok("ring_gather");
 }

@@ -83,7 +83,7 @@ RING_MAX = 8
 
 class Ring(C.Structure):
     _fields_ = [("nrank", C.c_int), ("rank", C.c_int), ("slot", (C.c_void_p * RING_MAX) * 2), ("pad", C.c_void_p * RING_MAX),
-                ("state", C.c_void_p), ("spin_limit", C.c_uint)]
+                ("state", C.c_void_p), ("spin_limit", C.c_uint), ("ll", (C.c_void_p * RING_MAX) * 2), ("ll_count", C.c_size_t)]
 
 
 class MoeRows(C.Structure):

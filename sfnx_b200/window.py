@@ -454,7 +454,8 @@ class WindowRunner:
             import torch.distributed._symmetric_memory as symm
 
             group = self.group if self.group is not None else self.dist.group.WORLD
-            buf = symm.empty(2 * count + 64, dtype=torch.float32, device=self.stack.dev)
+            nr = self.stack.ncard
+            buf = symm.empty(2 * count + 64 + 4 * nr * count, dtype=torch.float32, device=self.stack.dev)   # slots, flags, receive areas
             buf.zero_()
             torch.cuda.synchronize()
             hdl = symm.rendezvous(buf, group)
@@ -474,6 +475,9 @@ class WindowRunner:
         for r in range(self.stack.ncard):
             ring.slot[0][r], ring.slot[1][r] = ptrs[r], ptrs[r] + count * 4
             ring.pad[r] = ptrs[r] + 2 * count * 4
+            ll0 = ptrs[r] + (2 * count + 64) * 4   # 8-byte aligned: count is even
+            ring.ll[0][r], ring.ll[1][r] = ll0, ll0 + self.stack.ncard * count * 8
+        ring.ll_count = count
         self.ring_state = torch.zeros(4, dtype=torch.int32, device=self.stack.dev)
         ring.state = self.ring_state.data_ptr()
         ring.spin_limit = 1 << 20   # about a second of polling before a missing peer is reported

@@ -9,15 +9,38 @@ import pytest
 pytestmark = pytest.mark.gpu
 
 
-def _ring(L, G, torch, n, rank, slots, pads, state, limit):
+def _ring(L, G, torch, n, rank, slots, pads, state, limit, ll=None, ll_count=0):
     r = L.Ring()
     r.nrank, r.rank, r.state, r.spin_limit = n, rank, state.data_ptr(), limit
     for p in range(2):
         for k in range(n):
             r.slot[p][k] = slots[k][p].data_ptr()
+            if ll is not None:
+                r.ll[p][k] = ll[k][p].data_ptr()
     for k in range(n):
         r.pad[k] = pads[k].data_ptr()
+    r.ll_count = ll_count
     return r
+
+
+def _ll_areas(G, torch, n, rank, count, epoch, words_of):
+    """The GPUs' receive areas [GPU][parity] of n runs of `count` 8-byte words, as they are when the emulated peers have sent
+    exchange `epoch`: run s of this GPU's area of the epoch's parity holds words_of(s) (uint32 values) with the epoch in
+    the upper halves; everything else is zero (the peers' areas receive this GPU's stores)."""
+    areas = [[torch.zeros(n * count, dtype=torch.int64, device=G.DEV) for _ in range(2)] for _ in range(n)]
+    mine = areas[rank][epoch % 2].view(n, count)
+    for s_ in range(n):
+        if s_ == rank:
+            continue
+        w = np.ascontiguousarray(words_of(s_)).reshape(-1).view(np.uint32).astype(np.int64) | (np.int64(epoch) << 32)
+        mine[s_, :w.size] = G.dev(w)
+    return areas
+
+
+def _ll_sent(G, area, rank, count, nwords):
+    """What this GPU stored into a peer's area: (values as uint32, exchange numbers)."""
+    w = G.host(area.view(-1, count)[rank, :nwords])
+    return (w & 0xffffffff).astype(np.uint32), (w >> 32).astype(np.uint32)
 
 
 @pytest.mark.parametrize("n,T,row_len", [(2, 16, 3072), (4, 5, 1024), (8, 16, 3072), (3, 2, 20)])
@@ -103,7 +126,8 @@ def test_boundary_rows_equals_the_separate_steps(n, T, width, moe):
             slots = [[G.dev(adds[k]) if p == epoch % 2 else G.zeros((T, width)) for p in range(2)] for k in range(n)]
             pads = [torch.full((16,), epoch, dtype=torch.int32, device=G.DEV) for _ in range(n)]
             state = torch.tensor([epoch - 1, 0, 0, 0], dtype=torch.int32, device=G.DEV)
-            return _ring(L, G, torch, n, rank, slots, pads, state, 1 << 20), (slots, pads, state)
+            ll = _ll_areas(G, torch, n, rank, T * width, epoch, lambda k: adds[k])
+            return _ring(L, G, torch, n, rank, slots, pads, state, 1 << 20, ll, T * width), (slots, pads, state, ll)
 
         err = G.zeros(1, torch.int32)
         ring, keep = ring_for(1)
@@ -124,6 +148,10 @@ def test_boundary_rows_equals_the_separate_steps(n, T, width, moe):
         assert np.array_equal(G.host(q2), G.host(q1)), (n, rank, "q8_1")
         if n > 1:
             assert G.host(keep2[2]).tolist()[:3] == [1, 0, 0]
+            for k in range(n):   # every peer has this GPU's addend, marked with the exchange's number
+                if k != rank:
+                    vals, eps_ = _ll_sent(G, keep2[3][k][1], rank, T * width, T * width)
+                    assert np.array_equal(vals, mine.reshape(-1).view(np.uint32)) and (eps_ == 1).all()
     # a window's first half: no addend, the norm alone
     x3, y3, q3 = G.dev(x0), G.zeros((T, width)), G.zeros(T * (width // 32) * 36, torch.uint8)
     x4, y4, q4 = G.dev(x0), G.zeros((T, width)), G.zeros(T * (width // 32) * 36, torch.uint8)
@@ -161,11 +189,13 @@ def test_attn_finish_ring_equals_the_separate_steps(n, T, nq, hd):
         L.call("fnx_attn_finish", dparts.data_ptr(), n, rank, dqg.data_ptr(), out1.data_ptr(), T, nq, rank * own, own, hd, st)
         L.call("fnx_quantize_q8_1", out1.data_ptr(), q1.data_ptr(), own * hd, T, st)
         for epoch in (1, 2):
-            slots = [[G.dev(parts[k]) if (p == epoch % 2 and k != rank) else G.zeros((T, nq, hd + 2)) for p in range(2)] for k in range(n)]
-            pads = [torch.full((16,), epoch, dtype=torch.int32, device=G.DEV) for _ in range(n)]
+            slots = [[G.zeros(4) for p in range(2)] for k in range(n)]
+            pads = [G.zeros(16, torch.int32) for _ in range(n)]
             state = torch.tensor([epoch - 1, 0, 0, 0], dtype=torch.int32, device=G.DEV)
             err = G.zeros(1, torch.int32)
-            ring = _ring(L, G, torch, n, rank, slots, pads, state, 1 << 20)
+            cnt = T * own * (hd + 2)
+            ll = _ll_areas(G, torch, n, rank, cnt, epoch, lambda k: parts[k][:, rank * own:(rank + 1) * own])
+            ring = _ring(L, G, torch, n, rank, slots, pads, state, 1 << 20, ll, cnt)
             out2, q2 = G.zeros((T, own, hd)), G.zeros(T * (own * hd // 32) * 36, torch.uint8)
             mine = G.dev(parts[rank])
             L.call("fnx_attn_finish_ring", mine.data_ptr(), C.byref(ring) if n > 1 else None, dqg.data_ptr(), out2.data_ptr(), q2.data_ptr(), T, nq, hd,
@@ -176,7 +206,11 @@ def test_attn_finish_ring_equals_the_separate_steps(n, T, nq, hd):
             assert np.array_equal(G.host(q2), G.host(q1)), (n, rank, epoch, "q8_1")
             if n > 1:
                 assert G.host(state).tolist()[:3] == [epoch, 0, 0]
-                assert np.array_equal(G.host(slots[rank][epoch % 2]).view(np.uint32), parts[rank].view(np.uint32)), "published partials"
+                for k in range(n):   # every peer has this GPU's partials of the heads that peer owns
+                    if k != rank:
+                        vals, eps_ = _ll_sent(G, ll[k][epoch % 2], rank, cnt, cnt)
+                        want = np.ascontiguousarray(parts[rank][:, k * own:(k + 1) * own]).reshape(-1).view(np.uint32)
+                        assert np.array_equal(vals, want) and (eps_ == epoch).all(), "sent partials"
 
 
 @pytest.mark.parametrize("n,na,nb", [(2, 16, 16), (8, 16, 16), (4, 1024, 1024), (3, 5, 0)])
@@ -194,18 +228,12 @@ def test_ring_gather(n, na, nb):
     st = L.stream()
     for rank in range(n):
         for epoch in (1, 2):
-            def slot(k, p):
-                t = G.zeros(4096)
-                if p == epoch % 2 and k != rank:
-                    t[:na] = G.dev(A[k])
-                    if nb:
-                        t[na:na + nb] = G.dev(B[k]).view(torch.float32)
-                return t
-            slots = [[slot(k, p) for p in range(2)] for k in range(n)]
-            pads = [torch.full((16,), epoch, dtype=torch.int32, device=G.DEV) for _ in range(n)]
+            slots = [[G.zeros(4) for p in range(2)] for k in range(n)]
+            pads = [G.zeros(16, torch.int32) for _ in range(n)]
             state = torch.tensor([epoch - 1, 0, 0, 0], dtype=torch.int32, device=G.DEV)
             err = G.zeros(1, torch.int32)
-            ring = _ring(L, G, torch, n, rank, slots, pads, state, 1 << 20)
+            ll = _ll_areas(G, torch, n, rank, 4096, epoch, lambda k: np.concatenate([A[k].view(np.uint32), B[k].view(np.uint32)]))
+            ring = _ring(L, G, torch, n, rank, slots, pads, state, 1 << 20, ll, 4096)
             a, b = G.dev(A[rank]), G.dev(np.ascontiguousarray(B[rank])) if nb else None
             all_a, all_b = G.zeros((n, na)), G.zeros((n, max(nb, 1)), torch.int32)
             L.call("fnx_ring_gather", a.data_ptr(), na, b.data_ptr() if nb else None, nb, C.byref(ring), all_a.data_ptr(),
@@ -215,3 +243,28 @@ def test_ring_gather(n, na, nb):
             assert np.array_equal(G.host(all_a).view(np.uint32), A.view(np.uint32)), (n, rank, epoch)
             if nb:
                 assert np.array_equal(G.host(all_b)[:, :nb], B), (n, rank, epoch)
+
+
+def test_window_exchange_gives_up_when_a_peer_never_sends():
+    """The window's own exchanges poll this GPU's receive area for words that carry the exchange's number; with nothing
+    arriving and a short poll limit the kernel gives up with error bit 1 and the context stays usable."""
+    import torch
+
+    from sfnx_b200 import lib as L
+    from tests import gpu_util as G
+
+    n, na = 2, 16
+    slots = [[G.zeros(4) for _ in range(2)] for _ in range(n)]
+    pads = [G.zeros(16, torch.int32) for _ in range(n)]
+    ll = [[torch.zeros(n * 64, dtype=torch.int64, device=G.DEV) for _ in range(2)] for _ in range(n)]   # nothing ever arrives
+    state, err = G.zeros(4, torch.int32), G.zeros(1, torch.int32)
+    ring = _ring(L, G, torch, n, 0, slots, pads, state, 200, ll, 64)
+    a, all_a = G.dev(np.arange(na, dtype=np.float32)), G.zeros((n, na))
+    L.call("fnx_ring_gather", a.data_ptr(), na, None, 0, C.byref(ring), all_a.data_ptr(), None, err.data_ptr(), L.stream())
+    G.sync()
+    assert int(G.host(err)[0]) & 1 == 1
+    assert np.array_equal(G.host(all_a)[0], np.arange(na, dtype=np.float32))   # its own words are in place all the same
+    y = G.zeros(8)
+    y.fill_(3.0)
+    G.sync()
+    assert float(G.host(y)[0]) == 3.0
