@@ -642,9 +642,11 @@ class WindowRunner:
 
     def ring_self_check(self, rounds=8, seed=0):
         """The sum across GPUs on the real peers: every rank makes all ranks' seeded addends, runs `rounds` sums back to
-        back on its own addend through this runner's ring (slots of both parities, the flags' epochs running on) and
-        compares the bits with the same chunks added in the ring's order by plain elementwise float adds.  Returns
-        {"rounds", "bits_equal", "err"}; None when the sums go through NCCL."""
+        back on its own addend through this runner's ring - even rounds by fnx_ring_sum (slots and flags), odd rounds by the
+        window's own exchange, fnx_boundary_rows on a zero x (value + exchange-number words into the peers' receive
+        areas); both parities, the exchange numbers running on - and compares the bits with the same chunks added in the
+        ring's order by plain elementwise float adds.  Returns {"rounds", "bits_equal", "err"}; None when the sums go
+        through NCCL."""
         if self.ring is None:
             return None
         n, me, T, width = self.stack.ncard, self.stack.card, self.T, self.stack.shape.n
@@ -652,6 +654,7 @@ class WindowRunner:
         ok, err = True, 0
         x = torch.empty(T * width, dtype=torch.float32, device=self.stack.dev)
         errw = torch.zeros(1, dtype=torch.int32, device=self.stack.dev)
+        ones = torch.ones(width, dtype=torch.float32, device=self.stack.dev)
         with torch.cuda.stream(self.stream):
             for r in range(rounds):
                 g = torch.Generator(device=self.stack.dev)
@@ -664,8 +667,14 @@ class WindowRunner:
                     for k in range(1, n):
                         acc = acc + adds[(c + k) % n, :, lo:hi]
                     want[:, lo:hi] = acc
-                x.copy_(adds[me].reshape(-1))
-                L.call("fnx_ring_sum", x.data_ptr(), T, width, C.byref(self.ring), errw.data_ptr(), self.stream.cuda_stream)
+                if r % 2 == 0:
+                    x.copy_(adds[me].reshape(-1))
+                    L.call("fnx_ring_sum", x.data_ptr(), T, width, C.byref(self.ring), errw.data_ptr(), self.stream.cuda_stream)
+                else:   # x = 0 + sum: the sum's bits (no addend here is a zero)
+                    x.zero_()
+                    mine = adds[me].contiguous()
+                    L.call("fnx_boundary_rows", x.data_ptr(), mine.data_ptr(), None, C.byref(self.ring), ones.data_ptr(), None, None, T, width,
+                           1e-6, errw.data_ptr(), self.stream.cuda_stream)
                 ok = ok and bool(torch.equal(x.view(torch.int32), want.reshape(-1).view(torch.int32)))
             self.stream.synchronize()
             err = int(errw[0])
