@@ -1,6 +1,8 @@
 // Acceptance of a verify window on the host: greedy prefix match and rejection sampling against fixed drafts over the
-// rows' 64 candidates, and the merge of the GPUs' candidate lists.  The policy of the reference's Session (src/session.cpp:
-// 39-82 make_dist / draw, 469-510 the acceptance loop; src/engine_common.cu:640-653 the merge), as free functions.
+// rows' 64 candidates, and the merge of the GPUs' candidate lists.  Restated from the reference's Session, statement for
+// statement where the arithmetic demands it (src/session.cpp:39-82 make_dist / draw, 469-510 the acceptance loop;
+// src/engine_common.cu:640-653 the merge), as free functions over plain arrays: this is host policy the drop-in keeps,
+// and the reference's own object code is its checker (oracle/ref_accept.cpp).
 #include <algorithm>
 #include <cmath>
 #include <random>

@@ -155,3 +155,47 @@ def test_attention_rows_of_several_sequences():
     G.sync()
     ref = np.concatenate([r["part"][0] for r in refs])
     assert np.array_equal(G.host(part).view(np.uint32), ref.view(np.uint32))
+
+
+def test_attention_scan_timings(capsys):
+    """Device times of the three scans of one layer at the benchmark's shape (T = 16, 24 / 4 heads of 256, 32 768 positions on
+    one GPU): the tcgen05 scan over f16 rows, the exact-order scan over f16 rows and over int8 rows.  Printed; no bound
+    beyond finishing."""
+    import torch
+
+    from sfnx_b200 import lib as L
+    from tests import gpu_util as G
+
+    T, ctx, nq, nkv, hd = 16, 32768, 24, 4, 256
+    rows = ctx + 64
+    g = torch.Generator(device=G.DEV).manual_seed(3)
+    qg = torch.randn((T, nq, 2 * hd), generator=g, device=G.DEV)
+    kc = torch.randn((rows, nkv, hd), generator=g, device=G.DEV).half().view(torch.int16)
+    vc = torch.randn((rows, nkv, hd), generator=g, device=G.DEV).half().view(torch.int16)
+    halves = L.load().fnx_kvq_halves(rows, nkv, hd)
+    kq = torch.randint(-127, 127, (halves,), generator=g, device=G.DEV, dtype=torch.int16)
+    vq = torch.randint(-127, 127, (halves,), generator=g, device=G.DEV, dtype=torch.int16)
+    kq[rows * nkv * hd // 2:] = 0x1C00   # the scales: f16 2^-8
+    vq[rows * nkv * hd // 2:] = 0x1C00
+    pos0 = G.dev(np.array([ctx], np.int32))
+    part = G.zeros((T, nq, hd + 2))
+    scratch = G.zeros(L.load().fnx_attn_scratch_floats(nq, hd, T))
+    st = L.stream()
+    out = []
+    for name, entry, k, v, pages in (("tcgen05 scan, f16 rows", "fnx_attn_partial", kc, vc, L.KvPages(None, 0, 0, rows, 0)),
+                                     ("exact-order scan, f16 rows", "fnx_attn_partial_exact", kc, vc, L.KvPages(None, 0, 0, rows, 0)),
+                                     ("exact-order scan, int8 rows", "fnx_attn_partial_exact", kq, vq, L.KvPages(None, 0, 0, rows, 1))):
+        def run():
+            L.call(entry, qg.data_ptr(), k.data_ptr(), v.data_ptr(), pages, part.data_ptr(), 0, 1, T, pos0.data_ptr(), nq, nkv, hd, scratch.data_ptr(), st)
+        for _ in range(2):
+            run()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(torch.cuda.current_stream())
+        for _ in range(5):
+            run()
+        e1.record(torch.cuda.current_stream())
+        G.sync()
+        assert torch.isfinite(part).all()
+        out.append("%s: %.1f us" % (name, e0.elapsed_time(e1) * 1e3 / 5))
+    with capsys.disabled():
+        print("\nattention scans at 32 768 positions: " + "; ".join(out))
