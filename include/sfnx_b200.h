@@ -288,6 +288,9 @@ int fnx_hc_write(float* R, const float* bo, const float* inj, int T, int n, int 
  * err bit 4 on a timeout); here the read is three launches in stream order, so it has no barrier, takes no err word
  * and may run beside other streams' work.  scratch: fnx_hc_scratch_floats floats, never read before written. */
 size_t fnx_hc_scratch_floats(int T, int n, int hc, int lr);
+/* R[t][c] = x[t] for every stream c: a window's first residual (the reference's host fills the streams with the embedding
+ * row before it uploads them, src/engine.cu:782-789 embed_into) */
+int fnx_hc_expand(const float* x, float* R, int T, int n, int hc, void* st);
 int fnx_hc_read(float* R, const float* bo_prev, const float* inj_prev, const float* w_norm, FnxQ8S w_down, FnxQ8S w_up, const uint16_t* w_inj,
                 float eps, float* mixed, float* inject, float* scratch, void* q8, int T, int n, int hc, int lr, void* st);
 
@@ -368,7 +371,16 @@ typedef struct FnxStackCfg {
     int vocab0, vocab_rows; /* this GPU's vocabulary slice [vocab0, vocab0 + vocab_rows) */
     int nlayers, ncard, card;
     float eps, rope_base;
+    int hc, hc_lr; /* residual streams (0 or 1: one stream, plain residual + RMS norm) and the hyper-connections' low rank */
 } FnxStackCfg;
+
+/* one hyper-connection read's weights (reference LayerW hc_norm / hc_down / hc_up / hc_inj, src/model.hpp:120-124):
+ * norm [hc n], down split Q8_0 [lr][hc n], up split Q8_0 [hc n][lr], inj bf16 [hc][hc n] or null (the head's mixer) */
+typedef struct FnxHcW {
+    const float* norm;
+    FnxQ8S down, up;
+    const uint16_t* inj;
+} FnxHcW;
 
 typedef struct FnxLayer {
     int kind; /* 0: Gated DeltaNet, 1: attention */
@@ -395,11 +407,14 @@ typedef struct FnxLayer {
      * is not used) and fnx_window_commit replays the kept rows into S, also when every row is kept; without one it runs
      * fnx_gdn_core and the commit copies a checkpoint back. */
     float* gdn_log;
+    /* with cfg.hc > 1: the reads before the mixer half [0] and before the FFN half [1] (norm1 / norm2 are then unused) */
+    FnxHcW hcw[2];
 } FnxLayer;
 
 typedef struct FnxHead {
     const float* norm;
     FnxQ8S out;
+    FnxHcW mix; /* with cfg.hc > 1: the final mixer (no inject rows) instead of norm */
 } FnxHead;
 
 /* what the caller must do across GPUs after a stage (nothing when ncard is 1) */

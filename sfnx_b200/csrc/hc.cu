@@ -50,6 +50,14 @@ __global__ void k_hc_write(float* __restrict__ R, const float* __restrict__ bo, 
     *r = fadd(*r, fdiv(fmul(bo[(size_t) t * n + i], 2.0f), g));
 }
 
+// a window's first residual: every stream starts as the token's embedding row
+__global__ void k_hc_expand(const float* __restrict__ x, float* __restrict__ R, int n, int hc) {
+    pdl_wait();
+    pdl_go();
+    const int t = blockIdx.y, e = blockIdx.x * blockDim.x + threadIdx.x;
+    if (e < n * hc) R[(size_t) t * n * hc + e] = x[(size_t) t * n + e % n];
+}
+
 __device__ __forceinline__ float hc_rprime(const HcArgs& a, int t, int c, int i) {
     float r = a.R[((size_t) t * a.hc + c) * a.n + i];
     if (a.bo) r = ffma(a.bo[(size_t) t * a.n + i], fmul(2.0f, ex_sigmoid(fdiv(a.inj_prev[t * a.hc + c], (float) a.hc))), r);
@@ -281,6 +289,12 @@ int fnx_hc_write(float* R, const float* bo, const float* inj, int T, int n, int 
     FNX_REQUIRE(T >= 1 && T <= FNX_MAXT && n >= 1 && hc >= 1, "hc_write: %d rows, %d streams of %d", T, hc, n);
     launch(0, k_hc_write, dim3((n * hc + 255) / 256, T), 256, 0, strm(st), R, bo, inj, n, hc);
     return launch_ok("hc_write");
+}
+
+int fnx_hc_expand(const float* x, float* R, int T, int n, int hc, void* st) {
+    FNX_REQUIRE(T >= 1 && T <= FNX_MAXT && n >= 1 && hc >= 1, "hc_expand: %d rows, %d streams of %d", T, hc, n);
+    launch(0, k_hc_expand, dim3((n * hc + 255) / 256, T), 256, 0, strm(st), x, R, n, hc);
+    return launch_ok("hc_expand");
 }
 
 size_t fnx_hc_scratch_floats(int T, int n, int hc, int lr) {

@@ -84,7 +84,7 @@ struct Traced {
 // the workspace's buffers, as offsets from its base
 struct Ws {
     size_t x, bo, xn, xq, qkvz, ab, yq, qg, k, v, att, partials, att_scratch, rlogits, topi, topw, jobs_gu, jobs_dn, njobs, rscratch, gu,
-        hq, part, sh_gu, shq, sh, logits, keys, best_v, best_i, err, ctl, gdn_scratch, copy_jobs, replay_jobs, total;
+        hq, part, sh_gu, shq, sh, logits, keys, best_v, best_i, err, ctl, gdn_scratch, copy_jobs, replay_jobs, hc_R, hc_inj, hc_scratch, total;
 };
 
 static Ws carve(const FnxStackCfg& c) {
@@ -133,6 +133,10 @@ static Ws carve(const FnxStackCfg& c) {
     w.gdn_scratch = take(fnx_gdn_scratch_floats(c.nv) * 4);
     w.copy_jobs = take((size_t) c.nlayers * 2 * FNX_MAXT * sizeof(FnxCopyJob));   // up to a lane a row
     w.replay_jobs = take((size_t) c.nlayers * sizeof(FnxGdnReplay));
+    const size_t hcn = c.hc > 1 ? (size_t) c.hc : 0;   // hyper-connections: the residual streams, the two halves' inject values, the read's scratch
+    w.hc_R = take(T * hcn * n * 4);
+    w.hc_inj = take(2 * T * (hcn ? hcn : 1) * 4);
+    w.hc_scratch = take(hcn ? fnx_hc_scratch_floats((int) T, c.n, c.hc, c.hc_lr) * 4 : 0);
     w.total = o;
     return w;
 }
@@ -142,6 +146,8 @@ static int check_cfg(const FnxStackCfg* c) {
     if (c->n <= 0 || c->n % 512 || c->ff <= 0 || c->ff % 32 || c->nlayers < 1 || c->ncard < 1 || c->card < 0 || c->card >= c->ncard)
         return fail("window: hidden %d, ff slice %d, %d layers, GPU %d of %d", c->n, c->ff, c->nlayers, c->card, c->ncard);
     if (c->topk < 1 || c->topk > 16 || c->nq % c->ncard) return fail("window: top-%d, %d query heads over %d GPUs", c->topk, c->nq, c->ncard);
+    if (c->hc > 1 && (c->hc > 8 || c->hc_lr < 32 || c->hc_lr % 32 || c->hc_lr > 512))
+        return fail("window: %d residual streams with low rank %d (up to 8 streams, rank a multiple of 32 up to 512)", c->hc, c->hc_lr);
     return 0;
 }
 
@@ -255,12 +261,36 @@ static int window_stage(const FnxStackCfg* cfg, const FnxLayer* layers, const Fn
     const bool fused = fused_boundaries(c);
     const bool after_ffn = stage > 0 && stages[stage - 1].part == 2;
     const FnxMoeRows moe_rows{(const float*) (b + w.part), (const float*) (b + w.topw), (const float*) (b + w.sh), (const float*) (b + w.rlogits), c.nexp, c.topk};
+    // Hyper-connections (cfg.hc > 1; reference src/engine.cu:935, 1013-1016, 1049): the residual is hc streams R, a half
+    // begins with the read that folds the ended half's output into R (its sum across the GPUs first) and mixes the
+    // streams into the half's input; the two halves' inject values alternate between two buffers.
+    const bool hcm = c.hc > 1;
+    float* hcR = (float*) (b + w.hc_R);
+    float* inj_buf[2] = {(float*) (b + w.hc_inj), (float*) (b + w.hc_inj) + (size_t) FNX_MAXT * (hcm ? c.hc : 1)};
+    auto hc_begin = [&](const FnxHcW& hw, bool ffn_half) -> int {
+        // the ended half's rows into bo: the experts' rows weighted and added, or the mixer's output as it is
+        if (after_ffn && fused)   // (not fused: the FFN stage combined them itself, for the caller's sum)
+            TRY(fnx_moe_combine((const float*) (b + w.part), (const float*) (b + w.topw), (const float*) (b + w.sh), (const float*) (b + w.rlogits), c.nexp, bo,
+                                T, c.n, c.topk, st));
+        if (pending && c.ncard > 1 && g_ring_set) TRY(fnx_ring_sum(bo, T, c.n, &g_ring, (unsigned*) (b + w.err), st));
+        if (stage == 0) TRY(fnx_hc_expand(x, hcR, T, c.n, c.hc, st));
+        // a read before a mixer half (or the head's) takes the FFN half's inject values (buffer 1) and leaves its own in
+        // buffer 0; a read before an FFN half the other way round
+        const float* inj_prev = ffn_half ? inj_buf[0] : inj_buf[1];
+        float* inj_out = ffn_half ? inj_buf[1] : inj_buf[0];
+        return fnx_hc_read(hcR, pending, pending ? inj_prev : nullptr, hw.norm, hw.down, hw.up, hw.inj, c.eps, xn, hw.inj ? inj_out : nullptr,
+                           (float*) (b + w.hc_scratch), xq, T, c.n, c.hc, c.hc_lr, st);
+    };
     auto begin_half = [&](const float* norm_w, float* y) -> int {
+        if (hcm) {
+            if (sg.part == 3) return hc_begin(head->mix, false);
+            return hc_begin(sg.part == 2 ? layers[sg.layer].hcw[1] : layers[sg.layer].hcw[0], sg.part == 2);
+        }
         if (!fused) return fnx_rms_norm_rows(x, pending, norm_w, y, xq, T, c.n, c.eps, st);
         return fnx_boundary_rows(x, after_ffn ? nullptr : pending, after_ffn ? &moe_rows : nullptr, c.ncard > 1 ? &g_ring : nullptr, norm_w, y, xq, T, c.n,
                                  c.eps, (unsigned*) (b + w.err), st);
     };
-    const char* begin_name = fused ? "boundary" : "rms_norm";
+    const char* begin_name = hcm ? "hc_read" : fused ? "boundary" : "rms_norm";
     if (sg.part == 3) {
         FNX_REQUIRE(head, "window: no head");
         TRK(begin_name, begin_half(head->norm, nullptr));
@@ -373,7 +403,7 @@ static int window_stage(const FnxStackCfg* cfg, const FnxLayer* layers, const Fn
     } else {
         TRK("shared_expert", fnx_shared_expert(L.sh_gate_up, L.sh_down, xq, T, c.n, c.ff, (float*) (b + w.sh_gu), b + w.shq, (float*) (b + w.sh), st));
     }
-    if (!fused)   // fused: the next stage's boundary kernel weighs and adds the experts' rows itself
+    if (!fused)   // fused: the next stage's first kernel weighs and adds the experts' rows itself
         TRK("moe_combine", fnx_moe_combine((const float*) (b + w.part), (const float*) (b + w.topw), (const float*) (b + w.sh), rl, c.nexp, bo,
                                               T, c.n, c.topk, st));
     return 0;

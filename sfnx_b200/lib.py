@@ -51,7 +51,12 @@ class Rope(C.Structure):
 
 class StackCfg(C.Structure):
     _fields_ = [(k, C.c_int) for k in ("n", "nexp", "topk", "ff", "nk", "nv", "nq", "nkv", "hd", "nrot", "vocab0", "vocab_rows",
-                                        "nlayers", "ncard", "card")] + [("eps", C.c_float), ("rope_base", C.c_float)]
+                                        "nlayers", "ncard", "card")] + [("eps", C.c_float), ("rope_base", C.c_float), ("hc", C.c_int),
+                                                                        ("hc_lr", C.c_int)]
+
+
+class HcW(C.Structure):
+    _fields_ = [("norm", C.c_void_p), ("down", Q8S), ("up", Q8S), ("inj", C.c_void_p)]
 
 
 class Layer(C.Structure):
@@ -61,7 +66,8 @@ class Layer(C.Structure):
                 ("S", C.c_void_p), ("hist", C.c_void_p), ("snap", C.c_void_p), ("hsnap", C.c_void_p),
                 ("wq", Q8S), ("wk", Q8S), ("wv", Q8S), ("wo", Q8S), ("q_norm", C.c_void_p), ("k_norm", C.c_void_p),
                 ("kc", C.c_void_p), ("vc", C.c_void_p), ("pages", KvPages),
-                ("router", C.c_void_p), ("gate_up", Experts), ("down", Experts), ("sh_gate_up", Q8S), ("sh_down", Q8S), ("gdn_log", C.c_void_p)]
+                ("router", C.c_void_p), ("gate_up", Experts), ("down", Experts), ("sh_gate_up", Q8S), ("sh_down", Q8S), ("gdn_log", C.c_void_p),
+                ("hcw", HcW * 2)]
 
 
 class WindowLanes(C.Structure):
@@ -71,7 +77,7 @@ class WindowLanes(C.Structure):
 
 
 class Head(C.Structure):
-    _fields_ = [("norm", C.c_void_p), ("out", Q8S)]
+    _fields_ = [("norm", C.c_void_p), ("out", Q8S), ("mix", HcW)]
 
 
 class Sampling(C.Structure):
@@ -128,6 +134,7 @@ _SIGS = {
     "fnx_gdn_replay": [_p, _i, _i, _p],
     "fnx_ring_gather": [_p, _i, _p, _i, _p, _p, _p, _p, _p],
     "fnx_attn_finish_ring": [_p, _p, _p, _p, _p, _i, _i, _i, _p, _p],
+    "fnx_hc_expand": [_p, _p, _i, _i, _i, _p],
     "fnx_hc_write": [_p, _p, _p, _i, _i, _i, _p],
     "fnx_hc_read": [_p, _p, _p, _p, Q8S, Q8S, _p, _f, _p, _p, _p, _p, _i, _i, _i, _i, _p],
     "fnx_attn_prep_append": [_p, _p, _p, _p, _p, _p, _p, KvPages, _i, _i, _i, _p, _f, Rope, _i, _i, _i, _p],

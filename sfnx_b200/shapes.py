@@ -23,4 +23,6 @@ class StackShape:
     rope_base: float = 1e7
     sigma: float = 0.02
     experts: str = "q4k"   # routed experts: "q4k" (Q4_K gate|up, Q6_K down) or "q8_0" (both Q8_0)
+    hc: int = 1            # residual streams: 1 = plain residual + RMS norm; > 1 = hyper-connections (reads mix the streams)
+    hc_lr: int = 320       # the hyper-connections' low rank
     kv_q8: bool = False    # K/V rows as int8 in groups of 32 with f16 scales (the reference's kv_q8) instead of f16

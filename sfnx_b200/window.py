@@ -44,13 +44,15 @@ class SyntheticStack:
         self.v0, self.vrows = vocab_slice(s.vocab, ncard, card)
         self.kv_rows = lib.fnx_kv_rows_per_card(s.ctx + s.kv_slack, ncard)
         self.cfg = L.StackCfg(s.n, s.nexp, s.topk, self.ffs, self.nk, self.nv, s.nq, s.nkv, s.hd, s.nrot, self.v0, self.vrows,
-                              len(s.kinds), ncard, card, s.eps, s.rope_base)
+                              len(s.kinds), ncard, card, s.eps, s.rope_base, s.hc if s.hc > 1 else 0, s.hc_lr)
         self.layers = (L.Layer * len(s.kinds))()
         self.gdn_state = []   # (S, hist) of the DeltaNet layers, for snapshots
         for l, kind in enumerate(s.kinds):
             self._build_layer(l, kind)
         self.head = L.Head(self._t(torch.ones(s.n, device=self.dev)).data_ptr(), self._q8s(len(s.kinds), "output", s.vocab, s.n,
                                                                                           row_slice=slice(self.v0, self.v0 + self.vrows)))
+        if s.hc > 1:
+            self.head.mix = self._hcw(len(s.kinds), "mix", inject=False)
         emb = torch.empty(s.vocab * s.n, dtype=torch.float32, device=self.dev)
         L.call("fnx_synth_normal", emb.data_ptr(), emb.numel(), 1.0, _seed(seed, -1, "embed"), L.stream())
         self.embed = self._t(emb.half().view(s.vocab, s.n).view(torch.int16))
@@ -95,6 +97,20 @@ class SyntheticStack:
         self.named[(layer, name)] = (q, d)
         return L.Q8S(q.data_ptr(), d.data_ptr())
 
+    def _hcw(self, layer, name, inject=True):
+        """One hyper-connection read's weights (replicated on every GPU): norm [hc n] near 1, down Q8_0 [lr][hc n], up Q8_0
+        [hc n][lr], bf16 inject rows [hc][hc n]."""
+        s = self.shape
+        D = s.hc * s.n
+        norm = self._t(1 + 0.1 * self._normal(layer, name + "_norm", (D,), 1.0))
+        self.named[(layer, name + "_norm")] = norm
+        hw = L.HcW(norm.data_ptr(), self._q8s(layer, name + "_down", s.hc_lr, D), self._q8s(layer, name + "_up", D, s.hc_lr), None)
+        if inject:
+            inj = self._t((self._normal(layer, name + "_inj", (s.hc, D), 0.05).view(torch.int32) >> 16).to(torch.int16))
+            self.named[(layer, name + "_inj")] = inj
+            hw.inj = inj.data_ptr()
+        return hw
+
     def _kv_slice(self, layer, name):
         """This GPU's rows of a K or V cache N(0, 1) over every position: the whole cache is generated (the same on every
         GPU) and local row r = the row of position ((r / 4) ncard + card) 4 + r % 4.  With shape.kv_q8 the rows are int8
@@ -122,6 +138,8 @@ class SyntheticStack:
         Lr.kind = kind
         Lr.norm1 = self._t(torch.ones(s.n, device=self.dev)).data_ptr()
         Lr.norm2 = self._t(torch.ones(s.n, device=self.dev)).data_ptr()
+        if s.hc > 1:
+            Lr.hcw[0], Lr.hcw[1] = self._hcw(l, "hc0"), self._hcw(l, "hc1")
         if kind == 0:
             HS = L.HS
             khs = list(range(self.kh0, self.kh0 + self.nk))

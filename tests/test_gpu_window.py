@@ -52,11 +52,31 @@ class OracleStack:
         pending = None
         self.last = {"T": T, "tag": tag, "snaps": {}}
         ctl = np.array([pos0, tag], np.int32)
-        for l, kind in enumerate(s.kinds):
+        hc = s.hc if s.hc > 1 else 0
+        R = np.ascontiguousarray(np.repeat(x[:, None, :], hc, axis=1)) if hc else None   # every stream starts as the embedding row
+        inj = {"a": None, "f": None}
+
+        def hcw(layer, name):
+            return h[(layer, name + "_norm")], _q8s(h, (layer, name + "_down")), _q8s(h, (layer, name + "_up")), \
+                (h[(layer, name + "_inj")].view(np.uint16) if (layer, name + "_inj") in h else None)
+
+        def begin(layer, name, prev, out):
+            """A half's input: hyper-connections: the read that folds `pending` in (inject values of the half before from
+            inj[prev], this read's into inj[out]); else residual + RMS norm.  Returns (xn, xq)."""
+            nonlocal x
+            if hc:
+                norm, down, up, winj = hcw(layer, name)
+                mixed, i_out, q8 = O.hc_read(R, norm, down, up, s.eps, pending, inj[prev] if pending is not None else None, winj, want_q8=True)
+                if winj is not None:
+                    inj[out] = i_out
+                return mixed, q8
             if pending is not None:
                 x = x + pending
-            xn = O.rms_norm_rows(x, ones, s.eps)
-            xq = O.quantize_q8_1(xn)
+            xn_ = O.rms_norm_rows(x, ones, s.eps)
+            return xn_, O.quantize_q8_1(xn_)
+
+        for l, kind in enumerate(s.kinds):
+            xn, xq = begin(l, "hc0", "f", "a")
             if kind == 0:
                 qkvz = O.q8s_gemv(*_q8s(h, (l, "qkvz")), xq, T)
                 ab = O.gemv_f32(h[(l, "ab")], xn, 4)
@@ -76,8 +96,8 @@ class OracleStack:
                 part = O.attn_partial(qg, kc, vc, 0, 1, pos0, s.nq, s.nkv, s.hd, q8_rows=q8_rows)
                 att = O.attn_merge([part], qg, s.nq, s.hd)
                 bo = O.q8s_gemv(*_q8s(h, (l, "wo")), O.quantize_q8_1(att.reshape(T, -1)), T)
-            x = x + bo
-            xn = O.rms_norm_rows(x, ones, s.eps)
+            pending = bo
+            xn, xq = begin(l, "hc1", "a", "f")
             w = {"n": n, "nexp": s.nexp, "ffs": self.ffs, "router": h[(l, "router")], "sh_gu": _q8s(h, (l, "sh_gate_up")),
                  "sh_dn": _q8s(h, (l, "sh_down"))}
             if s.experts == "q8_0":
@@ -86,9 +106,8 @@ class OracleStack:
             else:
                 w["gu_q4k"] = h[(l, "gate_up")]
                 w["dn_planes"] = (h[(l, "down")][0], h[(l, "down")][1], h[(l, "down")][2].view(np.int8), h[(l, "down")][3].view(np.uint16))
-            pending = cases.moe_oracle(w, xn, s.topk)["out"]
-        x = x + pending
-        xq = O.quantize_q8_1(O.rms_norm_rows(x, ones, s.eps))
+            pending = cases.moe_oracle(w, xn, s.topk)["out"]   # quantises xn itself: the read's q8_1 rows are the same function of it
+        _, xq = begin(len(s.kinds), "mix", "f", "a")
         logits = O.q8s_gemv(*_q8s(h, (len(s.kinds), "output")), xq, T)
         _, best, err = O.argmax(logits)
         assert err == 0
@@ -100,11 +119,11 @@ class OracleStack:
             O.gdn_rollback(self.state[(l, "S")], self.state[(l, "hist")], snap, hsnap, np.array([0, tag], np.int32), self.nk, self.nv, T, n)
 
 
-def _make(kinds, seed, experts="q4k", kv_q8=False):
+def _make(kinds, seed, experts="q4k", kv_q8=False, hc=1):
     from sfnx_b200.window import StackShape, SyntheticStack, WindowRunner
 
     shape = StackShape(n=512, nexp=32, topk=4, ff=256, nkh=2, nvh=4, nq=4, nkv=2, hd=128, nrot=64, vocab=2048, kinds=kinds, ctx=300,
-                       kv_slack=256, experts=experts, kv_q8=kv_q8)
+                       kv_slack=256, experts=experts, kv_q8=kv_q8, hc=hc, hc_lr=64)
     stack = SyntheticStack(shape, seed=seed, device="cuda:0")
     return shape, stack, WindowRunner(stack, 16, graph=True), OracleStack(stack)
 
@@ -167,6 +186,16 @@ def test_window_q8_0_experts_bit_exact(monkeypatch):
     monkeypatch.setenv("FNX_ATTN_EXACT", "1")
     shape, stack, runner, orc = _make([0, 1], seed=8, experts="q8_0")
     _, total = _run_windows(shape, stack, runner, orc, nwin=3, seed=3, exact=True)
+    assert 3 <= total <= 48
+
+
+def test_window_hyper_connections_bit_exact(monkeypatch):
+    """Whole windows of a stack with four residual streams: every half begins with the hyper-connection read that folds
+    the half before into the streams (reference src/engine.cu:1013-1016, 935, 1049), the head with the final mixer;
+    logits, tokens, accepted counts and rolled-back state bit for bit against the same composition on the CPU oracle."""
+    monkeypatch.setenv("FNX_ATTN_EXACT", "1")
+    shape, stack, runner, orc = _make([0, 1, 0, 1], seed=10, hc=4)
+    _, total = _run_windows(shape, stack, runner, orc, nwin=3, seed=5, exact=True)
     assert 3 <= total <= 48
 
 
