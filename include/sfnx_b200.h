@@ -291,6 +291,8 @@ size_t fnx_hc_scratch_floats(int T, int n, int hc, int lr);
 /* R[t][c] = x[t] for every stream c: a window's first residual (the reference's host fills the streams with the embedding
  * row before it uploads them, src/engine.cu:782-789 embed_into) */
 int fnx_hc_expand(const float* x, float* R, int T, int n, int hc, void* st);
+/* reference src/kernels.hpp add_streams (src/kernels.cu:2207-2222): R[t][c] = h[t][c] + e[t] */
+int fnx_hc_add_streams(const float* h, const float* e, float* R, int T, int n, int hc, void* st);
 int fnx_hc_read(float* R, const float* bo_prev, const float* inj_prev, const float* w_norm, FnxQ8S w_down, FnxQ8S w_up, const uint16_t* w_inj,
                 float eps, float* mixed, float* inject, float* scratch, void* q8, int T, int n, int hc, int lr, void* st);
 
@@ -372,6 +374,7 @@ typedef struct FnxStackCfg {
     int nlayers, ncard, card;
     float eps, rope_base;
     int hc, hc_lr; /* residual streams (0 or 1: one stream, plain residual + RMS norm) and the hyper-connections' low rank */
+    int r_preset;  /* hc > 1: the streams are in place before stage 0 (fnx_draft_begin made them), not expanded from x */
 } FnxStackCfg;
 
 /* one hyper-connection read's weights (reference LayerW hc_norm / hc_down / hc_up / hc_inj, src/model.hpp:120-124):
@@ -417,11 +420,24 @@ typedef struct FnxHead {
     FnxHcW mix; /* with cfg.hc > 1: the final mixer (no inject rows) instead of norm */
 } FnxHead;
 
+/* The draft (MTP) layer: one attention layer with hyper-connections, its FFN, a final mixer and a head over a draft
+ * vocabulary, fed by a window's residual streams and the next tokens' embeddings (reference MtpCard, src/model.hpp:207-218;
+ * Engine::mtp_enqueue, src/engine.cu:1275-1313).  It runs as a one-layer stack (cfg with kinds = {attention}, hc > 1,
+ * r_preset = 1, vocab rows = this GPU's draft-vocabulary rows) whose streams fnx_draft_begin makes first:
+ *   R[t][c] = fc_hid . rms(src[t] over all streams, norm_hid)[c] + fc_emb . rms(emb[t], norm_emb)
+ * src [T][hc n] (rows of a window's streams), emb [T][n]; then fnx_window_stage for stages 0 .. as for any stack. */
+typedef struct FnxDraft {
+    const float *norm_emb, *norm_hid; /* [n], [hc n] */
+    FnxQ8S fc_emb, fc_hid;            /* [n][n] each */
+} FnxDraft;
+int fnx_draft_begin(const FnxStackCfg* cfg, const FnxDraft* d, void* ws, const float* src, const float* emb, int T, void* st);
+
 /* what the caller must do across GPUs after a stage (nothing when ncard is 1) */
 enum { FNX_AFTER_NONE = 0, FNX_AFTER_SUM_BO = 1, FNX_AFTER_GATHER_PARTIALS = 2, FNX_AFTER_GATHER_BEST = 3 };
 /* workspace buffers a caller reads or writes */
 enum { FNX_BUF_X = 0, FNX_BUF_BO = 1, FNX_BUF_PARTIALS = 2, FNX_BUF_BEST_V = 3, FNX_BUF_BEST_I = 4, FNX_BUF_ERR = 5, FNX_BUF_CTL = 6,
-       FNX_BUF_LOGITS = 7, FNX_BUF_COPY_JOBS = 8, FNX_BUF_NJOBS = 9 };
+       FNX_BUF_LOGITS = 7, FNX_BUF_COPY_JOBS = 8, FNX_BUF_NJOBS = 9,
+       FNX_BUF_STREAMS = 10 /* hc > 1: the residual streams [T][hc n] as the window left them (a draft layer's source rows) */ };
 
 size_t fnx_window_workspace_bytes(const FnxStackCfg* cfg);
 /* zeroes the counters the kernels expect at zero (once, before the first window) */

@@ -58,6 +58,14 @@ __global__ void k_hc_expand(const float* __restrict__ x, float* __restrict__ R, 
     if (e < n * hc) R[(size_t) t * n * hc + e] = x[(size_t) t * n + e % n];
 }
 
+// R[t][c][i] = h[t][c][i] + e[t][i] (reference src/kernels.cu:2207-2212)
+__global__ void k_hc_add_streams(const float* __restrict__ h, const float* __restrict__ e, float* __restrict__ R, int n, int hc) {
+    pdl_wait();
+    pdl_go();
+    const int t = blockIdx.y, j = blockIdx.x * blockDim.x + threadIdx.x;
+    if (j < n * hc) R[(size_t) t * n * hc + j] = fadd(h[(size_t) t * n * hc + j], e[(size_t) t * n + j % n]);
+}
+
 __device__ __forceinline__ float hc_rprime(const HcArgs& a, int t, int c, int i) {
     float r = a.R[((size_t) t * a.hc + c) * a.n + i];
     if (a.bo) r = ffma(a.bo[(size_t) t * a.n + i], fmul(2.0f, ex_sigmoid(fdiv(a.inj_prev[t * a.hc + c], (float) a.hc))), r);
@@ -295,6 +303,12 @@ int fnx_hc_expand(const float* x, float* R, int T, int n, int hc, void* st) {
     FNX_REQUIRE(T >= 1 && T <= FNX_MAXT && n >= 1 && hc >= 1, "hc_expand: %d rows, %d streams of %d", T, hc, n);
     launch(0, k_hc_expand, dim3((n * hc + 255) / 256, T), 256, 0, strm(st), x, R, n, hc);
     return launch_ok("hc_expand");
+}
+
+int fnx_hc_add_streams(const float* h, const float* e, float* R, int T, int n, int hc, void* st) {
+    FNX_REQUIRE(T >= 1 && T <= FNX_MAXT && n >= 1 && hc >= 1, "hc_add_streams: %d rows, %d streams of %d", T, hc, n);
+    launch(0, k_hc_add_streams, dim3((n * hc + 255) / 256, T), 256, 0, strm(st), h, e, R, n, hc);
+    return launch_ok("hc_add_streams");
 }
 
 size_t fnx_hc_scratch_floats(int T, int n, int hc, int lr) {

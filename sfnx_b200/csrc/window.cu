@@ -6,6 +6,8 @@
 #include <cstdlib>
 #include <cstring>
 
+#include <algorithm>
+
 #include "common.cuh"
 #include "moe_internal.cuh"
 
@@ -84,7 +86,7 @@ struct Traced {
 // the workspace's buffers, as offsets from its base
 struct Ws {
     size_t x, bo, xn, xq, qkvz, ab, yq, qg, k, v, att, partials, att_scratch, rlogits, topi, topw, jobs_gu, jobs_dn, njobs, rscratch, gu,
-        hq, part, sh_gu, shq, sh, logits, keys, best_v, best_i, err, ctl, gdn_scratch, copy_jobs, replay_jobs, hc_R, hc_inj, hc_scratch, total;
+        hq, part, sh_gu, shq, sh, logits, keys, best_v, best_i, err, ctl, gdn_scratch, copy_jobs, replay_jobs, hc_R, hc_inj, hc_scratch, dr_en, dr_e2, dr_h2, dr_q, total;
 };
 
 static Ws carve(const FnxStackCfg& c) {
@@ -137,6 +139,11 @@ static Ws carve(const FnxStackCfg& c) {
     w.hc_R = take(T * hcn * n * 4);
     w.hc_inj = take(2 * T * (hcn ? hcn : 1) * 4);
     w.hc_scratch = take(hcn ? fnx_hc_scratch_floats((int) T, c.n, c.hc, c.hc_lr) * 4 : 0);
+    const size_t dr = c.r_preset ? hcn : 0;   // the draft layer's prologue: normed embeddings, both projections, the streams' q8_1 rows
+    w.dr_en = take(dr ? T * n * 4 : 0);
+    w.dr_e2 = take(dr ? T * n * 4 : 0);
+    w.dr_h2 = take(T * dr * n * 4);
+    w.dr_q = take(T * dr * (n / 32) * 36);
     w.total = o;
     return w;
 }
@@ -215,6 +222,7 @@ void* fnx_window_buf(const FnxStackCfg* cfg, void* ws, int which) {
         case FNX_BUF_LOGITS: return b + w.logits;
         case FNX_BUF_COPY_JOBS: return b + w.copy_jobs;
         case FNX_BUF_NJOBS: return b + w.njobs;
+        case FNX_BUF_STREAMS: return b + w.hc_R;
     }
     fail("window_buf: no buffer %d", which);
     return nullptr;
@@ -273,7 +281,7 @@ static int window_stage(const FnxStackCfg* cfg, const FnxLayer* layers, const Fn
             TRY(fnx_moe_combine((const float*) (b + w.part), (const float*) (b + w.topw), (const float*) (b + w.sh), (const float*) (b + w.rlogits), c.nexp, bo,
                                 T, c.n, c.topk, st));
         if (pending && c.ncard > 1 && g_ring_set) TRY(fnx_ring_sum(bo, T, c.n, &g_ring, (unsigned*) (b + w.err), st));
-        if (stage == 0) TRY(fnx_hc_expand(x, hcR, T, c.n, c.hc, st));
+        if (stage == 0 && !c.r_preset) TRY(fnx_hc_expand(x, hcR, T, c.n, c.hc, st));
         // a read before a mixer half (or the head's) takes the FFN half's inject values (buffer 1) and leaves its own in
         // buffer 0; a read before an FFN half the other way round
         const float* inj_prev = ffn_half ? inj_buf[0] : inj_buf[1];
@@ -422,6 +430,26 @@ static int window_stage_sunk(const FnxStackCfg* cfg, const FnxLayer* layers, con
     const int rc = window_stage(cfg, layers, head, ws, T, stage, lanes, st);
     fault_sink(nullptr);
     return rc;
+}
+
+int fnx_draft_begin(const FnxStackCfg* cfg, const FnxDraft* d, void* ws, const float* src, const float* emb, int T, void* st) {
+    TRY(check_cfg(cfg));
+    FNX_REQUIRE(cfg->hc > 1 && cfg->r_preset && d && ws && src && emb, "draft_begin: a stack with residual streams made ahead (hc > 1, r_preset), weights and rows");
+    FNX_REQUIRE(T >= 1 && T <= FNX_MAXT, "draft_begin: T %d outside 1..%d", T, FNX_MAXT);
+    const FnxStackCfg& c = *cfg;
+    const Ws w = carve(c);
+    char* b = (char*) ws;
+    float *en = (float*) (b + w.dr_en), *e2 = (float*) (b + w.dr_e2), *h2 = (float*) (b + w.dr_h2);
+    uint8_t* dq = (uint8_t*) (b + w.dr_q);
+    const size_t rowq = (size_t) (c.n / 32) * 36;
+    // the tokens' embeddings: RMS norm, q8_1, fc_embedding
+    TRY(fnx_rms_norm_rows(const_cast<float*>(emb), nullptr, d->norm_emb, en, b + w.xq, T, c.n, c.eps, st));
+    TRY(fnx_q8s_gemv(d->fc_emb, c.n, c.n, b + w.xq, e2, c.n, T, st));
+    // the source rows: one RMS norm over all streams, then every stream of every row through fc_hidden (hc T rows of n)
+    TRY(fnx_rms_norm_rows(const_cast<float*>(src), nullptr, d->norm_hid, nullptr, dq, T, c.n * c.hc, c.eps, st));
+    for (int r0 = 0; r0 < c.hc * T; r0 += FNX_MAXT)
+        TRY(fnx_q8s_gemv(d->fc_hid, c.n, c.n, dq + (size_t) r0 * rowq, h2 + (size_t) r0 * c.n, c.n, std::min((int) FNX_MAXT, c.hc * T - r0), st));
+    return fnx_hc_add_streams(h2, e2, (float*) (b + w.hc_R), T, c.n, c.hc, st);
 }
 
 int fnx_window_stage(const FnxStackCfg* cfg, const FnxLayer* layers, const FnxHead* head, void* ws, int T, int stage, void* st) {

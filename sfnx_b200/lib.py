@@ -52,7 +52,7 @@ class Rope(C.Structure):
 class StackCfg(C.Structure):
     _fields_ = [(k, C.c_int) for k in ("n", "nexp", "topk", "ff", "nk", "nv", "nq", "nkv", "hd", "nrot", "vocab0", "vocab_rows",
                                         "nlayers", "ncard", "card")] + [("eps", C.c_float), ("rope_base", C.c_float), ("hc", C.c_int),
-                                                                        ("hc_lr", C.c_int)]
+                                                                        ("hc_lr", C.c_int), ("r_preset", C.c_int)]
 
 
 class HcW(C.Structure):
@@ -74,6 +74,10 @@ class WindowLanes(C.Structure):
     _fields_ = [("nseg", C.c_int), ("rows", C.c_int), ("ctl", C.c_void_p), ("row0", C.c_void_p), ("row_pos", C.c_void_p), ("row_pt", C.c_void_p),
                 ("ctl_host", C.c_void_p), ("pt_host", C.c_void_p), ("S", C.c_void_p), ("hist", C.c_void_p), ("S_host", C.c_void_p),
                 ("hist_host", C.c_void_p)]
+
+
+class Draft(C.Structure):
+    _fields_ = [("norm_emb", C.c_void_p), ("norm_hid", C.c_void_p), ("fc_emb", Q8S), ("fc_hid", Q8S)]
 
 
 class Head(C.Structure):
@@ -135,6 +139,8 @@ _SIGS = {
     "fnx_ring_gather": [_p, _i, _p, _i, _p, _p, _p, _p, _p],
     "fnx_attn_finish_ring": [_p, _p, _p, _p, _p, _i, _i, _i, _p, _p],
     "fnx_hc_expand": [_p, _p, _i, _i, _i, _p],
+    "fnx_hc_add_streams": [_p, _p, _p, _i, _i, _i, _p],
+    "fnx_draft_begin": [_p, _p, _p, _p, _p, _i, _p],
     "fnx_hc_write": [_p, _p, _p, _i, _i, _i, _p],
     "fnx_hc_read": [_p, _p, _p, _p, Q8S, Q8S, _p, _f, _p, _p, _p, _p, _i, _i, _i, _i, _p],
     "fnx_attn_prep_append": [_p, _p, _p, _p, _p, _p, _p, KvPages, _i, _i, _i, _p, _f, Rope, _i, _i, _i, _p],

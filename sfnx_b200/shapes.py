@@ -25,4 +25,5 @@ class StackShape:
     experts: str = "q4k"   # routed experts: "q4k" (Q4_K gate|up, Q6_K down) or "q8_0" (both Q8_0)
     hc: int = 1            # residual streams: 1 = plain residual + RMS norm; > 1 = hyper-connections (reads mix the streams)
     hc_lr: int = 320       # the hyper-connections' low rank
+    draft: bool = False    # the stack is a draft (MTP) layer: its streams come from a window's rows and the next tokens' embeddings
     kv_q8: bool = False    # K/V rows as int8 in groups of 32 with f16 scales (the reference's kv_q8) instead of f16

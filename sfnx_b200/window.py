@@ -44,7 +44,7 @@ class SyntheticStack:
         self.v0, self.vrows = vocab_slice(s.vocab, ncard, card)
         self.kv_rows = lib.fnx_kv_rows_per_card(s.ctx + s.kv_slack, ncard)
         self.cfg = L.StackCfg(s.n, s.nexp, s.topk, self.ffs, self.nk, self.nv, s.nq, s.nkv, s.hd, s.nrot, self.v0, self.vrows,
-                              len(s.kinds), ncard, card, s.eps, s.rope_base, s.hc if s.hc > 1 else 0, s.hc_lr)
+                              len(s.kinds), ncard, card, s.eps, s.rope_base, s.hc if s.hc > 1 else 0, s.hc_lr, 1 if s.draft else 0)
         self.layers = (L.Layer * len(s.kinds))()
         self.gdn_state = []   # (S, hist) of the DeltaNet layers, for snapshots
         for l, kind in enumerate(s.kinds):
@@ -53,6 +53,14 @@ class SyntheticStack:
                                                                                           row_slice=slice(self.v0, self.v0 + self.vrows)))
         if s.hc > 1:
             self.head.mix = self._hcw(len(s.kinds), "mix", inject=False)
+        self.draft = None
+        if s.draft:   # the draft layer's prologue (reference MtpCard: norm_emb, norm_hid, fc_emb, fc_hid; replicated)
+            assert s.hc > 1, "a draft layer mixes residual streams"
+            nl = len(s.kinds)
+            ne = self._t(1 + 0.1 * self._normal(nl, "norm_emb", (s.n,), 1.0))
+            nh = self._t(1 + 0.1 * self._normal(nl, "norm_hid", (s.hc * s.n,), 1.0))
+            self.named[(nl, "norm_emb")], self.named[(nl, "norm_hid")] = ne, nh
+            self.draft = L.Draft(ne.data_ptr(), nh.data_ptr(), self._q8s(nl, "fc_emb", s.n, s.n), self._q8s(nl, "fc_hid", s.n, s.n))
         emb = torch.empty(s.vocab * s.n, dtype=torch.float32, device=self.dev)
         L.call("fnx_synth_normal", emb.data_ptr(), emb.numel(), 1.0, _seed(seed, -1, "embed"), L.stream())
         self.embed = self._t(emb.half().view(s.vocab, s.n).view(torch.int16))
@@ -403,6 +411,9 @@ class WindowRunner:
         self.d_in = torch.zeros(L.MAXT + 2, dtype=torch.int32, device=stack.dev)
         self.ids, self.ctl_in = self.d_in[:L.MAXT], self.d_in[L.MAXT:]
         self.x = stack.buf(0, torch.float32, T * s.n)
+        if s.draft:   # a draft layer's inputs: rows of a window's residual streams, and the next tokens' embeddings
+            self.src = torch.zeros((T, s.hc * s.n), dtype=torch.float32, device=stack.dev)
+            self.demb = torch.zeros((T, s.n), dtype=torch.float32, device=stack.dev)
         self.bo = stack.buf(1, torch.float32, T * s.n)
         self.partials = stack.buf(2, torch.float32, stack.ncard * T * s.nq * (s.hd + 2))
         self.best_v = stack.buf(3, torch.float32, T)
@@ -510,7 +521,11 @@ class WindowRunner:
             L.call("fnx_window_side_stream", None, None, None)
         L.call("fnx_window_ring", C.byref(self.ring) if self.ring is not None else None)
         self.ctl.copy_(self.ctl_in)
-        L.call("fnx_embed_rows", stack.embed.data_ptr(), self.ids.data_ptr(), self.x.data_ptr(), T, stack.shape.n, st)
+        if stack.shape.draft:
+            L.call("fnx_embed_rows", stack.embed.data_ptr(), self.ids.data_ptr(), self.demb.data_ptr(), T, stack.shape.n, st)
+            L.call("fnx_draft_begin", C.byref(stack.cfg), C.byref(stack.draft), stack.ws.data_ptr(), self.src.data_ptr(), self.demb.data_ptr(), T, st)
+        else:
+            L.call("fnx_embed_rows", stack.embed.data_ptr(), self.ids.data_ptr(), self.x.data_ptr(), T, stack.shape.n, st)
         for i in range(self.nstages):
             if self.lanes is not None:
                 L.call("fnx_window_stage_lanes", C.byref(stack.cfg), stack.layers, C.byref(stack.head), stack.ws.data_ptr(), C.byref(self.lanes.c),
@@ -585,6 +600,24 @@ class WindowRunner:
             raise L.FnxError("window error word %d (bit 1: a peer's addend never came; bit 8: a bounded on-chip wait ran out; bit 16: a "
                              "non-finite logit); the window's results are not to be used, the next window starts clean" % err)
         return self.merge_best()
+
+    def draft_chain(self, src_row, token, pos0, k, tag):
+        """A draft (MTP) layer's runner with T = 1: k tokens one after the other, as the reference's session drafts them
+        (src/engine_common.cu:1197-1205 draft: the first step from a window's stream row, every later one from the draft
+        layer's own streams as its last window left them; each step's token = the step before's argmax).  src_row:
+        [hc n] floats on the device; returns the k drafted head rows (indices into the draft vocabulary)."""
+        assert self.stack.shape.draft and self.T == 1, "a draft layer's runner of one row"
+        streams = self.stack.buf(10, torch.float32, self.stack.shape.hc * self.stack.shape.n)
+        out = []
+        with torch.cuda.stream(self.stream):
+            self.src[0].copy_(src_row.reshape(-1))
+        for i in range(k):
+            tok = self.window([token], pos0 + i, tag)[0]
+            out.append(tok)
+            token = tok
+            with torch.cuda.stream(self.stream):
+                self.src[0].copy_(streams)
+        return out
 
     def window_lanes(self, rows, pos, tags):
         """One window of several sequences: rows = the T token ids (lane i's rows at i * lanes.rows ..), pos[i] / tags[i]

@@ -54,6 +54,13 @@ class OracleStack:
         ctl = np.array([pos0, tag], np.int32)
         hc = s.hc if s.hc > 1 else 0
         R = np.ascontiguousarray(np.repeat(x[:, None, :], hc, axis=1)) if hc else None   # every stream starts as the embedding row
+        if s.draft:   # a draft layer: the streams from a window's rows and the next tokens' embeddings (reference mtp_enqueue)
+            nl = len(s.kinds)
+            en = O.rms_norm_rows(x, h[(nl, "norm_emb")], s.eps)
+            e2 = O.q8s_gemv(*_q8s(h, (nl, "fc_emb")), O.quantize_q8_1(en), T)
+            hn = O.rms_norm_rows(np.ascontiguousarray(self.src.reshape(T, hc * n)), h[(nl, "norm_hid")], s.eps)
+            h2 = O.q8s_gemv(*_q8s(h, (nl, "fc_hid")), O.quantize_q8_1(np.ascontiguousarray(hn.reshape(T * hc, n))), T * hc)
+            R = np.ascontiguousarray(h2.reshape(T, hc, n) + e2[:, None, :])
         inj = {"a": None, "f": None}
 
         def hcw(layer, name):
@@ -108,6 +115,7 @@ class OracleStack:
                 w["dn_planes"] = (h[(l, "down")][0], h[(l, "down")][1], h[(l, "down")][2].view(np.int8), h[(l, "down")][3].view(np.uint16))
             pending = cases.moe_oracle(w, xn, s.topk)["out"]   # quantises xn itself: the read's q8_1 rows are the same function of it
         _, xq = begin(len(s.kinds), "mix", "f", "a")
+        self.last_R = R   # the streams with every half folded in (what a draft layer's next step starts from)
         logits = O.q8s_gemv(*_q8s(h, (len(s.kinds), "output")), xq, T)
         _, best, err = O.argmax(logits)
         assert err == 0
@@ -119,11 +127,11 @@ class OracleStack:
             O.gdn_rollback(self.state[(l, "S")], self.state[(l, "hist")], snap, hsnap, np.array([0, tag], np.int32), self.nk, self.nv, T, n)
 
 
-def _make(kinds, seed, experts="q4k", kv_q8=False, hc=1):
+def _make(kinds, seed, experts="q4k", kv_q8=False, hc=1, draft=False):
     from sfnx_b200.window import StackShape, SyntheticStack, WindowRunner
 
     shape = StackShape(n=512, nexp=32, topk=4, ff=256, nkh=2, nvh=4, nq=4, nkv=2, hd=128, nrot=64, vocab=2048, kinds=kinds, ctx=300,
-                       kv_slack=256, experts=experts, kv_q8=kv_q8, hc=hc, hc_lr=64)
+                       kv_slack=256, experts=experts, kv_q8=kv_q8, hc=hc, hc_lr=64, draft=draft)
     stack = SyntheticStack(shape, seed=seed, device="cuda:0")
     return shape, stack, WindowRunner(stack, 16, graph=True), OracleStack(stack)
 
@@ -197,6 +205,52 @@ def test_window_hyper_connections_bit_exact(monkeypatch):
     shape, stack, runner, orc = _make([0, 1, 0, 1], seed=10, hc=4)
     _, total = _run_windows(shape, stack, runner, orc, nwin=3, seed=5, exact=True)
     assert 3 <= total <= 48
+
+
+def test_draft_layer_bit_exact(monkeypatch):
+    """The draft (MTP) layer (reference Engine::mtp_enqueue, src/engine.cu:1275-1313): streams made from a window's rows
+    (fc_hidden of their RMS norm over all streams) and the next tokens' embeddings (fc_embedding of their RMS norm), one
+    attention layer with hyper-connections, its FFN, the final mixer and the head, over two windows that append to the
+    layer's own K/V cache: logits and argmax bit for bit against the same composition on the CPU oracle."""
+    import torch
+
+    monkeypatch.setenv("FNX_ATTN_EXACT", "1")
+    shape, stack, runner, orc = _make([1], seed=11, hc=4, draft=True)
+    rng = np.random.default_rng(12)
+    pos = shape.ctx
+    for wdw in range(2):
+        src = rng.standard_normal((16, shape.hc, shape.n)).astype(np.float32)
+        rows = [int(v) for v in rng.integers(0, shape.vocab, 16)]
+        orc.src = src
+        ref_logits, ref_best = orc.window(rows, pos, 1 + wdw)
+        runner.src.copy_(torch.from_numpy(src.reshape(16, -1)))
+        got_best = runner.window(rows, pos, 1 + wdw)
+        got_logits = runner.logits.detach().cpu().numpy()
+        assert np.array_equal(got_logits.view(np.uint32), ref_logits.view(np.uint32)), "logits, window %d" % wdw
+        assert got_best == ref_best
+        pos += 16
+
+
+def test_draft_chain_equals_the_oracles(monkeypatch):
+    """Four tokens drafted one after the other (a runner of one row: the first step from a given stream row, the later ones
+    from the draft layer's own streams, each token the argmax before it) against the same chain on the CPU oracle."""
+    import torch
+
+    from sfnx_b200.window import WindowRunner
+
+    monkeypatch.setenv("FNX_ATTN_EXACT", "1")
+    shape, stack, _, orc = _make([1], seed=13, hc=4, draft=True)
+    r1 = WindowRunner(stack, 1, graph=True)
+    rng = np.random.default_rng(14)
+    src0 = rng.standard_normal((shape.hc, shape.n)).astype(np.float32)
+    want, src, tok = [], src0, 5
+    for i in range(4):
+        orc.src = src[None]
+        _, best = orc.window([tok], shape.ctx + i, 1)
+        want.append(best[0])
+        tok, src = best[0], orc.last_R[0].copy()
+    got = r1.draft_chain(torch.from_numpy(src0).to(stack.dev), 5, shape.ctx, 4, 1)
+    assert got == want
 
 
 def test_window_int8_kv_bit_exact():
