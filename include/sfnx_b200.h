@@ -272,9 +272,40 @@ typedef struct FnxLaneRows {
 } FnxLaneRows;
 int fnx_attn_part_lanes(const float* qg, const uint16_t* kc, const uint16_t* vc, FnxKvPages g, FnxLaneRows lr, float* part, int card, int ncard,
                         int T, int nq, int nkv, int hd, float* scratch, void* st);
+/* the same scan for rows with a selection of positions (reference src/kernels.cu:504-505, 525: attn / attn_part_lanes with
+ * cells, n_cells): row t with n_cells[t] >= 0 attends the n_cells[t] local rows cells[t * maxsel ...] in that order, a row
+ * with n_cells[t] = -1 every owned position up to its own.  lr empty (both null): one sequence at *pos0 + t */
+int fnx_attn_partial_cells(const float* qg, const uint16_t* kc, const uint16_t* vc, FnxKvPages g, FnxLaneRows lr, float* part, int card,
+                           int ncard, int T, const int* pos0, int nq, int nkv, int hd, float* scratch, const int* cells, const int* n_cells,
+                           int maxsel, void* st);
 int fnx_attn_splits(int nkv);
 int fnx_attn_finish(const float* parts, int nparts, int first_part, const float* qg, float* out, int T, int nq, int h0, int nh,
                     int hd, void* st);
+
+/* ---- the attention layers' block selection (reference src/qsa.cuh; src/kernels.hpp:195-217 qsa_maxsel, qsa_rows, qsa_index,
+ * qsa_select, qsa_select_lanes, qsa).  Keys of FNX_QSA_DIM, FNX_QSA_HEADS query heads, blocks of FNX_QSA_POOL positions,
+ * the first 64 dimensions rotated; `top` (the reference's 2048 / 4 = 512) is how many blocks a row keeps.
+ *   y       [T][fnx_qsa_rows()]  the projection: 4 query heads, then the raw key (fnx_qsa_proj: bf16 weights wq [512][n],
+ *                                wk [128][n] as bit patterns, x [T][n] f32)
+ *   ring    [ring_rows][128] f16 the raw keys of the last positions (position p at row p % ring_rows; ring_rows >= T + 4)
+ *   pooled  f16 rows of 128      block b's key at b * 128, or with a page table at pt[b / bpp] * page + (b % bpp) * 128,
+ *                                bpp = g.rows / 4 * ncard (a page holds every GPU's blocks; every GPU holds all keys)
+ *   q       [T][4][128]          the normed, rotated query heads (fnx_qsa_index writes q, ring and pooled)
+ *   scores  [T][max_pools], cells [T][fnx_qsa_maxsel(top)], n_cells [T] (-1: the row keeps every block)
+ * fnx_qsa runs the three in order (wq null: y already holds the projection), as the reference's qsa(). */
+#define FNX_QSA_DIM 128
+#define FNX_QSA_HEADS 4
+#define FNX_QSA_POOL 4
+int fnx_qsa_rows(void);
+int fnx_qsa_maxsel(int top);
+int fnx_qsa_proj(const uint16_t* wq, const uint16_t* wk, const float* x, float* y, int T, int n, void* st);
+int fnx_qsa_index(const float* y, const float* qn, const float* kn, uint16_t* ring, int ring_rows, uint16_t* pooled, FnxKvPages g, int ncard,
+                  float* q, const int* pos0, int T, float eps, FnxRope rope, void* st);
+int fnx_qsa_select(const float* q, const uint16_t* pooled, FnxKvPages g, FnxLaneRows lr, float* scores, int* cells, int* n_cells, int max_pools,
+                   const int* pos0, int T, int card, int ncard, int top, void* st);
+int fnx_qsa(const uint16_t* wq, const uint16_t* wk, const float* x, int n, float* y, const float* qn, const float* kn, uint16_t* ring,
+            int ring_rows, uint16_t* pooled, FnxKvPages g, float* q, float* scores, int* cells, int* n_cells, int max_pools, const int* pos0,
+            int T, float eps, FnxRope rope, int card, int ncard, int top, void* st);
 
 /* ---- hyper-connections of the residual streams (R: [T][hc][n], hc streams of width n)
  * reference src/kernels.hpp:356 hc_write (src/kernels.cu:1493-1503): R[t][c] += bo[t] * 2 sigmoid(inj[t][c] / hc) */

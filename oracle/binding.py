@@ -323,6 +323,54 @@ def attn_partial(qg, kc, vc, card, ncard, pos0, nq, nkv, hd=256, q8_rows=0):
     return part
 
 
+def attn_partial_cells(qg, kc, vc, card, ncard, pos0, nq, nkv, cells, n_cells, hd=256, q8_rows=0):
+    """cells [T][maxsel] int32, n_cells [T] int32 (-1: the row attends every owned position)."""
+    T = qg.shape[0]
+    part = np.zeros((T, nq, hd + 2), np.float32)
+    g = KvPages(None, 0, 0, q8_rows, 1 if q8_rows else 0)
+    lib().orc_attn_partial_cells(P(qg), P(kc), P(vc), C.byref(g), P(part), card, ncard, T, pos0, nq, nkv, hd, P(cells), P(n_cells),
+                                 cells.shape[1])
+    return part
+
+
+# ---------------------------------------------------------------- the attention layers' block selection
+QSA_DIM, QSA_HEADS, QSA_POOL = 128, 4, 4
+
+
+def _pages(pt, page, rows):
+    return KvPages(pt.ctypes.data_as(C.POINTER(C.c_int)) if pt is not None else None, page, rows, 0, 0)
+
+
+def qsa_proj(wq, wk, x):
+    """wq [512][n], wk [128][n] bf16 bit patterns (uint16); x [T][n] f32 -> y [T][640]."""
+    T, n = x.shape
+    y = np.zeros((T, QSA_HEADS * QSA_DIM + QSA_DIM), np.float32)
+    lib().orc_qsa_proj(P(wq), P(wk), P(x), P(y), T, n)
+    return y
+
+
+def qsa_index(y, qn, kn, ring, pooled, pos0, eps, base, ncard=1, pt=None, page=0, rows=0):
+    """ring [ring_rows][128], pooled: uint16 (f16 bits), both updated in place; returns q [T][4][128]."""
+    T = y.shape[0]
+    q = np.zeros((T, QSA_HEADS, QSA_DIM), np.float32)
+    g = _pages(pt, page, rows)
+    lib().orc_qsa_index(P(y), P(qn), P(kn), P(ring), ring.shape[0], P(pooled), C.byref(g), ncard, P(q), pos0, T, C.c_float(eps),
+                        C.c_float(base))
+    return q
+
+
+def qsa_select(q, pooled, pos, top, max_pools, card=0, ncard=1, pt=None, page=0, rows=0):
+    """pos [T] int32: every row's position.  Returns (scores [T][max_pools], cells [T][4 top + 3], n_cells [T])."""
+    T = q.shape[0]
+    scores = np.zeros((T, max_pools), np.float32)
+    cells = np.zeros((T, top * QSA_POOL + QSA_POOL - 1), np.int32)
+    n_cells = np.zeros(T, np.int32)
+    g = _pages(pt, page, rows)
+    pos = np.ascontiguousarray(pos, np.int32)
+    lib().orc_qsa_select(P(q), P(pooled), C.byref(g), P(scores), P(cells), P(n_cells), max_pools, P(pos), None, T, card, ncard, top)
+    return scores, cells, n_cells
+
+
 def attn_merge(parts, qg, nq, hd=256):
     T = qg.shape[0]
     out = np.zeros((T, nq, hd), np.float32)

@@ -59,7 +59,7 @@ static void kv_append_row(o_half* cache, const OrcKvPages* g, int r, int nkv, in
 }
 
 /* RMS norm with weight, then rotation of the pairs (i, i + nrot/2), i < nrot/2, at position pos */
-static void norm_rope(float* x, const float* w, int pos, float eps, const float* freq, float mscale, int hd, int nrot) {
+void orc_norm_rope(float* x, const float* w, int pos, float eps, const float* freq, float mscale, int hd, int nrot) {
     float tot = 0.f;
     for (int wp = 0; wp < hd / 32; ++wp) {
         float v[32];
@@ -94,8 +94,8 @@ void orc_attn_prep_append(float* qg, float* k, const float* v, const float* q_no
     orc_rope_freqs(rope_base, nrot, freq);
     for (int t = 0; t < T; ++t) {
         const int p = pos0 + t, j = p / 4;
-        for (int h = 0; h < nq; ++h) norm_rope(qg + ((size_t) t * nq + h) * 2 * hd, q_norm, p, eps, freq, 1.0f, hd, nrot);
-        for (int h = 0; h < nkv; ++h) norm_rope(k + ((size_t) t * nkv + h) * hd, k_norm, p, eps, freq, 1.0f, hd, nrot);
+        for (int h = 0; h < nq; ++h) orc_norm_rope(qg + ((size_t) t * nq + h) * 2 * hd, q_norm, p, eps, freq, 1.0f, hd, nrot);
+        for (int h = 0; h < nkv; ++h) orc_norm_rope(k + ((size_t) t * nkv + h) * hd, k_norm, p, eps, freq, 1.0f, hd, nrot);
         if (j % ncard != card) continue;
         const int r = (j / ncard) * 4 + p % 4;
         kv_append_row(kc, g, r, nkv, hd, k + (size_t) t * nkv * hd);
@@ -103,9 +103,11 @@ void orc_attn_prep_append(float* qg, float* k, const float* v, const float* q_no
     }
 }
 
-/* this card's partial for every (row, head): part[(t nq + h) (hd + 2)] = acc[hd], m, z */
-void orc_attn_partial(const float* qg, const o_half* kc, const o_half* vc, const OrcKvPages* g, float* part, int card,
-                      int ncard, int T, int pos0, int nq, int nkv, int hd) {
+/* this card's partial for every (row, head): part[(t nq + h) (hd + 2)] = acc[hd], m, z.  cells / n_cells (NULL: none): a
+ * row with n_cells[t] >= 0 attends the n_cells[t] local rows cells[t maxsel ...] in that order instead of every owned
+ * position up to its own (the block selection's list, src/kernels.cu:504-505, 525) */
+void orc_attn_partial_cells(const float* qg, const o_half* kc, const o_half* vc, const OrcKvPages* g, float* part, int card,
+                            int ncard, int T, int pos0, int nq, int nkv, int hd, const int* cells, const int* n_cells, int maxsel) {
     const int qpk = nq / nkv;
     const float rs = o_rsqrt((float) hd);
 #pragma omp parallel for collapse(2)
@@ -113,7 +115,8 @@ void orc_attn_partial(const float* qg, const o_half* kc, const o_half* vc, const
         for (int h = 0; h < nq; ++h) {
             const int kvh = h / qpk;
             const float* q = qg + ((size_t) t * nq + h) * 2 * hd;
-            const int ctx = orc_kv_owned(pos0 + t, card, ncard);
+            const int* list = cells && n_cells[t] >= 0 ? cells + (size_t) t * maxsel : NULL;
+            const int ctx = list ? n_cells[t] : orc_kv_owned(pos0 + t, card, ncard);
             const int len = ((ctx + ATT_SPLITS - 1) / ATT_SPLITS + ATT_CH - 1) / ATT_CH * ATT_CH;
             float sm[ATT_SPLITS], sz[ATT_SPLITS];
             float* sacc = (float*) calloc((size_t) ATT_SPLITS * hd, sizeof(float));
@@ -131,7 +134,7 @@ void orc_attn_partial(const float* qg, const o_half* kc, const o_half* vc, const
                             continue;
                         }
                         float a = 0.f;
-                        for (int d = 0; d < hd; ++d) a = fmaf(q[d], kv_value(kc, g, c0 + pp, nkv, hd, kvh, d), a);
+                        for (int d = 0; d < hd; ++d) a = fmaf(q[d], kv_value(kc, g, list ? list[c0 + pp] : c0 + pp, nkv, hd, kvh, d), a);
                         sv[pp] = a * rs;
                         cmax = fmaxf(cmax, sv[pp]);
                     }
@@ -142,7 +145,7 @@ void orc_attn_partial(const float* qg, const o_half* kc, const o_half* vc, const
                     m = mn;
                     for (int d = 0; d < hd; ++d) acc[d] = acc[d] * sc;
                     for (int pp = 0; pp < np; ++pp) {
-                        for (int d = 0; d < hd; ++d) acc[d] = fmaf(w[pp], kv_value(vc, g, c0 + pp, nkv, hd, kvh, d), acc[d]);
+                        for (int d = 0; d < hd; ++d) acc[d] = fmaf(w[pp], kv_value(vc, g, list ? list[c0 + pp] : c0 + pp, nkv, hd, kvh, d), acc[d]);
                     }
                 }
                 sm[s] = m;
@@ -163,6 +166,11 @@ void orc_attn_partial(const float* qg, const o_half* kc, const o_half* vc, const
             o[hd + 1] = z;
             free(sacc);
         }
+}
+
+void orc_attn_partial(const float* qg, const o_half* kc, const o_half* vc, const OrcKvPages* g, float* part, int card,
+                      int ncard, int T, int pos0, int nq, int nkv, int hd) {
+    orc_attn_partial_cells(qg, kc, vc, g, part, card, ncard, T, pos0, nq, nkv, hd, NULL, NULL, 0);
 }
 
 /* the cards' partials merged per head in ring order for the head's owner card c (heads [c nq/ncard, (c+1) nq/ncard)):

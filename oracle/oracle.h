@@ -108,7 +108,16 @@ void orc_attn_prep_append(float* qg, float* k, const float* v, const float* q_no
                           int hd, int nrot);
 void orc_attn_partial(const float* qg, const o_half* kc, const o_half* vc, const OrcKvPages* g, float* part, int card, int ncard,
                       int T, int pos0, int nq, int nkv, int hd);
+void orc_attn_partial_cells(const float* qg, const o_half* kc, const o_half* vc, const OrcKvPages* g, float* part, int card, int ncard,
+                            int T, int pos0, int nq, int nkv, int hd, const int* cells, const int* n_cells, int maxsel);
 void orc_attn_merge(const float* const* parts, const float* qg, float* out, int ncard, int T, int nq, int hd);
+
+/* the attention layers' block selection (oqsa.c) */
+void orc_qsa_proj(const uint16_t* wq, const uint16_t* wk, const float* x, float* y, int T, int n);
+void orc_qsa_index(const float* y, const float* qn, const float* kn, o_half* ring, int ring_rows, o_half* pooled, const OrcKvPages* g,
+                   int ncard, float* q, int pos0, int T, float eps, float rope_base);
+void orc_qsa_select(const float* q, const o_half* pooled, const OrcKvPages* g, float* scores, int* cells, int* n_cells, int max_pools,
+                    const int* pos, const int* const* pts, int T, int card, int ncard, int top);
 
 /* hyper-connections (ohc.c) */
 void orc_hc_write(float* R, const float* bo, const float* inj, int T, int n, int hc);

@@ -126,14 +126,17 @@ template <int HD>
 __global__ void __launch_bounds__(AX_THREADS, 1) k_attn_rows(const float* __restrict__ qg, const uint16_t* __restrict__ kc,
                                                            const uint16_t* __restrict__ vc, FnxKvPages g, float* __restrict__ acc_out,
                                                            AttPart* __restrict__ mz_out, int T, int nq, int nkv,
-                                                           const int* __restrict__ pos0p, int card, int ncard, FnxLaneRows lr) {
+                                                           const int* __restrict__ pos0p, int card, int ncard, FnxLaneRows lr,
+                                                           const int* __restrict__ cells, const int* __restrict__ n_cells, int maxsel) {
     constexpr int G = AX_THREADS / HD, APT = AX_PT / G, KLD = HD + 4;   // thread groups over the pairs; accumulators a thread
     const int s = blockIdx.x, kvl = blockIdx.y, lead = blockIdx.z, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int qpk = nq / nkv;
-    __shared__ int ctx_s[FNX_MAXT], len_s[FNX_MAXT], rows_s[FNX_MAXT], nr_s;
+    __shared__ int ctx_s[FNX_MAXT], len_s[FNX_MAXT], rows_s[FNX_MAXT], list_s[FNX_MAXT], nr_s;
     __shared__ const int* pt_s[FNX_MAXT];
     if (tid < T) {
-        const int c = kv_owned(lr.pos ? *lr.pos[tid] : *pos0p + tid, card, ncard);
+        const bool listed = cells && n_cells[tid] >= 0;   // the row attends a list of its own (the block selection's)
+        const int c = listed ? n_cells[tid] : kv_owned(lr.pos ? *lr.pos[tid] : *pos0p + tid, card, ncard);
+        list_s[tid] = listed;
         ctx_s[tid] = c;
         len_s[tid] = ((c + ATT_SPLITS - 1) / ATT_SPLITS + ATT_CH - 1) / ATT_CH * ATT_CH;
         pt_s[tid] = lr.pt ? lr.pt[tid] : g.pt;
@@ -144,6 +147,7 @@ __global__ void __launch_bounds__(AX_THREADS, 1) k_attn_rows(const float* __rest
         bool first = true;
         for (int t = 0; t < T; ++t) {
             if (pt_s[t] != pt_s[lead] || len_s[t] != len_s[lead]) continue;
+            if (t != lead && (list_s[t] || list_s[lead])) continue;   // a listed row is a group of its own
             if (t < lead) first = false;
             else rows_s[nr++] = t;
         }
@@ -154,6 +158,7 @@ __global__ void __launch_bounds__(AX_THREADS, 1) k_attn_rows(const float* __rest
     if (nr == 0) return;   // an earlier row leads this row's group
     g.pt = pt_s[lead];
     const int len = len_s[lead], p0 = s * len;
+    const int* list = list_s[lead] ? cells + (size_t) lead * maxsel : nullptr;
     int pend = 0;          // where the group's longest row ends inside this run
     for (int r = 0; r < nr; ++r) pend = max(pend, min(ctx_s[rows_s[r]], p0 + len));
     extern __shared__ __align__(16) float ax_sm[];
@@ -192,8 +197,9 @@ __global__ void __launch_bounds__(AX_THREADS, 1) k_attn_rows(const float* __rest
                     uint2 kr = make_uint2(0, 0), vr = kr;
                     float kd8 = 0.f, vd8 = 0.f;
                     if (pp < npmax) {
-                        const size_t at = kvq_row_at(g, c0 + pp, nkv, HD) + (size_t) kvl * HD + 8 * c8;
-                        const size_t sc = kvq_scale_at(g, c0 + pp, nkv, HD) + ((size_t) kvl * HD + 8 * c8) / 32;
+                        const int r = list ? list[c0 + pp] : c0 + pp;
+                        const size_t at = kvq_row_at(g, r, nkv, HD) + (size_t) kvl * HD + 8 * c8;
+                        const size_t sc = kvq_scale_at(g, r, nkv, HD) + ((size_t) kvl * HD + 8 * c8) / 32;
                         kr = *reinterpret_cast<const uint2*>(reinterpret_cast<const int8_t*>(kc) + at);
                         vr = *reinterpret_cast<const uint2*>(reinterpret_cast<const int8_t*>(vc) + at);
                         kd8 = h2f(kc[sc]), vd8 = h2f(vc[sc]);
@@ -207,7 +213,7 @@ __global__ void __launch_bounds__(AX_THREADS, 1) k_attn_rows(const float* __rest
                 } else {
                     uint4 kr = make_uint4(0, 0, 0, 0), vr = kr;
                     if (pp < npmax) {
-                        const size_t at = kv_row_at(g, c0 + pp, nkv, HD) + (size_t) kvl * HD + 8 * c8;
+                        const size_t at = kv_row_at(g, list ? list[c0 + pp] : c0 + pp, nkv, HD) + (size_t) kvl * HD + 8 * c8;
                         kr = *reinterpret_cast<const uint4*>(kc + at);
                         vr = *reinterpret_cast<const uint4*>(vc + at);
                     }
@@ -404,7 +410,8 @@ size_t fnx_attn_scratch_floats(int nq, int hd, int T) {   // the larger of the e
 }
 
 static int attn_partial_rows(const float* qg, const uint16_t* kc, const uint16_t* vc, FnxKvPages g, float* part, int card, int ncard, int T,
-                             const int* pos0, FnxLaneRows lr, int nq, int nkv, int hd, float* scratch, void* st) {
+                             const int* pos0, FnxLaneRows lr, int nq, int nkv, int hd, float* scratch, void* st,
+                             const int* cells = nullptr, const int* n_cells = nullptr, int maxsel = 0) {
     FNX_REQUIRE(T >= 1 && T <= FNX_MAXT, "attn: T %d outside 1..%d", T, FNX_MAXT);
     FNX_REQUIRE(hd == 256 || hd == 128, "attn: head dim %d (128 or 256)", hd);
     FNX_REQUIRE(nkv >= 1 && nq % nkv == 0 && nq / nkv <= ATT_MAXQPK, "attn: %d query heads over %d KV heads", nq, nkv);
@@ -416,10 +423,10 @@ static int attn_partial_rows(const float* qg, const uint16_t* kc, const uint16_t
     const dim3 grid(ATT_SPLITS, nkv, T);   // block z = t works only when row t leads a group of rows
     if (hd == 256) {
         if (smem_optin(k_attn_rows<256>, sm, "attn partial")) return 1;
-        k_attn_rows<256><<<grid, AX_THREADS, sm, strm(st)>>>(qg, kc, vc, g, acc, mz, T, nq, nkv, pos0, card, ncard, lr);
+        k_attn_rows<256><<<grid, AX_THREADS, sm, strm(st)>>>(qg, kc, vc, g, acc, mz, T, nq, nkv, pos0, card, ncard, lr, cells, n_cells, maxsel);
     } else {
         if (smem_optin(k_attn_rows<128>, sm, "attn partial")) return 1;
-        k_attn_rows<128><<<grid, AX_THREADS, sm, strm(st)>>>(qg, kc, vc, g, acc, mz, T, nq, nkv, pos0, card, ncard, lr);
+        k_attn_rows<128><<<grid, AX_THREADS, sm, strm(st)>>>(qg, kc, vc, g, acc, mz, T, nq, nkv, pos0, card, ncard, lr, cells, n_cells, maxsel);
     }
     if (launch_ok("attn partial")) return 1;
     k_attn_join_runs<<<T, 256, (size_t) nq * ATT_SPLITS * sizeof(float), strm(st)>>>(acc, mz, part, nq, hd);
@@ -435,6 +442,14 @@ int fnx_attn_part_lanes(const float* qg, const uint16_t* kc, const uint16_t* vc,
                         int T, int nq, int nkv, int hd, float* scratch, void* st) {
     FNX_REQUIRE(lr.pos, "attn_part_lanes: no position words");
     return attn_partial_rows(qg, kc, vc, g, part, card, ncard, T, nullptr, lr, nq, nkv, hd, scratch, st);
+}
+
+int fnx_attn_partial_cells(const float* qg, const uint16_t* kc, const uint16_t* vc, FnxKvPages g, FnxLaneRows lr, float* part, int card,
+                           int ncard, int T, const int* pos0, int nq, int nkv, int hd, float* scratch, const int* cells, const int* n_cells,
+                           int maxsel, void* st) {
+    FNX_REQUIRE(lr.pos || pos0, "attn_partial_cells: no positions");
+    FNX_REQUIRE(!cells || (n_cells && maxsel > 0), "attn_partial_cells: a cell list without its counts or width");
+    return attn_partial_rows(qg, kc, vc, g, part, card, ncard, T, pos0, lr, nq, nkv, hd, scratch, st, cells, n_cells, maxsel);
 }
 
 int fnx_attn_finish(const float* parts, int nparts, int first_part, const float* qg, float* out, int T, int nq, int h0, int nh,

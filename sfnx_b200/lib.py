@@ -147,7 +147,14 @@ _SIGS = {
     "fnx_attn_partial": [_p, _p, _p, KvPages, _p, _i, _i, _i, _p, _i, _i, _i, _p, _p],
     "fnx_attn_partial_exact": [_p, _p, _p, KvPages, _p, _i, _i, _i, _p, _i, _i, _i, _p, _p],
     "fnx_attn_part_lanes": [_p, _p, _p, KvPages, LaneRows, _p, _i, _i, _i, _i, _i, _i, _p, _p],
+    "fnx_attn_partial_cells": [_p, _p, _p, KvPages, LaneRows, _p, _i, _i, _i, _p, _i, _i, _i, _p, _p, _p, _i, _p],
     "fnx_attn_finish": [_p, _i, _i, _p, _p, _i, _i, _i, _i, _i, _p],
+    "fnx_qsa_rows": [],
+    "fnx_qsa_maxsel": [_i],
+    "fnx_qsa_proj": [_p, _p, _p, _p, _i, _i, _p],
+    "fnx_qsa_index": [_p, _p, _p, _p, _i, _p, KvPages, _i, _p, _p, _i, _f, Rope, _p],
+    "fnx_qsa_select": [_p, _p, KvPages, LaneRows, _p, _p, _p, _i, _p, _i, _i, _i, _i, _p],
+    "fnx_qsa": [_p, _p, _p, _i, _p, _p, _p, _p, _i, _p, KvPages, _p, _p, _p, _p, _i, _p, _i, _f, Rope, _i, _i, _i, _p],
     "fnx_argmax": [_p, _i, _i, _i, _p, _p, _p, _p, _p],
     "fnx_penalize_row": [_p, _i, _p, _p, _p],
     "fnx_top_tokens": [_p, _i, _i, _i, _p, _p, _p, _i, _p, _p, _p, _p, _p],

@@ -234,3 +234,40 @@ def hc_case(T, n, hc, lr, seed, fold=True, inject=True):
     c["bo"] = rng.standard_normal((T, n)).astype(np.float32) if fold else None
     c["inj_prev"] = rng.standard_normal((T, hc)).astype(np.float32) if fold else None
     return c
+
+
+# ---------------------------------------------------------------- the attention layers' block selection
+def bf16_bits(a):
+    """float array -> bf16 bit patterns (uint16), round to nearest even."""
+    u = np.ascontiguousarray(a, np.float32).view(np.uint32)
+    return ((u + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.uint16)
+
+
+def qsa_case(T, pos0, n=256, top=8, seed=0, ties=False, ring_rows=64):
+    """Indexer weights (bf16), a window of T rows at positions pos0 .. pos0 + T - 1, a ring holding raw keys of earlier
+    positions and the pooled keys of the pos0 / 4 blocks completed before the window.  ties: the blocks' keys are drawn
+    from 20 distinct ones, so that many scores are equal and the rule among equals (the lower block first) decides."""
+    rng = np.random.default_rng(seed)
+    c = {"T": T, "pos0": pos0, "n": n, "top": top, "eps": 1e-6, "rope_base": 1e7}
+    c["wq"] = bf16_bits(0.05 * rng.standard_normal((512, n)))
+    c["wk"] = bf16_bits(0.05 * rng.standard_normal((128, n)))
+    c["x"] = rng.standard_normal((T, n)).astype(np.float32)
+    c["qn"] = (1 + 0.1 * rng.standard_normal(128)).astype(np.float32)
+    c["kn"] = (1 + 0.1 * rng.standard_normal(128)).astype(np.float32)
+    c["ring"] = rng.standard_normal((ring_rows, 128)).astype(np.float16).view(np.uint16)
+    c["max_pools"] = (pos0 + T) // 4 + 8
+    pooled = rng.standard_normal((c["max_pools"], 128)).astype(np.float16)
+    if ties:
+        pooled = pooled[rng.integers(0, 20, c["max_pools"])]
+    pooled[pos0 // 4:] = 0
+    c["pooled"] = pooled.view(np.uint16)
+    return c
+
+
+def qsa_oracle(c, card=0, ncard=1):
+    y = O.qsa_proj(c["wq"], c["wk"], c["x"])
+    ring, pooled = c["ring"].copy(), c["pooled"].copy()
+    q = O.qsa_index(y, c["qn"], c["kn"], ring, pooled, c["pos0"], c["eps"], c["rope_base"], ncard)
+    pos = np.arange(c["pos0"], c["pos0"] + c["T"], dtype=np.int32)
+    scores, cells, n_cells = O.qsa_select(q, pooled, pos, c["top"], c["max_pools"], card, ncard)
+    return {"y": y, "ring": ring, "pooled": pooled, "q": q, "scores": scores, "cells": cells, "n_cells": n_cells}

@@ -1,0 +1,196 @@
+"""GPU parity of the attention layers' block selection (projection, query / raw key / pooled keys, scores, selection) and of
+the scan over a selection's positions, bit for bit against the CPU oracle."""
+import numpy as np
+import pytest
+
+from tests import cases
+
+pytestmark = pytest.mark.gpu
+
+
+def _run(c, card=0, ncard=1, composite=False):
+    from sfnx_b200 import lib as L
+    from tests import gpu_util as G
+
+    T, n, top, mp = c["T"], c["n"], c["top"], c["max_pools"]
+    st = L.stream()
+    lib = L.load()
+    assert lib.fnx_qsa_rows() == 640 and lib.fnx_qsa_maxsel(top) == 4 * top + 3
+    wq, wk, x = G.dev(c["wq"]), G.dev(c["wk"]), G.dev(c["x"])
+    qn, kn, ring, pooled = G.dev(c["qn"]), G.dev(c["kn"]), G.dev(c["ring"]), G.dev(c["pooled"])
+    pos0 = G.dev(np.array([c["pos0"]], np.int32))
+    y, q = G.zeros((T, 640)), G.zeros((T, 4, 128))
+    scores = G.zeros((T, mp))
+    import torch
+
+    cells = torch.full((T, 4 * top + 3), -7, dtype=torch.int32, device=G.DEV)
+    n_cells = torch.full((T,), -7, dtype=torch.int32, device=G.DEV)
+    g, rope = L.KvPages(None, 0, 0, 0, 0), L.Rope(c["rope_base"], 64)
+    if composite:
+        L.call("fnx_qsa", wq.data_ptr(), wk.data_ptr(), x.data_ptr(), n, y.data_ptr(), qn.data_ptr(), kn.data_ptr(), ring.data_ptr(),
+               c["ring"].shape[0], pooled.data_ptr(), g, q.data_ptr(), scores.data_ptr(), cells.data_ptr(), n_cells.data_ptr(), mp,
+               pos0.data_ptr(), T, c["eps"], rope, card, ncard, top, st)
+    else:
+        L.call("fnx_qsa_proj", wq.data_ptr(), wk.data_ptr(), x.data_ptr(), y.data_ptr(), T, n, st)
+        L.call("fnx_qsa_index", y.data_ptr(), qn.data_ptr(), kn.data_ptr(), ring.data_ptr(), c["ring"].shape[0], pooled.data_ptr(), g, ncard,
+               q.data_ptr(), pos0.data_ptr(), T, c["eps"], rope, st)
+        L.call("fnx_qsa_select", q.data_ptr(), pooled.data_ptr(), g, L.LaneRows(None, None), scores.data_ptr(), cells.data_ptr(),
+               n_cells.data_ptr(), mp, pos0.data_ptr(), T, card, ncard, top, st)
+    G.sync()
+    return {"y": G.host(y), "q": G.host(q), "ring": G.host(ring, np.uint16), "pooled": G.host(pooled, np.uint16),
+            "scores": G.host(scores), "cells": G.host(cells), "n_cells": G.host(n_cells)}
+
+
+def _same(got, ref, c):
+    assert np.array_equal(got["y"].view(np.uint32), ref["y"].view(np.uint32)), "projection"
+    assert np.array_equal(got["q"].view(np.uint32), ref["q"].view(np.uint32)), "query heads"
+    assert np.array_equal(got["ring"], ref["ring"]), "raw keys"
+    assert np.array_equal(got["pooled"], ref["pooled"]), "pooled keys"
+    assert np.array_equal(got["n_cells"], ref["n_cells"]), "cell counts"
+    for t in range(c["T"]):
+        nc = ref["n_cells"][t]
+        if nc < 0:
+            continue
+        nv = (c["pos0"] + t + 1) // 4
+        assert np.array_equal(got["scores"][t, :nv].view(np.uint32), ref["scores"][t, :nv].view(np.uint32)), "scores of row %d" % t
+        assert np.array_equal(got["cells"][t, :nc], ref["cells"][t, :nc]), "cells of row %d" % t
+
+
+@pytest.mark.parametrize("T,pos0,n,top,ncard,card,ties", [
+    (16, 37, 256, 8, 1, 0, False),        # every row selects; blocks complete inside the window and from the ring
+    (16, 30, 3072, 8, 2, 1, False),       # the benchmark's width; the first rows see 8 blocks or fewer (dense), the later select
+    (5, 4001, 256, 64, 4, 2, True),       # ties decide; four GPUs' split
+    (16, 20470, 256, 512, 8, 3, False),   # the reference's top of 512 blocks over 5 000: tiles of 1024 scores
+    (1, 2, 256, 8, 1, 0, False),          # nothing to select, no block completed
+])
+def test_qsa_bit_exact(T, pos0, n, top, ncard, card, ties):
+    c = cases.qsa_case(T, pos0, n, top, seed=T + pos0, ties=ties)
+    ref = cases.qsa_oracle(c, card, ncard)
+    if ties:
+        t = c["T"] - 1
+        nv = (pos0 + t + 1) // 4
+        s = np.sort(ref["scores"][t, :nv])[::-1]
+        assert s[top - 1] == s[top], "the case holds no tie at the threshold"
+    _same(_run(c, card, ncard), ref, c)
+    _same(_run(c, card, ncard, composite=True), ref, c)
+
+
+def test_qsa_paged_and_lanes():
+    """Pooled keys behind page tables, two sequences' rows in one window (every row its own position and table): each
+    row's scores and cells are those of its own sequence alone."""
+    import torch
+
+    from sfnx_b200 import lib as L
+    from tests import gpu_util as G
+    from oracle import binding as O
+
+    top, ncard, card, rows_pp = 8, 2, 1, 8           # 8 local rows a page: 2 local blocks x 2 GPUs = 4 blocks a page
+    bpp = rows_pp // 4 * ncard
+    seqs = [cases.qsa_case(8, 61, 256, top, seed=3), cases.qsa_case(8, 122, 256, top, seed=4)]
+    npages = [(-(-s["max_pools"] // bpp)) for s in seqs]
+    rng = np.random.default_rng(9)
+    phys = rng.permutation(sum(npages) + 3).astype(np.int32)
+    page = 5 * 128 * bpp                              # halves a page: room for other layers' slots around the keys
+    pool = np.zeros((len(phys), page), np.uint16)
+    tables, refs, at = [], [], 0
+    for s, np_ in zip(seqs, npages):
+        pt = phys[at:at + np_].copy()
+        at += np_
+        tables.append(pt)
+        ref = cases.qsa_oracle(s, card, ncard)
+        refs.append(ref)
+        padded = np.zeros((np_ * bpp, 128), np.uint16)
+        padded[:s["max_pools"]] = ref["pooled"]     # the keys after the window's own blocks were pooled
+        for lp in range(np_):
+            pool[pt[lp], :bpp * 128] = padded[lp * bpp:(lp + 1) * bpp].reshape(-1)
+    st = L.stream()
+    d_pool = G.dev(pool)
+    d_tabs = [G.dev(t) for t in tables]
+    # window rows: 3 of sequence 0 (its rows 2, 5, 7), 2 of sequence 1 (rows 0, 6)
+    pick = [(0, 2), (0, 5), (0, 7), (1, 0), (1, 6)]
+    T = len(pick)
+    q = np.stack([refs[s]["q"][r] for s, r in pick])
+    pos = [G.dev(np.array([seqs[s]["pos0"] + r], np.int32)) for s, r in pick]
+    d_pos = torch.tensor([p.data_ptr() for p in pos], dtype=torch.int64, device=G.DEV)
+    d_pts = torch.tensor([d_tabs[s].data_ptr() for s, r in pick], dtype=torch.int64, device=G.DEV)
+    mp = max(s["max_pools"] for s in seqs)
+    scores = G.zeros((T, mp))
+    cells = torch.zeros((T, 4 * top + 3), dtype=torch.int32, device=G.DEV)
+    n_cells = torch.zeros((T,), dtype=torch.int32, device=G.DEV)
+    d_q = G.dev(q)
+    g = L.KvPages(None, page, rows_pp, 0, 0)
+    L.call("fnx_qsa_select", d_q.data_ptr(), d_pool.data_ptr(), g, L.LaneRows(d_pos.data_ptr(), d_pts.data_ptr()), scores.data_ptr(),
+           cells.data_ptr(), n_cells.data_ptr(), mp, None, T, card, ncard, top, st)
+    G.sync()
+    got_s, got_c, got_n = G.host(scores), G.host(cells), G.host(n_cells)
+    for i, (s, r) in enumerate(pick):
+        ref = refs[s]
+        nv = (seqs[s]["pos0"] + r + 1) // 4
+        assert got_n[i] == ref["n_cells"][r] and got_n[i] >= 0
+        assert np.array_equal(got_s[i, :nv].view(np.uint32), ref["scores"][r, :nv].view(np.uint32))
+        assert np.array_equal(got_c[i, :got_n[i]], ref["cells"][r, :got_n[i]])
+    # the index step writing pooled keys through a page table: sequence 0's window again, into a zeroed pool
+    s, pt = seqs[0], d_tabs[0]
+    pool2 = torch.zeros_like(d_pool)
+    ring, y = G.dev(s["ring"]), G.dev(refs[0]["y"])
+    qn, kn = G.dev(s["qn"]), G.dev(s["kn"])
+    q2 = G.zeros((8, 4, 128))
+    pos0 = G.dev(np.array([s["pos0"]], np.int32))
+    g2 = L.KvPages(pt.data_ptr(), page, rows_pp, 0, 0)
+    L.call("fnx_qsa_index", y.data_ptr(), qn.data_ptr(), kn.data_ptr(), ring.data_ptr(), s["ring"].shape[0], pool2.data_ptr(), g2, ncard,
+           q2.data_ptr(), pos0.data_ptr(), 8, s["eps"], L.Rope(s["rope_base"], 64), st)
+    G.sync()
+    got = G.host(pool2, np.uint16)
+    for b in range(s["pos0"] // 4, (s["pos0"] + 8) // 4):
+        want = refs[0]["pooled"][b]
+        have = got[tables[0][b // bpp], (b % bpp) * 128:(b % bpp + 1) * 128]
+        assert np.array_equal(have, want), "block %d through the page table" % b
+    assert np.array_equal(G.host(q2).view(np.uint32), refs[0]["q"].view(np.uint32))
+
+
+@pytest.mark.parametrize("hd,q8", [(256, False), (128, False), (256, True)])
+def test_attention_over_selected_cells(hd, q8):
+    """The exact-order scan with a selection: rows with a list attend its rows in its order, rows without every owned
+    position; partials bit for bit against the oracle."""
+    import torch
+
+    from sfnx_b200 import lib as L
+    from tests import gpu_util as G
+    from oracle import binding as O
+
+    T, ctx, ncard, card = 16, 900, 2, 1
+    nq, nkv = (8, 2) if hd == 128 else (24, 4)
+    c = cases.attn_case(T=T, ctx=ctx, nq=nq, nkv=nkv, hd=hd, ncard=ncard, seed=77)
+    if q8:
+        c = cases.attn_case_q8(c)
+    rng = np.random.default_rng(5)
+    maxsel = 4 * 40 + 3
+    cells = np.zeros((T, maxsel), np.int32)
+    n_cells = np.full(T, -1, np.int32)
+    for t in range(T):
+        if t % 3 == 1:
+            continue                                   # a dense row
+        owned = O.kv_owned(ctx + t, card, ncard)
+        blocks = np.sort(rng.choice(owned // 4, size=min(40, owned // 4) - (t % 2), replace=False))
+        sel = (blocks[:, None] * 4 + np.arange(4)).reshape(-1)
+        tail = np.arange(owned // 4 * 4, owned)
+        row = np.concatenate([sel, tail]).astype(np.int32)
+        cells[t, :len(row)], n_cells[t] = row, len(row)
+    q8_rows = c.get("q8_rows", 0)
+    qg, k = c["qg"].copy(), c["k"].copy()
+    kc, vc = c["kc"][card].copy(), c["vc"][card].copy()
+    O.attn_prep_append(qg, k, c["v"], c["qn"], c["kn"], kc, vc, card, ncard, c["pos0"], c["eps"], c["rope_base"], nq, nkv, hd, q8_rows=q8_rows)
+    want = O.attn_partial_cells(qg, kc, vc, card, ncard, c["pos0"], nq, nkv, cells, n_cells, hd, q8_rows=q8_rows)
+    dense = O.attn_partial(qg, kc, vc, card, ncard, c["pos0"], nq, nkv, hd, q8_rows=q8_rows)
+    assert np.array_equal(want[1].view(np.uint32), dense[1].view(np.uint32)) and not np.array_equal(want[0], dense[0])
+    st = L.stream()
+    d_qg, d_kc, d_vc = G.dev(qg), G.dev(kc), G.dev(vc)
+    d_cells, d_n = G.dev(cells), G.dev(n_cells)
+    pos0 = G.dev(np.array([c["pos0"]], np.int32))
+    part = G.zeros((T, nq, hd + 2))
+    scratch = G.zeros(L.load().fnx_attn_scratch_floats(nq, hd, T))
+    g = L.KvPages(None, 0, 0, q8_rows, 1 if q8 else 0)
+    L.call("fnx_attn_partial_cells", d_qg.data_ptr(), d_kc.data_ptr(), d_vc.data_ptr(), g, L.LaneRows(None, None), part.data_ptr(), card, ncard,
+           T, pos0.data_ptr(), nq, nkv, hd, scratch.data_ptr(), d_cells.data_ptr(), d_n.data_ptr(), maxsel, st)
+    G.sync()
+    assert np.array_equal(G.host(part).view(np.uint32), want.view(np.uint32))

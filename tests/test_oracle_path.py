@@ -340,3 +340,44 @@ def test_hyper_connections_against_float64(oracle):
     wi = (c["w_inj"].astype(np.uint32) << 16).view(np.float32).astype(np.float64)
     inj = np.einsum("jcn,tcn,tc->tj", wi.reshape(hc, hc, n), xs.reshape(T, hc, n), rs)
     assert np.allclose(inject, inj, rtol=1e-4, atol=1e-4)
+
+
+def test_block_selection_against_float64(oracle):
+    """The indexer's restatement against plain float64 numpy: projection, normed query heads, pooled keys and scores to
+    rounding; the selection as the `top` highest scores, this GPU's blocks of them ascending, then the row's tail; a scan over
+    a list naming every owned position equals the scan without a list."""
+    from tests import cases
+
+    O = oracle
+    T, pos0, top, ncard = 16, 201, 8, 2
+    c = cases.qsa_case(T, pos0, 256, top, seed=11)
+    r = [cases.qsa_oracle(c, card, ncard) for card in range(ncard)]
+    bf = lambda w: (w.astype(np.uint32) << 16).view(np.float32).astype(np.float64)
+    y64 = c["x"].astype(np.float64) @ np.concatenate([bf(c["wq"]), bf(c["wk"])]).T
+    assert np.allclose(r[0]["y"], y64, rtol=1e-4, atol=1e-4)
+    q = r[0]["q"].astype(np.float64)
+    want_norm = np.sqrt((c["qn"].astype(np.float64) ** 2 * (y64[:, :512].reshape(T, 4, 128) ** 2)
+                         / (y64[:, :512].reshape(T, 4, 128) ** 2).mean(-1, keepdims=True)).sum(-1))
+    assert np.allclose(np.linalg.norm(q, axis=-1), want_norm, rtol=1e-4)      # the rotation keeps the normed head's length
+    pooled = r[0]["pooled"].view(np.float16).astype(np.float64)
+    for t in range(T):
+        p = pos0 + t
+        nv, tail = (p + 1) // 4, (p + 1) % 4
+        s64 = np.maximum(q[t] @ pooled[:nv].T, 0).sum(0) / np.sqrt(128.0)
+        assert np.allclose(r[0]["scores"][t, :nv], s64, rtol=1e-4, atol=1e-4)
+        sel = np.sort(np.argsort(-r[0]["scores"][t, :nv], kind="stable")[:top])   # stable: the lower block among equals
+        for card in range(ncard):
+            mine = sel[sel % ncard == card]
+            cells = ((mine // ncard)[:, None] * 4 + np.arange(4)).reshape(-1)
+            if (p // 4) % ncard == card:
+                cells = np.concatenate([cells, (p // 4 // ncard) * 4 + np.arange(tail)])
+            assert r[card]["n_cells"][t] == len(cells) and np.array_equal(r[card]["cells"][t, :len(cells)], cells)
+    dense = cases.qsa_oracle(cases.qsa_case(4, 9, 256, top, seed=2))
+    assert (dense["n_cells"] == -1).all()
+    a = cases.attn_case(T=4, ctx=300, nq=8, nkv=2, hd=128, ncard=2, seed=3)
+    ref = cases.attn_oracle(a)
+    own = [O.kv_owned(300 + t, 1, 2) for t in range(4)]
+    cells = np.zeros((4, max(own)), np.int32)
+    cells[:] = np.arange(max(own))
+    part = O.attn_partial_cells(ref["qg"], ref["kc"][1], ref["vc"][1], 1, 2, 300, 8, 2, cells, np.array(own, np.int32), 128)
+    assert np.array_equal(part.view(np.uint32), ref["part"][1].view(np.uint32))
