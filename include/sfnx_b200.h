@@ -406,6 +406,9 @@ typedef struct FnxStackCfg {
     float eps, rope_base;
     int hc, hc_lr; /* residual streams (0 or 1: one stream, plain residual + RMS norm) and the hyper-connections' low rank */
     int r_preset;  /* hc > 1: the streams are in place before stage 0 (fnx_draft_begin made them), not expanded from x */
+    /* the attention layers' block selection (0: none): blocks a row keeps, rows of a layer's raw-key ring, blocks a layer's
+     * pooled keys hold.  With a selection the attention runs the exact-order scan over each row's cells */
+    int qsa_top, qsa_ring_rows, qsa_max_pools;
 } FnxStackCfg;
 
 /* one hyper-connection read's weights (reference LayerW hc_norm / hc_down / hc_up / hc_inj, src/model.hpp:120-124):
@@ -415,6 +418,14 @@ typedef struct FnxHcW {
     FnxQ8S down, up;
     const uint16_t* inj;
 } FnxHcW;
+
+/* an attention layer's indexer (reference LayerW idx_wq / idx_wk / idx_qn / idx_kn, src/engine.cu:911-912) with the
+ * sequence's raw-key ring and pooled keys of that layer; wq null: the layer selects nothing */
+typedef struct FnxQsaW {
+    const uint16_t *wq, *wk; /* bf16 [512][n], [128][n] */
+    const float *qn, *kn;    /* [128] each */
+    uint16_t *ring, *pooled; /* f16 [qsa_ring_rows][128], [qsa_max_pools][128] (or paged as the layer's K/V pages say) */
+} FnxQsaW;
 
 typedef struct FnxLayer {
     int kind; /* 0: Gated DeltaNet, 1: attention */
@@ -443,6 +454,7 @@ typedef struct FnxLayer {
     float* gdn_log;
     /* with cfg.hc > 1: the reads before the mixer half [0] and before the FFN half [1] (norm1 / norm2 are then unused) */
     FnxHcW hcw[2];
+    FnxQsaW idx;
 } FnxLayer;
 
 typedef struct FnxHead {

@@ -86,7 +86,7 @@ struct Traced {
 // the workspace's buffers, as offsets from its base
 struct Ws {
     size_t x, bo, xn, xq, qkvz, ab, yq, qg, k, v, att, partials, att_scratch, rlogits, topi, topw, jobs_gu, jobs_dn, njobs, rscratch, gu,
-        hq, part, sh_gu, shq, sh, logits, keys, best_v, best_i, err, ctl, gdn_scratch, copy_jobs, replay_jobs, hc_R, hc_inj, hc_scratch, dr_en, dr_e2, dr_h2, dr_q, total;
+        hq, part, sh_gu, shq, sh, logits, keys, best_v, best_i, err, ctl, gdn_scratch, copy_jobs, replay_jobs, hc_R, hc_inj, hc_scratch, dr_en, dr_e2, dr_h2, dr_q, qsa_y, qsa_q, qsa_scores, qsa_cells, qsa_ncells, total;
 };
 
 static Ws carve(const FnxStackCfg& c) {
@@ -144,6 +144,12 @@ static Ws carve(const FnxStackCfg& c) {
     w.dr_e2 = take(dr ? T * n * 4 : 0);
     w.dr_h2 = take(T * dr * n * 4);
     w.dr_q = take(T * dr * (n / 32) * 36);
+    const size_t qs = c.qsa_top > 0 ? 1 : 0;   // the block selection: projection, query heads, scores, cells and their counts
+    w.qsa_y = take(qs * T * fnx_qsa_rows() * 4);
+    w.qsa_q = take(qs * T * FNX_QSA_HEADS * FNX_QSA_DIM * 4);
+    w.qsa_scores = take(qs * T * (size_t) (c.qsa_max_pools > 0 ? c.qsa_max_pools : 0) * 4);
+    w.qsa_cells = take(qs * T * (size_t) fnx_qsa_maxsel(c.qsa_top > 0 ? c.qsa_top : 0) * 4);
+    w.qsa_ncells = take(qs * T * 4);
     w.total = o;
     return w;
 }
@@ -155,6 +161,8 @@ static int check_cfg(const FnxStackCfg* c) {
     if (c->topk < 1 || c->topk > 16 || c->nq % c->ncard) return fail("window: top-%d, %d query heads over %d GPUs", c->topk, c->nq, c->ncard);
     if (c->hc > 1 && (c->hc > 8 || c->hc_lr < 32 || c->hc_lr % 32 || c->hc_lr > 512))
         return fail("window: %d residual streams with low rank %d (up to 8 streams, rank a multiple of 32 up to 512)", c->hc, c->hc_lr);
+    if (c->qsa_top > 0 && (c->qsa_ring_rows < FNX_MAXT + FNX_QSA_POOL || c->qsa_max_pools < 1))
+        return fail("window: block selection with a ring of %d rows and %d pooled keys", c->qsa_ring_rows, c->qsa_max_pools);
     return 0;
 }
 
@@ -343,7 +351,9 @@ static int window_stage(const FnxStackCfg* cfg, const FnxLayer* layers, const Fn
         float* qg = (float*) (b + w.qg);
         float* k = (float*) (b + w.k);
         float* v = (float*) (b + w.v);
-        TRK(begin_name, begin_half(L.norm1, nullptr));
+        const bool select = c.qsa_top > 0 && L.idx.wq;
+        FNX_REQUIRE(!select || !lanes, "window: the block selection is not wired for windows of several sequences");
+        TRK(begin_name, begin_half(L.norm1, select ? xn : nullptr));
         {   // q, k and v in one launch
             const FnxQ8S ws[3] = {L.wq, L.wk, L.wv};
             const int rows3[3] = {c.nq * c.hd * 2, c.nkv * c.hd, c.nkv * c.hd};
@@ -369,6 +379,17 @@ static int window_stage(const FnxStackCfg* cfg, const FnxLayer* layers, const Fn
         }
         TRK("attn_prep_append", fnx_attn_prep_append(qg, k, v, L.q_norm, L.k_norm, L.kc, L.vc, L.pages, c.card, c.ncard, T, ctl, c.eps,
                                                         rope, c.nq, c.nkv, c.hd, st));
+        if (select) {   // the indexer on the half's input (reference src/engine.cu:911-912), then the scan over every row's cells
+            int* cells = (int*) (b + w.qsa_cells);
+            int* n_cells = (int*) (b + w.qsa_ncells);
+            TRK("qsa", fnx_qsa(L.idx.wq, L.idx.wk, xn, c.n, (float*) (b + w.qsa_y), L.idx.qn, L.idx.kn, L.idx.ring, c.qsa_ring_rows, L.idx.pooled,
+                               L.pages, (float*) (b + w.qsa_q), (float*) (b + w.qsa_scores), cells, n_cells, c.qsa_max_pools, ctl, T, c.eps,
+                               FnxRope{c.rope_base, 64},
+                               c.card, c.ncard, c.qsa_top, st));
+            TRK("attn_partial", fnx_attn_partial_cells(qg, L.kc, L.vc, L.pages, FnxLaneRows{nullptr, nullptr}, mine, c.card, c.ncard, T, ctl, c.nq,
+                                                          c.nkv, c.hd, (float*) (b + w.att_scratch), cells, n_cells, fnx_qsa_maxsel(c.qsa_top), st));
+            return 0;
+        }
         // FNX_ATTN_EXACT=1: the scan in the reference's order of sums (bit-reproducible against the CPU statement, several
         // times slower); default: the one-pass tensor-core scan
         if (env_on("FNX_EXACT") || env_on("FNX_ATTN_EXACT"))

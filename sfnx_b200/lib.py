@@ -52,11 +52,16 @@ class Rope(C.Structure):
 class StackCfg(C.Structure):
     _fields_ = [(k, C.c_int) for k in ("n", "nexp", "topk", "ff", "nk", "nv", "nq", "nkv", "hd", "nrot", "vocab0", "vocab_rows",
                                         "nlayers", "ncard", "card")] + [("eps", C.c_float), ("rope_base", C.c_float), ("hc", C.c_int),
-                                                                        ("hc_lr", C.c_int), ("r_preset", C.c_int)]
+                                                                        ("hc_lr", C.c_int), ("r_preset", C.c_int), ("qsa_top", C.c_int),
+                                                                        ("qsa_ring_rows", C.c_int), ("qsa_max_pools", C.c_int)]
 
 
 class HcW(C.Structure):
     _fields_ = [("norm", C.c_void_p), ("down", Q8S), ("up", Q8S), ("inj", C.c_void_p)]
+
+
+class QsaW(C.Structure):
+    _fields_ = [(k, C.c_void_p) for k in ("wq", "wk", "qn", "kn", "ring", "pooled")]
 
 
 class Layer(C.Structure):
@@ -67,7 +72,7 @@ class Layer(C.Structure):
                 ("wq", Q8S), ("wk", Q8S), ("wv", Q8S), ("wo", Q8S), ("q_norm", C.c_void_p), ("k_norm", C.c_void_p),
                 ("kc", C.c_void_p), ("vc", C.c_void_p), ("pages", KvPages),
                 ("router", C.c_void_p), ("gate_up", Experts), ("down", Experts), ("sh_gate_up", Q8S), ("sh_down", Q8S), ("gdn_log", C.c_void_p),
-                ("hcw", HcW * 2)]
+                ("hcw", HcW * 2), ("idx", QsaW)]
 
 
 class WindowLanes(C.Structure):

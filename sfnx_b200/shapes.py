@@ -26,4 +26,5 @@ class StackShape:
     hc: int = 1            # residual streams: 1 = plain residual + RMS norm; > 1 = hyper-connections (reads mix the streams)
     hc_lr: int = 320       # the hyper-connections' low rank
     draft: bool = False    # the stack is a draft (MTP) layer: its streams come from a window's rows and the next tokens' embeddings
+    qsa_top: int = 0       # blocks of 4 positions an attention row keeps (the reference: 512); 0: no block selection, every position attended
     kv_q8: bool = False    # K/V rows as int8 in groups of 32 with f16 scales (the reference's kv_q8) instead of f16

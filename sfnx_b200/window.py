@@ -44,7 +44,8 @@ class SyntheticStack:
         self.v0, self.vrows = vocab_slice(s.vocab, ncard, card)
         self.kv_rows = lib.fnx_kv_rows_per_card(s.ctx + s.kv_slack, ncard)
         self.cfg = L.StackCfg(s.n, s.nexp, s.topk, self.ffs, self.nk, self.nv, s.nq, s.nkv, s.hd, s.nrot, self.v0, self.vrows,
-                              len(s.kinds), ncard, card, s.eps, s.rope_base, s.hc if s.hc > 1 else 0, s.hc_lr, 1 if s.draft else 0)
+                              len(s.kinds), ncard, card, s.eps, s.rope_base, s.hc if s.hc > 1 else 0, s.hc_lr, 1 if s.draft else 0,
+                              s.qsa_top, 2048 if s.qsa_top else 0, (s.ctx + s.kv_slack) // 4 + 1 if s.qsa_top else 0)
         self.layers = (L.Layer * len(s.kinds))()
         self.gdn_state = []   # (S, hist) of the DeltaNet layers, for snapshots
         for l, kind in enumerate(s.kinds):
@@ -199,6 +200,15 @@ class SyntheticStack:
             Lr.kc, Lr.vc = kc.data_ptr(), vc.data_ptr()
             self.named[(l, "kc")], self.named[(l, "vc")] = kc, vc
             Lr.pages = L.KvPages(None, 0, 0, self.kv_rows, 1 if s.kv_q8 else 0)
+            if s.qsa_top:   # the indexer (replicated on every GPU), the raw keys of the last positions and the pooled keys of the context
+                bf16 = lambda t: self._t(((t.view(torch.int32) + 0x7FFF + ((t.view(torch.int32) >> 16) & 1)) >> 16).to(torch.int16))
+                iw = {"idx_wq": bf16(self._normal(l, "idx_wq", (512, s.n), 0.05)), "idx_wk": bf16(self._normal(l, "idx_wk", (128, s.n), 0.05)),
+                      "idx_qn": self._t(1 + 0.1 * self._normal(l, "idx_qn", (128,), 1.0)), "idx_kn": self._t(1 + 0.1 * self._normal(l, "idx_kn", (128,), 1.0)),
+                      "idx_ring": self._t(self._normal(l, "idx_ring", (self.cfg.qsa_ring_rows, 128), 1.0).half().view(torch.int16)),
+                      "idx_pooled": self._t(self._normal(l, "idx_pooled", (self.cfg.qsa_max_pools, 128), 1.0).half().view(torch.int16))}
+                for key, v in iw.items():
+                    self.named[(l, key)] = v
+                Lr.idx = L.QsaW(*(iw[k].data_ptr() for k in ("idx_wq", "idx_wk", "idx_qn", "idx_kn", "idx_ring", "idx_pooled")))
         # FFN
         self.named[(l, "router")] = self._t(self._normal(l, "router", (s.nexp + 1, s.n), s.sigma))
         Lr.router = self.named[(l, "router")].data_ptr()

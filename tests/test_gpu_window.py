@@ -41,8 +41,9 @@ class OracleStack:
     def __init__(self, stack):
         self.s, self.h = stack.shape, _host(stack)
         self.nk, self.nv, self.ffs, self.kv_rows = stack.nk, stack.nv, stack.ffs, stack.kv_rows
-        self.state = {k: v.copy() for k, v in self.h.items() if k[1] in ("S", "hist", "kc", "vc")}
+        self.state = {k: v.copy() for k, v in self.h.items() if k[1] in ("S", "hist", "kc", "vc", "idx_ring", "idx_pooled")}
         self.last = None
+        self.selected = 0   # rows that attended a selection instead of every position
 
     def window(self, ids, pos0, tag):
         s, h = self.s, self.h
@@ -100,7 +101,15 @@ class OracleStack:
                 hd1 = np.ones(s.hd, np.float32)
                 q8_rows = self.kv_rows if s.kv_q8 else 0
                 O.attn_prep_append(qg, k, v, hd1, hd1, kc, vc, 0, 1, pos0, s.eps, s.rope_base, s.nq, s.nkv, s.hd, s.nrot, q8_rows=q8_rows)
-                part = O.attn_partial(qg, kc, vc, 0, 1, pos0, s.nq, s.nkv, s.hd, q8_rows=q8_rows)
+                if s.qsa_top:   # the indexer on the half's input, then the scan over every row's selected cells
+                    ring, pooled = self.state[(l, "idx_ring")].view(np.uint16), self.state[(l, "idx_pooled")].view(np.uint16)
+                    y = O.qsa_proj(h[(l, "idx_wq")].view(np.uint16), h[(l, "idx_wk")].view(np.uint16), np.ascontiguousarray(xn))
+                    iq = O.qsa_index(y, h[(l, "idx_qn")], h[(l, "idx_kn")], ring, pooled, pos0, s.eps, s.rope_base)
+                    _, cells, n_cells = O.qsa_select(iq, pooled, np.arange(pos0, pos0 + T), s.qsa_top, pooled.shape[0])
+                    self.selected = self.selected + int((n_cells >= 0).sum())
+                    part = O.attn_partial_cells(qg, kc, vc, 0, 1, pos0, s.nq, s.nkv, cells, n_cells, s.hd, q8_rows=q8_rows)
+                else:
+                    part = O.attn_partial(qg, kc, vc, 0, 1, pos0, s.nq, s.nkv, s.hd, q8_rows=q8_rows)
                 att = O.attn_merge([part], qg, s.nq, s.hd)
                 bo = O.q8s_gemv(*_q8s(h, (l, "wo")), O.quantize_q8_1(att.reshape(T, -1)), T)
             pending = bo
@@ -127,11 +136,11 @@ class OracleStack:
             O.gdn_rollback(self.state[(l, "S")], self.state[(l, "hist")], snap, hsnap, np.array([0, tag], np.int32), self.nk, self.nv, T, n)
 
 
-def _make(kinds, seed, experts="q4k", kv_q8=False, hc=1, draft=False):
+def _make(kinds, seed, experts="q4k", kv_q8=False, hc=1, draft=False, qsa_top=0):
     from sfnx_b200.window import StackShape, SyntheticStack, WindowRunner
 
     shape = StackShape(n=512, nexp=32, topk=4, ff=256, nkh=2, nvh=4, nq=4, nkv=2, hd=128, nrot=64, vocab=2048, kinds=kinds, ctx=300,
-                       kv_slack=256, experts=experts, kv_q8=kv_q8, hc=hc, hc_lr=64, draft=draft)
+                       kv_slack=256, experts=experts, kv_q8=kv_q8, hc=hc, hc_lr=64, draft=draft, qsa_top=qsa_top)
     stack = SyntheticStack(shape, seed=seed, device="cuda:0")
     return shape, stack, WindowRunner(stack, 16, graph=True), OracleStack(stack)
 
@@ -259,6 +268,16 @@ def test_window_int8_kv_bit_exact():
     shape, stack, runner, orc = _make([0, 1, 0, 1], seed=9, kv_q8=True)
     _, total = _run_windows(shape, stack, runner, orc, nwin=3, seed=4, exact=True)
     assert 3 <= total <= 48
+
+
+@pytest.mark.parametrize("kv_q8", [False, True])
+def test_window_block_selection_bit_exact(kv_q8):
+    """Attention layers with the indexer (8 of the context's 75 blocks kept): raw keys, pooled blocks, scores, the
+    selection and the scan over each row's cells inside whole windows, through rollbacks that re-run rejected positions
+    (their ring rows and pooled blocks are written again before any row reads them), bit for bit."""
+    shape, stack, runner, orc = _make([0, 1, 0, 1], seed=21, kv_q8=kv_q8, qsa_top=8)
+    _, total = _run_windows(shape, stack, runner, orc, nwin=4, seed=5, exact=True)
+    assert 4 <= total <= 64 and orc.selected >= 4 * 2 * 16   # every row of every attention layer attended a selection
 
 
 def test_window_mixed_stack_exact_attention_bit_exact(monkeypatch):
