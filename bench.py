@@ -59,6 +59,8 @@ def parse():
     ap.add_argument("--vocab", type=int, default=151936, help="vocabulary (151936 = the benchmark configurations)")
     ap.add_argument("--expert-type", default="", choices=["", "q4k", "q8_0"], help="override the configuration's expert format")
     ap.add_argument("--hc", type=int, default=1, help="residual streams: > 1 runs the stack with hyper-connections (a read before every half)")
+    ap.add_argument("--qsa-top", type=int, default=0, help="blocks of 4 positions an attention row keeps (the reference: 512); 0 = every position "
+                    "attended, the benchmark configurations' attention")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="enqueue every window call by call instead of replaying a CUDA graph")
     ap.add_argument("--no-parity", action="store_true", help="N > 1: skip the comparison with the unsplit model")
@@ -155,7 +157,8 @@ def algorithmic_bytes(shape, ctx):
     return {"moe_gate_up": gu, "moe_down": dn, "router": (shape.nexp + 1) * n * 4, "shared": q8(2 * ff, n) + q8(n, ff),
             "gdn_core": 17 * state, "qkvz": q8((2 * shape.nkh + 2 * shape.nvh) * 128, n), "ssm_out": q8(n, shape.nvh * 128),
             "wq": q8(shape.nq * shape.hd * 2, n), "wkv": 2 * q8(shape.nkv * shape.hd, n), "wo": q8(n, shape.nq * shape.hd),
-            "attn_kv": ctx * shape.nkv * shape.hd * 2 * 2, "head": q8(shape.vocab, n) + T * shape.vocab * 4,
+            "attn_kv": (min(ctx, T * (4 * shape.qsa_top + 3)) if shape.qsa_top else ctx) * shape.nkv * shape.hd * 2 * 2,
+            "qsa": (640 * n * 2 + ctx // 4 * 128 * 2) if shape.qsa_top else 0, "head": q8(shape.vocab, n) + T * shape.vocab * 4,
             "ab": 2 * shape.nvh * n * 4, "rows": T * n * 4,
             "hc_read": (2 * q8(shape.hc_lr, shape.hc * n) + shape.hc * shape.hc * n * 2 + 2 * T * shape.hc * n * 4) if shape.hc > 1 else 0}
 
@@ -166,7 +169,7 @@ def window_bytes(shape, ctx, d_exp, world):
     kinds = shape.kinds
     split = (len(kinds) * (d_exp * (b["moe_gate_up"] + b["moe_down"]) + b["shared"]) + kinds.count(0) * (b["qkvz"] + b["ssm_out"] + b["gdn_core"]) +
              kinds.count(1) * (b["wo"] + b["attn_kv"]) + b["head"])
-    repl = len(kinds) * b["router"] + kinds.count(0) * b["ab"] + kinds.count(1) * (b["wq"] + b["wkv"]) + (2 * len(kinds) + 1) * b["hc_read"]
+    repl = len(kinds) * b["router"] + kinds.count(0) * b["ab"] + kinds.count(1) * (b["wq"] + b["wkv"] + b["qsa"]) + (2 * len(kinds) + 1) * b["hc_read"]
     return split / world + repl if world > 1 else split + repl
 
 
@@ -189,7 +192,9 @@ def workload_config(wl, shape, world):
                   "(126 MB of L2)" % (resident / 1e9, window / 1e9),
             "parallelism": "tp%d (FF blocks / value heads / KV positions / vocabulary)" % world,
             **({"hyper_connections": "%d residual streams, low rank %d: a read before every half and the head" % (shape.hc, shape.hc_lr)}
-               if shape.hc > 1 else {})}
+               if shape.hc > 1 else {}),
+            **({"block_selection": "every attention row keeps the %d best-scored blocks of 4 positions and its tail; the scan runs in the "
+                "exact order over each row's cells" % shape.qsa_top} if shape.qsa_top else {})}
 
 
 _REAL_STDOUT = None
@@ -233,7 +238,8 @@ def main():
     kinds, nseq, sampled = wl["kinds"], wl["nseq"], wl["sampled"]
     repeats = args.repeats or (max(1, min(10, math.ceil(200 / max(1, args.steps)))) if wl["name"] == "cfg2" else 1)
     nsteps = args.warmup + args.steps * repeats
-    shape = StackShape(kinds=kinds, ctx=wl["ctx"], kv_slack=(nsteps + 2) * T, nexp=args.experts, vocab=args.vocab, experts=wl["experts"], hc=args.hc)
+    shape = StackShape(kinds=kinds, ctx=wl["ctx"], kv_slack=(nsteps + 2) * T, nexp=args.experts, vocab=args.vocab, experts=wl["experts"], hc=args.hc,
+                       qsa_top=args.qsa_top)
     t_build = time.time()
     stack = SyntheticStack(shape, ncard=world, card=rank, seed=args.seed, device="cuda:%d" % local)
     seqs = [stack] + [stack.sequence_view(i) for i in range(1, nseq)]
@@ -474,7 +480,7 @@ def main():
         else:
             result["parity"] = None if args.no_parity else {"unavailable": "the unsplit model does not fit one GPU"}
     assert err_dev == 0, "device error word %d after the timed replay" % err_dev
-    if rank == 0 and world == 1 and not args.no_cpu_baseline and not sampled:
+    if rank == 0 and world == 1 and not args.no_cpu_baseline and not sampled and not args.qsa_top:   # (the CPU arm attends every position)
         import bench_reference
 
         result["cpu_baseline"] = bench_reference.cpu_baseline(wl, shape, accepted_per_step)

@@ -116,21 +116,25 @@ __global__ void k_attn_prep_append(float* qg, float* k, const float* v, const fl
 //   softmax: the pair's 32 weights sit across the lanes of one warp, as the reference's trees want them
 //   values : thread = head dimension, one accumulator per pair in registers, the chunk's 32 V values of that
 //            dimension in registers too
+// PT is how many (row, head) pairs a block applies a chunk to at a time: 96 for the groups of rows that attend every owned
+// position, 8 or 16 (a pair or two a warp, more blocks an SM) for a row with a list of its own, which shares its chunks
+// with no other row.
 // scratch: acc [T][nq][16][hd], then (m, z) [T][nq][16].
 struct AttPart {
     float m, z;
 };
 constexpr int AX_THREADS = 256, AX_WARPS = AX_THREADS / 32, AX_PT = 96, AX_PPW = AX_PT / AX_WARPS;
 
-template <int HD>
-__global__ void __launch_bounds__(AX_THREADS, 1) k_attn_rows(const float* __restrict__ qg, const uint16_t* __restrict__ kc,
+template <int HD, int PT>
+__global__ void __launch_bounds__(AX_THREADS, PT <= 16 ? 2 : 1) k_attn_rows(const float* __restrict__ qg, const uint16_t* __restrict__ kc,
                                                            const uint16_t* __restrict__ vc, FnxKvPages g, float* __restrict__ acc_out,
                                                            AttPart* __restrict__ mz_out, int T, int nq, int nkv,
                                                            const int* __restrict__ pos0p, int card, int ncard, FnxLaneRows lr,
-                                                           const int* __restrict__ cells, const int* __restrict__ n_cells, int maxsel) {
-    constexpr int G = AX_THREADS / HD, APT = AX_PT / G, KLD = HD + 4;   // thread groups over the pairs; accumulators a thread
+                                                           const int* __restrict__ cells, const int* __restrict__ n_cells, int maxsel, int which) {
+    constexpr int G = AX_THREADS / HD, APT = PT / G, PPW = PT / AX_WARPS, KLD = HD + 4;   // thread groups over the pairs; accumulators a thread
     const int s = blockIdx.x, kvl = blockIdx.y, lead = blockIdx.z, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int qpk = nq / nkv;
+    if (which && (cells && n_cells[lead] >= 0) != (which == 2)) return;   // this launch takes the other kind of rows
     __shared__ int ctx_s[FNX_MAXT], len_s[FNX_MAXT], rows_s[FNX_MAXT], list_s[FNX_MAXT], nr_s;
     __shared__ const int* pt_s[FNX_MAXT];
     if (tid < T) {
@@ -151,7 +155,8 @@ __global__ void __launch_bounds__(AX_THREADS, 1) k_attn_rows(const float* __rest
             if (t < lead) first = false;
             else rows_s[nr++] = t;
         }
-        nr_s = first ? nr : 0;
+        // which: 0 every group; 1 only rows that attend every owned position; 2 only rows with a list of their own
+        nr_s = first && !(which == 1 && list_s[lead]) && !(which == 2 && !list_s[lead]) ? nr : 0;
     }
     __syncthreads();
     const int nr = nr_s;
@@ -162,26 +167,26 @@ __global__ void __launch_bounds__(AX_THREADS, 1) k_attn_rows(const float* __rest
     int pend = 0;          // where the group's longest row ends inside this run
     for (int r = 0; r < nr; ++r) pend = max(pend, min(ctx_s[rows_s[r]], p0 + len));
     extern __shared__ __align__(16) float ax_sm[];
-    float* q_s = ax_sm;                          // [AX_PT][HD]
-    float* k_s = q_s + (size_t) AX_PT * HD;      // [32][HD + 4]
+    float* q_s = ax_sm;                          // [PT][HD]
+    float* k_s = q_s + (size_t) PT * HD;      // [32][HD + 4]
     float* v_s = k_s + (size_t) ATT_CH * KLD;    // [32][HD]
-    float* w_s = v_s + (size_t) ATT_CH * HD;     // [AX_PT][32]
-    float* sc_s = w_s + (size_t) AX_PT * ATT_CH; // [AX_PT]
-    int* np_s = reinterpret_cast<int*>(sc_s + AX_PT);   // [AX_PT]: positions of the chunk the pair takes (0: none)
+    float* w_s = v_s + (size_t) ATT_CH * HD;     // [PT][32]
+    float* sc_s = w_s + (size_t) PT * ATT_CH; // [PT]
+    int* np_s = reinterpret_cast<int*>(sc_s + PT);   // [PT]: positions of the chunk the pair takes (0: none)
     const float rs = ex_rsqrt((float) HD);
     const int grp = tid / HD, d = tid % HD;
     const int npairs = nr * qpk;
 #pragma unroll 1
-    for (int pb = 0; pb < npairs; pb += AX_PT) {
-        const int npt = min(AX_PT, npairs - pb);
+    for (int pb = 0; pb < npairs; pb += PT) {
+        const int npt = min(PT, npairs - pb);
         __syncthreads();
         for (int e = tid; e < npt * (HD / 4); e += AX_THREADS) {
             const int pi = e / (HD / 4), c4 = e % (HD / 4), t = rows_s[(pb + pi) / qpk], h = kvl * qpk + (pb + pi) % qpk;
             reinterpret_cast<float4*>(q_s + (size_t) pi * HD)[c4] = reinterpret_cast<const float4*>(qg + ((size_t) t * nq + h) * 2 * HD)[c4];
         }
-        float m[AX_PPW], z[AX_PPW];
+        float m[PPW], z[PPW];
 #pragma unroll
-        for (int i = 0; i < AX_PPW; ++i) m[i] = -INFINITY, z[i] = 0.f;
+        for (int i = 0; i < PPW; ++i) m[i] = -INFINITY, z[i] = 0.f;
         float acc[APT];
 #pragma unroll
         for (int i = 0; i < APT; ++i) acc[i] = 0.f;
@@ -231,15 +236,15 @@ __global__ void __launch_bounds__(AX_THREADS, 1) k_attn_rows(const float* __rest
             }
             __syncthreads();
             // ---- scores: this lane's position against the warp's pairs, each a fused chain over the head dimension
-            float sa[AX_PPW];
+            float sa[PPW];
 #pragma unroll
-            for (int i = 0; i < AX_PPW; ++i) sa[i] = 0.f;
+            for (int i = 0; i < PPW; ++i) sa[i] = 0.f;
             const float4* k4 = reinterpret_cast<const float4*>(k_s + (size_t) lane * KLD);
 #pragma unroll 2
             for (int c4 = 0; c4 < HD / 4; ++c4) {
                 const float4 kk = k4[c4];
 #pragma unroll
-                for (int i = 0; i < AX_PPW; ++i) {
+                for (int i = 0; i < PPW; ++i) {
                     const float4 qq = reinterpret_cast<const float4*>(q_s + (size_t) (warp + AX_WARPS * i) * HD)[c4];
                     sa[i] = ffma(qq.x, kk.x, sa[i]);
                     sa[i] = ffma(qq.y, kk.y, sa[i]);
@@ -249,7 +254,7 @@ __global__ void __launch_bounds__(AX_THREADS, 1) k_attn_rows(const float* __rest
             }
             // ---- the online-softmax step of every pair of the warp (all lanes hold the pair's m and z)
 #pragma unroll
-            for (int i = 0; i < AX_PPW; ++i) {
+            for (int i = 0; i < PPW; ++i) {
                 const int pi = warp + AX_WARPS * i;
                 if (pi < npt) {
                     const int t = rows_s[(pb + pi) / qpk];
@@ -307,7 +312,7 @@ __global__ void __launch_bounds__(AX_THREADS, 1) k_attn_rows(const float* __rest
             }
         }
 #pragma unroll
-        for (int i = 0; i < AX_PPW; ++i) {
+        for (int i = 0; i < PPW; ++i) {
             const int pi = warp + AX_WARPS * i;
             if (pi < npt && lane == 0) {
                 const int t = rows_s[(pb + pi) / qpk], h = kvl * qpk + (pb + pi) % qpk;
@@ -419,14 +424,21 @@ static int attn_partial_rows(const float* qg, const uint16_t* kc, const uint16_t
     FNX_REQUIRE(!g.q8 || lr.pt || g.pt || g.cap > 0, "attn: an int8 cache without a page table needs its row count (cap)");
     float* acc = scratch;
     AttPart* mz = (AttPart*) (scratch + (size_t) T * nq * ATT_SPLITS * hd);
-    const size_t sm = ((size_t) AX_PT * hd + (size_t) ATT_CH * (hd + 4) + (size_t) ATT_CH * hd + (size_t) AX_PT * ATT_CH + 2 * AX_PT) * sizeof(float);
     const dim3 grid(ATT_SPLITS, nkv, T);   // block z = t works only when row t leads a group of rows
+    auto run = [&](auto kern, int pt, int which) -> int {
+        const size_t sm = ((size_t) pt * hd + (size_t) ATT_CH * (hd + 4) + (size_t) ATT_CH * hd + (size_t) pt * ATT_CH + 2 * pt) * sizeof(float);
+        if (smem_optin(kern, sm, "attn partial")) return 1;
+        kern<<<grid, AX_THREADS, sm, strm(st)>>>(qg, kc, vc, g, acc, mz, T, nq, nkv, pos0, card, ncard, lr, cells, n_cells, maxsel, which);
+        return 0;
+    };
+    // rows with a list of their own go in a launch of their own with few pairs a block; the others in groups of up to 96
+    const bool small = nq / nkv <= 8;
     if (hd == 256) {
-        if (smem_optin(k_attn_rows<256>, sm, "attn partial")) return 1;
-        k_attn_rows<256><<<grid, AX_THREADS, sm, strm(st)>>>(qg, kc, vc, g, acc, mz, T, nq, nkv, pos0, card, ncard, lr, cells, n_cells, maxsel);
+        if (run(k_attn_rows<256, AX_PT>, AX_PT, cells ? 1 : 0)) return 1;
+        if (cells && (small ? run(k_attn_rows<256, 8>, 8, 2) : run(k_attn_rows<256, 16>, 16, 2))) return 1;
     } else {
-        if (smem_optin(k_attn_rows<128>, sm, "attn partial")) return 1;
-        k_attn_rows<128><<<grid, AX_THREADS, sm, strm(st)>>>(qg, kc, vc, g, acc, mz, T, nq, nkv, pos0, card, ncard, lr, cells, n_cells, maxsel);
+        if (run(k_attn_rows<128, AX_PT>, AX_PT, cells ? 1 : 0)) return 1;
+        if (cells && (small ? run(k_attn_rows<128, 8>, 8, 2) : run(k_attn_rows<128, 16>, 16, 2))) return 1;
     }
     if (launch_ok("attn partial")) return 1;
     k_attn_join_runs<<<T, 256, (size_t) nq * ATT_SPLITS * sizeof(float), strm(st)>>>(acc, mz, part, nq, hd);

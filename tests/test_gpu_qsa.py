@@ -194,3 +194,76 @@ def test_attention_over_selected_cells(hd, q8):
            T, pos0.data_ptr(), nq, nkv, hd, scratch.data_ptr(), d_cells.data_ptr(), d_n.data_ptr(), maxsel, st)
     G.sync()
     assert np.array_equal(G.host(part).view(np.uint32), want.view(np.uint32))
+
+
+def test_qsa_timings():
+    """Device times of the three steps at the benchmark's width (16 rows, hidden 3072, 512 blocks kept) over 32 768 and
+    262 144 positions, and of the scan over the selected cells; printed, and loosely bounded."""
+    import torch
+
+    from sfnx_b200 import lib as L
+    from tests import gpu_util as G
+
+    T, n, top = 16, 3072, 512
+    st = L.stream()
+    rng = np.random.default_rng(0)
+    wq, wk = G.dev(cases.bf16_bits(0.05 * rng.standard_normal((512, n)))), G.dev(cases.bf16_bits(0.05 * rng.standard_normal((128, n))))
+    x = G.dev(rng.standard_normal((T, n)).astype(np.float32))
+    qn = kn = G.dev(np.ones(128, np.float32))
+    ring = G.dev(rng.standard_normal((2048, 128)).astype(np.float16).view(np.uint16))
+    y, q = G.zeros((T, 640)), G.zeros((T, 4, 128))
+    cells = torch.zeros((T, 4 * top + 3), dtype=torch.int32, device=G.DEV)
+    n_cells = torch.zeros((T,), dtype=torch.int32, device=G.DEV)
+    g, rope, lr = L.KvPages(None, 0, 0, 0, 0), L.Rope(1e7, 64), L.LaneRows(None, None)
+    out = []
+    for ctx in (32768, 262144):
+        mp = ctx // 4 + 8
+        pooled = torch.randn((mp, 128), device=G.DEV).half().view(torch.int16)
+        scores = G.zeros((T, mp))
+        pos0 = G.dev(np.array([ctx], np.int32))
+        steps = {"proj": lambda: L.call("fnx_qsa_proj", wq.data_ptr(), wk.data_ptr(), x.data_ptr(), y.data_ptr(), T, n, st),
+                 "index": lambda: L.call("fnx_qsa_index", y.data_ptr(), qn.data_ptr(), kn.data_ptr(), ring.data_ptr(), 2048, pooled.data_ptr(), g, 1,
+                                         q.data_ptr(), pos0.data_ptr(), T, 1e-6, rope, st),
+                 "scores + selection": lambda: L.call("fnx_qsa_select", q.data_ptr(), pooled.data_ptr(), g, lr, scores.data_ptr(), cells.data_ptr(),
+                                                      n_cells.data_ptr(), mp, pos0.data_ptr(), T, 0, 1, top, st)}
+        for name, fn in steps.items():
+            for _ in range(3):
+                fn()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(20):
+                fn()
+            e1.record()
+            G.sync()
+            us = e0.elapsed_time(e1) * 1000 / 20
+            out.append("%s at %d positions: %.1f us" % (name, ctx, us))
+            assert us < 50000
+        assert int(n_cells.min()) >= 4 * top
+    # the scan over 16 rows' selections (2 048 + tail positions a row) at head dimension 256, 24 / 4 heads
+    nq, nkv, hd, rows = 24, 4, 256, 32768 + 64
+    kc = torch.randn((rows, nkv, hd), device=G.DEV).half().view(torch.int16)
+    vc = torch.randn((rows, nkv, hd), device=G.DEV).half().view(torch.int16)
+    qg = torch.randn((T, nq, 2 * hd), device=G.DEV)
+    part = G.zeros((T, nq, hd + 2))
+    scratch = G.zeros(L.load().fnx_attn_scratch_floats(nq, hd, T))
+    pos0 = G.dev(np.array([32768], np.int32))
+
+    def scan():
+        L.call("fnx_attn_partial_cells", qg.data_ptr(), kc.data_ptr(), vc.data_ptr(), g, lr, part.data_ptr(), 0, 1, T, pos0.data_ptr(), nq, nkv, hd,
+               scratch.data_ptr(), cells.data_ptr(), n_cells.data_ptr(), 4 * top + 3, st)
+
+    mp = 32768 // 4 + 8   # cells of the 32 768-position case again
+    pooled = torch.randn((mp, 128), device=G.DEV).half().view(torch.int16)
+    scores = G.zeros((T, mp))
+    L.call("fnx_qsa_select", q.data_ptr(), pooled.data_ptr(), g, lr, scores.data_ptr(), cells.data_ptr(), n_cells.data_ptr(), mp, pos0.data_ptr(), T, 0,
+           1, top, st)
+    for _ in range(3):
+        scan()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(10):
+        scan()
+    e1.record()
+    G.sync()
+    out.append("exact-order scan over the selected cells (16 rows x 2 051 positions): %.1f us" % (e0.elapsed_time(e1) * 1000 / 10))
+    print("\nblock selection: " + "; ".join(out))
