@@ -10,6 +10,7 @@
 #include "common.cuh"
 #include "exact_math.cuh"
 #include "moe_internal.cuh"
+#include "umma.cuh"
 
 namespace fnxk {
 
@@ -322,19 +323,186 @@ __global__ void __launch_bounds__(AX_THREADS, PT <= 16 ? 2 : 1) k_attn_rows(cons
     }
 }
 
-// the 16 runs of every (row t, head) as one partial: part[(t nq + h) (hd + 2)] = acc[hd], m, z.  Block = row t; a warp
-// per head first turns the runs' maxima into weights exp(m_s - max) (a run without positions is left out), z added in
+// ---------------------------------------------------------------- a row with a list of its own (the block selection's cells)
+// The same sums in the same order as k_attn_rows, laid out for a row that shares its positions with no other row: a block
+// takes (run s, KV head, row t) and up to `nch` chunks of 32 positions at a time.
+//   K rows   gathered into shared memory as f16 by one bulk (TMA) copy a position, rows padded by 16 bytes so that every
+//            lane reads its own row without bank conflicts;
+//   scores   warp c takes chunk c, lane = position: one fused chain over the head dimension per (position, head), the KV
+//            head's query heads side by side in registers (QM slots), so a lane runs up to QM independent chains;
+//   softmax  the chunks' maxima are exchanged through shared memory; warp c then knows the running maximum before its
+//            chunk (maxima are exact in any order) and makes its chunk's weights, their warp-tree sum and the rescale
+//            factor; z is chained over the chunks in order by one thread per head;
+//   values   thread = head dimension: per chunk in order, acc = acc * rescale, then + w v in ascending position, the 32
+//            V values of the dimension read straight from the cache (f16) into registers.
+// f16 caches only (an int8 cache's listed rows go through k_attn_rows).
+template <int HD, int QM>
+__global__ void __launch_bounds__(AX_THREADS) k_attn_cells(const float* __restrict__ qg, const uint16_t* __restrict__ kc, const uint16_t* __restrict__ vc,
+                                                          FnxKvPages g, float* __restrict__ acc_out, AttPart* __restrict__ mz_out, int nq, int nkv,
+                                                          FnxLaneRows lr, const int* __restrict__ cells, const int* __restrict__ n_cells, int maxsel,
+                                                          int nch, unsigned* fault) {
+    constexpr int KLD = HD + 8;   // halves a staged K row takes
+    const int s = blockIdx.x, kvl = blockIdx.y, t = blockIdx.z, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int ctx = n_cells[t];
+    if (ctx < 0) return;   // the row attends every owned position: k_attn_rows' launch takes it
+    const int qpk = nq / nkv;
+    if (lr.pt) g.pt = lr.pt[t];
+    const int* list = cells + (size_t) t * maxsel;
+    const int len = ((ctx + ATT_SPLITS - 1) / ATT_SPLITS + ATT_CH - 1) / ATT_CH * ATT_CH, p0 = s * len, p1 = min(ctx, p0 + len);
+    extern __shared__ __align__(16) unsigned char ac_sm[];
+    float* q_s = reinterpret_cast<float*>(ac_sm);                                  // [qpk][HD]
+    uint16_t* k_s = reinterpret_cast<uint16_t*>(q_s + (size_t) qpk * HD);          // [nch 32][KLD]
+    size_t* row_s = reinterpret_cast<size_t*>(k_s + (size_t) nch * ATT_CH * KLD);  // [nch 32] the positions' rows in the cache (halves)
+    float* w_s = reinterpret_cast<float*>(row_s + nch * ATT_CH);                   // [nch][qpk][32]
+    float* cm_s = w_s + (size_t) nch * qpk * ATT_CH;                               // [nch][qpk] chunk maxima
+    float* sc_s = cm_s + nch * qpk;                                                // [nch][qpk] rescale factors
+    float* sum_s = sc_s + nch * qpk;                                               // [nch][qpk] sums of weights
+    float* m_s = sum_s + nch * qpk;                                                // [qpk] running maximum before the group
+    float* z_s = m_s + qpk;                                                        // [qpk]
+    for (int e = tid; e < qpk * (HD / 4); e += AX_THREADS) {
+        const int pi = e / (HD / 4), c4 = e % (HD / 4);
+        reinterpret_cast<float4*>(q_s + (size_t) pi * HD)[c4] = reinterpret_cast<const float4*>(qg + ((size_t) t * nq + kvl * qpk + pi) * 2 * HD)[c4];
+    }
+    if (tid < qpk) m_s[tid] = -INFINITY, z_s[tid] = 0.f;
+    __shared__ __align__(8) unsigned long long kbar;
+    if (tid == 0) {
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(um_s32(&kbar)) : "memory");
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    unsigned kphase = 0;
+    float acc[QM];
+#pragma unroll
+    for (int i = 0; i < QM; ++i) acc[i] = 0.f;
+    const float rs = ex_rsqrt((float) HD);
+#pragma unroll 1
+    for (int g0 = p0; g0 < p1; g0 += nch * ATT_CH) {
+        const int ng = min(nch * ATT_CH, p1 - g0), nck = (ng + ATT_CH - 1) / ATT_CH;
+        __syncthreads();   // the group before has been used up (and q_s, m_s, z_s are written)
+        // one bulk copy a position: its K row (HD halves) into the padded row of k_s, all of the group's in flight at once,
+        // counted as bytes on the block's mbarrier (a bounded wait: on a timeout the fault word is set and the block goes on)
+        if (tid == 0) um_expect_tx(&kbar, (unsigned) ng * HD * 2);
+        __syncthreads();
+        for (int i = tid; i < ng; i += AX_THREADS) {
+            const size_t r = kv_row_at(g, list[g0 + i], nkv, HD) + (size_t) kvl * HD;
+            row_s[i] = r;
+            um_bulk(um_s32(k_s + (size_t) i * KLD), kc + r, HD * 2, &kbar);
+        }
+        um_wait(&kbar, kphase, fault);
+        kphase ^= 1u;
+        __syncthreads();   // (row_s is complete for the values)
+        // ---- scores of chunk `warp`
+        float sv[QM];
+        const int at = warp * ATT_CH + lane;
+        const bool have = warp < nck, valid = have && at < ng;
+        if (have) {
+            float sa[QM];
+#pragma unroll
+            for (int i = 0; i < QM; ++i) sa[i] = 0.f;
+            if (valid) {
+                const uint4* kr = reinterpret_cast<const uint4*>(k_s + (size_t) at * KLD);
+#pragma unroll 2
+                for (int c8 = 0; c8 < HD / 8; ++c8) {
+                    const uint4 u = kr[c8];
+                    const unsigned kw[4] = {u.x, u.y, u.z, u.w};
+                    float kf[8];
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) kf[2 * k] = h2f((uint16_t) (kw[k] & 0xffff)), kf[2 * k + 1] = h2f((uint16_t) (kw[k] >> 16));
+#pragma unroll
+                    for (int i = 0; i < QM; ++i)
+                        if (i < qpk) {
+                            const float4 qa = reinterpret_cast<const float4*>(q_s + (size_t) i * HD)[2 * c8];
+                            const float4 qb = reinterpret_cast<const float4*>(q_s + (size_t) i * HD)[2 * c8 + 1];
+                            float a = sa[i];
+                            a = ffma(qa.x, kf[0], a), a = ffma(qa.y, kf[1], a), a = ffma(qa.z, kf[2], a), a = ffma(qa.w, kf[3], a);
+                            a = ffma(qb.x, kf[4], a), a = ffma(qb.y, kf[5], a), a = ffma(qb.z, kf[6], a), a = ffma(qb.w, kf[7], a);
+                            sa[i] = a;
+                        }
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < QM; ++i)
+                if (i < qpk) {
+                    sv[i] = valid ? fmul(sa[i], rs) : -INFINITY;
+                    const float cm = wmax(sv[i]);
+                    if (lane == 0) cm_s[warp * qpk + i] = cm;
+                }
+        }
+        __syncthreads();
+        // ---- the chunk's weights against the running maximum before it
+        if (have) {
+#pragma unroll
+            for (int i = 0; i < QM; ++i)
+                if (i < qpk) {
+                    float mb = m_s[i];
+                    for (int c = 0; c < warp; ++c) mb = fmaxf(mb, cm_s[c * qpk + i]);
+                    const float mn = fmaxf(mb, cm_s[warp * qpk + i]);
+                    const float w = sv[i] == -INFINITY ? 0.f : ex_expf(fsub(sv[i], mn));
+                    const float sc = mb == -INFINITY ? 0.f : ex_expf(fsub(mb, mn));
+                    const float ws = wsum(w);
+                    w_s[((size_t) warp * qpk + i) * ATT_CH + lane] = w;
+                    if (lane == 0) sc_s[warp * qpk + i] = sc, sum_s[warp * qpk + i] = ws;
+                }
+        }
+        __syncthreads();
+        if (tid < qpk) {   // z and the maximum, chained over the group's chunks in order
+            float z = z_s[tid], m = m_s[tid];
+            for (int c = 0; c < nck; ++c) z = ffma(z, sc_s[c * qpk + tid], sum_s[c * qpk + tid]), m = fmaxf(m, cm_s[c * qpk + tid]);
+            z_s[tid] = z, m_s[tid] = m;   // read again only after the next group's first barriers
+        }
+        // ---- values
+        if (tid < HD) {
+            auto use = [&](const float* vv, int c) {
+                const int np = min(ATT_CH, ng - c * ATT_CH);
+#pragma unroll
+                for (int i = 0; i < QM; ++i)
+                    if (i < qpk) {
+                        float a = fmul(acc[i], sc_s[c * qpk + i]);
+                        const float4* w4 = reinterpret_cast<const float4*>(w_s + ((size_t) c * qpk + i) * ATT_CH);
+#pragma unroll
+                        for (int p4 = 0; p4 < ATT_CH / 4; ++p4) {
+                            const float4 ww = w4[p4];
+                            if (4 * p4 < np) a = ffma(ww.x, vv[4 * p4], a);
+                            if (4 * p4 + 1 < np) a = ffma(ww.y, vv[4 * p4 + 1], a);
+                            if (4 * p4 + 2 < np) a = ffma(ww.z, vv[4 * p4 + 2], a);
+                            if (4 * p4 + 3 < np) a = ffma(ww.w, vv[4 * p4 + 3], a);
+                        }
+                        acc[i] = a;
+                    }
+            };
+#pragma unroll 1
+            for (int c = 0; c < nck; ++c) {
+                // the chunk's 32 V values of this dimension, asked for together: every load is unconditional (a chunk's missing
+                // positions read its last one again; their weights are never used)
+                const int np = min(ATT_CH, ng - c * ATT_CH);
+                float vv[ATT_CH];
+#pragma unroll
+                for (int pp = 0; pp < ATT_CH; ++pp) vv[pp] = h2f(__ldg(vc + row_s[c * ATT_CH + min(pp, np - 1)] + tid));
+                use(vv, c);
+            }
+        }
+    }
+    __syncthreads();
+    if (tid < HD) {
+#pragma unroll
+        for (int i = 0; i < QM; ++i)
+            if (i < qpk) acc_out[(((size_t) t * nq + kvl * qpk + i) * ATT_SPLITS + s) * HD + tid] = acc[i];
+    }
+    if (tid < qpk) mz_out[((size_t) t * nq + kvl * qpk + tid) * ATT_SPLITS + s] = AttPart{m_s[tid], z_s[tid]};
+}
+
+// the 16 runs of every (row t, head) as one partial: part[(t nq + h) (hd + 2)] = acc[hd], m, z.  Block = (row t, head); its
+// first warp turns the runs' maxima into weights exp(m_s - max) (a run without positions is left out), z added in
 // run order by one lane; then every thread adds its elements' 16 weighted accumulators in run order.
 __global__ void __launch_bounds__(256) k_attn_join_runs(const float* __restrict__ acc_in, const AttPart* __restrict__ mz_in,
                                                         float* __restrict__ part, int nq, int hd) {
-    extern __shared__ float jw[];   // [nq][16] weights, negative where the run is left out
-    const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    for (int h = warp; h < nq; h += 8) {
-        const size_t base = ((size_t) t * nq + h) * ATT_SPLITS;
+    __shared__ float jw[ATT_SPLITS];   // the runs' weights, negative where the run is left out
+    const int t = blockIdx.x, h = blockIdx.y, tid = threadIdx.x, lane = tid & 31;
+    const size_t base = ((size_t) t * nq + h) * ATT_SPLITS;
+    if (tid < 32) {
         const AttPart p = lane < ATT_SPLITS ? mz_in[base + lane] : AttPart{-INFINITY, 0.f};
         const float mx = wmax(p.m);
         const float w = p.m == -INFINITY ? -1.f : ex_expf(fsub(p.m, mx));
-        if (lane < ATT_SPLITS) jw[h * ATT_SPLITS + lane] = w;
+        if (lane < ATT_SPLITS) jw[lane] = w;
         float zs = 0.f;
         for (int r = 0; r < ATT_SPLITS; ++r) {
             const float wr = __shfl_sync(0xffffffffu, w, r), zr = __shfl_sync(0xffffffffu, p.z, r);
@@ -346,15 +514,14 @@ __global__ void __launch_bounds__(256) k_attn_join_runs(const float* __restrict_
         }
     }
     __syncthreads();
-    for (int e = tid; e < nq * hd; e += 256) {
-        const int h = e / hd, i = e % hd;
-        const float* a = acc_in + ((size_t) t * nq + h) * ATT_SPLITS * hd + i;
+    for (int i = tid; i < hd; i += 256) {
+        const float* a = acc_in + base * hd + i;
         float v[ATT_SPLITS], acc = 0.f;
 #pragma unroll
         for (int r = 0; r < ATT_SPLITS; ++r) v[r] = a[(size_t) r * hd];
 #pragma unroll
         for (int r = 0; r < ATT_SPLITS; ++r) {
-            const float w = jw[h * ATT_SPLITS + r];
+            const float w = jw[r];
             if (w >= 0.f) acc = ffma(w, v[r], acc);
         }
         part[((size_t) t * nq + h) * (hd + 2) + i] = acc;
@@ -431,17 +598,30 @@ static int attn_partial_rows(const float* qg, const uint16_t* kc, const uint16_t
         kern<<<grid, AX_THREADS, sm, strm(st)>>>(qg, kc, vc, g, acc, mz, T, nq, nkv, pos0, card, ncard, lr, cells, n_cells, maxsel, which);
         return 0;
     };
-    // rows with a list of their own go in a launch of their own with few pairs a block; the others in groups of up to 96
+    auto listed = [&](auto kern) -> int {   // rows with a list over an f16 cache: as many chunks a group as the longest run has, 8 at most
+        const int qpk = nq / nkv, len_max = ((maxsel + ATT_SPLITS - 1) / ATT_SPLITS + ATT_CH - 1) / ATT_CH * ATT_CH;
+        const int nch = len_max / ATT_CH < AX_WARPS ? len_max / ATT_CH : AX_WARPS;
+        const size_t sm = (size_t) qpk * hd * 4 + (size_t) nch * ATT_CH * (hd + 8) * 2 + (size_t) nch * qpk * ATT_CH * 4 + (size_t) 3 * nch * qpk * 4 +
+                          (size_t) (2 * qpk + 2) * 4 + (size_t) nch * ATT_CH * sizeof(size_t) + 16;
+        if (smem_optin(kern, sm, "attn cells")) return 1;
+        unsigned* fault = device_fault_word();
+        if (!fault) return fail("attn cells: no fault word");
+        kern<<<grid, AX_THREADS, sm, strm(st)>>>(qg, kc, vc, g, acc, mz, nq, nkv, lr, cells, n_cells, maxsel, nch, fault);
+        return 0;
+    };
+    // rows with a list of their own go in a launch of their own; the others in groups of up to 96 pairs
     const bool small = nq / nkv <= 8;
     if (hd == 256) {
         if (run(k_attn_rows<256, AX_PT>, AX_PT, cells ? 1 : 0)) return 1;
-        if (cells && (small ? run(k_attn_rows<256, 8>, 8, 2) : run(k_attn_rows<256, 16>, 16, 2))) return 1;
+        if (cells && g.q8 && (small ? run(k_attn_rows<256, 8>, 8, 2) : run(k_attn_rows<256, 16>, 16, 2))) return 1;
+        if (cells && !g.q8 && (small ? listed(k_attn_cells<256, 8>) : listed(k_attn_cells<256, 16>))) return 1;
     } else {
         if (run(k_attn_rows<128, AX_PT>, AX_PT, cells ? 1 : 0)) return 1;
-        if (cells && (small ? run(k_attn_rows<128, 8>, 8, 2) : run(k_attn_rows<128, 16>, 16, 2))) return 1;
+        if (cells && g.q8 && (small ? run(k_attn_rows<128, 8>, 8, 2) : run(k_attn_rows<128, 16>, 16, 2))) return 1;
+        if (cells && !g.q8 && (small ? listed(k_attn_cells<128, 8>) : listed(k_attn_cells<128, 16>))) return 1;
     }
     if (launch_ok("attn partial")) return 1;
-    k_attn_join_runs<<<T, 256, (size_t) nq * ATT_SPLITS * sizeof(float), strm(st)>>>(acc, mz, part, nq, hd);
+    k_attn_join_runs<<<dim3(T, nq), 256, 0, strm(st)>>>(acc, mz, part, nq, hd);
     return launch_ok("attn join");
 }
 
