@@ -424,7 +424,9 @@ typedef struct FnxHcW {
 typedef struct FnxQsaW {
     const uint16_t *wq, *wk; /* bf16 [512][n], [128][n] */
     const float *qn, *kn;    /* [128] each */
-    uint16_t *ring, *pooled; /* f16 [qsa_ring_rows][128], [qsa_max_pools][128] (or paged as the layer's K/V pages say) */
+    uint16_t *ring, *pooled; /* f16 [qsa_ring_rows][128], [qsa_max_pools][128] (or paged by the layer's page tables) */
+    size_t page;             /* paged: halves a page of the pooled keys' pool takes (0: the K/V pages' own pitch, the keys
+                              * lying inside the K/V pages as in the reference's pool) */
 } FnxQsaW;
 
 typedef struct FnxLayer {
@@ -511,7 +513,10 @@ int fnx_window_ring(const FnxRing* ring);
  * s rows .. s rows + rows - 1.  Everything shared (norms, projections, router, experts, head) runs over all rows as in a
  * window of one sequence; the DeltaNet core chains each lane's rows through that lane's state (fnx_gdn_core_segs), the K/V
  * rows are appended lane by lane and every row's attention partial is taken on its lane's position and pages
- * (fnx_attn_part_lanes, the reference's order of sums).  Each lane's results are those of a window of its rows alone.
+ * (fnx_attn_part_lanes, the reference's order of sums).  With block selection (cfg.qsa_top > 0) the projection runs over
+ * all rows, every lane's rows are indexed on that lane's ring and pages, and the scores, the selection and the scan over
+ * the cells take every row on its lane's position and pages (reference src/engine.cu:1186-1200).  Each lane's results are
+ * those of a window of its rows alone.
  * The layers' S / hist fields are not used; kc / vc are the layer's paged pool. */
 typedef struct FnxWindowLanes {
     int nseg, rows;
@@ -525,6 +530,8 @@ typedef struct FnxWindowLanes {
     float* const* const* hist;  /* host [nlayers]: device array [nseg] of the lanes' conv histories */
     float* const* const* S_host;    /* host [nlayers] of host arrays [nseg]: the same pointers, for the commit */
     float* const* const* hist_host;
+    uint16_t* const* const* idx_ring_host; /* host [nlayers] of host arrays [nseg]: the lanes' raw-key rings of the attention
+                                            * layers with an indexer (null without block selection) */
 } FnxWindowLanes;
 int fnx_window_stage_lanes(const FnxStackCfg* cfg, const FnxLayer* layers, const FnxHead* head, void* ws, const FnxWindowLanes* lanes, int stage,
                            void* st);

@@ -352,7 +352,8 @@ static int window_stage(const FnxStackCfg* cfg, const FnxLayer* layers, const Fn
         float* k = (float*) (b + w.k);
         float* v = (float*) (b + w.v);
         const bool select = c.qsa_top > 0 && L.idx.wq;
-        FNX_REQUIRE(!select || !lanes, "window: the block selection is not wired for windows of several sequences");
+        FNX_REQUIRE(!select || !lanes || (lanes->idx_ring_host && lanes->idx_ring_host[sg.layer]), "window: layer %d selects blocks but the lanes bring no raw-key rings",
+                    sg.layer);
         TRK(begin_name, begin_half(L.norm1, select ? xn : nullptr));
         {   // q, k and v in one launch
             const FnxQ8S ws[3] = {L.wq, L.wk, L.wv};
@@ -373,8 +374,30 @@ static int window_stage(const FnxStackCfg* cfg, const FnxLayer* layers, const Fn
                                                                 L.kc, L.vc, pg, c.card, c.ncard, lanes->rows, lanes->ctl_host[sI], c.eps, rope, c.nq,
                                                                 c.nkv, c.hd, st));
             }
-            TRK("attn_partial", fnx_attn_part_lanes(qg, L.kc, L.vc, L.pages, FnxLaneRows{lanes->row_pos, lanes->row_pt}, mine, c.card, c.ncard, T,
-                                                       c.nq, c.nkv, c.hd, (float*) (b + w.att_scratch), st));
+            const FnxLaneRows lr{lanes->row_pos, lanes->row_pt};
+            if (select) {   // the projection over all rows, every lane's rows indexed on its ring and pages, then every row on its lane's
+                float* y = (float*) (b + w.qsa_y);
+                float* iq = (float*) (b + w.qsa_q);
+                int* cells = (int*) (b + w.qsa_cells);
+                int* n_cells = (int*) (b + w.qsa_ncells);
+                FnxKvPages kp = L.pages;   // the pooled keys' pages: the lanes' page tables over the keys' own pool
+                if (L.idx.page) kp.page = L.idx.page;
+                TRK("qsa", fnx_qsa_proj(L.idx.wq, L.idx.wk, xn, y, T, c.n, st));
+                for (int sI = 0; sI < lanes->nseg; ++sI) {
+                    const size_t r0 = (size_t) sI * lanes->rows;
+                    FnxKvPages pg = kp;
+                    pg.pt = lanes->pt_host[sI];
+                    TRK("qsa", fnx_qsa_index(y + r0 * fnx_qsa_rows(), L.idx.qn, L.idx.kn, lanes->idx_ring_host[sg.layer][sI], c.qsa_ring_rows, L.idx.pooled, pg,
+                                             c.ncard, iq + r0 * FNX_QSA_HEADS * FNX_QSA_DIM, lanes->ctl_host[sI], lanes->rows, c.eps, FnxRope{c.rope_base, 64}, st));
+                }
+                TRK("qsa", fnx_qsa_select(iq, L.idx.pooled, kp, lr, (float*) (b + w.qsa_scores), cells, n_cells, c.qsa_max_pools, nullptr, T, c.card,
+                                          c.ncard, c.qsa_top, st));
+                TRK("attn_partial", fnx_attn_partial_cells(qg, L.kc, L.vc, L.pages, lr, mine, c.card, c.ncard, T, nullptr, c.nq, c.nkv, c.hd,
+                                                              (float*) (b + w.att_scratch), cells, n_cells, fnx_qsa_maxsel(c.qsa_top), st));
+                return 0;
+            }
+            TRK("attn_partial", fnx_attn_part_lanes(qg, L.kc, L.vc, L.pages, lr, mine, c.card, c.ncard, T, c.nq, c.nkv, c.hd,
+                                                       (float*) (b + w.att_scratch), st));
             return 0;
         }
         TRK("attn_prep_append", fnx_attn_prep_append(qg, k, v, L.q_norm, L.k_norm, L.kc, L.vc, L.pages, c.card, c.ncard, T, ctl, c.eps,

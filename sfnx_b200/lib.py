@@ -61,7 +61,7 @@ class HcW(C.Structure):
 
 
 class QsaW(C.Structure):
-    _fields_ = [(k, C.c_void_p) for k in ("wq", "wk", "qn", "kn", "ring", "pooled")]
+    _fields_ = [(k, C.c_void_p) for k in ("wq", "wk", "qn", "kn", "ring", "pooled")] + [("page", C.c_size_t)]
 
 
 class Layer(C.Structure):
@@ -78,7 +78,7 @@ class Layer(C.Structure):
 class WindowLanes(C.Structure):
     _fields_ = [("nseg", C.c_int), ("rows", C.c_int), ("ctl", C.c_void_p), ("row0", C.c_void_p), ("row_pos", C.c_void_p), ("row_pt", C.c_void_p),
                 ("ctl_host", C.c_void_p), ("pt_host", C.c_void_p), ("S", C.c_void_p), ("hist", C.c_void_p), ("S_host", C.c_void_p),
-                ("hist_host", C.c_void_p)]
+                ("hist_host", C.c_void_p), ("idx_ring_host", C.c_void_p)]
 
 
 class Draft(C.Structure):

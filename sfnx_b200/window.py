@@ -361,6 +361,16 @@ class LaneSet:
             S_dev[l], h_dev[l] = ptr_dev(self.S[l]).data_ptr(), ptr_dev(self.hist[l]).data_ptr()
             S_host[l] = C.addressof(ptr_host([t.data_ptr() for t in self.S[l]]))
             h_host[l] = C.addressof(ptr_host([t.data_ptr() for t in self.hist[l]]))
+        # block selection: every lane's raw-key rings (one an attention layer); its pooled keys are its pages of the layer's pool
+        self.rings, ring_host = {}, [None] * nl
+        if s.qsa_top:
+            for l, kind in enumerate(s.kinds):
+                if kind != 1:
+                    continue
+                r0 = stack.named[(l, "idx_ring")]
+                self.rings[l] = [self._k(torch.roll(r0, 7 * i, 0).contiguous()) for i in range(nseg)]   # the lanes' histories differ
+                ring_host[l] = C.addressof(ptr_host([t.data_ptr() for t in self.rings[l]]))
+        self.bpp = rpp // 4 * stack.ncard   # blocks of 4 positions a page holds (every GPU's)
         ppl = self.region // rpp   # pages per lane
         self.pt = [self._k(torch.arange(i * ppl, (i + 1) * ppl, dtype=torch.int32, device=dev)) for i in range(nseg)]
         self.ctl = self._k(torch.zeros((nseg, 2), dtype=torch.int32, device=dev))
@@ -375,7 +385,9 @@ class LaneSet:
             self._k(torch.tensor([self.row_pos[t:t + 1].data_ptr() for t in range(T)], dtype=torch.int64, device=dev)).data_ptr(),
             self._k(torch.tensor([self.pt[t // rows].data_ptr() for t in range(T)], dtype=torch.int64, device=dev)).data_ptr(),
             C.addressof(ptr_host(ctl_ptrs)), C.addressof(ptr_host([t.data_ptr() for t in self.pt])),
-            C.addressof(ptr_host(S_dev)), C.addressof(ptr_host(h_dev)), C.addressof(ptr_host(S_host)), C.addressof(ptr_host(h_host)))
+            C.addressof(ptr_host(S_dev)), C.addressof(ptr_host(h_dev)), C.addressof(ptr_host(S_host)), C.addressof(ptr_host(h_host)),
+            C.addressof(ptr_host(ring_host)) if s.qsa_top else None)
+        assert not s.qsa_top or nseg * ppl * self.bpp <= stack.cfg.qsa_max_pools, "the pooled keys' pool is too small for the lanes' pages"
         # the attention layers' pools as pages of rpp local rows (a lane's table is filled in per call)
         self.paged = L.KvPages(None, rpp * s.nkv * s.hd, rpp, 0)
 
@@ -388,6 +400,7 @@ class LaneSet:
         for l, kind in enumerate(self.stack.shape.kinds):
             if kind == 1:
                 self.stack.layers[l].pages = self.paged if on else L.KvPages(None, 0, 0, self.stack.kv_rows)
+                self.stack.layers[l].idx.page = self.bpp * 128 if on else 0   # the pooled keys' pool in pages of bpp keys
 
     def positions(self, pos, tags):
         """Lane i's window starts at position pos[i] with tag tags[i] (host lists)."""

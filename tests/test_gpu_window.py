@@ -337,11 +337,13 @@ def test_window_sampled_acceptance_matches_oracle():
     assert 4 <= total <= 64
 
 
-def test_window_of_several_sequences_equals_each_alone(monkeypatch):
+@pytest.mark.parametrize("qsa_top", [0, 4])
+def test_window_of_several_sequences_equals_each_alone(monkeypatch, qsa_top):
     """The reference's batch property (tools/batch_check.hpp: "batched lanes = alone"): three sequences x four rows in one
     window of 12 rows give, bit for bit, the logits, DeltaNet states, conv histories and K/V rows that each sequence's
     window of four rows gives alone, and cutting every lane back to its own accepted prefix gives the states the
-    one-sequence rollback gives."""
+    one-sequence rollback gives.  qsa_top = 4: the attention layers select blocks (every row sees 10 to 26 of them); each
+    lane's raw-key ring and pooled keys come out as alone too."""
     import torch
 
     from sfnx_b200 import lib as L
@@ -349,7 +351,7 @@ def test_window_of_several_sequences_equals_each_alone(monkeypatch):
 
     monkeypatch.setenv("FNX_ATTN_EXACT", "1")   # the one-sequence windows in the order of sums the lanes' scan uses
     shape = StackShape(n=512, nexp=32, topk=4, ff=256, nkh=2, nvh=4, nq=4, nkv=2, hd=128, nrot=64, vocab=2048, kinds=(0, 1, 0, 1), ctx=300,
-                       kv_slack=256)
+                       kv_slack=256, qsa_top=qsa_top)
     stack = SyntheticStack(shape, seed=11, device="cuda:0", gdn_log=False)   # lanes keep checkpoints
     nseg, rows = 3, 4
     lanes = LaneSet(stack, nseg, rows)
@@ -360,6 +362,9 @@ def test_window_of_several_sequences_equals_each_alone(monkeypatch):
     pool = {l: (stack.named[(l, "kc")], stack.named[(l, "vc")]) for l in att}
     state0 = {(l, i): (lanes.S[l][i].clone(), lanes.hist[l][i].clone()) for l in gdn for i in range(nseg)}
     pool0 = {l: (k.clone(), v.clone()) for l, (k, v) in pool.items()}
+    idx = {l: [stack.named[(l, "idx_pooled")]] + lanes.rings[l] for l in att} if qsa_top else {}   # the pooled keys' pool, the lanes' rings
+    idx0 = {l: [x.clone() for x in ts] for l, ts in idx.items()}
+    keys_a_lane = lanes.region // lanes.rpp * lanes.bpp * 128 * 2   # bytes of a lane's run of the pooled keys' pool
 
     def restore():
         for (l, i), (S, h) in state0.items():
@@ -368,6 +373,9 @@ def test_window_of_several_sequences_equals_each_alone(monkeypatch):
         for l, (k, v) in pool0.items():
             pool[l][0].copy_(k)
             pool[l][1].copy_(v)
+        for l, ts in idx0.items():
+            for x, x0 in zip(idx[l], ts):
+                x.copy_(x0)
         torch.cuda.synchronize()
 
     rng = np.random.default_rng(12)
@@ -385,6 +393,9 @@ def test_window_of_several_sequences_equals_each_alone(monkeypatch):
             stack.layers[l].kc = pool[l][0].data_ptr() + i * lanes.region * row_bytes
             stack.layers[l].vc = pool[l][1].data_ptr() + i * lanes.region * row_bytes
             stack.layers[l].pages = L.KvPages(None, 0, 0, lanes.region)
+            if qsa_top:
+                stack.layers[l].idx.ring = lanes.rings[l][i].data_ptr()
+                stack.layers[l].idx.pooled = idx[l][0].data_ptr() + i * keys_a_lane
         best = alone.window(ids[i], pos[i], tags[i])
         logits = alone.logits.clone()
         full = {l: (lanes.S[l][i].clone(), lanes.hist[l][i].clone()) for l in gdn}
@@ -393,10 +404,13 @@ def test_window_of_several_sequences_equals_each_alone(monkeypatch):
         cut = {l: (lanes.S[l][i].clone(), lanes.hist[l][i].clone()) for l in gdn}
         want.append((best, logits, full, cut))
     pool_alone = {l: (k.clone(), v.clone()) for l, (k, v) in pool.items()}
+    idx_alone = {l: [x.clone() for x in ts] for l, ts in idx.items()}
     # ---- the three together
     restore()
     for l in att:
         stack.layers[l].kc, stack.layers[l].vc = pool[l][0].data_ptr(), pool[l][1].data_ptr()
+        if qsa_top:
+            stack.layers[l].idx.pooled = idx[l][0].data_ptr()
     lanes.set_paged(True)
     best = batched.window_lanes([t for lane in ids for t in lane], pos, tags)
     logits = batched.logits.clone()
@@ -407,6 +421,8 @@ def test_window_of_several_sequences_equals_each_alone(monkeypatch):
             assert torch.equal(lanes.S[l][i], want[i][2][l][0]) and torch.equal(lanes.hist[l][i], want[i][2][l][1]), (i, l)
     for l in att:
         assert torch.equal(pool[l][0], pool_alone[l][0]) and torch.equal(pool[l][1], pool_alone[l][1]), "appended K/V rows"
+        for x, xa in zip(idx.get(l, []), idx_alone.get(l, [])):
+            assert torch.equal(x, xa), "pooled keys and raw-key rings"
     batched.commit_lanes(keep, tags)
     for i in range(nseg):
         for l in gdn:
