@@ -381,3 +381,47 @@ def test_block_selection_against_float64(oracle):
     cells[:] = np.arange(max(own))
     part = O.attn_partial_cells(ref["qg"], ref["kc"][1], ref["vc"][1], 1, 2, 300, 8, 2, cells, np.array(own, np.int32), 128)
     assert np.array_equal(part.view(np.uint32), ref["part"][1].view(np.uint32))
+
+
+def test_block_selection_edges(oracle):
+    """Edges of the selection: exactly `top` visible blocks is still dense and one more selects; a window that starts inside
+    a block pools it from the ring's earlier rows and its own; every GPU's cells together are the selection, each block once;
+    equal scores keep the lower blocks."""
+    from tests import cases
+
+    O = oracle
+    top = 8
+    c = cases.qsa_case(8, 4 * top - 4, 256, top, seed=5)          # rows at positions 28 .. 35: 7, 7, 7, 8, 8, 8, 8, 9 visible blocks
+    r = cases.qsa_oracle(c)
+    assert list(r["n_cells"][:7]) == [-1] * 7 and r["n_cells"][7] == 4 * top   # position 35 completes block 8: nine visible, no tail
+    # pooling across the window's start: position 30 and 31 in the window, 28 and 29 from the ring
+    c = cases.qsa_case(4, 30, 256, top, seed=6)
+    r = cases.qsa_oracle(c)
+    y = r["y"][:, 512:]
+    raw = [c["ring"][28 % 64].view(np.float16).astype(np.float32), c["ring"][29 % 64].view(np.float16).astype(np.float32),
+           y[0].astype(np.float16).astype(np.float32), y[1].astype(np.float16).astype(np.float32)]
+    mean = (((raw[0] + raw[1]) + raw[2]) + raw[3]) * np.float32(0.25)
+    got = r["pooled"][7].view(np.float16).astype(np.float64)
+    want = mean.astype(np.float64) / np.sqrt((mean.astype(np.float64) ** 2).mean() + 1e-6) * c["kn"]
+    assert np.allclose(np.linalg.norm(got), np.linalg.norm(want), rtol=2e-3)          # the rotation keeps the length
+    assert np.allclose(got[64:], want[64:], rtol=2e-3, atol=2e-3)                      # dimensions past the rotary are the normed mean
+    # the GPUs' cells together
+    c = cases.qsa_case(6, 801, 256, top, seed=7, ties=True)
+    parts = [cases.qsa_oracle(c, card, 4) for card in range(4)]
+    for t in range(6):
+        p = 801 + t
+        nv = (p + 1) // 4
+        blocks = []
+        for card, r in enumerate(parts):
+            cells = r["cells"][t, :r["n_cells"][t]]
+            full = cells[:len(cells) // 4 * 4].reshape(-1, 4) if (p // 4) % 4 != card else cells[:len(cells) - (p + 1) % 4].reshape(-1, 4)
+            assert (full == full[:, :1] + np.arange(4)).all()
+            blocks += [int(b) // 4 * 4 + card for b in full[:, 0]]                    # local block -> global block
+        s = parts[0]["scores"][t, :nv]
+        assert len(blocks) == top and len(set(blocks)) == top
+        thr = np.sort(s)[::-1][top - 1]
+        kept = sorted(blocks)
+        assert all(s[b] >= thr for b in kept)
+        ties = [b for b in range(nv) if s[b] == thr]
+        kept_ties = [b for b in kept if s[b] == thr]
+        assert kept_ties == ties[:len(kept_ties)]                                       # the lower blocks among equals
