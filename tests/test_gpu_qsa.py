@@ -62,6 +62,8 @@ def _same(got, ref, c):
     (5, 4001, 256, 64, 4, 2, True),       # ties decide; four GPUs' split
     (16, 20470, 256, 512, 8, 3, False),   # the reference's top of 512 blocks over 5 000: tiles of 1024 scores
     (1, 2, 256, 8, 1, 0, False),          # nothing to select, no block completed
+    (16, 70000, 256, 512, 2, 1, False),   # 17 500 blocks: three tiles of 1024 scores a block of the selection's cluster
+    (4, 70001, 256, 512, 1, 0, True),     # the same with ties: equal scores counted across tiles and across the cluster's blocks
 ])
 def test_qsa_bit_exact(T, pos0, n, top, ncard, card, ties):
     c = cases.qsa_case(T, pos0, n, top, seed=T + pos0, ties=ties)
