@@ -12,6 +12,10 @@
  * lanes joined by the descending xor-tree; a score's chain over the key's dimensions in pairs, odd first; the heads
  * added in order.  A row at position p sees the blocks [0, (p + 1) / 4); with `top` or fewer of them every block is kept
  * and the row is marked dense (n_cells = -1).
+ *
+ * Parity unpinned: the reference's tests hold no vectors for the indexer (it is exercised only through whole-model
+ * logits) and its kernels were not run against this file; what pins it is the float64 restatement and the selection's
+ * definition (tests/test_oracle_path.py).
  */
 #include "oracle.h"
 
